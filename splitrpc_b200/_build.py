@@ -1,0 +1,123 @@
+"""In-tree build of the native library ``splitrpc_b200/_C*.so``.
+
+One shared object holds the C++ host core, every CUDA kernel (compiled for
+sm_100a only) and the pybind11 bindings.  Objects are cached under
+``splitrpc_b200/build/`` keyed by a hash of the source, its headers and the
+flags, so a rebuild only recompiles what changed.  ``nvcc`` cross-compiles
+without a GPU; the CUDA runtime is linked statically and driver entry points are
+resolved at run time, so the library imports on a machine without a driver.
+"""
+from __future__ import annotations
+
+import hashlib
+import os
+import shutil
+import subprocess
+import sys
+import sysconfig
+from concurrent.futures import ThreadPoolExecutor
+from pathlib import Path
+
+PKG = Path(__file__).resolve().parent
+CSRC = PKG / "csrc"
+BUILD = PKG / "build"
+EXT_SUFFIX = sysconfig.get_config_var("EXT_SUFFIX") or ".so"
+TARGET = PKG / f"_C{EXT_SUFFIX}"
+
+GENCODE = ["-gencode", "arch=compute_100a,code=sm_100a"]
+NVCC_FLAGS = GENCODE + [
+    "-lineinfo", "-O3", "-std=c++17", "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC,-O3,-Wall,-Wno-unused-function",
+    "-Xcudafe", "--diag_suppress=177",
+]
+CXX_FLAGS = ["-O3", "-std=c++17", "-fPIC", "-Wall", "-Wno-unused-function", "-fvisibility=hidden", "-pthread"]
+
+
+def _nvcc() -> str:
+    for cand in (os.environ.get("NVCC"), shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
+        if cand and Path(cand).exists():
+            return cand
+    raise RuntimeError("nvcc not found; the native library cannot be built")
+
+
+def _includes() -> list[str]:
+    import pybind11
+
+    cuda_home = Path(_nvcc()).resolve().parent.parent
+    return [f"-I{CSRC}", f"-I{pybind11.get_include()}", f"-I{sysconfig.get_paths()['include']}", f"-I{cuda_home}/include"]
+
+
+def sources() -> list[Path]:
+    out = sorted(CSRC.glob("*.cpp")) + sorted((CSRC / "cuda").glob("*.cu"))
+    return out
+
+
+def _headers_digest() -> str:
+    h = hashlib.sha256()
+    for p in sorted(list(CSRC.rglob("*.h")) + list(CSRC.rglob("*.cuh"))):
+        h.update(p.name.encode())
+        h.update(p.read_bytes())
+    return h.hexdigest()
+
+
+def _obj_for(src: Path, hdr_digest: str, verbose_ptxas: bool) -> tuple[Path, list[str]]:
+    is_cu = src.suffix == ".cu"
+    flags = (NVCC_FLAGS + (["-Xptxas", "-v"] if verbose_ptxas else [])) if is_cu else CXX_FLAGS
+    key = hashlib.sha256((src.read_text() + hdr_digest + " ".join(flags)).encode()).hexdigest()[:16]
+    obj = BUILD / f"{src.stem}.{key}.o"
+    if is_cu:
+        cmd = [_nvcc(), "-c", str(src), "-o", str(obj)] + flags + _includes()
+    else:
+        cmd = [os.environ.get("CXX", "g++"), "-c", str(src), "-o", str(obj)] + flags + _includes()
+    return obj, cmd
+
+
+def build(force: bool = False, verbose: bool = False, verbose_ptxas: bool = False) -> Path:
+    """Compiles what changed and links ``_C``; returns the path of the library."""
+    BUILD.mkdir(exist_ok=True)
+    hdr = _headers_digest()
+    jobs = [_obj_for(s, hdr, verbose_ptxas) for s in sources()]
+    todo = [(o, c) for o, c in jobs if force or not o.exists()]
+
+    def run(job):
+        obj, cmd = job
+        if verbose:
+            print(" ".join(cmd), flush=True)
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError(f"compile failed: {' '.join(cmd)}\n{r.stdout}\n{r.stderr}")
+        if (verbose or verbose_ptxas) and (r.stdout or r.stderr):
+            print(r.stdout + r.stderr, flush=True)
+        return obj
+
+    if todo:
+        with ThreadPoolExecutor(max_workers=min(8, len(todo))) as ex:
+            list(ex.map(run, todo))
+    objs = [o for o, _ in jobs]
+    stamp = BUILD / "link.stamp"
+    link_key = hashlib.sha256(" ".join(str(o) for o in objs).encode()).hexdigest()
+    if force or todo or not TARGET.exists() or not stamp.exists() or stamp.read_text() != link_key:
+        cmd = [_nvcc(), "-shared", "-o", str(TARGET)] + [str(o) for o in objs] + GENCODE + ["-cudart", "static", "-lpthread", "-ldl", "-lrt"]
+        if verbose:
+            print(" ".join(cmd), flush=True)
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError(f"link failed: {' '.join(cmd)}\n{r.stdout}\n{r.stderr}")
+        stamp.write_text(link_key)
+        # drop objects of older source versions
+        keep = {o.name for o in objs}
+        for p in BUILD.glob("*.o"):
+            if p.name not in keep:
+                p.unlink()
+    return TARGET
+
+
+def up_to_date() -> bool:
+    if not TARGET.exists():
+        return False
+    hdr = _headers_digest()
+    return all(_obj_for(s, hdr, False)[0].exists() for s in sources())
+
+
+if __name__ == "__main__":
+    t = build(force="--force" in sys.argv, verbose="-v" in sys.argv, verbose_ptxas="--ptxas" in sys.argv)
+    print(t)

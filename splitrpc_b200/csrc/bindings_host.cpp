@@ -1,0 +1,635 @@
+// Python bindings of the host core: wire format, pools, transports, server,
+// load generator, CPU/GPU apps and the local (no network) benchmark.
+#include <pybind11/functional.h>
+#include <pybind11/numpy.h>
+#include <pybind11/pybind11.h>
+#include <pybind11/stl.h>
+
+#include "cuda/apps_gpu.h"
+#include "host/apps_cpu.h"
+#include "host/loadgen.h"
+#include "host/splitrpc_server.h"
+
+namespace py = pybind11;
+
+void bind_ops(py::module_& m);  // bindings_ops.cpp
+
+namespace {
+
+py::bytes hdr_bytes(const p2p_rpc_hdr& h) { return py::bytes(reinterpret_cast<const char*>(&h), RPC_HEADER_LEN); }
+
+p2p_rpc_hdr hdr_from(const std::string& b) {
+  if (b.size() != RPC_HEADER_LEN) throw std::invalid_argument("header must be 64 bytes");
+  p2p_rpc_hdr h;
+  std::memcpy(&h, b.data(), RPC_HEADER_LEN);
+  return h;
+}
+
+py::dict parse_header(const std::string& b) {
+  p2p_rpc_hdr h = hdr_from(b);
+  py::dict d;
+  d["dst_mac"] = mac_to_string(get_eth_header(&h)->dst_mac_);
+  d["src_mac"] = mac_to_string(get_eth_header(&h)->src_mac_);
+  d["eth_type"] = ntohs(get_eth_header(&h)->eth_type_);
+  d["src_ip"] = ipv4_to_string(get_ip_header(&h)->src_ip);
+  d["dst_ip"] = ipv4_to_string(get_ip_header(&h)->dst_ip);
+  d["ip_tot_len"] = ntohs(get_ip_header(&h)->tot_len);
+  d["ip_proto"] = get_ip_header(&h)->protocol;
+  d["src_port"] = ntohs(get_udp_header(&h)->src_port);
+  d["dst_port"] = ntohs(get_udp_header(&h)->dst_port);
+  d["udp_len"] = ntohs(get_udp_header(&h)->len);
+  d["udp_check"] = (uint16_t)get_udp_header(&h)->check;
+  d["req_token"] = (uint64_t)h.req_token;
+  d["sock_perf_header"] = (int64_t)h.sock_perf_header;
+  d["seq_num"] = (uint16_t)h.seq_num;
+  return d;
+}
+
+// A transport port plus whatever owns it.
+struct PortHolder {
+  Transport* port = nullptr;
+  std::shared_ptr<void> owner;
+};
+
+struct LoopbackPair {
+  std::shared_ptr<LoopbackPort> server, client;
+  std::string server_mem;
+};
+
+ArenaMem make_arena(const std::string& kind, size_t bytes) {
+  if (kind == "malloc") return make_malloc_arena(bytes);
+  if (kind == "pinned") {
+    const SrpcDeviceOps* ops = srpc_cuda_ops();
+    void *h = nullptr, *d = nullptr;
+    if (!ops || ops->host_alloc_mapped(bytes, &h, &d) != 0)
+      throw std::runtime_error("pinned arena needs a working CUDA device");
+    ArenaMem m;
+    m.host = (uint8_t*)h;
+    m.dev = (uint8_t*)d;
+    m.bytes = bytes;
+    m.release = [ops, h] { ops->host_free(h); };
+    return m;
+  }
+  throw std::invalid_argument("arena kind must be 'malloc' or 'pinned'");
+}
+
+// ---- apps
+struct PyAppState {
+  py::function run;
+  size_t req_size, resp_size;
+};
+
+int py_app_run(AppCtx* c) {
+  PyAppState* s = static_cast<PyAppState*>(c->app_ctx_internal);
+  py::gil_scoped_acquire gil;
+  try {
+    s->run((uintptr_t)c->h_stub->req, (uintptr_t)c->h_stub->resp, c->curr_batch_size, (uintptr_t)c->work_stream,
+           (uintptr_t)c->d_stub);
+  } catch (py::error_already_set& e) {
+    srpc_log(SRPC_LOG_ERROR, "python app raised: %s", e.what());
+    return 0;
+  }
+  return 1;
+}
+int py_app_cleanup(AppCtx* c) {
+  PyAppState* s = static_cast<PyAppState*>(c->app_ctx_internal);
+  py::gil_scoped_acquire gil;
+  delete s;
+  c->app_ctx_internal = nullptr;
+  return 1;
+}
+int cpu_app_cleanup(AppCtx* c) {
+  delete cpu_state(c);
+  c->app_ctx_internal = nullptr;
+  return 1;
+}
+
+struct AppHolder {
+  std::unique_ptr<P2pRpcAppInfo> info;
+  std::unique_ptr<P2pRpcSgEngine> engine;
+  std::string name;
+};
+
+std::vector<std::vector<float>> to_weights(const std::vector<py::array_t<float, py::array::c_style | py::array::forcecast>>& ws) {
+  std::vector<std::vector<float>> out;
+  for (auto& a : ws) out.emplace_back(a.data(), a.data() + a.size());
+  return out;
+}
+
+std::unique_ptr<P2pRpcSgEngine> make_engine(const std::string& kind, int device, int copy_type) {
+  if (kind == "zc") return std::make_unique<P2pRpcSgZcEngine>();
+  if (kind == "cpu") return std::make_unique<P2pRpcSgCpuEngine>();
+  if (kind == "gpu") {
+    P2pRpcSgEngine* e = srpc_make_gpu_sg_engine(device, copy_type);
+    if (!e) throw std::runtime_error("GPU scatter-gather engine needs a CUDA device");
+    return std::unique_ptr<P2pRpcSgEngine>(e);
+  }
+  throw std::invalid_argument("engine must be 'zc', 'cpu' or 'gpu'");
+}
+
+std::shared_ptr<AppHolder> make_app(const std::string& name, int device, size_t req_size, size_t resp_size,
+                                    const std::vector<py::array_t<float, py::array::c_style | py::array::forcecast>>& weights,
+                                    int pool_size, int launch_type, int batch, const std::string& engine, int copy_type) {
+  auto h = std::make_shared<AppHolder>();
+  h->name = name;
+  auto w = to_weights(weights);
+  if (device < 0) {
+    auto* s = new CpuAppState;
+    s->req_size = req_size;
+    s->resp_size = resp_size;
+    s->weights = std::move(w);
+    AppRunCB run = nullptr;
+    if (name == "echo") run = cpu_echo_run;
+    else if (name == "vec_add") run = cpu_vec_add_run;
+    else if (name == "matmul") run = cpu_mm_run;
+    else if (name == "lenet5") run = cpu_lenet5_run;
+    else if (name == "lenet_ref") run = cpu_lenet_ref_run;
+    else if (name == "lstm") run = cpu_lstm_run;
+    if (!run) {
+      delete s;
+      throw std::invalid_argument("unknown CPU app '" + name + "'");
+    }
+    h->info.reset(new P2pRpcAppInfo(cpu_app_noop, run, cpu_app_cleanup, cpu_app_noop, -1, req_size, resp_size, pool_size,
+                                    s, launch_type, batch));
+  } else {
+    GpuAppHandle g = srpc_make_gpu_app(name.c_str(), device, req_size, resp_size, w);
+    if (!g.run) throw std::runtime_error("GPU app '" + name + "' unavailable (unknown name or no CUDA device)");
+    h->info.reset(new P2pRpcAppInfo(g.init, g.run, g.cleanup, g.complete, device, req_size, resp_size, pool_size,
+                                    g.internal, launch_type, batch));
+  }
+  h->engine = make_engine(engine.empty() ? (device < 0 ? "cpu" : "gpu") : engine, device, copy_type);
+  return h;
+}
+
+std::shared_ptr<AppHolder> make_python_app(py::function run, int device, size_t req_size, size_t resp_size, int pool_size,
+                                           int launch_type, int batch, const std::string& engine, int copy_type) {
+  auto h = std::make_shared<AppHolder>();
+  h->name = "python";
+  auto* s = new PyAppState{std::move(run), req_size, resp_size};
+  h->info.reset(new P2pRpcAppInfo(cpu_app_noop, py_app_run, py_app_cleanup, cpu_app_noop, device, req_size, resp_size,
+                                  pool_size, s, launch_type, batch));
+  h->engine = make_engine(engine.empty() ? (device < 0 ? "cpu" : "gpu") : engine, device, copy_type);
+  return h;
+}
+
+// Members are destroyed in reverse order: the server (and its threads) goes
+// first, then the apps it was running, then the port.
+struct ServerHolder {
+  PortHolder port;
+  std::vector<std::shared_ptr<AppHolder>> apps;
+  std::unique_ptr<SplitRpcServer> server;
+};
+
+struct ClientHolder {
+  PortHolder port;
+  std::unique_ptr<P2pRpcAppClient> client;
+};
+
+app_req_cb req_cb_by_name(const std::string& k) {
+  if (k == "echo") return echo_fill;
+  if (k == "vec_add") return vec_add_fill;
+  if (k == "const5") return const_float_fill;
+  if (k == "uniform") return uniform_float_fill;
+  throw std::invalid_argument("payload kind must be echo, vec_add, const5 or uniform");
+}
+app_resp_cb resp_cb_by_name(const std::string& k) {
+  if (k == "echo") return echo_check;
+  if (k == "vec_add") return vec_add_check;
+  return nullptr;
+}
+
+}  // namespace
+
+PYBIND11_MODULE(_C, m) {
+  m.doc() = "splitrpc_b200 native core";
+  m.attr("RPC_HEADER_LEN") = (int)RPC_HEADER_LEN;
+  m.attr("UDP_HEADER_LEN") = (int)UDP_HEADER_LEN;
+  m.attr("RPC_HEADER_TAIL_LEN") = (int)RPC_HEADER_TAIL_LEN;
+  m.attr("MAX_BI_SIZE") = (int)MAX_BI_SIZE;
+  m.def("rpc_mtu", [] { return rpc_mtu(); });
+  m.def("set_rpc_mtu", [](size_t v) { set_rpc_mtu(v); });
+  m.def("set_log_level", [](int l) { srpc_set_log_level(l); });
+  m.def("read_env_int", [](const std::string& n, long d) { return readEnvInfo<long>(n.c_str(), d); });
+  m.def("cuda_available", [] {
+    const SrpcDeviceOps* o = srpc_cuda_ops();
+    return o && o->device_count() > 0;
+  });
+
+  // ---- wire
+  m.def("client_conn_template", [](const std::string& uri) {
+    p2p_rpc_conn_info* c = initialize_client_conn_info(uri);
+    if (!c) throw std::invalid_argument("bad client URI");
+    py::bytes b = hdr_bytes(c->hdr_template);
+    release_conn_info(c);
+    return b;
+  });
+  m.def("server_conn_template", [](const std::string& uri) {
+    p2p_rpc_conn_info* c = initialize_src_conn_info(uri);
+    if (!c) throw std::invalid_argument("bad server URI");
+    py::bytes b = hdr_bytes(c->hdr_template);
+    release_conn_info(c);
+    return b;
+  });
+  m.def("reply_template", [](const std::string& server_tmpl, const std::string& recv_hdr) {
+    p2p_rpc_conn_info c;
+    c.hdr_template = hdr_from(server_tmpl);
+    p2p_rpc_hdr r = hdr_from(recv_hdr);
+    set_conn_info(&c, &r);
+    return hdr_bytes(c.hdr_template);
+  });
+  m.def("parse_header", &parse_header);
+  m.def("build_fragments",
+        [](const std::string& tmpl, uint64_t token, const std::string& payload, size_t mtu, bool is_reply) {
+          p2p_rpc_conn_info c;
+          c.hdr_template = hdr_from(tmpl);
+          py::list out;
+          size_t n = num_fragments(payload.size(), mtu), left = payload.size();
+          for (size_t i = 0; i < n; i++) {
+            size_t len = left < mtu ? left : mtu;
+            p2p_rpc_hdr h;
+            fill_frag_hdr(&h, &c, token, (uint16_t)i, (uint16_t)len, is_reply);
+            out.append(py::make_tuple(hdr_bytes(h), py::bytes(payload.data() + i * mtu, len)));
+            left -= len;
+          }
+          return out;
+        },
+        py::arg("conn_template"), py::arg("token"), py::arg("payload"), py::arg("mtu"), py::arg("is_reply") = false);
+  m.def("swap_header", [](const std::string& b) {
+    p2p_rpc_hdr h = hdr_from(b);
+    swap_eth_hdr(&h);
+    add_udp_cksum(&h);
+    return hdr_bytes(h);
+  });
+  m.def("ipv4_pseudo_csum", [](const std::string& b) {
+    p2p_rpc_hdr h = hdr_from(b);
+    return ipv4_pseudo_csum(get_ip_header(&h));
+  });
+  m.def("ipv4_header_csum", [](const std::string& b) {
+    p2p_rpc_hdr h = hdr_from(b);
+    return ipv4_header_csum(get_ip_header(&h));
+  });
+  m.def("num_fragments", &num_fragments);
+
+  // ---- stats
+  m.def("percentile", [](std::vector<uint64_t> v, double p) { return getPercentile(v, p); });
+  m.def("mean", [](const std::vector<uint64_t>& v) { return getMean(v); });
+  m.def("format_stat", [](const std::string& k, const std::vector<uint64_t>& v) { return format_stat(k, v); });
+
+  // ---- tring
+  py::class_<P2pRpcTring>(m, "P2pRpcTring")
+      .def(py::init([](uintptr_t base, size_t cap) { return new P2pRpcTring((void*)base, cap); }))
+      .def("get_next", [](P2pRpcTring& t, size_t n) { return (uintptr_t)t.get_next(n); })
+      .def_property_readonly("offset", &P2pRpcTring::offset);
+
+  // ---- copy-list builders (addresses are plain integers)
+  m.def("gather_list", [](const std::vector<std::pair<uintptr_t, size_t>>& frags, uintptr_t dst) {
+    auto bufs = std::make_unique<p2p_bufs>();
+    auto skb = std::make_unique<p2p_sk_buf>();
+    bufs->num_items = (uint16_t)frags.size();
+    for (size_t i = 0; i < frags.size(); i++) {
+      bufs->burst_items[i] = frags[i].first;
+      bufs->item_size[i] = frags[i].second;
+    }
+    gather_skbs(skb.get(), bufs.get(), (uint8_t*)dst);
+    std::vector<std::tuple<uintptr_t, uintptr_t, size_t>> out;
+    for (size_t i = 0; i < skb->num_items; i++) out.emplace_back(skb->i_buf[i], skb->o_buf[i], skb->len[i]);
+    return out;
+  });
+  m.def("scatter_list", [](const std::vector<std::pair<uintptr_t, size_t>>& frags, uintptr_t src) {
+    auto bufs = std::make_unique<p2p_bufs>();
+    auto skb = std::make_unique<p2p_sk_buf>();
+    bufs->num_items = (uint16_t)frags.size();
+    for (size_t i = 0; i < frags.size(); i++) {
+      bufs->burst_items[i] = frags[i].first;
+      bufs->item_size[i] = frags[i].second;
+    }
+    scatter_skbs(skb.get(), bufs.get(), (uint8_t*)src);
+    std::vector<std::tuple<uintptr_t, uintptr_t, size_t>> out;
+    for (size_t i = 0; i < skb->num_items; i++) out.emplace_back(skb->i_buf[i], skb->o_buf[i], skb->len[i]);
+    return out;
+  });
+
+  // ---- reassembly harness: feeds (header, payload) pairs through the pool and the CPU engine
+  struct Reassembler {
+    P2pRpcRRPool pool;
+    P2pRpcSgCpuEngine eng;
+    std::vector<std::unique_ptr<std::string>> keep;
+    size_t req_size;
+    Reassembler(size_t req, int pool_size) : pool(pool_size), req_size(req) {
+      p2p_rpc_conn_info* c = initialize_src_conn_info("b8:ce:f6:cc:6a:52,192.168.25.1,50051");
+      pool.setup_and_init_rr_pool(c, req);
+      release_conn_info(c);
+    }
+  };
+  py::class_<Reassembler>(m, "Reassembler")
+      .def(py::init<size_t, int>(), py::arg("req_size"), py::arg("pool_size") = 64)
+      .def("feed",
+           [](Reassembler& r, const std::string& hdr, const std::string& payload) -> py::object {
+             p2p_rpc_hdr h = hdr_from(hdr);
+             r.keep.emplace_back(new std::string(payload));
+             const std::string& kept = *r.keep.back();
+             P2pRpcRr* rr = r.pool.append_to_rr(&h, 1, (uintptr_t)kept.data(), kept.size());
+             if (!rr) return py::none();
+             if (!rr->is_rr_ready()) return py::none();
+             r.pool.mark_rx_ready_rr(rr);
+             P2pRpcRr* ready = r.pool.get_next_rx_ready_rr();
+             std::string out(r.req_size, '\0');
+             g_params p{(uint8_t*)out.data(), nullptr};
+             r.eng.gather(ready, &p);
+             uint64_t tok = ready->req_token;
+             size_t runs = ready->payload_sk_bufs->num_items;
+             r.pool.reap_rr(ready);
+             return py::make_tuple(tok, py::bytes(out), runs);
+           })
+      .def("expire", [](Reassembler& r, uint64_t timeout_ns) { return r.pool.expire_stale(getCurNs(), timeout_ns, nullptr); })
+      .def_property_readonly("partial", [](Reassembler& r) { return r.pool.num_partial(); })
+      .def_property_readonly("counters", [](Reassembler& r) {
+        const RrPoolCounters& c = r.pool.counters();
+        py::dict d;
+        d["allocated"] = c.allocated;
+        d["grown"] = c.grown;
+        d["dropped_zero_token"] = c.dropped_zero_token;
+        d["dropped_bad_seq"] = c.dropped_bad_seq;
+        d["dropped_dup"] = c.dropped_dup;
+        d["expired"] = c.expired;
+        d["rx_ready"] = c.rx_ready;
+        d["reaped"] = c.reaped;
+        return d;
+      });
+
+  // ---- transports
+  py::class_<PortHolder>(m, "Port")
+      .def_property_readonly("name", [](PortHolder& p) { return std::string(p.port->name()); })
+      .def_property_readonly("counters", [](PortHolder& p) {
+        py::dict d;
+        TransportCounters& c = p.port->counters;
+        d["rx_pkts"] = c.rx_pkts.load();
+        d["tx_pkts"] = c.tx_pkts.load();
+        d["rx_bytes"] = c.rx_bytes.load();
+        d["tx_bytes"] = c.tx_bytes.load();
+        d["tx_dropped"] = c.tx_dropped.load();
+        d["arena_full"] = c.arena_full.load();
+        d["injected_faults"] = c.injected_faults.load();
+        return d;
+      });
+
+  m.def("make_loopback_pair",
+        [](size_t slot_bytes, size_t n_slots, const std::string& server_mem) {
+          auto srv = std::make_shared<LoopbackPort>(make_arena(server_mem, slot_bytes * n_slots),
+                                                    make_arena(server_mem, slot_bytes * n_slots), slot_bytes);
+          auto cli = std::make_shared<LoopbackPort>(make_malloc_arena(slot_bytes * n_slots),
+                                                    make_malloc_arena(slot_bytes * n_slots), slot_bytes);
+          LoopbackPort::connect(srv.get(), cli.get());
+          // Each port keeps the other alive, since it delivers into its arenas.
+          auto both = std::make_shared<std::pair<std::shared_ptr<LoopbackPort>, std::shared_ptr<LoopbackPort>>>(srv, cli);
+          PortHolder s{srv.get(), both}, c{cli.get(), both};
+          return py::make_tuple(s, c);
+        },
+        py::arg("slot_bytes"), py::arg("n_slots") = 4096, py::arg("server_mem") = "malloc");
+  m.def("set_loopback_faults",
+        [](PortHolder& p, double drop, double dup, double reorder, double truncate, bool zero_token, int force_seq,
+           uint64_t seed) {
+          auto* lp = dynamic_cast<LoopbackPort*>(p.port);
+          if (!lp) throw std::invalid_argument("not a loopback port");
+          LoopbackFaults f;
+          f.drop = drop;
+          f.duplicate = dup;
+          f.reorder = reorder;
+          f.truncate = truncate;
+          f.zero_token = zero_token;
+          f.force_seq = force_seq;
+          f.seed = seed;
+          lp->set_faults(f);
+        },
+        py::arg("port"), py::arg("drop") = 0.0, py::arg("duplicate") = 0.0, py::arg("reorder") = 0.0,
+        py::arg("truncate") = 0.0, py::arg("zero_token") = false, py::arg("force_seq") = -1, py::arg("seed") = 99);
+  m.def("make_udp_port",
+        [](const std::string& ip, int port, size_t slot_bytes, size_t n_slots, const std::string& dst_ip, int dst_port) {
+          auto u = std::make_shared<UdpPort>(ip.c_str(), port, slot_bytes, n_slots);
+          if (!u->ok()) throw std::runtime_error("UDP bind failed");
+          if (!dst_ip.empty()) u->set_destination(dst_ip.c_str(), dst_port);
+          return py::make_tuple(PortHolder{u.get(), u}, u->bound_port());
+        },
+        py::arg("ip"), py::arg("port"), py::arg("slot_bytes"), py::arg("n_slots") = 4096, py::arg("dst_ip") = "",
+        py::arg("dst_port") = 0);
+  m.def("dpdk_available", [] { return init_dpdk_ctx(dpdk_ctx{}) != nullptr; });
+
+  // ---- apps
+  py::class_<AppHolder, std::shared_ptr<AppHolder>>(m, "App")
+      .def_property_readonly("name", [](AppHolder& a) { return a.name; })
+      .def_property_readonly("init_ok", [](AppHolder& a) { return a.info->init_ok; })
+      .def_property_readonly("work_stream", [](AppHolder& a) { return (uintptr_t)a.info->app_ctx->work_stream; })
+      .def_property_readonly("d_stub", [](AppHolder& a) { return (uintptr_t)a.info->app_ctx->d_stub; })
+      .def_property_readonly("req_ring", [](AppHolder& a) {
+        auto* mp = a.info->app_rr_pool->rr_mem_pool;
+        return py::make_tuple((uintptr_t)mp->get_req_addr_range(), mp->get_req_addr_pool_size(), mp->is_double_mapped());
+      })
+      .def_property_readonly("resp_ring", [](AppHolder& a) {
+        auto* mp = a.info->app_rr_pool->rr_mem_pool;
+        return py::make_tuple((uintptr_t)mp->get_resp_addr_range(), mp->get_resp_addr_pool_size(), mp->is_double_mapped());
+      })
+      .def_property_readonly("sg_counters", [](AppHolder& a) {
+        py::dict d;
+        d["gathers"] = a.engine->counters.gathers;
+        d["scatters"] = a.engine->counters.scatters;
+        d["items"] = a.engine->counters.items;
+        d["bytes"] = a.engine->counters.bytes;
+        d["timeouts"] = a.engine->counters.timeouts;
+        d["engine"] = std::string(a.engine->name());
+        return d;
+      });
+  m.def("make_app", &make_app, py::arg("name"), py::arg("device") = -1, py::arg("req_size") = 1024,
+        py::arg("resp_size") = 1024, py::arg("weights") = std::vector<py::array_t<float>>{}, py::arg("pool_size") = 256,
+        py::arg("launch_type") = 1, py::arg("batch") = 1, py::arg("engine") = "", py::arg("copy_type") = 2);
+  m.def("make_python_app", &make_python_app, py::arg("run"), py::arg("device") = -1, py::arg("req_size") = 1024,
+        py::arg("resp_size") = 1024, py::arg("pool_size") = 256, py::arg("launch_type") = 1, py::arg("batch") = 1,
+        py::arg("engine") = "", py::arg("copy_type") = 2);
+
+  // Local benchmark without a network: fill slot windows, run do_batch_work_sync
+  // `iters` times, return the per-iteration host times in ns (reference
+  // src/local_bench/p2p_rpc_local_bench.cc:40-115).
+  m.def("local_bench",
+        [](std::shared_ptr<AppHolder> app, int iters, int batch, py::object fill) {
+          P2pRpcAsyncAppServer srv;
+          int idx = srv.register_app(app->info.get());
+          P2pRpcAppRrPool* pool = app->info->app_rr_pool;
+          pool->init_pool();
+          std::vector<uint64_t> ns;
+          py::list outs;
+          for (int it = 0; it < iters; it++) {
+            int first = -1;
+            for (int b = 0; b < batch; b++) {
+              P2pRpcAppRr* r = pool->get_next();
+              if (b == 0) first = r->rr_idx;
+              if (!fill.is_none()) fill((uintptr_t)r->h_stub->req, r->req_size, it * batch + b);
+            }
+            uint64_t t0;
+            bool ok;
+            {
+              py::gil_scoped_release rel;
+              t0 = getCurNs();
+              ok = srv.do_batch_work_sync(idx, first, batch);
+              ns.push_back(getCurNs() - t0);
+            }
+            if (!ok) throw std::runtime_error("local_bench: bounded wait ran out");
+            if (it == iters - 1) outs.append((uintptr_t)pool->get_app_rr(first)->h_stub->resp);
+          }
+          return py::make_tuple(ns, outs);
+        },
+        py::arg("app"), py::arg("iters"), py::arg("batch") = 1, py::arg("fill") = py::none());
+
+  // ---- server
+  py::class_<ServerHolder, std::shared_ptr<ServerHolder>>(m, "Server")
+      .def(py::init([](PortHolder port, const std::string& uri, size_t req_size, size_t resp_size, int server_mode,
+                       int max_batch, int zerocopy, int rr_pool_size, uint64_t reassembly_timeout_ns, int steer_policy,
+                       int gather_burst) {
+             auto h = std::make_shared<ServerHolder>();
+             ServerConfig c;
+             if (!uri.empty()) c.server_uri = uri;
+             c.req_size = req_size;
+             c.resp_size = resp_size;
+             c.server_mode = server_mode;
+             c.max_batch = max_batch;
+             c.zerocopy = zerocopy;
+             c.rr_pool_size = rr_pool_size;
+             c.reassembly_timeout_ns = reassembly_timeout_ns;
+             c.steer_policy = steer_policy;
+             c.gather_burst = gather_burst;
+             h->port = port;
+             h->server.reset(new SplitRpcServer(port.port, c));
+             return h;
+           }),
+           py::arg("port"), py::arg("uri") = "", py::arg("req_size") = 1024, py::arg("resp_size") = 1024,
+           py::arg("server_mode") = 2, py::arg("max_batch") = 1, py::arg("zerocopy") = 0, py::arg("rr_pool_size") = 1023,
+           py::arg("reassembly_timeout_ns") = 200000000ull, py::arg("steer_policy") = 0, py::arg("gather_burst") = 64)
+      .def("add_replica",
+           [](ServerHolder& s, std::shared_ptr<AppHolder> app) {
+             s.apps.push_back(app);
+             return s.server->add_replica(app->info.get(), app->engine.get());
+           })
+      .def("start", [](ServerHolder& s) { s.server->start(); })
+      .def("stop", [](ServerHolder& s) {
+        py::gil_scoped_release rel;
+        s.server->stop();
+      })
+      .def("mark_replica_down", [](ServerHolder& s, int i, bool d) { s.server->mark_replica_down(i, d); })
+      .def("stats",
+           [](ServerHolder& s) {
+             ServerStats st = s.server->stats();
+             py::dict d;
+             d["rx_pkts"] = st.rx_pkts;
+             d["rx_reqs"] = st.rx_reqs;
+             d["tx_resps"] = st.tx_resps;
+             d["tx_pkts"] = st.tx_pkts;
+             d["dropped_pkts"] = st.dropped_pkts;
+             d["expired"] = st.expired;
+             d["ring_full"] = st.ring_full;
+             d["tx_alloc_fail"] = st.tx_alloc_fail;
+             d["sg_errors"] = st.sg_errors;
+             py::list reps;
+             for (auto& r : st.replicas) {
+               py::dict rd;
+               rd["steered"] = r.steered;
+               rd["completed"] = r.completed;
+               rd["ring_full"] = r.ring_full;
+               reps.append(rd);
+             }
+             d["replicas"] = reps;
+             return d;
+           })
+      .def("worker_stats", [](ServerHolder& s, int replica) {
+        WorkerStats w = s.server->worker_stats(replica);
+        py::dict d;
+        d["num_req"] = w.num_req;
+        d["num_batches"] = w.num_batches;
+        d["wait_timeouts"] = w.wait_timeouts;
+        d["batch_hist"] = w.batch_hist;
+        d["work_ns"] = w.work_ns;
+        return d;
+      });
+
+  // ---- client / load generator
+  py::class_<ClientHolder, std::shared_ptr<ClientHolder>>(m, "Client")
+      .def(py::init([](PortHolder port, size_t req_size, size_t resp_size, uint64_t total, uint64_t warmup,
+                       const std::string& payload, bool verify, const std::string& exp_name, const std::string& out_dir,
+                       const std::string& uri, int n_payloads, uint64_t seed, uint64_t drain_timeout_ns) {
+             auto h = std::make_shared<ClientHolder>();
+             ClientConfig c;
+             c.req_size = req_size;
+             c.resp_size = resp_size;
+             c.total_requests = total;
+             c.num_warmup = warmup;
+             c.verify = verify;
+             c.exp_name = exp_name;
+             c.out_dir = out_dir;
+             if (!uri.empty()) c.client_uri = uri;
+             c.n_payloads = n_payloads;
+             c.seed = seed;
+             c.drain_timeout_ns = drain_timeout_ns;
+             h->port = port;
+             h->client.reset(new P2pRpcAppClient(port.port, c, req_cb_by_name(payload), resp_cb_by_name(payload)));
+             h->client->PreProcessRequests();
+             return h;
+           }),
+           py::arg("port"), py::arg("req_size") = 1024, py::arg("resp_size") = 1024, py::arg("total") = 100,
+           py::arg("warmup") = 10, py::arg("payload") = "echo", py::arg("verify") = false,
+           py::arg("exp_name") = "splitrpc", py::arg("out_dir") = ".", py::arg("uri") = "", py::arg("n_payloads") = 16,
+           py::arg("seed") = 12345, py::arg("drain_timeout_ns") = 10000000000ull)
+      .def("run_closed_loop",
+           [](ClientHolder& c, int outstanding) {
+             py::gil_scoped_release rel;
+             return c.client->run_closed_loop(outstanding);
+           })
+      .def("run_open_loop",
+           [](ClientHolder& c, double rate, int cov, int threads) {
+             py::gil_scoped_release rel;
+             return c.client->run_open_loop(rate, cov, threads);
+           },
+           py::arg("rate"), py::arg("cov") = 1, py::arg("threads") = 1)
+      .def("post_process", [](ClientHolder& c) { return c.client->PostProcessResponses(); })
+      .def("save_stats", [](ClientHolder& c, bool raw) { return c.client->stats().saveStats({"sojournTime"}, raw); },
+           py::arg("dump_raw") = false)
+      .def("stats_json", [](ClientHolder& c) { return c.client->stats().to_json(); })
+      .def("sojourn_ns", [](ClientHolder& c) { return c.client->stats().samples("sojournTime"); })
+      .def("payload", [](ClientHolder& c, int i) {
+        const auto& p = c.client->payload(i);
+        return py::bytes((const char*)p.data(), p.size());
+      })
+      .def("response", [](ClientHolder& c, uint64_t i) {
+        const auto& p = c.client->response(i);
+        return py::bytes((const char*)p.data(), p.size());
+      })
+      .def_property_readonly("sent", [](ClientHolder& c) { return c.client->sent(); })
+      .def_property_readonly("received", [](ClientHolder& c) { return c.client->received(); })
+      .def_property_readonly("verify_failures", [](ClientHolder& c) { return c.client->verify_failures(); })
+      .def_property_readonly("bad_tokens", [](ClientHolder& c) { return c.client->bad_tokens(); });
+
+  // ---- arrival processes
+  m.def("arrival_schedule", [](double rate, int cov, uint64_t n, uint64_t seed) {
+    LoadGenerator lg(1.0 / rate, cov, seed);
+    std::vector<uint64_t> t(n);
+    uint64_t cur = 0;
+    for (auto& x : t) x = cur = lg.nextReqArr(cur, false);
+    return t;
+  });
+
+  // ---- CPU oracles callable on numpy arrays
+  m.def("cpu_lenet5", [](const std::vector<py::array_t<float, py::array::c_style | py::array::forcecast>>& weights,
+                         py::array_t<float, py::array::c_style | py::array::forcecast> x) {
+    CpuAppState s;
+    s.weights = to_weights(weights);
+    ssize_t n = x.size() / 784;
+    py::array_t<float> out({n, (ssize_t)10});
+    for (ssize_t i = 0; i < n; i++) cpu_lenet5_one(&s, x.data() + i * 784, out.mutable_data() + i * 10);
+    return out;
+  });
+  m.def("cpu_lstm", [](const std::vector<py::array_t<float, py::array::c_style | py::array::forcecast>>& weights,
+                       py::array_t<float, py::array::c_style | py::array::forcecast> x, int layers, int steps, int H) {
+    auto w = to_weights(weights);
+    py::array_t<float> out((ssize_t)H);
+    cpu_lstm_forward(w, layers, steps, H, 0.0f, x.data(), out.mutable_data());
+    return out;
+  });
+
+  bind_ops(m);
+}

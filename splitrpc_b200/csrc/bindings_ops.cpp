@@ -1,0 +1,85 @@
+// Python bindings of the CUDA kernels.  Tensors cross this boundary as raw device
+// addresses (int) plus shapes; the Python layer owns allocation through PyTorch.
+#include <pybind11/pybind11.h>
+#include <pybind11/stl.h>
+
+#include <cuda_runtime.h>
+
+#include "cuda/gemm_tcgen05.h"
+#include "cuda/ops_api.h"
+
+namespace py = pybind11;
+
+static void check(cudaError_t e, const char* what) {
+  if (e != cudaSuccess) throw std::runtime_error(std::string(what) + ": " + cudaGetErrorString(e));
+}
+
+static GemmEpilogue make_ep(uintptr_t out, int ldo, bool out_fp32, uintptr_t bias, uintptr_t residual, int ldr, int act) {
+  GemmEpilogue ep;
+  ep.out = (void*)out;
+  ep.ldo = ldo;
+  ep.out_fp32 = out_fp32 ? 1 : 0;
+  ep.bias = (const float*)bias;
+  ep.residual = (const __nv_bfloat16*)residual;
+  ep.ldr = ldr;
+  ep.act = act;
+  return ep;
+}
+
+void bind_ops(py::module_& m) {
+  m.def("device_caps", [](int dev) {
+    int vmm = 0, memops = 0, gdr = 0, maj = 0, min = 0, nsm = 0;
+    py::dict d;
+    if (srpc_device_caps(dev, &vmm, &memops, &gdr, &maj, &min, &nsm) != 0) return d;
+    d["vmm"] = vmm;
+    d["stream_memops"] = memops;
+    d["gdr_with_vmm"] = gdr;
+    d["sm"] = maj * 10 + min;
+    d["num_sms"] = nsm;
+    return d;
+  });
+
+  // ---- scatter-gather
+  m.def("sg_copy",
+        [](const std::vector<SgTuple>& items, int impl, int n_blocks, uintptr_t stream) {
+          check(srpc_sg_copy_list(items, impl, n_blocks, (cudaStream_t)stream), "sg_copy");
+        },
+        py::arg("items"), py::arg("impl") = 0, py::arg("n_blocks") = 0, py::arg("stream") = 0);
+  m.def("sg_cast_bf16",
+        [](const std::vector<SgTuple>& items, float scale, float shift, int n_blocks, uintptr_t stream) {
+          check(srpc_sg_cast_list(items, scale, shift, n_blocks, (cudaStream_t)stream), "sg_cast_bf16");
+        },
+        py::arg("items"), py::arg("scale") = 1.0f, py::arg("shift") = 0.0f, py::arg("n_blocks") = 0, py::arg("stream") = 0);
+  m.def("sg_list_create", &srpc_sg_list_create);
+  m.def("sg_list_destroy", &srpc_sg_list_destroy);
+  m.def("sg_list_launch",
+        [](uintptr_t h, int impl, int n_blocks, uintptr_t stream) {
+          check(srpc_sg_list_launch(h, impl, n_blocks, (cudaStream_t)stream), "sg_list_launch");
+        },
+        py::arg("handle"), py::arg("impl") = 0, py::arg("n_blocks") = 0, py::arg("stream") = 0);
+
+  // ---- tensor-core GEMM / convolution
+  m.attr("ACT_NONE") = (int)GEMM_ACT_NONE;
+  m.attr("ACT_RELU") = (int)GEMM_ACT_RELU;
+  m.attr("ACT_GELU") = (int)GEMM_ACT_GELU;
+  m.def("gemm_bf16",
+        [](uintptr_t a, int lda, uintptr_t b, int ldb, int M, int N, int K, uintptr_t out, int ldo, bool out_fp32,
+           uintptr_t bias, uintptr_t residual, int ldr, int act, uintptr_t status, uintptr_t stream) {
+          GemmEpilogue ep = make_ep(out, ldo, out_fp32, bias, residual, ldr, act);
+          check(srpc_gemm_bf16((const void*)a, lda, (const void*)b, ldb, M, N, K, ep, (uint32_t*)status, (cudaStream_t)stream),
+                "gemm_bf16");
+        },
+        py::arg("a"), py::arg("lda"), py::arg("b"), py::arg("ldb"), py::arg("M"), py::arg("N"), py::arg("K"), py::arg("out"),
+        py::arg("ldo"), py::arg("out_fp32") = false, py::arg("bias") = 0, py::arg("residual") = 0, py::arg("ldr") = 0,
+        py::arg("act") = 0, py::arg("status") = 0, py::arg("stream") = 0);
+  m.def("conv_bf16",
+        [](uintptr_t in, uintptr_t w, int n, int h, int wd, int cin, int cout, int r, int s, int stride, int pad,
+           uintptr_t out, uintptr_t bias, uintptr_t residual, int act, uintptr_t status, uintptr_t stream) {
+          ConvShape cs{n, h, wd, cin, cout, r, s, stride, pad, (h + 2 * pad - r) / stride + 1, (wd + 2 * pad - s) / stride + 1};
+          GemmEpilogue ep = make_ep(out, cout, false, bias, residual, cout, act);
+          check(srpc_conv_bf16((const void*)in, (const void*)w, cs, ep, (uint32_t*)status, (cudaStream_t)stream), "conv_bf16");
+        },
+        py::arg("input"), py::arg("weight"), py::arg("n"), py::arg("h"), py::arg("w"), py::arg("cin"), py::arg("cout"),
+        py::arg("r"), py::arg("s"), py::arg("stride"), py::arg("pad"), py::arg("out"), py::arg("bias") = 0,
+        py::arg("residual") = 0, py::arg("act") = 0, py::arg("status") = 0, py::arg("stream") = 0);
+}

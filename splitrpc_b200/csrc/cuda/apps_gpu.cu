@@ -1,0 +1,400 @@
+// GPU apps behind the four-callback interface: echo, vec_add, matmul, LeNet-5.
+//
+// Each app dispatches on app_ctx->launch_type like the originals
+// (reference src/apps/lenet/lenet_vanilla.cuh:30-74):
+//   1  plain kernel launches on the work stream
+//   3  a resident kernel that waits on the app doorbell (value = batch size),
+//      runs one batch and writes 2 back; it leaves after an idle limit and the
+//      host re-arms it on the next run
+//   4  CUDA graph replay, one captured graph per batch size
+// (type 2, device-side launch with device-side synchronisation, does not exist
+// on this architecture and is rejected at init).  Kernels read the request and
+// response pointers through the device-visible stub, never from launch
+// arguments, so graphs and resident kernels follow the ring as it advances
+// (reference src/apps/vec_add/vector_add.cu:56-61).
+#include <cuda_runtime.h>
+
+#include <map>
+#include <string>
+#include <vector>
+
+#include "../host/apps_cpu.h"
+#include "../host/p2p_rpc_app.h"
+#include "apps_gpu.h"
+#include "ptx.cuh"
+
+namespace {
+
+struct GpuAppState {
+  std::string name;
+  size_t req_size = 0, resp_size = 0;
+  int dim = 0;
+  float* d_weights = nullptr;           // all parameters, concatenated
+  std::vector<size_t> w_off;            // float offsets of each tensor
+  std::map<int, cudaGraphExec_t> graphs;  // batch size -> graph
+  bool resident = false;
+  uint32_t* d_pt_status = nullptr;      // resident kernel: 0 running, 1 left
+  uint32_t* h_pt_status = nullptr;
+  uint64_t idle_ns = 200000000ull;
+};
+
+GpuAppState* st(AppCtx* c) { return static_cast<GpuAppState*>(c->app_ctx_internal); }
+
+// ------------------------------------------------------------------ kernels
+__global__ void echo_kernel(const g_params* stub, size_t req_size, size_t resp_size, int batch) {
+  const uint8_t* req = stub->req;
+  uint8_t* resp = stub->resp;
+  size_t n = req_size < resp_size ? req_size : resp_size;
+  bool vec = (((uintptr_t)req | (uintptr_t)resp | req_size | resp_size) & 15) == 0;
+  for (int b = blockIdx.y; b < batch; b += gridDim.y) {
+    const uint8_t* s = req + (size_t)b * req_size;
+    uint8_t* d = resp + (size_t)b * resp_size;
+    size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x, nth = (size_t)gridDim.x * blockDim.x;
+    if (vec) {
+      for (size_t i = tid; i < n / 16; i += nth) reinterpret_cast<uint4*>(d)[i] = reinterpret_cast<const uint4*>(s)[i];
+    } else {
+      for (size_t i = tid; i < n; i += nth) d[i] = s[i];
+    }
+  }
+}
+
+__device__ __forceinline__ uint32_t add1_bytes(uint32_t v) {
+  // per-byte +1 without carries between bytes
+  uint32_t low = (v & 0x7F7F7F7Fu) + 0x01010101u;
+  return low ^ (v & 0x80808080u);
+}
+
+__device__ __forceinline__ void vec_add_body(const uint8_t* req, uint8_t* resp, size_t req_size, size_t resp_size,
+                                             int batch, size_t tid, size_t nth, int b0, int bstride) {
+  size_t n = req_size < resp_size ? req_size : resp_size;
+  bool vec = (((uintptr_t)req | (uintptr_t)resp | req_size | resp_size) & 15) == 0;
+  for (int b = b0; b < batch; b += bstride) {
+    const uint8_t* s = req + (size_t)b * req_size;
+    uint8_t* d = resp + (size_t)b * resp_size;
+    if (vec) {
+      for (size_t i = tid; i < n / 16; i += nth) {
+        uint4 v = reinterpret_cast<const uint4*>(s)[i];
+        v.x = add1_bytes(v.x);
+        v.y = add1_bytes(v.y);
+        v.z = add1_bytes(v.z);
+        v.w = add1_bytes(v.w);
+        reinterpret_cast<uint4*>(d)[i] = v;
+      }
+    } else {
+      for (size_t i = tid; i < n; i += nth) d[i] = (uint8_t)(s[i] + 1);
+    }
+  }
+}
+
+__global__ void vec_add_kernel(const g_params* stub, size_t req_size, size_t resp_size, int batch) {
+  vec_add_body(stub->req, stub->resp, req_size, resp_size, batch, (size_t)blockIdx.x * blockDim.x + threadIdx.x,
+               (size_t)gridDim.x * blockDim.x, blockIdx.y, gridDim.y);
+}
+
+// Resident vec_add: one block; waits (bounded) for the doorbell to hold a batch
+// size, serves the batch, answers 2.
+__global__ void vec_add_resident(const g_params* stub, volatile uint32_t* door_bell, size_t req_size, size_t resp_size,
+                                 uint64_t idle_ns, uint32_t* status) {
+  __shared__ uint32_t s_batch;
+  uint64_t last = ptx::globaltimer_ns();
+  for (;;) {
+    if (threadIdx.x == 0) {
+      uint32_t v = 0;
+      for (int spin = 0; spin < 4096; spin++) {
+        v = ptx::ld_acquire_sys(door_bell);
+        if (v == APP_DOORBELL_EXIT) break;
+        if (v != APP_DOORBELL_IDLE && (v & APP_DOORBELL_START)) {
+          v &= ~APP_DOORBELL_START;
+          break;
+        }
+        if (ptx::globaltimer_ns() - last > idle_ns) {
+          v = 3u;
+          break;
+        }
+        v = 0;
+        __nanosleep(200);
+      }
+      s_batch = v;
+    }
+    __syncthreads();
+    uint32_t batch = s_batch;
+    __syncthreads();
+    if (batch == 3u) break;   // exit request or idle limit
+    if (batch == 0) continue;
+    g_params p = *stub;
+    vec_add_body(p.req, p.resp, req_size, resp_size, (int)batch, threadIdx.x, blockDim.x, 0, 1);
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      ptx::st_release_sys(door_bell, 2u);
+      last = ptx::globaltimer_ns();
+    }
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) ptx::st_release_sys(status, 1u);
+}
+
+// C = A.B for one small square fp32 problem per block (d <= 128).
+__global__ void mm_kernel(const g_params* stub, size_t req_size, size_t resp_size, int d, int batch) {
+  extern __shared__ float sm[];
+  for (int b = blockIdx.x; b < batch; b += gridDim.x) {
+    const float* A = reinterpret_cast<const float*>(stub->req + (size_t)b * req_size);
+    const float* B = A + (size_t)d * d;
+    float* C = reinterpret_cast<float*>(stub->resp + (size_t)b * resp_size);
+    float* sB = sm;  // B staged in shared memory (<= 64 KB)
+    for (int i = threadIdx.x; i < d * d; i += blockDim.x) sB[i] = B[i];
+    __syncthreads();
+    for (int o = threadIdx.x; o < d * d; o += blockDim.x) {
+      int i = o / d, j = o % d;
+      float acc = 0.f;
+      for (int k = 0; k < d; k++) acc += A[i * d + k] * sB[k * d + j];
+      C[o] = acc;
+    }
+    __syncthreads();
+  }
+}
+
+// LeNet-5, whole network in one kernel, one image per block (256 threads).
+// Activations stay in shared memory; fc weights stream from L2.
+struct LeNetW {
+  const float *c1w, *c1b, *c2w, *c2b, *f1w, *f1b, *f2w, *f2b, *f3w, *f3b;
+};
+
+__global__ void __launch_bounds__(256) lenet5_kernel(const g_params* stub, LeNetW w, int batch) {
+  __shared__ float x[28 * 28];
+  __shared__ float p1[6 * 14 * 14];
+  __shared__ float p2[16 * 5 * 5];
+  __shared__ float f1[120];
+  __shared__ float f2[84];
+  __shared__ float lg[10];
+  __shared__ float wc1[6 * 25 + 6];
+  __shared__ float wc2[16 * 6 * 25 + 16];
+  const int t = threadIdx.x;
+  for (int i = t; i < 150; i += 256) wc1[i] = w.c1w[i];
+  for (int i = t; i < 6; i += 256) wc1[150 + i] = w.c1b[i];
+  for (int i = t; i < 2400; i += 256) wc2[i] = w.c2w[i];
+  for (int i = t; i < 16; i += 256) wc2[2400 + i] = w.c2b[i];
+  for (int b = blockIdx.x; b < batch; b += gridDim.x) {
+    const float* in = reinterpret_cast<const float*>(stub->req + (size_t)b * LENET5_REQ_BYTES);
+    float* out = reinterpret_cast<float*>(stub->resp + (size_t)b * LENET5_RESP_BYTES);
+    __syncthreads();
+    for (int i = t; i < 784; i += 256) x[i] = in[i];
+    __syncthreads();
+    // conv1 (pad 2) + relu + 2x2 maxpool fused: each thread makes pooled outputs
+    for (int o = t; o < 6 * 14 * 14; o += 256) {
+      int k = o / 196, r = (o % 196) / 14, c = o % 14;
+      float best = -1e30f;
+      for (int dy = 0; dy < 2; dy++)
+        for (int dx = 0; dx < 2; dx++) {
+          int oh = 2 * r + dy, ow = 2 * c + dx;
+          float acc = wc1[150 + k];
+          for (int i = 0; i < 5; i++) {
+            int ih = oh + i - 2;
+            if (ih < 0 || ih >= 28) continue;
+            for (int j = 0; j < 5; j++) {
+              int iw = ow + j - 2;
+              if (iw < 0 || iw >= 28) continue;
+              acc += x[ih * 28 + iw] * wc1[k * 25 + i * 5 + j];
+            }
+          }
+          best = fmaxf(best, acc);
+        }
+      p1[o] = fmaxf(best, 0.f);
+    }
+    __syncthreads();
+    // conv2 (no pad) + relu + maxpool
+    for (int o = t; o < 16 * 5 * 5; o += 256) {
+      int k = o / 25, r = (o % 25) / 5, c = o % 5;
+      float best = -1e30f;
+      for (int dy = 0; dy < 2; dy++)
+        for (int dx = 0; dx < 2; dx++) {
+          int oh = 2 * r + dy, ow = 2 * c + dx;
+          float acc = wc2[2400 + k];
+          for (int ch = 0; ch < 6; ch++)
+            for (int i = 0; i < 5; i++)
+              for (int j = 0; j < 5; j++)
+                acc += p1[ch * 196 + (oh + i) * 14 + ow + j] * wc2[(k * 6 + ch) * 25 + i * 5 + j];
+          best = fmaxf(best, acc);
+        }
+      p2[o] = fmaxf(best, 0.f);
+    }
+    __syncthreads();
+    // fc1: 120 outputs, warp per output row
+    for (int o = t / 32; o < 120; o += 8) {
+      float acc = 0.f;
+      for (int i = t % 32; i < 400; i += 32) acc += p2[i] * w.f1w[o * 400 + i];
+      for (int s = 16; s; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
+      if (t % 32 == 0) f1[o] = fmaxf(acc + w.f1b[o], 0.f);
+    }
+    __syncthreads();
+    for (int o = t / 32; o < 84; o += 8) {
+      float acc = 0.f;
+      for (int i = t % 32; i < 120; i += 32) acc += f1[i] * w.f2w[o * 120 + i];
+      for (int s = 16; s; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
+      if (t % 32 == 0) f2[o] = fmaxf(acc + w.f2b[o], 0.f);
+    }
+    __syncthreads();
+    for (int o = t / 32; o < 10; o += 8) {
+      float acc = 0.f;
+      for (int i = t % 32; i < 84; i += 32) acc += f2[i] * w.f3w[o * 84 + i];
+      for (int s = 16; s; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
+      if (t % 32 == 0) lg[o] = acc + w.f3b[o];
+    }
+    __syncthreads();
+    if (t == 0) {
+      float m = lg[0];
+      for (int i = 1; i < 10; i++) m = fmaxf(m, lg[i]);
+      float e[10], s = 0.f;
+      for (int i = 0; i < 10; i++) {
+        e[i] = __expf(lg[i] - m);
+        s += e[i];
+      }
+      for (int i = 0; i < 10; i++) out[i] = e[i] / s;
+    }
+  }
+}
+
+// ------------------------------------------------------------------ launch
+LeNetW lenet_w(const GpuAppState* s) {
+  const float* b = s->d_weights;
+  LeNetW w{b + s->w_off[0], b + s->w_off[1], b + s->w_off[2], b + s->w_off[3], b + s->w_off[4],
+           b + s->w_off[5], b + s->w_off[6], b + s->w_off[7], b + s->w_off[8], b + s->w_off[9]};
+  return w;
+}
+
+void launch_kernels(AppCtx* c, int batch) {
+  GpuAppState* s = st(c);
+  cudaStream_t q = c->work_stream;
+  if (s->name == "echo") {
+    size_t n = s->req_size < s->resp_size ? s->req_size : s->resp_size;
+    int bx = (int)((n / 16 + 255) / 256);
+    bx = bx < 1 ? 1 : (bx > 296 ? 296 : bx);
+    echo_kernel<<<dim3(bx, batch > 64 ? 64 : batch), 256, 0, q>>>(c->d_stub, s->req_size, s->resp_size, batch);
+  } else if (s->name == "vec_add") {
+    size_t n = s->req_size < s->resp_size ? s->req_size : s->resp_size;
+    int bx = (int)((n / 16 + 255) / 256);
+    bx = bx < 1 ? 1 : (bx > 296 ? 296 : bx);
+    vec_add_kernel<<<dim3(bx, batch > 64 ? 64 : batch), 256, 0, q>>>(c->d_stub, s->req_size, s->resp_size, batch);
+  } else if (s->name == "matmul") {
+    mm_kernel<<<batch, 256, (size_t)s->dim * s->dim * 4, q>>>(c->d_stub, s->req_size, s->resp_size, s->dim, batch);
+  } else if (s->name == "lenet5") {
+    lenet5_kernel<<<batch, 256, 0, q>>>(c->d_stub, lenet_w(s), batch);
+  }
+}
+
+int gpu_app_init(AppCtx* c) {
+  GpuAppState* s = st(c);
+  if (c->launch_type == 2) {
+    srpc_log(SRPC_LOG_ERROR, "launch type 2 (device-side launch + device-side sync) is not available on sm_100");
+    return 0;
+  }
+  if (c->launch_type == 3 && s->name != "vec_add") {
+    srpc_log(SRPC_LOG_WARN, "resident launch type is implemented for vec_add only; using kernel launches");
+    c->launch_type = 1;
+  }
+  cudaSetDevice(c->device_id);
+  if (s->name == "matmul") {
+    if (!s->dim) s->dim = mm_dim_from_req(s->req_size);
+    if (s->dim > 128) return 0;
+    cudaFuncSetAttribute(mm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 128 * 4);
+  }
+  if (c->launch_type == 3) {
+    cudaHostAlloc(&s->h_pt_status, 4, cudaHostAllocMapped);
+    cudaHostGetDevicePointer((void**)&s->d_pt_status, s->h_pt_status, 0);
+    *s->h_pt_status = 1;  // not running yet
+  }
+  return 1;
+}
+
+int gpu_app_run(AppCtx* c) {
+  GpuAppState* s = st(c);
+  cudaSetDevice(c->device_id);
+  int batch = c->curr_batch_size;
+  if (c->launch_type == 0) return 1;
+  if (c->launch_type == 3) {
+    if (*(volatile uint32_t*)s->h_pt_status == 1u) {  // resident kernel absent: arm it
+      *s->h_pt_status = 0;
+      c->ResetAppRunStatus();
+      std::atomic_thread_fence(std::memory_order_seq_cst);
+      vec_add_resident<<<1, 1024, 0, c->work_stream>>>(c->d_stub, c->d_door_bell, s->req_size, s->resp_size, s->idle_ns,
+                                                       s->d_pt_status);
+    }
+    c->NotifyAppRunStart();
+    return cudaGetLastError() == cudaSuccess;
+  }
+  if (c->launch_type == 4) {
+    auto it = s->graphs.find(batch);
+    if (it == s->graphs.end()) {
+      cudaGraph_t g;
+      cudaStreamBeginCapture(c->work_stream, cudaStreamCaptureModeThreadLocal);
+      launch_kernels(c, batch);
+      if (cudaStreamEndCapture(c->work_stream, &g) != cudaSuccess) return 0;
+      cudaGraphExec_t ge;
+      if (cudaGraphInstantiate(&ge, g, 0) != cudaSuccess) return 0;
+      cudaGraphDestroy(g);
+      it = s->graphs.emplace(batch, ge).first;
+      c->graphCreated = true;
+      c->instance = ge;
+    }
+    return cudaGraphLaunch(it->second, c->work_stream) == cudaSuccess;
+  }
+  launch_kernels(c, batch);
+  return cudaGetLastError() == cudaSuccess;
+}
+
+int gpu_app_complete(AppCtx* c) {
+  if (c->launch_type == 3) c->ResetAppRunStatus();
+  return 1;
+}
+
+int gpu_app_cleanup(AppCtx* c) {
+  GpuAppState* s = st(c);
+  cudaSetDevice(c->device_id);
+  if (c->launch_type == 3 && s->h_pt_status) {
+    __atomic_store_n(c->door_bell, 3u, __ATOMIC_RELEASE);  // exit request
+    cudaStreamSynchronize(c->work_stream);
+    cudaFreeHost(s->h_pt_status);
+  }
+  for (auto& kv : s->graphs) cudaGraphExecDestroy(kv.second);
+  if (s->d_weights) cudaFree(s->d_weights);
+  delete s;
+  c->app_ctx_internal = nullptr;
+  return 1;
+}
+
+}  // namespace
+
+GpuAppHandle srpc_make_gpu_app(const char* name, int device_id, size_t req_size, size_t resp_size,
+                               const std::vector<std::vector<float>>& weights) {
+  GpuAppHandle h{};
+  int n = 0;
+  if (cudaGetDeviceCount(&n) != cudaSuccess || device_id >= n) return h;
+  std::string nm(name);
+  if (nm != "echo" && nm != "vec_add" && nm != "matmul" && nm != "lenet5") return h;
+  GpuAppState* s = new GpuAppState;
+  s->name = nm;
+  s->req_size = req_size;
+  s->resp_size = resp_size;
+  s->idle_ns = (uint64_t)readEnvInfo<uint64_t>("P2P_RPC_APP_IDLE_MS", 200) * 1000000ull;
+  if (nm == "lenet5") {
+    if (weights.size() != 10) {
+      delete s;
+      return h;
+    }
+    size_t total = 0;
+    for (auto& w : weights) {
+      s->w_off.push_back(total);
+      total += (w.size() + 3) / 4 * 4;
+    }
+    cudaSetDevice(device_id);
+    cudaMalloc(&s->d_weights, total * 4);
+    for (size_t i = 0; i < weights.size(); i++)
+      cudaMemcpy(s->d_weights + s->w_off[i], weights[i].data(), weights[i].size() * 4, cudaMemcpyHostToDevice);
+  }
+  h.internal = s;
+  h.init = gpu_app_init;
+  h.run = gpu_app_run;
+  h.cleanup = gpu_app_cleanup;
+  h.complete = gpu_app_complete;
+  return h;
+}

@@ -1,0 +1,252 @@
+// CUDA implementation of the device-operation table used by the host core.
+//
+// Ring memory is a CUDA virtual-memory-management allocation mapped twice back to
+// back in one reserved address range, so a window of consecutive slots that runs
+// past the end of the ring is still contiguous (same idea as reference
+// src/p2p_rpc_app_rr_mem_pool.h:213-339), with read/write access granted to every
+// GPU that can reach the owner over NVLink.  Doorbell words are mapped pinned
+// host memory.  Stream-ordered doorbell waits and writes use the driver's stream
+// memory operations (reference src/utils/g_utils.cu:42-53).  Driver entry points
+// are resolved at run time, so the library loads on machines without a driver.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <mutex>
+#include <string>
+
+#include "../host/p2p_rpc_app.h"
+#include "driver_api.h"
+
+static thread_local std::string g_last_error;
+
+static int fail(const char* what, cudaError_t e) {
+  g_last_error = std::string(what) + ": " + cudaGetErrorString(e);
+  return -1;
+}
+static int fail_drv(const char* what, CUresult r) {
+  g_last_error = std::string(what) + ": CUresult " + std::to_string((int)r);
+  return -1;
+}
+#define RT(call)                                   \
+  do {                                             \
+    cudaError_t _e = (call);                       \
+    if (_e != cudaSuccess) return fail(#call, _e); \
+  } while (0)
+#define DRV(call)                                        \
+  do {                                                   \
+    CUresult _r = (call);                                \
+    if (_r != CUDA_SUCCESS) return fail_drv(#call, _r);  \
+  } while (0)
+
+const SrpcDriverApi* srpc_driver_api() {
+  static SrpcDriverApi api;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    auto get = [](const char* name, void** fn) {
+      cudaDriverEntryPointQueryResult q;
+      if (cudaGetDriverEntryPoint(name, fn, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess)
+        *fn = nullptr;
+    };
+    get("cuMemCreate", (void**)&api.MemCreate);
+    get("cuMemRelease", (void**)&api.MemRelease);
+    get("cuMemAddressReserve", (void**)&api.MemAddressReserve);
+    get("cuMemAddressFree", (void**)&api.MemAddressFree);
+    get("cuMemMap", (void**)&api.MemMap);
+    get("cuMemUnmap", (void**)&api.MemUnmap);
+    get("cuMemSetAccess", (void**)&api.MemSetAccess);
+    get("cuMemGetAllocationGranularity", (void**)&api.MemGetAllocationGranularity);
+    get("cuStreamWaitValue32", (void**)&api.StreamWaitValue32);
+    get("cuStreamWriteValue32", (void**)&api.StreamWriteValue32);
+    get("cuTensorMapEncodeTiled", (void**)&api.TensorMapEncodeTiled);
+    get("cuDeviceGetAttribute", (void**)&api.DeviceGetAttribute);
+    api.ok = api.MemCreate && api.MemMap && api.StreamWaitValue32 && api.TensorMapEncodeTiled;
+  });
+  return &api;
+}
+
+struct RingImpl {
+  CUmemGenericAllocationHandle handle;
+  CUdeviceptr va;
+  size_t cap;
+  bool vmm;
+};
+
+static int d_device_count() {
+  int n = 0;
+  if (cudaGetDeviceCount(&n) != cudaSuccess) return 0;
+  return n;
+}
+static int d_set_device(int dev) {
+  RT(cudaSetDevice(dev));
+  return 0;
+}
+static int d_stream_create(int dev, cudaStream_t* s) {
+  RT(cudaSetDevice(dev));
+  RT(cudaStreamCreateWithFlags(s, cudaStreamNonBlocking));
+  return 0;
+}
+static int d_stream_destroy(cudaStream_t s) {
+  RT(cudaStreamDestroy(s));
+  return 0;
+}
+static int d_stream_sync(cudaStream_t s) {
+  RT(cudaStreamSynchronize(s));
+  return 0;
+}
+static int d_stream_query(cudaStream_t s) {
+  cudaError_t e = cudaStreamQuery(s);
+  if (e == cudaSuccess) return 0;
+  if (e == cudaErrorNotReady) return 1;
+  return fail("cudaStreamQuery", e);
+}
+static int d_wait32(cudaStream_t s, volatile uint32_t* addr, uint32_t v) {
+  const SrpcDriverApi* d = srpc_driver_api();
+  if (!d->StreamWaitValue32) return fail_drv("cuStreamWaitValue32 unavailable", CUDA_ERROR_NOT_SUPPORTED);
+  DRV(d->StreamWaitValue32((CUstream)s, (CUdeviceptr)(uintptr_t)addr, v, CU_STREAM_WAIT_VALUE_EQ));
+  return 0;
+}
+static int d_write32(cudaStream_t s, volatile uint32_t* addr, uint32_t v) {
+  const SrpcDriverApi* d = srpc_driver_api();
+  if (!d->StreamWriteValue32) return fail_drv("cuStreamWriteValue32 unavailable", CUDA_ERROR_NOT_SUPPORTED);
+  DRV(d->StreamWriteValue32((CUstream)s, (CUdeviceptr)(uintptr_t)addr, v, CU_STREAM_WRITE_VALUE_DEFAULT));
+  return 0;
+}
+static int d_event_create(cudaEvent_t* e) {
+  RT(cudaEventCreateWithFlags(e, cudaEventDisableTiming));
+  return 0;
+}
+static int d_event_destroy(cudaEvent_t e) {
+  RT(cudaEventDestroy(e));
+  return 0;
+}
+
+static int d_ring_alloc(int dev, size_t min_bytes, bool peer_access, SrpcRingMem* out) {
+  RT(cudaSetDevice(dev));
+  RT(cudaFree(0));  // make sure the primary context exists before driver calls
+  const SrpcDriverApi* d = srpc_driver_api();
+  RingImpl* impl = new RingImpl{};
+  if (d->ok) {
+    CUmemAllocationProp prop = {};
+    prop.type = CU_MEM_ALLOCATION_TYPE_PINNED;
+    prop.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
+    prop.location.id = dev;
+    size_t gran = 0;
+    DRV(d->MemGetAllocationGranularity(&gran, &prop, CU_MEM_ALLOC_GRANULARITY_MINIMUM));
+    size_t cap = (min_bytes + gran - 1) / gran * gran;
+    if (cap == 0) cap = gran;
+    DRV(d->MemCreate(&impl->handle, cap, &prop, 0));
+    CUresult r = d->MemAddressReserve(&impl->va, 2 * cap, gran, 0, 0);
+    if (r != CUDA_SUCCESS) {
+      d->MemRelease(impl->handle);
+      delete impl;
+      return fail_drv("cuMemAddressReserve", r);
+    }
+    DRV(d->MemMap(impl->va, cap, 0, impl->handle, 0));
+    DRV(d->MemMap(impl->va + cap, cap, 0, impl->handle, 0));
+    // Grant access to the owner and to every peer that can address it.
+    int ndev = d_device_count();
+    std::vector<CUmemAccessDesc> acc;
+    for (int p = 0; p < ndev; p++) {
+      int can = (p == dev);
+      if (p != dev && peer_access) cudaDeviceCanAccessPeer(&can, p, dev);
+      if (!can) continue;
+      CUmemAccessDesc a = {};
+      a.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
+      a.location.id = p;
+      a.flags = CU_MEM_ACCESS_FLAGS_PROT_READWRITE;
+      acc.push_back(a);
+    }
+    DRV(d->MemSetAccess(impl->va, 2 * cap, acc.data(), acc.size()));
+    impl->cap = cap;
+    impl->vmm = true;
+    out->base = (void*)impl->va;
+    out->capacity = cap;
+    out->double_mapped = true;
+  } else {
+    // No virtual memory management: plain allocation, windows must not wrap.
+    void* p = nullptr;
+    RT(cudaMalloc(&p, min_bytes));
+    impl->va = (CUdeviceptr)(uintptr_t)p;
+    impl->cap = min_bytes;
+    impl->vmm = false;
+    out->base = p;
+    out->capacity = min_bytes;
+    out->double_mapped = false;
+  }
+  out->impl = impl;
+  return 0;
+}
+
+static int d_ring_free(SrpcRingMem* m) {
+  RingImpl* impl = static_cast<RingImpl*>(m->impl);
+  if (!impl) return 0;
+  const SrpcDriverApi* d = srpc_driver_api();
+  if (impl->vmm) {
+    d->MemUnmap(impl->va, 2 * impl->cap);
+    d->MemAddressFree(impl->va, 2 * impl->cap);
+    d->MemRelease(impl->handle);
+  } else {
+    cudaFree((void*)(uintptr_t)impl->va);
+  }
+  delete impl;
+  m->impl = nullptr;
+  m->base = nullptr;
+  return 0;
+}
+
+static int d_host_alloc_mapped(size_t bytes, void** h, void** dptr) {
+  RT(cudaHostAlloc(h, bytes, cudaHostAllocMapped | cudaHostAllocPortable));
+  RT(cudaHostGetDevicePointer(dptr, *h, 0));
+  memset(*h, 0, bytes);
+  return 0;
+}
+static int d_host_free(void* h) {
+  RT(cudaFreeHost(h));
+  return 0;
+}
+static int d_dev_alloc(int dev, size_t bytes, void** p) {
+  RT(cudaSetDevice(dev));
+  RT(cudaMalloc(p, bytes));
+  return 0;
+}
+static int d_dev_free(void* p) {
+  RT(cudaFree(p));
+  return 0;
+}
+static int d_memcpy_async(void* dst, const void* src, size_t n, cudaStream_t s) {
+  RT(cudaMemcpyAsync(dst, src, n, cudaMemcpyDefault, s));
+  return 0;
+}
+static int d_memset_async(void* dst, int v, size_t n, cudaStream_t s) {
+  RT(cudaMemsetAsync(dst, v, n, s));
+  return 0;
+}
+static int d_graph_launch(cudaGraphExec_t g, cudaStream_t s) {
+  RT(cudaGraphLaunch(g, s));
+  return 0;
+}
+static const char* d_last_error() { return g_last_error.c_str(); }
+
+extern "C" const SrpcDeviceOps* srpc_cuda_ops() {
+  static const SrpcDeviceOps ops = {
+      d_device_count, d_set_device,  d_stream_create, d_stream_destroy,    d_stream_sync, d_stream_query, d_wait32,
+      d_write32,      d_event_create, d_event_destroy, d_ring_alloc,        d_ring_free,   d_host_alloc_mapped,
+      d_host_free,    d_dev_alloc,    d_dev_free,      d_memcpy_async,      d_memset_async, d_graph_launch, d_last_error};
+  return &ops;
+}
+
+// Capability report in the spirit of reference src/splitrpc_server/device_test.cu:8-41.
+extern "C" int srpc_device_caps(int dev, int* vmm, int* stream_memops, int* gdr_with_vmm, int* sm_major, int* sm_minor,
+                                int* n_sm) {
+  const SrpcDriverApi* d = srpc_driver_api();
+  if (!d->DeviceGetAttribute) return -1;
+  cudaDeviceProp p;
+  if (cudaGetDeviceProperties(&p, dev) != cudaSuccess) return -1;
+  *sm_major = p.major;
+  *sm_minor = p.minor;
+  *n_sm = p.multiProcessorCount;
+  d->DeviceGetAttribute(vmm, CU_DEVICE_ATTRIBUTE_VIRTUAL_MEMORY_MANAGEMENT_SUPPORTED, dev);
+  *stream_memops = 1;  // stream memory operations are always on since CUDA 12
+  d->DeviceGetAttribute(gdr_with_vmm, CU_DEVICE_ATTRIBUTE_GPU_DIRECT_RDMA_WITH_CUDA_VMM_SUPPORTED, dev);
+  return 0;
+}

@@ -1,0 +1,38 @@
+// Launch API of the tcgen05 GEMM / implicit-GEMM convolution kernels.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "driver_api.h"
+
+enum GemmAct { GEMM_ACT_NONE = 0, GEMM_ACT_RELU = 1, GEMM_ACT_GELU = 2 };
+enum GemmErr { GEMM_OK = 0, GEMM_ERR_PRODUCER_WAIT = 1, GEMM_ERR_MMA_WAIT = 2, GEMM_ERR_EPILOGUE_WAIT = 3 };
+
+// out[row, col] = act(acc + bias[col] + residual[row, col]); leading dimensions in elements.
+struct GemmEpilogue {
+  void* out = nullptr;
+  int ldo = 0;
+  int out_fp32 = 0;
+  const float* bias = nullptr;
+  const __nv_bfloat16* residual = nullptr;
+  int ldr = 0;
+  int act = GEMM_ACT_NONE;
+};
+
+struct ConvShape {
+  int n, h, w, cin;     // input NHWC
+  int cout, r, s;       // filter [cout][r][s][cin]
+  int stride, pad;
+  int oh, ow;
+};
+
+// D[M,N] = A[M,K] . B[N,K]^T, bf16 operands (row strides lda/ldb elements, multiples of 8), fp32 accumulation.
+// `status` may be null; otherwise it receives a GemmErr code when a bounded wait ran out.
+cudaError_t srpc_gemm_bf16(const void* A, int lda, const void* B, int ldb, int M, int N, int K, const GemmEpilogue& ep,
+                           uint32_t* status, cudaStream_t stream);
+
+// NHWC bf16 convolution as an implicit GEMM; cin must be a multiple of 64.
+cudaError_t srpc_conv_bf16(const void* in, const void* weight, const ConvShape& cs, const GemmEpilogue& ep,
+                           uint32_t* status, cudaStream_t stream);

@@ -1,0 +1,20 @@
+// C++ entry points of the CUDA kernels used by the Python bindings.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <tuple>
+#include <vector>
+
+extern "C" int srpc_device_caps(int dev, int* vmm, int* stream_memops, int* gdr_with_vmm, int* sm_major, int* sm_minor,
+                                int* n_sm);
+
+using SgTuple = std::tuple<uintptr_t, uintptr_t, uint32_t>;
+// One-shot: uploads the list, launches, and returns after the copy finished.
+cudaError_t srpc_sg_copy_list(const std::vector<SgTuple>& items, int impl, int n_blocks, cudaStream_t stream);
+cudaError_t srpc_sg_cast_list(const std::vector<SgTuple>& items, float scale, float shift, int n_blocks, cudaStream_t stream);
+// Resident copy list in device memory for repeated launches (benchmarks, graphs).
+uintptr_t srpc_sg_list_create(const std::vector<SgTuple>& items);
+void srpc_sg_list_destroy(uintptr_t handle);
+cudaError_t srpc_sg_list_launch(uintptr_t handle, int impl, int n_blocks, cudaStream_t stream);

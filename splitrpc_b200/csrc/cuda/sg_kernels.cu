@@ -1,0 +1,283 @@
+// Scatter-gather copy kernels for sm_100a.
+//
+// Replaces the single-block persistent copy loop, the block-per-buffer kernel and
+// the device-side memcpy kernel of reference src/transport/g_copy_ng.cu:17-163
+// with chunked multi-block kernels:
+//   sg_copy_simt     16-byte vector copies, any alignment handled by peeling
+//   sg_copy_bulk     one thread per block drives a ring of shared-memory stages
+//                    with cp.async.bulk (TMA) loads and stores; other warps take
+//                    the chunks that are not 16-byte aligned
+//   sg_cast_bf16     gather fused with fp32 -> bf16 deserialisation
+//   sg_persistent    doorbell-driven resident variant (host rings a sequence
+//                    number in mapped memory; the last block to finish publishes
+//                    it back with a system-scope release store)
+// All waits are bounded; a wait that runs out sets an error word and the kernel
+// returns after draining its own outstanding copies.
+#include "ptx.cuh"
+#include "sg_kernels.cuh"
+
+namespace {
+
+__device__ __forceinline__ uint32_t find_item(const SgItem* items, uint32_t n, uint32_t chunk) {
+  uint32_t lo = 0, hi = n - 1;
+  while (lo < hi) {
+    uint32_t mid = (lo + hi + 1) >> 1;
+    if (items[mid].first_chunk <= chunk) lo = mid;
+    else hi = mid - 1;
+  }
+  return lo;
+}
+
+struct ChunkRef {
+  const uint8_t* src;
+  uint8_t* dst;
+  uint32_t len;
+};
+
+__device__ __forceinline__ ChunkRef chunk_ref(const SgItem* items, uint32_t n_items, uint32_t chunk) {
+  uint32_t it = find_item(items, n_items, chunk);
+  uint64_t off = (uint64_t)(chunk - items[it].first_chunk) * SG_CHUNK;
+  uint32_t left = items[it].len - (uint32_t)off;
+  ChunkRef r;
+  r.src = reinterpret_cast<const uint8_t*>(items[it].src + off);
+  r.dst = reinterpret_cast<uint8_t*>(items[it].dst + off);
+  r.len = left < SG_CHUNK ? left : SG_CHUNK;
+  return r;
+}
+
+// Copies one chunk with `nthr` threads (thread index `t`).
+__device__ __forceinline__ void copy_chunk_simt(const uint8_t* src, uint8_t* dst, uint32_t len, uint32_t t, uint32_t nthr) {
+  uint32_t head = (uint32_t)((16 - ((uintptr_t)dst & 15)) & 15);
+  if (head > len) head = len;
+  for (uint32_t i = t; i < head; i += nthr) dst[i] = src[i];
+  const uint8_t* s = src + head;
+  uint8_t* d = dst + head;
+  uint32_t body = len - head;
+  if (((uintptr_t)s & 15) == 0) {
+    uint32_t nv = body >> 4;
+    const uint4* s4 = reinterpret_cast<const uint4*>(s);
+    uint4* d4 = reinterpret_cast<uint4*>(d);
+    for (uint32_t i = t; i < nv; i += nthr) d4[i] = s4[i];
+    for (uint32_t i = (nv << 4) + t; i < body; i += nthr) d[i] = s[i];
+  } else if (((uintptr_t)s & 3) == 0) {
+    uint32_t nv = body >> 2;
+    const uint32_t* s1 = reinterpret_cast<const uint32_t*>(s);
+    uint32_t* d1 = reinterpret_cast<uint32_t*>(d);
+    for (uint32_t i = t; i < nv; i += nthr) d1[i] = s1[i];
+    for (uint32_t i = (nv << 2) + t; i < body; i += nthr) d[i] = s[i];
+  } else {
+    for (uint32_t i = t; i < body; i += nthr) d[i] = s[i];
+  }
+}
+
+__global__ void __launch_bounds__(256) sg_copy_simt(const SgItem* __restrict__ items, uint32_t n_items, uint32_t n_chunks) {
+  for (uint32_t c = blockIdx.x; c < n_chunks; c += gridDim.x) {
+    ChunkRef r = chunk_ref(items, n_items, c);
+    copy_chunk_simt(r.src, r.dst, r.len, threadIdx.x, blockDim.x);
+  }
+}
+
+__device__ __forceinline__ bool bulk_ok(const ChunkRef& r) {
+  return ((((uintptr_t)r.src) | ((uintptr_t)r.dst) | (uintptr_t)r.len) & 15) == 0 && r.len > 0;
+}
+
+constexpr int BULK_STAGES = 8;
+constexpr int BULK_AHEAD = 4;
+constexpr int BULK_THREADS = 128;
+
+// Runs the bulk-copy pipeline of one block over chunks {first, first+stride, ...}
+// that pass bulk_ok.  Called by one thread.  Returns false if a wait ran out.
+__device__ bool bulk_pipeline(const SgItem* items, uint32_t n_items, uint32_t n_chunks, uint32_t first, uint32_t stride,
+                              uint8_t* stages, uint64_t* bars, uint32_t& phase_bits) {
+  // k counts eligible chunks handled by this block.
+  uint32_t load_c = first, store_c = first;  // chunk cursors of the load and the store side
+  uint32_t k_load = 0, k_store = 0;
+  bool ok = true;
+  auto next_eligible = [&](uint32_t c) {
+    while (c < n_chunks) {
+      ChunkRef r = chunk_ref(items, n_items, c);
+      if (bulk_ok(r)) break;
+      c += stride;
+    }
+    return c;
+  };
+  load_c = next_eligible(load_c);
+  store_c = load_c;
+  auto issue_load = [&]() {
+    ChunkRef r = chunk_ref(items, n_items, load_c);
+    uint32_t s = k_load % BULK_STAGES;
+    // The store that last used this stage must have finished reading it.
+    if (k_load >= BULK_STAGES) ptx::bulk_wait_read<BULK_STAGES - BULK_AHEAD - 1>();
+    ptx::mbar_expect_tx(&bars[s], r.len);
+    ptx::bulk_g2s(stages + (size_t)s * SG_CHUNK, r.src, r.len, &bars[s]);
+    k_load++;
+    load_c = next_eligible(load_c + stride);
+  };
+  for (int i = 0; i < BULK_AHEAD && load_c < n_chunks; i++) issue_load();
+  while (store_c < n_chunks) {
+    if (load_c < n_chunks) issue_load();
+    ChunkRef r = chunk_ref(items, n_items, store_c);
+    uint32_t s = k_store % BULK_STAGES;
+    if (!ptx::mbar_wait(&bars[s], (phase_bits >> s) & 1u)) {
+      ok = false;
+      break;
+    }
+    phase_bits ^= (1u << s);
+    ptx::bulk_s2g(r.dst, stages + (size_t)s * SG_CHUNK, r.len);
+    ptx::bulk_commit();
+    k_store++;
+    store_c = next_eligible(store_c + stride);
+  }
+  ptx::bulk_wait_all<0>();
+  return ok;
+}
+
+__global__ void __launch_bounds__(BULK_THREADS) sg_copy_bulk(const SgItem* __restrict__ items, uint32_t n_items,
+                                                             uint32_t n_chunks, uint32_t* error) {
+  extern __shared__ __align__(128) uint8_t smem_raw[];
+  uint8_t* stages = smem_raw;
+  __shared__ __align__(8) uint64_t bars[BULK_STAGES];
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < BULK_STAGES; i++) ptx::mbar_init(&bars[i], 1);
+    ptx::fence_mbar_init();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    uint32_t phase_bits = 0;
+    if (!bulk_pipeline(items, n_items, n_chunks, blockIdx.x, gridDim.x, stages, bars, phase_bits) && error) *error = 1;
+  } else if (threadIdx.x >= 32) {
+    // Warps 1..3 take the chunks the bulk path cannot move.
+    for (uint32_t c = blockIdx.x; c < n_chunks; c += gridDim.x) {
+      ChunkRef r = chunk_ref(items, n_items, c);
+      if (!bulk_ok(r)) copy_chunk_simt(r.src, r.dst, r.len, threadIdx.x - 32, BULK_THREADS - 32);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256) sg_cast_bf16(const SgItem* __restrict__ items, uint32_t n_items, uint32_t n_chunks,
+                                                    float scale, float shift) {
+  for (uint32_t c = blockIdx.x; c < n_chunks; c += gridDim.x) {
+    uint32_t it = find_item(items, n_items, c);
+    uint64_t off = (uint64_t)(c - items[it].first_chunk) * SG_CHUNK;  // byte offset in the fp32 source
+    uint32_t left = items[it].len - (uint32_t)off;
+    uint32_t len = left < SG_CHUNK ? left : SG_CHUNK;
+    const float* s = reinterpret_cast<const float*>(items[it].src + off);
+    __nv_bfloat16* d = reinterpret_cast<__nv_bfloat16*>(items[it].dst + off / 2);
+    uint32_t n = len >> 2;
+    if (((((uintptr_t)s) & 15) | (((uintptr_t)d) & 7)) == 0) {
+      uint32_t nv = n >> 2;
+      for (uint32_t i = threadIdx.x; i < nv; i += blockDim.x) {
+        float4 v = reinterpret_cast<const float4*>(s)[i];
+        __nv_bfloat162 a = __floats2bfloat162_rn((v.x - shift) * scale, (v.y - shift) * scale);
+        __nv_bfloat162 b = __floats2bfloat162_rn((v.z - shift) * scale, (v.w - shift) * scale);
+        uint2 o;
+        o.x = *reinterpret_cast<uint32_t*>(&a);
+        o.y = *reinterpret_cast<uint32_t*>(&b);
+        reinterpret_cast<uint2*>(d)[i] = o;
+      }
+      for (uint32_t i = (nv << 2) + threadIdx.x; i < n; i += blockDim.x) d[i] = __float2bfloat16((s[i] - shift) * scale);
+    } else {
+      for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) d[i] = __float2bfloat16((s[i] - shift) * scale);
+    }
+  }
+}
+
+// Resident engine.  Each block polls the doorbell; a new sequence number means
+// the item list is valid.  Blocks never wait for one another: each finishes its
+// share, and the block that brings the arrival counter to gridDim.x * seq
+// publishes `done`.
+__global__ void __launch_bounds__(256) sg_persistent(SgCtrl* ctrl, uint32_t* counter) {
+  __shared__ uint32_t s_cmd;
+  __shared__ SgItem s_items[SG_PERSISTENT_ITEMS];
+  uint32_t seen = ctrl->done;  // submissions up to `done` were served by an earlier launch
+  uint64_t last = ptx::globaltimer_ns();
+  const uint64_t idle_limit = ctrl->idle_limit_ns;
+  for (;;) {
+    if (threadIdx.x == 0) {
+      uint32_t cmd = 0;  // 0 keep polling, 1 work, 2 leave
+      for (int spin = 0; spin < 4096; spin++) {
+        uint32_t db = ptx::ld_acquire_sys(&ctrl->doorbell);
+        if (db != seen) {
+          cmd = 1;
+          break;
+        }
+        if (ptx::ld_relaxed_sys(&ctrl->exit_flag) || ptx::globaltimer_ns() - last > idle_limit) {
+          cmd = 2;
+          break;
+        }
+        __nanosleep(200);
+      }
+      s_cmd = cmd;
+    }
+    __syncthreads();
+    uint32_t cmd = s_cmd;
+    __syncthreads();
+    if (cmd == 2) break;
+    if (cmd == 0) continue;
+    seen++;
+    uint32_t n_items = ctrl->n_items, n_chunks = ctrl->n_chunks;
+    if (n_items > SG_PERSISTENT_ITEMS) n_items = SG_PERSISTENT_ITEMS;
+    // One pass over PCIe brings the list into shared memory; lookups stay on chip.
+    {
+      const uint64_t* src = reinterpret_cast<const uint64_t*>(const_cast<const SgItem*>(ctrl->items));
+      uint64_t* dst = reinterpret_cast<uint64_t*>(s_items);
+      for (uint32_t i = threadIdx.x; i < n_items * 3; i += blockDim.x) dst[i] = src[i];
+    }
+    __syncthreads();
+    for (uint32_t c = blockIdx.x; c < n_chunks; c += gridDim.x) {
+      ChunkRef r = chunk_ref(s_items, n_items, c);
+      copy_chunk_simt(r.src, r.dst, r.len, threadIdx.x, blockDim.x);
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      uint32_t prev = atomicAdd(counter, 1u);
+      if (prev + 1 == gridDim.x) {
+        atomicExch(counter, 0u);
+        __threadfence_system();
+        ptx::st_release_sys(&ctrl->done, seen);
+      }
+      last = ptx::globaltimer_ns();
+    }
+  }
+  if (threadIdx.x == 0) atomicAdd_system(const_cast<uint32_t*>(&ctrl->exited), 1u);
+}
+
+}  // namespace
+
+static int clamp_blocks(int n_blocks, uint32_t n_chunks) {
+  if (n_blocks <= 0) n_blocks = 148 * 4;
+  if ((uint32_t)n_blocks > n_chunks) n_blocks = (int)n_chunks;
+  return n_blocks < 1 ? 1 : n_blocks;
+}
+
+cudaError_t sg_launch_copy(const SgItem* d_items, uint32_t n_items, uint32_t n_chunks, int impl, int n_blocks,
+                           cudaStream_t stream) {
+  if (n_items == 0 || n_chunks == 0) return cudaSuccess;
+  if (impl == SG_IMPL_BULK) {
+    static bool attr_set = false;
+    size_t smem = (size_t)BULK_STAGES * SG_CHUNK;
+    if (!attr_set) {
+      cudaError_t e = cudaFuncSetAttribute(sg_copy_bulk, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return e;
+      attr_set = true;
+    }
+    int nb = clamp_blocks(n_blocks > 0 ? n_blocks : 148, n_chunks);
+    sg_copy_bulk<<<nb, BULK_THREADS, smem, stream>>>(d_items, n_items, n_chunks, nullptr);
+  } else {
+    sg_copy_simt<<<clamp_blocks(n_blocks, n_chunks), 256, 0, stream>>>(d_items, n_items, n_chunks);
+  }
+  return cudaGetLastError();
+}
+
+cudaError_t sg_launch_cast_bf16(const SgItem* d_items, uint32_t n_items, uint32_t n_chunks, float scale, float shift,
+                                int n_blocks, cudaStream_t stream) {
+  if (n_items == 0 || n_chunks == 0) return cudaSuccess;
+  sg_cast_bf16<<<clamp_blocks(n_blocks, n_chunks), 256, 0, stream>>>(d_items, n_items, n_chunks, scale, shift);
+  return cudaGetLastError();
+}
+
+cudaError_t sg_launch_persistent(SgCtrl* d_ctrl, uint32_t* d_counter, int n_blocks, cudaStream_t stream) {
+  sg_persistent<<<n_blocks, 256, 0, stream>>>(d_ctrl, d_counter);
+  return cudaGetLastError();
+}

@@ -1,0 +1,59 @@
+// Scatter-gather copy kernels and their launch API.
+//
+// A copy list is an array of SgItem {src, dst, len}; the list is cut into chunks
+// of SG_CHUNK bytes and chunks are spread over thread blocks, so one launch moves
+// every fragment run of a whole batch of requests.  Sources and destinations may
+// be local HBM, mapped pinned host memory (the receive/transmit arenas) or a peer
+// GPU's memory reached over NVLink.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+static constexpr uint32_t SG_CHUNK = 16384;
+static constexpr uint32_t SG_MAX_ITEMS = 8192;        // per launch
+static constexpr uint32_t SG_PERSISTENT_ITEMS = 1024;  // per doorbell ring of the resident engine
+
+struct SgItem {
+  uint64_t src;
+  uint64_t dst;
+  uint32_t len;
+  uint32_t first_chunk;  // index of this item's first chunk in the launch-wide chunk numbering
+};
+
+// Control block of the persistent engine; lives in mapped pinned host memory.
+struct SgCtrl {
+  volatile uint32_t doorbell;   // host: sequence number of the newest submission
+  volatile uint32_t done;       // device: sequence number of the newest finished submission
+  volatile uint32_t exit_flag;  // host: 1 asks the kernel to leave
+  volatile uint32_t exited;     // device: number of thread blocks that have left
+  volatile uint32_t n_items;
+  volatile uint32_t n_chunks;
+  volatile uint32_t error;      // device: non-zero when a bounded wait ran out
+  uint32_t _pad;
+  uint64_t idle_limit_ns;       // a block leaves after this long without new work
+  SgItem items[SG_PERSISTENT_ITEMS];
+};
+
+enum SgImpl { SG_IMPL_SIMT = 0, SG_IMPL_BULK = 1 };
+
+// One launch over a copy list that the device can read (device or mapped memory).
+cudaError_t sg_launch_copy(const SgItem* d_items, uint32_t n_items, uint32_t n_chunks, int impl, int n_blocks,
+                           cudaStream_t stream);
+// fp32 -> bf16 gather: every item copies len/4 floats to len/4 bf16 values,
+// computing (x - shift) * scale on the way.
+cudaError_t sg_launch_cast_bf16(const SgItem* d_items, uint32_t n_items, uint32_t n_chunks, float scale, float shift,
+                                int n_blocks, cudaStream_t stream);
+// Persistent engine: `counter` is a zero-initialised device word.
+cudaError_t sg_launch_persistent(SgCtrl* d_ctrl, uint32_t* d_counter, int n_blocks, cudaStream_t stream);
+
+// Host helper: fills first_chunk and returns the chunk count.
+static inline uint32_t sg_assign_chunks(SgItem* items, uint32_t n) {
+  uint32_t c = 0;
+  for (uint32_t i = 0; i < n; i++) {
+    items[i].first_chunk = c;
+    c += (items[i].len + SG_CHUNK - 1) / SG_CHUNK;
+  }
+  return c;
+}
+static_assert(sizeof(SgItem) == 24, "three 8-byte words");

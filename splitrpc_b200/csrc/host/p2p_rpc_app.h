@@ -1,0 +1,387 @@
+// App-side runtime: stub, device abstraction, ring memory, request slots, app context.
+//
+// What an app sees of a call is a g_params stub {req, resp} that points into the
+// request and response rings (reference src/p2p_rpc_app_stub.h:11-29).  The rings
+// are mapped twice back to back in virtual memory, so a batch of consecutive
+// slots is contiguous even when it crosses the end of the ring (reference
+// src/p2p_rpc_app_rr_mem_pool.h:213-339).  Each slot has a 32-bit state word
+// (FREE -> RX_COMPLETE -> WORK_COMPLETE -> TX_COMPLETE) that doubles as the
+// doorbell a GPU stream can wait on.
+//
+// The host core never calls CUDA directly: everything device-specific goes
+// through the SrpcDeviceOps table, which the CUDA half of the library fills in.
+// device_id < 0 selects the CPU "device" (memfd double mapping, synchronous
+// execution), which is what the GPU-less plumbing configuration runs on.
+#pragma once
+
+#include <sys/mman.h>
+#include <unistd.h>
+
+#include <climits>
+#include <numeric>
+
+#include "config_utils.h"
+
+typedef struct CUstream_st* cudaStream_t;
+typedef struct CUevent_st* cudaEvent_t;
+typedef struct CUgraph_st* cudaGraph_t;
+typedef struct CUgraphExec_st* cudaGraphExec_t;
+
+// ------------------------------------------------------------------ stubs
+#define MAX_NUM_TENSORS 4
+// Multi-tensor form: each input tensor of a batch is contiguous by itself.
+struct g_params_v2 {
+  uintptr_t inputs[MAX_NUM_TENSORS];
+  uintptr_t outputs[MAX_NUM_TENSORS];
+  size_t input_tensor_size[MAX_NUM_TENSORS];
+  size_t output_tensor_size[MAX_NUM_TENSORS];
+} __attribute__((packed));
+
+struct g_params {
+  uint8_t* req;
+  uint8_t* resp;
+} __attribute__((packed));
+
+static constexpr uint32_t APP_DOORBELL_START = 0x40000000u;
+static constexpr uint32_t APP_DOORBELL_IDLE = 0xFFFFFFFFu;
+static constexpr uint32_t APP_DOORBELL_RUN_DONE = 1u;   // written from the stream after a run
+static constexpr uint32_t APP_DOORBELL_PT_DONE = 2u;    // written by a resident kernel after a batch
+static constexpr uint32_t APP_DOORBELL_EXIT = 3u;       // asks a resident kernel to leave
+
+enum APP_RR_STATUS : uint32_t { FREE = 0, RX_COMPLETE = 1, WORK_COMPLETE = 2, TX_COMPLETE = 3 };
+
+// ------------------------------------------------------------------ tring
+// Bump-pointer address generator over a ring-shaped address range (reference
+// src/p2p_rpc_tring.h:10-34): get_next(n) returns the current address and
+// advances by n modulo the capacity.
+class P2pRpcTring {
+  uintptr_t base_;
+  size_t capacity_;
+  size_t offset_ = 0;
+
+ public:
+  P2pRpcTring(void* base, size_t capacity) : base_((uintptr_t)base), capacity_(capacity) {}
+  void* get_next(size_t size) {
+    void* ret = (void*)(base_ + offset_);
+    offset_ = (offset_ + size) % capacity_;
+    return ret;
+  }
+  size_t offset() const { return offset_; }
+  size_t capacity() const { return capacity_; }
+  void* base() const { return (void*)base_; }
+  void reset() { offset_ = 0; }
+};
+
+// ------------------------------------------------------------------ device ops
+struct SrpcRingMem {
+  void* base = nullptr;      // start of the (double) mapping
+  size_t capacity = 0;       // bytes of physical ring (mapping covers 2x when double_mapped)
+  bool double_mapped = false;
+  void* impl = nullptr;      // backend bookkeeping
+};
+
+struct SrpcDeviceOps {
+  int (*device_count)();
+  int (*set_device)(int dev);
+  int (*stream_create)(int dev, cudaStream_t* s);
+  int (*stream_destroy)(cudaStream_t s);
+  int (*stream_sync)(cudaStream_t s);
+  int (*stream_query)(cudaStream_t s);  // 0 = idle, 1 = busy, <0 error
+  int (*stream_wait_value32)(cudaStream_t s, volatile uint32_t* d_addr, uint32_t value);
+  int (*stream_write_value32)(cudaStream_t s, volatile uint32_t* d_addr, uint32_t value);
+  int (*event_create)(cudaEvent_t* e);
+  int (*event_destroy)(cudaEvent_t e);
+  int (*ring_alloc)(int dev, size_t min_bytes, bool peer_access, SrpcRingMem* out);
+  int (*ring_free)(SrpcRingMem* m);
+  int (*host_alloc_mapped)(size_t bytes, void** host_ptr, void** dev_ptr);
+  int (*host_free)(void* host_ptr);
+  int (*dev_alloc)(int dev, size_t bytes, void** p);
+  int (*dev_free)(void* p);
+  int (*memcpy_async)(void* dst, const void* src, size_t n, cudaStream_t s);
+  int (*memset_async)(void* dst, int v, size_t n, cudaStream_t s);
+  int (*graph_launch)(cudaGraphExec_t g, cudaStream_t s);
+  const char* (*last_error)();
+};
+
+// Implemented by the CUDA half; returns nullptr when the library was built
+// without it.
+extern "C" const SrpcDeviceOps* srpc_cuda_ops();
+
+static inline const SrpcDeviceOps* srpc_require_cuda(const char* what) {
+  const SrpcDeviceOps* ops = srpc_cuda_ops();
+  if (!ops) {
+    srpc_log(SRPC_LOG_ERROR, "%s needs the CUDA half of the library, which is not available", what);
+    std::abort();
+  }
+  return ops;
+}
+
+// ------------------------------------------------------------------ ring memory
+static inline size_t find_lcm(size_t a, size_t b) { return a / std::gcd(a, b) * b; }
+
+// Host ring mapped twice back to back with memfd + MAP_FIXED.
+static inline bool srpc_host_ring_alloc(size_t min_bytes, SrpcRingMem* out) {
+  size_t page = (size_t)sysconf(_SC_PAGESIZE);
+  size_t cap = (min_bytes + page - 1) / page * page;
+  int fd = memfd_create("splitrpc_ring", 0);
+  if (fd < 0) return false;
+  if (ftruncate(fd, (off_t)cap) != 0) {
+    close(fd);
+    return false;
+  }
+  void* va = mmap(nullptr, 2 * cap, PROT_NONE, MAP_PRIVATE | MAP_ANONYMOUS, -1, 0);
+  if (va == MAP_FAILED) {
+    close(fd);
+    return false;
+  }
+  void* a = mmap(va, cap, PROT_READ | PROT_WRITE, MAP_SHARED | MAP_FIXED, fd, 0);
+  void* b = mmap((uint8_t*)va + cap, cap, PROT_READ | PROT_WRITE, MAP_SHARED | MAP_FIXED, fd, 0);
+  close(fd);
+  if (a == MAP_FAILED || b == MAP_FAILED) {
+    munmap(va, 2 * cap);
+    return false;
+  }
+  out->base = va;
+  out->capacity = cap;
+  out->double_mapped = true;
+  out->impl = nullptr;
+  return true;
+}
+static inline void srpc_host_ring_free(SrpcRingMem* m) {
+  if (m->base) munmap(m->base, 2 * m->capacity);
+  m->base = nullptr;
+}
+
+// Request ring, response ring and per-slot state words of one app.
+// On a GPU the rings are CUDA virtual-memory allocations mapped twice (and made
+// accessible to every peer GPU when `peer_access` is set); the state words live
+// in mapped pinned host memory so that the host can poll them and a GPU stream
+// (or a peer GPU) can wait on or write them.
+class P2pRpcAppRrMemPool {
+  int device_id_;
+  SrpcRingMem req_{}, resp_{};
+  volatile uint32_t* h_doorbells_ = nullptr;
+  volatile uint32_t* d_doorbells_ = nullptr;
+  size_t n_doorbells_ = 0;
+
+ public:
+  P2pRpcAppRrMemPool(int pool_size, int device_id, size_t req_size, size_t resp_size, bool peer_access = true)
+      : device_id_(device_id), n_doorbells_((size_t)pool_size) {
+    size_t req_bytes = (size_t)pool_size * req_size, resp_bytes = (size_t)pool_size * resp_size;
+    if (device_id < 0) {
+      if (!srpc_host_ring_alloc(req_bytes, &req_) || !srpc_host_ring_alloc(resp_bytes, &resp_)) {
+        srpc_log(SRPC_LOG_ERROR, "host ring allocation failed (%zu + %zu bytes)", req_bytes, resp_bytes);
+        std::abort();
+      }
+      void* p = nullptr;
+      if (posix_memalign(&p, 64, n_doorbells_ * sizeof(uint32_t)) != 0) std::abort();
+      h_doorbells_ = d_doorbells_ = (volatile uint32_t*)p;
+    } else {
+      const SrpcDeviceOps* ops = srpc_require_cuda("a GPU request ring");
+      if (ops->ring_alloc(device_id, req_bytes, peer_access, &req_) != 0 ||
+          ops->ring_alloc(device_id, resp_bytes, peer_access, &resp_) != 0) {
+        srpc_log(SRPC_LOG_ERROR, "GPU ring allocation failed: %s", ops->last_error());
+        std::abort();
+      }
+      void *h = nullptr, *d = nullptr;
+      if (ops->host_alloc_mapped(n_doorbells_ * sizeof(uint32_t), &h, &d) != 0) std::abort();
+      h_doorbells_ = (volatile uint32_t*)h;
+      d_doorbells_ = (volatile uint32_t*)d;
+    }
+    for (size_t i = 0; i < n_doorbells_; i++) h_doorbells_[i] = APP_RR_STATUS::FREE;
+  }
+  ~P2pRpcAppRrMemPool() {
+    if (device_id_ < 0) {
+      srpc_host_ring_free(&req_);
+      srpc_host_ring_free(&resp_);
+      free((void*)h_doorbells_);
+    } else if (const SrpcDeviceOps* ops = srpc_cuda_ops()) {
+      ops->ring_free(&req_);
+      ops->ring_free(&resp_);
+      ops->host_free((void*)h_doorbells_);
+    }
+  }
+  void* get_req_addr_range() const { return req_.base; }
+  void* get_resp_addr_range() const { return resp_.base; }
+  size_t get_req_addr_pool_size() const { return req_.capacity; }
+  size_t get_resp_addr_pool_size() const { return resp_.capacity; }
+  bool is_double_mapped() const { return req_.double_mapped && resp_.double_mapped; }
+  volatile uint32_t* get_doorbells_host() const { return h_doorbells_; }
+  volatile uint32_t* get_doorbells_device() const { return d_doorbells_; }
+};
+
+// ------------------------------------------------------------------ app slots
+class P2pRpcAppRr {
+ public:
+  g_params* h_stub = nullptr;
+  g_params* d_stub = nullptr;
+  volatile uint32_t* h_state = nullptr;
+  volatile uint32_t* d_state = nullptr;
+  size_t req_size = 0, resp_size = 0;
+  void* rpc_rr = nullptr;  // transport-side record this slot currently serves
+  int rr_idx = 0;
+
+  void print_app_rr_info() const {
+    std::printf("app_rr %p idx=%d req=%p resp=%p state=%u\n", (const void*)this, rr_idx, (void*)h_stub->req,
+                (void*)h_stub->resp, h_state ? *h_state : 0u);
+  }
+};
+
+// N slots over the two rings.  get_next() hands the producer the next slot and
+// binds it to the next req/resp addresses of the rings (reference
+// src/p2p_rpc_app_rr.h:82-191).
+class P2pRpcAppRrPool {
+  int pool_size_;
+  int device_id_;
+  g_params* h_stubs_ = nullptr;
+  g_params* d_stubs_ = nullptr;
+  P2pRpcTring *req_pool_, *resp_pool_;
+  size_t pi_idx_ = 0;
+  bool stubs_mapped_ = false;
+
+ public:
+  size_t req_size, resp_size;
+  P2pRpcAppRr* rr_pool;
+  P2pRpcAppRrMemPool* rr_mem_pool;
+
+  P2pRpcAppRrPool(int pool_size, int device_id, size_t _req_size, size_t _resp_size)
+      : pool_size_(pool_size), device_id_(device_id), req_size(_req_size), resp_size(_resp_size) {
+    rr_pool = new P2pRpcAppRr[pool_size];
+    rr_mem_pool = new P2pRpcAppRrMemPool(pool_size, device_id, req_size, resp_size);
+    req_pool_ = new P2pRpcTring(rr_mem_pool->get_req_addr_range(), rr_mem_pool->get_req_addr_pool_size());
+    resp_pool_ = new P2pRpcTring(rr_mem_pool->get_resp_addr_range(), rr_mem_pool->get_resp_addr_pool_size());
+    if (device_id >= 0) {
+      // Slot stubs in mapped pinned memory: kernels that read the stub indirectly
+      // (graph replay, persistent kernels) see host updates without a copy.
+      void *h = nullptr, *d = nullptr;
+      if (srpc_require_cuda("slot stubs")->host_alloc_mapped(sizeof(g_params) * pool_size, &h, &d) != 0) std::abort();
+      h_stubs_ = (g_params*)h;
+      d_stubs_ = (g_params*)d;
+      stubs_mapped_ = true;
+    } else {
+      h_stubs_ = d_stubs_ = new g_params[pool_size];
+    }
+    volatile uint32_t* hs = rr_mem_pool->get_doorbells_host();
+    volatile uint32_t* ds = rr_mem_pool->get_doorbells_device();
+    for (int i = 0; i < pool_size; i++) {
+      P2pRpcAppRr& r = rr_pool[i];
+      r.req_size = req_size;
+      r.resp_size = resp_size;
+      r.h_stub = &h_stubs_[i];
+      r.d_stub = &d_stubs_[i];
+      r.h_state = &hs[i];
+      r.d_state = &ds[i];
+      r.h_stub->req = nullptr;
+      r.h_stub->resp = nullptr;
+      r.rr_idx = i;
+    }
+  }
+  ~P2pRpcAppRrPool() {
+    delete req_pool_;
+    delete resp_pool_;
+    if (stubs_mapped_) {
+      if (const SrpcDeviceOps* ops = srpc_cuda_ops()) ops->host_free(h_stubs_);
+    } else {
+      delete[] h_stubs_;
+    }
+    delete rr_mem_pool;
+    delete[] rr_pool;
+  }
+
+  int get_pool_size() const { return pool_size_; }
+  int get_device_id() const { return device_id_; }
+  P2pRpcAppRr* get_app_rr_pool() { return rr_pool; }
+  P2pRpcAppRr* get_app_rr(int idx) { return (idx >= 0 && idx < pool_size_) ? &rr_pool[idx] : nullptr; }
+  void init_pool() {
+    pi_idx_ = 0;
+    req_pool_->reset();
+    resp_pool_->reset();
+  }
+  size_t producer_index() const { return pi_idx_; }
+
+  P2pRpcAppRr* get_next() {
+    P2pRpcAppRr* r = &rr_pool[pi_idx_];
+    r->h_stub->req = (uint8_t*)req_pool_->get_next(req_size);
+    r->h_stub->resp = (uint8_t*)resp_pool_->get_next(resp_size);
+    pi_idx_ = (pi_idx_ + 1) % (size_t)pool_size_;
+    return r;
+  }
+};
+
+// ------------------------------------------------------------------ app context
+// Execution context handed to the four app callbacks (reference
+// src/p2p_rpc_app_ctx.h:24-112).  The doorbell is one word shared by host and
+// device: UINT_MAX = armed/idle, 1 = run finished (written from the stream),
+// 2 = persistent kernel finished, batch size = start signal for a persistent app.
+template <class T>
+class MetaAppCtx {
+ public:
+  T* h_stub = nullptr;
+  T* d_stub = nullptr;
+  uint32_t* door_bell = nullptr;
+  uint32_t* d_door_bell = nullptr;
+  void* app_ctx_internal = nullptr;
+  int curr_batch_size = 1;
+  int next_batch_size = 1;
+  cudaStream_t work_stream = nullptr;
+  cudaEvent_t work_complete = nullptr;
+  void* curr_rr = nullptr;
+  uint8_t launch_type = 1;  // 0 none, 1 kernel, 2 device-side launch, 3 persistent kernel, 4 CUDA graph
+  int device_id = -1;
+  bool graphCreated = false;
+  cudaGraph_t graph = nullptr;
+  cudaGraphExec_t instance = nullptr;
+  uint64_t wait_budget_ns = 2000000000ull;  // bound on every host-side spin
+  int last_status = 0;                      // 0 ok, -1 a bounded wait ran out
+
+  // Makes the work stream wait until *d_state == value.
+  void AppRrRunNotify(volatile uint32_t* d_state, int value) {
+    if (device_id >= 0) {
+      srpc_require_cuda("stream wait")->stream_wait_value32(work_stream, d_state, (uint32_t)value);
+    } else {
+      last_status = spin_until(d_state, (uint32_t)value) ? 0 : -1;
+    }
+  }
+  void AppRunNotify(int value) { AppRrRunNotify((volatile uint32_t*)d_door_bell, value); }
+
+  // Writes `value` into the doorbell once everything queued so far has finished.
+  void AppCompleteNotify(uint32_t value = 2) {
+    if (device_id >= 0) {
+      srpc_require_cuda("stream write")->stream_write_value32(work_stream, (volatile uint32_t*)d_door_bell, value);
+    } else {
+      __atomic_store_n(door_bell, value, __ATOMIC_RELEASE);
+    }
+  }
+  // Start signal for a resident app kernel: the batch size with the start bit set
+  // (so that batch sizes 1..3 cannot be mistaken for the status values).
+  void NotifyAppRunStart() {
+    __atomic_store_n(door_bell, APP_DOORBELL_START | (uint32_t)curr_batch_size, __ATOMIC_SEQ_CST);
+  }
+  bool IsAppRunComplete() const { return __atomic_load_n(door_bell, __ATOMIC_ACQUIRE) == 1u; }
+  void ResetAppRunStatus() { __atomic_store_n(door_bell, (uint32_t)UINT_MAX, __ATOMIC_SEQ_CST); }
+
+  // Returns false when the bounded wait ran out.
+  bool WaitForAppRunComplete() {
+    if (launch_type == 3) return spin_until((volatile uint32_t*)door_bell, 2u);
+    if (device_id >= 0) return srpc_require_cuda("stream sync")->stream_sync(work_stream) == 0;
+    return true;
+  }
+
+ private:
+  bool spin_until(volatile uint32_t* p, uint32_t v) const {
+    uint64_t t0 = getCurNs();
+    uint32_t spins = 0;
+    while (__atomic_load_n(p, __ATOMIC_ACQUIRE) != v) {
+      if ((++spins & 0x3FF) == 0 && getCurNs() - t0 > wait_budget_ns) return false;
+    }
+    return true;
+  }
+};
+
+typedef MetaAppCtx<g_params> AppCtx;
+using AppInitCB = int (*)(AppCtx*);
+using AppRunCB = int (*)(AppCtx*);
+using AppCleanupCB = int (*)(AppCtx*);
+using AppRunAsyncCB = int (*)(AppCtx*);
+using AppRunWaitCB = int (*)(AppCtx*);
+using AppCompleteCB = int (*)(AppCtx*);

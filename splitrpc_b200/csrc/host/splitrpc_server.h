@@ -1,0 +1,345 @@
+// Server process wiring: receive thread, shunter thread, one worker per replica.
+//
+// Same three-stage host pipeline as reference
+// src/splitrpc_server/p2p_rpc_dpdk_server.cc:45-197 — the receive loop parses
+// 64-byte headers and reassembles by token, the shunter moves ready requests
+// into app ring slots through a scatter-gather engine and sends finished
+// responses, the worker runs the app over the slot ring — generalised to several
+// replicas (one app instance per GPU) with flow steering between them, and with
+// bounded waits, reassembly timeouts and back-pressure counters instead of
+// unbounded spins.  The CPU never reads or writes payload bytes here: it passes
+// pointers to the engines.
+#pragma once
+
+#include <thread>
+
+#include "p2p_rpc_async_app_server.h"
+#include "p2p_rpc_sg_engine.h"
+#include "transport.h"
+
+struct ServerConfig {
+  std::string server_uri = "b8:ce:f6:cc:6a:52,192.168.25.1,50051";
+  size_t req_size = 1024, resp_size = 1024;
+  int server_mode = 0;      // 0 sync fixed batch, 1 async (stream armed), 2 dynamic batching
+  int max_batch = 1;        // fixed batch (modes 0/1) or upper bound (mode 2)
+  int zerocopy = 0;         // 1 = serve out of the receive buffers (single-fragment requests)
+  int rr_pool_size = 4095;
+  uint64_t reassembly_timeout_ns = 200000000ull;
+  int steer_policy = 0;     // 0 = round robin in runs of max_batch, 1 = least outstanding
+  int gather_burst = 64;    // requests per scatter-gather submission
+};
+
+struct ReplicaStats {
+  uint64_t steered = 0, completed = 0, ring_full = 0;
+};
+
+struct ServerStats {
+  uint64_t rx_pkts = 0, rx_reqs = 0, tx_resps = 0, tx_pkts = 0, dropped_pkts = 0, expired = 0, ring_full = 0,
+           tx_alloc_fail = 0, sg_errors = 0;
+  std::vector<ReplicaStats> replicas;
+};
+
+class SplitRpcServer {
+  struct Replica {
+    P2pRpcAppInfo* app = nullptr;
+    P2pRpcSgEngine* engine = nullptr;
+    int app_idx = -1;
+    int tx_idx = 0;                        // next slot whose response goes out
+    std::atomic<int> outstanding{0};
+    std::atomic<bool> down{false};         // steering skips a replica marked down
+    ReplicaStats stats;
+    std::thread worker;
+  };
+
+  Transport* port_;
+  ServerConfig cfg_;
+  p2p_rpc_conn_info* server_conn_ = nullptr;
+  P2pRpcRRPool rr_pool_;
+  P2pRpcAsyncAppServer app_server_;
+  std::vector<std::unique_ptr<Replica>> replicas_;
+  std::thread rx_thread_, shunter_thread_;
+  std::atomic<bool> quit_{false};
+  std::atomic<bool> running_{false};
+  struct LiveStats {
+    std::atomic<uint64_t> rx_pkts{0}, rx_reqs{0}, tx_resps{0}, tx_pkts{0}, dropped_pkts{0}, expired{0}, ring_full{0},
+        tx_alloc_fail{0}, sg_errors{0};
+  } stats_;
+  int rr_cursor_ = 0, rr_run_ = 0;
+  // Per transport record: the packets it holds (for release) — indexed through
+  // transport_mbufs as slot+1 so that 0 means "none".
+  size_t resp_frags_;
+
+  void rx_loop() {
+    std::vector<SrpcPkt> pkts(1024);
+    uint64_t last_sweep = getCurNs();
+    while (!quit_.load(std::memory_order_acquire)) {
+      int n = port_->rx_burst(pkts.data(), (int)pkts.size());
+      for (int i = 0; i < n; i++) {
+        SrpcPkt& p = pkts[i];
+        stats_.rx_pkts++;
+        P2pRpcRr* rr = rr_pool_.append_to_rr(p.hdr, (uintptr_t)p.slot + 1, (uintptr_t)port_->rx_dev_ptr(p), p.len);
+        if (!rr) {
+          stats_.dropped_pkts++;
+          port_->release_rx(&p, 1);
+          continue;
+        }
+        if (rr->is_rr_ready()) {
+          rr_pool_.mark_rx_ready_rr(rr);
+          stats_.rx_reqs++;
+        } else if (rr->payload_size > rr->max_payload_size) {
+          // More bytes than the app's request size: protocol violation, drop.
+          release_rr_rx(rr);
+          rr_pool_.drop_partial(rr);
+          stats_.dropped_pkts++;
+        }
+      }
+      uint64_t now = getCurNs();
+      if (now - last_sweep > cfg_.reassembly_timeout_ns / 4 + 1) {
+        last_sweep = now;
+        stats_.expired += rr_pool_.expire_stale(now, cfg_.reassembly_timeout_ns, [this](P2pRpcRr* rr) { release_rr_rx(rr); });
+      }
+    }
+  }
+
+  void release_rr_rx(P2pRpcRr* rr) {
+    for (size_t i = 0; i < rr->transport_mbufs->num_items; i++) {
+      uintptr_t h = rr->transport_mbufs->burst_items[i];
+      if (!h) continue;
+      SrpcPkt p;
+      p.slot = (uint32_t)(h - 1);
+      port_->release_rx(&p, 1);
+      rr->transport_mbufs->burst_items[i] = 0;
+    }
+  }
+
+  int pick_replica() {
+    int n = (int)replicas_.size();
+    if (n == 1) return replicas_[0]->down.load() ? -1 : 0;
+    if (cfg_.steer_policy == 1) {
+      int best = -1, best_out = INT_MAX;
+      for (int i = 0; i < n; i++) {
+        if (replicas_[i]->down.load()) continue;
+        int o = replicas_[i]->outstanding.load(std::memory_order_relaxed);
+        if (o < best_out) {
+          best_out = o;
+          best = i;
+        }
+      }
+      return best;
+    }
+    // Round robin in runs of max_batch so that a replica receives whole batches.
+    for (int tries = 0; tries < n; tries++) {
+      if (rr_run_ >= cfg_.max_batch) {
+        rr_run_ = 0;
+        rr_cursor_ = (rr_cursor_ + 1) % n;
+      }
+      if (!replicas_[rr_cursor_]->down.load()) {
+        rr_run_++;
+        return rr_cursor_;
+      }
+      rr_run_ = cfg_.max_batch;
+    }
+    return -1;
+  }
+
+  // Prepares the response side of a record: transmit buffers + reply headers.
+  bool prepare_tx(P2pRpcRr* rr) {
+    std::vector<SrpcPkt> tx(resp_frags_);
+    if (!port_->alloc_tx(tx.data(), (int)resp_frags_)) return false;
+    rr->clear_bufs();
+    size_t left = cfg_.resp_size, mtu = rpc_mtu();
+    for (size_t i = 0; i < resp_frags_; i++) {
+      size_t len = left < mtu ? left : mtu;
+      left -= len;
+      fill_frag_hdr(tx[i].hdr, &rr->_client_conn_info, rr->req_token, (uint16_t)i, (uint16_t)len, true);
+      rr->rr_append_mbuf((uintptr_t)tx[i].slot + 1, (uintptr_t)tx[i].hdr, (uintptr_t)tx[i].payload, len);
+    }
+    return true;
+  }
+
+  void shunter_loop() {
+    const int burst = cfg_.gather_burst;
+    std::vector<P2pRpcRr*> rrs((size_t)burst);
+    std::vector<g_params*> stubs((size_t)burst);
+    std::vector<P2pRpcAppRr*> slots((size_t)burst);
+    P2pRpcRr* pending = nullptr;  // a ready request that found its replica's ring full
+    while (!quit_.load(std::memory_order_acquire)) {
+      // ---- RX half: ready requests -> app ring slots
+      int target = -1, nb = 0;
+      while (nb < burst) {
+        P2pRpcRr* rr = pending ? pending : rr_pool_.get_next_rx_ready_rr();
+        if (!rr) break;
+        int t = pending ? rr->steer_target : pick_replica();
+        pending = nullptr;
+        if (t < 0) {  // every replica is down: drop the request
+          release_rr_rx(rr);
+          rr_pool_.reap_rr(rr);
+          stats_.dropped_pkts++;
+          continue;
+        }
+        rr->steer_target = t;
+        if (target >= 0 && t != target) {  // one submission serves one replica
+          pending = rr;
+          break;
+        }
+        Replica& rep = *replicas_[t];
+        // The next producer slot is bound to ring addresses only once it is free.
+        P2pRpcAppRrPool* arp = rep.app->app_rr_pool;
+        P2pRpcAppRr* slot = arp->get_app_rr((int)arp->producer_index());
+        if (__atomic_load_n(slot->h_state, __ATOMIC_ACQUIRE) != APP_RR_STATUS::FREE) {
+          rep.stats.ring_full++;
+          stats_.ring_full++;
+          pending = rr;
+          break;
+        }
+        target = t;
+        slot = arp->get_next();
+        rrs[nb] = rr;
+        stubs[nb] = slot->h_stub;
+        slots[nb] = slot;
+        slot->rpc_rr = rr;
+        rr->app_rr_idx = slot->rr_idx;
+        nb++;
+      }
+      if (nb > 0) {
+        Replica& rep = *replicas_[target];
+        int rc = rep.engine->gather_batch(rrs.data(), stubs.data(), nb);
+        if (rc != 0) stats_.sg_errors++;
+        for (int i = 0; i < nb; i++) {
+          if (!cfg_.zerocopy) {
+            release_rr_rx(rrs[i]);
+            if (!prepare_tx(rrs[i])) stats_.tx_alloc_fail++;
+          }
+          __atomic_store_n(slots[i]->h_state, (uint32_t)APP_RR_STATUS::RX_COMPLETE, __ATOMIC_RELEASE);
+        }
+        rep.outstanding.fetch_add(nb);
+        rep.stats.steered += (uint64_t)nb;
+      }
+      // ---- TX half: finished slots -> responses
+      for (auto& rep_ptr : replicas_) {
+        Replica& rep = *rep_ptr;
+        int nt = 0;
+        const int pool_n = rep.app->app_rr_pool->get_pool_size();
+        while (nt < burst) {
+          P2pRpcAppRr* slot = rep.app->app_rr_pool->get_app_rr((rep.tx_idx + nt) % pool_n);
+          if (__atomic_load_n(slot->h_state, __ATOMIC_ACQUIRE) != APP_RR_STATUS::WORK_COMPLETE) break;
+          rrs[nt] = (P2pRpcRr*)slot->rpc_rr;
+          stubs[nt] = slot->h_stub;
+          slots[nt] = slot;
+          nt++;
+        }
+        if (nt == 0) continue;
+        if (cfg_.zerocopy) {
+          send_zerocopy(rep, rrs.data(), slots.data(), nt);
+        } else {
+          int rc = rep.engine->scatter_batch(rrs.data(), stubs.data(), nt);
+          if (rc != 0) stats_.sg_errors++;
+          for (int i = 0; i < nt; i++) {
+            P2pRpcRr* rr = rrs[i];
+            std::vector<SrpcPkt> tx(rr->transport_mbufs->num_items);
+            for (size_t k = 0; k < tx.size(); k++) {
+              tx[k].slot = (uint32_t)(rr->transport_mbufs->burst_items[k] - 1);
+              tx[k].hdr = (p2p_rpc_hdr*)rr->hdr_bufs->burst_items[k];
+              tx[k].payload = (uint8_t*)rr->payload_bufs->burst_items[k];
+              tx[k].len = (uint32_t)rr->payload_bufs->item_size[k];
+            }
+            stats_.tx_pkts += (uint64_t)port_->tx_burst(tx.data(), (int)tx.size());
+            stats_.tx_resps++;
+            rr_pool_.reap_rr(rr);
+          }
+        }
+        for (int i = 0; i < nt; i++) {
+          slots[i]->rpc_rr = nullptr;
+          __atomic_store_n(slots[i]->h_state, (uint32_t)APP_RR_STATUS::FREE, __ATOMIC_RELEASE);
+        }
+        rep.tx_idx = (rep.tx_idx + nt) % pool_n;
+        rep.outstanding.fetch_sub(nt);
+        rep.stats.completed += (uint64_t)nt;
+      }
+    }
+  }
+
+  // Zero-copy replies: the app answered in the receive buffer; build the reply
+  // header by swapping the request header in place and send header + the first
+  // resp_size bytes of the same buffer back.
+  void send_zerocopy(Replica&, P2pRpcRr** rrs, P2pRpcAppRr** slots, int n) {
+    for (int i = 0; i < n; i++) {
+      P2pRpcRr* rr = rrs[i];
+      p2p_rpc_hdr h;
+      fill_frag_hdr(&h, &rr->_client_conn_info, rr->req_token, 0, (uint16_t)cfg_.resp_size, true);
+      const uint8_t* payload = port_->rx_host_ptr((uint32_t)(rr->transport_mbufs->burst_items[0] - 1));
+      uint32_t len = (uint32_t)cfg_.resp_size;
+      stats_.tx_pkts += (uint64_t)port_->tx_copy(&h, &payload, &len, 1);
+      stats_.tx_resps++;
+      release_rr_rx(rr);
+      rr_pool_.reap_rr(rr);
+      (void)slots;
+    }
+  }
+
+ public:
+  SplitRpcServer(Transport* port, const ServerConfig& cfg)
+      : port_(port), cfg_(cfg), rr_pool_(cfg.rr_pool_size), resp_frags_(num_fragments(cfg.resp_size, rpc_mtu())) {
+    server_conn_ = initialize_src_conn_info(cfg.server_uri);
+    rr_pool_.setup_and_init_rr_pool(server_conn_, cfg.req_size);
+  }
+  ~SplitRpcServer() {
+    stop();
+    release_conn_info(server_conn_);
+  }
+
+  // Adds a replica: an app instance (its own slot ring) and the engine that
+  // fills that ring.  Returns the replica index.
+  int add_replica(P2pRpcAppInfo* app, P2pRpcSgEngine* engine) {
+    auto r = std::make_unique<Replica>();
+    r->app = app;
+    r->engine = engine;
+    r->app_idx = app_server_.register_app(app);
+    app->app_rr_pool->init_pool();
+    replicas_.push_back(std::move(r));
+    return (int)replicas_.size() - 1;
+  }
+  P2pRpcAsyncAppServer& app_server() { return app_server_; }
+  P2pRpcRRPool& rr_pool() { return rr_pool_; }
+  void mark_replica_down(int idx, bool down) { replicas_[idx]->down.store(down); }
+
+  void start() {
+    if (running_.exchange(true)) return;
+    quit_.store(false);
+    app_server_.reset_quit();
+    for (auto& rp : replicas_) {
+      Replica* r = rp.get();
+      r->app->app_ctx->curr_batch_size = cfg_.max_batch;
+      r->app->app_ctx->next_batch_size = cfg_.max_batch;
+      r->worker = std::thread([this, r] {
+        switch (cfg_.server_mode) {
+          case 1: app_server_.async_worker_loop(r->app_idx); break;
+          case 2: app_server_.dynamic_batching_sync_worker_loop(r->app_idx, cfg_.max_batch); break;
+          default: app_server_.sync_worker_loop(r->app_idx); break;
+        }
+      });
+    }
+    rx_thread_ = std::thread([this] { rx_loop(); });
+    shunter_thread_ = std::thread([this] { shunter_loop(); });
+  }
+
+  void stop() {
+    if (!running_.exchange(false)) return;
+    quit_.store(true, std::memory_order_release);
+    app_server_.quit();
+    if (rx_thread_.joinable()) rx_thread_.join();
+    if (shunter_thread_.joinable()) shunter_thread_.join();
+    for (auto& rp : replicas_)
+      if (rp->worker.joinable()) rp->worker.join();
+  }
+
+  ServerStats stats() {
+    ServerStats s;
+    s.rx_pkts = stats_.rx_pkts; s.rx_reqs = stats_.rx_reqs; s.tx_resps = stats_.tx_resps; s.tx_pkts = stats_.tx_pkts;
+    s.dropped_pkts = stats_.dropped_pkts; s.expired = stats_.expired; s.ring_full = stats_.ring_full;
+    s.tx_alloc_fail = stats_.tx_alloc_fail; s.sg_errors = stats_.sg_errors;
+    for (auto& rp : replicas_) s.replicas.push_back(rp->stats);
+    return s;
+  }
+  WorkerStats worker_stats(int replica) { return app_server_.stats(replicas_[replica]->app_idx); }
+};

@@ -1,0 +1,462 @@
+// Packet transports behind one interface.
+//
+// The server only ever sees packets as {header pointer, payload pointer, length}
+// triples with the header and the payload in separate buffers ("header/data
+// split", reference src/transport/dpdk_init.cc:79-98): headers land in host
+// memory that the CPU parses, payloads land in a buffer arena the GPU can read.
+// Three back-ends implement the interface:
+//   LoopbackPort  in-process link that plays the NIC: the sender's tx_burst
+//                 writes header and payload into the receiver's arenas exactly
+//                 like a DMA engine would, with optional fault injection;
+//   UdpPort       kernel UDP sockets (reference src/transport/udp_rx_tx.h:15-93),
+//                 22-byte header on the wire;
+//   DpdkPort      placeholder for a DPDK + GPUDirect RDMA port (reference
+//                 src/transport/dpdk_init.cc:309-398); not buildable without
+//                 DPDK, creation reports that.
+#pragma once
+
+#include <netinet/in.h>
+#include <sys/socket.h>
+
+#include <functional>
+#include <memory>
+
+#include "mpmc_ring.h"
+#include "p2p_rpc.h"
+
+struct SrpcPkt {
+  p2p_rpc_hdr* hdr = nullptr;   // 64-byte header in host memory
+  uint8_t* payload = nullptr;   // payload location (host view when it is host memory)
+  uint32_t len = 0;             // payload bytes
+  uint32_t slot = 0;            // arena slot index (transport bookkeeping)
+};
+
+struct TransportCounters {
+  std::atomic<uint64_t> rx_pkts{0}, tx_pkts{0}, rx_bytes{0}, tx_bytes{0}, tx_dropped{0}, rx_runts{0},
+      arena_full{0}, injected_faults{0};
+};
+
+// Memory the payload arena of a port lives in.  `host` is what the emulated NIC
+// (or the socket layer) writes through; `dev` is the address the GPU uses for the
+// same bytes (equal to host for plain host memory).
+struct ArenaMem {
+  uint8_t* host = nullptr;
+  uint8_t* dev = nullptr;
+  size_t bytes = 0;
+  std::function<void()> release;  // frees the memory when the arena dies
+};
+
+static inline ArenaMem make_malloc_arena(size_t bytes) {
+  ArenaMem m;
+  void* p = nullptr;
+  if (posix_memalign(&p, 4096, bytes) != 0) std::abort();
+  std::memset(p, 0, bytes);
+  m.host = m.dev = (uint8_t*)p;
+  m.bytes = bytes;
+  m.release = [p] { free(p); };
+  return m;
+}
+
+// Fixed-size slots handed out in ring order, so the fragments of one message
+// occupy consecutive slots and adjacent payloads coalesce into one copy.  Headers
+// live in a parallel host array with the same slot index.
+class PktArena {
+  ArenaMem mem_;
+  size_t slot_bytes_, n_slots_;
+  std::unique_ptr<p2p_rpc_hdr[]> hdrs_;
+  std::unique_ptr<std::atomic<uint8_t>[]> busy_;
+  std::atomic<uint64_t> next_{0};
+  std::mutex claim_mu_;
+
+ public:
+  PktArena(ArenaMem mem, size_t slot_bytes) : mem_(std::move(mem)), slot_bytes_(slot_bytes) {
+    n_slots_ = mem_.bytes / slot_bytes_;
+    hdrs_.reset(new p2p_rpc_hdr[n_slots_]);
+    busy_.reset(new std::atomic<uint8_t>[n_slots_]);
+    for (size_t i = 0; i < n_slots_; i++) busy_[i].store(0);
+  }
+  ~PktArena() {
+    if (mem_.release) mem_.release();
+  }
+  size_t num_slots() const { return n_slots_; }
+  size_t slot_bytes() const { return slot_bytes_; }
+  uint8_t* host_base() const { return mem_.host; }
+  uint8_t* dev_base() const { return mem_.dev; }
+  size_t bytes() const { return mem_.bytes; }
+  uint8_t* host_ptr(uint32_t slot) const { return mem_.host + (size_t)slot * slot_bytes_; }
+  uint8_t* dev_ptr(uint32_t slot) const { return mem_.dev + (size_t)slot * slot_bytes_; }
+  p2p_rpc_hdr* hdr_ptr(uint32_t slot) const { return &hdrs_[slot]; }
+  uint8_t* to_dev(const uint8_t* host) const { return mem_.dev + (host - mem_.host); }
+  uint8_t* to_host(const uint8_t* dev) const { return mem_.host + (dev - mem_.dev); }
+
+  // Claims n consecutive slots (they may wrap around the end of the arena).
+  // Fails without side effects when any of them is still in use.
+  bool claim(uint32_t n, uint32_t* first) {
+    std::lock_guard<std::mutex> g(claim_mu_);
+    uint64_t start = next_.load(std::memory_order_relaxed);
+    if (n > n_slots_) return false;
+    for (uint32_t i = 0; i < n; i++)
+      if (busy_[(start + i) % n_slots_].load(std::memory_order_acquire)) return false;
+    for (uint32_t i = 0; i < n; i++) busy_[(start + i) % n_slots_].store(1, std::memory_order_relaxed);
+    next_.store(start + n, std::memory_order_relaxed);
+    *first = (uint32_t)(start % n_slots_);
+    return true;
+  }
+  void release(uint32_t slot) { busy_[slot % n_slots_].store(0, std::memory_order_release); }
+  size_t in_use() const {
+    size_t c = 0;
+    for (size_t i = 0; i < n_slots_; i++) c += busy_[i].load(std::memory_order_relaxed);
+    return c;
+  }
+};
+
+class Transport {
+ public:
+  TransportCounters counters;
+  virtual ~Transport() = default;
+  // Receives up to `max` packets; never blocks.
+  virtual int rx_burst(SrpcPkt* out, int max) = 0;
+  // Hands buffers of received packets back to the port.
+  virtual void release_rx(const SrpcPkt* pkts, int n) = 0;
+  // Reserves n transmit buffers (consecutive slots); payload pointers are
+  // device-view addresses a GPU may write.  Returns false when the arena is full.
+  virtual bool alloc_tx(SrpcPkt* out, int n) = 0;
+  // Sends packets whose headers and payloads were filled in place in buffers from
+  // alloc_tx.  Returns how many were accepted; the buffers are released.
+  virtual int tx_burst(const SrpcPkt* pkts, int n) = 0;
+  // Sends packets whose payload lives anywhere in host memory (client side).
+  virtual int tx_copy(const p2p_rpc_hdr* hdrs, const uint8_t* const* payloads, const uint32_t* lens, int n) = 0;
+  virtual const char* name() const = 0;
+  // Device-view address of a received payload (identity for host arenas).
+  virtual uint8_t* rx_dev_ptr(const SrpcPkt& p) const { return p.payload; }
+  virtual uint8_t* tx_host_ptr(const SrpcPkt& p) const { return p.payload; }
+  // Host-view address of the payload buffer of receive slot `slot`.
+  virtual uint8_t* rx_host_ptr(uint32_t slot) const = 0;
+};
+
+// ------------------------------------------------------------------ loopback
+// Host-side fault injector of the loopback link.  Probabilities are per packet;
+// reorder swaps a packet with its successor in the same burst; truncate shortens
+// the payload by `truncate_bytes`.
+struct LoopbackFaults {
+  double drop = 0, duplicate = 0, reorder = 0, truncate = 0;
+  uint32_t truncate_bytes = 1;
+  bool zero_token = false;       // stamp token 0 on every packet
+  int force_seq = -1;            // overwrite seq_num (e.g. with an out-of-range value)
+  uint64_t seed = 99;
+};
+
+class LoopbackPort;
+
+class LoopbackLink {
+ public:
+  LoopbackFaults faults_to_server, faults_to_client;
+};
+
+class LoopbackPort : public Transport {
+  std::unique_ptr<PktArena> rx_arena_, tx_arena_;
+  MpmcRing<SrpcPkt> rx_ring_;
+  LoopbackPort* peer_ = nullptr;
+  LoopbackFaults faults_;  // applied to packets this port SENDS
+  SrpcRng rng_;
+  std::mutex tx_mu_;
+
+  // The emulated DMA: place one packet into the peer's receive arena.
+  bool deliver(const p2p_rpc_hdr* hdr, const uint8_t* payload_host, uint32_t len, uint32_t slot) {
+    PktArena* a = peer_->rx_arena_.get();
+    if (len > a->slot_bytes()) {
+      counters.tx_dropped++;
+      return false;
+    }
+    p2p_rpc_hdr* h = a->hdr_ptr(slot);
+    std::memcpy(h, hdr, RPC_HEADER_LEN);
+    if (len) std::memcpy(a->host_ptr(slot), payload_host, len);
+    SrpcPkt p;
+    p.hdr = h;
+    p.payload = a->host_ptr(slot);
+    p.len = len;
+    p.slot = slot;
+    std::atomic_thread_fence(std::memory_order_release);
+    if (!peer_->rx_ring_.push(p)) {
+      a->release(slot);
+      counters.tx_dropped++;
+      return false;
+    }
+    return true;
+  }
+
+  int send_list(const p2p_rpc_hdr* const* hdrs, const uint8_t* const* payloads, const uint32_t* lens, int n) {
+    std::lock_guard<std::mutex> g(tx_mu_);
+    // Fault injection happens "on the wire", before delivery.
+    std::vector<int> order;
+    order.reserve((size_t)n * 2);
+    for (int i = 0; i < n; i++) {
+      if (faults_.drop > 0 && rng_.uniform() < faults_.drop) {
+        counters.injected_faults++;
+        continue;
+      }
+      order.push_back(i);
+      if (faults_.duplicate > 0 && rng_.uniform() < faults_.duplicate) {
+        counters.injected_faults++;
+        order.push_back(i);
+      }
+    }
+    if (faults_.reorder > 0)
+      for (size_t i = 0; i + 1 < order.size(); i++)
+        if (rng_.uniform() < faults_.reorder) {
+          std::swap(order[i], order[i + 1]);
+          counters.injected_faults++;
+          i++;
+        }
+    if (order.empty()) return n;
+    uint32_t first = 0;
+    PktArena* a = peer_->rx_arena_.get();
+    if (!a->claim((uint32_t)order.size(), &first)) {
+      counters.arena_full++;
+      return 0;
+    }
+    for (size_t k = 0; k < order.size(); k++) {
+      int i = order[k];
+      uint32_t slot = (uint32_t)((first + k) % a->num_slots());
+      p2p_rpc_hdr h = *hdrs[i];
+      uint32_t len = lens[i];
+      if (faults_.zero_token) h.req_token = 0;
+      if (faults_.force_seq >= 0) h.seq_num = (uint16_t)faults_.force_seq;
+      if (faults_.truncate > 0 && rng_.uniform() < faults_.truncate) {
+        len = len > faults_.truncate_bytes ? len - faults_.truncate_bytes : 0;
+        counters.injected_faults++;
+      }
+      if (deliver(&h, payloads[i], len, slot)) {
+        counters.tx_pkts++;
+        counters.tx_bytes += len;
+      }
+    }
+    return n;
+  }
+
+ public:
+  LoopbackPort(ArenaMem rx_mem, ArenaMem tx_mem, size_t slot_bytes, size_t ring_depth = 65536)
+      : rx_arena_(new PktArena(std::move(rx_mem), slot_bytes)),
+        tx_arena_(new PktArena(std::move(tx_mem), slot_bytes)),
+        rx_ring_(ring_depth) {}
+
+  static void connect(LoopbackPort* a, LoopbackPort* b) {
+    a->peer_ = b;
+    b->peer_ = a;
+  }
+  void set_faults(const LoopbackFaults& f) {
+    faults_ = f;
+    rng_ = SrpcRng(f.seed);
+  }
+  PktArena* rx_arena() { return rx_arena_.get(); }
+  PktArena* tx_arena() { return tx_arena_.get(); }
+
+  int rx_burst(SrpcPkt* out, int max) override {
+    int n = 0;
+    while (n < max && rx_ring_.pop(out[n])) {
+      counters.rx_bytes += out[n].len;
+      n++;
+    }
+    counters.rx_pkts += (uint64_t)n;
+    return n;
+  }
+  void release_rx(const SrpcPkt* pkts, int n) override {
+    for (int i = 0; i < n; i++) rx_arena_->release(pkts[i].slot);
+  }
+  bool alloc_tx(SrpcPkt* out, int n) override {
+    uint32_t first = 0;
+    if (!tx_arena_->claim((uint32_t)n, &first)) {
+      counters.arena_full++;
+      return false;
+    }
+    for (int i = 0; i < n; i++) {
+      uint32_t s = (uint32_t)((first + i) % tx_arena_->num_slots());
+      out[i].slot = s;
+      out[i].hdr = tx_arena_->hdr_ptr(s);
+      out[i].payload = tx_arena_->dev_ptr(s);
+      out[i].len = 0;
+    }
+    return true;
+  }
+  int tx_burst(const SrpcPkt* pkts, int n) override {
+    if (!peer_) return 0;
+    std::vector<const p2p_rpc_hdr*> hdrs((size_t)n);
+    std::vector<const uint8_t*> pl((size_t)n);
+    std::vector<uint32_t> lens((size_t)n);
+    for (int i = 0; i < n; i++) {
+      hdrs[i] = pkts[i].hdr;
+      pl[i] = tx_arena_->host_ptr(pkts[i].slot);
+      lens[i] = pkts[i].len;
+    }
+    int sent = send_list(hdrs.data(), pl.data(), lens.data(), n);
+    for (int i = 0; i < n; i++) tx_arena_->release(pkts[i].slot);
+    return sent;
+  }
+  int tx_copy(const p2p_rpc_hdr* hdrs, const uint8_t* const* payloads, const uint32_t* lens, int n) override {
+    if (!peer_) return 0;
+    std::vector<const p2p_rpc_hdr*> hp((size_t)n);
+    for (int i = 0; i < n; i++) hp[i] = &hdrs[i];
+    return send_list(hp.data(), payloads, lens, n);
+  }
+  uint8_t* rx_dev_ptr(const SrpcPkt& p) const override { return rx_arena_->to_dev(p.payload); }
+  uint8_t* tx_host_ptr(const SrpcPkt& p) const override { return tx_arena_->to_host(p.payload); }
+  uint8_t* rx_host_ptr(uint32_t slot) const override { return rx_arena_->host_ptr(slot); }
+  const char* name() const override { return "loopback"; }
+};
+
+// ------------------------------------------------------------------ kernel UDP
+// Datagram = 22-byte UdpRpcHdr + payload.  The 64-byte in-memory header is
+// synthesised on receive (source address recorded in the L3/L4 fields) so the
+// layers above are transport agnostic.
+class UdpPort : public Transport {
+  int fd_ = -1;
+  std::unique_ptr<PktArena> rx_arena_, tx_arena_;
+  std::vector<uint8_t> scratch_, tx_scratch_;  // receive side / transmit side staging
+  std::mutex tx_mu_;
+  sockaddr_in default_dst_{};
+  bool has_dst_ = false;
+
+ public:
+  UdpPort(const char* bind_ip, int bind_port, size_t slot_bytes, size_t n_slots = 4096)
+      : rx_arena_(new PktArena(make_malloc_arena(slot_bytes * n_slots), slot_bytes)),
+        tx_arena_(new PktArena(make_malloc_arena(slot_bytes * n_slots), slot_bytes)),
+        scratch_(slot_bytes + RPC_HEADER_TAIL_LEN),
+        tx_scratch_(slot_bytes + RPC_HEADER_TAIL_LEN) {
+    fd_ = ::socket(AF_INET, SOCK_DGRAM | SOCK_NONBLOCK, 0);
+    int sz = 2 << 20;
+    setsockopt(fd_, SOL_SOCKET, SO_RCVBUF, &sz, sizeof(sz));
+    setsockopt(fd_, SOL_SOCKET, SO_SNDBUF, &sz, sizeof(sz));
+    sockaddr_in a{};
+    a.sin_family = AF_INET;
+    a.sin_port = htons((uint16_t)bind_port);
+    inet_pton(AF_INET, bind_ip, &a.sin_addr);
+    if (::bind(fd_, (sockaddr*)&a, sizeof(a)) != 0) {
+      srpc_log(SRPC_LOG_ERROR, "UdpPort: bind %s:%d failed", bind_ip, bind_port);
+      ::close(fd_);
+      fd_ = -1;
+    }
+  }
+  ~UdpPort() override {
+    if (fd_ >= 0) ::close(fd_);
+  }
+  bool ok() const { return fd_ >= 0; }
+  int bound_port() const {
+    sockaddr_in a{};
+    socklen_t l = sizeof(a);
+    getsockname(fd_, (sockaddr*)&a, &l);
+    return ntohs(a.sin_port);
+  }
+  void set_destination(const char* ip, int port) {
+    default_dst_.sin_family = AF_INET;
+    default_dst_.sin_port = htons((uint16_t)port);
+    inet_pton(AF_INET, ip, &default_dst_.sin_addr);
+    has_dst_ = true;
+  }
+
+  int rx_burst(SrpcPkt* out, int max) override {
+    int n = 0;
+    while (n < max) {
+      sockaddr_in from{};
+      socklen_t fl = sizeof(from);
+      ssize_t r = ::recvfrom(fd_, scratch_.data(), scratch_.size(), 0, (sockaddr*)&from, &fl);
+      if (r < 0) break;
+      if ((size_t)r < RPC_HEADER_TAIL_LEN) {
+        counters.rx_runts++;
+        continue;
+      }
+      uint32_t slot = 0;
+      if (!rx_arena_->claim(1, &slot)) {
+        counters.arena_full++;
+        break;
+      }
+      p2p_rpc_hdr* h = rx_arena_->hdr_ptr(slot);
+      std::memset(h, 0, sizeof(*h));
+      std::memcpy(get_req_tail(h), scratch_.data(), RPC_HEADER_TAIL_LEN);
+      get_ip_header(h)->src_ip = from.sin_addr.s_addr;
+      get_udp_header(h)->src_port = from.sin_port;
+      uint32_t len = (uint32_t)(r - (ssize_t)RPC_HEADER_TAIL_LEN);
+      std::memcpy(rx_arena_->host_ptr(slot), scratch_.data() + RPC_HEADER_TAIL_LEN, len);
+      out[n].hdr = h;
+      out[n].payload = rx_arena_->host_ptr(slot);
+      out[n].len = len;
+      out[n].slot = slot;
+      counters.rx_bytes += len;
+      n++;
+    }
+    counters.rx_pkts += (uint64_t)n;
+    return n;
+  }
+  void release_rx(const SrpcPkt* pkts, int n) override {
+    for (int i = 0; i < n; i++) rx_arena_->release(pkts[i].slot);
+  }
+  bool alloc_tx(SrpcPkt* out, int n) override {
+    uint32_t first = 0;
+    if (!tx_arena_->claim((uint32_t)n, &first)) return false;
+    for (int i = 0; i < n; i++) {
+      uint32_t s = (uint32_t)((first + i) % tx_arena_->num_slots());
+      out[i].slot = s;
+      out[i].hdr = tx_arena_->hdr_ptr(s);
+      out[i].payload = tx_arena_->dev_ptr(s);
+      out[i].len = 0;
+    }
+    return true;
+  }
+  int send_one(const p2p_rpc_hdr* h, const uint8_t* payload, uint32_t len) {
+    sockaddr_in to = default_dst_;
+    const ipv4_hdr* ip = get_ip_header(const_cast<p2p_rpc_hdr*>(h));
+    const udp_hdr* u = get_udp_header(const_cast<p2p_rpc_hdr*>(h));
+    if (!has_dst_ || (ip->dst_ip != 0 && u->dst_port != 0)) {
+      to.sin_family = AF_INET;
+      to.sin_addr.s_addr = ip->dst_ip;
+      to.sin_port = u->dst_port;
+    }
+    std::lock_guard<std::mutex> g(tx_mu_);
+    if (len + RPC_HEADER_TAIL_LEN > tx_scratch_.size()) {
+      counters.tx_dropped++;
+      return 0;
+    }
+    std::memcpy(tx_scratch_.data(), reinterpret_cast<const uint8_t*>(h) + UDP_HEADER_LEN, RPC_HEADER_TAIL_LEN);
+    if (len) std::memcpy(tx_scratch_.data() + RPC_HEADER_TAIL_LEN, payload, len);
+    for (int tries = 0; tries < 100; tries++) {
+      ssize_t r = ::sendto(fd_, tx_scratch_.data(), RPC_HEADER_TAIL_LEN + len, 0, (sockaddr*)&to, sizeof(to));
+      if (r >= 0) {
+        counters.tx_pkts++;
+        counters.tx_bytes += len;
+        return 1;
+      }
+    }
+    counters.tx_dropped++;
+    return 0;
+  }
+  int tx_burst(const SrpcPkt* pkts, int n) override {
+    int s = 0;
+    for (int i = 0; i < n; i++) {
+      s += send_one(pkts[i].hdr, tx_arena_->host_ptr(pkts[i].slot), pkts[i].len);
+      tx_arena_->release(pkts[i].slot);
+    }
+    return s;
+  }
+  int tx_copy(const p2p_rpc_hdr* hdrs, const uint8_t* const* payloads, const uint32_t* lens, int n) override {
+    int s = 0;
+    for (int i = 0; i < n; i++) s += send_one(&hdrs[i], payloads[i], lens[i]);
+    return s;
+  }
+  uint8_t* rx_host_ptr(uint32_t slot) const override { return rx_arena_->host_ptr(slot); }
+  const char* name() const override { return "udp"; }
+};
+
+// ------------------------------------------------------------------ DPDK placeholder
+enum MEM_ALLOC_TYPES { HOST_MEM_ONLY = 0, DEV_MEM_ONLY = 1, BUFFER_SPLIT = 2 };
+
+struct dpdk_ctx {
+  int nic_port = 0, queue_id = 0, mem_alloc_type = HOST_MEM_ONLY, device_id = 0, zerocopy_mode = 0;
+};
+
+// A DPDK port needs libdpdk, an mlx5 NIC and GPUDirect RDMA; none exist on a
+// machine without a NIC.  The function documents the slot where such a port plugs
+// in (it must implement Transport with its mbuf pools as the arenas) and reports
+// that it is unavailable.
+static inline Transport* init_dpdk_ctx(const dpdk_ctx&) {
+  srpc_log(SRPC_LOG_ERROR, "DPDK transport requested but this build has no DPDK; use the loopback or UDP transport");
+  return nullptr;
+}

@@ -1,0 +1,88 @@
+"""PyTorch-facing wrappers of the hand-written sm_100a kernels.
+
+Each function takes ``torch`` CUDA tensors, checks layout, allocates the output
+(or uses ``out=``) and launches the kernel on the current stream through the
+native library.  There is no fallback path: calling these without the native
+library or without a GPU raises.
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import _C
+
+ACT = {None: _C.ACT_NONE, "none": _C.ACT_NONE, "relu": _C.ACT_RELU, "gelu": _C.ACT_GELU}
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t: torch.Tensor | None) -> int:
+    return 0 if t is None else t.data_ptr()
+
+
+_status_words: dict[int, torch.Tensor] = {}
+
+
+def status_word(device: int | None = None) -> torch.Tensor:
+    """Per-device int32 word that kernels write an error code into when a bounded wait runs out."""
+    dev = torch.cuda.current_device() if device is None else device
+    if dev not in _status_words:
+        _status_words[dev] = torch.zeros(1, dtype=torch.int32, device=f"cuda:{dev}")
+    return _status_words[dev]
+
+
+def check_status() -> None:
+    """Raises if any kernel launched so far on this device reported a timed-out wait (synchronises)."""
+    code = int(status_word().item())
+    if code != 0:
+        status_word().zero_()
+        raise RuntimeError(f"kernel reported error status {code} (a bounded device-side wait ran out)")
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, bias: torch.Tensor | None = None, residual: torch.Tensor | None = None,
+         act: str | None = None, out: torch.Tensor | None = None, out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """``act(a @ b.T + bias + residual)`` with a ``[M,K]`` and b ``[N,K]`` bf16 (row-major, K contiguous).
+
+    bias is fp32 ``[N]``; residual is bf16 ``[M,N]``; the result is bf16 or fp32 ``[M,N]``.
+    """
+    assert a.is_cuda and b.is_cuda and a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
+    assert a.dim() == 2 and b.dim() == 2 and a.shape[1] == b.shape[1]
+    assert a.stride(1) == 1 and b.stride(1) == 1
+    M, K = a.shape
+    N = b.shape[0]
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=a.device)
+    assert out.stride(1) == 1 and out.shape == (M, N)
+    if bias is not None:
+        assert bias.dtype == torch.float32 and bias.numel() == N
+    if residual is not None:
+        assert residual.dtype == torch.bfloat16 and residual.shape == (M, N) and residual.stride(1) == 1
+    _C.gemm_bf16(a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0), M, N, K, out.data_ptr(), out.stride(0),
+                 out.dtype == torch.float32, _ptr(bias), _ptr(residual), residual.stride(0) if residual is not None else 0,
+                 ACT[act], status_word().data_ptr(), _stream())
+    return out
+
+
+def conv2d_nhwc(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, residual: torch.Tensor | None = None,
+                stride: int = 1, pad: int = 0, act: str | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Convolution of an NHWC bf16 tensor with ``[Cout, R, S, Cin]`` bf16 filters (Cin a multiple of 64)."""
+    assert x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.is_contiguous() and w.is_contiguous()
+    n, h, wd, cin = x.shape
+    cout, r, s, cin2 = w.shape
+    assert cin == cin2 and cin % 64 == 0 and cout % 8 == 0
+    oh, ow = (h + 2 * pad - r) // stride + 1, (wd + 2 * pad - s) // stride + 1
+    if out is None:
+        out = torch.empty((n, oh, ow, cout), dtype=torch.bfloat16, device=x.device)
+    assert out.is_contiguous() and out.shape == (n, oh, ow, cout)
+    if residual is not None:
+        assert residual.shape == out.shape and residual.is_contiguous() and residual.dtype == torch.bfloat16
+    _C.conv_bf16(x.data_ptr(), w.data_ptr(), n, h, wd, cin, cout, r, s, stride, pad, out.data_ptr(), _ptr(bias),
+                 _ptr(residual), ACT[act], status_word().data_ptr(), _stream())
+    return out
+
+
+def sg_copy(items, impl: int = 0, n_blocks: int = 0) -> None:
+    """Runs a copy list ``[(src_addr, dst_addr, nbytes)]`` on the current stream and waits for it."""
+    _C.sg_copy(list(items), impl, n_blocks, _stream())

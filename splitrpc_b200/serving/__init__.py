@@ -1,0 +1,50 @@
+"""Serving layer: wires transports, apps and the native server together from Python."""
+from __future__ import annotations
+
+import numpy as np
+
+from .. import _C
+
+
+def lenet5_random_weights(seed: int = 0) -> list[np.ndarray]:
+    """Random-init LeNet-5 parameters in the order the native apps expect."""
+    rng = np.random.default_rng(seed)
+    shapes = [(6, 1, 5, 5), (6,), (16, 6, 5, 5), (16,), (120, 400), (120,), (84, 120), (84,), (10, 84), (10,)]
+    return [(rng.standard_normal(s) * 0.1).astype(np.float32) for s in shapes]
+
+
+def smoke_test(device: int = 0) -> dict:
+    """Serves a few LeNet-5 requests end to end on ``device`` through the loopback transport and
+    checks them against the CPU oracle; then runs one tensor-core GEMM."""
+    import torch
+
+    if not _C.cuda_available():
+        raise RuntimeError("smoke test needs a CUDA device")
+    _C.set_rpc_mtu(8192)
+    w = lenet5_random_weights()
+    sp, cp = _C.make_loopback_pair(8192, 256, "pinned")
+    app = _C.make_app("lenet5", device, 3136, 40, w, 128, 1, 8, "gpu", 2)
+    srv = _C.Server(sp, req_size=3136, resp_size=40, server_mode=2, max_batch=8)
+    srv.add_replica(app)
+    srv.start()
+    cli = _C.Client(cp, req_size=3136, resp_size=40, total=64, warmup=0, payload="uniform", verify=True)
+    ok = cli.run_closed_loop(8)
+    srv.stop()
+    if not ok or cli.received != 64:
+        raise RuntimeError(f"smoke: served {cli.received}/64 requests")
+    x = np.frombuffer(cli.payload(5), dtype=np.float32)
+    ref = _C.cpu_lenet5(w, x)[0]
+    got = np.frombuffer(cli.response(5), dtype=np.float32)
+    np.testing.assert_allclose(got, ref, rtol=1e-4, atol=1e-5)
+
+    from .. import ops
+
+    torch.cuda.set_device(device)
+    a = torch.randn(256, 256, device="cuda").bfloat16()
+    b = torch.randn(256, 256, device="cuda").bfloat16()
+    out = ops.gemm(a, b)
+    ops.check_status()
+    err = ((out.float() - a.float() @ b.float().t()).norm() / (a.float() @ b.float().t()).norm()).item()
+    if err > 1e-2:
+        raise RuntimeError(f"smoke: gemm relative error {err}")
+    return {"served": int(cli.received), "gemm_rel_err": err}

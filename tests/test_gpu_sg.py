@@ -1,0 +1,161 @@
+"""GPU tests of the scatter-gather kernels, ring memory and the GPU apps behind the server."""
+import numpy as np
+import pytest
+
+from conftest import lenet5_weights
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def torch_cuda():
+    import torch
+
+    assert torch.cuda.is_available(), "GPU tests need a CUDA device"
+    torch.cuda.set_device(0)
+    return torch
+
+
+def _random_list(torch, rng, n_items, max_len, align):
+    total = n_items * (max_len + 64)
+    src = torch.randint(0, 256, (total,), dtype=torch.uint8, device="cuda")
+    dst = torch.zeros(total, dtype=torch.uint8, device="cuda")
+    ref = torch.zeros(total, dtype=torch.uint8, device="cuda")
+    items = []
+    so = do = 0
+    for _ in range(n_items):
+        ln = int(rng.integers(1, max_len + 1))
+        s_off = so + (int(rng.integers(0, 16)) if not align else 0)
+        d_off = do + (int(rng.integers(0, 16)) if not align else 0)
+        if align:
+            ln = (ln + 15) // 16 * 16
+        items.append((src.data_ptr() + s_off, dst.data_ptr() + d_off, ln))
+        ref[d_off:d_off + ln] = src[s_off:s_off + ln]
+        so = (s_off + ln + 15) // 16 * 16
+        do = (d_off + ln + 15) // 16 * 16
+    return src, dst, ref, items
+
+
+@pytest.mark.parametrize("impl", [0, 1])
+@pytest.mark.parametrize("align", [True, False])
+def test_sg_copy_matches_reference(C, torch_cuda, impl, align):
+    torch = torch_cuda
+    rng = np.random.default_rng(5 + impl)
+    src, dst, ref, items = _random_list(torch, rng, 37, 70000, align)
+    C.sg_copy(items, impl)
+    torch.cuda.synchronize()
+    assert torch.equal(dst, ref)
+
+
+def test_sg_copy_from_mapped_host_memory(C, torch_cuda):
+    torch = torch_cuda
+    host = torch.randint(0, 256, (1 << 20,), dtype=torch.uint8).pin_memory()
+    dst = torch.zeros(1 << 20, dtype=torch.uint8, device="cuda")
+    for impl in (0, 1):
+        dst.zero_()
+        items = [(host.data_ptr() + i * 8192, dst.data_ptr() + i * 8192, 8192) for i in range(128)]
+        C.sg_copy(items, impl)
+        torch.cuda.synchronize()
+        assert torch.equal(dst.cpu(), host)
+
+
+def test_sg_cast_bf16(C, torch_cuda):
+    torch = torch_cuda
+    x = torch.randn(3 * 224 * 224 * 2, device="cuda")
+    out = torch.zeros(x.numel(), dtype=torch.bfloat16, device="cuda")
+    half = x.numel() // 2
+    items = [(x.data_ptr(), out.data_ptr(), half * 4), (x.data_ptr() + half * 4, out.data_ptr() + half * 2, half * 4)]
+    C.sg_cast_bf16(items, 0.5, 0.25)
+    torch.cuda.synchronize()
+    ref = ((x - 0.25) * 0.5).to(torch.bfloat16)
+    assert torch.equal(out, ref)
+
+
+def test_device_caps(C, torch_cuda):
+    caps = C.device_caps(0)
+    assert caps["sm"] >= 100 and caps["vmm"] == 1 and caps["num_sms"] > 100
+
+
+def test_ring_is_double_mapped(C, torch_cuda):
+    import ctypes
+
+    torch = torch_cuda
+    app = C.make_app("echo", 0, 3000, 3000, [], 64, 1, 1)
+    base, cap, dbl = app.req_ring
+    assert dbl and cap >= 64 * 3000
+    # bytes written through the first mapping are visible through the second
+    src = torch.arange(256, dtype=torch.uint8, device="cuda")
+    C.sg_copy([(src.data_ptr(), base + cap - 128, 256)], 0)  # runs across the end of the ring
+    back = torch.zeros(256, dtype=torch.uint8, device="cuda")
+    C.sg_copy([(base + cap - 128, back.data_ptr(), 128), (base, back.data_ptr() + 128, 128)], 0)
+    torch.cuda.synchronize()
+    assert torch.equal(back, src)
+
+
+def _serve_gpu(C, app_name, req, resp, total, mode, max_batch, payload, copy_type, launch_type=1, weights=(),
+               outstanding=8, slot=8192):
+    sp, cp = C.make_loopback_pair(slot, 2048, "pinned")
+    app = C.make_app(app_name, 0, req, resp, list(weights), 256, launch_type, max_batch, "gpu", copy_type)
+    assert app.init_ok
+    srv = C.Server(sp, req_size=req, resp_size=resp, server_mode=mode, max_batch=max_batch)
+    srv.add_replica(app)
+    srv.start()
+    cli = C.Client(cp, req_size=req, resp_size=resp, total=total, warmup=5, payload=payload, verify=True)
+    ok = cli.run_closed_loop(outstanding)
+    st = cli.post_process()
+    ss = srv.stats()
+    ws = srv.worker_stats(0)
+    sg = app.sg_counters
+    srv.stop()
+    return ok, cli, st, ss, ws, sg
+
+
+@pytest.mark.parametrize("copy_type", [0, 1, 2, 3])
+def test_gpu_echo_all_copy_types(C, torch_cuda, mtu8k, copy_type):
+    ok, cli, st, ss, ws, sg = _serve_gpu(C, "echo", 40000, 40000, 120, 2, 8, "echo", copy_type)
+    assert ok and cli.received == 120 and cli.verify_failures == 0
+    assert ss["sg_errors"] == 0 and sg["timeouts"] == 0 and sg["engine"] == "gpu"
+
+
+@pytest.mark.parametrize("launch_type", [1, 3, 4])
+def test_gpu_vec_add_launch_types(C, torch_cuda, mtu8k, launch_type):
+    ok, cli, st, ss, ws, sg = _serve_gpu(C, "vec_add", 16384, 16384, 100, 2, 4, "vec_add", 2, launch_type)
+    assert ok and cli.received == 100 and cli.verify_failures == 0 and ws["wait_timeouts"] == 0
+
+
+def test_gpu_async_stream_armed_mode(C, torch_cuda, mtu8k):
+    ok, cli, st, ss, ws, sg = _serve_gpu(C, "vec_add", 8192, 8192, 200, 1, 4, "vec_add", 2, outstanding=8)
+    assert ok and cli.received == 200 and cli.verify_failures == 0
+    assert set(ws["batch_hist"]) == {4}
+
+
+def test_gpu_lenet5_matches_cpu_oracle(C, torch_cuda, mtu8k):
+    w = lenet5_weights()
+    ok, cli, st, ss, ws, sg = _serve_gpu(C, "lenet5", 3136, 40, 400, 2, 32, "uniform", 2, 4, weights=w, outstanding=64)
+    assert ok and cli.received == 400
+    for i in (0, 100, 399):
+        x = np.frombuffer(cli.payload(i % 16), dtype=np.float32)
+        ref = C.cpu_lenet5(w, x)[0]
+        got = np.frombuffer(cli.response(i), dtype=np.float32)
+        np.testing.assert_allclose(got, ref, rtol=1e-4, atol=1e-5)
+
+
+def test_gpu_matmul(C, torch_cuda, mtu8k):
+    sp, cp = C.make_loopback_pair(8192, 1024, "pinned")
+    app = C.make_app("matmul", 0, 32768, 16384, [], 64, 1, 2, "gpu", 2)
+    srv = C.Server(sp, req_size=32768, resp_size=16384, server_mode=2, max_batch=2)
+    srv.add_replica(app)
+    srv.start()
+    cli = C.Client(cp, req_size=32768, resp_size=16384, total=20, warmup=0, payload="uniform", verify=True)
+    assert cli.run_closed_loop(2)
+    srv.stop()
+    req = np.frombuffer(cli.payload(5), dtype=np.float32)
+    a, b = req[:4096].reshape(64, 64), req[4096:].reshape(64, 64)
+    got = np.frombuffer(cli.response(5), dtype=np.float32).reshape(64, 64)
+    np.testing.assert_allclose(got, a @ b, rtol=1e-4, atol=1e-4)
+
+
+def test_local_bench_gpu(C, torch_cuda):
+    app = C.make_app("vec_add", 0, 1024, 1024, [], 64, 1, 1, "gpu", 2)
+    ns, outs = C.local_bench(app, 200, 1)
+    assert len(ns) == 200
