@@ -1,0 +1,267 @@
+"""Headline benchmark: requests/s of dynamic-batched model serving, per GPU replica.
+
+    python bench.py --gpus N --steps K --warmup W [--config resnet50|bert_base|lenet5|echo]
+
+One process per GPU (launched under torchrun for N > 1; RANK/LOCAL_RANK/WORLD_SIZE
+come from the environment).  Every rank serves one data-parallel replica of the
+model on its GPU.  A "step" is one full batch (``max_batch`` requests) through
+the serving path.  Two numbers are produced:
+
+* ``value``: device-timed.  K steps of {scatter-gather kernel that pulls the
+  batch's 8 KB fragments out of the pinned receive arena into the request ring,
+  the model's CUDA graph, the response scatter kernel into the pinned transmit
+  arena}, bracketed by CUDA events on the serving stream, max over ranks.
+* ``e2e``: the same metric through the public serving API: the load generator
+  sends fragmented requests over the loopback transport (an emulated NIC that
+  DMA-writes into pinned host rings), the native server reassembles, gathers,
+  batches dynamically, runs the graphs and sends responses, and the client
+  receives them on the host.  The host->device bytes are the request fragments
+  the GPU pulls from pinned memory; the device->host bytes are the responses.
+
+Rank 0 prints one JSON line.  ``--impl reference`` reports why the original
+server cannot run here.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+CONFIGS = {
+    "resnet50": dict(model="ResNet-50 v1.5 bf16 (BN folded), 3x224x224 fp32 requests in 8 KB fragments", max_batch=64,
+                     payload="normal", seq=None),
+    "bert_base": dict(model="BERT-base bf16 classifier, seq 128 int32 ids", max_batch=32, payload="ids", seq=128),
+    "lenet5": dict(model="LeNet-5 fp32", max_batch=32, payload="uniform", seq=None),
+}
+
+
+class ClockSampler:
+    """Samples SM clock, power and throttle reasons of one GPU with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu, self.samples, self.proc = gpu_index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "200"], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.samples.append([f.strip() for f in line.split(",")])
+
+    def stop(self) -> dict:
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+        sm, mx, reasons = [], 0, set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for s in self.samples:
+            try:
+                sm.append(float(s[0]))
+                mx = max(mx, float(s[1]))
+                for n, v in zip(names, s[3:7]):
+                    if v.lower().startswith("active"):
+                        reasons.add(n)
+            except (ValueError, IndexError):
+                continue
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx or None, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def build_model(config: str, device: int):
+    if config == "resnet50":
+        from splitrpc_b200.models import ResNet50
+
+        return ResNet50(device=device, max_batch=CONFIGS[config]["max_batch"])
+    if config == "bert_base":
+        from splitrpc_b200.models import BertClassifier, BERT_BASE
+
+        return BertClassifier(BERT_BASE, seq=128, device=device, max_batch=CONFIGS[config]["max_batch"])
+    raise SystemExit(f"unknown config {config}")
+
+
+def device_timed(srv, steps: int, warmup: int):
+    """K steps of gather -> graph -> response scatter on the serving stream, timed with CUDA events."""
+    import torch
+
+    from splitrpc_b200 import _C
+
+    app, nb = srv.app, srv.max_batch
+    req, resp = srv.req_size, srv.resp_size
+    mtu = 8192
+    # Two batches worth of fragments in pinned, GPU-mapped host memory (> L2 for the big models), alternated.
+    n_sets = 2
+    pinned = torch.empty(n_sets * nb * req, dtype=torch.uint8).pin_memory()
+    pinned.random_(0, 256) if req < 4096 else pinned.view(torch.float32).normal_()
+    if srv.model.__class__.__name__ == "BertClassifier":
+        pinned.view(torch.int32).random_(0, 30522)
+    tx = torch.empty(nb * max(resp, 16), dtype=torch.uint8).pin_memory()
+    req_base, _, _ = app.req_ring
+    resp_base, _, _ = app.resp_ring
+    lists = []
+    for s in range(n_sets):
+        items = []
+        for r in range(nb):
+            off = 0
+            while off < req:  # one item per 8 KB fragment, as the reassembly delivers them
+                ln = min(mtu, req - off)
+                items.append((pinned.data_ptr() + (s * nb + r) * req + off, req_base + r * req + off, ln))
+                off += ln
+        lists.append(_C.sg_list_create(items))
+    out_list = _C.sg_list_create([(resp_base + r * resp, tx.data_ptr() + r * resp, resp) for r in range(nb)])
+    app.set_stub()
+    stream = srv.stream
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=f"cuda:{srv.device}")
+
+    def step(i):
+        _C.sg_list_launch(lists[i % n_sets], 0, 0, stream.cuda_stream)
+        app.launch(nb)
+        _C.sg_list_launch(out_list, 0, 0, stream.cuda_stream)
+
+    with torch.cuda.stream(stream):
+        for i in range(warmup):
+            step(i)
+        stream.synchronize()
+        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+        for i in range(steps):
+            flush.zero_()  # L2 flush between timed iterations (outside the timed events)
+            evs[i][0].record(stream)
+            step(i)
+            evs[i][1].record(stream)
+        stream.synchronize()
+    ms = [a.elapsed_time(b) for a, b in evs]
+    for h in lists + [out_list]:
+        _C.sg_list_destroy(h)
+    return ms
+
+
+def run_ours(args, rank: int, world: int, local_rank: int) -> dict:
+    import torch
+
+    from splitrpc_b200 import ops
+    from splitrpc_b200.serving import ModelServer
+
+    cfg = CONFIGS[args.config]
+    nb = cfg["max_batch"]
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    model = build_model(args.config, local_rank)
+    srv = ModelServer(model, device=local_rank, max_batch=nb, server_mode=2, copy_type=2, outstanding=2 * nb)
+
+    def barrier():
+        if dist:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-timed
+    barrier()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    ms = device_timed(srv, args.steps, max(args.warmup, 3))
+    barrier()
+    total_ms = sum(ms)
+    t = torch.tensor([total_ms], device="cuda", dtype=torch.float64)
+    if dist:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    max_total_ms = float(t.item())
+    ops.check_status()
+    value = world * nb * args.steps / (max_total_ms / 1e3)
+
+    # ---- end to end through the public API
+    barrier()
+    n_req = nb * args.steps
+    n_warm = nb * max(args.warmup, 3)
+    srv.start()
+    cli = srv.client(total=n_req + n_warm, warmup=n_warm, payload=cfg["payload"], n_payloads=8)
+    barrier()
+    ok = cli.run_closed_loop(2 * nb)
+    st = cli.post_process()
+    clocks = sampler.stop()
+    ws = srv.server.worker_stats(0)
+    srv.stop()
+    e2e_rps = st.get("throughput_est", 0.0) if ok else 0.0
+    t2 = torch.tensor([e2e_rps, st.get("p50_sojournTime_us", 0.0), st.get("p99_sojournTime_us", 0.0)], device="cuda",
+                      dtype=torch.float64)
+    if dist:
+        s = t2.clone()
+        dist.all_reduce(s, op=dist.ReduceOp.SUM)
+        m = t2.clone()
+        dist.all_reduce(m, op=dist.ReduceOp.MAX)
+        e2e_total, p50, p99 = float(s[0]), float(m[1]), float(m[2])
+    else:
+        e2e_total, p50, p99 = float(t2[0]), float(t2[1]), float(t2[2])
+    hist = ws["batch_hist"]
+    mean_bs = sum(k * v for k, v in hist.items()) / max(1, sum(hist.values()))
+    launches_per_step = 2 + model.kernels_per_forward
+    result = {
+        "metric": "req/s (dynamic batching, device-timed, max over ranks)", "value": round(value, 1), "unit": "req/s",
+        "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(max_total_ms / args.steps, 4),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "impl": "splitrpc_b200",
+        "config": {"model": cfg["model"], "global_batch": nb * world, "seq_len": cfg["seq"], "parallelism": f"dp{world}",
+                   "step": f"one batch of {nb} requests per GPU: gather fragments from pinned host arena + model graph + response scatter",
+                   "l2": "256 MiB buffer written between timed iterations; inputs alternate between two pinned sets",
+                   "weights": "random init"},
+        "clocks": clocks,
+        "e2e": {"value": round(e2e_total, 1), "unit": "req/s", "h2d_bytes_per_step": nb * srv.req_size,
+                "d2h_bytes_per_step": nb * srv.resp_size, "p50_us": round(p50, 1), "p99_us": round(p99, 1),
+                "mean_batch": round(mean_bs, 2), "requests": n_req, "outstanding": 2 * nb,
+                "path": "loadgen -> loopback NIC (pinned rings) -> native server -> SG kernel -> CUDA graph -> SG kernel -> client"},
+        "gpu_launches": launches_per_step * args.steps,
+    }
+    if dist:
+        dist.destroy_process_group()
+    return result
+
+
+def run_reference(args) -> dict:
+    return {"impl": "reference", "unavailable": "the original server needs DPDK 21.08, gdrcopy, libibverbs/rdmacm, ONNX "
+            "Runtime + TensorRT and a spdlog submodule, none of which exist offline on this image; it has no setup.py/pyproject "
+            "so the pip install into baseline/_ref fails"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=30)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--config", default="resnet50", choices=sorted(CONFIGS))
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        if rank == 0:
+            print(json.dumps(run_reference(args)), flush=True)
+        return
+    res = run_ours(args, rank, world, local_rank)
+    if rank == 0:
+        print(json.dumps(res), flush=True)
+
+
+if __name__ == "__main__":
+    main()

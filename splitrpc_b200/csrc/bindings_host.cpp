@@ -108,6 +108,7 @@ struct AppHolder {
   std::unique_ptr<P2pRpcAppInfo> info;
   std::unique_ptr<P2pRpcSgEngine> engine;
   std::string name;
+  void* graph_internal = nullptr;  // state of a graph app (owned by the app's cleanup callback)
 };
 
 std::vector<std::vector<float>> to_weights(const std::vector<py::array_t<float, py::array::c_style | py::array::forcecast>>& ws) {
@@ -172,6 +173,18 @@ std::shared_ptr<AppHolder> make_python_app(py::function run, int device, size_t 
   return h;
 }
 
+std::shared_ptr<AppHolder> make_graph_app(int device, size_t req_size, size_t resp_size, int pool_size, int batch,
+                                          const std::string& engine, int copy_type) {
+  auto h = std::make_shared<AppHolder>();
+  h->name = "graph";
+  GpuAppHandle g = srpc_make_graph_app();
+  h->graph_internal = g.internal;
+  h->info.reset(new P2pRpcAppInfo(g.init, g.run, g.cleanup, g.complete, device, req_size, resp_size, pool_size, g.internal,
+                                  4, batch));
+  h->engine = make_engine(engine.empty() ? "gpu" : engine, device, copy_type);
+  return h;
+}
+
 // Members are destroyed in reverse order: the server (and its threads) goes
 // first, then the apps it was running, then the port.
 struct ServerHolder {
@@ -190,7 +203,9 @@ app_req_cb req_cb_by_name(const std::string& k) {
   if (k == "vec_add") return vec_add_fill;
   if (k == "const5") return const_float_fill;
   if (k == "uniform") return uniform_float_fill;
-  throw std::invalid_argument("payload kind must be echo, vec_add, const5 or uniform");
+  if (k == "normal") return normal_float_fill;
+  if (k == "ids") return token_ids_fill;
+  throw std::invalid_argument("payload kind must be echo, vec_add, const5, uniform, normal or ids");
 }
 app_resp_cb resp_cb_by_name(const std::string& k) {
   if (k == "echo") return echo_check;
@@ -428,6 +443,34 @@ PYBIND11_MODULE(_C, m) {
         auto* mp = a.info->app_rr_pool->rr_mem_pool;
         return py::make_tuple((uintptr_t)mp->get_resp_addr_range(), mp->get_resp_addr_pool_size(), mp->is_double_mapped());
       })
+      .def("capture_begin",
+           [](AppHolder& a) {
+             if (int e = srpc_capture_begin(a.info->app_ctx->work_stream)) throw std::runtime_error("capture_begin: CUDA error " + std::to_string(e));
+           })
+      .def("capture_end",
+           [](AppHolder& a, int batch) {
+             if (!a.graph_internal) throw std::runtime_error("capture_end: not a graph app");
+             cudaGraphExec_t exec = nullptr;
+             if (int e = srpc_capture_end(a.info->app_ctx->work_stream, &exec)) throw std::runtime_error("capture_end: CUDA error " + std::to_string(e));
+             srpc_graph_app_set(a.graph_internal, batch, exec);
+           })
+      .def("sync", [](AppHolder& a) { return a.info->app_ctx->WaitForAppRunComplete(); })
+      // Points the app's stub at explicit addresses (default: the start of both rings),
+      // e.g. before a warm-up run or a stand-alone timing loop.
+      .def("set_stub",
+           [](AppHolder& a, uintptr_t req, uintptr_t resp) {
+             auto* mp = a.info->app_rr_pool->rr_mem_pool;
+             a.info->app_ctx->h_stub->req = req ? (uint8_t*)req : (uint8_t*)mp->get_req_addr_range();
+             a.info->app_ctx->h_stub->resp = resp ? (uint8_t*)resp : (uint8_t*)mp->get_resp_addr_range();
+             std::atomic_thread_fence(std::memory_order_seq_cst);
+           },
+           py::arg("req") = 0, py::arg("resp") = 0)
+      // Runs the app once for `batch` requests at the current stub without waiting.
+      .def("launch",
+           [](AppHolder& a, int batch) {
+             a.info->app_ctx->curr_batch_size = batch;
+             if (!a.info->app_run(a.info->app_ctx)) throw std::runtime_error("app run failed");
+           })
       .def_property_readonly("sg_counters", [](AppHolder& a) {
         py::dict d;
         d["gathers"] = a.engine->counters.gathers;
@@ -441,6 +484,8 @@ PYBIND11_MODULE(_C, m) {
   m.def("make_app", &make_app, py::arg("name"), py::arg("device") = -1, py::arg("req_size") = 1024,
         py::arg("resp_size") = 1024, py::arg("weights") = std::vector<py::array_t<float>>{}, py::arg("pool_size") = 256,
         py::arg("launch_type") = 1, py::arg("batch") = 1, py::arg("engine") = "", py::arg("copy_type") = 2);
+  m.def("make_graph_app", &make_graph_app, py::arg("device") = 0, py::arg("req_size") = 1024, py::arg("resp_size") = 1024,
+        py::arg("pool_size") = 256, py::arg("batch") = 1, py::arg("engine") = "", py::arg("copy_type") = 2);
   m.def("make_python_app", &make_python_app, py::arg("run"), py::arg("device") = -1, py::arg("req_size") = 1024,
         py::arg("resp_size") = 1024, py::arg("pool_size") = 256, py::arg("launch_type") = 1, py::arg("batch") = 1,
         py::arg("engine") = "", py::arg("copy_type") = 2);

@@ -6,6 +6,7 @@
 #include <cuda_runtime.h>
 
 #include "cuda/gemm_tcgen05.h"
+#include "cuda/nn_kernels.h"
 #include "cuda/ops_api.h"
 
 namespace py = pybind11;
@@ -62,6 +63,7 @@ void bind_ops(py::module_& m) {
   m.attr("ACT_NONE") = (int)GEMM_ACT_NONE;
   m.attr("ACT_RELU") = (int)GEMM_ACT_RELU;
   m.attr("ACT_GELU") = (int)GEMM_ACT_GELU;
+  m.attr("ACT_TANH") = (int)GEMM_ACT_TANH;
   m.def("gemm_bf16",
         [](uintptr_t a, int lda, uintptr_t b, int ldb, int M, int N, int K, uintptr_t out, int ldo, bool out_fp32,
            uintptr_t bias, uintptr_t residual, int ldr, int act, uintptr_t status, uintptr_t stream) {
@@ -82,4 +84,53 @@ void bind_ops(py::module_& m) {
         py::arg("input"), py::arg("weight"), py::arg("n"), py::arg("h"), py::arg("w"), py::arg("cin"), py::arg("cout"),
         py::arg("r"), py::arg("s"), py::arg("stride"), py::arg("pad"), py::arg("out"), py::arg("bias") = 0,
         py::arg("residual") = 0, py::arg("act") = 0, py::arg("status") = 0, py::arg("stream") = 0);
+
+  // ---- memory-bound layers
+  m.def("stem_im2col",
+        [](uintptr_t d_stub, uintptr_t direct_in, int batch, uintptr_t out, std::vector<float> mean, std::vector<float> inv_std,
+           uintptr_t stream) {
+          if (mean.size() != 3 || inv_std.size() != 3) throw std::invalid_argument("mean / inv_std need 3 values");
+          check(nn_stem_im2col((const void*)d_stub, (const float*)direct_in, batch, (void*)out, mean.data(), inv_std.data(),
+                               (cudaStream_t)stream),
+                "stem_im2col");
+        });
+  m.def("maxpool3x3s2", [](uintptr_t in, uintptr_t out, int n, int h, int w, int c, uintptr_t stream) {
+    check(nn_maxpool3x3s2((const void*)in, (void*)out, n, h, w, c, (cudaStream_t)stream), "maxpool3x3s2");
+  });
+  m.def("global_avgpool", [](uintptr_t in, uintptr_t out, int n, int hw, int c, uintptr_t stream) {
+    check(nn_global_avgpool((const void*)in, (void*)out, n, hw, c, (cudaStream_t)stream), "global_avgpool");
+  });
+  m.def("softmax_response",
+        [](uintptr_t logits, int rows, int n, int ld, uintptr_t d_stub, uintptr_t direct_out, size_t resp_stride,
+           bool write_argmax, uintptr_t counter, uintptr_t flag, uint32_t flag_value, uintptr_t stream) {
+          check(nn_softmax_response((const float*)logits, rows, n, ld, (const void*)d_stub, (void*)direct_out, resp_stride,
+                                    write_argmax ? 1 : 0, (uint32_t*)counter, (uint32_t*)flag, flag_value,
+                                    (cudaStream_t)stream),
+                "softmax_response");
+        },
+        py::arg("logits"), py::arg("rows"), py::arg("n"), py::arg("ld"), py::arg("d_stub") = 0, py::arg("direct_out") = 0,
+        py::arg("resp_stride") = 0, py::arg("write_argmax") = false, py::arg("counter") = 0, py::arg("flag") = 0,
+        py::arg("flag_value") = 0, py::arg("stream") = 0);
+  m.def("layernorm",
+        [](uintptr_t x, uintptr_t residual, uintptr_t gamma, uintptr_t beta, uintptr_t y, int rows, int hidden, float eps,
+           uintptr_t stream) {
+          check(nn_layernorm((const void*)x, (const void*)residual, (const float*)gamma, (const float*)beta, (void*)y, rows,
+                             hidden, eps, (cudaStream_t)stream),
+                "layernorm");
+        });
+  m.def("bert_embed_ln",
+        [](uintptr_t d_stub, uintptr_t direct_ids, size_t req_stride, int batch, int seq, uintptr_t word, uintptr_t pos,
+           uintptr_t type, uintptr_t gamma, uintptr_t beta, uintptr_t y, int hidden, int vocab, float eps, uintptr_t stream) {
+          check(nn_bert_embed_ln((const void*)d_stub, (const int*)direct_ids, req_stride, batch, seq, (const void*)word,
+                                 (const void*)pos, (const void*)type, (const float*)gamma, (const float*)beta, (void*)y,
+                                 hidden, vocab, eps, (cudaStream_t)stream),
+                "bert_embed_ln");
+        });
+  m.def("attention_d64",
+        [](uintptr_t qkv, uintptr_t out, int batch, int seq, int heads, int ld_qkv, int q_off, int k_off, int v_off,
+           int ld_out, uintptr_t stream) {
+          check(nn_attention_d64((const void*)qkv, (void*)out, batch, seq, heads, ld_qkv, q_off, k_off, v_off, ld_out,
+                                 (cudaStream_t)stream),
+                "attention_d64");
+        });
 }

@@ -121,7 +121,12 @@ __global__ void vec_add_resident(const g_params* stub, volatile uint32_t* door_b
     __syncthreads();
     if (batch == 3u) break;   // exit request or idle limit
     if (batch == 0) continue;
-    g_params p = *stub;
+    // The stub lives in mapped host memory and changes between batches while this
+    // kernel stays resident: read it with system-scope loads, never from a cache.
+    g_params p;
+    p.req = reinterpret_cast<uint8_t*>(ptx::ld_relaxed_sys_u64(reinterpret_cast<const uint64_t*>(stub)));
+    p.resp = reinterpret_cast<uint8_t*>(ptx::ld_relaxed_sys_u64(reinterpret_cast<const uint64_t*>(stub) + 1));
+    __threadfence();  // drop request-ring lines an earlier lap may have left in L1
     vec_add_body(p.req, p.resp, req_size, resp_size, (int)batch, threadIdx.x, blockDim.x, 0, 1);
     __threadfence_system();
     __syncthreads();

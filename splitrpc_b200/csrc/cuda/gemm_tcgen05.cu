@@ -40,6 +40,8 @@ struct SmemLayout {
 __device__ __forceinline__ void epilogue_store(const GemmEpilogue& ep, uint32_t tmem_base, int warp_q, int lane, int m0,
                                                int n0, int M, int N, int BN) {
   const int row = m0 + warp_q * 32 + lane;
+  const bool vec_out = ((ep.ldo & 7) == 0) && (((uintptr_t)ep.out & 15) == 0);
+  const bool vec_res = ((ep.ldr & 7) == 0) && (((uintptr_t)ep.residual & 15) == 0);
   for (int c = 0; c < BN; c += 32) {
     uint32_t r[32];
     ptx::tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(warp_q * 32) << 16) + (uint32_t)c, r);
@@ -57,7 +59,7 @@ __device__ __forceinline__ void epilogue_store(const GemmEpilogue& ep, uint32_t 
     }
     if (ep.residual) {
       const __nv_bfloat16* rp = ep.residual + (size_t)row * ep.ldr + col0;
-      if (col0 + 32 <= N) {
+      if (col0 + 32 <= N && vec_res) {
 #pragma unroll
         for (int j = 0; j < 32; j += 8) {
           uint4 q = *reinterpret_cast<const uint4*>(rp + j);
@@ -79,13 +81,16 @@ __device__ __forceinline__ void epilogue_store(const GemmEpilogue& ep, uint32_t 
     } else if (ep.act == GEMM_ACT_GELU) {
 #pragma unroll
       for (int j = 0; j < 32; j++) v[j] = gelu_f(v[j]);
+    } else if (ep.act == GEMM_ACT_TANH) {
+#pragma unroll
+      for (int j = 0; j < 32; j++) v[j] = tanhf(v[j]);
     }
     if (ep.out_fp32) {
       float* op = reinterpret_cast<float*>(ep.out) + (size_t)row * ep.ldo + col0;
       for (int j = 0; j < 32 && col0 + j < N; j++) op[j] = v[j];
     } else {
       __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(ep.out) + (size_t)row * ep.ldo + col0;
-      if (col0 + 32 <= N) {
+      if (col0 + 32 <= N && vec_out) {
 #pragma unroll
         for (int j = 0; j < 32; j += 8) {
           uint4 q;
@@ -397,8 +402,6 @@ cudaError_t srpc_gemm_bf16(const void* A, int lda, const void* B, int ldb, int M
                            uint32_t* status, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return cudaErrorInvalidValue;
   if ((lda % 8) || (ldb % 8) || (K % 8) || ((uintptr_t)A & 15) || ((uintptr_t)B & 15)) return cudaErrorInvalidValue;
-  if (!ep.out_fp32 && ((ep.ldo % 8) || ((uintptr_t)ep.out & 15))) return cudaErrorInvalidValue;
-  if (ep.residual && ((ep.ldr % 8) || ((uintptr_t)ep.residual & 15))) return cudaErrorInvalidValue;
   const int bn = (N <= 64) ? 64 : 128;
   CUtensorMap ta, tb;
   cudaError_t e = encode_2d(&ta, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda * 2, BK, BM);

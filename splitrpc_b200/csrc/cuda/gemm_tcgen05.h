@@ -7,7 +7,7 @@
 
 #include "driver_api.h"
 
-enum GemmAct { GEMM_ACT_NONE = 0, GEMM_ACT_RELU = 1, GEMM_ACT_GELU = 2 };
+enum GemmAct { GEMM_ACT_NONE = 0, GEMM_ACT_RELU = 1, GEMM_ACT_GELU = 2, GEMM_ACT_TANH = 3 };
 enum GemmErr { GEMM_OK = 0, GEMM_ERR_PRODUCER_WAIT = 1, GEMM_ERR_MMA_WAIT = 2, GEMM_ERR_EPILOGUE_WAIT = 3 };
 
 // out[row, col] = act(acc + bias[col] + residual[row, col]); leading dimensions in elements.

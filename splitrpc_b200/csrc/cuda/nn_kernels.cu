@@ -1,0 +1,400 @@
+// Memory-bound layers around the tensor-core kernels: request deserialisation,
+// pooling, normalisation, softmax/argmax response writers, embedding and attention.
+//
+// These stand in for the cuDNN/TensorRT layers the original reaches through ONNX
+// Runtime (reference src/apps/ort_app.h:511-516).  Activations are bf16 (NHWC for
+// images, [tokens, hidden] for sequences); statistics are computed in fp32.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <float.h>
+#include <stdint.h>
+
+#include "../host/p2p_rpc_app.h"
+#include "nn_kernels.h"
+#include "ptx.cuh"
+
+namespace {
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int s = 16; s; s >>= 1) v += __shfl_xor_sync(0xffffffffu, v, s);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int s = 16; s; s >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, s));
+  return v;
+}
+
+// Block-wide sum of one value per thread (blockDim.x <= 1024, multiple of 32).
+__device__ __forceinline__ float block_sum(float v, float* sh) {
+  v = warp_sum(v);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = blockDim.x >> 5;
+  __syncthreads();
+  if (l == 0) sh[w] = v;
+  __syncthreads();
+  float t = (l < nw) ? sh[l] : 0.f;
+  t = warp_sum(t);
+  return t;
+}
+
+// ------------------------------------------------------------------ ResNet stem input
+// Request = fp32 CHW image (3 x 224 x 224).  Writes the im2col matrix of the 7x7
+// stride-2 pad-3 stem convolution: row = output pixel (n, oy, ox), 192 bf16
+// columns = k index c*49 + ky*7 + kx for k < 147, zero above, after
+// (x - mean[c]) * inv_std[c].  One thread writes 8 columns (one 16-byte store).
+__global__ void __launch_bounds__(256) stem_im2col(const g_params* stub, const float* __restrict__ direct_in, int batch,
+                                                   __nv_bfloat16* __restrict__ out, float3 mean, float3 inv_std) {
+  const float* in = direct_in ? direct_in : reinterpret_cast<const float*>(stub->req);
+  const size_t total = (size_t)batch * 112 * 112 * 24;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const int kc = (int)(i % 24);
+    const size_t pix = i / 24;
+    const int ox = (int)(pix % 112), oy = (int)((pix / 112) % 112), n = (int)(pix / (112 * 112));
+    const float* img = in + (size_t)n * 3 * 224 * 224;
+    __nv_bfloat16 v[8];
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+      const int k = kc * 8 + j;
+      float x = 0.f;
+      if (k < 147) {
+        const int c = k / 49, rem = k - c * 49, ky = rem / 7, kx = rem - ky * 7;
+        const int iy = oy * 2 - 3 + ky, ix = ox * 2 - 3 + kx;
+        if (iy >= 0 && iy < 224 && ix >= 0 && ix < 224) {
+          const float m = c == 0 ? mean.x : (c == 1 ? mean.y : mean.z);
+          const float s = c == 0 ? inv_std.x : (c == 1 ? inv_std.y : inv_std.z);
+          x = (__ldg(img + ((size_t)c * 224 + iy) * 224 + ix) - m) * s;
+        }
+      }
+      v[j] = __float2bfloat16(x);
+    }
+    *reinterpret_cast<uint4*>(out + pix * 192 + kc * 8) = *reinterpret_cast<const uint4*>(v);
+  }
+}
+
+// 3x3 stride-2 pad-1 max pooling, NHWC bf16, 8 channels per thread.
+__global__ void __launch_bounds__(256) maxpool3x3s2(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out,
+                                                    int n, int h, int w, int c) {
+  const int oh = (h + 2 - 3) / 2 + 1, ow = (w + 2 - 3) / 2 + 1, cv = c / 8;
+  const size_t total = (size_t)n * oh * ow * cv;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const int cc = (int)(i % cv);
+    size_t p = i / cv;
+    const int ox = (int)(p % ow);
+    p /= ow;
+    const int oy = (int)(p % oh), b = (int)(p / oh);
+    float m[8];
+#pragma unroll
+    for (int j = 0; j < 8; j++) m[j] = -FLT_MAX;
+    for (int dy = 0; dy < 3; dy++) {
+      const int iy = oy * 2 - 1 + dy;
+      if (iy < 0 || iy >= h) continue;
+      for (int dx = 0; dx < 3; dx++) {
+        const int ix = ox * 2 - 1 + dx;
+        if (ix < 0 || ix >= w) continue;
+        uint4 q = *reinterpret_cast<const uint4*>(in + (((size_t)b * h + iy) * w + ix) * c + cc * 8);
+        const __nv_bfloat162* hq = reinterpret_cast<const __nv_bfloat162*>(&q);
+#pragma unroll
+        for (int t = 0; t < 4; t++) {
+          float2 f = __bfloat1622float2(hq[t]);
+          m[2 * t] = fmaxf(m[2 * t], f.x);
+          m[2 * t + 1] = fmaxf(m[2 * t + 1], f.y);
+        }
+      }
+    }
+    uint4 o;
+    __nv_bfloat162* ho = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int t = 0; t < 4; t++) ho[t] = __floats2bfloat162_rn(m[2 * t], m[2 * t + 1]);
+    *reinterpret_cast<uint4*>(out + (((size_t)b * oh + oy) * ow + ox) * c + cc * 8) = o;
+  }
+}
+
+// Global average pooling NHWC -> [n, c]; one block per image, threads over channels.
+__global__ void __launch_bounds__(256) global_avgpool(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out,
+                                                      int hw, int c) {
+  const int b = blockIdx.x;
+  for (int ch = threadIdx.x * 2; ch < c; ch += blockDim.x * 2) {
+    float s0 = 0.f, s1 = 0.f;
+    for (int p = 0; p < hw; p++) {
+      float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(in + ((size_t)b * hw + p) * c + ch));
+      s0 += f.x;
+      s1 += f.y;
+    }
+    *reinterpret_cast<__nv_bfloat162*>(out + (size_t)b * c + ch) = __floats2bfloat162_rn(s0 / hw, s1 / hw);
+  }
+}
+
+// ------------------------------------------------------------------ response writers
+// Softmax over `n` fp32 logits per row written as fp32 into the response slot of
+// each request (stub->resp + row * resp_stride), optionally followed by the
+// argmax class as int32.  When `flag` is set, the block that finishes last
+// publishes `flag_value` with a system-scope release store: the response is in
+// place (possibly in a peer GPU's or the host's memory) before the flag is seen.
+__global__ void __launch_bounds__(256) softmax_response(const float* __restrict__ logits, int n, int ld, const g_params* stub,
+                                                        uint8_t* direct_out, size_t resp_stride, int write_argmax,
+                                                        uint32_t* counter, volatile uint32_t* flag, uint32_t flag_value) {
+  __shared__ float sh[32];
+  __shared__ float s_max, s_sum;
+  __shared__ int s_arg;
+  const int row = blockIdx.x;
+  const float* x = logits + (size_t)row * ld;
+  uint8_t* base = (direct_out ? direct_out : stub->resp) + (size_t)row * resp_stride;
+  float m = -FLT_MAX;
+  int am = 0;
+  for (int i = threadIdx.x; i < n; i += blockDim.x)
+    if (x[i] > m) {
+      m = x[i];
+      am = i;
+    }
+  // block arg-max
+  float wm = warp_max(m);
+  unsigned ball = __ballot_sync(0xffffffffu, m == wm);
+  int src = __ffs(ball) - 1;
+  int wam = __shfl_sync(0xffffffffu, am, src);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = blockDim.x >> 5;
+  __shared__ int sh_i[32];
+  if (l == 0) {
+    sh[w] = wm;
+    sh_i[w] = wam;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float bm = sh[0];
+    int bi = sh_i[0];
+    for (int k = 1; k < nw; k++)
+      if (sh[k] > bm) {
+        bm = sh[k];
+        bi = sh_i[k];
+      }
+    s_max = bm;
+    s_arg = bi;
+  }
+  __syncthreads();
+  const float mx = s_max;
+  float s = 0.f;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) s += __expf(x[i] - mx);
+  s = block_sum(s, sh);
+  if (threadIdx.x == 0) s_sum = s;
+  __syncthreads();
+  const float inv = 1.f / s_sum;
+  float* o = reinterpret_cast<float*>(base);
+  for (int i = threadIdx.x; i < n; i += blockDim.x) o[i] = __expf(x[i] - mx) * inv;
+  if (write_argmax && threadIdx.x == 0) reinterpret_cast<int*>(base)[n] = s_arg;
+  if (flag) {
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      uint32_t prev = atomicAdd(counter, 1u);
+      if (prev + 1 == gridDim.x) {
+        atomicExch(counter, 0u);
+        __threadfence_system();
+        ptx::st_release_sys(flag, flag_value);
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------ LayerNorm (+ residual)
+// y = LN(x + residual) * gamma + beta, one row per block; hidden <= 8 * blockDim.x.
+__global__ void __launch_bounds__(256) layernorm_rows(const __nv_bfloat16* __restrict__ x,
+                                                      const __nv_bfloat16* __restrict__ residual,
+                                                      const float* __restrict__ gamma, const float* __restrict__ beta,
+                                                      __nv_bfloat16* __restrict__ y, int hidden, float eps) {
+  __shared__ float sh[32];
+  const size_t row = blockIdx.x;
+  const __nv_bfloat16* xr = x + row * hidden;
+  const __nv_bfloat16* rr = residual ? residual + row * hidden : nullptr;
+  float v[8];
+  int cnt = 0;
+  float s = 0.f;
+  for (int i = threadIdx.x; i < hidden && cnt < 8; i += blockDim.x, cnt++) {
+    float f = __bfloat162float(xr[i]);
+    if (rr) f += __bfloat162float(rr[i]);
+    v[cnt] = f;
+    s += f;
+  }
+  const float mean = block_sum(s, sh) / hidden;
+  float q = 0.f;
+  for (int k = 0; k < cnt; k++) q += (v[k] - mean) * (v[k] - mean);
+  const float var = block_sum(q, sh) / hidden;
+  const float rstd = rsqrtf(var + eps);
+  cnt = 0;
+  for (int i = threadIdx.x; i < hidden && cnt < 8; i += blockDim.x, cnt++)
+    y[row * hidden + i] = __float2bfloat16((v[cnt] - mean) * rstd * gamma[i] + beta[i]);
+}
+
+// ------------------------------------------------------------------ BERT embedding
+// Request = seq int32 token ids per sequence.  y[token] = LN(word[id] + pos[t] + type[0]).
+// Reads ids through the stub (ring window) or from `direct_ids`.
+__global__ void __launch_bounds__(256) bert_embed_ln(const g_params* stub, const int* __restrict__ direct_ids, size_t req_stride,
+                                                     int seq, const __nv_bfloat16* __restrict__ word,
+                                                     const __nv_bfloat16* __restrict__ pos,
+                                                     const __nv_bfloat16* __restrict__ type, const float* __restrict__ gamma,
+                                                     const float* __restrict__ beta, __nv_bfloat16* __restrict__ y, int hidden,
+                                                     int vocab, float eps) {
+  __shared__ float sh[32];
+  const int tok = blockIdx.x, b = tok / seq, t = tok - b * seq;
+  const int* ids = direct_ids ? direct_ids + (size_t)b * seq
+                              : reinterpret_cast<const int*>(stub->req + (size_t)b * req_stride);
+  int id = ids[t];
+  id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
+  float v[8];
+  int cnt = 0;
+  float s = 0.f;
+  for (int i = threadIdx.x; i < hidden && cnt < 8; i += blockDim.x, cnt++) {
+    float f = __bfloat162float(word[(size_t)id * hidden + i]) + __bfloat162float(pos[(size_t)t * hidden + i]) +
+              __bfloat162float(type[i]);
+    v[cnt] = f;
+    s += f;
+  }
+  const float mean = block_sum(s, sh) / hidden;
+  float q = 0.f;
+  for (int k = 0; k < cnt; k++) q += (v[k] - mean) * (v[k] - mean);
+  const float rstd = rsqrtf(block_sum(q, sh) / hidden + eps);
+  cnt = 0;
+  for (int i = threadIdx.x; i < hidden && cnt < 8; i += blockDim.x, cnt++)
+    y[(size_t)tok * hidden + i] = __float2bfloat16((v[cnt] - mean) * rstd * gamma[i] + beta[i]);
+}
+
+// ------------------------------------------------------------------ attention (head dim 64)
+// qkv: [tokens, 3*hidden] bf16 with q | k | v blocks; out: [tokens, hidden].
+// One block = one (sequence, head, tile of 32 queries); K and V of the head sit in
+// shared memory; one warp handles 4 queries at a time with fp32 accumulation.
+// This is the simple SIMT form of the operator; it keeps every intermediate on chip.
+template <int SEQ>
+__global__ void __launch_bounds__(256) attention_d64(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restrict__ out,
+                                                     int heads, int ld_qkv, int q_off, int k_off, int v_off, int ld_out,
+                                                     float scale) {
+  extern __shared__ __align__(16) uint8_t att_smem[];
+  __nv_bfloat16* sK = reinterpret_cast<__nv_bfloat16*>(att_smem);        // [SEQ][64+2] padded rows
+  __nv_bfloat16* sV = sK + SEQ * 66;                                     // [SEQ][64]
+  float* sP = reinterpret_cast<float*>(sV + SEQ * 64);                   // [8 warps][SEQ]
+  const int qt = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const size_t tok0 = (size_t)b * SEQ;
+  for (int i = threadIdx.x; i < SEQ * 32; i += blockDim.x) {
+    const int r = i >> 5, c = (i & 31) * 2;
+    const __nv_bfloat16* row = qkv + (tok0 + r) * ld_qkv + h * 64 + c;
+    *reinterpret_cast<__nv_bfloat162*>(sK + r * 66 + c) = *reinterpret_cast<const __nv_bfloat162*>(row + k_off);
+    *reinterpret_cast<__nv_bfloat162*>(sV + r * 64 + c) = *reinterpret_cast<const __nv_bfloat162*>(row + v_off);
+  }
+  __syncthreads();
+  float* p = sP + warp * SEQ;
+  for (int qi = warp; qi < 32; qi += 8) {
+    const int q = qt * 32 + qi;
+    if (q >= SEQ) break;
+    const __nv_bfloat16* qrow = qkv + (tok0 + q) * ld_qkv + q_off + h * 64;
+    float2 qv = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(qrow + lane * 2));
+    // scores: each lane owns keys lane, lane+32, ...
+    float mx = -FLT_MAX;
+    for (int k0 = 0; k0 < SEQ; k0 += 32) {
+      const int k = k0 + lane;
+      float acc = 0.f;
+#pragma unroll 8
+      for (int d = 0; d < 64; d += 2) {
+        float2 kv = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(sK + k * 66 + d));
+        const float qx = __shfl_sync(0xffffffffu, qv.x, d >> 1), qy = __shfl_sync(0xffffffffu, qv.y, d >> 1);
+        acc += qx * kv.x + qy * kv.y;
+      }
+      acc *= scale;
+      p[k] = acc;
+      mx = fmaxf(mx, acc);
+    }
+    mx = warp_max(mx);
+    float sum = 0.f;
+    for (int k = lane; k < SEQ; k += 32) {
+      const float e = __expf(p[k] - mx);
+      p[k] = e;
+      sum += e;
+    }
+    sum = warp_sum(sum);
+    __syncwarp();
+    // out: each lane owns dims 2*lane, 2*lane+1
+    float o0 = 0.f, o1 = 0.f;
+    for (int k = 0; k < SEQ; k++) {
+      const float pk = p[k];
+      float2 vv = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(sV + k * 64 + lane * 2));
+      o0 += pk * vv.x;
+      o1 += pk * vv.y;
+    }
+    const float inv = 1.f / sum;
+    *reinterpret_cast<__nv_bfloat162*>(out + (tok0 + q) * ld_out + h * 64 + lane * 2) = __floats2bfloat162_rn(o0 * inv, o1 * inv);
+    __syncwarp();
+  }
+}
+
+int grid_for(size_t total, int threads) {
+  size_t b = (total + threads - 1) / threads;
+  size_t cap = 148 * 16;
+  return (int)(b < 1 ? 1 : (b > cap ? cap : b));
+}
+
+}  // namespace
+
+cudaError_t nn_stem_im2col(const void* d_stub, const float* direct_in, int batch, void* out, const float mean[3],
+                           const float inv_std[3], cudaStream_t s) {
+  size_t total = (size_t)batch * 112 * 112 * 24;
+  stem_im2col<<<grid_for(total, 256), 256, 0, s>>>((const g_params*)d_stub, direct_in, batch, (__nv_bfloat16*)out,
+                                                   make_float3(mean[0], mean[1], mean[2]),
+                                                   make_float3(inv_std[0], inv_std[1], inv_std[2]));
+  return cudaGetLastError();
+}
+cudaError_t nn_maxpool3x3s2(const void* in, void* out, int n, int h, int w, int c, cudaStream_t s) {
+  if (c % 8) return cudaErrorInvalidValue;
+  int oh = (h - 1) / 2 + 1, ow = (w - 1) / 2 + 1;
+  maxpool3x3s2<<<grid_for((size_t)n * oh * ow * (c / 8), 256), 256, 0, s>>>((const __nv_bfloat16*)in, (__nv_bfloat16*)out, n,
+                                                                          h, w, c);
+  return cudaGetLastError();
+}
+cudaError_t nn_global_avgpool(const void* in, void* out, int n, int hw, int c, cudaStream_t s) {
+  if (c % 2) return cudaErrorInvalidValue;
+  global_avgpool<<<n, 256, 0, s>>>((const __nv_bfloat16*)in, (__nv_bfloat16*)out, hw, c);
+  return cudaGetLastError();
+}
+cudaError_t nn_softmax_response(const float* logits, int rows, int n, int ld, const void* d_stub, void* direct_out,
+                                size_t resp_stride, int write_argmax, uint32_t* counter, uint32_t* flag, uint32_t flag_value,
+                                cudaStream_t s) {
+  if (rows <= 0) return cudaSuccess;
+  softmax_response<<<rows, 256, 0, s>>>(logits, n, ld, (const g_params*)d_stub, (uint8_t*)direct_out, resp_stride,
+                                        write_argmax, counter, flag, flag_value);
+  return cudaGetLastError();
+}
+cudaError_t nn_layernorm(const void* x, const void* residual, const float* gamma, const float* beta, void* y, int rows,
+                         int hidden, float eps, cudaStream_t s) {
+  if (hidden > 2048) return cudaErrorInvalidValue;
+  layernorm_rows<<<rows, 256, 0, s>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)residual, gamma, beta,
+                                      (__nv_bfloat16*)y, hidden, eps);
+  return cudaGetLastError();
+}
+cudaError_t nn_bert_embed_ln(const void* d_stub, const int* direct_ids, size_t req_stride, int batch, int seq, const void* word,
+                             const void* pos, const void* type, const float* gamma, const float* beta, void* y, int hidden,
+                             int vocab, float eps, cudaStream_t s) {
+  if (hidden > 2048) return cudaErrorInvalidValue;
+  bert_embed_ln<<<batch * seq, 256, 0, s>>>((const g_params*)d_stub, direct_ids, req_stride, seq, (const __nv_bfloat16*)word,
+                                            (const __nv_bfloat16*)pos, (const __nv_bfloat16*)type, gamma, beta,
+                                            (__nv_bfloat16*)y, hidden, vocab, eps);
+  return cudaGetLastError();
+}
+cudaError_t nn_attention_d64(const void* qkv, void* out, int batch, int seq, int heads, int ld_qkv, int q_off, int k_off,
+                             int v_off, int ld_out, cudaStream_t s) {
+  const float scale = 0.125f;
+  dim3 grid((seq + 31) / 32, heads, batch);
+  if (seq == 128) {
+    const int smem = 128 * 66 * 2 + 128 * 64 * 2 + 8 * 128 * 4;
+    attention_d64<128><<<grid, 256, smem, s>>>((const __nv_bfloat16*)qkv, (__nv_bfloat16*)out, heads, ld_qkv, q_off, k_off,
+                                               v_off, ld_out, scale);
+  } else if (seq == 384) {
+    const int smem = 384 * 66 * 2 + 384 * 64 * 2 + 8 * 384 * 4;
+    static bool attr = false;
+    if (!attr) {
+      cudaFuncSetAttribute(attention_d64<384>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+      attr = true;
+    }
+    attention_d64<384><<<grid, 256, smem, s>>>((const __nv_bfloat16*)qkv, (__nv_bfloat16*)out, heads, ld_qkv, q_off, k_off,
+                                               v_off, ld_out, scale);
+  } else {
+    return cudaErrorInvalidValue;
+  }
+  return cudaGetLastError();
+}

@@ -221,7 +221,7 @@ __global__ void __launch_bounds__(256) sg_persistent(SgCtrl* ctrl, uint32_t* cou
     {
       const uint64_t* src = reinterpret_cast<const uint64_t*>(const_cast<const SgItem*>(ctrl->items));
       uint64_t* dst = reinterpret_cast<uint64_t*>(s_items);
-      for (uint32_t i = threadIdx.x; i < n_items * 3; i += blockDim.x) dst[i] = src[i];
+      for (uint32_t i = threadIdx.x; i < n_items * 3; i += blockDim.x) dst[i] = ptx::ld_relaxed_sys_u64(src + i);
     }
     __syncthreads();
     for (uint32_t c = blockIdx.x; c < n_chunks; c += gridDim.x) {

@@ -227,6 +227,28 @@ static inline int uniform_float_fill(uint8_t* p, size_t n, uint64_t seq) {
   return 0;
 }
 
+// Seeded token ids: int32 uniform over a 30522-word vocabulary.
+static inline int token_ids_fill(uint8_t* p, size_t n, uint64_t seq) {
+  SrpcRng r(0xB5297A4Dull * (seq + 1) + 777);
+  int32_t* ids = reinterpret_cast<int32_t*>(p);
+  for (size_t i = 0; i < n / 4; i++) ids[i] = (int32_t)(r.next() % 30522u);
+  return 0;
+}
+// Seeded standard-normal floats (Box-Muller), one stream per request index.
+static inline int normal_float_fill(uint8_t* p, size_t n, uint64_t seq) {
+  SrpcRng r(0x2545F491ull * (seq + 1) + 4242);
+  float* f = reinterpret_cast<float*>(p);
+  size_t m = n / 4;
+  for (size_t i = 0; i < m; i += 2) {
+    double u1 = r.uniform(), u2 = r.uniform();
+    if (u1 < 1e-300) u1 = 1e-300;
+    double rad = std::sqrt(-2.0 * std::log(u1));
+    f[i] = (float)(rad * std::cos(6.283185307179586 * u2));
+    if (i + 1 < m) f[i + 1] = (float)(rad * std::sin(6.283185307179586 * u2));
+  }
+  return 0;
+}
+
 // ------------------------------------------------------------------ client
 enum R_STATES : uint32_t { R_CREATE = 0, R_SENT, R_RECV, R_ERROR };
 

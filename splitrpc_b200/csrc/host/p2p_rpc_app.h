@@ -337,7 +337,12 @@ class MetaAppCtx {
   // Makes the work stream wait until *d_state == value.
   void AppRrRunNotify(volatile uint32_t* d_state, int value) {
     if (device_id >= 0) {
-      srpc_require_cuda("stream wait")->stream_wait_value32(work_stream, d_state, (uint32_t)value);
+      const SrpcDeviceOps* ops = srpc_require_cuda("stream wait");
+      ops->set_device(device_id);  // driver-level memops need this thread bound to the device's context
+      if (ops->stream_wait_value32(work_stream, d_state, (uint32_t)value) != 0) {
+        srpc_log(SRPC_LOG_ERROR, "stream wait failed: %s", ops->last_error());
+        last_status = -2;
+      }
     } else {
       last_status = spin_until(d_state, (uint32_t)value) ? 0 : -1;
     }
@@ -347,7 +352,12 @@ class MetaAppCtx {
   // Writes `value` into the doorbell once everything queued so far has finished.
   void AppCompleteNotify(uint32_t value = 2) {
     if (device_id >= 0) {
-      srpc_require_cuda("stream write")->stream_write_value32(work_stream, (volatile uint32_t*)d_door_bell, value);
+      const SrpcDeviceOps* ops = srpc_require_cuda("stream write");
+      ops->set_device(device_id);
+      if (ops->stream_write_value32(work_stream, (volatile uint32_t*)d_door_bell, value) != 0) {
+        srpc_log(SRPC_LOG_ERROR, "stream write failed: %s", ops->last_error());
+        last_status = -2;
+      }
     } else {
       __atomic_store_n(door_bell, value, __ATOMIC_RELEASE);
     }

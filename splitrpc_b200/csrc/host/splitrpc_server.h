@@ -223,6 +223,7 @@ class SplitRpcServer {
         while (nt < burst) {
           P2pRpcAppRr* slot = rep.app->app_rr_pool->get_app_rr((rep.tx_idx + nt) % pool_n);
           if (__atomic_load_n(slot->h_state, __ATOMIC_ACQUIRE) != APP_RR_STATUS::WORK_COMPLETE) break;
+          if (!slot->rpc_rr) break;  // completed without ever being filled: leave it to the worker's accounting
           rrs[nt] = (P2pRpcRr*)slot->rpc_rr;
           stubs[nt] = slot->h_stub;
           slots[nt] = slot;

@@ -1,0 +1,3 @@
+"""Model families served by the stack, built from this library's sm_100a kernels."""
+from .resnet import ResNet50  # noqa: F401
+from .bert import BertClassifier, BERT_BASE, BERT_LARGE  # noqa: F401

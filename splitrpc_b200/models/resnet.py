@@ -1,0 +1,164 @@
+"""ResNet-50 (v1.5, batch-norm folded into the convolutions) in bf16 NHWC.
+
+Every convolution is the tcgen05 implicit-GEMM kernel: 1x1 stride-1 layers run as
+plain TMA-fed GEMMs over ``[N*H*W, Cin]``, 3x3 and strided layers gather their
+rows; bias, residual add and ReLU live in the GEMM epilogue.  The stem reads the
+fp32 CHW request bytes where the scatter-gather engine put them (through the
+device stub), normalises, casts and lays out its im2col matrix in one pass.
+The classifier's softmax writes straight into the response ring.
+
+All activations live in buffers allocated once for ``max_batch``; ``forward``
+only launches kernels, so it can be captured into a CUDA graph per batch size.
+The original serves this model through ONNX Runtime + TensorRT
+(reference ``src/apps/ort_app.h:477-527``, ``src/apps/ort_defs.h:90-140``).
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from .. import ops
+
+REQ_BYTES = 3 * 224 * 224 * 4
+RESP_BYTES = 1000 * 4
+_LAYERS = ((64, 3, 1), (128, 4, 2), (256, 6, 2), (512, 3, 2))
+
+
+class ResNet50:
+    req_size = REQ_BYTES
+    resp_size = RESP_BYTES
+
+    def __init__(self, device: int = 0, max_batch: int = 64, seed: int = 0, normalize: bool = False):
+        self.device = torch.device("cuda", device)
+        self.max_batch = max_batch
+        self.mean = ops.IMAGENET_MEAN if normalize else (0.0, 0.0, 0.0)
+        self.inv_std = ops.IMAGENET_INV_STD if normalize else (1.0, 1.0, 1.0)
+        g = torch.Generator(device="cpu").manual_seed(seed)
+        self.params: dict[str, torch.Tensor] = {}
+
+        def conv(name, cout, cin, k, gain=1.0):
+            std = gain * math.sqrt(2.0 / (cin * k * k))
+            w = torch.randn((cout, k, k, cin), generator=g) * std
+            self.params[name + ".w"] = w.to(self.device, torch.bfloat16).contiguous()
+            self.params[name + ".b"] = (torch.randn((cout,), generator=g) * 0.05).to(self.device, torch.float32)
+
+        # stem weight in im2col order [64, 192]: k = c*49 + ky*7 + kx, zero padded from 147
+        w = torch.randn((64, 3, 7, 7), generator=g) * math.sqrt(2.0 / 147)
+        stem = torch.zeros((64, 192))
+        stem[:, :147] = w.reshape(64, 147)
+        self.params["stem.w"] = stem.to(self.device, torch.bfloat16).contiguous()
+        self.params["stem.w_nchw"] = w.to(self.device)
+        self.params["stem.b"] = (torch.randn((64,), generator=g) * 0.05).to(self.device, torch.float32)
+        cin = 64
+        self.blocks = []
+        for li, (width, n, stride) in enumerate(_LAYERS):
+            for bi in range(n):
+                s = stride if bi == 0 else 1
+                name = f"l{li}.b{bi}"
+                conv(name + ".c1", width, cin, 1)
+                conv(name + ".c2", width, width, 3)
+                conv(name + ".c3", width * 4, width, 1, gain=0.5)
+                ds = bi == 0
+                if ds:
+                    conv(name + ".ds", width * 4, cin, 1, gain=0.5)
+                self.blocks.append((name, cin, width, s, ds))
+                cin = width * 4
+        self.params["fc.w"] = (torch.randn((1000, 2048), generator=g) * math.sqrt(1.0 / 2048)).to(self.device, torch.bfloat16)
+        self.params["fc.b"] = (torch.randn((1000,), generator=g) * 0.05).to(self.device, torch.float32)
+        self._plan(max_batch)
+
+    # ------------------------------------------------------------------ buffers
+    def _plan(self, nb: int) -> None:
+        dev, bf = self.device, torch.bfloat16
+        self.buf = {
+            "im2col": torch.empty((nb * 112 * 112, 192), dtype=bf, device=dev),
+            "stem": torch.empty((nb, 112, 112, 64), dtype=bf, device=dev),
+            "pool": torch.empty((nb, 56, 56, 64), dtype=bf, device=dev),
+            "avg": torch.empty((nb, 2048), dtype=bf, device=dev),
+            "logits": torch.empty((nb, 1000), dtype=torch.float32, device=dev),
+        }
+        h = 56
+        for name, cin, width, s, ds in self.blocks:
+            ho = h // s
+            self.buf[name + ".t1"] = torch.empty((nb, h, h, width), dtype=bf, device=dev)
+            self.buf[name + ".t2"] = torch.empty((nb, ho, ho, width), dtype=bf, device=dev)
+            self.buf[name + ".out"] = torch.empty((nb, ho, ho, width * 4), dtype=bf, device=dev)
+            if ds:
+                self.buf[name + ".ds"] = torch.empty((nb, ho, ho, width * 4), dtype=bf, device=dev)
+            h = ho
+        self.kernels_per_forward = 3 + sum(3 + (1 if b[4] else 0) for b in self.blocks) + 3
+
+    # ------------------------------------------------------------------ forward
+    def _conv1x1(self, x, name, out, act, residual=None):
+        """1x1 stride-1 convolution as a plain GEMM over the pixels."""
+        n, h, w, cin = x.shape
+        wt = self.params[name + ".w"]
+        cout = wt.shape[0]
+        ops.gemm(x.view(n * h * w, cin), wt.view(cout, cin), bias=self.params[name + ".b"],
+                 residual=None if residual is None else residual.view(n * h * w, cout), act=act,
+                 out=out.view(n * h * w, cout))
+        return out
+
+    def forward(self, batch: int, x: torch.Tensor | None = None, d_stub: int = 0, out: torch.Tensor | None = None,
+                flag_ptr: int = 0, flag_value: int = 0, counter: torch.Tensor | None = None) -> torch.Tensor:
+        """Launches the whole network for ``batch`` images on the current stream.
+
+        Input: fp32 ``[batch,3,224,224]`` tensor ``x`` or the request window behind ``d_stub``.
+        Output: fp32 softmax rows in ``out`` (``[batch,1000]``) or the response window behind ``d_stub``.
+        """
+        p, b = self.params, self.buf
+        nb = batch
+        ops.stem_im2col(b["im2col"], nb, x=x, d_stub=d_stub, mean=self.mean, inv_std=self.inv_std)
+        ops.gemm(b["im2col"][: nb * 12544], p["stem.w"], bias=p["stem.b"], act="relu", out=b["stem"][:nb].view(nb * 12544, 64))
+        cur = ops.maxpool3x3s2(b["stem"][:nb], out=b["pool"][:nb])
+        for name, cin, width, s, ds in self.blocks:
+            t1 = self._conv1x1(cur, name + ".c1", b[name + ".t1"][:nb], "relu")
+            t2 = ops.conv2d_nhwc(t1, p[name + ".c2.w"], bias=p[name + ".c2.b"], stride=s, pad=1, act="relu",
+                                 out=b[name + ".t2"][:nb])
+            if ds:
+                if s == 1:
+                    idn = self._conv1x1(cur, name + ".ds", b[name + ".ds"][:nb], None)
+                else:
+                    idn = ops.conv2d_nhwc(cur, p[name + ".ds.w"], bias=p[name + ".ds.b"], stride=s, pad=0, act=None,
+                                          out=b[name + ".ds"][:nb])
+            else:
+                idn = cur
+            cur = self._conv1x1(t2, name + ".c3", b[name + ".out"][:nb], "relu", residual=idn)
+        avg = ops.global_avgpool(cur, out=b["avg"][:nb])
+        ops.gemm(avg, p["fc.w"], bias=p["fc.b"], out=b["logits"][:nb])
+        ops.softmax_response(b["logits"][:nb], nb, out=out, d_stub=0 if out is not None else d_stub, resp_stride=RESP_BYTES,
+                             counter=counter, flag_ptr=flag_ptr, flag_value=flag_value)
+        return b["logits"][:nb]
+
+    __call__ = forward
+
+    # ------------------------------------------------------------------ oracle
+    @torch.no_grad()
+    def reference_forward(self, x: torch.Tensor) -> torch.Tensor:
+        """Plain PyTorch fp32 evaluation of the same network and weights (returns softmax rows)."""
+        import torch.nn.functional as F
+
+        p = self.params
+        mean = torch.tensor(self.mean, device=x.device).view(1, 3, 1, 1)
+        inv = torch.tensor(self.inv_std, device=x.device).view(1, 3, 1, 1)
+
+        def cw(name):
+            return p[name + ".w"].float().permute(0, 3, 1, 2).contiguous(), p[name + ".b"]
+
+        y = F.relu(F.conv2d((x.float() - mean) * inv, p["stem.w_nchw"].to(torch.bfloat16).float(), p["stem.b"], 2, 3))
+        y = F.max_pool2d(y, 3, 2, 1)
+        for name, cin, width, s, ds in self.blocks:
+            w1, b1 = cw(name + ".c1")
+            w2, b2 = cw(name + ".c2")
+            w3, b3 = cw(name + ".c3")
+            t = F.relu(F.conv2d(y, w1, b1))
+            t = F.relu(F.conv2d(t, w2, b2, s, 1))
+            idn = y
+            if ds:
+                wd, bd = cw(name + ".ds")
+                idn = F.conv2d(y, wd, bd, s)
+            y = F.relu(F.conv2d(t, w3, b3) + idn)
+        y = y.mean((2, 3))
+        logits = y @ p["fc.w"].float().t() + p["fc.b"]
+        return torch.softmax(logits, -1)

@@ -11,7 +11,7 @@ import torch
 
 from .. import _C
 
-ACT = {None: _C.ACT_NONE, "none": _C.ACT_NONE, "relu": _C.ACT_RELU, "gelu": _C.ACT_GELU}
+ACT = {None: _C.ACT_NONE, "none": _C.ACT_NONE, "relu": _C.ACT_RELU, "gelu": _C.ACT_GELU, "tanh": _C.ACT_TANH}
 
 
 def _stream() -> int:
@@ -86,3 +86,82 @@ def conv2d_nhwc(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = No
 def sg_copy(items, impl: int = 0, n_blocks: int = 0) -> None:
     """Runs a copy list ``[(src_addr, dst_addr, nbytes)]`` on the current stream and waits for it."""
     _C.sg_copy(list(items), impl, n_blocks, _stream())
+
+
+IMAGENET_MEAN = (0.485, 0.456, 0.406)
+IMAGENET_INV_STD = (1 / 0.229, 1 / 0.224, 1 / 0.225)
+
+
+def stem_im2col(out: torch.Tensor, batch: int, x: torch.Tensor | None = None, d_stub: int = 0,
+                mean=(0.0, 0.0, 0.0), inv_std=(1.0, 1.0, 1.0)) -> torch.Tensor:
+    """im2col of the 7x7/2 stem over fp32 CHW images (given directly or through a device stub), fused with
+    normalisation and the bf16 cast.  ``out`` is ``[batch*112*112, 192]`` bf16."""
+    assert out.dtype == torch.bfloat16 and out.is_contiguous() and out.numel() >= batch * 112 * 112 * 192
+    if x is not None:
+        assert x.dtype == torch.float32 and x.is_contiguous() and x.numel() >= batch * 3 * 224 * 224
+    _C.stem_im2col(d_stub, _ptr(x), batch, out.data_ptr(), list(mean), list(inv_std), _stream())
+    return out
+
+
+def maxpool3x3s2(x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    n, h, w, c = x.shape
+    oh, ow = (h - 1) // 2 + 1, (w - 1) // 2 + 1
+    if out is None:
+        out = torch.empty((n, oh, ow, c), dtype=torch.bfloat16, device=x.device)
+    _C.maxpool3x3s2(x.data_ptr(), out.data_ptr(), n, h, w, c, _stream())
+    return out
+
+
+def global_avgpool(x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    n, h, w, c = x.shape
+    if out is None:
+        out = torch.empty((n, c), dtype=torch.bfloat16, device=x.device)
+    _C.global_avgpool(x.data_ptr(), out.data_ptr(), n, h * w, c, _stream())
+    return out
+
+
+def softmax_response(logits: torch.Tensor, rows: int, out: torch.Tensor | None = None, d_stub: int = 0,
+                     resp_stride: int | None = None, write_argmax: bool = False, counter: torch.Tensor | None = None,
+                     flag_ptr: int = 0, flag_value: int = 0) -> None:
+    """Row softmax of fp32 logits written as fp32 into response slots (``out`` or the stub's response window)."""
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1
+    n = logits.shape[1]
+    if resp_stride is None:
+        resp_stride = (n + (1 if write_argmax else 0)) * 4
+    _C.softmax_response(logits.data_ptr(), rows, n, logits.stride(0), d_stub, _ptr(out), resp_stride, write_argmax,
+                        _ptr(counter), flag_ptr, flag_value, _stream())
+
+
+def layernorm(x: torch.Tensor, gamma: torch.Tensor, beta: torch.Tensor, residual: torch.Tensor | None = None,
+              out: torch.Tensor | None = None, eps: float = 1e-12) -> torch.Tensor:
+    """``LN(x + residual) * gamma + beta`` over the last dimension (bf16 in/out, fp32 parameters)."""
+    rows, hidden = x.shape
+    if out is None:
+        out = torch.empty_like(x)
+    _C.layernorm(x.data_ptr(), _ptr(residual), gamma.data_ptr(), beta.data_ptr(), out.data_ptr(), rows, hidden, eps, _stream())
+    return out
+
+
+def bert_embed_ln(out: torch.Tensor, batch: int, seq: int, word: torch.Tensor, pos: torch.Tensor, typ: torch.Tensor,
+                  gamma: torch.Tensor, beta: torch.Tensor, ids: torch.Tensor | None = None, d_stub: int = 0,
+                  req_stride: int | None = None, eps: float = 1e-12) -> torch.Tensor:
+    """Embedding gather (word + position + type 0) + LayerNorm, reading int32 ids directly or through a stub."""
+    vocab, hidden = word.shape
+    if req_stride is None:
+        req_stride = seq * 4
+    _C.bert_embed_ln(d_stub, _ptr(ids), req_stride, batch, seq, word.data_ptr(), pos.data_ptr(), typ.data_ptr(),
+                     gamma.data_ptr(), beta.data_ptr(), out.data_ptr(), hidden, vocab, eps, _stream())
+    return out
+
+
+def attention_d64(qkv: torch.Tensor, batch: int, seq: int, heads: int, out: torch.Tensor | None = None,
+                  offsets: tuple[int, int, int] | None = None) -> torch.Tensor:
+    """Multi-head attention with head dim 64 over ``qkv = [tokens, q|k|v]`` (all-ones mask)."""
+    hidden = heads * 64
+    if offsets is None:
+        offsets = (0, hidden, 2 * hidden)
+    if out is None:
+        out = torch.empty((batch * seq, hidden), dtype=torch.bfloat16, device=qkv.device)
+    _C.attention_d64(qkv.data_ptr(), out.data_ptr(), batch, seq, heads, qkv.stride(0), offsets[0], offsets[1], offsets[2],
+                     out.stride(0), _stream())
+    return out

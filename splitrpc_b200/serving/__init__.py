@@ -4,6 +4,7 @@ from __future__ import annotations
 import numpy as np
 
 from .. import _C
+from .engine import ModelServer  # noqa: F401
 
 
 def lenet5_random_weights(seed: int = 0) -> list[np.ndarray]:

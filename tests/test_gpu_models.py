@@ -1,0 +1,112 @@
+"""Model numerics against plain PyTorch fp32 and end-to-end serving of the models."""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def torch_cuda():
+    import torch
+
+    assert torch.cuda.is_available()
+    torch.cuda.set_device(0)
+    return torch
+
+
+def test_nn_layers_match_pytorch(torch_cuda):
+    torch = torch_cuda
+    from splitrpc_b200 import ops
+
+    F = torch.nn.functional
+    x = torch.randn(3, 56, 56, 64, device="cuda").bfloat16()
+    ref = F.max_pool2d(x.float().permute(0, 3, 1, 2), 3, 2, 1).permute(0, 2, 3, 1)
+    assert torch.equal(ops.maxpool3x3s2(x).float(), ref)
+    y = torch.randn(4, 7, 7, 2048, device="cuda").bfloat16()
+    torch.testing.assert_close(ops.global_avgpool(y).float(), y.float().mean((1, 2)), rtol=1e-2, atol=1e-2)
+    h = torch.randn(300, 768, device="cuda").bfloat16()
+    r = torch.randn(300, 768, device="cuda").bfloat16()
+    g, b = torch.randn(768, device="cuda"), torch.randn(768, device="cuda")
+    ln = ops.layernorm(h, g, b, residual=r)
+    torch.testing.assert_close(ln.float(), F.layer_norm(h.float() + r.float(), (768,), g, b, 1e-12), rtol=2e-2, atol=2e-2)
+    logits = torch.randn(5, 1000, device="cuda")
+    out = torch.zeros(5, 1001, device="cuda")
+    ops.softmax_response(logits, 5, out=out, resp_stride=1001 * 4, write_argmax=True)
+    torch.cuda.synchronize()
+    torch.testing.assert_close(out[:, :1000], torch.softmax(logits, -1), rtol=1e-4, atol=1e-6)
+    assert torch.equal(out[:, 1000].view(torch.int32), logits.argmax(-1).int())
+    img = torch.randn(2, 3, 224, 224, device="cuda")
+    col = torch.zeros(2 * 112 * 112, 192, dtype=torch.bfloat16, device="cuda")
+    ops.stem_im2col(col, 2, x=img, mean=(0.1, 0.2, 0.3), inv_std=(2.0, 3.0, 4.0))
+    m = torch.tensor([0.1, 0.2, 0.3], device="cuda").view(1, 3, 1, 1)
+    s = torch.tensor([2.0, 3.0, 4.0], device="cuda").view(1, 3, 1, 1)
+    unf = F.unfold((img - m) * s, 7, padding=3, stride=2).transpose(1, 2).reshape(-1, 147)
+    torch.testing.assert_close(col[:, :147].float(), unf.bfloat16().float(), rtol=0, atol=0)
+    assert col[:, 147:].abs().max() == 0
+
+
+@pytest.mark.parametrize("seq,heads", [(128, 12), (384, 16)])
+def test_attention_matches_pytorch(torch_cuda, seq, heads):
+    torch = torch_cuda
+    from splitrpc_b200 import ops
+
+    B, H = 2, heads * 64
+    qkv = (torch.randn(B * seq, 3 * H, device="cuda") * 0.5).bfloat16()
+    out = ops.attention_d64(qkv, B, seq, heads)
+    q, k, v = (t.float().view(B, seq, heads, 64).transpose(1, 2) for t in qkv.split(H, dim=1))
+    ref = (torch.softmax(q @ k.transpose(-1, -2) / 8.0, -1) @ v).transpose(1, 2).reshape(B * seq, H)
+    torch.testing.assert_close(out.float(), ref, rtol=2e-2, atol=2e-2)
+
+
+def test_resnet50_matches_fp32_reference(torch_cuda):
+    torch = torch_cuda
+    from splitrpc_b200 import ops
+    from splitrpc_b200.models import ResNet50
+
+    m = ResNet50(device=0, max_batch=4)
+    x = torch.randn(3, 3, 224, 224, device="cuda")
+    out = torch.zeros(3, 1000, device="cuda")
+    logits = m.forward(3, x=x, out=out)
+    ops.check_status()
+    ref = m.reference_forward(x)
+    assert torch.isfinite(out).all() and abs(out.sum().item() - 3.0) < 1e-3
+    # bf16 activations through 53 layers: compare the probability rows as vectors
+    cos = torch.nn.functional.cosine_similarity(out, ref, dim=1)
+    assert cos.min().item() > 0.98, cos
+    assert (out.argmax(1) == ref.argmax(1)).float().mean().item() >= 2 / 3
+
+
+def test_bert_matches_fp32_reference(torch_cuda):
+    torch = torch_cuda
+    from splitrpc_b200 import ops
+    from splitrpc_b200.models import BertClassifier, BERT_BASE
+
+    m = BertClassifier(BERT_BASE, seq=128, device=0, max_batch=4)
+    ids = torch.randint(0, 30522, (3, 128), device="cuda", dtype=torch.int32)
+    out = torch.zeros(3, 2, device="cuda")
+    m.forward(3, ids=ids, out=out)
+    ops.check_status()
+    ref = m.reference_forward(ids)
+    torch.testing.assert_close(out, ref, rtol=5e-2, atol=3e-2)
+
+
+def test_model_server_end_to_end_resnet(torch_cuda):
+    torch = torch_cuda
+    from splitrpc_b200.models import ResNet50
+    from splitrpc_b200.serving import ModelServer
+
+    m = ResNet50(device=0, max_batch=8)
+    srv = ModelServer(m, device=0, max_batch=8, outstanding=16)
+    with srv:
+        cli = srv.client(total=48, warmup=0, payload="normal", verify=True, n_payloads=4)
+        assert cli.run_closed_loop(16)
+        assert cli.received == 48
+        stats = srv.server.stats()
+        ws = srv.server.worker_stats(0)
+    assert stats["sg_errors"] == 0 and ws["wait_timeouts"] == 0
+    x = torch.from_numpy(np.frombuffer(cli.payload(1), dtype=np.float32).copy()).view(1, 3, 224, 224).cuda()
+    direct = torch.zeros(1, 1000, device="cuda")
+    m.forward(1, x=x, out=direct)
+    torch.cuda.synchronize()
+    got = torch.from_numpy(np.frombuffer(cli.response(5), dtype=np.float32).copy())  # request 5 used payload 5 % 4 == 1
+    torch.testing.assert_close(got, direct[0].cpu(), rtol=1e-3, atol=1e-5)
