@@ -66,24 +66,26 @@ void bind_ops(py::module_& m) {
   m.attr("ACT_TANH") = (int)GEMM_ACT_TANH;
   m.def("gemm_bf16",
         [](uintptr_t a, int lda, uintptr_t b, int ldb, int M, int N, int K, uintptr_t out, int ldo, bool out_fp32,
-           uintptr_t bias, uintptr_t residual, int ldr, int act, uintptr_t status, uintptr_t stream) {
+           uintptr_t bias, uintptr_t residual, int ldr, int act, uintptr_t status, uintptr_t stream, int impl) {
           GemmEpilogue ep = make_ep(out, ldo, out_fp32, bias, residual, ldr, act);
-          check(srpc_gemm_bf16((const void*)a, lda, (const void*)b, ldb, M, N, K, ep, (uint32_t*)status, (cudaStream_t)stream),
+          auto fn = impl == 1 ? srpc_gemm_bf16 : srpc_gemm_bf16_v2;
+          check(fn((const void*)a, lda, (const void*)b, ldb, M, N, K, ep, (uint32_t*)status, (cudaStream_t)stream),
                 "gemm_bf16");
         },
         py::arg("a"), py::arg("lda"), py::arg("b"), py::arg("ldb"), py::arg("M"), py::arg("N"), py::arg("K"), py::arg("out"),
         py::arg("ldo"), py::arg("out_fp32") = false, py::arg("bias") = 0, py::arg("residual") = 0, py::arg("ldr") = 0,
-        py::arg("act") = 0, py::arg("status") = 0, py::arg("stream") = 0);
+        py::arg("act") = 0, py::arg("status") = 0, py::arg("stream") = 0, py::arg("impl") = 2);
   m.def("conv_bf16",
         [](uintptr_t in, uintptr_t w, int n, int h, int wd, int cin, int cout, int r, int s, int stride, int pad,
-           uintptr_t out, uintptr_t bias, uintptr_t residual, int act, uintptr_t status, uintptr_t stream) {
+           uintptr_t out, uintptr_t bias, uintptr_t residual, int act, uintptr_t status, uintptr_t stream, int impl) {
           ConvShape cs{n, h, wd, cin, cout, r, s, stride, pad, (h + 2 * pad - r) / stride + 1, (wd + 2 * pad - s) / stride + 1};
           GemmEpilogue ep = make_ep(out, cout, false, bias, residual, cout, act);
-          check(srpc_conv_bf16((const void*)in, (const void*)w, cs, ep, (uint32_t*)status, (cudaStream_t)stream), "conv_bf16");
+          auto fn = impl == 1 ? srpc_conv_bf16 : srpc_conv_bf16_tma;
+          check(fn((const void*)in, (const void*)w, cs, ep, (uint32_t*)status, (cudaStream_t)stream), "conv_bf16");
         },
         py::arg("input"), py::arg("weight"), py::arg("n"), py::arg("h"), py::arg("w"), py::arg("cin"), py::arg("cout"),
         py::arg("r"), py::arg("s"), py::arg("stride"), py::arg("pad"), py::arg("out"), py::arg("bias") = 0,
-        py::arg("residual") = 0, py::arg("act") = 0, py::arg("status") = 0, py::arg("stream") = 0);
+        py::arg("residual") = 0, py::arg("act") = 0, py::arg("status") = 0, py::arg("stream") = 0, py::arg("impl") = 2);
 
   // ---- memory-bound layers
   m.def("stem_im2col",

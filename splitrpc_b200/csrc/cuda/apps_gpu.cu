@@ -95,31 +95,30 @@ __global__ void vec_add_kernel(const g_params* stub, size_t req_size, size_t res
 // size, serves the batch, answers 2.
 __global__ void vec_add_resident(const g_params* stub, volatile uint32_t* door_bell, size_t req_size, size_t resp_size,
                                  uint64_t idle_ns, uint32_t* status) {
-  __shared__ uint32_t s_batch;
+  __shared__ uint32_t s_batch, s_leave;
   uint64_t last = ptx::globaltimer_ns();
   for (;;) {
     if (threadIdx.x == 0) {
-      uint32_t v = 0;
+      uint32_t batch = 0, leave = 0;
       for (int spin = 0; spin < 4096; spin++) {
-        v = ptx::ld_acquire_sys(door_bell);
-        if (v == APP_DOORBELL_EXIT) break;
+        const uint32_t v = ptx::ld_acquire_sys(door_bell);
+        if (v == APP_DOORBELL_EXIT || ptx::globaltimer_ns() - last > idle_ns) {
+          leave = 1;  // exit request or idle limit
+          break;
+        }
         if (v != APP_DOORBELL_IDLE && (v & APP_DOORBELL_START)) {
-          v &= ~APP_DOORBELL_START;
+          batch = v & ~APP_DOORBELL_START;
           break;
         }
-        if (ptx::globaltimer_ns() - last > idle_ns) {
-          v = 3u;
-          break;
-        }
-        v = 0;
         __nanosleep(200);
       }
-      s_batch = v;
+      s_batch = batch;
+      s_leave = leave;
     }
     __syncthreads();
-    uint32_t batch = s_batch;
+    const uint32_t batch = s_batch, leave = s_leave;
     __syncthreads();
-    if (batch == 3u) break;   // exit request or idle limit
+    if (leave) break;
     if (batch == 0) continue;
     // The stub lives in mapped host memory and changes between batches while this
     // kernel stays resident: read it with system-scope loads, never from a cache.

@@ -1,0 +1,560 @@
+// Persistent tcgen05 GEMM / convolution kernel (the production path).
+//
+//   D[M,N] = act(A[M,K] . B[N,K]^T + bias + residual)          (GEMM mode)
+//   out = act(conv(in NHWC, filter [Cout][R][S][Cin]) + bias + residual)   (convolution mode)
+//
+// One CTA per SM loops over output tiles (128 x BN).  Warp roles:
+//   warp 0   one elected thread issues TMA loads for every k-block of every tile
+//            of this CTA, running ahead through a STAGES-deep shared-memory ring
+//            that is not drained at tile boundaries;
+//   warp 1   one elected thread issues tcgen05.mma into one of two TMEM
+//            accumulators (2 x BN columns), so tile i+1 accumulates while tile i
+//            is being written out;
+//   warps 2-5 read the accumulator with tcgen05.ld, apply bias / residual /
+//            activation, stage the bf16 tile in 128-byte-swizzled shared memory
+//            and hand it to a TMA store (full-line coalesced writes, bounds
+//            clipped by the tensor map).
+// In convolution mode the A operand needs no im2col and no gather: a tile is a
+// PW x PH x PN patch of output pixels, and the rows for filter tap (fr, fs) are
+// one 4-D TMA box over the NHWC input shifted by the tap offset, with element
+// strides equal to the convolution stride; out-of-image coordinates are
+// zero-filled by the TMA unit, which is exactly the padding.
+// All operands live in this GPU's memory; no load uses multicast.  Every wait
+// is bounded; on a timeout the kernel records an error code, stops issuing work,
+// frees its tensor memory and returns.
+#include <algorithm>
+#include <cstring>
+#include <mutex>
+#include <unordered_map>
+
+#include "gemm_tcgen05.h"
+#include "ptx.cuh"
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 64;
+constexpr int UMMA_K = 16;
+constexpr int THREADS = 192;
+constexpr int EPI_THREADS = 128;
+
+struct TileParams {
+  int mode;          // 0 GEMM, 1 convolution
+  int M, N, K;       // GEMM view (M = rows, N = columns)
+  int num_kb;
+  int tiles_m, tiles_n;
+  // convolution
+  int pw, ph, pn;            // output patch of one tile
+  int tiles_w, tiles_h;      // tiles along W and H (tiles_m = tiles_w * tiles_h * tiles_img)
+  int oh, ow, nimg;
+  int r, s, cblocks, stride, pad;
+  uint32_t a_box_bytes;      // bytes one A box writes
+  int rows_used;             // pw * ph * pn
+};
+
+__device__ __forceinline__ float gelu_f(float x) { return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f)); }
+
+__device__ __forceinline__ void named_bar_sync(int id, int count) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
+}
+
+// Barrier over `count` threads that also returns the AND of their predicates.
+__device__ __forceinline__ bool named_bar_all(int id, int count, bool pred) {
+  uint32_t out;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %3, 0;\n\t"
+      "barrier.cta.red.and.pred p, %1, %2, q;\n\tselp.u32 %0, 1, 0, p;\n\t}\n"
+      : "=r"(out)
+      : "r"(id), "r"(count), "r"((uint32_t)pred)
+      : "memory");
+  return out != 0;
+}
+
+__device__ __forceinline__ void tma_load_4d_box(void* smem_dst, const CUtensorMap* m, uint64_t* bar, int c0, int c1, int c2,
+                                                int c3) {
+  ptx::tma_load_4d(smem_dst, m, bar, c0, c1, c2, c3);
+}
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap* m, const void* smem_src, int c0, int c1, int c2, int c3) {
+  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(m),
+               "r"(ptx::smem_u32(smem_src)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+               : "memory");
+}
+
+struct TileCoord {
+  int m_idx, n_idx;
+  int w0, h0, img0;  // convolution patch origin (output pixels)
+};
+
+__device__ __forceinline__ TileCoord tile_coord(const TileParams& p, int tile) {
+  TileCoord t;
+  t.n_idx = tile % p.tiles_n;  // column tiles of one row block run back to back: A stays in L2
+  t.m_idx = tile / p.tiles_n;
+  t.w0 = t.h0 = t.img0 = 0;
+  if (p.mode == 1) {
+    int tw = t.m_idx % p.tiles_w;
+    int rest = t.m_idx / p.tiles_w;
+    int th = rest % p.tiles_h;
+    int ti = rest / p.tiles_h;
+    t.w0 = tw * p.pw;
+    t.h0 = th * p.ph;
+    t.img0 = ti * p.pn;
+  }
+  return t;
+}
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_conv_persistent(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                     const __grid_constant__ CUtensorMap tmap_out, TileParams p, GemmEpilogue ep, int use_tma_store,
+                     uint32_t* status) {
+  constexpr int A_BYTES = BM * BK * 2;
+  constexpr int B_BYTES = BN * BK * 2;
+  constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  constexpr int OUT_HALF_BYTES = BM * 128;       // 128 rows x 64 bf16 columns
+  constexpr int OUT_BYTES = (BN / 64) * OUT_HALF_BYTES;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* stage_out = smem + (size_t)STAGES * STAGE_BYTES;
+  __shared__ __align__(8) uint64_t full_bar[STAGES];
+  __shared__ __align__(8) uint64_t empty_bar[STAGES];
+  __shared__ __align__(8) uint64_t tmem_full_bar[2];
+  __shared__ __align__(8) uint64_t tmem_empty_bar[2];
+  __shared__ uint32_t tmem_base_smem;
+  __shared__ uint32_t s_error;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int num_tiles = p.tiles_m * p.tiles_n;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; s++) {
+      ptx::mbar_init(&full_bar[s], 1);
+      ptx::mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; a++) {
+      ptx::mbar_init(&tmem_full_bar[a], 1);
+      ptx::mbar_init(&tmem_empty_bar[a], 4);  // one arrival per epilogue warp
+    }
+    ptx::fence_mbar_init();
+    s_error = 0;
+    ptx::prefetch_tmap(&tmap_a);
+    ptx::prefetch_tmap(&tmap_b);
+    if (use_tma_store) ptx::prefetch_tmap(&tmap_out);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(&tmem_base_smem, 2 * BN);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = tmem_base_smem;
+
+  if (warp == 0) {
+    if (ptx::elect_one()) {
+      uint32_t it = 0;  // running k-block counter across tiles
+      for (int tile = blockIdx.x; tile < num_tiles && *(volatile uint32_t*)&s_error == 0; tile += gridDim.x) {
+        const TileCoord tc = tile_coord(p, tile);
+        for (int kb = 0; kb < p.num_kb; kb++, it++) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1u;
+          if (!ptx::mbar_wait(&empty_bar[s], ph ^ 1u)) {
+            atomicExch(&s_error, GEMM_ERR_PRODUCER_WAIT);
+            break;
+          }
+          uint8_t* sa = smem + (size_t)s * STAGE_BYTES;
+          if (p.mode == 0) {
+            ptx::mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+            ptx::tma_load_2d(sa, &tmap_a, &full_bar[s], kb * BK, tc.m_idx * BM);
+          } else {
+            ptx::mbar_expect_tx(&full_bar[s], p.a_box_bytes + B_BYTES);
+            const int tap = kb / p.cblocks, cb = kb - tap * p.cblocks;
+            const int fr = tap / p.s, fs = tap - fr * p.s;
+            tma_load_4d_box(sa, &tmap_a, &full_bar[s], cb * BK, tc.w0 * p.stride + fs - p.pad,
+                            tc.h0 * p.stride + fr - p.pad, tc.img0);
+          }
+          ptx::tma_load_2d(sa + A_BYTES, &tmap_b, &full_bar[s], kb * BK, tc.n_idx * BN);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (ptx::elect_one()) {
+      const uint32_t idesc = ptx::umma_idesc_bf16(BM, BN);
+      uint32_t it = 0, local = 0;
+      for (int tile = blockIdx.x; tile < num_tiles && *(volatile uint32_t*)&s_error == 0; tile += gridDim.x, local++) {
+        const uint32_t acc = local & 1u;
+        if (!ptx::mbar_wait(&tmem_empty_bar[acc], ((local >> 1) & 1u) ^ 1u)) {
+          atomicExch(&s_error, GEMM_ERR_MMA_WAIT);
+          break;
+        }
+        ptx::tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        bool ok = true;
+        for (int kb = 0; kb < p.num_kb; kb++, it++) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1u;
+          if (!ptx::mbar_wait(&full_bar[s], ph)) {
+            atomicExch(&s_error, GEMM_ERR_MMA_WAIT);
+            ok = false;
+            break;
+          }
+          ptx::tc_fence_after();
+          const uint32_t sa = ptx::smem_u32(smem + (size_t)s * STAGE_BYTES);
+          const uint32_t sb = sa + A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; k++)
+            ptx::umma_bf16(d_tmem, ptx::umma_desc_sw128(sa + k * UMMA_K * 2), ptx::umma_desc_sw128(sb + k * UMMA_K * 2), idesc,
+                           (kb | k) != 0 ? 1u : 0u);
+          ptx::umma_commit(&empty_bar[s]);
+        }
+        if (!ok) break;
+        ptx::umma_commit(&tmem_full_bar[acc]);
+      }
+    }
+  } else {
+    // ---------------- epilogue warps
+    const int warp_q = warp & 3;
+    const int row = warp_q * 32 + lane;  // row of the tile this thread owns
+    const int et = threadIdx.x - 64;     // 0..127 among the epilogue threads
+    uint32_t local = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, local++) {
+      const uint32_t acc = local & 1u;
+      const TileCoord tc = tile_coord(p, tile);
+      // Each thread's wait is bounded; the vote makes the outcome uniform so that no
+      // thread is left alone at a later barrier.
+      const bool mine = (*(volatile uint32_t*)&s_error == 0) && ptx::mbar_wait(&tmem_full_bar[acc], (local >> 1) & 1u);
+      if (!named_bar_all(2, EPI_THREADS, mine)) {
+        if (lane == 0) atomicExch(&s_error, GEMM_ERR_EPILOGUE_WAIT);
+        break;
+      }
+      ptx::tc_fence_after();
+      // Where this thread's row lives in the output.
+      bool row_ok;
+      size_t row_off;  // element offset of the row start in out / residual (leading dimension applied)
+      if (p.mode == 0) {
+        const int m = tc.m_idx * BM + row;
+        row_ok = m < p.M;
+        row_off = (size_t)m;
+      } else {
+        const int pw_i = row % p.pw, rest = row / p.pw;
+        const int ph_i = rest % p.ph, pn_i = rest / p.ph;
+        const int x = tc.w0 + pw_i, y = tc.h0 + ph_i, img = tc.img0 + pn_i;
+        row_ok = row < p.rows_used && x < p.ow && y < p.oh && img < p.nimg;
+        row_off = ((size_t)img * p.oh + y) * p.ow + x;
+      }
+      const int n0 = tc.n_idx * BN;
+      if (use_tma_store) {
+        // The previous tile's store must have finished reading the staging buffer.
+        if (et == 0) ptx::bulk_wait_read<0>();
+        named_bar_sync(1, EPI_THREADS);
+      }
+      const bool vec_res = ep.residual && ((ep.ldr & 7) == 0) && (((uintptr_t)ep.residual & 15) == 0);
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 32) {
+        uint32_t r[32];
+        ptx::tmem_ld_32x32b_x32(tmem_base + acc * BN + ((uint32_t)(warp_q * 32) << 16) + (uint32_t)c, r);
+        ptx::tmem_ld_wait();
+        const int col0 = n0 + c;
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; j++) v[j] = __uint_as_float(r[j]);
+        if (ep.bias) {
+          if (col0 + 32 <= p.N) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              float4 b4 = __ldg(reinterpret_cast<const float4*>(ep.bias + col0 + j));
+              v[j] += b4.x;
+              v[j + 1] += b4.y;
+              v[j + 2] += b4.z;
+              v[j + 3] += b4.w;
+            }
+          } else {
+            for (int j = 0; j < 32; j++)
+              if (col0 + j < p.N) v[j] += __ldg(ep.bias + col0 + j);
+          }
+        }
+        if (ep.residual && row_ok && col0 < p.N) {
+          const __nv_bfloat16* rp = ep.residual + row_off * ep.ldr + col0;
+          if (col0 + 32 <= p.N && vec_res) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              uint4 q = __ldg(reinterpret_cast<const uint4*>(rp + j));
+              const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+#pragma unroll
+              for (int t = 0; t < 4; t++) {
+                float2 f = __bfloat1622float2(h[t]);
+                v[j + 2 * t] += f.x;
+                v[j + 2 * t + 1] += f.y;
+              }
+            }
+          } else {
+            for (int j = 0; j < 32 && col0 + j < p.N; j++) v[j] += __bfloat162float(rp[j]);
+          }
+        }
+        if (ep.act == GEMM_ACT_RELU) {
+#pragma unroll
+          for (int j = 0; j < 32; j++) v[j] = fmaxf(v[j], 0.f);
+        } else if (ep.act == GEMM_ACT_GELU) {
+#pragma unroll
+          for (int j = 0; j < 32; j++) v[j] = gelu_f(v[j]);
+        } else if (ep.act == GEMM_ACT_TANH) {
+#pragma unroll
+          for (int j = 0; j < 32; j++) v[j] = tanhf(v[j]);
+        }
+        if (use_tma_store) {
+          uint8_t* half = stage_out + (size_t)(c >> 6) * OUT_HALF_BYTES + (size_t)row * 128;
+          const int chunk0 = (c & 63) >> 3;  // first 16-byte chunk of this 32-column group inside the 128-byte row
+#pragma unroll
+          for (int j = 0; j < 4; j++) {
+            uint4 q;
+            __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&q);
+#pragma unroll
+            for (int t = 0; t < 4; t++) h[t] = __floats2bfloat162_rn(v[j * 8 + 2 * t], v[j * 8 + 2 * t + 1]);
+            *reinterpret_cast<uint4*>(half + (((chunk0 + j) ^ (row & 7)) << 4)) = q;
+          }
+        } else if (row_ok && col0 < p.N) {
+          if (ep.out_fp32) {
+            float* op = reinterpret_cast<float*>(ep.out) + row_off * ep.ldo + col0;
+            for (int j = 0; j < 32 && col0 + j < p.N; j++) op[j] = v[j];
+          } else {
+            __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(ep.out) + row_off * ep.ldo + col0;
+            for (int j = 0; j < 32 && col0 + j < p.N; j++) op[j] = __float2bfloat16(v[j]);
+          }
+        }
+      }
+      // Accumulator drained: give it back to the MMA warp.
+      ptx::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(&tmem_empty_bar[acc]);
+      if (use_tma_store) {
+        ptx::fence_proxy_async_smem();
+        named_bar_sync(1, EPI_THREADS);
+        if (et == 0) {
+#pragma unroll
+          for (int hcol = 0; hcol < BN / 64; hcol++) {
+            if (n0 + hcol * 64 >= p.N) break;
+            const void* src = stage_out + (size_t)hcol * OUT_HALF_BYTES;
+            if (p.mode == 0) ptx::tma_store_2d(&tmap_out, src, n0 + hcol * 64, tc.m_idx * BM);
+            else tma_store_4d(&tmap_out, src, n0 + hcol * 64, tc.w0, tc.h0, tc.img0);
+          }
+          ptx::bulk_commit();
+        }
+      }
+    }
+    if (use_tma_store && et == 0) ptx::bulk_wait_all<0>();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (s_error != 0) {
+    if (threadIdx.x == 0 && status) atomicExch(status, s_error);
+    __nanosleep(1000000);  // let loads that are still in flight land before the block leaves
+    __syncthreads();
+  }
+  if (warp == 1) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem_base, 2 * BN);
+  }
+  (void)OUT_BYTES;
+}
+
+// ------------------------------------------------------------------ host side
+struct MapKey {
+  const void* ptr;
+  uint64_t d[5];
+  uint64_t st[4];
+  uint32_t box[5];
+  uint32_t es[5];
+  int rank;
+  bool operator==(const MapKey& o) const { return std::memcmp(this, &o, sizeof(MapKey)) == 0; }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    const uint64_t* w = reinterpret_cast<const uint64_t*>(&k);
+    size_t h = 1469598103934665603ull;
+    for (size_t i = 0; i < sizeof(MapKey) / 8; i++) h = (h ^ w[i]) * 1099511628211ull;
+    return h;
+  }
+};
+
+// Tensor maps are cached: encoding costs microseconds and the same layers run
+// for every batch.
+cudaError_t get_map(CUtensorMap* out, const void* ptr, int rank, const uint64_t* dims, const uint64_t* strides_bytes,
+                    const uint32_t* box, const uint32_t* estr) {
+  static std::mutex mu;
+  static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+  MapKey k;
+  std::memset(&k, 0, sizeof(k));
+  k.ptr = ptr;
+  k.rank = rank;
+  for (int i = 0; i < rank; i++) {
+    k.d[i] = dims[i];
+    k.box[i] = box[i];
+    k.es[i] = estr[i];
+    if (i + 1 < rank) k.st[i] = strides_bytes[i];
+  }
+  std::lock_guard<std::mutex> g(mu);
+  auto it = cache.find(k);
+  if (it != cache.end()) {
+    *out = it->second;
+    return cudaSuccess;
+  }
+  const SrpcDriverApi* d = srpc_driver_api();
+  if (!d->TensorMapEncodeTiled) return cudaErrorNotSupported;
+  cuuint64_t gd[5], gs[4];
+  cuuint32_t bx[5], es[5];
+  for (int i = 0; i < rank; i++) {
+    gd[i] = dims[i];
+    bx[i] = box[i];
+    es[i] = estr[i];
+    if (i + 1 < rank) gs[i] = strides_bytes[i];
+  }
+  CUresult r = d->TensorMapEncodeTiled(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (cuuint32_t)rank, const_cast<void*>(ptr), gd, gs,
+                                       bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                       CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
+  if (cache.size() > 4096) cache.clear();
+  cache.emplace(k, *out);
+  return cudaSuccess;
+}
+
+cudaError_t map_2d(CUtensorMap* m, const void* ptr, uint64_t inner, uint64_t outer, uint64_t row_stride_bytes,
+                   uint32_t box_inner, uint32_t box_outer) {
+  uint64_t dims[2] = {inner, outer}, st[1] = {row_stride_bytes};
+  uint32_t box[2] = {box_inner, box_outer}, es[2] = {1, 1};
+  return get_map(m, ptr, 2, dims, st, box, es);
+}
+
+int num_sms() {
+  static int n = 0;
+  if (!n) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (n <= 0) n = 148;
+  }
+  return n;
+}
+
+template <int BN, int STAGES>
+cudaError_t launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& to, const TileParams& p,
+                   const GemmEpilogue& ep, int use_tma_store, uint32_t* status, cudaStream_t st) {
+  static bool attr = false;
+  const int smem = STAGES * (BM * BK * 2 + BN * BK * 2) + (BN / 64) * BM * 128 + 1024;
+  if (!attr) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_conv_persistent<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return e;
+    attr = true;
+  }
+  const int tiles = p.tiles_m * p.tiles_n;
+  const int grid = std::min(tiles, num_sms());
+  gemm_conv_persistent<BN, STAGES><<<grid, THREADS, smem, st>>>(ta, tb, to, p, ep, use_tma_store, status);
+  return cudaGetLastError();
+}
+
+cudaError_t dispatch(int bn, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& to, const TileParams& p,
+                     const GemmEpilogue& ep, int use_tma_store, uint32_t* status, cudaStream_t st) {
+  if (bn == 64) return launch<64, 6>(ta, tb, to, p, ep, use_tma_store, status, st);
+  return launch<128, 5>(ta, tb, to, p, ep, use_tma_store, status, st);
+}
+
+}  // namespace
+
+cudaError_t srpc_gemm_bf16_v2(const void* A, int lda, const void* B, int ldb, int M, int N, int K, const GemmEpilogue& ep,
+                              uint32_t* status, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return cudaErrorInvalidValue;
+  if ((lda % 8) || (ldb % 8) || (K % 8) || ((uintptr_t)A & 15) || ((uintptr_t)B & 15)) return cudaErrorInvalidValue;
+  if (ep.bias && ((uintptr_t)ep.bias & 15)) return cudaErrorInvalidValue;
+  const int bn = (N <= 64) ? 64 : 128;
+  TileParams p{};
+  p.mode = 0;
+  p.M = M;
+  p.N = N;
+  p.K = K;
+  p.num_kb = (K + BK - 1) / BK;
+  p.tiles_m = (M + BM - 1) / BM;
+  p.tiles_n = (N + bn - 1) / bn;
+  CUtensorMap ta, tb, to;
+  cudaError_t e = map_2d(&ta, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda * 2, BK, BM);
+  if (e != cudaSuccess) return e;
+  e = map_2d(&tb, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb * 2, BK, (uint32_t)bn);
+  if (e != cudaSuccess) return e;
+  int use_tma_store = (!ep.out_fp32 && (ep.ldo % 8) == 0 && ((uintptr_t)ep.out & 15) == 0) ? 1 : 0;
+  if (use_tma_store) {
+    e = map_2d(&to, ep.out, (uint64_t)N, (uint64_t)M, (uint64_t)ep.ldo * 2, 64, BM);
+    if (e != cudaSuccess) return e;
+  } else {
+    to = ta;
+  }
+  return dispatch(bn, ta, tb, to, p, ep, use_tma_store, status, stream);
+}
+
+// Picks the output patch (pw x ph x pn <= 128 pixels) that wastes the fewest tile rows.
+static void pick_patch(int ow, int oh, int nimg, int* pw, int* ph, int* pn) {
+  double best = -1;
+  for (int w = 1; w <= std::min(ow, 64); w++)
+    for (int h = 1; h <= std::min(oh, 128 / w); h++) {
+      int n = std::min(nimg, 128 / (w * h));
+      if (n < 1) continue;
+      long tiles = (long)((ow + w - 1) / w) * ((oh + h - 1) / h) * ((nimg + n - 1) / n);
+      double eff = (double)ow * oh * nimg / ((double)tiles * 128.0);
+      double score = eff + 1e-4 * w;  // ties: longer contiguous runs
+      if (score > best) {
+        best = score;
+        *pw = w;
+        *ph = h;
+        *pn = n;
+      }
+    }
+}
+
+cudaError_t srpc_conv_bf16_tma(const void* in, const void* weight, const ConvShape& cs, const GemmEpilogue& ep,
+                               uint32_t* status, cudaStream_t stream) {
+  if (cs.cin % BK || cs.cout % 8) return cudaErrorInvalidValue;
+  if (((uintptr_t)in & 15) || ((uintptr_t)weight & 15) || ((uintptr_t)ep.out & 15) || ep.out_fp32) return cudaErrorInvalidValue;
+  if (ep.bias && ((uintptr_t)ep.bias & 15)) return cudaErrorInvalidValue;
+  const int bn = (cs.cout <= 64) ? 64 : 128;
+  TileParams p{};
+  p.mode = 1;
+  p.oh = cs.oh;
+  p.ow = cs.ow;
+  p.nimg = cs.n;
+  p.M = cs.n * cs.oh * cs.ow;
+  p.N = cs.cout;
+  p.K = cs.r * cs.s * cs.cin;
+  p.r = cs.r;
+  p.s = cs.s;
+  p.cblocks = cs.cin / BK;
+  p.num_kb = cs.r * cs.s * p.cblocks;
+  p.stride = cs.stride;
+  p.pad = cs.pad;
+  pick_patch(cs.ow, cs.oh, cs.n, &p.pw, &p.ph, &p.pn);
+  p.rows_used = p.pw * p.ph * p.pn;
+  p.tiles_w = (cs.ow + p.pw - 1) / p.pw;
+  p.tiles_h = (cs.oh + p.ph - 1) / p.ph;
+  p.tiles_m = p.tiles_w * p.tiles_h * ((cs.n + p.pn - 1) / p.pn);
+  p.tiles_n = (cs.cout + bn - 1) / bn;
+  p.a_box_bytes = (uint32_t)p.rows_used * 128u;
+  CUtensorMap ta, tb, to;
+  {
+    uint64_t dims[4] = {(uint64_t)cs.cin, (uint64_t)cs.w, (uint64_t)cs.h, (uint64_t)cs.n};
+    uint64_t st[3] = {(uint64_t)cs.cin * 2, (uint64_t)cs.w * cs.cin * 2, (uint64_t)cs.h * cs.w * cs.cin * 2};
+    uint32_t box[4] = {BK, (uint32_t)(p.pw * cs.stride), (uint32_t)(p.ph * cs.stride), (uint32_t)p.pn};
+    uint32_t es[4] = {1, (uint32_t)cs.stride, (uint32_t)cs.stride, 1};
+    if (box[1] > 256 || box[2] > 256) return cudaErrorInvalidValue;
+    cudaError_t e = get_map(&ta, in, 4, dims, st, box, es);
+    if (e != cudaSuccess) return e;
+  }
+  cudaError_t e = map_2d(&tb, weight, (uint64_t)p.K, (uint64_t)cs.cout, (uint64_t)p.K * 2, BK, (uint32_t)bn);
+  if (e != cudaSuccess) return e;
+  {
+    uint64_t dims[4] = {(uint64_t)cs.cout, (uint64_t)cs.ow, (uint64_t)cs.oh, (uint64_t)cs.n};
+    uint64_t st[3] = {(uint64_t)cs.cout * 2, (uint64_t)cs.ow * cs.cout * 2, (uint64_t)cs.oh * cs.ow * cs.cout * 2};
+    uint32_t box[4] = {64, (uint32_t)p.pw, (uint32_t)p.ph, (uint32_t)p.pn};
+    uint32_t es[4] = {1, 1, 1, 1};
+    e = get_map(&to, ep.out, 4, dims, st, box, es);
+    if (e != cudaSuccess) return e;
+  }
+  GemmEpilogue ep2 = ep;
+  ep2.ldo = cs.cout;
+  if (ep2.residual) ep2.ldr = cs.cout;
+  return dispatch(bn, ta, tb, to, p, ep2, 1, status, stream);
+}

@@ -33,6 +33,13 @@ struct ConvShape {
 cudaError_t srpc_gemm_bf16(const void* A, int lda, const void* B, int ldb, int M, int N, int K, const GemmEpilogue& ep,
                            uint32_t* status, cudaStream_t stream);
 
+// Persistent variants (production path): double-buffered TMEM accumulators, TMA-store epilogue; the convolution
+// reads its A operand with shifted 4-D TMA boxes instead of gathering rows.
+cudaError_t srpc_gemm_bf16_v2(const void* A, int lda, const void* B, int ldb, int M, int N, int K, const GemmEpilogue& ep,
+                              uint32_t* status, cudaStream_t stream);
+cudaError_t srpc_conv_bf16_tma(const void* in, const void* weight, const ConvShape& cs, const GemmEpilogue& ep,
+                               uint32_t* status, cudaStream_t stream);
+
 // NHWC bf16 convolution as an implicit GEMM; cin must be a multiple of 64.
 cudaError_t srpc_conv_bf16(const void* in, const void* weight, const ConvShape& cs, const GemmEpilogue& ep,
                            uint32_t* status, cudaStream_t stream);

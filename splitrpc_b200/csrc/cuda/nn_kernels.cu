@@ -41,8 +41,10 @@ __device__ __forceinline__ float block_sum(float v, float* sh) {
 // ------------------------------------------------------------------ ResNet stem input
 // Request = fp32 CHW image (3 x 224 x 224).  Writes the im2col matrix of the 7x7
 // stride-2 pad-3 stem convolution: row = output pixel (n, oy, ox), 192 bf16
-// columns = k index c*49 + ky*7 + kx for k < 147, zero above, after
-// (x - mean[c]) * inv_std[c].  One thread writes 8 columns (one 16-byte store).
+// columns ordered k = ky*24 + c*8 + kx (kx = 7 and k >= 168 are zero), after
+// (x - mean[c]) * inv_std[c].  With this order one 16-byte chunk of a row is 7
+// consecutive input pixels of one image row and channel, so a thread reads 28
+// contiguous bytes and writes one 16-byte store.
 __global__ void __launch_bounds__(256) stem_im2col(const g_params* stub, const float* __restrict__ direct_in, int batch,
                                                    __nv_bfloat16* __restrict__ out, float3 mean, float3 inv_std) {
   const float* in = direct_in ? direct_in : reinterpret_cast<const float*>(stub->req);
@@ -50,25 +52,28 @@ __global__ void __launch_bounds__(256) stem_im2col(const g_params* stub, const f
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
     const int kc = (int)(i % 24);
     const size_t pix = i / 24;
-    const int ox = (int)(pix % 112), oy = (int)((pix / 112) % 112), n = (int)(pix / (112 * 112));
-    const float* img = in + (size_t)n * 3 * 224 * 224;
-    __nv_bfloat16 v[8];
+    uint4 o = make_uint4(0u, 0u, 0u, 0u);
+    if (kc < 21) {
+      const int ky = kc / 3, c = kc - ky * 3;
+      const int ox = (int)(pix % 112), oy = (int)((pix / 112) % 112), n = (int)(pix / (112 * 112));
+      const int iy = oy * 2 - 3 + ky, ix0 = ox * 2 - 3;
+      if (iy >= 0 && iy < 224) {
+        const float m = c == 0 ? mean.x : (c == 1 ? mean.y : mean.z);
+        const float s = c == 0 ? inv_std.x : (c == 1 ? inv_std.y : inv_std.z);
+        const float* row = in + (((size_t)n * 3 + c) * 224 + iy) * 224;
+        float v[8];
 #pragma unroll
-    for (int j = 0; j < 8; j++) {
-      const int k = kc * 8 + j;
-      float x = 0.f;
-      if (k < 147) {
-        const int c = k / 49, rem = k - c * 49, ky = rem / 7, kx = rem - ky * 7;
-        const int iy = oy * 2 - 3 + ky, ix = ox * 2 - 3 + kx;
-        if (iy >= 0 && iy < 224 && ix >= 0 && ix < 224) {
-          const float m = c == 0 ? mean.x : (c == 1 ? mean.y : mean.z);
-          const float s = c == 0 ? inv_std.x : (c == 1 ? inv_std.y : inv_std.z);
-          x = (__ldg(img + ((size_t)c * 224 + iy) * 224 + ix) - m) * s;
+        for (int j = 0; j < 7; j++) {
+          const int ix = ix0 + j;
+          v[j] = (ix >= 0 && ix < 224) ? (__ldg(row + ix) - m) * s : 0.f;
         }
+        v[7] = 0.f;
+        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+        for (int t = 0; t < 4; t++) h[t] = __floats2bfloat162_rn(v[2 * t], v[2 * t + 1]);
       }
-      v[j] = __float2bfloat16(x);
     }
-    *reinterpret_cast<uint4*>(out + pix * 192 + kc * 8) = *reinterpret_cast<const uint4*>(v);
+    *reinterpret_cast<uint4*>(out + pix * 192 + kc * 8) = o;
   }
 }
 

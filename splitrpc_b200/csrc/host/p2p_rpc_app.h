@@ -306,6 +306,17 @@ class P2pRpcAppRrPool {
     pi_idx_ = (pi_idx_ + 1) % (size_t)pool_size_;
     return r;
   }
+
+  // Ring addresses of the seq-th slot handed out since init_pool().  The rings
+  // advance by a fixed size per slot, so the addresses of a window are known
+  // before its producer has bound it; a consumer that arms work ahead of arrival
+  // (the stream-armed worker) uses this instead of the slot's own stub.
+  g_params window_stub(uint64_t seq) const {
+    g_params p;
+    p.req = (uint8_t*)req_pool_->base() + (size_t)((seq * (uint64_t)req_size) % req_pool_->capacity());
+    p.resp = (uint8_t*)resp_pool_->base() + (size_t)((seq * (uint64_t)resp_size) % resp_pool_->capacity());
+    return p;
+  }
 };
 
 // ------------------------------------------------------------------ app context

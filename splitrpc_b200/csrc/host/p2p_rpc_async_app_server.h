@@ -40,6 +40,7 @@ class P2pRpcAppInfo {
   uint32_t* door_bells = nullptr;
   uint32_t* d_door_bells = nullptr;
   bool init_ok = false;
+  uint64_t consumer_seq = 0;  // slots consumed by the stream-armed worker since the pool was initialised
 
   // `internal` is stored in app_ctx->app_ctx_internal before app_init runs, so a
   // callback set can be shared by several instances with different state.
@@ -250,7 +251,10 @@ class P2pRpcAsyncAppServer {
   void pre_launch_work(int appIdx, int start_rr_idx, int last_rr_idx) {
     P2pRpcAppInfo* a = all_apps[appIdx];
     AppCtx* c = a->app_ctx;
-    *c->h_stub = *a->app_rr_pool->get_app_rr(start_rr_idx)->h_stub;
+    // The window may not have been bound by its producer yet: take its addresses
+    // from the ring arithmetic, not from the slot.
+    *c->h_stub = a->app_rr_pool->window_stub(a->consumer_seq);
+    (void)start_rr_idx;
     std::atomic_thread_fence(std::memory_order_seq_cst);
     c->AppRrRunNotify(a->app_rr_pool->get_app_rr(last_rr_idx)->d_state, APP_RR_STATUS::RX_COMPLETE);
     if (c->last_status == 0 || c->device_id >= 0) a->app_run(c);
@@ -263,7 +267,7 @@ class P2pRpcAsyncAppServer {
     P2pRpcAppRrPool* pool = a->app_rr_pool;
     const int n = a->rr_pool_size;
     int ci = 0;
-    // The stub must point at valid ring addresses before anything is armed.
+    a->consumer_seq = 0;
     c->ResetAppRunStatus();
     if (c->device_id < 0) c->wait_budget_ns = 20000000ull;  // CPU device: poll in 20 ms slices
     bool armed = false;
@@ -291,6 +295,7 @@ class P2pRpcAsyncAppServer {
         note_batch(appIdx, bs, getCurNs() - t0);
       }
       num_req.fetch_add((uint64_t)bs);
+      a->consumer_seq += (uint64_t)bs;
       update_batch_size(appIdx);
       c->ResetAppRunStatus();
       if (a->app_complete) a->app_complete(c);

@@ -43,10 +43,11 @@ class ResNet50:
             self.params[name + ".w"] = w.to(self.device, torch.bfloat16).contiguous()
             self.params[name + ".b"] = (torch.randn((cout,), generator=g) * 0.05).to(self.device, torch.float32)
 
-        # stem weight in im2col order [64, 192]: k = c*49 + ky*7 + kx, zero padded from 147
+        # stem weight in the im2col order of ops.stem_im2col: [64, 192] with k = ky*24 + c*8 + kx (kx < 7), zeros elsewhere
         w = torch.randn((64, 3, 7, 7), generator=g) * math.sqrt(2.0 / 147)
-        stem = torch.zeros((64, 192))
-        stem[:, :147] = w.reshape(64, 147)
+        stem = torch.zeros((64, 7, 3, 8))
+        stem[:, :, :, :7] = w.permute(0, 2, 1, 3)
+        stem = torch.cat([stem.reshape(64, 168), torch.zeros((64, 24))], dim=1)
         self.params["stem.w"] = stem.to(self.device, torch.bfloat16).contiguous()
         self.params["stem.w_nchw"] = w.to(self.device)
         self.params["stem.b"] = (torch.randn((64,), generator=g) * 0.05).to(self.device, torch.float32)

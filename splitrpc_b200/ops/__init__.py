@@ -14,6 +14,10 @@ from .. import _C
 ACT = {None: _C.ACT_NONE, "none": _C.ACT_NONE, "relu": _C.ACT_RELU, "gelu": _C.ACT_GELU, "tanh": _C.ACT_TANH}
 
 
+# 2 = persistent kernels (TMA-store epilogue, TMA tap-shift convolution); 1 = one tile per block, gathered convolution.
+GEMM_IMPL = int(__import__("os").environ.get("SPLITRPC_GEMM_IMPL", "2"))
+
+
 def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
@@ -61,7 +65,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, bias: torch.Tensor | None = None, res
         assert residual.dtype == torch.bfloat16 and residual.shape == (M, N) and residual.stride(1) == 1
     _C.gemm_bf16(a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0), M, N, K, out.data_ptr(), out.stride(0),
                  out.dtype == torch.float32, _ptr(bias), _ptr(residual), residual.stride(0) if residual is not None else 0,
-                 ACT[act], status_word().data_ptr(), _stream())
+                 ACT[act], status_word().data_ptr(), _stream(), GEMM_IMPL)
     return out
 
 
@@ -79,7 +83,7 @@ def conv2d_nhwc(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = No
     if residual is not None:
         assert residual.shape == out.shape and residual.is_contiguous() and residual.dtype == torch.bfloat16
     _C.conv_bf16(x.data_ptr(), w.data_ptr(), n, h, wd, cin, cout, r, s, stride, pad, out.data_ptr(), _ptr(bias),
-                 _ptr(residual), ACT[act], status_word().data_ptr(), _stream())
+                 _ptr(residual), ACT[act], status_word().data_ptr(), _stream(), GEMM_IMPL)
     return out
 
 

@@ -40,9 +40,10 @@ def test_nn_layers_match_pytorch(torch_cuda):
     ops.stem_im2col(col, 2, x=img, mean=(0.1, 0.2, 0.3), inv_std=(2.0, 3.0, 4.0))
     m = torch.tensor([0.1, 0.2, 0.3], device="cuda").view(1, 3, 1, 1)
     s = torch.tensor([2.0, 3.0, 4.0], device="cuda").view(1, 3, 1, 1)
-    unf = F.unfold((img - m) * s, 7, padding=3, stride=2).transpose(1, 2).reshape(-1, 147)
-    torch.testing.assert_close(col[:, :147].float(), unf.bfloat16().float(), rtol=0, atol=0)
-    assert col[:, 147:].abs().max() == 0
+    unf = F.unfold((img - m) * s, 7, padding=3, stride=2).transpose(1, 2).reshape(-1, 3, 7, 7)  # [pix, c, ky, kx]
+    got = col[:, :168].float().view(-1, 7, 3, 8)  # [pix, ky, c, kx8]
+    torch.testing.assert_close(got[..., :7], unf.permute(0, 2, 1, 3).bfloat16().float(), rtol=0, atol=0)
+    assert got[..., 7].abs().max() == 0 and col[:, 168:].abs().max() == 0
 
 
 @pytest.mark.parametrize("seq,heads", [(128, 12), (384, 16)])

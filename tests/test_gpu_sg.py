@@ -120,7 +120,7 @@ def test_gpu_echo_all_copy_types(C, torch_cuda, mtu8k, copy_type):
 @pytest.mark.parametrize("launch_type", [1, 3, 4])
 def test_gpu_vec_add_launch_types(C, torch_cuda, mtu8k, launch_type):
     ok, cli, st, ss, ws, sg = _serve_gpu(C, "vec_add", 16384, 16384, 100, 2, 4, "vec_add", 2, launch_type)
-    assert ok and cli.received == 100 and cli.verify_failures == 0 and ws["wait_timeouts"] == 0
+    assert (ok, cli.received, cli.verify_failures, ws["wait_timeouts"], ss["sg_errors"]) == (True, 100, 0, 0, 0), (ws["batch_hist"], ss)
 
 
 def test_gpu_async_stream_armed_mode(C, torch_cuda, mtu8k):
