@@ -128,6 +128,13 @@ void bind_ops(py::module_& m) {
                                  hidden, vocab, eps, (cudaStream_t)stream),
                 "bert_embed_ln");
         });
+  m.def("attention_tc",
+        [](uintptr_t qk, int ld_qk, uintptr_t vt, int ld_vt, uintptr_t out, int ld_out, uintptr_t v_bias, int batch, int seq,
+           int heads, uintptr_t status, uintptr_t stream) {
+          check(nn_attention_tc((const void*)qk, ld_qk, (const void*)vt, ld_vt, (void*)out, ld_out, (const float*)v_bias, batch,
+                                seq, heads, (uint32_t*)status, (cudaStream_t)stream),
+                "attention_tc");
+        });
   m.def("attention_d64",
         [](uintptr_t qkv, uintptr_t out, int batch, int seq, int heads, int ld_qkv, int q_off, int k_off, int v_off,
            int ld_out, uintptr_t stream) {

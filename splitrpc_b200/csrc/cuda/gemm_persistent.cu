@@ -10,10 +10,12 @@
 //   warp 1   one elected thread issues tcgen05.mma into one of two TMEM
 //            accumulators (2 x BN columns), so tile i+1 accumulates while tile i
 //            is being written out;
-//   warps 2-5 read the accumulator with tcgen05.ld, apply bias / residual /
-//            activation, stage the bf16 tile in 128-byte-swizzled shared memory
-//            and hand it to a TMA store (full-line coalesced writes, bounds
-//            clipped by the tensor map).
+//   warps 2-9 read the accumulator with tcgen05.ld (two warps per TMEM lane
+//            quarter, half of the columns each), release it at once, apply bias /
+//            residual (prefetched before the accumulator is ready) / activation,
+//            stage the bf16 tile in one of two 128-byte-swizzled shared-memory
+//            buffers and hand it to a TMA store (full-line coalesced writes,
+//            bounds clipped by the tensor map).
 // In convolution mode the A operand needs no im2col and no gather: a tile is a
 // PW x PH x PN patch of output pixels, and the rows for filter tap (fr, fs) are
 // one 4-D TMA box over the NHWC input shifted by the tap offset, with element
@@ -35,8 +37,8 @@ namespace {
 constexpr int BM = 128;
 constexpr int BK = 64;
 constexpr int UMMA_K = 16;
-constexpr int THREADS = 192;
-constexpr int EPI_THREADS = 128;
+constexpr int THREADS = 320;  // warp 0 TMA, warp 1 MMA, warps 2-9 epilogue
+constexpr int EPI_THREADS = 256;
 
 struct TileParams {
   int mode;          // 0 GEMM, 1 convolution
@@ -132,7 +134,7 @@ gemm_conv_persistent(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     }
     for (int a = 0; a < 2; a++) {
       ptx::mbar_init(&tmem_full_bar[a], 1);
-      ptx::mbar_init(&tmem_empty_bar[a], 4);  // one arrival per epilogue warp
+      ptx::mbar_init(&tmem_empty_bar[a], 8);  // one arrival per epilogue warp
     }
     ptx::fence_mbar_init();
     s_error = 0;
@@ -211,25 +213,21 @@ gemm_conv_persistent(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       }
     }
   } else {
-    // ---------------- epilogue warps
+    // ---------------- epilogue warps (8): warp pair (w, w+4) shares a TMEM lane quarter and splits the columns
+    constexpr int CPW = BN / 2;          // columns per warp
+    constexpr int NCH = CPW / 32;        // 32-column chunks per warp
     const int warp_q = warp & 3;
+    const int chalf = (warp - 2) >> 2;   // which half of the tile's columns
     const int row = warp_q * 32 + lane;  // row of the tile this thread owns
-    const int et = threadIdx.x - 64;     // 0..127 among the epilogue threads
+    const int et = threadIdx.x - 64;     // 0..255 among the epilogue threads
+    const bool vec_res = ep.residual && ((ep.ldr & 7) == 0) && (((uintptr_t)ep.residual & 15) == 0);
     uint32_t local = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, local++) {
       const uint32_t acc = local & 1u;
       const TileCoord tc = tile_coord(p, tile);
-      // Each thread's wait is bounded; the vote makes the outcome uniform so that no
-      // thread is left alone at a later barrier.
-      const bool mine = (*(volatile uint32_t*)&s_error == 0) && ptx::mbar_wait(&tmem_full_bar[acc], (local >> 1) & 1u);
-      if (!named_bar_all(2, EPI_THREADS, mine)) {
-        if (lane == 0) atomicExch(&s_error, GEMM_ERR_EPILOGUE_WAIT);
-        break;
-      }
-      ptx::tc_fence_after();
       // Where this thread's row lives in the output.
       bool row_ok;
-      size_t row_off;  // element offset of the row start in out / residual (leading dimension applied)
+      size_t row_off;  // pixel / row index (leading dimension not yet applied)
       if (p.mode == 0) {
         const int m = tc.m_idx * BM + row;
         row_ok = m < p.M;
@@ -242,21 +240,45 @@ gemm_conv_persistent(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         row_off = ((size_t)img * p.oh + y) * p.ow + x;
       }
       const int n0 = tc.n_idx * BN;
+      const int cbase = chalf * CPW;  // first tile column of this warp
+      // Residual rows are fetched before the accumulator is awaited, so their latency hides behind the MMAs.
+      uint4 resq[CPW / 8];
+      const bool res_vec_tile = vec_res && row_ok && (n0 + cbase + CPW <= p.N);
+      if (res_vec_tile) {
+        const __nv_bfloat16* rp = ep.residual + row_off * ep.ldr + n0 + cbase;
+#pragma unroll
+        for (int j = 0; j < CPW / 8; j++) resq[j] = __ldg(reinterpret_cast<const uint4*>(rp) + j);
+      }
+      // Each thread's wait is bounded; the vote makes the outcome uniform so that no
+      // thread is left alone at a later barrier.
+      const bool mine = (*(volatile uint32_t*)&s_error == 0) && ptx::mbar_wait(&tmem_full_bar[acc], (local >> 1) & 1u);
+      if (!named_bar_all(2, EPI_THREADS, mine)) {
+        if (lane == 0) atomicExch(&s_error, GEMM_ERR_EPILOGUE_WAIT);
+        break;
+      }
+      ptx::tc_fence_after();
+      uint32_t r[CPW];
+#pragma unroll
+      for (int ch = 0; ch < NCH; ch++)
+        ptx::tmem_ld_32x32b_x32(tmem_base + acc * BN + ((uint32_t)(warp_q * 32) << 16) + (uint32_t)(cbase + ch * 32), r + ch * 32);
+      ptx::tmem_ld_wait();
+      // Accumulator is in registers: give it back to the MMA warp right away.
+      ptx::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(&tmem_empty_bar[acc]);
+      uint8_t* sbuf = stage_out + (size_t)(local & 1u) * OUT_BYTES;
       if (use_tma_store) {
-        // The previous tile's store must have finished reading the staging buffer.
-        if (et == 0) ptx::bulk_wait_read<0>();
+        // The store issued two tiles ago must have finished reading this staging buffer.
+        if (et == 0) ptx::bulk_wait_read<1>();
         named_bar_sync(1, EPI_THREADS);
       }
-      const bool vec_res = ep.residual && ((ep.ldr & 7) == 0) && (((uintptr_t)ep.residual & 15) == 0);
-#pragma unroll 1
-      for (int c = 0; c < BN; c += 32) {
-        uint32_t r[32];
-        ptx::tmem_ld_32x32b_x32(tmem_base + acc * BN + ((uint32_t)(warp_q * 32) << 16) + (uint32_t)c, r);
-        ptx::tmem_ld_wait();
+#pragma unroll
+      for (int ch = 0; ch < NCH; ch++) {
+        const int c = cbase + ch * 32;  // tile column of this chunk
         const int col0 = n0 + c;
         float v[32];
 #pragma unroll
-        for (int j = 0; j < 32; j++) v[j] = __uint_as_float(r[j]);
+        for (int j = 0; j < 32; j++) v[j] = __uint_as_float(r[ch * 32 + j]);
         if (ep.bias) {
           if (col0 + 32 <= p.N) {
 #pragma unroll
@@ -268,26 +290,28 @@ gemm_conv_persistent(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
               v[j + 3] += b4.w;
             }
           } else {
+#pragma unroll
             for (int j = 0; j < 32; j++)
               if (col0 + j < p.N) v[j] += __ldg(ep.bias + col0 + j);
           }
         }
         if (ep.residual && row_ok && col0 < p.N) {
-          const __nv_bfloat16* rp = ep.residual + row_off * ep.ldr + col0;
-          if (col0 + 32 <= p.N && vec_res) {
+          if (res_vec_tile) {
 #pragma unroll
-            for (int j = 0; j < 32; j += 8) {
-              uint4 q = __ldg(reinterpret_cast<const uint4*>(rp + j));
-              const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+            for (int j = 0; j < 4; j++) {
+              const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&resq[ch * 4 + j]);
 #pragma unroll
               for (int t = 0; t < 4; t++) {
                 float2 f = __bfloat1622float2(h[t]);
-                v[j + 2 * t] += f.x;
-                v[j + 2 * t + 1] += f.y;
+                v[j * 8 + 2 * t] += f.x;
+                v[j * 8 + 2 * t + 1] += f.y;
               }
             }
           } else {
-            for (int j = 0; j < 32 && col0 + j < p.N; j++) v[j] += __bfloat162float(rp[j]);
+            const __nv_bfloat16* rp = ep.residual + row_off * ep.ldr + col0;
+            #pragma unroll
+            for (int j = 0; j < 32; j++)
+              if (col0 + j < p.N) v[j] += __bfloat162float(rp[j]);
           }
         }
         if (ep.act == GEMM_ACT_RELU) {
@@ -301,7 +325,7 @@ gemm_conv_persistent(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
           for (int j = 0; j < 32; j++) v[j] = tanhf(v[j]);
         }
         if (use_tma_store) {
-          uint8_t* half = stage_out + (size_t)(c >> 6) * OUT_HALF_BYTES + (size_t)row * 128;
+          uint8_t* half = sbuf + (size_t)(c >> 6) * OUT_HALF_BYTES + (size_t)row * 128;
           const int chunk0 = (c & 63) >> 3;  // first 16-byte chunk of this 32-column group inside the 128-byte row
 #pragma unroll
           for (int j = 0; j < 4; j++) {
@@ -314,17 +338,17 @@ gemm_conv_persistent(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         } else if (row_ok && col0 < p.N) {
           if (ep.out_fp32) {
             float* op = reinterpret_cast<float*>(ep.out) + row_off * ep.ldo + col0;
-            for (int j = 0; j < 32 && col0 + j < p.N; j++) op[j] = v[j];
+            #pragma unroll
+            for (int j = 0; j < 32; j++)
+              if (col0 + j < p.N) op[j] = v[j];
           } else {
             __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(ep.out) + row_off * ep.ldo + col0;
-            for (int j = 0; j < 32 && col0 + j < p.N; j++) op[j] = __float2bfloat16(v[j]);
+            #pragma unroll
+            for (int j = 0; j < 32; j++)
+              if (col0 + j < p.N) op[j] = __float2bfloat16(v[j]);
           }
         }
       }
-      // Accumulator drained: give it back to the MMA warp.
-      ptx::tc_fence_before();
-      __syncwarp();
-      if (lane == 0) ptx::mbar_arrive(&tmem_empty_bar[acc]);
       if (use_tma_store) {
         ptx::fence_proxy_async_smem();
         named_bar_sync(1, EPI_THREADS);
@@ -332,7 +356,7 @@ gemm_conv_persistent(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
 #pragma unroll
           for (int hcol = 0; hcol < BN / 64; hcol++) {
             if (n0 + hcol * 64 >= p.N) break;
-            const void* src = stage_out + (size_t)hcol * OUT_HALF_BYTES;
+            const void* src = sbuf + (size_t)hcol * OUT_HALF_BYTES;
             if (p.mode == 0) ptx::tma_store_2d(&tmap_out, src, n0 + hcol * 64, tc.m_idx * BM);
             else tma_store_4d(&tmap_out, src, n0 + hcol * 64, tc.w0, tc.h0, tc.img0);
           }
@@ -353,7 +377,6 @@ gemm_conv_persistent(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     ptx::tc_fence_after();
     ptx::tmem_dealloc(tmem_base, 2 * BN);
   }
-  (void)OUT_BYTES;
 }
 
 // ------------------------------------------------------------------ host side
@@ -438,7 +461,7 @@ template <int BN, int STAGES>
 cudaError_t launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& to, const TileParams& p,
                    const GemmEpilogue& ep, int use_tma_store, uint32_t* status, cudaStream_t st) {
   static bool attr = false;
-  const int smem = STAGES * (BM * BK * 2 + BN * BK * 2) + (BN / 64) * BM * 128 + 1024;
+  const int smem = STAGES * (BM * BK * 2 + BN * BK * 2) + 2 * (BN / 64) * BM * 128 + 1024;
   if (!attr) {
     cudaError_t e = cudaFuncSetAttribute(gemm_conv_persistent<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
@@ -453,7 +476,7 @@ cudaError_t launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorM
 cudaError_t dispatch(int bn, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& to, const TileParams& p,
                      const GemmEpilogue& ep, int use_tma_store, uint32_t* status, cudaStream_t st) {
   if (bn == 64) return launch<64, 6>(ta, tb, to, p, ep, use_tma_store, status, st);
-  return launch<128, 5>(ta, tb, to, p, ep, use_tma_store, status, st);
+  return launch<128, 4>(ta, tb, to, p, ep, use_tma_store, status, st);
 }
 
 }  // namespace

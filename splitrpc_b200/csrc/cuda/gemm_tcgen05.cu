@@ -72,7 +72,9 @@ __device__ __forceinline__ void epilogue_store(const GemmEpilogue& ep, uint32_t 
           }
         }
       } else {
-        for (int j = 0; j < 32 && col0 + j < N; j++) v[j] += __bfloat162float(rp[j]);
+        #pragma unroll
+            for (int j = 0; j < 32; j++)
+              if (col0 + j < N) v[j] += __bfloat162float(rp[j]);
       }
     }
     if (ep.act == GEMM_ACT_RELU) {
@@ -87,7 +89,9 @@ __device__ __forceinline__ void epilogue_store(const GemmEpilogue& ep, uint32_t 
     }
     if (ep.out_fp32) {
       float* op = reinterpret_cast<float*>(ep.out) + (size_t)row * ep.ldo + col0;
-      for (int j = 0; j < 32 && col0 + j < N; j++) op[j] = v[j];
+      #pragma unroll
+            for (int j = 0; j < 32; j++)
+              if (col0 + j < N) op[j] = v[j];
     } else {
       __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(ep.out) + (size_t)row * ep.ldo + col0;
       if (col0 + 32 <= N && vec_out) {
@@ -100,7 +104,9 @@ __device__ __forceinline__ void epilogue_store(const GemmEpilogue& ep, uint32_t 
           *reinterpret_cast<uint4*>(op + j) = q;
         }
       } else {
-        for (int j = 0; j < 32 && col0 + j < N; j++) op[j] = __float2bfloat16(v[j]);
+        #pragma unroll
+            for (int j = 0; j < 32; j++)
+              if (col0 + j < N) op[j] = __float2bfloat16(v[j]);
       }
     }
   }

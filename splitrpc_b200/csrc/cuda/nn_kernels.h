@@ -19,5 +19,8 @@ cudaError_t nn_layernorm(const void* x, const void* residual, const float* gamma
 cudaError_t nn_bert_embed_ln(const void* d_stub, const int* direct_ids, size_t req_stride, int batch, int seq, const void* word,
                              const void* pos, const void* type, const float* gamma, const float* beta, void* y, int hidden,
                              int vocab, float eps, cudaStream_t s);
+// Tensor-core attention: qk = [tokens, 2*hidden] (Q | K), vt = [hidden, tokens] (V transposed), out = [tokens, hidden].
+cudaError_t nn_attention_tc(const void* qk, int ld_qk, const void* vt, int ld_vt, void* out, int ld_out, const float* v_bias,
+                            int batch, int seq, int heads, uint32_t* status, cudaStream_t s);
 cudaError_t nn_attention_d64(const void* qkv, void* out, int batch, int seq, int heads, int ld_qkv, int q_off, int k_off,
                              int v_off, int ld_out, cudaStream_t s);

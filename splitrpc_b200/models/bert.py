@@ -37,9 +37,11 @@ BERT_LARGE = BertConfig(24, 1024, 16, 4096)
 
 
 class BertClassifier:
-    def __init__(self, cfg: BertConfig = BERT_BASE, seq: int = 128, device: int = 0, max_batch: int = 32, seed: int = 0):
+    def __init__(self, cfg: BertConfig = BERT_BASE, seq: int = 128, device: int = 0, max_batch: int = 32, seed: int = 0,
+                 attention: str = "tensor_core"):
         assert cfg.hidden == cfg.heads * 64, "attention kernel is specialised for head dim 64"
         self.cfg, self.seq, self.max_batch = cfg, seq, max_batch
+        self.attention = attention  # "tensor_core" (tcgen05 kernel) or "simt"
         self.device = torch.device("cuda", device)
         self.req_size = seq * 4
         self.resp_size = cfg.num_labels * 4
@@ -69,12 +71,13 @@ class BertClassifier:
         T = max_batch * seq
         self.buf = {
             "x": torch.empty((T, H), dtype=bf, device=dev), "qkv": torch.empty((T, 3 * H), dtype=bf, device=dev),
+            "vt": torch.empty((H, T), dtype=bf, device=dev),
             "ctx": torch.empty((T, H), dtype=bf, device=dev), "attn": torch.empty((T, H), dtype=bf, device=dev),
             "x1": torch.empty((T, H), dtype=bf, device=dev), "ffn": torch.empty((T, F), dtype=bf, device=dev),
             "y": torch.empty((T, H), dtype=bf, device=dev), "pooled": torch.empty((max_batch, H), dtype=bf, device=dev),
             "logits": torch.empty((max_batch, 8), dtype=torch.float32, device=dev),
         }
-        self.kernels_per_forward = 1 + 7 * cfg.layers + 3
+        self.kernels_per_forward = 1 + (8 if attention == "tensor_core" else 7) * cfg.layers + 3
 
     def forward(self, batch: int, ids: torch.Tensor | None = None, d_stub: int = 0, out: torch.Tensor | None = None,
                 flag_ptr: int = 0, flag_value: int = 0, counter: torch.Tensor | None = None) -> torch.Tensor:
@@ -85,8 +88,17 @@ class BertClassifier:
                           d_stub=d_stub, req_stride=self.req_size)
         for l in range(cfg.layers):
             q = f"l{l}."
-            ops.gemm(x, p[q + "qkv.w"], bias=p[q + "qkv.b"], out=qkv)
-            ops.attention_d64(qkv, batch, S, cfg.heads, out=ctx)
+            if self.attention == "tensor_core":
+                H = cfg.hidden
+                # Q|K projection, then V^T = Wv . x^T with swapped operands (already K-major for P.V); the V bias
+                # is added to the attention output.
+                ops.gemm(x, p[q + "qkv.w"][: 2 * H], bias=p[q + "qkv.b"][: 2 * H], out=qkv[:, : 2 * H])
+                vt = b["vt"][:, :T] if T == b["vt"].shape[1] else b["vt"].view(-1)[: H * T].view(H, T)
+                ops.gemm(p[q + "qkv.w"][2 * H:], x, out=vt)
+                ops.attention_tc(qkv[:, : 2 * H], vt, batch, S, cfg.heads, v_bias=p[q + "qkv.b"][2 * H:], out=ctx)
+            else:
+                ops.gemm(x, p[q + "qkv.w"], bias=p[q + "qkv.b"], out=qkv)
+                ops.attention_d64(qkv, batch, S, cfg.heads, out=ctx)
             ops.gemm(ctx, p[q + "o.w"], bias=p[q + "o.b"], residual=x, out=attn)
             ops.layernorm(attn, p[q + "ln1.g"], p[q + "ln1.b"], out=x1)
             ops.gemm(x1, p[q + "f1.w"], bias=p[q + "f1.b"], act="gelu", out=ffn)

@@ -169,3 +169,20 @@ def attention_d64(qkv: torch.Tensor, batch: int, seq: int, heads: int, out: torc
     _C.attention_d64(qkv.data_ptr(), out.data_ptr(), batch, seq, heads, qkv.stride(0), offsets[0], offsets[1], offsets[2],
                      out.stride(0), _stream())
     return out
+
+
+def attention_tc(qk: torch.Tensor, vt: torch.Tensor, batch: int, seq: int, heads: int, v_bias: torch.Tensor | None = None,
+                 out: torch.Tensor | None = None) -> torch.Tensor:
+    """Tensor-core attention (head dim 64, all-ones mask).
+
+    ``qk`` is ``[tokens, 2*hidden]`` (Q | K), ``vt`` is ``[hidden, tokens]`` (V transposed, without its bias);
+    ``v_bias`` (fp32 ``[hidden]``) is added to the output.  Returns ``[tokens, hidden]`` bf16.
+    """
+    hidden = heads * 64
+    assert qk.dtype == torch.bfloat16 and vt.dtype == torch.bfloat16 and qk.stride(1) == 1 and vt.stride(1) == 1
+    assert qk.shape == (batch * seq, 2 * hidden) and vt.shape == (hidden, batch * seq)
+    if out is None:
+        out = torch.empty((batch * seq, hidden), dtype=torch.bfloat16, device=qk.device)
+    _C.attention_tc(qk.data_ptr(), qk.stride(0), vt.data_ptr(), vt.stride(0), out.data_ptr(), out.stride(0), _ptr(v_bias),
+                    batch, seq, heads, status_word().data_ptr(), _stream())
+    return out

@@ -59,6 +59,23 @@ def test_attention_matches_pytorch(torch_cuda, seq, heads):
     torch.testing.assert_close(out.float(), ref, rtol=2e-2, atol=2e-2)
 
 
+@pytest.mark.parametrize("seq,heads", [(128, 12), (384, 16)])
+def test_tensor_core_attention_matches_pytorch(torch_cuda, seq, heads):
+    torch = torch_cuda
+    from splitrpc_b200 import ops
+
+    B, H = 3, heads * 64
+    qk = (torch.randn(B * seq, 2 * H, device="cuda") * 0.7).bfloat16()
+    v = (torch.randn(B * seq, H, device="cuda") * 0.5).bfloat16()
+    vb = torch.randn(H, device="cuda")
+    out = ops.attention_tc(qk, v.t().contiguous(), B, seq, heads, v_bias=vb)
+    ops.check_status()
+    q, k = (t.float().view(B, seq, heads, 64).transpose(1, 2) for t in qk.split(H, dim=1))
+    vv = v.float().view(B, seq, heads, 64).transpose(1, 2)
+    ref = (torch.softmax(q @ k.transpose(-1, -2) / 8.0, -1) @ vv).transpose(1, 2).reshape(B * seq, H) + vb
+    torch.testing.assert_close(out.float(), ref, rtol=2e-2, atol=2e-2)
+
+
 def test_resnet50_matches_fp32_reference(torch_cuda):
     torch = torch_cuda
     from splitrpc_b200 import ops
