@@ -6,6 +6,7 @@
 #include <cuda_runtime.h>
 
 #include "cuda/gemm_tcgen05.h"
+#include "cuda/gemm_tp.h"
 #include "cuda/nn_kernels.h"
 #include "cuda/ops_api.h"
 
@@ -86,6 +87,71 @@ void bind_ops(py::module_& m) {
         py::arg("input"), py::arg("weight"), py::arg("n"), py::arg("h"), py::arg("w"), py::arg("cin"), py::arg("cout"),
         py::arg("r"), py::arg("s"), py::arg("stride"), py::arg("pad"), py::arg("out"), py::arg("bias") = 0,
         py::arg("residual") = 0, py::arg("act") = 0, py::arg("status") = 0, py::arg("stream") = 0, py::arg("impl") = 2);
+
+  // ---- tensor-parallel fused kernels
+  m.def("gemm_tp",
+        [](uintptr_t a, int lda, uintptr_t b, int ldb, int M, int N, int K, uintptr_t out, int ldo, uintptr_t bias, int act,
+           int tp, int rank, uint32_t epoch, uintptr_t mblock_ready, int n_copy, std::vector<uintptr_t> src,
+           uintptr_t gathered, uintptr_t src_ready, int rs, std::vector<uintptr_t> dst, std::vector<uintptr_t> dst_flag,
+           uintptr_t owner_count, uintptr_t status, uintptr_t stream, uintptr_t epoch_base) {
+          GemmEpilogue ep = make_ep(out, ldo, false, bias, 0, 0, act);
+          TpParams t;
+          t.tp = tp;
+          t.rank = rank;
+          t.epoch = epoch;
+          t.epoch_base = (const uint32_t*)epoch_base;
+          t.mblock_ready = (uint32_t*)mblock_ready;
+          t.n_copy = n_copy;
+          for (size_t i = 0; i < src.size() && i < TP_MAX_RANKS; i++) t.src[i] = (const uint8_t*)src[i];
+          t.gathered = (uint8_t*)gathered;
+          t.src_ready = (const uint32_t*)src_ready;
+          t.rs = rs;
+          for (size_t i = 0; i < dst.size() && i < TP_MAX_RANKS; i++) t.dst[i] = (uint8_t*)dst[i];
+          for (size_t i = 0; i < dst_flag.size() && i < TP_MAX_RANKS; i++) t.dst_flag[i] = (uint32_t*)dst_flag[i];
+          t.owner_count = (uint32_t*)owner_count;
+          check(srpc_gemm_tp((const void*)a, lda, (const void*)b, ldb, M, N, K, ep, t, (uint32_t*)status, (cudaStream_t)stream),
+                "gemm_tp");
+        },
+        py::arg("a"), py::arg("lda"), py::arg("b"), py::arg("ldb"), py::arg("M"), py::arg("N"), py::arg("K"), py::arg("out"),
+        py::arg("ldo"), py::arg("bias") = 0, py::arg("act") = 0, py::arg("tp") = 1, py::arg("rank") = 0, py::arg("epoch") = 0,
+        py::arg("mblock_ready") = 0, py::arg("n_copy") = 0, py::arg("src") = std::vector<uintptr_t>{},
+        py::arg("gathered") = 0, py::arg("src_ready") = 0, py::arg("rs") = 0, py::arg("dst") = std::vector<uintptr_t>{},
+        py::arg("dst_flag") = std::vector<uintptr_t>{}, py::arg("owner_count") = 0, py::arg("status") = 0,
+        py::arg("stream") = 0, py::arg("epoch_base") = 0);
+  m.def("tp_wait", [](uintptr_t flags, int n, uint32_t epoch, uintptr_t epoch_base, uintptr_t status, uintptr_t stream) {
+    check(srpc_tp_wait((const uint32_t*)flags, n, epoch, (const uint32_t*)epoch_base, (uint32_t*)status, (cudaStream_t)stream),
+          "tp_wait");
+  });
+  m.def("tp_bump", [](uintptr_t word, uint32_t delta, uintptr_t stream) {
+    check(srpc_tp_bump((uint32_t*)word, delta, (cudaStream_t)stream), "tp_bump");
+  });
+  m.def("tp_signal", [](std::vector<uintptr_t> peer_flags, uint32_t epoch, uintptr_t stream, uintptr_t epoch_base) {
+    TpSignal s{};
+    s.tp = (int)peer_flags.size();
+    s.epoch = epoch;
+    s.epoch_base = (const uint32_t*)epoch_base;
+    for (size_t i = 0; i < peer_flags.size() && i < TP_MAX_RANKS; i++) s.peer_flag[i] = (uint32_t*)peer_flags[i];
+    check(srpc_tp_signal(s, (cudaStream_t)stream), "tp_signal");
+  });
+  m.def("layernorm_reduce",
+        [](std::vector<uintptr_t> slots, uintptr_t flags, uint32_t epoch, uintptr_t bias, uintptr_t residual, uintptr_t gamma,
+           uintptr_t beta, uintptr_t out, int rows, int hidden, float eps, uintptr_t status, uintptr_t stream,
+           uintptr_t epoch_base) {
+          TpReduce r{};
+          r.tp = (int)slots.size();
+          r.hidden = hidden;
+          r.epoch = epoch;
+          r.epoch_base = (const uint32_t*)epoch_base;
+          r.flags = (const uint32_t*)flags;
+          for (size_t i = 0; i < slots.size() && i < TP_MAX_RANKS; i++) r.slots[i] = (const __nv_bfloat16*)slots[i];
+          r.bias = (const float*)bias;
+          r.residual = (const __nv_bfloat16*)residual;
+          r.gamma = (const float*)gamma;
+          r.beta = (const float*)beta;
+          r.out = (__nv_bfloat16*)out;
+          r.eps = eps;
+          check(srpc_layernorm_reduce(r, rows, (uint32_t*)status, (cudaStream_t)stream), "layernorm_reduce");
+        });
 
   // ---- memory-bound layers
   m.def("stem_im2col",

@@ -8,7 +8,12 @@
 #include "driver_api.h"
 
 enum GemmAct { GEMM_ACT_NONE = 0, GEMM_ACT_RELU = 1, GEMM_ACT_GELU = 2, GEMM_ACT_TANH = 3 };
-enum GemmErr { GEMM_OK = 0, GEMM_ERR_PRODUCER_WAIT = 1, GEMM_ERR_MMA_WAIT = 2, GEMM_ERR_EPILOGUE_WAIT = 3 };
+enum GemmErr {
+  GEMM_OK = 0, GEMM_ERR_PRODUCER_WAIT = 1, GEMM_ERR_MMA_WAIT = 2, GEMM_ERR_EPILOGUE_WAIT = 3,
+  GEMM_ERR_TP_SRC_WAIT = 4,     // a peer never published its shard
+  GEMM_ERR_TP_BLOCK_WAIT = 5,   // a copier block never delivered a row block
+  GEMM_ERR_TP_REDUCE_WAIT = 6,  // a source rank never delivered its partial tiles
+};
 
 // out[row, col] = act(acc + bias[col] + residual[row, col]); leading dimensions in elements.
 struct GemmEpilogue {

@@ -1,0 +1,514 @@
+// Tensor-parallel GEMMs fused with their collectives over NVLink peer memory.
+//
+// The original system has no multi-GPU path at all (one device per process,
+// reference src/utils/config_utils.h:42-44); these kernels are what lets one model
+// span several B200s.  Both are the persistent tcgen05 GEMM (TMA-fed operands,
+// TMEM accumulators, 128 x 128 tiles) with the collective folded in:
+//
+//  all-gather -> GEMM   D[T, N_local] = act(concat_r(X_r)[T, K] . W[N_local, K]^T + bias)
+//    X is sharded by rows over the ranks.  A few "copier" blocks of the same launch
+//    pull the remote shards over NVLink (plain peer loads, 16 bytes per thread)
+//    into a local gathered buffer, one 128-row block at a time, and publish each
+//    block with a release store; the GEMM blocks visit row blocks in rotated
+//    order (own shard first) and their TMA producer waits (bounded) for a block's
+//    flag before loading it from LOCAL memory.  So each remote byte crosses
+//    NVLink once, and the transfer overlaps the math tile by tile.
+//
+//  GEMM -> reduce-scatter   P_r[T, N] = A_r[T, K_local] . W_r[N, K_local]^T,  D = sum_r P_r sharded by rows
+//    Every rank computes partial tiles and its epilogue stores each finished tile
+//    straight into the owner rank's slot for this source (peer stores, coalesced
+//    16-byte vectors out of the shared-memory staging tile).  When a rank has
+//    delivered all tiles of an owner it publishes a flag in that owner's memory
+//    with a system-scope release.  The owner's reduction (sum of the slots + bias
+//    + residual + LayerNorm, see layernorm_reduce) waits for the flags, so the
+//    reduction itself is fused into the normalisation that follows.
+//
+// No load uses multicast; remote data is only touched by plain loads/stores.
+// Every wait on a flag (another block's or another rank's) is bounded: when it
+// runs out the kernel records an error code and winds down.
+#include <algorithm>
+#include <cstring>
+
+#include "gemm_tcgen05.h"
+#include "gemm_tp.h"
+#include "ptx.cuh"
+
+namespace {
+
+constexpr int BM = 128, BN = 128, BK = 64, UMMA_K = 16;
+constexpr int STAGES = 4;
+constexpr int THREADS = 320;
+constexpr int EPI_THREADS = 256;
+constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int OUT_HALF_BYTES = BM * 128, OUT_BYTES = 2 * OUT_HALF_BYTES;
+constexpr uint64_t FLAG_WAIT_NS = 2000000000ull;
+
+__device__ __forceinline__ float gelu_f(float x) { return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f)); }
+__device__ __forceinline__ void named_bar_sync(int id, int count) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
+}
+__device__ __forceinline__ bool named_bar_all(int id, int count, bool pred) {
+  uint32_t out;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %3, 0;\n\t"
+      "barrier.cta.red.and.pred p, %1, %2, q;\n\tselp.u32 %0, 1, 0, p;\n\t}\n"
+      : "=r"(out)
+      : "r"(id), "r"(count), "r"((uint32_t)pred)
+      : "memory");
+  return out != 0;
+}
+
+// Bounded wait until *flag >= epoch (flags only ever grow).
+__device__ __forceinline__ bool wait_flag_gpu(const uint32_t* flag, uint32_t epoch) {
+  const uint64_t t0 = ptx::globaltimer_ns();
+  for (;;) {
+    for (int i = 0; i < 32; i++) {
+      if ((int32_t)(ptx::ld_acquire_gpu(flag) - epoch) >= 0) return true;
+      __nanosleep(100);
+    }
+    if (ptx::globaltimer_ns() - t0 > FLAG_WAIT_NS) return false;
+  }
+}
+__device__ __forceinline__ bool wait_flag_sys(const uint32_t* flag, uint32_t epoch) {
+  const uint64_t t0 = ptx::globaltimer_ns();
+  for (;;) {
+    for (int i = 0; i < 32; i++) {
+      if ((int32_t)(ptx::ld_acquire_sys(flag) - epoch) >= 0) return true;
+      __nanosleep(200);
+    }
+    if (ptx::globaltimer_ns() - t0 > FLAG_WAIT_NS) return false;
+  }
+}
+
+// Copier role: pulls remote row blocks into the local gathered buffer.
+__device__ void copier(const TpParams& tp, int copier_idx, uint32_t* status) {
+  __shared__ uint32_t s_ok;
+  const int remote_blocks = (tp.tp - 1) * tp.mblocks_per_rank;
+  for (int i = copier_idx; i < remote_blocks; i += tp.n_copy) {
+    // i-th remote block in rotated order: ranks rank+1, rank+2, ... ; blocks of a rank in order
+    const int step = i / tp.mblocks_per_rank + 1;
+    const int r = (tp.rank + step) % tp.tp;
+    const int blk = i % tp.mblocks_per_rank;
+    if (threadIdx.x == 0) s_ok = wait_flag_sys(tp.src_ready + r, tp.epoch) ? 1u : 0u;
+    __syncthreads();
+    if (!s_ok) {
+      if (threadIdx.x == 0 && status) atomicExch(status, GEMM_ERR_TP_SRC_WAIT);
+      return;
+    }
+    const uint4* src = reinterpret_cast<const uint4*>(tp.src[r] + (size_t)blk * tp.mblock_bytes);
+    const int m = r * tp.mblocks_per_rank + blk;
+    uint4* dst = reinterpret_cast<uint4*>(tp.gathered + (size_t)m * tp.mblock_bytes);
+    const int n16 = (int)(tp.mblock_bytes >> 4);
+    // 4 independent 16-byte loads in flight per thread to cover NVLink latency
+    int j = threadIdx.x;
+    for (; j + 3 * (int)blockDim.x < n16; j += 4 * blockDim.x) {
+      uint4 a = src[j], b = src[j + blockDim.x], c = src[j + 2 * blockDim.x], d = src[j + 3 * blockDim.x];
+      dst[j] = a;
+      dst[j + blockDim.x] = b;
+      dst[j + 2 * blockDim.x] = c;
+      dst[j + 3 * blockDim.x] = d;
+    }
+    for (; j < n16; j += blockDim.x) dst[j] = src[j];
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) ptx::st_release_gpu(tp.mblock_ready + m, tp.epoch);
+  }
+}
+
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+               const __grid_constant__ CUtensorMap tmap_out, int M, int N, int K, GemmEpilogue ep, const TpParams tp_in,
+               uint32_t* status) {
+  TpParams tp = tp_in;
+  if (tp.epoch_base) tp.epoch += *tp.epoch_base;
+  const int gemm_ctas = (int)gridDim.x - tp.n_copy;
+  if ((int)blockIdx.x >= gemm_ctas) {
+    copier(tp, (int)blockIdx.x - gemm_ctas, status);
+    return;
+  }
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* stage_out = smem + (size_t)STAGES * STAGE_BYTES;
+  __shared__ __align__(8) uint64_t full_bar[STAGES];
+  __shared__ __align__(8) uint64_t empty_bar[STAGES];
+  __shared__ __align__(8) uint64_t tmem_full_bar[2];
+  __shared__ __align__(8) uint64_t tmem_empty_bar[2];
+  __shared__ uint32_t tmem_base_smem;
+  __shared__ uint32_t s_error;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
+  const int num_tiles = tiles_m * tiles_n;
+  const int num_kb = (K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; s++) {
+      ptx::mbar_init(&full_bar[s], 1);
+      ptx::mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; a++) {
+      ptx::mbar_init(&tmem_full_bar[a], 1);
+      ptx::mbar_init(&tmem_empty_bar[a], 8);
+    }
+    ptx::fence_mbar_init();
+    s_error = 0;
+    ptx::prefetch_tmap(&tmap_a);
+    ptx::prefetch_tmap(&tmap_b);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(&tmem_base_smem, 2 * BN);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = tmem_base_smem;
+
+  // Tile order: row blocks rotated so that this rank's own shard comes first.
+  auto tile_mn = [&](int tile, int* m_idx, int* n_idx) {
+    *n_idx = tile % tiles_n;
+    *m_idx = (tile / tiles_n + tp.m_rot) % tiles_m;
+  };
+
+  if (warp == 0) {
+    if (ptx::elect_one()) {
+      uint32_t it = 0;
+      for (int tile = blockIdx.x; tile < num_tiles && *(volatile uint32_t*)&s_error == 0; tile += gemm_ctas) {
+        int m_idx, n_idx;
+        tile_mn(tile, &m_idx, &n_idx);
+        if (tp.mblock_ready) {
+          // Remote row blocks arrive through the copier blocks of this launch.
+          const int owner = m_idx / tp.mblocks_per_rank;
+          if (owner != tp.rank) {
+            if (!wait_flag_gpu(tp.mblock_ready + m_idx, tp.epoch)) {
+              atomicExch(&s_error, GEMM_ERR_TP_BLOCK_WAIT);
+              break;
+            }
+            ptx::fence_proxy_async_all();  // generic-proxy writes of the copier -> async-proxy (TMA) reads
+          }
+        }
+        for (int kb = 0; kb < num_kb; kb++, it++) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1u;
+          if (!ptx::mbar_wait(&empty_bar[s], ph ^ 1u)) {
+            atomicExch(&s_error, GEMM_ERR_PRODUCER_WAIT);
+            break;
+          }
+          uint8_t* sa = smem + (size_t)s * STAGE_BYTES;
+          ptx::mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+          ptx::tma_load_2d(sa, &tmap_a, &full_bar[s], kb * BK, m_idx * BM);
+          ptx::tma_load_2d(sa + A_BYTES, &tmap_b, &full_bar[s], kb * BK, n_idx * BN);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (ptx::elect_one()) {
+      const uint32_t idesc = ptx::umma_idesc_bf16(BM, BN);
+      uint32_t it = 0, local = 0;
+      for (int tile = blockIdx.x; tile < num_tiles && *(volatile uint32_t*)&s_error == 0; tile += gemm_ctas, local++) {
+        const uint32_t acc = local & 1u;
+        if (!ptx::mbar_wait(&tmem_empty_bar[acc], ((local >> 1) & 1u) ^ 1u)) {
+          atomicExch(&s_error, GEMM_ERR_MMA_WAIT);
+          break;
+        }
+        ptx::tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        bool ok = true;
+        for (int kb = 0; kb < num_kb; kb++, it++) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1u;
+          if (!ptx::mbar_wait(&full_bar[s], ph)) {
+            atomicExch(&s_error, GEMM_ERR_MMA_WAIT);
+            ok = false;
+            break;
+          }
+          ptx::tc_fence_after();
+          const uint32_t sa = ptx::smem_u32(smem + (size_t)s * STAGE_BYTES);
+          const uint32_t sb = sa + A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; k++)
+            ptx::umma_bf16(d_tmem, ptx::umma_desc_sw128(sa + k * UMMA_K * 2), ptx::umma_desc_sw128(sb + k * UMMA_K * 2), idesc,
+                           (kb | k) != 0 ? 1u : 0u);
+          ptx::umma_commit(&empty_bar[s]);
+        }
+        if (!ok) break;
+        ptx::umma_commit(&tmem_full_bar[acc]);
+      }
+    }
+  } else {
+    constexpr int CPW = BN / 2, NCH = CPW / 32;
+    const int warp_q = warp & 3;
+    const int chalf = (warp - 2) >> 2;
+    const int row = warp_q * 32 + lane;
+    const int et = threadIdx.x - 64;
+    uint32_t local = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gemm_ctas, local++) {
+      const uint32_t acc = local & 1u;
+      int m_idx, n_idx;
+      tile_mn(tile, &m_idx, &n_idx);
+      const int n0 = n_idx * BN, cbase = chalf * CPW;
+      const bool mine = (*(volatile uint32_t*)&s_error == 0) && ptx::mbar_wait(&tmem_full_bar[acc], (local >> 1) & 1u);
+      if (!named_bar_all(2, EPI_THREADS, mine)) {
+        if (lane == 0) atomicExch(&s_error, GEMM_ERR_EPILOGUE_WAIT);
+        break;
+      }
+      ptx::tc_fence_after();
+      uint32_t r[CPW];
+#pragma unroll
+      for (int ch = 0; ch < NCH; ch++)
+        ptx::tmem_ld_32x32b_x32(tmem_base + acc * BN + ((uint32_t)(warp_q * 32) << 16) + (uint32_t)(cbase + ch * 32), r + ch * 32);
+      ptx::tmem_ld_wait();
+      ptx::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(&tmem_empty_bar[acc]);
+      uint8_t* sbuf = stage_out + (size_t)(local & 1u) * OUT_BYTES;
+      if (!tp.rs) {
+        if (et == 0) ptx::bulk_wait_read<1>();
+      }
+      named_bar_sync(1, EPI_THREADS);  // staging buffer free (TMA store drained, or the previous peer-store pass done)
+#pragma unroll
+      for (int ch = 0; ch < NCH; ch++) {
+        const int c = cbase + ch * 32;
+        const int col0 = n0 + c;
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; j++) v[j] = __uint_as_float(r[ch * 32 + j]);
+        if (ep.bias && col0 + 32 <= N) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 4) {
+            float4 b4 = __ldg(reinterpret_cast<const float4*>(ep.bias + col0 + j));
+            v[j] += b4.x;
+            v[j + 1] += b4.y;
+            v[j + 2] += b4.z;
+            v[j + 3] += b4.w;
+          }
+        }
+        if (ep.act == GEMM_ACT_GELU) {
+#pragma unroll
+          for (int j = 0; j < 32; j++) v[j] = gelu_f(v[j]);
+        } else if (ep.act == GEMM_ACT_RELU) {
+#pragma unroll
+          for (int j = 0; j < 32; j++) v[j] = fmaxf(v[j], 0.f);
+        }
+        uint8_t* half = sbuf + (size_t)(c >> 6) * OUT_HALF_BYTES + (size_t)row * 128;
+        const int chunk0 = (c & 63) >> 3;
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+          uint4 q;
+          __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&q);
+#pragma unroll
+          for (int t = 0; t < 4; t++) h[t] = __floats2bfloat162_rn(v[j * 8 + 2 * t], v[j * 8 + 2 * t + 1]);
+          *reinterpret_cast<uint4*>(half + (((chunk0 + j) ^ (row & 7)) << 4)) = q;
+        }
+      }
+      if (!tp.rs) {
+        ptx::fence_proxy_async_smem();
+        named_bar_sync(1, EPI_THREADS);
+        if (et == 0) {
+          for (int hcol = 0; hcol < BN / 64; hcol++) {
+            if (n0 + hcol * 64 >= N) break;
+            ptx::tma_store_2d(&tmap_out, sbuf + (size_t)hcol * OUT_HALF_BYTES, n0 + hcol * 64, m_idx * BM);
+          }
+          ptx::bulk_commit();
+        }
+      } else {
+        // Peer-store epilogue: the tile goes to the slot this rank owns on the row block's owner.
+        named_bar_sync(1, EPI_THREADS);
+        const int owner = m_idx / tp.mblocks_per_rank;
+        const int local_m0 = (m_idx - owner * tp.mblocks_per_rank) * BM;
+        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(tp.dst[owner]);
+        // 16 threads write one 256-byte row segment; 16 rows per pass
+        const int seg = et & 15, r0 = et >> 4;
+#pragma unroll 2
+        for (int rr = r0; rr < BM; rr += EPI_THREADS / 16) {
+          const int col = n0 + seg * 8;
+          if (col < N) {
+            const uint8_t* src = sbuf + (size_t)(seg >> 3) * OUT_HALF_BYTES + (size_t)rr * 128 + (((seg & 7) ^ (rr & 7)) << 4);
+            uint4 q = *reinterpret_cast<const uint4*>(src);
+            *reinterpret_cast<uint4*>(dst + (size_t)(local_m0 + rr) * ep.ldo + col) = q;
+          }
+        }
+        __threadfence_system();
+        named_bar_sync(1, EPI_THREADS);
+        if (et == 0) {
+          const uint32_t done = atomicAdd(tp.owner_count + owner, 1u) + 1u;
+          if (done == (uint32_t)tp.tiles_per_owner) {
+            atomicExch(tp.owner_count + owner, 0u);
+            __threadfence_system();
+            ptx::st_release_sys(tp.dst_flag[owner], tp.epoch);
+          }
+        }
+      }
+    }
+    if (!tp.rs && et == 0) ptx::bulk_wait_all<0>();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (s_error != 0) {
+    if (threadIdx.x == 0 && status) atomicExch(status, s_error);
+    __nanosleep(1000000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem_base, 2 * BN);
+  }
+}
+
+cudaError_t map_2d(CUtensorMap* m, const void* ptr, uint64_t inner, uint64_t outer, uint64_t row_stride_bytes,
+                   uint32_t box_inner, uint32_t box_outer) {
+  const SrpcDriverApi* d = srpc_driver_api();
+  if (!d->TensorMapEncodeTiled) return cudaErrorNotSupported;
+  cuuint64_t dims[2] = {inner, outer};
+  cuuint64_t st[1] = {row_stride_bytes};
+  cuuint32_t box[2] = {box_inner, box_outer};
+  cuuint32_t es[2] = {1, 1};
+  CUresult r = d->TensorMapEncodeTiled(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, st, box, es,
+                                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                       CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
+}
+
+// Signals every peer that this rank's shard for `epoch` is complete.
+__global__ void tp_signal_peers(TpSignal sig) {
+  const int p = threadIdx.x;
+  if (p < sig.tp) {
+    const uint32_t e = sig.epoch + (sig.epoch_base ? *sig.epoch_base : 0u);
+    __threadfence_system();
+    ptx::st_release_sys(sig.peer_flag[p], e);
+  }
+}
+
+// y = LN(sum_r slot_r[row] + bias + residual) * gamma + beta; waits (bounded) until every source rank has
+// published `epoch` in flags[r].
+__global__ void __launch_bounds__(256) layernorm_reduce(TpReduce rd, uint32_t* status) {
+  __shared__ float sh[32];
+  __shared__ uint32_t s_ok;
+  if (threadIdx.x == 0) {
+    uint32_t ok = 1;
+    const uint32_t e = rd.epoch + (rd.epoch_base ? *rd.epoch_base : 0u);
+    for (int r = 0; r < rd.tp && ok; r++) ok = wait_flag_sys(rd.flags + r, e) ? 1u : 0u;
+    s_ok = ok;
+  }
+  __syncthreads();
+  if (!s_ok) {
+    if (threadIdx.x == 0 && status) atomicExch(status, GEMM_ERR_TP_REDUCE_WAIT);
+    return;
+  }
+  const size_t row = blockIdx.x;
+  float v[8];
+  int cnt = 0;
+  float s = 0.f;
+  for (int i = threadIdx.x; i < rd.hidden && cnt < 8; i += blockDim.x, cnt++) {
+    float f = rd.bias ? rd.bias[i] : 0.f;
+    for (int r = 0; r < rd.tp; r++) f += __bfloat162float(rd.slots[r][row * rd.hidden + i]);
+    if (rd.residual) f += __bfloat162float(rd.residual[row * rd.hidden + i]);
+    v[cnt] = f;
+    s += f;
+  }
+  auto block_sum = [&](float x) {
+#pragma unroll
+    for (int o = 16; o; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
+    const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = blockDim.x >> 5;
+    __syncthreads();
+    if (l == 0) sh[w] = x;
+    __syncthreads();
+    float t = (l < nw) ? sh[l] : 0.f;
+#pragma unroll
+    for (int o = 16; o; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+    return t;
+  };
+  const float mean = block_sum(s) / rd.hidden;
+  float q = 0.f;
+  for (int k = 0; k < cnt; k++) q += (v[k] - mean) * (v[k] - mean);
+  const float rstd = rsqrtf(block_sum(q) / rd.hidden + rd.eps);
+  cnt = 0;
+  for (int i = threadIdx.x; i < rd.hidden && cnt < 8; i += blockDim.x, cnt++)
+    rd.out[row * rd.hidden + i] = __float2bfloat16((v[cnt] - mean) * rstd * rd.gamma[i] + rd.beta[i]);
+}
+
+int num_sms() {
+  static int n = 0;
+  if (!n) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (n <= 0) n = 148;
+  }
+  return n;
+}
+
+}  // namespace
+
+cudaError_t srpc_gemm_tp(const void* A, int lda, const void* B, int ldb, int M, int N, int K, const GemmEpilogue& ep,
+                         const TpParams& tp_in, uint32_t* status, cudaStream_t stream) {
+  if (M <= 0 || N < 0 || K <= 0 || (M % BM) != 0) return cudaErrorInvalidValue;
+  if ((lda % 8) || (ldb % 8) || (K % 8) || ((uintptr_t)A & 15) || ((uintptr_t)B & 15) || (ep.ldo % 8)) return cudaErrorInvalidValue;
+  TpParams tp = tp_in;
+  if (tp.tp < 1 || tp.tp > TP_MAX_RANKS || (M / BM) % tp.tp != 0) return cudaErrorInvalidValue;
+  tp.mblocks_per_rank = (M / BM) / tp.tp;
+  tp.m_rot = tp.rank * tp.mblocks_per_rank;
+  tp.mblock_bytes = (size_t)BM * lda * 2;
+  const int tiles_n = (N + BN - 1) / BN;
+  tp.tiles_per_owner = tp.mblocks_per_rank * tiles_n;
+  if (!tp.mblock_ready) tp.n_copy = 0;
+  static bool attr = false;
+  const int smem = STAGES * STAGE_BYTES + 2 * OUT_BYTES + 1024;
+  if (!attr) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tp_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return e;
+    attr = true;
+  }
+  CUtensorMap ta, tb, to;
+  cudaError_t e = map_2d(&ta, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda * 2, BK, BM);
+  if (e != cudaSuccess) return e;
+  if (N > 0) {
+    e = map_2d(&tb, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb * 2, BK, BN);
+    if (e != cudaSuccess) return e;
+  } else {
+    tb = ta;
+  }
+  if (!tp.rs && N > 0) {
+    e = map_2d(&to, ep.out, (uint64_t)N, (uint64_t)M, (uint64_t)ep.ldo * 2, 64, BM);
+    if (e != cudaSuccess) return e;
+  } else {
+    to = ta;
+  }
+  const int tiles = (M / BM) * tiles_n;
+  int gemm_ctas = std::min(std::max(tiles, 1), num_sms() - tp.n_copy);
+  if (gemm_ctas < 1) return cudaErrorInvalidValue;
+  gemm_tp_kernel<<<gemm_ctas + tp.n_copy, THREADS, smem, stream>>>(ta, tb, to, M, N, K, ep, tp, status);
+  return cudaGetLastError();
+}
+
+cudaError_t srpc_tp_signal(const TpSignal& sig, cudaStream_t stream) {
+  tp_signal_peers<<<1, 32, 0, stream>>>(sig);
+  return cudaGetLastError();
+}
+
+__global__ void tp_wait_kernel(const uint32_t* flags, int n, uint32_t epoch, const uint32_t* epoch_base, uint32_t* status) {
+  const int i = threadIdx.x;
+  if (i < n) {
+    const uint32_t e = epoch + (epoch_base ? *epoch_base : 0u);
+    if (!wait_flag_sys(flags + i, e) && status) atomicExch(status, GEMM_ERR_TP_SRC_WAIT);
+  }
+}
+
+cudaError_t srpc_tp_wait(const uint32_t* flags, int n, uint32_t epoch, const uint32_t* epoch_base, uint32_t* status,
+                         cudaStream_t stream) {
+  tp_wait_kernel<<<1, 32, 0, stream>>>(flags, n, epoch, epoch_base, status);
+  return cudaGetLastError();
+}
+
+__global__ void tp_bump_kernel(uint32_t* word, uint32_t delta) { *word += delta; }
+
+cudaError_t srpc_tp_bump(uint32_t* word, uint32_t delta, cudaStream_t stream) {
+  tp_bump_kernel<<<1, 1, 0, stream>>>(word, delta);
+  return cudaGetLastError();
+}
+
+cudaError_t srpc_layernorm_reduce(const TpReduce& rd, int rows, uint32_t* status, cudaStream_t stream) {
+  if (rd.hidden > 2048 || rd.tp < 1 || rd.tp > TP_MAX_RANKS) return cudaErrorInvalidValue;
+  layernorm_reduce<<<rows, 256, 0, stream>>>(rd, status);
+  return cudaGetLastError();
+}

@@ -1,0 +1,65 @@
+// Launch API of the tensor-parallel fused kernels (all-gather -> GEMM, GEMM ->
+// reduce-scatter, reduce + LayerNorm) over NVLink peer memory.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "gemm_tcgen05.h"
+
+#define TP_MAX_RANKS 8
+
+struct TpParams {
+  int tp = 1, rank = 0;
+  uint32_t epoch = 0;            // flags are monotonically increasing step numbers
+  const uint32_t* epoch_base = nullptr;  // optional device word added to `epoch` at run time (lets a captured
+                                         // graph use fresh step numbers on every replay)
+  // ---- all-gather side (mblock_ready == nullptr: A is entirely local)
+  uint32_t* mblock_ready = nullptr;  // local flags, one per 128-row block of A
+  int n_copy = 0;                    // copier blocks appended to the grid
+  const uint8_t* src[TP_MAX_RANKS] = {};  // src[r]: rank r's own shard (rows r*M/tp ...) in r's memory
+  uint8_t* gathered = nullptr;       // local A buffer [M, K]; this rank's shard is already in place
+  const uint32_t* src_ready = nullptr;  // local words [tp]: peers publish their shard's epoch here
+  // ---- reduce-scatter side (rs == 0: plain local output)
+  int rs = 0;
+  uint8_t* dst[TP_MAX_RANKS] = {};       // dst[o]: slot for this rank's partial rows on owner o ([M/tp, ldo])
+  uint32_t* dst_flag[TP_MAX_RANKS] = {};  // dst_flag[o]: word on owner o that receives the epoch when all tiles are there
+  uint32_t* owner_count = nullptr;       // local zeroed counters [tp]
+  // ---- filled in by the launcher
+  int mblocks_per_rank = 0, m_rot = 0, tiles_per_owner = 0;
+  size_t mblock_bytes = 0;
+};
+
+struct TpSignal {
+  int tp;
+  uint32_t epoch;
+  const uint32_t* epoch_base;
+  uint32_t* peer_flag[TP_MAX_RANKS];  // peer_flag[p]: this rank's word in peer p's signal area
+};
+
+struct TpReduce {
+  int tp, hidden;
+  uint32_t epoch;
+  const uint32_t* epoch_base;
+  const uint32_t* flags;                       // local words [tp] written by the source ranks
+  const __nv_bfloat16* slots[TP_MAX_RANKS];    // local partial buffers, one per source rank, [rows, hidden]
+  const float* bias;
+  const __nv_bfloat16* residual;               // [rows, hidden] or null
+  const float *gamma, *beta;
+  __nv_bfloat16* out;
+  float eps;
+};
+
+// D = act(A . B^T + bias); A is [M, K] with M/128 divisible by tp.  With tp.mblock_ready set, remote row blocks of A
+// are pulled into tp.gathered by copier blocks of the same launch (N == 0 gives a pure all-gather).  With tp.rs set,
+// finished tiles are stored into the owners' slots instead of ep.out (ep.ldo = row stride of a slot).
+cudaError_t srpc_gemm_tp(const void* A, int lda, const void* B, int ldb, int M, int N, int K, const GemmEpilogue& ep,
+                         const TpParams& tp, uint32_t* status, cudaStream_t stream);
+cudaError_t srpc_tp_signal(const TpSignal& sig, cudaStream_t stream);
+// Stream-ordered bounded wait until flags[0..n) >= epoch (+ *epoch_base); a timeout sets *status.
+cudaError_t srpc_tp_wait(const uint32_t* flags, int n, uint32_t epoch, const uint32_t* epoch_base, uint32_t* status,
+                         cudaStream_t stream);
+// *word += delta, stream ordered (advances the step-number base between forward passes).
+cudaError_t srpc_tp_bump(uint32_t* word, uint32_t delta, cudaStream_t stream);
+cudaError_t srpc_layernorm_reduce(const TpReduce& rd, int rows, uint32_t* status, cudaStream_t stream);
