@@ -58,13 +58,15 @@ class TensorParallel:
     def begin_step(self) -> None:
         """Start of a forward pass: waits until every peer has finished the previous pass (they may still be reading
         this rank's buffers), then advances the step-number base.  Captured into graphs like any other launch."""
-        _C.tp_wait(self.flags[self._site["DONE"]].data_ptr(), self.tp, self.STEP - 1, self.epoch_base.data_ptr(),
+        # Pass f ends by publishing DONE = base(f) (the base after its own bump); before bumping, the current base is
+        # exactly that value (0 before the first pass, which the zero-initialised flags satisfy).
+        _C.tp_wait(self.flags[self._site["DONE"]].data_ptr(), self.tp, 0, self.epoch_base.data_ptr(),
                    status_word().data_ptr(), _stream())
         _C.tp_bump(self.epoch_base.data_ptr(), self.STEP, _stream())
 
     def end_step(self) -> None:
         """End of a forward pass: tells every peer that this rank no longer reads their buffers."""
-        self.signal("DONE", self.STEP - 1)
+        self.signal("DONE", 0)
 
     def signal(self, which: str, epoch: int) -> None:
         """Tells every peer that this rank's shard of gathered buffer ``which`` holds step ``epoch``."""
