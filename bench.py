@@ -38,7 +38,8 @@ CONFIGS = {
     "resnet50": dict(model="ResNet-50 v1.5 bf16 (BN folded), 3x224x224 fp32 requests in 8 KB fragments", max_batch=64,
                      payload="normal", seq=None),
     "bert_base": dict(model="BERT-base bf16 classifier, seq 128 int32 ids", max_batch=32, payload="ids", seq=128),
-    "lenet5": dict(model="LeNet-5 fp32", max_batch=32, payload="uniform", seq=None),
+    "bert_large_tp": dict(model="BERT-large bf16 classifier, seq 384 int32 ids, tensor parallel over all GPUs",
+                          max_batch=16, payload="ids", seq=384),
 }
 
 
@@ -92,6 +93,8 @@ def build_model(config: str, device: int):
         from splitrpc_b200.models import ResNet50
 
         return ResNet50(device=device, max_batch=CONFIGS[config]["max_batch"])
+    if config == "lenet5":
+        raise SystemExit("lenet5 is served by the built-in app: see tests/test_gpu_sg.py and serving.smoke_test")
     if config == "bert_base":
         from splitrpc_b200.models import BertClassifier, BERT_BASE
 
@@ -237,6 +240,94 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> dict:
     return result
 
 
+def run_tp(args, rank: int, world: int, local_rank: int) -> dict:
+    """BERT-large, one batch of 16 x 384 tokens per step, all GPUs cooperating on every batch (tensor parallel)."""
+    import torch
+    import torch.distributed as dist
+
+    from splitrpc_b200 import ops
+    from splitrpc_b200.models import BERT_LARGE, BertClassifierTP
+    from splitrpc_b200.parallel import init_distributed
+
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    init_distributed()
+    cfg = CONFIGS[args.config]
+    B, S = cfg["max_batch"], cfg["seq"]
+    model = BertClassifierTP(BERT_LARGE, seq=S, device=local_rank, batch=B)
+    dev = torch.device("cuda", local_rank)
+    warm = max(args.warmup, 3)
+    n_sets = 4
+    ids_host = [torch.randint(0, 30522, (B, S), dtype=torch.int32, generator=torch.Generator().manual_seed(i)).pin_memory()
+                for i in range(n_sets)]
+    ids_dev = torch.zeros((B, S), dtype=torch.int32, device=dev)
+    probs = torch.zeros((B, 2), dtype=torch.float32, device=dev)
+    probs_host = torch.zeros((B, 2), dtype=torch.float32).pin_memory()
+    stream = torch.cuda.Stream(device=dev)
+    with torch.cuda.stream(stream):
+        model.forward(ids_dev, out=probs)  # warm-up outside capture (sets kernel attributes)
+        stream.synchronize()
+        dist.barrier()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            model.forward(ids_dev, out=probs)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    sampler = ClockSampler(local_rank)
+
+    def one_step(i, e2e):
+        if e2e:
+            ids_dev.copy_(ids_host[i % n_sets], non_blocking=True)  # host -> device copy of the step's inputs
+        graph.replay()
+        if e2e:
+            probs_host.copy_(probs, non_blocking=True)              # device -> host read of the result
+
+    results = {}
+    with torch.cuda.stream(stream):
+        for mode in ("device", "e2e"):
+            for i in range(warm):
+                one_step(i, mode == "e2e")
+            stream.synchronize()
+            dist.barrier()
+            if mode == "device":
+                sampler.start()
+            evs = []
+            for i in range(args.steps):
+                if mode == "device":
+                    flush.zero_()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(stream)
+                one_step(i, mode == "e2e")
+                e1.record(stream)
+                evs.append((e0, e1))
+                if mode == "e2e":
+                    stream.synchronize()  # the client waits for the result before it sends the next batch
+            stream.synchronize()
+            dist.barrier()
+            t = torch.tensor([sum(a.elapsed_time(b) for a, b in evs)], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            results[mode] = float(t.item())
+    clocks = sampler.stop()
+    ops.check_status()
+    value = B * args.steps / (results["device"] / 1e3)
+    e2e = B * args.steps / (results["e2e"] / 1e3)
+    res = {
+        "metric": "req/s (tensor-parallel batch serving, device-timed, max over ranks)", "value": round(value, 1),
+        "unit": "req/s", "n_gpus": world, "steps": args.steps, "warmup": warm, "ms_per_step": round(results["device"] / args.steps, 4),
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "impl": "splitrpc_b200",
+        "config": {"model": cfg["model"], "global_batch": B, "seq_len": S, "parallelism": f"tp{world}",
+                   "step": "one batch of 16 sequences through the tensor-parallel CUDA graph on all ranks",
+                   "l2": "256 MiB buffer written between timed iterations", "weights": "random init"},
+        "clocks": clocks,
+        "e2e": {"value": round(e2e, 1), "unit": "req/s", "h2d_bytes_per_step": B * S * 4, "d2h_bytes_per_step": B * 2 * 4,
+                "path": "pinned host ids -> cudaMemcpyAsync -> TP graph on every rank -> probabilities copied back to pinned host",
+                "note": "the batch is handed to the model API directly; the RPC front end serves tensor-parallel groups on rank 0 only"},
+        "gpu_launches": model.kernels_per_forward * args.steps,
+    }
+    dist.barrier()
+    dist.destroy_process_group()
+    return res
+
+
 def run_reference(args) -> dict:
     return {"impl": "reference", "unavailable": "the original server needs DPDK 21.08, gdrcopy, libibverbs/rdmacm, ONNX "
             "Runtime + TensorRT and a spdlog submodule, none of which exist offline on this image; it has no setup.py/pyproject "
@@ -258,7 +349,7 @@ def main():
         if rank == 0:
             print(json.dumps(run_reference(args)), flush=True)
         return
-    res = run_ours(args, rank, world, local_rank)
+    res = run_tp(args, rank, world, local_rank) if args.config == "bert_large_tp" else run_ours(args, rank, world, local_rank)
     if rank == 0:
         print(json.dumps(res), flush=True)
 
