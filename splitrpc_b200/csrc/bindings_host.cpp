@@ -597,7 +597,8 @@ PYBIND11_MODULE(_C, m) {
   py::class_<ClientHolder, std::shared_ptr<ClientHolder>>(m, "Client")
       .def(py::init([](PortHolder port, size_t req_size, size_t resp_size, uint64_t total, uint64_t warmup,
                        const std::string& payload, bool verify, const std::string& exp_name, const std::string& out_dir,
-                       const std::string& uri, int n_payloads, uint64_t seed, uint64_t drain_timeout_ns) {
+                       const std::string& uri, int n_payloads, uint64_t seed, uint64_t drain_timeout_ns,
+                       bool send_by_reference) {
              auto h = std::make_shared<ClientHolder>();
              ClientConfig c;
              c.req_size = req_size;
@@ -611,6 +612,7 @@ PYBIND11_MODULE(_C, m) {
              c.n_payloads = n_payloads;
              c.seed = seed;
              c.drain_timeout_ns = drain_timeout_ns;
+             c.send_by_reference = send_by_reference;
              h->port = port;
              h->client.reset(new P2pRpcAppClient(port.port, c, req_cb_by_name(payload), resp_cb_by_name(payload)));
              h->client->PreProcessRequests();
@@ -619,7 +621,7 @@ PYBIND11_MODULE(_C, m) {
            py::arg("port"), py::arg("req_size") = 1024, py::arg("resp_size") = 1024, py::arg("total") = 100,
            py::arg("warmup") = 10, py::arg("payload") = "echo", py::arg("verify") = false,
            py::arg("exp_name") = "splitrpc", py::arg("out_dir") = ".", py::arg("uri") = "", py::arg("n_payloads") = 16,
-           py::arg("seed") = 12345, py::arg("drain_timeout_ns") = 10000000000ull)
+           py::arg("seed") = 12345, py::arg("drain_timeout_ns") = 10000000000ull, py::arg("send_by_reference") = false)
       .def("run_closed_loop",
            [](ClientHolder& c, int outstanding) {
              py::gil_scoped_release rel;

@@ -52,6 +52,9 @@ void bind_ops(py::module_& m) {
           check(srpc_sg_cast_list(items, scale, shift, n_blocks, (cudaStream_t)stream), "sg_cast_bf16");
         },
         py::arg("items"), py::arg("scale") = 1.0f, py::arg("shift") = 0.0f, py::arg("n_blocks") = 0, py::arg("stream") = 0);
+  m.def("memcpy_async", [](uintptr_t dst, uintptr_t src, size_t n, uintptr_t stream) {
+    check(cudaMemcpyAsync((void*)dst, (const void*)src, n, cudaMemcpyDefault, (cudaStream_t)stream), "memcpy_async");
+  });
   m.def("sg_list_create", &srpc_sg_list_create);
   m.def("sg_list_destroy", &srpc_sg_list_destroy);
   m.def("sg_list_launch",

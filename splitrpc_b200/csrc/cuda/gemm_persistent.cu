@@ -89,8 +89,15 @@ struct TileCoord {
 
 __device__ __forceinline__ TileCoord tile_coord(const TileParams& p, int tile) {
   TileCoord t;
-  t.n_idx = tile % p.tiles_n;  // column tiles of one row block run back to back: A stays in L2
-  t.m_idx = tile / p.tiles_n;
+  // Grouped order: the ~148 tiles in flight at any time cover GROUP_M row blocks x ~18 column blocks, so the A and B
+  // blocks they share are read from DRAM once and then hit in L2.
+  constexpr int GROUP_M = 8;
+  const int per_group = GROUP_M * p.tiles_n;
+  const int g = tile / per_group, in_g = tile - g * per_group;
+  const int m_first = g * GROUP_M;
+  const int gm = (p.tiles_m - m_first) < GROUP_M ? (p.tiles_m - m_first) : GROUP_M;
+  t.m_idx = m_first + in_g % gm;
+  t.n_idx = in_g / gm;
   t.w0 = t.h0 = t.img0 = 0;
   if (p.mode == 1) {
     int tw = t.m_idx % p.tiles_w;

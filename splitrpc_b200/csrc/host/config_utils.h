@@ -135,6 +135,29 @@ static inline void sleepUntil(uint64_t target_ns) {
   }
 }
 
+// Polling loops spin while there is work and back off to short sleeps after a run of empty polls, so that an idle
+// server (or several servers on one host) does not burn a core per thread.  P2P_RPC_IDLE_SPIN sets how many empty
+// polls are tolerated before sleeping (0 = always spin).
+struct IdleBackoff {
+  int limit;
+  int idle = 0;
+  IdleBackoff() : limit(spin_limit()) {}
+  static int spin_limit() {
+    static int v = readEnvInfo<int>("P2P_RPC_IDLE_SPIN", 4000);
+    return v;
+  }
+  void busy() { idle = 0; }
+  void empty() {
+    if (limit > 0 && ++idle > limit) {
+      std::this_thread::sleep_for(std::chrono::microseconds(20));
+    } else {
+#if defined(__x86_64__)
+      __builtin_ia32_pause();
+#endif
+    }
+  }
+};
+
 // ------------------------------------------------------------------ stats
 // Percentile rule of the measurement protocol: element at index round(p*(n-1))
 // of the sorted sample (reference src/utils/stats_utils.h:10-21).

@@ -16,6 +16,7 @@
 #include <thread>
 #include <unordered_map>
 
+#include "p2p_rpc_app.h"
 #include "p2p_rpc_rr.h"
 #include "transport.h"
 
@@ -272,6 +273,7 @@ struct ClientConfig {
   std::string out_dir = ".";
   uint64_t seed = 12345;
   uint64_t drain_timeout_ns = 10000000000ull;  // give up waiting for replies after this long
+  bool send_by_reference = false;  // payload pool in pinned memory, handed to the transport without a host copy
 };
 
 class P2pRpcAppClient {
@@ -280,6 +282,8 @@ class P2pRpcAppClient {
   p2p_rpc_conn_info* conn_;
   std::vector<CallToken> tokens_;
   std::vector<std::vector<uint8_t>> payloads_;
+  std::vector<uint8_t*> payload_ptrs_;   // where each payload lives (own vector, or the pinned pool)
+  uint8_t* pinned_pool_ = nullptr;
   std::vector<std::vector<uint8_t>> resp_bufs_;      // reassembly buffer per token
   std::atomic<uint64_t> n_sent_{0}, n_recv_{0}, n_bad_token_{0}, n_verify_fail_{0}, next_idx_{0};
   std::atomic<bool> exit_flag_{false};
@@ -311,6 +315,8 @@ class P2pRpcAppClient {
         stats_(cfg.exp_name, cfg.out_dir) {}
   ~P2pRpcAppClient() {
     stop_listener();
+    if (pinned_pool_)
+      if (const SrpcDeviceOps* ops = srpc_cuda_ops()) ops->host_free(pinned_pool_);
     release_conn_info(conn_);
   }
   std::string getName() const { return "P2pRpcAppClient"; }
@@ -325,9 +331,25 @@ class P2pRpcAppClient {
   // Builds the request payloads and marks the warm-up calls.
   void PreProcessRequests() {
     payloads_.resize((size_t)cfg_.n_payloads);
+    payload_ptrs_.resize((size_t)cfg_.n_payloads);
+    if (cfg_.send_by_reference) {
+      const SrpcDeviceOps* ops = srpc_cuda_ops();
+      void *h = nullptr, *d = nullptr;
+      size_t stride = (cfg_.req_size + 255) / 256 * 256;
+      if (!ops || ops->host_alloc_mapped(stride * (size_t)cfg_.n_payloads, &h, &d) != 0 || h != d) {
+        srpc_log(SRPC_LOG_WARN, "send_by_reference needs pinned memory with unified addressing; copying instead");
+        if (h) ops->host_free(h);
+        cfg_.send_by_reference = false;
+      } else {
+        pinned_pool_ = (uint8_t*)h;
+        for (int i = 0; i < cfg_.n_payloads; i++) payload_ptrs_[i] = pinned_pool_ + (size_t)i * stride;
+      }
+    }
     for (int i = 0; i < cfg_.n_payloads; i++) {
       payloads_[i].resize(cfg_.req_size);
       req_cb_(payloads_[i].data(), cfg_.req_size, (uint64_t)i);
+      if (cfg_.send_by_reference) std::memcpy(payload_ptrs_[i], payloads_[i].data(), cfg_.req_size);
+      else payload_ptrs_[i] = payloads_[i].data();
     }
     resp_bufs_.resize(tokens_.size());
     for (size_t i = 0; i < tokens_.size(); i++) {
@@ -341,7 +363,7 @@ class P2pRpcAppClient {
   // the transport refused it (receiver arena full); the caller may retry.
   bool SchedRequest(uint64_t idx) {
     CallToken& t = tokens_[idx];
-    const std::vector<uint8_t>& pl = payloads_[t.payload_idx];
+    const uint8_t* pl = payload_ptrs_[t.payload_idx];
     std::vector<p2p_rpc_hdr> hdrs(n_frags_);
     std::vector<const uint8_t*> ptrs(n_frags_);
     std::vector<uint32_t> lens(n_frags_);
@@ -349,13 +371,14 @@ class P2pRpcAppClient {
     for (size_t i = 0; i < n_frags_; i++) {
       size_t len = left < mtu_ ? left : mtu_;
       fill_frag_hdr(&hdrs[i], conn_, (uint64_t)(uintptr_t)&t, (uint16_t)i, (uint16_t)len, false);
-      ptrs[i] = pl.data() + i * mtu_;
+      ptrs[i] = pl + i * mtu_;
       lens[i] = (uint32_t)len;
       left -= len;
     }
     t.dispatchNs = getCurNs();
     t.call_state.store(R_SENT, std::memory_order_release);
-    int rc = port_->tx_copy(hdrs.data(), ptrs.data(), lens.data(), (int)n_frags_);
+    int rc = cfg_.send_by_reference ? port_->tx_ref(hdrs.data(), ptrs.data(), lens.data(), (int)n_frags_)
+                                    : port_->tx_copy(hdrs.data(), ptrs.data(), lens.data(), (int)n_frags_);
     if (rc <= 0) {
       t.call_state.store(R_CREATE, std::memory_order_release);
       return false;
@@ -380,8 +403,11 @@ class P2pRpcAppClient {
   void CompleteReqListener() {
     std::vector<SrpcPkt> pkts(256);
     std::unordered_map<uint64_t, uint32_t> got;  // token -> bytes so far
+    IdleBackoff backoff;
     while (!exit_flag_.load(std::memory_order_acquire)) {
       int n = port_->rx_burst(pkts.data(), (int)pkts.size());
+      if (n > 0) backoff.busy();
+      else backoff.empty();
       for (int i = 0; i < n; i++) {
         SrpcPkt& p = pkts[i];
         size_t idx = 0;

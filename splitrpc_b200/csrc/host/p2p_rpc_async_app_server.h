@@ -200,8 +200,13 @@ class P2pRpcAsyncAppServer {
     P2pRpcAppRrPool* pool = a->app_rr_pool;
     const int n = a->rr_pool_size;
     int ci = 0, si = 0, win = 0;
+    IdleBackoff backoff;
     while (!should_stop()) {
-      if (load_state(pool->get_app_rr(ci)->h_state) != APP_RR_STATUS::RX_COMPLETE) continue;
+      if (load_state(pool->get_app_rr(ci)->h_state) != APP_RR_STATUS::RX_COMPLETE) {
+        backoff.empty();
+        continue;
+      }
+      backoff.busy();
       ci = (ci + 1) % n;
       if (++win < a->app_ctx->curr_batch_size) continue;
       uint64_t t0 = getCurNs();
@@ -224,12 +229,17 @@ class P2pRpcAsyncAppServer {
     P2pRpcAppRrPool* pool = a->app_rr_pool;
     const int n = a->rr_pool_size;
     int ci = 0, si = 0, win = 0;
+    IdleBackoff backoff;
     while (!should_stop()) {
       while (win < max_batch_size && load_state(pool->get_app_rr(ci)->h_state) == APP_RR_STATUS::RX_COMPLETE) {
         win++;
         ci = (ci + 1) % n;
       }
-      if (win == 0) continue;
+      if (win == 0) {
+        backoff.empty();
+        continue;
+      }
+      backoff.busy();
       uint64_t t0 = getCurNs();
       bool ok = do_batch_work_sync(appIdx, si, win);
       for (int i = si; i != ci; i = (i + 1) % n) store_state(pool->get_app_rr(i)->h_state, APP_RR_STATUS::WORK_COMPLETE);
@@ -271,6 +281,7 @@ class P2pRpcAsyncAppServer {
     c->ResetAppRunStatus();
     if (c->device_id < 0) c->wait_budget_ns = 20000000ull;  // CPU device: poll in 20 ms slices
     bool armed = false;
+    IdleBackoff backoff;
     uint64_t t0 = getCurNs();
     while (!should_stop()) {
       if (!armed) {
@@ -284,7 +295,11 @@ class P2pRpcAsyncAppServer {
         pre_launch_work(appIdx, ci, (ci + c->curr_batch_size - 1) % n);
         armed = true;
       }
-      if (!c->IsAppRunComplete()) continue;
+      if (!c->IsAppRunComplete()) {
+        backoff.empty();
+        continue;
+      }
+      backoff.busy();
       int bs = c->curr_batch_size;
       for (int i = 0; i < bs; i++) {
         store_state(pool->get_app_rr(ci)->h_state, APP_RR_STATUS::WORK_COMPLETE);

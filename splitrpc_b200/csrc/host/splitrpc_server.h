@@ -72,8 +72,11 @@ class SplitRpcServer {
   void rx_loop() {
     std::vector<SrpcPkt> pkts(1024);
     uint64_t last_sweep = getCurNs();
+    IdleBackoff backoff;
     while (!quit_.load(std::memory_order_acquire)) {
       int n = port_->rx_burst(pkts.data(), (int)pkts.size());
+      if (n > 0) backoff.busy();
+      else backoff.empty();
       for (int i = 0; i < n; i++) {
         SrpcPkt& p = pkts[i];
         stats_.rx_pkts++;
@@ -163,7 +166,12 @@ class SplitRpcServer {
     std::vector<g_params*> stubs((size_t)burst);
     std::vector<P2pRpcAppRr*> slots((size_t)burst);
     P2pRpcRr* pending = nullptr;  // a ready request that found its replica's ring full
+    IdleBackoff backoff;
+    bool did_work = true;
     while (!quit_.load(std::memory_order_acquire)) {
+      if (did_work) backoff.busy();
+      else backoff.empty();
+      did_work = false;
       // ---- RX half: ready requests -> app ring slots
       int target = -1, nb = 0;
       while (nb < burst) {
@@ -202,6 +210,7 @@ class SplitRpcServer {
         nb++;
       }
       if (nb > 0) {
+        did_work = true;
         Replica& rep = *replicas_[target];
         int rc = rep.engine->gather_batch(rrs.data(), stubs.data(), nb);
         if (rc != 0) stats_.sg_errors++;
@@ -230,6 +239,7 @@ class SplitRpcServer {
           nt++;
         }
         if (nt == 0) continue;
+        did_work = true;
         if (cfg_.zerocopy) {
           send_zerocopy(rep, rrs.data(), slots.data(), nt);
         } else {

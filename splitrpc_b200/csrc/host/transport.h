@@ -126,6 +126,12 @@ class Transport {
   virtual int tx_burst(const SrpcPkt* pkts, int n) = 0;
   // Sends packets whose payload lives anywhere in host memory (client side).
   virtual int tx_copy(const p2p_rpc_hdr* hdrs, const uint8_t* const* payloads, const uint32_t* lens, int n) = 0;
+  // Sends packets whose payloads already sit in memory the receiver's GPU can read (registered, pinned): only
+  // headers and descriptors move, the payload is handed over by reference, like a NIC sending from registered
+  // memory.  The caller keeps the payload unchanged until the reply arrives.  Default: falls back to tx_copy.
+  virtual int tx_ref(const p2p_rpc_hdr* hdrs, const uint8_t* const* payloads, const uint32_t* lens, int n) {
+    return tx_copy(hdrs, payloads, lens, n);
+  }
   virtual const char* name() const = 0;
   // Device-view address of a received payload (identity for host arenas).
   virtual uint8_t* rx_dev_ptr(const SrpcPkt& p) const { return p.payload; }
@@ -154,6 +160,10 @@ class LoopbackLink {
 };
 
 class LoopbackPort : public Transport {
+  static constexpr uint32_t kExternalSlot = 0xFFFFFFFFu;  // packet whose payload is not an arena slot
+  static constexpr uint32_t kExtHdrs = 1u << 16;          // header ring for by-reference packets
+  std::unique_ptr<p2p_rpc_hdr[]> ext_hdrs_{new p2p_rpc_hdr[kExtHdrs]};
+  uint32_t ext_next_ = 0;
   std::unique_ptr<PktArena> rx_arena_, tx_arena_;
   MpmcRing<SrpcPkt> rx_ring_;
   LoopbackPort* peer_ = nullptr;
@@ -261,7 +271,28 @@ class LoopbackPort : public Transport {
     return n;
   }
   void release_rx(const SrpcPkt* pkts, int n) override {
-    for (int i = 0; i < n; i++) rx_arena_->release(pkts[i].slot);
+    for (int i = 0; i < n; i++)
+      if (pkts[i].slot != kExternalSlot) rx_arena_->release(pkts[i].slot);
+  }
+  int tx_ref(const p2p_rpc_hdr* hdrs, const uint8_t* const* payloads, const uint32_t* lens, int n) override {
+    if (!peer_) return 0;
+    std::lock_guard<std::mutex> g(tx_mu_);
+    for (int i = 0; i < n; i++) {
+      SrpcPkt p;
+      p.hdr = &peer_->ext_hdrs_[peer_->ext_next_++ & (kExtHdrs - 1)];
+      std::memcpy(p.hdr, &hdrs[i], RPC_HEADER_LEN);
+      p.payload = const_cast<uint8_t*>(payloads[i]);
+      p.len = lens[i];
+      p.slot = kExternalSlot;
+      std::atomic_thread_fence(std::memory_order_release);
+      if (!peer_->rx_ring_.push(p)) {
+        counters.tx_dropped++;
+        return i;
+      }
+      counters.tx_pkts++;
+      counters.tx_bytes += lens[i];
+    }
+    return n;
   }
   bool alloc_tx(SrpcPkt* out, int n) override {
     uint32_t first = 0;
@@ -298,7 +329,10 @@ class LoopbackPort : public Transport {
     for (int i = 0; i < n; i++) hp[i] = &hdrs[i];
     return send_list(hp.data(), payloads, lens, n);
   }
-  uint8_t* rx_dev_ptr(const SrpcPkt& p) const override { return rx_arena_->to_dev(p.payload); }
+  // Payloads handed over by reference live in pinned memory whose device address equals its host address.
+  uint8_t* rx_dev_ptr(const SrpcPkt& p) const override {
+    return p.slot == kExternalSlot ? p.payload : rx_arena_->to_dev(p.payload);
+  }
   uint8_t* tx_host_ptr(const SrpcPkt& p) const override { return tx_arena_->to_host(p.payload); }
   uint8_t* rx_host_ptr(uint32_t slot) const override { return rx_arena_->host_ptr(slot); }
   const char* name() const override { return "loopback"; }
