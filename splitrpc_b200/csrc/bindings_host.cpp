@@ -324,6 +324,28 @@ PYBIND11_MODULE(_C, m) {
     return out;
   });
 
+  // Multi-tensor pack list of one request: frags = [(addr, len)], tensors = [(batch_base_addr, tensor_bytes)].
+  m.def("pack_list", [](const std::vector<std::pair<uintptr_t, size_t>>& frags,
+                        const std::vector<std::pair<uintptr_t, size_t>>& tensors, int batch_index) {
+    auto bufs = std::make_unique<p2p_bufs>();
+    auto skb = std::make_unique<p2p_sk_buf>();
+    bufs->num_items = (uint16_t)frags.size();
+    for (size_t i = 0; i < frags.size(); i++) {
+      bufs->burst_items[i] = frags[i].first;
+      bufs->item_size[i] = frags[i].second;
+    }
+    g_params_v2 stub{};
+    if (tensors.size() > MAX_NUM_TENSORS) throw std::invalid_argument("at most 4 tensors per request");
+    for (size_t k = 0; k < tensors.size(); k++) {
+      stub.inputs[k] = tensors[k].first;
+      stub.input_tensor_size[k] = tensors[k].second;
+    }
+    gather_skbs_v2(skb.get(), bufs.get(), &stub, (int)tensors.size(), batch_index);
+    std::vector<std::tuple<uintptr_t, uintptr_t, size_t>> out;
+    for (size_t i = 0; i < skb->num_items; i++) out.emplace_back(skb->i_buf[i], skb->o_buf[i], skb->len[i]);
+    return out;
+  });
+
   // ---- reassembly harness: feeds (header, payload) pairs through the pool and the CPU engine
   struct Reassembler {
     P2pRpcRRPool pool;

@@ -9,6 +9,7 @@
 #include "cuda/gemm_tp.h"
 #include "cuda/nn_kernels.h"
 #include "cuda/ops_api.h"
+#include "cuda/parity_kernels.h"
 
 namespace py = pybind11;
 
@@ -155,6 +156,10 @@ void bind_ops(py::module_& m) {
           r.eps = eps;
           check(srpc_layernorm_reduce(r, rows, (uint32_t*)status, (cudaStream_t)stream), "layernorm_reduce");
         });
+
+  m.def("swap_hdrs", [](uintptr_t hdr_ptrs, uintptr_t hdrs_contig, int n, bool clear_sockperf, uintptr_t stream) {
+    check(srpc_swap_hdrs((void* const*)hdr_ptrs, (void*)hdrs_contig, n, clear_sockperf ? 1 : 0, (cudaStream_t)stream), "swap_hdrs");
+  });
 
   // ---- memory-bound layers
   m.def("stem_im2col",

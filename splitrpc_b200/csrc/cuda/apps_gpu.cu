@@ -21,6 +21,7 @@
 #include "../host/apps_cpu.h"
 #include "../host/p2p_rpc_app.h"
 #include "apps_gpu.h"
+#include "parity_kernels.h"
 #include "ptx.cuh"
 
 namespace {
@@ -36,6 +37,8 @@ struct GpuAppState {
   uint32_t* d_pt_status = nullptr;      // resident kernel: 0 running, 1 left
   uint32_t* h_pt_status = nullptr;
   uint64_t idle_ns = 200000000ull;
+  float* d_scratch = nullptr;           // lstm: inter-layer hand-off buffer
+  int lstm_clusters = 16;
 };
 
 GpuAppState* st(AppCtx* c) { return static_cast<GpuAppState*>(c->app_ctx_internal); }
@@ -283,6 +286,11 @@ void launch_kernels(AppCtx* c, int batch) {
     mm_kernel<<<batch, 256, (size_t)s->dim * s->dim * 4, q>>>(c->d_stub, s->req_size, s->resp_size, s->dim, batch);
   } else if (s->name == "lenet5") {
     lenet5_kernel<<<batch, 256, 0, q>>>(c->d_stub, lenet_w(s), batch);
+  } else if (s->name == "lenet_ref") {
+    const float* b = s->d_weights;
+    srpc_lenet_ref(c->d_stub, nullptr, nullptr, b + s->w_off[0], b + s->w_off[1], b + s->w_off[2], b + s->w_off[3], batch, q);
+  } else if (s->name == "lstm") {
+    srpc_lstm(c->d_stub, nullptr, nullptr, s->d_weights, s->d_scratch, s->lstm_clusters, batch, 0.0f, q);
   }
 }
 
@@ -301,6 +309,9 @@ int gpu_app_init(AppCtx* c) {
     if (!s->dim) s->dim = mm_dim_from_req(s->req_size);
     if (s->dim > 128) return 0;
     cudaFuncSetAttribute(mm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 128 * 4);
+  }
+  if (s->name == "lstm") {
+    if (cudaMalloc(&s->d_scratch, srpc_lstm_scratch_bytes(s->lstm_clusters)) != cudaSuccess) return 0;
   }
   if (c->launch_type == 3) {
     cudaHostAlloc(&s->h_pt_status, 4, cudaHostAllocMapped);
@@ -361,6 +372,7 @@ int gpu_app_cleanup(AppCtx* c) {
   }
   for (auto& kv : s->graphs) cudaGraphExecDestroy(kv.second);
   if (s->d_weights) cudaFree(s->d_weights);
+  if (s->d_scratch) cudaFree(s->d_scratch);
   delete s;
   c->app_ctx_internal = nullptr;
   return 1;
@@ -374,14 +386,15 @@ GpuAppHandle srpc_make_gpu_app(const char* name, int device_id, size_t req_size,
   int n = 0;
   if (cudaGetDeviceCount(&n) != cudaSuccess || device_id >= n) return h;
   std::string nm(name);
-  if (nm != "echo" && nm != "vec_add" && nm != "matmul" && nm != "lenet5") return h;
+  if (nm != "echo" && nm != "vec_add" && nm != "matmul" && nm != "lenet5" && nm != "lenet_ref" && nm != "lstm") return h;
   GpuAppState* s = new GpuAppState;
   s->name = nm;
   s->req_size = req_size;
   s->resp_size = resp_size;
   s->idle_ns = (uint64_t)readEnvInfo<uint64_t>("P2P_RPC_APP_IDLE_MS", 200) * 1000000ull;
-  if (nm == "lenet5") {
-    if (weights.size() != 10) {
+  const size_t want = nm == "lenet5" ? 10 : (nm == "lenet_ref" ? 4 : (nm == "lstm" ? 24 : 0));
+  if (want) {
+    if (weights.size() != want) {
       delete s;
       return h;
     }

@@ -1,0 +1,223 @@
+// Remaining device-side pieces of the original system, rebuilt for sm_100a:
+//   swap_hdrs        reply-header construction on the GPU for headers that live in
+//                    GPU-visible memory (reference src/transport/g_udp_handler.cu:96-178)
+//   lenet_ref        the 20/50/10 LeNet of reference src/apps/lenet/lenet_vanilla.cu:17-192
+//                    (uint8 pixels, (x-127)/128, conv 5x5 pad 1, tanh, 2x2 max pool, dense, softmax)
+//                    as one kernel per batch instead of twelve launches per image
+//   lstm_wavefront   the 8-layer x 8-step stacked LSTM (hidden 256) of reference
+//                    src/apps/nnfusion_lstm/nnfusion_rt.cu:13870-13877,1213-1283 as one
+//                    cluster launch per batch: the 8 blocks of a cluster own one layer
+//                    each and advance along anti-diagonals with a cluster barrier per step
+//                    (32 launches per inference in the original)
+#include <cooperative_groups.h>
+#include <cuda_runtime.h>
+#include <math.h>
+
+#include "../host/p2p_rpc.h"
+#include "../host/p2p_rpc_app.h"
+#include "parity_kernels.h"
+
+namespace cg = cooperative_groups;
+
+namespace {
+
+// ------------------------------------------------------------------ header swap
+__global__ void swap_hdrs_kernel(p2p_rpc_hdr* const* hdrs, int n, int clear_sockperf) {
+  int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  p2p_rpc_hdr* h = hdrs[i];
+  swap_eth_hdr(h);
+  if (clear_sockperf) set_sockperf_header(h);
+  add_udp_cksum(h);
+}
+
+__global__ void swap_hdrs_contig_kernel(p2p_rpc_hdr* hdrs, int n, int clear_sockperf) {
+  int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  p2p_rpc_hdr* h = hdrs + i;
+  swap_eth_hdr(h);
+  if (clear_sockperf) set_sockperf_header(h);
+  add_udp_cksum(h);
+}
+
+// ------------------------------------------------------------------ reference-format LeNet
+struct LenetRefW {
+  const float *c1, *c2, *fc, *fb;
+};
+
+__global__ void __launch_bounds__(256) lenet_ref_kernel(const g_params* stub, const uint8_t* direct_in, float* direct_out,
+                                                        LenetRefW w, int batch) {
+  __shared__ float x[784];
+  __shared__ float p1[20 * 13 * 13];
+  __shared__ float p2[50 * 5 * 5];
+  __shared__ float lg[10];
+  __shared__ float wc1[500];
+  const int t = threadIdx.x;
+  for (int i = t; i < 500; i += 256) wc1[i] = w.c1[i];
+  const uint8_t* in_base = direct_in ? direct_in : stub->req;
+  float* out_base = direct_out ? direct_out : reinterpret_cast<float*>(stub->resp);
+  for (int b = blockIdx.x; b < batch; b += gridDim.x) {
+    const uint8_t* in = in_base + (size_t)b * 784;
+    float* out = out_base + (size_t)b * 10;
+    __syncthreads();
+    for (int i = t; i < 784; i += 256) x[i] = ((float)in[i] - 127.f) / 128.f;
+    __syncthreads();
+    // conv1 (1->20, 5x5, pad 1: 28->26) + tanh + 2x2 max pool (->13)
+    for (int o = t; o < 20 * 169; o += 256) {
+      const int k = o / 169, r = (o % 169) / 13, c = o % 13;
+      float best = -1e30f;
+      for (int dy = 0; dy < 2; dy++)
+        for (int dx = 0; dx < 2; dx++) {
+          const int oh = 2 * r + dy, ow = 2 * c + dx;
+          float acc = 0.f;
+          for (int i = 0; i < 5; i++) {
+            const int ih = oh + i - 1;
+            if (ih < 0 || ih >= 28) continue;
+            for (int j = 0; j < 5; j++) {
+              const int iw = ow + j - 1;
+              if (iw < 0 || iw >= 28) continue;
+              acc += x[ih * 28 + iw] * wc1[k * 25 + i * 5 + j];
+            }
+          }
+          best = fmaxf(best, tanhf(acc));
+        }
+      p1[o] = best;
+    }
+    __syncthreads();
+    // conv2 (20->50, 5x5, pad 1: 13->11) + tanh + max pool (->5)
+    for (int o = t; o < 50 * 25; o += 256) {
+      const int k = o / 25, r = (o % 25) / 5, c = o % 5;
+      float best = -1e30f;
+      for (int dy = 0; dy < 2; dy++)
+        for (int dx = 0; dx < 2; dx++) {
+          const int oh = 2 * r + dy, ow = 2 * c + dx;
+          float acc = 0.f;
+          for (int ch = 0; ch < 20; ch++)
+            for (int i = 0; i < 5; i++) {
+              const int ih = oh + i - 1;
+              if (ih < 0 || ih >= 13) continue;
+              for (int j = 0; j < 5; j++) {
+                const int iw = ow + j - 1;
+                if (iw < 0 || iw >= 13) continue;
+                acc += p1[ch * 169 + ih * 13 + iw] * __ldg(w.c2 + ((k * 20 + ch) * 5 + i) * 5 + j);
+              }
+            }
+          best = fmaxf(best, tanhf(acc));
+        }
+      p2[o] = best;
+    }
+    __syncthreads();
+    for (int o = t / 32; o < 10; o += 8) {
+      float acc = 0.f;
+      for (int i = t % 32; i < 1250; i += 32) acc += p2[i] * __ldg(w.fc + o * 1250 + i);
+      for (int s = 16; s; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
+      if (t % 32 == 0) lg[o] = acc + w.fb[o];
+    }
+    __syncthreads();
+    if (t == 0) {
+      float m = lg[0];
+      for (int i = 1; i < 10; i++) m = fmaxf(m, lg[i]);
+      float e[10], s = 0.f;
+      for (int i = 0; i < 10; i++) {
+        e[i] = expf(lg[i] - m);
+        s += e[i];
+      }
+      for (int i = 0; i < 10; i++) out[i] = e[i] / s;
+    }
+  }
+}
+
+// ------------------------------------------------------------------ LSTM wavefront
+constexpr int LH = 256, LLAYERS = 8, LSTEPS = 8;
+
+__device__ __forceinline__ float sigmoidf_(float v) { return 1.f / (1.f + __expf(-v)); }
+
+// One cluster (8 blocks) per request; block l owns layer l.  At wave w block l computes cell (l, t = w - l):
+//   gates = W_l . in + U_l . h_prev + b_l   (in = request step t for layer 0, else h of layer l-1 at step t)
+// Layer outputs cross blocks through a small global scratch [request][layer][step][256]; the cluster barrier
+// between waves orders the writes of wave w before the reads of wave w+1.
+__global__ void __cluster_dims__(LLAYERS, 1, 1) __launch_bounds__(1024)
+lstm_wavefront_kernel(const g_params* stub, const float* direct_in, float* direct_out, const float* __restrict__ weights,
+                      float* __restrict__ scratch, int batch, float forget_bias) {
+  cg::cluster_group cluster = cg::this_cluster();
+  const int l = (int)cluster.block_rank();
+  __shared__ float s_in[LH], s_h[LH], s_c[LH], s_g[4 * LH];
+  const int t = threadIdx.x;
+  const size_t per_layer = (size_t)8 * LH * LH + 4 * LH;
+  const float* W = weights + (size_t)l * per_layer;
+  const float* U = W + (size_t)4 * LH * LH;
+  const float* B = U + (size_t)4 * LH * LH;
+  const int n_clusters = gridDim.x / LLAYERS;
+  const float* in_base = direct_in ? direct_in : reinterpret_cast<const float*>(stub->req);
+  float* out_base = direct_out ? direct_out : reinterpret_cast<float*>(stub->resp);
+  for (int req = blockIdx.x / LLAYERS; req < batch; req += n_clusters) {
+    const float* x = in_base + (size_t)req * LSTEPS * LH;
+    float* y = out_base + (size_t)req * LH;
+    float* sc = scratch + (size_t)(blockIdx.x / LLAYERS) * LLAYERS * LSTEPS * LH;
+    if (t < LH) {
+      s_h[t] = 0.f;
+      s_c[t] = 0.f;
+    }
+    __syncthreads();
+    for (int w = 0; w < LLAYERS + LSTEPS - 1; w++) {
+      const int step = w - l;
+      if (step >= 0 && step < LSTEPS) {
+        if (t < LH) s_in[t] = (l == 0) ? x[step * LH + t] : sc[((l - 1) * LSTEPS + step) * LH + t];
+        __syncthreads();
+        // 1024 threads = 4 gates x 256 outputs; each thread one dot product of length 512
+        {
+          const int g = t >> 8, o = t & 255;
+          const float4* wr = reinterpret_cast<const float4*>(W + ((size_t)g * LH + o) * LH);
+          const float4* ur = reinterpret_cast<const float4*>(U + ((size_t)g * LH + o) * LH);
+          float acc = B[g * LH + o];
+#pragma unroll 4
+          for (int k = 0; k < LH / 4; k++) {
+            const float4 a = __ldg(wr + k), b = __ldg(ur + k);
+            acc += a.x * s_in[4 * k] + a.y * s_in[4 * k + 1] + a.z * s_in[4 * k + 2] + a.w * s_in[4 * k + 3];
+            acc += b.x * s_h[4 * k] + b.y * s_h[4 * k + 1] + b.z * s_h[4 * k + 2] + b.w * s_h[4 * k + 3];
+          }
+          s_g[t] = acc;
+        }
+        __syncthreads();
+        if (t < LH) {
+          const float ig = s_g[t], gg = s_g[LH + t], fg = s_g[2 * LH + t], og = s_g[3 * LH + t];
+          const float c = sigmoidf_(fg + forget_bias) * s_c[t] + sigmoidf_(ig) * tanhf(gg);
+          const float h = tanhf(c) * sigmoidf_(og);
+          s_c[t] = c;
+          s_h[t] = h;
+          sc[(l * LSTEPS + step) * LH + t] = h;
+          if (l == LLAYERS - 1 && step == LSTEPS - 1) y[t] = h;
+        }
+        __syncthreads();
+      }
+      cluster.sync();
+    }
+  }
+}
+
+}  // namespace
+
+cudaError_t srpc_swap_hdrs(void* const* d_hdr_ptrs, void* d_hdrs_contig, int n, int clear_sockperf, cudaStream_t s) {
+  if (n <= 0) return cudaSuccess;
+  if (d_hdr_ptrs) swap_hdrs_kernel<<<(n + 255) / 256, 256, 0, s>>>((p2p_rpc_hdr* const*)d_hdr_ptrs, n, clear_sockperf);
+  else swap_hdrs_contig_kernel<<<(n + 255) / 256, 256, 0, s>>>((p2p_rpc_hdr*)d_hdrs_contig, n, clear_sockperf);
+  return cudaGetLastError();
+}
+
+cudaError_t srpc_lenet_ref(const void* d_stub, const void* direct_in, float* direct_out, const float* c1, const float* c2,
+                           const float* fc, const float* fb, int batch, cudaStream_t s) {
+  LenetRefW w{c1, c2, fc, fb};
+  lenet_ref_kernel<<<batch, 256, 0, s>>>((const g_params*)d_stub, (const uint8_t*)direct_in, direct_out, w, batch);
+  return cudaGetLastError();
+}
+
+size_t srpc_lstm_scratch_bytes(int max_clusters) { return (size_t)max_clusters * LLAYERS * LSTEPS * LH * sizeof(float); }
+
+cudaError_t srpc_lstm(const void* d_stub, const float* direct_in, float* direct_out, const float* weights, float* scratch,
+                      int max_clusters, int batch, float forget_bias, cudaStream_t s) {
+  int clusters = batch < max_clusters ? batch : max_clusters;
+  if (clusters < 1) return cudaSuccess;
+  lstm_wavefront_kernel<<<clusters * LLAYERS, 1024, 0, s>>>((const g_params*)d_stub, direct_in, direct_out, weights, scratch,
+                                                           batch, forget_bias);
+  return cudaGetLastError();
+}

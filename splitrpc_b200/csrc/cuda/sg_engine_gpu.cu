@@ -207,6 +207,12 @@ class P2pRpcSgGpuEngine : public P2pRpcSgEngine {
     PROF_STOP(Scatter);
     return rc;
   }
+  int copy_list(const p2p_sk_buf* skb) override {
+    cudaSetDevice(device_id);
+    uint32_t ni = 0;
+    if (!append(skb, &ni)) return -4;
+    return submit(ni);
+  }
   const char* name() const override { return "gpu"; }
 };
 

@@ -59,6 +59,49 @@ static inline void scatter_skbs(p2p_sk_buf* skb, const p2p_bufs* frags, uint8_t*
   skb->num_items = n;
 }
 
+// Multi-tensor gather list.  A request is the concatenation of n_tensors tensors of sizes
+// stub->input_tensor_size[k]; request number `batch_index` of a batch must land at
+// stub->inputs[k] + batch_index * size[k], so that every input tensor of the batch is contiguous by itself
+// (the layout g_params_v2 describes, reference src/p2p_rpc_app_stub.h:7-20, which the original never fills in:
+// it batches by treating consecutive ring slots as one tensor, which is only right for single-input models).
+// Fragments and tensor boundaries are walked together; adjacent pieces are merged.
+static inline void gather_skbs_v2(p2p_sk_buf* skb, const p2p_bufs* frags, const g_params_v2* stub, int n_tensors,
+                                  int batch_index) {
+  size_t n = 0;
+  int k = 0;
+  size_t t_off = 0;  // bytes of tensor k already placed
+  uintptr_t run_src_end = 0, run_dst_end = 0;
+  for (size_t i = 0; i < frags->num_items && k < n_tensors; i++) {
+    uintptr_t src = frags->burst_items[i];
+    size_t left = frags->item_size[i];
+    while (left > 0 && k < n_tensors) {
+      size_t tsz = stub->input_tensor_size[k];
+      size_t take = tsz - t_off < left ? tsz - t_off : left;
+      uintptr_t dst = stub->inputs[k] + (uintptr_t)batch_index * tsz + t_off;
+      if (take > 0) {
+        if (n > 0 && src == run_src_end && dst == run_dst_end) {
+          skb->len[n - 1] += take;
+        } else if (n < MAX_BI_SIZE) {
+          skb->i_buf[n] = src;
+          skb->o_buf[n] = dst;
+          skb->len[n] = take;
+          n++;
+        }
+        run_src_end = src + take;
+        run_dst_end = dst + take;
+      }
+      src += take;
+      left -= take;
+      t_off += take;
+      if (t_off == tsz) {
+        k++;
+        t_off = 0;
+      }
+    }
+  }
+  skb->num_items = n;
+}
+
 struct SgCounters {
   uint64_t gathers = 0, scatters = 0, items = 0, bytes = 0, timeouts = 0;
 };
@@ -99,6 +142,17 @@ class P2pRpcSgEngine {
     int rc = 0;
     for (int i = 0; i < n; i++) rc |= scatter(rrs[i], stubs[i]);
     return rc;
+  }
+  // Executes an already built copy list.  Engines that cannot copy (zero copy) return -1.
+  virtual int copy_list(const p2p_sk_buf* skb) {
+    (void)skb;
+    return -1;
+  }
+  // Multi-tensor gather of one request into slot `batch_index` of the per-tensor batch buffers.
+  int gather_v2(P2pRpcRr* rr, const g_params_v2* stub, int n_tensors, int batch_index) {
+    gather_skbs_v2(rr->payload_sk_bufs, rr->payload_bufs, stub, n_tensors, batch_index);
+    counters.gathers++;
+    return copy_list(rr->payload_sk_bufs);
   }
   virtual const char* name() const = 0;
 };
@@ -157,6 +211,7 @@ class P2pRpcSgCpuEngine : public P2pRpcSgEngine {
     PROF_STOP(Scatter);
     return rc;
   }
+  int copy_list(const p2p_sk_buf* skb) override { return run(skb); }
   const char* name() const override { return "cpu"; }
 };
 

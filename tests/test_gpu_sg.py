@@ -159,3 +159,50 @@ def test_local_bench_gpu(C, torch_cuda):
     app = C.make_app("vec_add", 0, 1024, 1024, [], 64, 1, 1, "gpu", 2)
     ns, outs = C.local_bench(app, 200, 1)
     assert len(ns) == 200
+
+
+def test_gpu_header_swap_matches_host(C, torch_cuda):
+    torch = torch_cuda
+    uri = "b8:ce:f6:cc:6a:53,192.168.25.2,50052,b8:ce:f6:cc:6a:52,192.168.25.1,50051"
+    tmpl = C.client_conn_template(uri)
+    hdrs = [C.build_fragments(tmpl, 1000 + i, bytes(100 + i), 1024)[0][0] for i in range(300)]
+    dev = torch.tensor(np.frombuffer(b"".join(hdrs), dtype=np.uint8).copy(), device="cuda")
+    C.swap_hdrs(0, dev.data_ptr(), 300, False, 0)
+    torch.cuda.synchronize()
+    got = dev.cpu().numpy().tobytes()
+    for i in (0, 77, 299):
+        assert got[i * 64:(i + 1) * 64] == C.swap_header(hdrs[i])
+
+
+def test_gpu_lenet_ref_and_lstm_match_cpu_oracles(C, torch_cuda, mtu8k):
+    rng = np.random.default_rng(3)
+    w = [(rng.standard_normal(s) * 0.1).astype(np.float32) for s in [(20, 1, 5, 5), (50, 20, 5, 5), (10, 1250), (10,)]]
+    outs = {}
+    for dev in (-1, 0):
+        sp, cp = C.make_loopback_pair(8192, 512, "pinned" if dev >= 0 else "malloc")
+        app = C.make_app("lenet_ref", dev, 784, 40, w, 64, 1, 4)
+        srv = C.Server(sp, req_size=784, resp_size=40, server_mode=2, max_batch=4)
+        srv.add_replica(app)
+        srv.start()
+        cli = C.Client(cp, req_size=784, resp_size=40, total=40, warmup=0, payload="echo", verify=True)
+        assert cli.run_closed_loop(4) and cli.received == 40
+        srv.stop()
+        outs[dev] = np.frombuffer(cli.response(7), dtype=np.float32).copy()
+    np.testing.assert_allclose(outs[0], outs[-1], rtol=1e-3, atol=1e-5)
+    H = 256
+    lw = []
+    for _ in range(8):
+        lw += [(rng.standard_normal((4, H, H)) * 0.05).astype(np.float32), (rng.standard_normal((4, H, H)) * 0.05).astype(np.float32),
+               (rng.standard_normal((4, H)) * 0.1).astype(np.float32)]
+    sp, cp = C.make_loopback_pair(8192, 512, "pinned")
+    app = C.make_app("lstm", 0, 8192, 1024, lw, 64, 1, 4)
+    srv = C.Server(sp, req_size=8192, resp_size=1024, server_mode=2, max_batch=4)
+    srv.add_replica(app)
+    srv.start()
+    cli = C.Client(cp, req_size=8192, resp_size=1024, total=24, warmup=0, payload="uniform", verify=True)
+    assert cli.run_closed_loop(4) and cli.received == 24
+    srv.stop()
+    x = np.frombuffer(cli.payload(3), dtype=np.float32)
+    ref = C.cpu_lstm(lw, x, 8, 8, H)
+    got = np.frombuffer(cli.response(3), dtype=np.float32)
+    np.testing.assert_allclose(got, ref, rtol=1e-3, atol=1e-4)

@@ -116,3 +116,26 @@ def test_percentile_rule(C):
     assert C.percentile(v, 0.5) == 51 and C.percentile(v, 0.99) == 100 and C.percentile(v, 0.999) == 101
     assert C.percentile([], 0.5) == 0.0
     assert abs(C.mean([1, 2, 3, 4]) - 2.5) < 1e-12
+
+
+def test_multi_tensor_pack_list(C):
+    """BERT-SQuAD style request: 4 tensors (8 B + 3 x 2048 B) in 1 KB fragments, packed into per-tensor batch buffers."""
+    import ctypes
+
+    sizes = [8, 2048, 2048, 2048]
+    req = np.arange(sum(sizes), dtype=np.uint32).astype(np.uint8)  # 6152 bytes with a recognisable pattern
+    frag_bufs = [np.ascontiguousarray(req[o:o + 1024]) for o in range(0, len(req), 1024)]
+    frags = [(b.ctypes.data, len(b)) for b in frag_bufs]
+    batch = 3
+    outs = [np.zeros(batch * s, dtype=np.uint8) for s in sizes]
+    tensors = [(o.ctypes.data, s) for o, s in zip(outs, sizes)]
+    for bi in range(batch):
+        lst = C.pack_list(frags, tensors, bi)
+        assert len(lst) <= len(frags) + len(sizes)
+        for src, dst, ln in lst:
+            ctypes.memmove(dst, src, ln)
+    off = 0
+    for o, s in zip(outs, sizes):
+        for bi in range(batch):
+            assert np.array_equal(o[bi * s:(bi + 1) * s], req[off:off + s])
+        off += s
