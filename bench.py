@@ -172,7 +172,8 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> dict:
 
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     model = build_model(args.config, local_rank)
-    srv = ModelServer(model, device=local_rank, max_batch=nb, server_mode=2, copy_type=2, outstanding=2 * nb)
+    outstanding = 3 * nb  # closed-loop depth: one batch running, one being gathered, one in the clients' hands
+    srv = ModelServer(model, device=local_rank, max_batch=nb, server_mode=2, copy_type=2, outstanding=outstanding)
 
     def barrier():
         if dist:
@@ -201,9 +202,9 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> dict:
     # Requests are sent by reference: the payload pool sits in pinned, GPU-mapped host memory (as a NIC's registered
     # buffers would) and only headers + descriptors cross the emulated wire; the GPU pulls every fragment of every
     # request out of that host memory each step.
-    cli = srv.client(total=n_req + n_warm, warmup=n_warm, payload=cfg["payload"], n_payloads=2 * nb, send_by_reference=True)
+    cli = srv.client(total=n_req + n_warm, warmup=n_warm, payload=cfg["payload"], n_payloads=outstanding, send_by_reference=True)
     barrier()
-    ok = cli.run_closed_loop(2 * nb)
+    ok = cli.run_closed_loop(outstanding)
     st = cli.post_process()
     clocks = sampler.stop()
     ws = srv.server.worker_stats(0)
@@ -234,7 +235,7 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> dict:
         "clocks": clocks,
         "e2e": {"value": round(e2e_total, 1), "unit": "req/s", "h2d_bytes_per_step": nb * srv.req_size,
                 "d2h_bytes_per_step": nb * srv.resp_size, "p50_us": round(p50, 1), "p99_us": round(p99, 1),
-                "mean_batch": round(mean_bs, 2), "requests": n_req, "outstanding": 2 * nb,
+                "mean_batch": round(mean_bs, 2), "requests": n_req, "outstanding": outstanding,
                 "path": "loadgen (fragments in pinned host memory, sent by reference) -> loopback NIC -> native server "
                         "(reassembly, steering, dynamic batching) -> SG kernel pulls fragments over PCIe -> CUDA graph -> "
                         "SG kernel writes responses to the pinned transmit arena -> client"},

@@ -60,6 +60,8 @@ __device__ __forceinline__ bool named_bar_all(int id, int count, bool pred) {
 
 // Bounded wait until *flag >= epoch (flags only ever grow).
 __device__ __forceinline__ bool wait_flag_gpu(const uint32_t* flag, uint32_t epoch) {
+  for (int i = 0; i < 64; i++)  // fast path: no timer read when the flag is (almost) there
+    if ((int32_t)(ptx::ld_acquire_gpu(flag) - epoch) >= 0) return true;
   const uint64_t t0 = ptx::globaltimer_ns();
   for (;;) {
     for (int i = 0; i < 32; i++) {
@@ -70,6 +72,8 @@ __device__ __forceinline__ bool wait_flag_gpu(const uint32_t* flag, uint32_t epo
   }
 }
 __device__ __forceinline__ bool wait_flag_sys(const uint32_t* flag, uint32_t epoch) {
+  for (int i = 0; i < 16; i++)
+    if ((int32_t)(ptx::ld_acquire_sys(flag) - epoch) >= 0) return true;
   const uint64_t t0 = ptx::globaltimer_ns();
   for (;;) {
     for (int i = 0; i < 32; i++) {

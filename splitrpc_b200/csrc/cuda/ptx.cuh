@@ -84,19 +84,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait: gives up after SRPC_MBAR_WAIT_NS of wall time (checked every 64
-// polls), far beyond any healthy wait inside a kernel.
-#ifndef SRPC_MBAR_WAIT_NS
-#define SRPC_MBAR_WAIT_NS 1000000000ull
+// Bounded wait: gives up after SRPC_MBAR_WAIT_CYCLES SM clock cycles (about two seconds), far beyond any healthy
+// wait inside a kernel.  The bound uses the SM-local cycle counter, which costs a few cycles to read; the global
+// nanosecond timer is far slower to read and would sit on the critical path of every producer/consumer hand-off.
+#ifndef SRPC_MBAR_WAIT_CYCLES
+#define SRPC_MBAR_WAIT_CYCLES 4000000000ll
 #endif
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t t0 = globaltimer_ns();
+#pragma unroll 1
+  for (int i = 0; i < 1024; i++)
+    if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
   for (;;) {
 #pragma unroll 1
-    for (int i = 0; i < 64; i++)
+    for (int i = 0; i < 256; i++)
       if (mbar_try_wait(bar, parity)) return true;
-    if (globaltimer_ns() - t0 > SRPC_MBAR_WAIT_NS) return false;
+    if (clock64() - t0 > SRPC_MBAR_WAIT_CYCLES) return false;
   }
 }
 
