@@ -229,6 +229,58 @@ __global__ void __launch_bounds__(256) layernorm_rows(const __nv_bfloat16* __res
     y[row * hidden + i] = __float2bfloat16((v[cnt] - mean) * rstd * gamma[i] + beta[i]);
 }
 
+// Warp-per-row LayerNorm for hidden sizes that are multiples of 256 (up to 2048): each lane owns hidden/32 values as
+// 16-byte vectors, the row never leaves registers, and both reductions are warp shuffles.
+template <int VPL>  // uint4 vectors per lane: hidden = VPL * 256
+__global__ void __launch_bounds__(256) layernorm_rows_warp(const __nv_bfloat16* __restrict__ x,
+                                                           const __nv_bfloat16* __restrict__ residual,
+                                                           const float* __restrict__ gamma, const float* __restrict__ beta,
+                                                           __nv_bfloat16* __restrict__ y, int rows, float eps) {
+  constexpr int HIDDEN = VPL * 256;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row = blockIdx.x * 8 + warp;
+  if (row >= rows) return;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * HIDDEN);
+  const uint4* rr = residual ? reinterpret_cast<const uint4*>(residual + (size_t)row * HIDDEN) : nullptr;
+  float v[VPL * 8];
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < VPL; i++) {
+    uint4 q = xr[i * 32 + lane];
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+    uint4 q2 = rr ? rr[i * 32 + lane] : make_uint4(0u, 0u, 0u, 0u);
+    const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&q2);
+#pragma unroll
+    for (int t = 0; t < 4; t++) {
+      float2 f = __bfloat1622float2(h[t]), g = __bfloat1622float2(h2[t]);
+      v[i * 8 + 2 * t] = f.x + g.x;
+      v[i * 8 + 2 * t + 1] = f.y + g.y;
+      s += v[i * 8 + 2 * t] + v[i * 8 + 2 * t + 1];
+    }
+  }
+  const float mean = warp_sum(s) * (1.f / HIDDEN);
+  float q = 0.f;
+#pragma unroll
+  for (int k = 0; k < VPL * 8; k++) q += (v[k] - mean) * (v[k] - mean);
+  const float rstd = rsqrtf(warp_sum(q) * (1.f / HIDDEN) + eps);
+  uint4* yr = reinterpret_cast<uint4*>(y + (size_t)row * HIDDEN);
+#pragma unroll
+  for (int i = 0; i < VPL; i++) {
+    const int c0 = (i * 32 + lane) * 8;
+    const float4 g0 = __ldg(reinterpret_cast<const float4*>(gamma + c0)), g1 = __ldg(reinterpret_cast<const float4*>(gamma + c0 + 4));
+    const float4 b0 = __ldg(reinterpret_cast<const float4*>(beta + c0)), b1 = __ldg(reinterpret_cast<const float4*>(beta + c0 + 4));
+    const float gg[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+    const float bb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+    uint4 o;
+    __nv_bfloat162* ho = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int t = 0; t < 4; t++)
+      ho[t] = __floats2bfloat162_rn((v[i * 8 + 2 * t] - mean) * rstd * gg[2 * t] + bb[2 * t],
+                                    (v[i * 8 + 2 * t + 1] - mean) * rstd * gg[2 * t + 1] + bb[2 * t + 1]);
+    yr[i * 32 + lane] = o;
+  }
+}
+
 // ------------------------------------------------------------------ BERT embedding
 // Request = seq int32 token ids per sequence.  y[token] = LN(word[id] + pos[t] + type[0]).
 // Reads ids through the stub (ring window) or from `direct_ids`.
@@ -368,8 +420,15 @@ cudaError_t nn_softmax_response(const float* logits, int rows, int n, int ld, co
 cudaError_t nn_layernorm(const void* x, const void* residual, const float* gamma, const float* beta, void* y, int rows,
                          int hidden, float eps, cudaStream_t s) {
   if (hidden > 2048) return cudaErrorInvalidValue;
-  layernorm_rows<<<rows, 256, 0, s>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)residual, gamma, beta,
-                                      (__nv_bfloat16*)y, hidden, eps);
+  const bool aligned = (((uintptr_t)x | (uintptr_t)y | (uintptr_t)residual | (uintptr_t)gamma | (uintptr_t)beta) & 15) == 0;
+  const int grid = (rows + 7) / 8;
+  const __nv_bfloat16 *xp = (const __nv_bfloat16*)x, *rp = (const __nv_bfloat16*)residual;
+  __nv_bfloat16* yp = (__nv_bfloat16*)y;
+  if (aligned && hidden == 768) layernorm_rows_warp<3><<<grid, 256, 0, s>>>(xp, rp, gamma, beta, yp, rows, eps);
+  else if (aligned && hidden == 1024) layernorm_rows_warp<4><<<grid, 256, 0, s>>>(xp, rp, gamma, beta, yp, rows, eps);
+  else if (aligned && hidden == 512) layernorm_rows_warp<2><<<grid, 256, 0, s>>>(xp, rp, gamma, beta, yp, rows, eps);
+  else if (aligned && hidden == 256) layernorm_rows_warp<1><<<grid, 256, 0, s>>>(xp, rp, gamma, beta, yp, rows, eps);
+  else layernorm_rows<<<rows, 256, 0, s>>>(xp, rp, gamma, beta, yp, hidden, eps);
   return cudaGetLastError();
 }
 cudaError_t nn_bert_embed_ln(const void* d_stub, const int* direct_ids, size_t req_stride, int batch, int seq, const void* word,
