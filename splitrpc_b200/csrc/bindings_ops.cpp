@@ -82,15 +82,22 @@ void bind_ops(py::module_& m) {
         py::arg("act") = 0, py::arg("status") = 0, py::arg("stream") = 0, py::arg("impl") = 2);
   m.def("conv_bf16",
         [](uintptr_t in, uintptr_t w, int n, int h, int wd, int cin, int cout, int r, int s, int stride, int pad,
-           uintptr_t out, uintptr_t bias, uintptr_t residual, int act, uintptr_t status, uintptr_t stream, int impl) {
+           uintptr_t out, uintptr_t bias, uintptr_t residual, int act, uintptr_t status, uintptr_t stream, int impl,
+           long pix_stride, long row_stride, long img_stride) {
           ConvShape cs{n, h, wd, cin, cout, r, s, stride, pad, (h + 2 * pad - r) / stride + 1, (wd + 2 * pad - s) / stride + 1};
+          cs.in_pix_stride = pix_stride;
+          cs.in_row_stride = row_stride;
+          cs.in_img_stride = img_stride;
+          if ((pix_stride || row_stride || img_stride) && impl == 1)
+            throw std::invalid_argument("conv_bf16: input strides need the TMA implementation");
           GemmEpilogue ep = make_ep(out, cout, false, bias, residual, cout, act);
           auto fn = impl == 1 ? srpc_conv_bf16 : srpc_conv_bf16_tma;
           check(fn((const void*)in, (const void*)w, cs, ep, (uint32_t*)status, (cudaStream_t)stream), "conv_bf16");
         },
         py::arg("input"), py::arg("weight"), py::arg("n"), py::arg("h"), py::arg("w"), py::arg("cin"), py::arg("cout"),
         py::arg("r"), py::arg("s"), py::arg("stride"), py::arg("pad"), py::arg("out"), py::arg("bias") = 0,
-        py::arg("residual") = 0, py::arg("act") = 0, py::arg("status") = 0, py::arg("stream") = 0, py::arg("impl") = 2);
+        py::arg("residual") = 0, py::arg("act") = 0, py::arg("status") = 0, py::arg("stream") = 0, py::arg("impl") = 2,
+        py::arg("pix_stride") = 0, py::arg("row_stride") = 0, py::arg("img_stride") = 0);
 
   // ---- tensor-parallel fused kernels
   m.def("gemm_tp",
@@ -169,6 +176,14 @@ void bind_ops(py::module_& m) {
           check(nn_stem_im2col((const void*)d_stub, (const float*)direct_in, batch, (void*)out, mean.data(), inv_std.data(),
                                (cudaStream_t)stream),
                 "stem_im2col");
+        });
+  m.def("stem_s2d",
+        [](uintptr_t d_stub, uintptr_t direct_in, int batch, uintptr_t out, std::vector<float> mean, std::vector<float> inv_std,
+           uintptr_t stream) {
+          if (mean.size() != 3 || inv_std.size() != 3) throw std::invalid_argument("mean / inv_std need 3 values");
+          check(nn_stem_s2d((const void*)d_stub, (const float*)direct_in, batch, (void*)out, mean.data(), inv_std.data(),
+                            (cudaStream_t)stream),
+                "stem_s2d");
         });
   m.def("maxpool3x3s2", [](uintptr_t in, uintptr_t out, int n, int h, int w, int c, uintptr_t stream) {
     check(nn_maxpool3x3s2((const void*)in, (void*)out, n, h, w, c, (cudaStream_t)stream), "maxpool3x3s2");

@@ -41,7 +41,10 @@ constexpr int UMMA_K = 16;
 // Output staging buffers per CTA.  A TMA store holds its buffer until the write has drained, which takes a few
 // microseconds under load; with too few buffers the epilogue stalls on them and the store stream, not DRAM, sets
 // the pace of memory-bound shapes.
-constexpr int OUT_BUFS = 2;
+constexpr int OUT_BUFS = 3;
+constexpr int MAX_OUT_BUFS = 4;
+// How many tiles ahead the residual tile is loaded (see TileParams::res_tma).
+constexpr int RES_DIST = 2;
 // warp 0 TMA, warp 1 MMA, then two epilogue warps per TMEM lane quarter (each takes half of the tile's columns)
 template <int BN>
 struct Threads {
@@ -66,6 +69,10 @@ struct TileParams {
   // handful of L2 lines that hold them becomes the bottleneck of the whole GPU.
   int b_stationary;
   int ctas_per_n;            // CTAs that share one column block (grid = ctas_per_n * tiles_n)
+  // Residual through TMA: the residual tile of a later tile is loaded into that tile's output staging buffer while
+  // earlier tiles are still in their epilogue; the epilogue then adds the accumulator to it in place.  Plain loads
+  // of the residual from the epilogue threads leave each of them waiting a full DRAM round trip per tile.
+  int res_tma;
 };
 
 __device__ __forceinline__ float gelu_f(float x) { return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f)); }
@@ -135,11 +142,11 @@ __device__ __forceinline__ bool get_tile(const TileParams& p, int j, TileCoord* 
   return true;
 }
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, int OB>
 __global__ void __launch_bounds__(Threads<BN>::TOTAL, 1)
 gemm_conv_persistent(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                     const __grid_constant__ CUtensorMap tmap_out, TileParams p, GemmEpilogue ep, int use_tma_store_mode,
-                     uint32_t* status) {
+                     const __grid_constant__ CUtensorMap tmap_out, const __grid_constant__ CUtensorMap tmap_res, TileParams p,
+                     GemmEpilogue ep, int use_tma_store_mode, uint32_t* status) {
   const int use_tma_store = use_tma_store_mode == 1 ? 1 : 0;
   constexpr int A_BYTES = BM * BK * 2;
   constexpr int B_BYTES = BN * BK * 2;
@@ -163,9 +170,10 @@ gemm_conv_persistent(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   // the commit -> wake-up -> tcgen05.ld -> release round trip of short (few k-block) tiles.
   constexpr int ACC = BN == 256 ? 2 : 4;
   constexpr int ACC_LOG2 = BN == 256 ? 1 : 2;
-  constexpr int OB = BN == 256 ? 1 : OUT_BUFS;  // output staging buffers
+  static_assert(OB >= 1 && OB <= MAX_OUT_BUFS, "output staging buffers");
   __shared__ __align__(8) uint64_t tmem_full_bar[ACC];
   __shared__ __align__(8) uint64_t tmem_empty_bar[ACC];
+  __shared__ __align__(8) uint64_t res_full_bar[MAX_OUT_BUFS];
   __shared__ uint32_t tmem_base_smem;
   __shared__ uint32_t s_error;
 
@@ -181,11 +189,13 @@ gemm_conv_persistent(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       ptx::mbar_init(&tmem_full_bar[a], 1);
       ptx::mbar_init(&tmem_empty_bar[a], Threads<BN>::EPI / 32);  // one arrival per epilogue warp
     }
+    for (int b = 0; b < MAX_OUT_BUFS; b++) ptx::mbar_init(&res_full_bar[b], 1);
     ptx::fence_mbar_init();
     s_error = 0;
     ptx::prefetch_tmap(&tmap_a);
     ptx::prefetch_tmap(&tmap_b);
     if (use_tma_store) ptx::prefetch_tmap(&tmap_out);
+    if (p.res_tma) ptx::prefetch_tmap(&tmap_res);
   }
   if (warp == 1) {
     ptx::tmem_alloc(&tmem_base_smem, ACC * BN);
@@ -286,9 +296,27 @@ gemm_conv_persistent(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     const int chalf = (warp - 2) >> 2;   // which 32-column group of the tile this warp takes
     const int row = warp_q * 32 + lane;  // row of the tile this thread owns
     const int et = threadIdx.x - 64;     // 0..255 among the epilogue threads
-    const bool vec_res = ep.residual && ((ep.ldr & 7) == 0) && (((uintptr_t)ep.residual & 15) == 0);
+    const bool res_tma = OB > RES_DIST && p.res_tma != 0;
+    const bool vec_res = !res_tma && ep.residual && ((ep.ldr & 7) == 0) && (((uintptr_t)ep.residual & 15) == 0);
     uint32_t local = 0;
     TileCoord tc;
+    // Loads the residual tile of this CTA's jj-th tile into staging buffer jj % OB (one elected thread).
+    auto load_residual = [&](int jj) {
+      TileCoord tn;
+      if (!get_tile(p, jj, &tn)) return;
+      const int b = jj % OB;
+      uint8_t* dst = stage_out + (size_t)b * OUT_BYTES;
+      int boxes = 0;
+      for (int hcol = 0; hcol < BN / 64; hcol++)
+        if (tn.n_idx * BN + hcol * 64 < p.N) boxes++;
+      ptx::mbar_expect_tx(&res_full_bar[b], (uint32_t)(boxes * OUT_HALF_BYTES));
+      for (int hcol = 0; hcol < boxes; hcol++)
+        ptx::tma_load_2d(dst + (size_t)hcol * OUT_HALF_BYTES, &tmap_res, &res_full_bar[b], tn.n_idx * BN + hcol * 64,
+                         tn.m_idx * BM);
+    };
+    if (res_tma && et == 0) {
+      for (int jj = 0; jj < RES_DIST; jj++) load_residual(jj);
+    }
     for (int j = 0; get_tile(p, j, &tc); j++, local++) {
       const uint32_t acc = local & (ACC - 1);
       // Where this thread's row lives in the output.
@@ -317,7 +345,8 @@ gemm_conv_persistent(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       }
       // Each thread's wait is bounded; the vote makes the outcome uniform so that no
       // thread is left alone at a later barrier.
-      const bool mine = (*(volatile uint32_t*)&s_error == 0) && ptx::mbar_wait(&tmem_full_bar[acc], (local >> ACC_LOG2) & 1u);
+      bool mine = (*(volatile uint32_t*)&s_error == 0) && ptx::mbar_wait(&tmem_full_bar[acc], (local >> ACC_LOG2) & 1u);
+      if (res_tma && mine) mine = ptx::mbar_wait(&res_full_bar[local % OB], (local / OB) & 1u);
       if (!named_bar_all(2, EPI_THREADS, mine)) {
         if (lane == 0) atomicExch(&s_error, GEMM_ERR_EPILOGUE_WAIT);
         break;
@@ -345,8 +374,9 @@ gemm_conv_persistent(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         continue;
       }
       uint8_t* sbuf = stage_out + (size_t)(local % OB) * OUT_BYTES;
-      if (use_tma_store) {
-        // The store issued OB tiles ago must have finished reading this staging buffer.
+      if (use_tma_store && !res_tma) {
+        // The store issued OB tiles ago must have finished reading this staging buffer.  (With the residual in the
+        // buffer that was checked before the residual load was issued.)
         if (et == 0) ptx::bulk_wait_read<OB - 1>();
         named_bar_sync(1, EPI_THREADS);
       }
@@ -382,7 +412,21 @@ gemm_conv_persistent(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
               if (col0 + j < p.N) v[j] += __ldg(ep.bias + col0 + j);
           }
         }
-        if (ep.residual && row_ok && col0 < p.N) {
+        if (res_tma) {
+          const uint8_t* half = sbuf + (size_t)(c >> 6) * OUT_HALF_BYTES + (size_t)row * 128;
+          const int chunk0 = (c & 63) >> 3;
+#pragma unroll
+          for (int j = 0; j < 4; j++) {
+            const uint4 q = *reinterpret_cast<const uint4*>(half + (((chunk0 + j) ^ (row & 7)) << 4));
+            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+#pragma unroll
+            for (int t = 0; t < 4; t++) {
+              float2 f = __bfloat1622float2(h[t]);
+              v[j * 8 + 2 * t] += f.x;
+              v[j * 8 + 2 * t + 1] += f.y;
+            }
+          }
+        } else if (ep.residual && row_ok && col0 < p.N) {
           if (res_vec_tile) {
 #pragma unroll
             for (int j = 0; j < 4; j++) {
@@ -461,6 +505,12 @@ gemm_conv_persistent(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
             else tma_store_4d(&tmap_out, src, n0 + hcol * 64, tc.w0, tc.h0, tc.img0);
           }
           ptx::bulk_commit();
+          if (res_tma) {
+            // The tile RES_DIST ahead takes the buffer of the tile OB - RES_DIST back, so all stores but the last
+            // OB - RES_DIST must have been read.
+            ptx::bulk_wait_read<(OB > RES_DIST ? OB - RES_DIST : 0)>();
+            load_residual(j + RES_DIST);
+          }
         }
       }
     }
@@ -557,13 +607,13 @@ int num_sms() {
   return n;
 }
 
-template <int BN, int STAGES>
-cudaError_t launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& to, const TileParams& p_in,
-                   const GemmEpilogue& ep, int use_tma_store, uint32_t* status, cudaStream_t st) {
+template <int BN, int STAGES, int OB>
+cudaError_t launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& to, const CUtensorMap& tr,
+                   const TileParams& p_in, const GemmEpilogue& ep, int use_tma_store, uint32_t* status, cudaStream_t st) {
   static bool attr = false;
-  const int smem = STAGES * (BM * BK * 2 + BN * BK * 2) + (BN == 256 ? 1 : OUT_BUFS) * (BN / 64) * BM * 128 + 1024;
+  const int smem = STAGES * (BM * BK * 2 + BN * BK * 2) + OB * (BN / 64) * BM * 128 + 1024;
   if (!attr) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_conv_persistent<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaError_t e = cudaFuncSetAttribute(gemm_conv_persistent<BN, STAGES, OB>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
     attr = true;
   }
@@ -581,15 +631,15 @@ cudaError_t launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorM
       grid = per_n * p.tiles_n;
     }
   }
-  gemm_conv_persistent<BN, STAGES><<<grid, Threads<BN>::TOTAL, smem, st>>>(ta, tb, to, p, ep, use_tma_store, status);
+  gemm_conv_persistent<BN, STAGES, OB><<<grid, Threads<BN>::TOTAL, smem, st>>>(ta, tb, to, tr, p, ep, use_tma_store, status);
   return cudaGetLastError();
 }
 
-cudaError_t dispatch(int bn, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& to, const TileParams& p,
-                     const GemmEpilogue& ep, int use_tma_store, uint32_t* status, cudaStream_t st) {
-  if (bn == 64) return launch<64, 6>(ta, tb, to, p, ep, use_tma_store, status, st);
-  if (bn == 256) return launch<256, 3>(ta, tb, to, p, ep, use_tma_store, status, st);
-  return launch<128, 4>(ta, tb, to, p, ep, use_tma_store, status, st);
+cudaError_t dispatch(int bn, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& to, const CUtensorMap& tr,
+                     const TileParams& p, const GemmEpilogue& ep, int use_tma_store, uint32_t* status, cudaStream_t st) {
+  if (bn == 64) return launch<64, 6, OUT_BUFS>(ta, tb, to, tr, p, ep, use_tma_store, status, st);
+  if (bn == 256) return launch<256, 3, 1>(ta, tb, to, tr, p, ep, use_tma_store, status, st);
+  return launch<128, 4, OUT_BUFS>(ta, tb, to, tr, p, ep, use_tma_store, status, st);
 }
 
 }  // namespace
@@ -608,9 +658,20 @@ cudaError_t srpc_gemm_bf16_v2(const void* A, int lda, const void* B, int ldb, in
   if (M <= 0 || N <= 0 || K <= 0) return cudaErrorInvalidValue;
   if ((lda % 8) || (ldb % 8) || (K % 8) || ((uintptr_t)A & 15) || ((uintptr_t)B & 15)) return cudaErrorInvalidValue;
   if (ep.bias && ((uintptr_t)ep.bias & 15)) return cudaErrorInvalidValue;
-  const int bn = pick_bn(N, (M + BM - 1) / BM, ep.out_fp32 == 0);
+  int use_tma_store = (!ep.out_fp32 && (ep.ldo % 8) == 0 && ((uintptr_t)ep.out & 15) == 0) ? 1 : 0;
+  if (use_tma_store) {
+    // Epilogue store path: 1 = staged TMA store (default), 3 = 16-byte vector stores straight from registers.
+    static const int mode = [] { const char* e = getenv("SPLITRPC_GEMM_STORE"); return e ? atoi(e) : 1; }();
+    if (mode >= 2 && mode <= 5) use_tma_store = mode;
+  }
+  static const int allow_res_tma = [] { const char* e = getenv("SPLITRPC_GEMM_RES_TMA"); return e ? atoi(e) : 1; }();
+  const bool res_tma = allow_res_tma && use_tma_store == 1 && ep.residual && (ep.ldr % 8) == 0 &&
+                       ((uintptr_t)ep.residual & 15) == 0;
+  // The residual ring lives in the output staging buffers, which the 256-wide tile has only one of.
+  const int bn = res_tma ? (N <= 64 ? 64 : 128) : pick_bn(N, (M + BM - 1) / BM, ep.out_fp32 == 0);
   TileParams p{};
   p.mode = 0;
+  p.res_tma = res_tma ? 1 : 0;
   p.M = M;
   p.N = N;
   p.K = K;
@@ -622,19 +683,18 @@ cudaError_t srpc_gemm_bf16_v2(const void* A, int lda, const void* B, int ldb, in
   if (e != cudaSuccess) return e;
   e = map_2d(&tb, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb * 2, BK, (uint32_t)bn);
   if (e != cudaSuccess) return e;
-  int use_tma_store = (!ep.out_fp32 && (ep.ldo % 8) == 0 && ((uintptr_t)ep.out & 15) == 0) ? 1 : 0;
-  if (use_tma_store) {
-    // Epilogue store path: 1 = staged TMA store (default), 3 = 16-byte vector stores straight from registers.
-    static const int mode = [] { const char* e = getenv("SPLITRPC_GEMM_STORE"); return e ? atoi(e) : 1; }();
-    if (mode >= 2 && mode <= 5) use_tma_store = mode;
-  }
+  CUtensorMap tr = ta;
   if (use_tma_store == 1) {
     e = map_2d(&to, ep.out, (uint64_t)N, (uint64_t)M, (uint64_t)ep.ldo * 2, 64, BM);
     if (e != cudaSuccess) return e;
+    if (res_tma) {
+      e = map_2d(&tr, ep.residual, (uint64_t)N, (uint64_t)M, (uint64_t)ep.ldr * 2, 64, BM);
+      if (e != cudaSuccess) return e;
+    }
   } else {
     to = ta;
   }
-  return dispatch(bn, ta, tb, to, p, ep, use_tma_store, status, stream);
+  return dispatch(bn, ta, tb, to, tr, p, ep, use_tma_store, status, stream);
 }
 
 // Picks the output patch (pw x ph x pn <= 128 pixels) that wastes the fewest tile rows.
@@ -685,8 +745,12 @@ cudaError_t srpc_conv_bf16_tma(const void* in, const void* weight, const ConvSha
   p.a_box_bytes = (uint32_t)p.rows_used * 128u;
   CUtensorMap ta, tb, to;
   {
+    const uint64_t pix = cs.in_pix_stride ? (uint64_t)cs.in_pix_stride : (uint64_t)cs.cin;
+    const uint64_t rowst = cs.in_row_stride ? (uint64_t)cs.in_row_stride : (uint64_t)cs.w * pix;
+    const uint64_t imgst = cs.in_img_stride ? (uint64_t)cs.in_img_stride : (uint64_t)cs.h * rowst;
+    if ((pix % 8) || (rowst % 8) || (imgst % 8)) return cudaErrorInvalidValue;
     uint64_t dims[4] = {(uint64_t)cs.cin, (uint64_t)cs.w, (uint64_t)cs.h, (uint64_t)cs.n};
-    uint64_t st[3] = {(uint64_t)cs.cin * 2, (uint64_t)cs.w * cs.cin * 2, (uint64_t)cs.h * cs.w * cs.cin * 2};
+    uint64_t st[3] = {pix * 2, rowst * 2, imgst * 2};
     uint32_t box[4] = {BK, (uint32_t)(p.pw * cs.stride), (uint32_t)(p.ph * cs.stride), (uint32_t)p.pn};
     uint32_t es[4] = {1, (uint32_t)cs.stride, (uint32_t)cs.stride, 1};
     if (box[1] > 256 || box[2] > 256) return cudaErrorInvalidValue;
@@ -706,5 +770,5 @@ cudaError_t srpc_conv_bf16_tma(const void* in, const void* weight, const ConvSha
   GemmEpilogue ep2 = ep;
   ep2.ldo = cs.cout;
   if (ep2.residual) ep2.ldr = cs.cout;
-  return dispatch(bn, ta, tb, to, p, ep2, 1, status, stream);
+  return dispatch(bn, ta, tb, to, ta, p, ep2, 1, status, stream);
 }

@@ -31,6 +31,10 @@ struct ConvShape {
   int cout, r, s;       // filter [cout][r][s][cin]
   int stride, pad;
   int oh, ow;
+  // Input strides in elements; 0 = dense NHWC (pixel stride cin, row stride w*cin, image stride h*w*cin).  A pixel
+  // stride smaller than cin makes neighbouring pixels overlap: a window of several narrow pixels is then read as one
+  // 64-channel pixel without being copied first (TMA path only; every stride a multiple of 8 elements).
+  long in_pix_stride = 0, in_row_stride = 0, in_img_stride = 0;
 };
 
 // D[M,N] = A[M,K] . B[N,K]^T, bf16 operands (row strides lda/ldb elements, multiples of 8), fp32 accumulation.

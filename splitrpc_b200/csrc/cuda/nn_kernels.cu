@@ -77,6 +77,45 @@ __global__ void __launch_bounds__(256) stem_im2col(const g_params* stub, const f
   }
 }
 
+// Space-to-depth form of the stem input.  The 7x7 stride-2 pad-3 convolution over 3 channels equals a 4x4 stride-1
+// convolution over the 2x2 space-to-depth transform of the zero-padded (230 x 230) image.  Writes
+// out[n][Y][X][16] bf16 with Y, X < 115 and channel dy*8 + dx*3 + c = normalised input pixel (2Y+dy-3, 2X+dx-3) of
+// channel c (zero outside the image; channels 6, 7, 14, 15 are zero).  Four horizontally adjacent pixels are 64
+// contiguous channels, so the convolution reads its rows straight from this array through a tensor map whose pixel
+// stride is 16 elements: no im2col matrix is ever written (27 MB per 64 images instead of 308 MB).
+__global__ void __launch_bounds__(256) stem_s2d(const g_params* stub, const float* __restrict__ direct_in, int batch,
+                                                __nv_bfloat16* __restrict__ out, float3 mean, float3 inv_std) {
+  const float* in = direct_in ? direct_in : reinterpret_cast<const float*>(stub->req);
+  const size_t total = (size_t)batch * 115 * 115 * 2;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const int dy = (int)(i & 1);
+    const size_t pix = i >> 1;
+    const int X = (int)(pix % 115), Y = (int)((pix / 115) % 115), n = (int)(pix / (115 * 115));
+    const int iy = 2 * Y + dy - 3, ix0 = 2 * X - 3;
+    float v[8];
+#pragma unroll
+    for (int j = 0; j < 8; j++) v[j] = 0.f;
+    if (iy >= 0 && iy < 224) {
+#pragma unroll
+      for (int c = 0; c < 3; c++) {
+        const float m = c == 0 ? mean.x : (c == 1 ? mean.y : mean.z);
+        const float s = c == 0 ? inv_std.x : (c == 1 ? inv_std.y : inv_std.z);
+        const float* row = in + (((size_t)n * 3 + c) * 224 + iy) * 224;
+#pragma unroll
+        for (int dx = 0; dx < 2; dx++) {
+          const int ix = ix0 + dx;
+          if (ix >= 0 && ix < 224) v[dx * 3 + c] = (__ldg(row + ix) - m) * s;
+        }
+      }
+    }
+    uint4 o;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int t = 0; t < 4; t++) h[t] = __floats2bfloat162_rn(v[2 * t], v[2 * t + 1]);
+    *reinterpret_cast<uint4*>(out + pix * 16 + dy * 8) = o;
+  }
+}
+
 // 3x3 stride-2 pad-1 max pooling, NHWC bf16, 8 channels per thread.
 __global__ void __launch_bounds__(256) maxpool3x3s2(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out,
                                                     int n, int h, int w, int c) {
@@ -395,6 +434,14 @@ cudaError_t nn_stem_im2col(const void* d_stub, const float* direct_in, int batch
   stem_im2col<<<grid_for(total, 256), 256, 0, s>>>((const g_params*)d_stub, direct_in, batch, (__nv_bfloat16*)out,
                                                    make_float3(mean[0], mean[1], mean[2]),
                                                    make_float3(inv_std[0], inv_std[1], inv_std[2]));
+  return cudaGetLastError();
+}
+cudaError_t nn_stem_s2d(const void* d_stub, const float* direct_in, int batch, void* out, const float mean[3],
+                        const float inv_std[3], cudaStream_t s) {
+  size_t total = (size_t)batch * 115 * 115 * 2;
+  stem_s2d<<<grid_for(total, 256), 256, 0, s>>>((const g_params*)d_stub, direct_in, batch, (__nv_bfloat16*)out,
+                                                make_float3(mean[0], mean[1], mean[2]),
+                                                make_float3(inv_std[0], inv_std[1], inv_std[2]));
   return cudaGetLastError();
 }
 cudaError_t nn_maxpool3x3s2(const void* in, void* out, int n, int h, int w, int c, cudaStream_t s) {

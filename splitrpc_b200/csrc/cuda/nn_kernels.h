@@ -9,6 +9,9 @@
 
 cudaError_t nn_stem_im2col(const void* d_stub, const float* direct_in, int batch, void* out, const float mean[3],
                            const float inv_std[3], cudaStream_t s);
+// Space-to-depth form of the same input: out[batch][115][115][16] bf16 (see nn_kernels.cu).
+cudaError_t nn_stem_s2d(const void* d_stub, const float* direct_in, int batch, void* out, const float mean[3],
+                        const float inv_std[3], cudaStream_t s);
 cudaError_t nn_maxpool3x3s2(const void* in, void* out, int n, int h, int w, int c, cudaStream_t s);
 cudaError_t nn_global_avgpool(const void* in, void* out, int n, int hw, int c, cudaStream_t s);
 cudaError_t nn_softmax_response(const float* logits, int rows, int n, int ld, const void* d_stub, void* direct_out,

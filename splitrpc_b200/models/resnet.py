@@ -4,7 +4,9 @@ Every convolution is the tcgen05 implicit-GEMM kernel: 1x1 stride-1 layers run a
 plain TMA-fed GEMMs over ``[N*H*W, Cin]``, 3x3 and strided layers gather their
 rows; bias, residual add and ReLU live in the GEMM epilogue.  The stem reads the
 fp32 CHW request bytes where the scatter-gather engine put them (through the
-device stub), normalises, casts and lays out its im2col matrix in one pass.
+device stub), normalises, casts and writes their 2x2 space-to-depth form; the 7x7/2
+convolution then runs as four row taps over overlapping 64-channel windows of that
+array (a tensor map with a 32-byte pixel stride), so no im2col matrix exists.
 The classifier's softmax writes straight into the response ring.
 
 All activations live in buffers allocated once for ``max_batch``; ``forward``
@@ -50,6 +52,7 @@ class ResNet50:
         stem = torch.cat([stem.reshape(64, 168), torch.zeros((64, 24))], dim=1)
         self.params["stem.w"] = stem.to(self.device, torch.bfloat16).contiguous()
         self.params["stem.w_nchw"] = w.to(self.device)
+        self.params["stem.w_s2d"] = ops.stem_weight_s2d(w.to(self.device))
         self.params["stem.b"] = (torch.randn((64,), generator=g) * 0.05).to(self.device, torch.float32)
         cin = 64
         self.blocks = []
@@ -73,7 +76,7 @@ class ResNet50:
     def _plan(self, nb: int) -> None:
         dev, bf = self.device, torch.bfloat16
         self.buf = {
-            "im2col": torch.empty((nb * 112 * 112, 192), dtype=bf, device=dev),
+            "s2d": torch.empty((nb, 115, 115, 16), dtype=bf, device=dev),
             "stem": torch.empty((nb, 112, 112, 64), dtype=bf, device=dev),
             "pool": torch.empty((nb, 56, 56, 64), dtype=bf, device=dev),
             "avg": torch.empty((nb, 2048), dtype=bf, device=dev),
@@ -110,8 +113,8 @@ class ResNet50:
         """
         p, b = self.params, self.buf
         nb = batch
-        ops.stem_im2col(b["im2col"], nb, x=x, d_stub=d_stub, mean=self.mean, inv_std=self.inv_std)
-        ops.gemm(b["im2col"][: nb * 12544], p["stem.w"], bias=p["stem.b"], act="relu", out=b["stem"][:nb].view(nb * 12544, 64))
+        ops.stem_s2d(b["s2d"], nb, x=x, d_stub=d_stub, mean=self.mean, inv_std=self.inv_std)
+        ops.stem_conv(b["s2d"], p["stem.w_s2d"], nb, bias=p["stem.b"], act="relu", out=b["stem"][:nb])
         cur = ops.maxpool3x3s2(b["stem"][:nb], out=b["pool"][:nb])
         for name, cin, width, s, ds in self.blocks:
             t1 = self._conv1x1(cur, name + ".c1", b[name + ".t1"][:nb], "relu")

@@ -107,6 +107,46 @@ def stem_im2col(out: torch.Tensor, batch: int, x: torch.Tensor | None = None, d_
     return out
 
 
+def stem_s2d(out: torch.Tensor, batch: int, x: torch.Tensor | None = None, d_stub: int = 0,
+             mean=(0.0, 0.0, 0.0), inv_std=(1.0, 1.0, 1.0)) -> torch.Tensor:
+    """Normalised bf16 space-to-depth form of fp32 CHW 224x224 images: ``out[batch, 115, 115, 16]`` with channel
+    ``dy*8 + dx*3 + c`` = pixel ``(2Y+dy-3, 2X+dx-3)`` of channel ``c`` (zero outside the image)."""
+    assert out.dtype == torch.bfloat16 and out.is_contiguous() and out.numel() >= batch * 115 * 115 * 16
+    if x is not None:
+        assert x.dtype == torch.float32 and x.is_contiguous() and x.numel() >= batch * 3 * 224 * 224
+    _C.stem_s2d(d_stub, _ptr(x), batch, out.data_ptr(), list(mean), list(inv_std), _stream())
+    return out
+
+
+def stem_weight_s2d(w: torch.Tensor) -> torch.Tensor:
+    """Re-orders ``[64, 3, 7, 7]`` stem filters into the ``[64, 4, 1, 64]`` bf16 filters that ``stem_conv`` expects:
+    tap row ``ky' = ky // 2``, channel ``kx'*16 + dy*8 + dx*3 + c`` with ``ky = 2ky'+dy``, ``kx = 2kx'+dx``."""
+    cout = w.shape[0]
+    w8 = torch.zeros((cout, 3, 8, 8), dtype=torch.float32, device=w.device)
+    w8[:, :, :7, :7] = w.float()
+    w8 = w8.view(cout, 3, 4, 2, 4, 2)  # [o, c, ky', dy, kx', dx]
+    w2 = torch.zeros((cout, 4, 4, 16), dtype=torch.float32, device=w.device)
+    for dy in range(2):
+        for dx in range(2):
+            for c in range(3):
+                w2[:, :, :, dy * 8 + dx * 3 + c] = w8[:, c, :, dy, :, dx]
+    return w2.view(cout, 4, 1, 64).to(torch.bfloat16).contiguous()
+
+
+def stem_conv(s2d: torch.Tensor, w2: torch.Tensor, batch: int, bias: torch.Tensor | None = None, act: str | None = "relu",
+              out: torch.Tensor | None = None) -> torch.Tensor:
+    """The 7x7/2 stem as a 4x1-tap convolution over overlapping 64-channel windows of ``stem_s2d``'s output."""
+    assert s2d.dtype == torch.bfloat16 and s2d.is_contiguous() and s2d.numel() >= batch * 115 * 115 * 16
+    cout = w2.shape[0]
+    assert tuple(w2.shape) == (cout, 4, 1, 64) and w2.dtype == torch.bfloat16 and w2.is_contiguous()
+    if out is None:
+        out = torch.empty((batch, 112, 112, cout), dtype=torch.bfloat16, device=s2d.device)
+    assert out.is_contiguous() and out.numel() >= batch * 112 * 112 * cout
+    _C.conv_bf16(s2d.data_ptr(), w2.data_ptr(), batch, 115, 112, 64, cout, 4, 1, 1, 0, out.data_ptr(), _ptr(bias), 0,
+                 ACT[act], status_word().data_ptr(), _stream(), 2, 16, 115 * 16, 115 * 115 * 16)
+    return out
+
+
 def maxpool3x3s2(x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
     n, h, w, c = x.shape
     oh, ow = (h - 1) // 2 + 1, (w - 1) // 2 + 1

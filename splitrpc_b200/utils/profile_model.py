@@ -44,6 +44,12 @@ def _work(name, args, kwargs, out):
         oh, ow = out.shape[1], out.shape[2]
         by = 2 * (x.numel() + w.numel() + out.numel()) + (2 * out.numel() if kwargs.get("residual") is not None else 0)
         return 2.0 * n * oh * ow * cout * r * s * cin, by, f"{n}x{h}x{wd}x{cin}->{cout} k{r} s{kwargs.get('stride', 1)}"
+    if name == "stem_s2d":
+        batch = args[1]
+        return 0.0, batch * (3 * 224 * 224 * 4 + 115 * 115 * 16 * 2), f"b{batch}"
+    if name == "stem_conv":
+        batch = args[2]
+        return 2.0 * batch * 12544 * 64 * 256, 2 * batch * (115 * 115 * 16 + 12544 * 64), f"b{batch} 4x1 taps x 64ch windows"
     if name == "stem_im2col":
         batch = args[1]
         return 0.0, batch * (3 * 224 * 224 * 4 + 112 * 112 * 192 * 2), f"b{batch}"
@@ -83,7 +89,7 @@ def main():
 
     records = []
     if not args.no_events:
-        for name in ("gemm", "conv2d_nhwc", "stem_im2col", "maxpool3x3s2", "global_avgpool", "softmax_response", "layernorm",
+        for name in ("gemm", "conv2d_nhwc", "stem_im2col", "stem_s2d", "stem_conv", "maxpool3x3s2", "global_avgpool", "softmax_response", "layernorm",
                      "bert_embed_ln", "attention_d64"):
             fn = getattr(ops, name)
 

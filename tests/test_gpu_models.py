@@ -46,6 +46,35 @@ def test_nn_layers_match_pytorch(torch_cuda):
     assert got[..., 7].abs().max() == 0 and col[:, 168:].abs().max() == 0
 
 
+def test_space_to_depth_stem_matches_conv2d(torch_cuda):
+    """stem_s2d + stem_conv (4x1 taps over overlapping 64-channel windows) against an fp32 7x7/2 convolution."""
+    torch = torch_cuda
+    import torch.nn.functional as F
+    from splitrpc_b200 import ops
+
+    nb = 3
+    img = torch.randn(nb, 3, 224, 224, device="cuda")
+    w = torch.randn(64, 3, 7, 7, device="cuda") * 0.1
+    bias = torch.randn(64, device="cuda")
+    mean, inv = (0.1, 0.2, 0.3), (2.0, 3.0, 4.0)
+    s2d = torch.full((nb, 115, 115, 16), 7.0, dtype=torch.bfloat16, device="cuda")
+    ops.stem_s2d(s2d, nb, x=img, mean=mean, inv_std=inv)
+    m = torch.tensor(mean, device="cuda").view(1, 3, 1, 1)
+    s = torch.tensor(inv, device="cuda").view(1, 3, 1, 1)
+    xn = ((img - m) * s).bfloat16().float()
+    pad = F.pad(xn, (3, 3, 3, 3))  # [nb, 3, 230, 230]
+    want = torch.zeros(nb, 115, 115, 16, device="cuda")
+    for dy in range(2):
+        for dx in range(2):
+            for c in range(3):
+                want[..., dy * 8 + dx * 3 + c] = pad[:, c, dy::2, dx::2]
+    torch.testing.assert_close(s2d.float(), want, rtol=0, atol=0)
+    out = ops.stem_conv(s2d, ops.stem_weight_s2d(w), nb, bias=bias, act="relu")
+    ops.check_status()
+    ref = F.relu(F.conv2d(xn, w.bfloat16().float(), bias, 2, 3)).permute(0, 2, 3, 1)
+    torch.testing.assert_close(out.float(), ref, rtol=2e-2, atol=3e-2)
+
+
 @pytest.mark.parametrize("seq,heads", [(128, 12), (384, 16)])
 def test_attention_matches_pytorch(torch_cuda, seq, heads):
     torch = torch_cuda
