@@ -133,6 +133,10 @@ void bind_ops(py::module_& m) {
     check(srpc_tp_wait((const uint32_t*)flags, n, epoch, (const uint32_t*)epoch_base, (uint32_t*)status, (cudaStream_t)stream),
           "tp_wait");
   });
+  m.def("tp_begin", [](uintptr_t flags, int n, uintptr_t epoch_base, uint32_t delta, uintptr_t status, uintptr_t stream) {
+    check(srpc_tp_begin((const uint32_t*)flags, n, (uint32_t*)epoch_base, delta, (uint32_t*)status, (cudaStream_t)stream),
+          "tp_begin");
+  });
   m.def("tp_bump", [](uintptr_t word, uint32_t delta, uintptr_t stream) {
     check(srpc_tp_bump((uint32_t*)word, delta, (cudaStream_t)stream), "tp_bump");
   });
@@ -147,7 +151,7 @@ void bind_ops(py::module_& m) {
   m.def("layernorm_reduce",
         [](std::vector<uintptr_t> slots, uintptr_t flags, uint32_t epoch, uintptr_t bias, uintptr_t residual, uintptr_t gamma,
            uintptr_t beta, uintptr_t out, int rows, int hidden, float eps, uintptr_t status, uintptr_t stream,
-           uintptr_t epoch_base) {
+           uintptr_t epoch_base, std::vector<uintptr_t> sig_flags, uint32_t sig_epoch, uintptr_t done_count) {
           TpReduce r{};
           r.tp = (int)slots.size();
           r.hidden = hidden;
@@ -161,8 +165,16 @@ void bind_ops(py::module_& m) {
           r.beta = (const float*)beta;
           r.out = (__nv_bfloat16*)out;
           r.eps = eps;
+          r.sig_tp = done_count ? (int)std::min(sig_flags.size(), (size_t)TP_MAX_RANKS) : 0;
+          r.sig_epoch = sig_epoch;
+          for (int i = 0; i < r.sig_tp; i++) r.sig_peer_flag[i] = (uint32_t*)sig_flags[i];
+          r.done_count = (uint32_t*)done_count;
           check(srpc_layernorm_reduce(r, rows, (uint32_t*)status, (cudaStream_t)stream), "layernorm_reduce");
-        });
+        },
+        py::arg("slots"), py::arg("flags"), py::arg("epoch"), py::arg("bias"), py::arg("residual"), py::arg("gamma"),
+        py::arg("beta"), py::arg("out"), py::arg("rows"), py::arg("hidden"), py::arg("eps"), py::arg("status"),
+        py::arg("stream"), py::arg("epoch_base"), py::arg("sig_flags") = std::vector<uintptr_t>{}, py::arg("sig_epoch") = 0,
+        py::arg("done_count") = 0);
 
   m.def("swap_hdrs", [](uintptr_t hdr_ptrs, uintptr_t hdrs_contig, int n, bool clear_sockperf, uintptr_t stream) {
     check(srpc_swap_hdrs((void* const*)hdr_ptrs, (void*)hdrs_contig, n, clear_sockperf ? 1 : 0, (cudaStream_t)stream), "swap_hdrs");

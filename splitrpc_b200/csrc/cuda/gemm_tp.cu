@@ -7,7 +7,7 @@
 //
 //  all-gather -> GEMM   D[T, N_local] = act(concat_r(X_r)[T, K] . W[N_local, K]^T + bias)
 //    X is sharded by rows over the ranks.  A few "copier" blocks of the same launch
-//    pull the remote shards over NVLink (plain peer loads, 16 bytes per thread)
+//    pull the remote shards over NVLink (rings of 16 KB bulk copies, no multicast)
 //    into a local gathered buffer, one 128-row block at a time, and publish each
 //    block with a release store; the GEMM blocks visit row blocks in rotated
 //    order (own shard first) and their TMA producer waits (bounded) for a block's
@@ -23,7 +23,7 @@
 //    + residual + LayerNorm, see layernorm_reduce) waits for the flags, so the
 //    reduction itself is fused into the normalisation that follows.
 //
-// No load uses multicast; remote data is only touched by plain loads/stores.
+// No load uses multicast; remote data is only touched by plain loads/stores and non-multicast bulk copies.
 // Every wait on a flag (another block's or another rank's) is bounded: when it
 // runs out the kernel records an error code and winds down.
 #include <algorithm>
@@ -84,39 +84,86 @@ __device__ __forceinline__ bool wait_flag_sys(const uint32_t* flag, uint32_t epo
   }
 }
 
-// Copier role: pulls remote row blocks into the local gathered buffer.
-__device__ void copier(const TpParams& tp, int copier_idx, uint32_t* status) {
-  __shared__ uint32_t s_ok;
+// Copier role: pulls remote row blocks into the local gathered buffer.  One thread per copier block drives a ring of
+// 16 KB bulk copies (peer memory -> shared memory -> local memory; no multicast): COPY_AHEAD loads are in flight per
+// block, so a handful of blocks keep a few MB on the wire, which is what NVLink's latency needs to run at link rate.
+// (Plain 16-byte loads from 320 threads kept 20 KB per block in flight and reached about 100 GB/s.)
+constexpr int COPY_CHUNK = 16384;
+constexpr int COPY_SLOTS = 12;
+constexpr int COPY_AHEAD = 10;
+
+__device__ void copier(const TpParams& tp, int copier_idx, uint8_t* ring, uint32_t* status) {
+  __shared__ __align__(8) uint64_t cbar[COPY_SLOTS];
+  if (threadIdx.x != 0) return;
+  for (int s = 0; s < COPY_SLOTS; s++) ptx::mbar_init(&cbar[s], 1);
+  ptx::fence_mbar_init();
   const int remote_blocks = (tp.tp - 1) * tp.mblocks_per_rank;
-  for (int i = copier_idx; i < remote_blocks; i += tp.n_copy) {
-    // i-th remote block in rotated order: ranks rank+1, rank+2, ... ; blocks of a rank in order
-    const int step = i / tp.mblocks_per_rank + 1;
-    const int r = (tp.rank + step) % tp.tp;
+  const int my_blocks = copier_idx < remote_blocks ? (remote_blocks - copier_idx + tp.n_copy - 1) / tp.n_copy : 0;
+  const uint32_t cpb = (uint32_t)((tp.mblock_bytes + COPY_CHUNK - 1) / COPY_CHUNK);  // chunks per row block
+  const uint32_t total = (uint32_t)my_blocks * cpb;
+  struct Chunk {
+    const uint8_t* src;
+    uint8_t* dst;
+    uint32_t len;
+    int r, m;
+    bool first, last;
+  };
+  auto chunk_at = [&](uint32_t q) {
+    Chunk c;
+    const int i = copier_idx + (int)(q / cpb) * tp.n_copy;  // i-th remote block in rotated order: ranks rank+1, rank+2, ...
+    const uint32_t k = q % cpb;
+    c.r = (tp.rank + i / tp.mblocks_per_rank + 1) % tp.tp;
     const int blk = i % tp.mblocks_per_rank;
-    if (threadIdx.x == 0) s_ok = wait_flag_sys(tp.src_ready + r, tp.epoch) ? 1u : 0u;
-    __syncthreads();
-    if (!s_ok) {
-      if (threadIdx.x == 0 && status) atomicExch(status, GEMM_ERR_TP_SRC_WAIT);
-      return;
+    c.m = c.r * tp.mblocks_per_rank + blk;
+    const size_t off = (size_t)k * COPY_CHUNK;
+    c.src = tp.src[c.r] + (size_t)blk * tp.mblock_bytes + off;
+    c.dst = tp.gathered + (size_t)c.m * tp.mblock_bytes + off;
+    const size_t left = tp.mblock_bytes - off;
+    c.len = (uint32_t)(left < (size_t)COPY_CHUNK ? left : (size_t)COPY_CHUNK);
+    c.first = k == 0;
+    c.last = k + 1 == cpb;
+    return c;
+  };
+  uint32_t q_load = 0, phase_bits = 0;
+  bool ok = true;
+  auto issue_load = [&]() {
+    const Chunk c = chunk_at(q_load);
+    if (c.first && !wait_flag_sys(tp.src_ready + c.r, tp.epoch)) {
+      if (status) atomicExch(status, GEMM_ERR_TP_SRC_WAIT);
+      return false;
     }
-    const uint4* src = reinterpret_cast<const uint4*>(tp.src[r] + (size_t)blk * tp.mblock_bytes);
-    const int m = r * tp.mblocks_per_rank + blk;
-    uint4* dst = reinterpret_cast<uint4*>(tp.gathered + (size_t)m * tp.mblock_bytes);
-    const int n16 = (int)(tp.mblock_bytes >> 4);
-    // 4 independent 16-byte loads in flight per thread to cover NVLink latency
-    int j = threadIdx.x;
-    for (; j + 3 * (int)blockDim.x < n16; j += 4 * blockDim.x) {
-      uint4 a = src[j], b = src[j + blockDim.x], c = src[j + 2 * blockDim.x], d = src[j + 3 * blockDim.x];
-      dst[j] = a;
-      dst[j + blockDim.x] = b;
-      dst[j + 2 * blockDim.x] = c;
-      dst[j + 3 * blockDim.x] = d;
+    const uint32_t s = q_load % COPY_SLOTS;
+    // The store that last used this slot must have finished reading it.
+    if (q_load >= COPY_SLOTS) ptx::bulk_wait_read<COPY_SLOTS - COPY_AHEAD - 1>();
+    ptx::mbar_expect_tx(&cbar[s], c.len);
+    ptx::bulk_g2s(ring + (size_t)s * COPY_CHUNK, c.src, c.len, &cbar[s]);
+    q_load++;
+    return true;
+  };
+  for (int i = 0; i < COPY_AHEAD && q_load < total && ok; i++) ok = issue_load();
+  for (uint32_t q = 0; q < total && ok; q++) {
+    if (q_load < total) ok = issue_load();
+    if (!ok) break;
+    const Chunk c = chunk_at(q);
+    const uint32_t s = q % COPY_SLOTS;
+    if (!ptx::mbar_wait(&cbar[s], (phase_bits >> s) & 1u)) {
+      if (status) atomicExch(status, GEMM_ERR_TP_BLOCK_WAIT);
+      ok = false;
+      break;
     }
-    for (; j < n16; j += blockDim.x) dst[j] = src[j];
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) ptx::st_release_gpu(tp.mblock_ready + m, tp.epoch);
+    phase_bits ^= (1u << s);
+    ptx::bulk_s2g(c.dst, ring + (size_t)s * COPY_CHUNK, c.len);
+    ptx::bulk_commit();
+    if (c.last) {
+      // Whole row block written: make the bulk stores visible, then publish the block to the GEMM blocks.
+      ptx::bulk_wait_all<0>();
+      ptx::fence_proxy_async_all();
+      __threadfence();
+      ptx::st_release_gpu(tp.mblock_ready + c.m, tp.epoch);
+    }
   }
+  ptx::bulk_wait_all<0>();
+  if (!ok) __nanosleep(1000000);  // let loads that are still in flight land before the block leaves
 }
 
 __global__ void __launch_bounds__(THREADS, 1)
@@ -126,12 +173,12 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   TpParams tp = tp_in;
   if (tp.epoch_base) tp.epoch += *tp.epoch_base;
   const int gemm_ctas = (int)gridDim.x - tp.n_copy;
-  if ((int)blockIdx.x >= gemm_ctas) {
-    copier(tp, (int)blockIdx.x - gemm_ctas, status);
-    return;
-  }
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  if ((int)blockIdx.x >= gemm_ctas) {
+    copier(tp, (int)blockIdx.x - gemm_ctas, smem, status);
+    return;
+  }
   uint8_t* stage_out = smem + (size_t)STAGES * STAGE_BYTES;
   __shared__ __align__(8) uint64_t full_bar[STAGES];
   __shared__ __align__(8) uint64_t empty_bar[STAGES];
@@ -383,6 +430,8 @@ __global__ void tp_signal_peers(TpSignal sig) {
   }
 }
 
+__device__ __forceinline__ void reduce_signal(const TpReduce& rd);
+
 // y = LN(sum_r slot_r[row] + bias + residual) * gamma + beta; waits (bounded) until every source rank has
 // published `epoch` in flags[r].
 __global__ void __launch_bounds__(256) layernorm_reduce(TpReduce rd, uint32_t* status) {
@@ -429,6 +478,104 @@ __global__ void __launch_bounds__(256) layernorm_reduce(TpReduce rd, uint32_t* s
   cnt = 0;
   for (int i = threadIdx.x; i < rd.hidden && cnt < 8; i += blockDim.x, cnt++)
     rd.out[row * rd.hidden + i] = __float2bfloat16((v[cnt] - mean) * rstd * rd.gamma[i] + rd.beta[i]);
+  reduce_signal(rd);
+}
+
+// Last block out publishes the step number to the peers (see TpReduce::sig_*).
+__device__ __forceinline__ void reduce_signal(const TpReduce& rd) {
+  if (rd.sig_tp <= 0 || !rd.done_count) return;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const uint32_t old = atomicAdd(rd.done_count, 1u);
+    if (old == gridDim.x - 1) {
+      *rd.done_count = 0;  // every block has counted: ready for the next launch (and for graph replay)
+      const uint32_t e = rd.sig_epoch + (rd.epoch_base ? *rd.epoch_base : 0u);
+      __threadfence_system();
+      for (int p = 0; p < rd.sig_tp; p++) ptx::st_release_sys(rd.sig_peer_flag[p], e);
+    }
+  }
+}
+
+// Same computation with one warp per row and 16-byte accesses; hidden = VPL * 256.
+template <int VPL>
+__global__ void __launch_bounds__(256) layernorm_reduce_warp(TpReduce rd, int rows, uint32_t* status) {
+  __shared__ uint32_t s_ok;
+  if (threadIdx.x == 0) {
+    uint32_t ok = 1;
+    const uint32_t e = rd.epoch + (rd.epoch_base ? *rd.epoch_base : 0u);
+    for (int r = 0; r < rd.tp && ok; r++) ok = wait_flag_sys(rd.flags + r, e) ? 1u : 0u;
+    s_ok = ok;
+  }
+  __syncthreads();
+  if (!s_ok) {
+    if (threadIdx.x == 0 && status) atomicExch(status, GEMM_ERR_TP_REDUCE_WAIT);
+    return;
+  }
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
+  constexpr int H = VPL * 256;
+  if (row < rows) {
+    float v[VPL * 8];
+#pragma unroll
+    for (int c = 0; c < VPL; c++) {
+      const int col = (c * 32 + lane) * 8;
+      if (rd.bias) {
+        const float4 b0 = __ldg(reinterpret_cast<const float4*>(rd.bias + col));
+        const float4 b1 = __ldg(reinterpret_cast<const float4*>(rd.bias + col + 4));
+        v[c * 8 + 0] = b0.x; v[c * 8 + 1] = b0.y; v[c * 8 + 2] = b0.z; v[c * 8 + 3] = b0.w;
+        v[c * 8 + 4] = b1.x; v[c * 8 + 5] = b1.y; v[c * 8 + 6] = b1.z; v[c * 8 + 7] = b1.w;
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; j++) v[c * 8 + j] = 0.f;
+      }
+    }
+    auto add_row = [&](const __nv_bfloat16* base) {
+#pragma unroll
+      for (int c = 0; c < VPL; c++) {
+        // slots are written by peers through NVLink: read them past L1
+        const uint4 q = __ldcg(reinterpret_cast<const uint4*>(base + (size_t)row * H + (c * 32 + lane) * 8));
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+#pragma unroll
+        for (int t = 0; t < 4; t++) {
+          const float2 f = __bfloat1622float2(h[t]);
+          v[c * 8 + 2 * t] += f.x;
+          v[c * 8 + 2 * t + 1] += f.y;
+        }
+      }
+    };
+    for (int r = 0; r < rd.tp; r++) add_row(rd.slots[r]);
+    if (rd.residual) add_row(rd.residual);
+    float s = 0.f;
+#pragma unroll
+    for (int j = 0; j < VPL * 8; j++) s += v[j];
+#pragma unroll
+    for (int o = 16; o; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    const float mean = s / H;
+    float q = 0.f;
+#pragma unroll
+    for (int j = 0; j < VPL * 8; j++) q += (v[j] - mean) * (v[j] - mean);
+#pragma unroll
+    for (int o = 16; o; o >>= 1) q += __shfl_xor_sync(0xffffffffu, q, o);
+    const float rstd = rsqrtf(q / H + rd.eps);
+#pragma unroll
+    for (int c = 0; c < VPL; c++) {
+      const int col = (c * 32 + lane) * 8;
+      float g[8], b[8];
+      *reinterpret_cast<float4*>(g) = __ldg(reinterpret_cast<const float4*>(rd.gamma + col));
+      *reinterpret_cast<float4*>(g + 4) = __ldg(reinterpret_cast<const float4*>(rd.gamma + col + 4));
+      *reinterpret_cast<float4*>(b) = __ldg(reinterpret_cast<const float4*>(rd.beta + col));
+      *reinterpret_cast<float4*>(b + 4) = __ldg(reinterpret_cast<const float4*>(rd.beta + col + 4));
+      uint4 o;
+      __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+      for (int t = 0; t < 4; t++)
+        h[t] = __floats2bfloat162_rn((v[c * 8 + 2 * t] - mean) * rstd * g[2 * t] + b[2 * t],
+                                     (v[c * 8 + 2 * t + 1] - mean) * rstd * g[2 * t + 1] + b[2 * t + 1]);
+      *reinterpret_cast<uint4*>(rd.out + (size_t)row * H + col) = o;
+    }
+  }
+  reduce_signal(rd);
 }
 
 int num_sms() {
@@ -504,6 +651,21 @@ cudaError_t srpc_tp_wait(const uint32_t* flags, int n, uint32_t epoch, const uin
   return cudaGetLastError();
 }
 
+// Start of a pass in one launch: wait until flags[0..n) have reached the current base, then advance the base.
+__global__ void tp_begin_kernel(const uint32_t* flags, int n, uint32_t* epoch_base, uint32_t delta, uint32_t* status) {
+  const int i = threadIdx.x;
+  if (i < n && !wait_flag_sys(flags + i, *epoch_base) && status) atomicExch(status, GEMM_ERR_TP_SRC_WAIT);
+  __syncwarp();
+  if (i == 0) *epoch_base += delta;
+}
+
+cudaError_t srpc_tp_begin(const uint32_t* flags, int n, uint32_t* epoch_base, uint32_t delta, uint32_t* status,
+                          cudaStream_t stream) {
+  if (n < 1 || n > 32 || !epoch_base) return cudaErrorInvalidValue;
+  tp_begin_kernel<<<1, 32, 0, stream>>>(flags, n, epoch_base, delta, status);
+  return cudaGetLastError();
+}
+
 __global__ void tp_bump_kernel(uint32_t* word, uint32_t delta) { *word += delta; }
 
 cudaError_t srpc_tp_bump(uint32_t* word, uint32_t delta, cudaStream_t stream) {
@@ -513,6 +675,13 @@ cudaError_t srpc_tp_bump(uint32_t* word, uint32_t delta, cudaStream_t stream) {
 
 cudaError_t srpc_layernorm_reduce(const TpReduce& rd, int rows, uint32_t* status, cudaStream_t stream) {
   if (rd.hidden > 2048 || rd.tp < 1 || rd.tp > TP_MAX_RANKS) return cudaErrorInvalidValue;
-  layernorm_reduce<<<rows, 256, 0, stream>>>(rd, status);
+  bool aligned = (((uintptr_t)rd.out | (uintptr_t)rd.residual | (uintptr_t)rd.bias | (uintptr_t)rd.gamma | (uintptr_t)rd.beta) & 15) == 0;
+  for (int r = 0; r < rd.tp; r++) aligned = aligned && (((uintptr_t)rd.slots[r]) & 15) == 0;
+  const int blocks = (rows + 7) / 8;
+  if (aligned && rd.hidden == 1024) layernorm_reduce_warp<4><<<blocks, 256, 0, stream>>>(rd, rows, status);
+  else if (aligned && rd.hidden == 768) layernorm_reduce_warp<3><<<blocks, 256, 0, stream>>>(rd, rows, status);
+  else if (aligned && rd.hidden == 512) layernorm_reduce_warp<2><<<blocks, 256, 0, stream>>>(rd, rows, status);
+  else if (aligned && rd.hidden == 256) layernorm_reduce_warp<1><<<blocks, 256, 0, stream>>>(rd, rows, status);
+  else layernorm_reduce<<<rows, 256, 0, stream>>>(rd, status);
   return cudaGetLastError();
 }

@@ -49,6 +49,12 @@ struct TpReduce {
   const float *gamma, *beta;
   __nv_bfloat16* out;
   float eps;
+  // Optional: when the last block has written its rows, publish `sig_epoch` (+ *epoch_base) in every peer's flag word,
+  // so that no separate signalling launch is needed.  `done_count` is a zeroed device word owned by the caller.
+  int sig_tp;
+  uint32_t sig_epoch;
+  uint32_t* sig_peer_flag[TP_MAX_RANKS];
+  uint32_t* done_count;
 };
 
 // D = act(A . B^T + bias); A is [M, K] with M/128 divisible by tp.  With tp.mblock_ready set, remote row blocks of A
@@ -60,6 +66,9 @@ cudaError_t srpc_tp_signal(const TpSignal& sig, cudaStream_t stream);
 // Stream-ordered bounded wait until flags[0..n) >= epoch (+ *epoch_base); a timeout sets *status.
 cudaError_t srpc_tp_wait(const uint32_t* flags, int n, uint32_t epoch, const uint32_t* epoch_base, uint32_t* status,
                          cudaStream_t stream);
+// srpc_tp_wait(flags, n, 0, epoch_base) followed by srpc_tp_bump(epoch_base, delta), as one launch.
+cudaError_t srpc_tp_begin(const uint32_t* flags, int n, uint32_t* epoch_base, uint32_t delta, uint32_t* status,
+                          cudaStream_t stream);
 // *word += delta, stream ordered (advances the step-number base between forward passes).
 cudaError_t srpc_tp_bump(uint32_t* word, uint32_t delta, cudaStream_t stream);
 cudaError_t srpc_layernorm_reduce(const TpReduce& rd, int rows, uint32_t* status, cudaStream_t stream);

@@ -63,7 +63,7 @@ class BertClassifierTP:
                     "ctx": torch.empty((T, Hl), dtype=bf, device=dev), "ffn": torch.empty((T, Fl), dtype=bf, device=dev),
                     "pooled": torch.empty((batch, H), dtype=bf, device=dev),
                     "logits": torch.empty((batch, 8), dtype=torch.float32, device=dev)}
-        self.kernels_per_forward = 4 + 10 * cfg.layers + 5
+        self.kernels_per_forward = 3 + 8 * cfg.layers + 5
 
     def forward(self, ids: torch.Tensor, out: torch.Tensor | None = None, d_stub: int = 0) -> torch.Tensor:
         """``ids``: int32 ``[batch, seq]`` (identical on every rank).  Returns fp32 logits ``[batch, num_labels]``."""
@@ -81,12 +81,11 @@ class BertClassifierTP:
             ops.gemm(p[q + "v.w"], t.gathered["A"], out=b["vt"])  # V^T from the gathered activations
             ops.attention_tc(b["qk"], b["vt"], B, S, self.heads_local, v_bias=p[q + "v.b"], out=b["ctx"])
             t.gemm_rs(b["ctx"], p[q + "o.w"], "RS1", e)
-            t.ln_reduce("RS1", e, p[q + "o.b"], t.shard("A"), p[q + "ln1.g"], p[q + "ln1.b"], out=t.shard("B"))
-            t.signal("B", e)
+            t.ln_reduce("RS1", e, p[q + "o.b"], t.shard("A"), p[q + "ln1.g"], p[q + "ln1.b"], out=t.shard("B"), signal=("B", e))
             t.ag_gemm("B", p[q + "f1.w"], e, bias=p[q + "f1.b"], act="gelu", out=b["ffn"])
             t.gemm_rs(b["ffn"], p[q + "f2.w"], "RS2", e)
-            t.ln_reduce("RS2", e, p[q + "f2.b"], t.shard("B"), p[q + "ln2.g"], p[q + "ln2.b"], out=t.shard("A"))
-            t.signal("A", e + 1)
+            t.ln_reduce("RS2", e, p[q + "f2.b"], t.shard("B"), p[q + "ln2.g"], p[q + "ln2.b"], out=t.shard("A"),
+                        signal=("A", e + 1))
         t.ag_gemm("A", None, cfg.layers + 1)  # plain all-gather of the final hidden states
         t.end_step()
         x = t.gathered["A"]

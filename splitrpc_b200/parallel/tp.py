@@ -43,6 +43,7 @@ class TensorParallel:
         self.mblock_ready = {k: torch.zeros(tokens // 128, dtype=torch.int32, device=device) for k in ("A", "B")}
         self.owner_count = torch.zeros(8, dtype=torch.int32, device=device)
         self.epoch_base = torch.zeros(1, dtype=torch.int32, device=device)
+        self.done_count = torch.zeros(1, dtype=torch.int32, device=device)
         a.barrier()
 
     # ------------------------------------------------------------------ helpers
@@ -60,9 +61,8 @@ class TensorParallel:
         this rank's buffers), then advances the step-number base.  Captured into graphs like any other launch."""
         # Pass f ends by publishing DONE = base(f) (the base after its own bump); before bumping, the current base is
         # exactly that value (0 before the first pass, which the zero-initialised flags satisfy).
-        _C.tp_wait(self.flags[self._site["DONE"]].data_ptr(), self.tp, 0, self.epoch_base.data_ptr(),
-                   status_word().data_ptr(), _stream())
-        _C.tp_bump(self.epoch_base.data_ptr(), self.STEP, _stream())
+        _C.tp_begin(self.flags[self._site["DONE"]].data_ptr(), self.tp, self.epoch_base.data_ptr(), self.STEP,
+                    status_word().data_ptr(), _stream())
 
     def end_step(self) -> None:
         """End of a forward pass: tells every peer that this rank no longer reads their buffers."""
@@ -100,11 +100,18 @@ class TensorParallel:
                    _stream(), self.epoch_base.data_ptr())
 
     def ln_reduce(self, site: str, epoch: int, bias: torch.Tensor, residual: torch.Tensor | None, gamma: torch.Tensor,
-                  beta: torch.Tensor, out: torch.Tensor, eps: float = 1e-12) -> torch.Tensor:
-        """``out = LN(sum over source ranks of the site's slots + bias + residual)`` on this rank's rows."""
+                  beta: torch.Tensor, out: torch.Tensor, eps: float = 1e-12, signal: tuple[str, int] | None = None) -> torch.Tensor:
+        """``out = LN(sum over source ranks of the site's slots + bias + residual)`` on this rank's rows.
+
+        ``signal=(which, epoch)`` makes the kernel's last block tell every peer that this rank's shard of gathered
+        buffer ``which`` (normally ``out``) holds that step, instead of a separate :meth:`signal` launch."""
         s = self.slots[site]
         slot_ptrs = [s[r].data_ptr() for r in range(self.tp)]
+        sig_flags, sig_epoch, done = [], 0, 0
+        if signal is not None:
+            sig_flags = [self._flag_ptr(signal[0], p, self.rank) for p in range(self.tp)]
+            sig_epoch, done = signal[1], self.done_count.data_ptr()
         _C.layernorm_reduce(slot_ptrs, self.flags[self._site[site]].data_ptr(), epoch, _ptr(bias), _ptr(residual),
                             gamma.data_ptr(), beta.data_ptr(), out.data_ptr(), self.rows, self.hidden, eps,
-                            status_word().data_ptr(), _stream(), self.epoch_base.data_ptr())
+                            status_word().data_ptr(), _stream(), self.epoch_base.data_ptr(), sig_flags, sig_epoch, done)
         return out
