@@ -61,7 +61,9 @@ def _headers_digest() -> str:
 
 def _obj_for(src: Path, hdr_digest: str, verbose_ptxas: bool) -> tuple[Path, list[str]]:
     is_cu = src.suffix == ".cu"
-    flags = (NVCC_FLAGS + (["-Xptxas", "-v"] if verbose_ptxas else [])) if is_cu else CXX_FLAGS
+    # SPLITRPC_NVCC_EXTRA: extra nvcc flags for a one-off build, e.g. -DSRPC_GEMM_TRACE (phase time stamps in the GEMM)
+    extra = os.environ.get("SPLITRPC_NVCC_EXTRA", "").split()
+    flags = (NVCC_FLAGS + extra + (["-Xptxas", "-v"] if verbose_ptxas else [])) if is_cu else CXX_FLAGS
     key = hashlib.sha256((src.read_text() + hdr_digest + " ".join(flags)).encode()).hexdigest()[:16]
     obj = BUILD / f"{src.stem}.{key}.o"
     if is_cu:

@@ -99,6 +99,13 @@ void bind_ops(py::module_& m) {
         py::arg("residual") = 0, py::arg("act") = 0, py::arg("status") = 0, py::arg("stream") = 0, py::arg("impl") = 2,
         py::arg("pix_stride") = 0, py::arg("row_stride") = 0, py::arg("img_stride") = 0);
 
+  m.def("gemm_trace", [](bool two_sm) {
+    unsigned long long t[12] = {0};
+    int n = two_sm ? srpc_gemm2_trace_read(t, 12) : srpc_gemm_trace_read(t, 10);
+    std::vector<uint64_t> v(t, t + n);
+    return v;
+  }, py::arg("two_sm") = false);
+
   // ---- tensor-parallel fused kernels
   m.def("gemm_tp",
         [](uintptr_t a, int lda, uintptr_t b, int ldb, int M, int N, int K, uintptr_t out, int ldo, uintptr_t bias, int act,

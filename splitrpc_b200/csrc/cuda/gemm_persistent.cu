@@ -48,7 +48,8 @@ constexpr int RES_DIST = 2;
 // warp 0 TMA, warp 1 MMA, then two epilogue warps per TMEM lane quarter (each takes half of the tile's columns)
 template <int BN>
 struct Threads {
-  static constexpr int EPI = BN == 256 ? 512 : 256;   // BN = 256: four warps per quarter, 64 columns each
+  // BN = 256 / 192: four / three warps per quarter, 64 columns each
+  static constexpr int EPI = BN == 256 ? 512 : (BN == 192 ? 384 : 256);
   static constexpr int TOTAL = 64 + EPI;
 };
 
@@ -75,7 +76,7 @@ struct TileParams {
   int res_tma;
 };
 
-__device__ __forceinline__ float gelu_f(float x) { return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f)); }
+__device__ __forceinline__ float gelu_f(float x) { return ptx::gelu_erf_fast(x); }
 
 __device__ __forceinline__ void named_bar_sync(int id, int count) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
@@ -102,6 +103,17 @@ __device__ __forceinline__ void tma_store_4d(const CUtensorMap* m, const void* s
                "r"(ptx::smem_u32(smem_src)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
                : "memory");
 }
+
+// Optional phase time stamps of block 0 (build with -DSRPC_GEMM_TRACE): where a short kernel spends its time.
+#ifdef SRPC_GEMM_TRACE
+__device__ unsigned long long g_gemm_trace[16];
+#define GEMM_TRACE(slot)                                                         \
+  do {                                                                           \
+    if (blockIdx.x == 0) g_gemm_trace[slot] = ptx::globaltimer_ns();             \
+  } while (0)
+#else
+#define GEMM_TRACE(slot) ((void)0)
+#endif
 
 struct TileCoord {
   int m_idx, n_idx;
@@ -168,18 +180,23 @@ gemm_conv_persistent(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   uint8_t* a_ring = smem + panel_bytes;
   // Four TMEM accumulators: up to four tiles can be between "MMA issued" and "accumulator read back", which hides
   // the commit -> wake-up -> tcgen05.ld -> release round trip of short (few k-block) tiles.
-  constexpr int ACC = BN == 256 ? 2 : 4;
-  constexpr int ACC_LOG2 = BN == 256 ? 1 : 2;
+  constexpr int ACC = BN >= 192 ? 2 : 4;
+  constexpr int ACC_LOG2 = BN >= 192 ? 1 : 2;
+  constexpr int ACC_STRIDE = BN == 192 ? 256 : BN;  // TMEM columns between accumulators (allocation is a power of two)
   static_assert(OB >= 1 && OB <= MAX_OUT_BUFS, "output staging buffers");
   __shared__ __align__(8) uint64_t tmem_full_bar[ACC];
   __shared__ __align__(8) uint64_t tmem_empty_bar[ACC];
   __shared__ __align__(8) uint64_t res_full_bar[MAX_OUT_BUFS];
   __shared__ uint32_t tmem_base_smem;
   __shared__ uint32_t s_error;
+  // Bias of the current tile's columns, double-buffered over consecutive tiles: fetched while the accumulator is still
+  // being computed, then read as broadcasts (a global load per chunk would sit on the epilogue's critical path).
+  __shared__ __align__(16) float s_bias[2][BN];
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
+    GEMM_TRACE(0);
     ptx::mbar_init(&bpanel_bar, 1);
     for (int s = 0; s < MAX_STAGES; s++) {
       ptx::mbar_init(&full_bar[s], 1);
@@ -197,51 +214,73 @@ gemm_conv_persistent(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     if (use_tma_store) ptx::prefetch_tmap(&tmap_out);
     if (p.res_tma) ptx::prefetch_tmap(&tmap_res);
   }
+  // TMA producer = thread 0.  Its state lives across two calls: the first fills the (initially free) ring right after
+  // the barriers exist, before the block-wide set-up barrier, so that the first operands are already in flight while
+  // tensor memory is being allocated; the second runs the rest of the schedule.
+  int pr_s = 0, pr_j = 0, pr_kb = 0;
+  uint32_t pr_ph = 0;
+  bool pr_more = true;
+  auto produce = [&](int budget) {
+    const uint32_t b_tx = p.b_stationary ? 0u : (uint32_t)B_BYTES;
+    TileCoord tc;
+    while (pr_more && budget > 0) {
+      if (!get_tile(p, pr_j, &tc) || *(volatile uint32_t*)&s_error != 0) {
+        pr_more = false;
+        break;
+      }
+      for (; pr_kb < p.num_kb && budget > 0; pr_kb++, budget--) {
+        if (!ptx::mbar_wait(&empty_bar[pr_s], pr_ph ^ 1u)) {
+          atomicExch(&s_error, GEMM_ERR_PRODUCER_WAIT);
+          pr_more = false;
+          return;
+        }
+        uint8_t* sa = a_ring + (size_t)pr_s * a_stride;
+        if (p.mode == 0) {
+          ptx::mbar_expect_tx(&full_bar[pr_s], (uint32_t)A_BYTES + b_tx);
+          ptx::tma_load_2d(sa, &tmap_a, &full_bar[pr_s], pr_kb * BK, tc.m_idx * BM);
+        } else {
+          ptx::mbar_expect_tx(&full_bar[pr_s], p.a_box_bytes + b_tx);
+          const int tap = pr_kb / p.cblocks, cb = pr_kb - tap * p.cblocks;
+          const int fr = tap / p.s, fs = tap - fr * p.s;
+          tma_load_4d_box(sa, &tmap_a, &full_bar[pr_s], cb * BK, tc.w0 * p.stride + fs - p.pad,
+                          tc.h0 * p.stride + fr - p.pad, tc.img0);
+        }
+        if (!p.b_stationary) ptx::tma_load_2d(sa + A_BYTES, &tmap_b, &full_bar[pr_s], pr_kb * BK, tc.n_idx * BN);
+        if (pr_j == 0 && pr_kb == 0) GEMM_TRACE(2);
+        if (++pr_s == nst) {
+          pr_s = 0;
+          pr_ph ^= 1u;
+        }
+      }
+      if (pr_kb == p.num_kb) {
+        pr_kb = 0;
+        pr_j++;
+      }
+    }
+  };
+  if (threadIdx.x == 0) {
+    TileCoord tc;
+    if (p.b_stationary && get_tile(p, 0, &tc)) {
+      ptx::mbar_expect_tx(&bpanel_bar, (uint32_t)panel_bytes);
+      for (int kb = 0; kb < p.num_kb; kb++)
+        ptx::tma_load_2d(smem + (size_t)kb * B_BYTES, &tmap_b, &bpanel_bar, kb * BK, tc.n_idx * BN);
+    }
+    produce(nst < 2 ? nst : 2);  // more would hold thread 0 (and with it the set-up barrier) behind a full TMA queue
+  }
   if (warp == 1) {
-    ptx::tmem_alloc(&tmem_base_smem, ACC * BN);
+    ptx::tmem_alloc(&tmem_base_smem, ACC * ACC_STRIDE);
     ptx::tmem_relinquish();
   }
   ptx::tc_fence_before();
   __syncthreads();
   ptx::tc_fence_after();
   const uint32_t tmem_base = tmem_base_smem;
+  if (threadIdx.x == 0) GEMM_TRACE(1);
 
-  if (warp == 0) {
-    if (ptx::elect_one()) {
-      int s = 0;          // ring position and phase, advanced per k-block across tiles (no division in the loop)
-      uint32_t ph = 0;
-      TileCoord tc;
-      if (p.b_stationary && get_tile(p, 0, &tc)) {
-        ptx::mbar_expect_tx(&bpanel_bar, (uint32_t)panel_bytes);
-        for (int kb = 0; kb < p.num_kb; kb++)
-          ptx::tma_load_2d(smem + (size_t)kb * B_BYTES, &tmap_b, &bpanel_bar, kb * BK, tc.n_idx * BN);
-      }
-      const uint32_t b_tx = p.b_stationary ? 0u : (uint32_t)B_BYTES;
-      for (int j = 0; get_tile(p, j, &tc) && *(volatile uint32_t*)&s_error == 0; j++) {
-        for (int kb = 0; kb < p.num_kb; kb++) {
-          if (!ptx::mbar_wait(&empty_bar[s], ph ^ 1u)) {
-            atomicExch(&s_error, GEMM_ERR_PRODUCER_WAIT);
-            break;
-          }
-          uint8_t* sa = a_ring + (size_t)s * a_stride;
-          if (p.mode == 0) {
-            ptx::mbar_expect_tx(&full_bar[s], (uint32_t)A_BYTES + b_tx);
-            ptx::tma_load_2d(sa, &tmap_a, &full_bar[s], kb * BK, tc.m_idx * BM);
-          } else {
-            ptx::mbar_expect_tx(&full_bar[s], p.a_box_bytes + b_tx);
-            const int tap = kb / p.cblocks, cb = kb - tap * p.cblocks;
-            const int fr = tap / p.s, fs = tap - fr * p.s;
-            tma_load_4d_box(sa, &tmap_a, &full_bar[s], cb * BK, tc.w0 * p.stride + fs - p.pad,
-                            tc.h0 * p.stride + fr - p.pad, tc.img0);
-          }
-          if (!p.b_stationary) ptx::tma_load_2d(sa + A_BYTES, &tmap_b, &full_bar[s], kb * BK, tc.n_idx * BN);
-          if (++s == nst) {
-            s = 0;
-            ph ^= 1u;
-          }
-        }
-      }
-    }
+  if (threadIdx.x == 0) {
+    produce(1 << 30);  // the rest of the k-blocks, paced by the MMA warp through the empty barriers
+  } else if (warp == 0) {
+    // lanes 1-31 of the producer warp have nothing to do
   } else if (warp == 1) {
     if (ptx::elect_one()) {
       const uint32_t idesc = ptx::umma_idesc_bf16(BM, BN);
@@ -261,7 +300,7 @@ gemm_conv_persistent(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
           break;
         }
         ptx::tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * BN;
+        const uint32_t d_tmem = tmem_base + acc * ACC_STRIDE;
         bool ok = true;
         for (int kb = 0; kb < p.num_kb; kb++) {
           if (!ptx::mbar_wait(&full_bar[s], ph)) {
@@ -270,6 +309,7 @@ gemm_conv_persistent(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
             break;
           }
           ptx::tc_fence_after();
+          if (j == 0 && kb == 0) GEMM_TRACE(3);
           const uint32_t sa = ptx::smem_u32(a_ring + (size_t)s * a_stride);
           const uint32_t sb = p.b_stationary ? ptx::smem_u32(smem + (size_t)kb * B_BYTES) : sa + A_BYTES;
 #pragma unroll
@@ -284,12 +324,13 @@ gemm_conv_persistent(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         }
         if (!ok) break;
         ptx::umma_commit(&tmem_full_bar[acc]);
+        if (j == 0) GEMM_TRACE(4);
       }
     }
   } else {
     // ---------------- epilogue warps (8): warp pair (w, w+4) shares a TMEM lane quarter and splits the columns
     constexpr int CPW = BN / (Threads<BN>::EPI / 128);  // columns per warp
-    constexpr bool LEAN = BN == 256;     // 18 warps per CTA: keep the accumulator in registers one chunk at a time
+    constexpr bool LEAN = BN >= 192;     // 14-18 warps per CTA: keep the accumulator in registers one chunk at a time
     constexpr int NCH = CPW / 32;        // 32-column chunks per warp
     constexpr int EPI_THREADS = Threads<BN>::EPI;
     const int warp_q = warp & 3;
@@ -343,8 +384,10 @@ gemm_conv_persistent(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
 #pragma unroll
         for (int j = 0; j < CPW / 8; j++) resq[j] = __ldg(reinterpret_cast<const uint4*>(rp) + j);
       }
+      float* bias_s = s_bias[local & 1u];
+      if (ep.bias && et < BN) bias_s[et] = (n0 + et < p.N) ? __ldg(ep.bias + n0 + et) : 0.f;
       // Each thread's wait is bounded; the vote makes the outcome uniform so that no
-      // thread is left alone at a later barrier.
+      // thread is left alone at a later barrier.  (It also orders the bias writes before their reads.)
       bool mine = (*(volatile uint32_t*)&s_error == 0) && ptx::mbar_wait(&tmem_full_bar[acc], (local >> ACC_LOG2) & 1u);
       if (res_tma && mine) mine = ptx::mbar_wait(&res_full_bar[local % OB], (local / OB) & 1u);
       if (!named_bar_all(2, EPI_THREADS, mine)) {
@@ -352,6 +395,7 @@ gemm_conv_persistent(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         break;
       }
       ptx::tc_fence_after();
+      if (j == 0 && et == 0) GEMM_TRACE(5);
       if (use_tma_store_mode == 5) {  // experiment: release the accumulator without reading it
         ptx::tc_fence_before();
         __syncwarp();
@@ -359,7 +403,7 @@ gemm_conv_persistent(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         continue;
       }
       uint32_t r[LEAN ? 32 : CPW];
-      const uint32_t t_addr = tmem_base + acc * BN + ((uint32_t)(warp_q * 32) << 16) + (uint32_t)cbase;
+      const uint32_t t_addr = tmem_base + acc * ACC_STRIDE + ((uint32_t)(warp_q * 32) << 16) + (uint32_t)cbase;
       if (!LEAN) {
 #pragma unroll
         for (int ch = 0; ch < NCH; ch++) ptx::tmem_ld_32x32b_x32(t_addr + ch * 32, r + ch * 32);
@@ -397,19 +441,13 @@ gemm_conv_persistent(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
 #pragma unroll
         for (int j = 0; j < 32; j++) v[j] = __uint_as_float(r[(LEAN ? 0 : ch * 32) + j]);
         if (ep.bias) {
-          if (col0 + 32 <= p.N) {
 #pragma unroll
-            for (int j = 0; j < 32; j += 4) {
-              float4 b4 = __ldg(reinterpret_cast<const float4*>(ep.bias + col0 + j));
-              v[j] += b4.x;
-              v[j + 1] += b4.y;
-              v[j + 2] += b4.z;
-              v[j + 3] += b4.w;
-            }
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; j++)
-              if (col0 + j < p.N) v[j] += __ldg(ep.bias + col0 + j);
+          for (int j = 0; j < 32; j += 4) {
+            const float4 b4 = *reinterpret_cast<const float4*>(bias_s + c + j);
+            v[j] += b4.x;
+            v[j + 1] += b4.y;
+            v[j + 2] += b4.z;
+            v[j + 3] += b4.w;
           }
         }
         if (res_tma) {
@@ -505,6 +543,7 @@ gemm_conv_persistent(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
             else tma_store_4d(&tmap_out, src, n0 + hcol * 64, tc.w0, tc.h0, tc.img0);
           }
           ptx::bulk_commit();
+          if (j == 0) GEMM_TRACE(6);
           if (res_tma) {
             // The tile RES_DIST ahead takes the buffer of the tile OB - RES_DIST back, so all stores but the last
             // OB - RES_DIST must have been read.
@@ -514,10 +553,15 @@ gemm_conv_persistent(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         }
       }
     }
-    if (use_tma_store && et == 0) ptx::bulk_wait_all<0>();
+    if (use_tma_store && et == 0) {
+      GEMM_TRACE(7);
+      ptx::bulk_wait_all<0>();
+      GEMM_TRACE(8);
+    }
   }
   ptx::tc_fence_before();
   __syncthreads();
+  if (threadIdx.x == 0) GEMM_TRACE(9);
   if (s_error != 0) {
     if (threadIdx.x == 0 && status) atomicExch(status, s_error);
     __nanosleep(1000000);  // let loads that are still in flight land before the block leaves
@@ -525,7 +569,7 @@ gemm_conv_persistent(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   }
   if (warp == 1) {
     ptx::tc_fence_after();
-    ptx::tmem_dealloc(tmem_base, ACC * BN);
+    ptx::tmem_dealloc(tmem_base, ACC * ACC_STRIDE);
   }
 }
 
@@ -623,7 +667,7 @@ cudaError_t launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorM
   p.b_stationary = 0;
   p.ctas_per_n = 0;
   static const int allow_bs = [] { const char* e = getenv("SPLITRPC_GEMM_BSTAT"); return e ? atoi(e) : 1; }();
-  if (allow_bs && p.num_kb <= (BN == 256 ? 2 : 4) && p.tiles_n <= num_sms()) {
+  if (allow_bs && p.num_kb <= (BN >= 192 ? 2 : 4) && p.tiles_n <= num_sms()) {
     const int per_n = std::min(num_sms() / p.tiles_n, p.tiles_m);
     if (per_n >= 1 && p.tiles_m >= 2 * per_n) {  // at least two tiles per CTA to pay for the panel load
       p.b_stationary = 1;
@@ -639,18 +683,72 @@ cudaError_t dispatch(int bn, const CUtensorMap& ta, const CUtensorMap& tb, const
                      const TileParams& p, const GemmEpilogue& ep, int use_tma_store, uint32_t* status, cudaStream_t st) {
   if (bn == 64) return launch<64, 6, OUT_BUFS>(ta, tb, to, tr, p, ep, use_tma_store, status, st);
   if (bn == 256) return launch<256, 3, 1>(ta, tb, to, tr, p, ep, use_tma_store, status, st);
+  if (bn == 192) return launch<192, 4, 1>(ta, tb, to, tr, p, ep, use_tma_store, status, st);
   return launch<128, 4, OUT_BUFS>(ta, tb, to, tr, p, ep, use_tma_store, status, st);
 }
 
 }  // namespace
 
-// Tile width: 256 columns (one MMA instruction covers the whole tile row, half as many instruction issues and
-// A re-reads) when there are enough tiles to fill the GPU; 64 for narrow outputs; else 128.
-static int pick_bn(int N, int tiles_m, bool bf16_out) {
+cudaError_t srpc_tensor_map_2d(CUtensorMap* m, const void* ptr, uint64_t inner, uint64_t outer, uint64_t row_stride_bytes,
+                               uint32_t box_inner, uint32_t box_outer) {
+  return map_2d(m, ptr, inner, outer, row_stride_bytes, box_inner, box_outer);
+}
+
+int srpc_gemm_trace_read(unsigned long long* out, int n) {
+#ifdef SRPC_GEMM_TRACE
+  if (n > 16) n = 16;
+  if (cudaMemcpyFromSymbol(out, g_gemm_trace, n * sizeof(unsigned long long)) != cudaSuccess) return 0;
+  return n;
+#else
+  (void)out;
+  (void)n;
+  return 0;
+#endif
+}
+
+// Tile shape.  Narrow outputs take 64 columns.  Otherwise the shape with the lowest estimated time wins: rounds of
+// tiles over the SMs (or SM pairs) x (k-blocks x time per k-block + hand-over).  The per-k-block times are what the
+// kernels measure on large problems: the one-SM 128-wide tile is bound by the issue rate of its four MMAs per
+// k-block, the wider one-SM tiles by operand delivery, the two-SM tiles (256 rows per SM pair, gemm_2sm.cu) by the
+// tensor pipe.  Returns the width; *two_sm says which kernel.
+static int pick_tile(int M, int N, int num_kb, bool bf16_out, bool allow_two_sm, bool* two_sm) {
   static const int allow256 = [] { const char* e = getenv("SPLITRPC_GEMM_BN256"); return e ? atoi(e) : 1; }();
+  static const int allow192 = [] { const char* e = getenv("SPLITRPC_GEMM_BN192"); return e ? atoi(e) : 1; }();
+  *two_sm = false;
   if (N <= 64) return 64;
-  if (allow256 && bf16_out && N >= 256 && ((N % 256) == 0 || N >= 1024) && (long)tiles_m * ((N + 255) / 256) >= 96) return 256;
-  return 128;
+  struct Cand {
+    int bn, rows, units;
+    double t_kb;  // microseconds per 64-deep k-block
+    bool pair;
+  };
+  const int sms = num_sms();
+  // (the pair kernels run at about 0.4 us per k-block whatever their width: the stage ring covers one round trip
+  //  MMA done -> stage free -> TMA -> stage full, not more)
+  const Cand cands[6] = {{256, 256, sms / 2, 0.40, true},  {192, 256, sms / 2, 0.40, true}, {128, 256, sms / 2, 0.40, true},
+                         {256, 128, sms, 0.49, false},     {192, 128, sms, 0.37, false},    {128, 128, sms, 0.27, false}};
+  int best = 128;
+  double best_cost = 1e30;
+  for (const Cand& c : cands) {
+    // pairs only where the k loop dominates: short-K shapes are bound by memory and keep the B-stationary schedule
+    if (c.pair && !(allow_two_sm && M >= 256 && num_kb >= 8)) continue;
+    if (c.bn == 256 && !(allow256 && bf16_out && N >= 256 && ((N % 256) == 0 || N >= 1024))) continue;
+    if (c.bn == 192 && !(allow192 && bf16_out && N >= 192 && ((N % 192) == 0 || N >= 1536))) continue;
+    if (c.pair && c.bn == 128 && (N % 128) != 0 && N < 1024) continue;
+    const long tiles = (long)((M + c.rows - 1) / c.rows) * ((N + c.bn - 1) / c.bn);
+    const long rounds = (tiles + c.units - 1) / c.units;
+    const double cost = (double)rounds * (num_kb * c.t_kb + 0.25) + (c.pair ? 0.3 : 0.0);  // pairs: cluster set-up
+    if (cost < best_cost * 0.98) {  // near-ties go to the candidate listed first
+      best_cost = cost;
+      best = c.bn;
+      *two_sm = c.pair;
+    }
+  }
+  return best;
+}
+
+static int pick_bn(int N, int tiles_m, int num_kb, bool bf16_out) {
+  bool two_sm;
+  return pick_tile(tiles_m * BM, N, num_kb, bf16_out, false, &two_sm);
 }
 
 cudaError_t srpc_gemm_bf16_v2(const void* A, int lda, const void* B, int ldb, int M, int N, int K, const GemmEpilogue& ep,
@@ -665,10 +763,15 @@ cudaError_t srpc_gemm_bf16_v2(const void* A, int lda, const void* B, int ldb, in
     if (mode >= 2 && mode <= 5) use_tma_store = mode;
   }
   static const int allow_res_tma = [] { const char* e = getenv("SPLITRPC_GEMM_RES_TMA"); return e ? atoi(e) : 1; }();
+  // Short-K shapes are bound by memory and gain from the prefetched residual; with a long K the plain residual loads of
+  // the epilogue hide behind the next tile's MMAs and the tile width matters more.
   const bool res_tma = allow_res_tma && use_tma_store == 1 && ep.residual && (ep.ldr % 8) == 0 &&
-                       ((uintptr_t)ep.residual & 15) == 0;
-  // The residual ring lives in the output staging buffers, which the 256-wide tile has only one of.
-  const int bn = res_tma ? (N <= 64 ? 64 : 128) : pick_bn(N, (M + BM - 1) / BM, ep.out_fp32 == 0);
+                       ((uintptr_t)ep.residual & 15) == 0 && K <= 512;
+  // The residual ring lives in the output staging buffers, which the wide tiles have only one of.
+  bool two_sm = false;
+  const int bn = res_tma ? (N <= 64 ? 64 : 128)
+                         : pick_tile(M, N, (K + BK - 1) / BK, ep.out_fp32 == 0, srpc_gemm_2sm_eligible(M, N, K, ep), &two_sm);
+  if (two_sm) return srpc_gemm_bf16_2sm(A, lda, B, ldb, M, N, K, bn, ep, status, stream);
   TileParams p{};
   p.mode = 0;
   p.res_tma = res_tma ? 1 : 0;
@@ -740,7 +843,7 @@ cudaError_t srpc_conv_bf16_tma(const void* in, const void* weight, const ConvSha
   p.tiles_w = (cs.ow + p.pw - 1) / p.pw;
   p.tiles_h = (cs.oh + p.ph - 1) / p.ph;
   p.tiles_m = p.tiles_w * p.tiles_h * ((cs.n + p.pn - 1) / p.pn);
-  const int bn = pick_bn(cs.cout, p.tiles_m, true);
+  const int bn = pick_bn(cs.cout, p.tiles_m, p.num_kb, true);
   p.tiles_n = (cs.cout + bn - 1) / bn;
   p.a_box_bytes = (uint32_t)p.rows_used * 128u;
   CUtensorMap ta, tb, to;

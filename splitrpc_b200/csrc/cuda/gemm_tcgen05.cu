@@ -28,7 +28,7 @@ constexpr int UMMA_K = 16;
 constexpr int GEMM_THREADS = 192;  // warp 0 producer, warp 1 mma, warps 2-5 epilogue
 constexpr int CONV_THREADS = 320;  // warps 0-3 gather producers, warp 4 B-loader, warp 5 mma, warps 6-9 epilogue
 
-__device__ __forceinline__ float gelu_f(float x) { return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f)); }
+__device__ __forceinline__ float gelu_f(float x) { return ptx::gelu_erf_fast(x); }
 
 template <int BN>
 struct SmemLayout {

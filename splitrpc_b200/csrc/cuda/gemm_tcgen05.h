@@ -49,6 +49,21 @@ cudaError_t srpc_gemm_bf16_v2(const void* A, int lda, const void* B, int ldb, in
 cudaError_t srpc_conv_bf16_tma(const void* in, const void* weight, const ConvShape& cs, const GemmEpilogue& ep,
                                uint32_t* status, cudaStream_t stream);
 
+// Two-SM variant (CTA pairs, 256 x bn tiles with bn = 128, 192 or 256, tcgen05.mma.cta_group::2) for compute-bound
+// shapes; bf16 output with 16-byte aligned rows only.  srpc_gemm_bf16_v2 selects it by itself; SPLITRPC_GEMM_2SM=0
+// turns it off.
+bool srpc_gemm_2sm_eligible(int M, int N, int K, const GemmEpilogue& ep);
+cudaError_t srpc_gemm_bf16_2sm(const void* A, int lda, const void* B, int ldb, int M, int N, int K, int bn,
+                               const GemmEpilogue& ep, uint32_t* status, cudaStream_t stream);
+
+// Phase time stamps (ns, %globaltimer) of block 0 of the last persistent launch; returns 0 unless the library was
+// built with -DSRPC_GEMM_TRACE.  Slots: 0 entry, 1 set-up done, 2 first loads issued, 3 first operands landed,
+// 4 first tile's MMAs issued, 5 first accumulator ready, 6 first tile's store issued, 7 last epilogue done,
+// 8 stores drained, 9 all warps done.
+int srpc_gemm_trace_read(unsigned long long* out, int n);
+// Same for the two-SM kernel; slots 10 and 11 = operands of k-blocks 8 and 24 of the first tile landed.
+int srpc_gemm2_trace_read(unsigned long long* out, int n);
+
 // NHWC bf16 convolution as an implicit GEMM; cin must be a multiple of 64.
 cudaError_t srpc_conv_bf16(const void* in, const void* weight, const ConvShape& cs, const GemmEpilogue& ep,
                            uint32_t* status, cudaStream_t stream);

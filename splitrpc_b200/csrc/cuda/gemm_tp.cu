@@ -43,7 +43,7 @@ constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTE
 constexpr int OUT_HALF_BYTES = BM * 128, OUT_BYTES = 2 * OUT_HALF_BYTES;
 constexpr uint64_t FLAG_WAIT_NS = 2000000000ull;
 
-__device__ __forceinline__ float gelu_f(float x) { return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f)); }
+__device__ __forceinline__ float gelu_f(float x) { return ptx::gelu_erf_fast(x); }
 __device__ __forceinline__ void named_bar_sync(int id, int count) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
 }

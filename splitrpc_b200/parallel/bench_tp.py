@@ -22,10 +22,28 @@ from .tp import TensorParallel
 NVLINK_GBS = 770.0
 
 
-def _time(fn, iters, pre=None):
+def _time(fn, iters, pre=None, graph=True):
+    """Median CUDA-event time of ``fn`` (max over ranks).  With ``graph`` the launches of ``fn`` are captured once and
+    replayed, so the figure is the device time of the kernels and not the host's launch rate."""
     fn()
     torch.cuda.synchronize()
     dist.barrier()
+    if graph:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                fn()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        dist.barrier()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            fn()
+        fn = g.replay
+        fn()
+        torch.cuda.synchronize()
+        dist.barrier()
     ts = []
     for _ in range(iters):
         if pre:
@@ -50,6 +68,7 @@ def main():
     ap.add_argument("--ffn", type=int, default=4096)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--n-copy", type=int, default=16)
+    ap.add_argument("--no-graph", action="store_true", help="time eager launches instead of graph replays")
     args = ap.parse_args()
     rank, world, local_rank = init_distributed()
     dev = torch.device("cuda", local_rank)
@@ -68,6 +87,7 @@ def main():
     y = torch.empty((T, Fl), dtype=torch.bfloat16, device=dev)
     out = torch.empty((rows, H), dtype=torch.bfloat16, device=dev)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    use_graph = not args.no_graph
 
     # ---- fused all-gather -> GEMM
     def fused_ag():
@@ -77,7 +97,7 @@ def main():
         tpc.end_step()
 
     tpc.shard("A").copy_(x_shard)
-    t_ag = _time(fused_ag, args.iters, pre=flush.zero_)
+    t_ag = _time(fused_ag, args.iters, pre=flush.zero_, graph=use_graph)
     # baseline: NCCL all-gather then the same GEMM kernel on local memory
     gathered = torch.empty((T, H), dtype=torch.bfloat16, device=dev)
 
@@ -85,7 +105,8 @@ def main():
         dist.all_gather_into_tensor(gathered, x_shard)
         ops.gemm(gathered, w1, bias=b1, act="gelu", out=y)
 
-    t_ag_base = _time(nccl_ag, args.iters, pre=flush.zero_)
+    t_ag_base = _time(nccl_ag, args.iters, pre=flush.zero_, graph=use_graph)
+    t_ag_gemm = _time(lambda: ops.gemm(gathered, w1, bias=b1, act="gelu", out=y), args.iters, pre=flush.zero_, graph=use_graph)
 
     # ---- fused GEMM -> reduce-scatter + reduce/LayerNorm
     def fused_rs():
@@ -94,7 +115,7 @@ def main():
         tpc.ln_reduce("RS1", 1, b2, tpc.shard("A"), gamma, beta, out)
         tpc.end_step()
 
-    t_rs = _time(fused_rs, args.iters, pre=flush.zero_)
+    t_rs = _time(fused_rs, args.iters, pre=flush.zero_, graph=use_graph)
     partial = torch.empty((T, H), dtype=torch.bfloat16, device=dev)
     red = torch.empty((rows, H), dtype=torch.bfloat16, device=dev)
 
@@ -103,7 +124,8 @@ def main():
         dist.reduce_scatter_tensor(red, partial)
         ops.layernorm(red, gamma, beta, residual=x_shard, out=out)
 
-    t_rs_base = _time(nccl_rs, args.iters, pre=flush.zero_)
+    t_rs_base = _time(nccl_rs, args.iters, pre=flush.zero_, graph=use_graph)
+    t_rs_gemm = _time(lambda: ops.gemm(y, w2, out=partial), args.iters, pre=flush.zero_, graph=use_graph)
     ops.check_status()
     if rank == 0:
         fl = 2.0 * T * Fl * H
@@ -111,7 +133,9 @@ def main():
         nv_rs = (world - 1) * rows * H * 2          # bytes each rank pushes
         roof_ag = max(fl / (tf * 1e12), nv_ag / (NVLINK_GBS * 1e9)) * 1e3
         roof_rs = max(fl / (tf * 1e12), nv_rs / (NVLINK_GBS * 1e9)) * 1e3
-        print(f"tp={world} tokens={T} hidden={H} ffn={F} (local {Fl})")
+        print(f"tp={world} tokens={T} hidden={H} ffn={F} (local {Fl}), {'graph replays' if use_graph else 'eager launches'}")
+        print(f"the two GEMMs alone on local memory: {t_ag_gemm * 1e3:.1f} us ({fl / t_ag_gemm / 1e9:.0f} TFLOP/s), "
+              f"{t_rs_gemm * 1e3:.1f} us ({fl / t_rs_gemm / 1e9:.0f} TFLOP/s)")
         print(f"all-gather->GEMM      fused {t_ag * 1e3:8.1f} us   NCCL all-gather + GEMM {t_ag_base * 1e3:8.1f} us   "
               f"roofline {roof_ag * 1e3:6.1f} us -> {roof_ag / t_ag:.2f} of roofline ({tag} GEMM peak, 770 GB/s NVLink)")
         print(f"GEMM->reduce-scatter+LN fused {t_rs * 1e3:8.1f} us   GEMM + NCCL reduce-scatter + LN {t_rs_base * 1e3:8.1f} us   "

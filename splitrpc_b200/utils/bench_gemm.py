@@ -27,6 +27,8 @@ def main():
     ap.add_argument("--act", default=None)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--no-flush", action="store_true")
+    ap.add_argument("--graph", action="store_true", help="time graph replays of (flush, op) pairs minus the flushes alone")
+    ap.add_argument("--library", action="store_true", help="time PyTorch's cuBLAS / cuDNN call for the same shape instead")
     args = ap.parse_args()
     torch.cuda.set_device(0)
     hbm, tf, tag = _peaks()
@@ -39,6 +41,14 @@ def main():
         out = torch.empty(n, oh, ow, cout, dtype=torch.bfloat16, device="cuda")
         res = torch.randn_like(out) if args.residual else None
         fn = lambda: ops.conv2d_nhwc(x, wt, bias=bias, residual=res, stride=s, pad=pad, act=args.act, out=out)
+        if args.library:
+            import torch.nn.functional as F
+
+            torch.backends.cudnn.benchmark = True
+            xl = x.permute(0, 3, 1, 2)  # NHWC storage seen as NCHW = channels-last
+            wl = wt.permute(0, 3, 1, 2)
+            bl = bias.bfloat16()
+            fn = lambda: F.conv2d(xl, wl, bl, s, pad)
         flops = 2.0 * n * oh * ow * cout * k * k * cin
         nbytes = 2 * (x.numel() + wt.numel() + out.numel() * (2 if args.residual else 1))
         desc = f"conv {args.conv}"
@@ -50,6 +60,9 @@ def main():
         out = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
         res = torch.randn(M, N, device="cuda").bfloat16() if args.residual else None
         fn = lambda: ops.gemm(a, b, bias=bias, residual=res, act=args.act, out=out)
+        if args.library:
+            bl = bias.bfloat16()
+            fn = lambda: torch.nn.functional.linear(a, b, bl)
         flops = 2.0 * M * N * K
         nbytes = 2 * (M * K + N * K + M * N * (2 if args.residual else 1))
         desc = f"gemm M{M} N{N} K{K}"
@@ -58,16 +71,48 @@ def main():
         fn()
     torch.cuda.synchronize()
     times = []
-    for _ in range(args.iters):
-        if not args.no_flush:
-            flush.zero_()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        fn()
-        e1.record()
-        torch.cuda.synchronize()
-        times.append(e0.elapsed_time(e1))
+    if args.graph:
+        # Device time without host launch latency or event granularity: a graph of `iters` x (flush, op) minus a graph
+        # of `iters` x (flush), each replayed five times.
+        def replay_ms(with_op):
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                fn()
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                for _ in range(args.iters):
+                    flush.zero_()
+                    if with_op:
+                        fn()
+            g.replay()
+            torch.cuda.synchronize()
+            ts = []
+            for _ in range(5):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                g.replay()
+                e1.record()
+                torch.cuda.synchronize()
+                ts.append(e0.elapsed_time(e1))
+            return sorted(ts)[2]
+
+        times = [(replay_ms(True) - replay_ms(False)) / args.iters]
+    else:
+        for _ in range(args.iters):
+            if not args.no_flush:
+                flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            times.append(e0.elapsed_time(e1))
     ops.check_status()
+    if args.library:
+        desc = "library " + desc + " (bias only, no activation or residual)"
     times.sort()
     ms = times[len(times) // 2]
     print(f"{desc}{' +res' if args.residual else ''}: median {ms * 1e3:.1f} us  {flops / ms / 1e9:.1f} TFLOP/s "

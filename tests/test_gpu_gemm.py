@@ -53,6 +53,31 @@ def test_gemm_epilogue(env, act):
     assert _rel_err(torch, out32, ref32) < 2e-3
 
 
+@pytest.mark.parametrize("M,N,K", [(4096, 768, 3072), (4096, 1536, 768), (1000, 576, 1024)])
+def test_gemm_wide_tiles_with_epilogue(env, M, N, K):
+    """Shapes that select the 192-column tile (N a multiple of 192); long K keeps the residual on plain loads."""
+    torch, ops = env
+    a = (torch.randn(M, K, device="cuda") * 0.2).bfloat16()
+    b = (torch.randn(N, K, device="cuda") * 0.2).bfloat16()
+    bias = torch.randn(N, device="cuda")
+    res = torch.randn(M, N, device="cuda").bfloat16()
+    out = ops.gemm(a, b, bias=bias, residual=res, act="gelu")
+    ops.check_status()
+    ref = torch.nn.functional.gelu(a.float() @ b.float().t() + bias + res.float())
+    assert _rel_err(torch, out, ref) < 1e-2
+
+
+def test_gelu_epilogue_matches_erf_definition(env):
+    """The epilogue's rational erfc approximation against torch's exact GELU over a wide range of inputs."""
+    torch, ops = env
+    x = torch.linspace(-8, 8, 128 * 256, device="cuda").view(128, 256)
+    eye = torch.eye(256, device="cuda").bfloat16()
+    out = ops.gemm(x.bfloat16(), eye, act="gelu", out_dtype=torch.float32)
+    ops.check_status()
+    ref = torch.nn.functional.gelu(x.bfloat16().float())
+    assert (out - ref).abs().max().item() < 2e-6
+
+
 @pytest.mark.parametrize("n,h,cin,cout,r,stride,pad", [(2, 56, 64, 64, 3, 1, 1), (4, 28, 128, 128, 3, 1, 1),
                                                        (2, 56, 256, 128, 1, 2, 0), (3, 14, 256, 256, 3, 1, 1),
                                                        (2, 7, 512, 512, 3, 1, 1), (2, 56, 64, 256, 1, 1, 0),
