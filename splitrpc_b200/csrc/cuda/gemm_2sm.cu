@@ -41,8 +41,12 @@ template <int BN>
 struct Cfg {
   static constexpr int B_BYTES = (BN / 2) * BK * 2;  // this CTA's half of the B rows
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STAGES = BN == 256 ? 5 : (BN == 192 ? 6 : 7);
-  static constexpr int OUT_BYTES = (BN / 64) * OUT_HALF_BYTES;
+  // The 256-wide tile writes its output in two passes of 128 columns through a 32 KB staging buffer: the memory goes
+  // to a sixth operand stage, and the k loop runs at (round-trip latency) / (stages).
+  static constexpr int PASSES = BN == 256 ? 2 : 1;
+  static constexpr int PASS_COLS = BN / PASSES;
+  static constexpr int STAGES = BN == 256 ? 6 : (BN == 192 ? 6 : 7);
+  static constexpr int OUT_BYTES = (PASS_COLS / 64) * OUT_HALF_BYTES;
   static constexpr int EPI_THREADS = 2 * BN;
   static constexpr int THREADS = 64 + EPI_THREADS;
   static constexpr int ACC_STRIDE = BN == 192 ? 256 : BN;  // TMEM columns between the two accumulators
@@ -100,6 +104,8 @@ gemm_2sm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
                 uint32_t* status) {
   constexpr int B_BYTES = Cfg<BN>::B_BYTES, STAGE_BYTES = Cfg<BN>::STAGE_BYTES, STAGES = Cfg<BN>::STAGES;
   constexpr int EPI_THREADS = Cfg<BN>::EPI_THREADS, ACC_STRIDE = Cfg<BN>::ACC_STRIDE, TMEM_COLS = Cfg<BN>::TMEM_COLS;
+  constexpr int PASSES = Cfg<BN>::PASSES, PASS_COLS = Cfg<BN>::PASS_COLS;
+  constexpr int CH = PASS_COLS / 32 / (EPI_THREADS / 128);  // 32-column chunks per warp and pass
   (void)B_BYTES;
   extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* stage_out = smem + (size_t)STAGES * STAGE_BYTES;
@@ -215,18 +221,18 @@ gemm_2sm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       }
     }
   } else if (warp >= 2) {
-    // ---------------- epilogue: warps (w, w+4, w+8, w+12) share a TMEM lane quarter, 64 columns each
+    // ---------------- epilogue: the warps of a TMEM lane quarter (w, w+4, ...) split the columns of a pass
     const int warp_q = warp & 3;
-    const int cgroup = (warp - 2) >> 2;      // 0 .. BN/64 - 1
+    const int cgroup = (warp - 2) >> 2;      // 0 .. EPI_THREADS/128 - 1
     const int row = warp_q * 32 + lane;      // row of this CTA's half tile
     const int et = threadIdx.x - 64;
-    const int cbase = cgroup * 64;
     const bool vec_res = ep.residual && ((ep.ldr & 7) == 0) && (((uintptr_t)ep.residual & 15) == 0);
     uint32_t local = 0;
     PairTile t;
     for (int j = 0; layout_ok && pair_tile(j, tiles_m2, tiles_n, &t); j++, local++) {
       const uint32_t acc = local & 1u;
-      const int m = (t.m2 * 2 + (int)rank) * BM + row;
+      const int row0 = (t.m2 * 2 + (int)rank) * BM;
+      const int m = row0 + row;
       const bool row_ok = m < M;
       const int n0 = t.n * BN;
       float* bias_s = s_bias[local & 1u];
@@ -238,86 +244,90 @@ gemm_2sm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       }
       ptx::tc_fence_after();
       if (j == 0 && et == 0) GEMM2_TRACE(5);
-      // The previous tile's store must have finished reading the staging buffer.
-      if (et == 0) ptx::bulk_wait_read<0>();
-      named_bar_sync(1, EPI_THREADS);
-      const uint32_t t_addr = tmem_base + acc * ACC_STRIDE + ((uint32_t)(warp_q * 32) << 16) + (uint32_t)cbase;
 #pragma unroll
-      for (int ch = 0; ch < 2; ch++) {
-        const int c = cbase + ch * 32;
-        const int col0 = n0 + c;
-        uint32_t r[32];
-        ptx::tmem_ld_32x32b_x32(t_addr + ch * 32, r);
-        ptx::tmem_ld_wait();
-        if (ch == 1) {  // accumulator is in registers: hand it back to the leader's MMA thread
-          ptx::tc_fence_before();
-          __syncwarp();
-          if (lane == 0) ptx::mbar_arrive_cluster(ptx::mapa_shared(ptx::smem_u32(&tmem_empty_bar[acc]), 0));
-        }
-        float v[32];
+      for (int pass = 0; pass < PASSES; pass++) {
+        // The previous store must have finished reading the staging buffer.
+        if (et == 0) ptx::bulk_wait_read<0>();
+        named_bar_sync(1, EPI_THREADS);
 #pragma unroll
-        for (int q = 0; q < 32; q++) v[q] = __uint_as_float(r[q]);
-        if (ep.bias) {
-#pragma unroll
-          for (int q = 0; q < 32; q += 4) {
-            const float4 b4 = *reinterpret_cast<const float4*>(bias_s + c + q);
-            v[q] += b4.x;
-            v[q + 1] += b4.y;
-            v[q + 2] += b4.z;
-            v[q + 3] += b4.w;
+        for (int ch = 0; ch < CH; ch++) {
+          const int cp = (cgroup * CH + ch) * 32;   // column inside the pass
+          const int c = pass * PASS_COLS + cp;      // column inside the tile
+          const int col0 = n0 + c;
+          uint32_t r[32];
+          ptx::tmem_ld_32x32b_x32(tmem_base + acc * ACC_STRIDE + ((uint32_t)(warp_q * 32) << 16) + (uint32_t)c, r);
+          ptx::tmem_ld_wait();
+          if (pass == PASSES - 1 && ch == CH - 1) {  // last read: hand the accumulator back to the leader's MMA thread
+            ptx::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive_cluster(ptx::mapa_shared(ptx::smem_u32(&tmem_empty_bar[acc]), 0));
           }
-        }
-        if (ep.residual && row_ok && col0 < N) {
-          const __nv_bfloat16* rp = ep.residual + (size_t)m * ep.ldr + col0;
-          if (vec_res && col0 + 32 <= N) {
+          float v[32];
 #pragma unroll
-            for (int q = 0; q < 4; q++) {
-              const uint4 rq = __ldg(reinterpret_cast<const uint4*>(rp) + q);
-              const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&rq);
+          for (int q = 0; q < 32; q++) v[q] = __uint_as_float(r[q]);
+          if (ep.bias) {
 #pragma unroll
-              for (int u = 0; u < 4; u++) {
-                const float2 f = __bfloat1622float2(h[u]);
-                v[q * 8 + 2 * u] += f.x;
-                v[q * 8 + 2 * u + 1] += f.y;
-              }
+            for (int q = 0; q < 32; q += 4) {
+              const float4 b4 = *reinterpret_cast<const float4*>(bias_s + c + q);
+              v[q] += b4.x;
+              v[q + 1] += b4.y;
+              v[q + 2] += b4.z;
+              v[q + 3] += b4.w;
             }
-          } else {
+          }
+          if (ep.residual && row_ok && col0 < N) {
+            const __nv_bfloat16* rp = ep.residual + (size_t)m * ep.ldr + col0;
+            if (vec_res && col0 + 32 <= N) {
 #pragma unroll
-            for (int q = 0; q < 32; q++)
-              if (col0 + q < N) v[q] += __bfloat162float(rp[q]);
+              for (int q = 0; q < 4; q++) {
+                const uint4 rq = __ldg(reinterpret_cast<const uint4*>(rp) + q);
+                const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&rq);
+#pragma unroll
+                for (int u = 0; u < 4; u++) {
+                  const float2 f = __bfloat1622float2(h[u]);
+                  v[q * 8 + 2 * u] += f.x;
+                  v[q * 8 + 2 * u + 1] += f.y;
+                }
+              }
+            } else {
+#pragma unroll
+              for (int q = 0; q < 32; q++)
+                if (col0 + q < N) v[q] += __bfloat162float(rp[q]);
+            }
+          }
+          if (ep.act == GEMM_ACT_RELU) {
+#pragma unroll
+            for (int q = 0; q < 32; q++) v[q] = fmaxf(v[q], 0.f);
+          } else if (ep.act == GEMM_ACT_GELU) {
+#pragma unroll
+            for (int q = 0; q < 32; q++) v[q] = ptx::gelu_erf_fast(v[q]);
+          } else if (ep.act == GEMM_ACT_TANH) {
+#pragma unroll
+            for (int q = 0; q < 32; q++) v[q] = tanhf(v[q]);
+          }
+          uint8_t* half = stage_out + (size_t)(cp >> 6) * OUT_HALF_BYTES + (size_t)row * 128;
+          const int chunk0 = (cp & 63) >> 3;
+#pragma unroll
+          for (int q = 0; q < 4; q++) {
+            uint4 o;
+            __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+            for (int u = 0; u < 4; u++) h[u] = __floats2bfloat162_rn(v[q * 8 + 2 * u], v[q * 8 + 2 * u + 1]);
+            *reinterpret_cast<uint4*>(half + (((chunk0 + q) ^ (row & 7)) << 4)) = o;
           }
         }
-        if (ep.act == GEMM_ACT_RELU) {
+        ptx::fence_proxy_async_smem();
+        named_bar_sync(1, EPI_THREADS);
+        if (et == 0) {
 #pragma unroll
-          for (int q = 0; q < 32; q++) v[q] = fmaxf(v[q], 0.f);
-        } else if (ep.act == GEMM_ACT_GELU) {
-#pragma unroll
-          for (int q = 0; q < 32; q++) v[q] = ptx::gelu_erf_fast(v[q]);
-        } else if (ep.act == GEMM_ACT_TANH) {
-#pragma unroll
-          for (int q = 0; q < 32; q++) v[q] = tanhf(v[q]);
+          for (int hcol = 0; hcol < PASS_COLS / 64; hcol++) {
+            const int col = n0 + pass * PASS_COLS + hcol * 64;
+            if (col >= N || row0 >= M) break;
+            ptx::tma_store_2d(&tmap_out, stage_out + (size_t)hcol * OUT_HALF_BYTES, col, row0);
+          }
+          ptx::bulk_commit();
+          if (j == 0 && pass == PASSES - 1) GEMM2_TRACE(6);
         }
-        uint8_t* half = stage_out + (size_t)(c >> 6) * OUT_HALF_BYTES + (size_t)row * 128;
-        const int chunk0 = (c & 63) >> 3;
-#pragma unroll
-        for (int q = 0; q < 4; q++) {
-          uint4 o;
-          __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&o);
-#pragma unroll
-          for (int u = 0; u < 4; u++) h[u] = __floats2bfloat162_rn(v[q * 8 + 2 * u], v[q * 8 + 2 * u + 1]);
-          *reinterpret_cast<uint4*>(half + (((chunk0 + q) ^ (row & 7)) << 4)) = o;
-        }
-      }
-      ptx::fence_proxy_async_smem();
-      named_bar_sync(1, EPI_THREADS);
-      if (et == 0) {
-#pragma unroll
-        for (int hcol = 0; hcol < BN / 64; hcol++) {
-          if (n0 + hcol * 64 >= N || (t.m2 * 2 + (int)rank) * BM >= M) break;
-          ptx::tma_store_2d(&tmap_out, stage_out + (size_t)hcol * OUT_HALF_BYTES, n0 + hcol * 64, (t.m2 * 2 + (int)rank) * BM);
-        }
-        ptx::bulk_commit();
-        if (j == 0) GEMM2_TRACE(6);
       }
     }
     if (et == 0) {

@@ -667,7 +667,11 @@ cudaError_t launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorM
   p.b_stationary = 0;
   p.ctas_per_n = 0;
   static const int allow_bs = [] { const char* e = getenv("SPLITRPC_GEMM_BSTAT"); return e ? atoi(e) : 1; }();
-  if (allow_bs && p.num_kb <= (BN >= 192 ? 2 : 4) && p.tiles_n <= num_sms()) {
+  // The panel may take the ring's memory as long as three A stages remain (a 3x3 convolution over 64 channels keeps its
+  // nine 8 KB filter taps resident: otherwise every CTA re-reads the same few L2 lines for every tile).
+  const int panel = p.num_kb * BN * BK * 2, ring = STAGES * (BM * BK * 2 + BN * BK * 2);
+  const bool panel_fits = p.mode == 1 ? panel + 3 * BM * BK * 2 <= ring : p.num_kb <= (BN >= 192 ? 2 : 4);
+  if (allow_bs && panel_fits && p.tiles_n <= num_sms()) {
     const int per_n = std::min(num_sms() / p.tiles_n, p.tiles_m);
     if (per_n >= 1 && p.tiles_m >= 2 * per_n) {  // at least two tiles per CTA to pay for the panel load
       p.b_stationary = 1;

@@ -48,4 +48,16 @@ def smoke_test(device: int = 0) -> dict:
     err = ((out.float() - a.float() @ b.float().t()).norm() / (a.float() @ b.float().t()).norm()).item()
     if err > 1e-2:
         raise RuntimeError(f"smoke: gemm relative error {err}")
-    return {"served": int(cli.received), "gemm_rel_err": err}
+    # one small forward of the flagship model (ResNet-50, batch 2) through the same kernels the server's graph replays
+    from ..models import ResNet50
+
+    model = ResNet50(device=device, max_batch=2)
+    x = torch.randn(2, 3, 224, 224, device="cuda")
+    probs = torch.empty(2, 1000, device="cuda")
+    model.forward(2, x=x, out=probs)
+    torch.cuda.synchronize()
+    ops.check_status()
+    ref = model.reference_forward(x)
+    if not torch.allclose(probs.sum(-1), torch.ones(2, device="cuda"), atol=1e-3) or not torch.equal(probs.argmax(-1), ref.argmax(-1)):
+        raise RuntimeError("smoke: ResNet-50 forward disagrees with the PyTorch evaluation of the same weights")
+    return {"served": int(cli.received), "gemm_rel_err": err, "resnet50_top1_match": True}
