@@ -153,7 +153,8 @@ def device_timed(srv, steps: int, warmup: int):
         w = i % n_sets
         if i >= n_sets:
             sg_stream.wait_event(done[i - n_sets])  # the window's previous batch has been answered
-        _C.sg_list_launch(lists[w], 0, 48, sg_stream.cuda_stream)  # PCIe-bound: a small grid reaches the link rate
+        # PCIe-bound: a few 1024-thread blocks on the SMs that the model's persistent kernels leave free
+        _C.sg_list_launch(lists[w], 0, -srv.reserve_sms if srv.reserve_sms > 0 else 48, sg_stream.cuda_stream)
         gathered[i].record(sg_stream)
         stream.wait_event(gathered[i])
         # the stub is re-pointed in stream order, as the stream-armed server mode does

@@ -99,6 +99,9 @@ void bind_ops(py::module_& m) {
         py::arg("residual") = 0, py::arg("act") = 0, py::arg("status") = 0, py::arg("stream") = 0, py::arg("impl") = 2,
         py::arg("pix_stride") = 0, py::arg("row_stride") = 0, py::arg("img_stride") = 0);
 
+  m.def("gemm_reserve_sms", [](int n) { srpc_gemm_reserve_sms(n); }, py::arg("n"));
+  m.def("gemm_grid_sms", []() { return srpc_gemm_grid_sms(); });
+  m.def("gemm_reserved_sms", []() { return srpc_gemm_reserved_sms(); });
   m.def("gemm_trace", [](bool two_sm) {
     unsigned long long t[12] = {0};
     int n = two_sm ? srpc_gemm2_trace_read(t, 12) : srpc_gemm_trace_read(t, 10);

@@ -115,7 +115,9 @@ gemm_2sm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
   __shared__ __align__(8) uint64_t tmem_empty_bar[2];  // used in the leader only: arrivals from both CTAs' epilogue warps
   __shared__ uint32_t tmem_base_smem;
   __shared__ uint32_t s_error;
-  __shared__ __align__(16) float s_bias[2][BN];
+  // One buffer is enough: the last named barrier of a tile (before its store) comes after every read of that tile's
+  // bias, and a thread writes the next tile's bias only after passing it.
+  __shared__ __align__(16) float s_bias[BN];
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = ptx::cluster_ctarank();
@@ -235,7 +237,7 @@ gemm_2sm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       const int m = row0 + row;
       const bool row_ok = m < M;
       const int n0 = t.n * BN;
-      float* bias_s = s_bias[local & 1u];
+      float* bias_s = s_bias;
       if (ep.bias && et < BN) bias_s[et] = (n0 + et < N) ? __ldg(ep.bias + n0 + et) : 0.f;
       const bool mine = (*(volatile uint32_t*)&s_error == 0) && ptx::mbar_wait(&tmem_full_bar[acc], (local >> 1) & 1u);
       if (!named_bar_all(2, EPI_THREADS, mine)) {  // uniform outcome; also orders the bias writes before their reads
@@ -383,7 +385,7 @@ cudaError_t launch_2sm(const void* A, int lda, const void* B, int ldb, int M, in
   e = srpc_tensor_map_2d(&to, ep.out, (uint64_t)N, (uint64_t)M, (uint64_t)ep.ldo * 2, 64, BM);
   if (e != cudaSuccess) return e;
   const int tiles_m2 = (M + 2 * BM - 1) / (2 * BM), tiles_n = (N + BN - 1) / BN;
-  const int clusters = std::min(tiles_m2 * tiles_n, max_clusters);
+  const int clusters = std::min(tiles_m2 * tiles_n, std::min(max_clusters, srpc_gemm_grid_sms() / 2));
   gemm_2sm_kernel<BN><<<2 * clusters, C::THREADS, C::SMEM_BYTES, stream>>>(ta, tb, to, M, N, K, tiles_m2, tiles_n, ep, status);
   return cudaGetLastError();
 }

@@ -165,8 +165,11 @@ gemm_conv_persistent(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   constexpr int OUT_HALF_BYTES = BM * 128;       // 128 rows x 64 bf16 columns
   constexpr int OUT_BYTES = (BN / 64) * OUT_HALF_BYTES;
-  extern __shared__ __align__(1024) uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  // No slack for manual alignment: the widest configuration then leaves 2 KB of the SM's shared memory, which is what
+  // one small block of another stream (the scatter-gather kernel) needs to share the SM; a block that takes all of
+  // it keeps every other block off its SM.
+  extern __shared__ __align__(1024) uint8_t smem[];
+  const bool layout_ok = (ptx::smem_u32(smem) & 1023u) == 0;
   uint8_t* stage_out = smem + (size_t)STAGES * STAGE_BYTES;
   constexpr int MAX_STAGES = 8;
   __shared__ __align__(8) uint64_t full_bar[MAX_STAGES];
@@ -208,7 +211,7 @@ gemm_conv_persistent(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     }
     for (int b = 0; b < MAX_OUT_BUFS; b++) ptx::mbar_init(&res_full_bar[b], 1);
     ptx::fence_mbar_init();
-    s_error = 0;
+    s_error = layout_ok ? 0u : (uint32_t)GEMM_ERR_PRODUCER_WAIT;
     ptx::prefetch_tmap(&tmap_a);
     ptx::prefetch_tmap(&tmap_b);
     if (use_tma_store) ptx::prefetch_tmap(&tmap_out);
@@ -258,7 +261,7 @@ gemm_conv_persistent(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       }
     }
   };
-  if (threadIdx.x == 0) {
+  if (threadIdx.x == 0 && layout_ok) {
     TileCoord tc;
     if (p.b_stationary && get_tile(p, 0, &tc)) {
       ptx::mbar_expect_tx(&bpanel_bar, (uint32_t)panel_bytes);
@@ -640,6 +643,11 @@ cudaError_t map_2d(CUtensorMap* m, const void* ptr, uint64_t inner, uint64_t out
   return get_map(m, ptr, 2, dims, st, box, es);
 }
 
+// SMs that the persistent kernels size their grids for.  A persistent kernel has one block per SM and a fixed tile
+// schedule; if a block of another stream (the scatter-gather kernel that runs beside the model) holds an SM, one of
+// this kernel's blocks starts only when another has finished and the whole kernel takes twice as long.  Leaving a
+// few SMs out of the grid keeps room for such blocks (srpc_gemm_reserve_sms, or SPLITRPC_GEMM_RESERVE_SMS).
+int g_reserve_sms = -1;
 int num_sms() {
   static int n = 0;
   if (!n) {
@@ -648,14 +656,19 @@ int num_sms() {
     cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
     if (n <= 0) n = 148;
   }
-  return n;
+  if (g_reserve_sms < 0) {
+    const char* e = getenv("SPLITRPC_GEMM_RESERVE_SMS");
+    g_reserve_sms = e ? atoi(e) : 0;
+  }
+  const int r = g_reserve_sms < n / 2 ? g_reserve_sms : n / 2;
+  return n - r;
 }
 
 template <int BN, int STAGES, int OB>
 cudaError_t launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& to, const CUtensorMap& tr,
                    const TileParams& p_in, const GemmEpilogue& ep, int use_tma_store, uint32_t* status, cudaStream_t st) {
   static bool attr = false;
-  const int smem = STAGES * (BM * BK * 2 + BN * BK * 2) + OB * (BN / 64) * BM * 128 + 1024;
+  const int smem = STAGES * (BM * BK * 2 + BN * BK * 2) + OB * (BN / 64) * BM * 128;
   if (!attr) {
     cudaError_t e = cudaFuncSetAttribute(gemm_conv_persistent<BN, STAGES, OB>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
@@ -692,6 +705,13 @@ cudaError_t dispatch(int bn, const CUtensorMap& ta, const CUtensorMap& tb, const
 }
 
 }  // namespace
+
+void srpc_gemm_reserve_sms(int n) { g_reserve_sms = n < 0 ? 0 : n; }
+int srpc_gemm_grid_sms() { return num_sms(); }
+int srpc_gemm_reserved_sms() {
+  (void)num_sms();
+  return g_reserve_sms > 0 ? g_reserve_sms : 0;
+}
 
 cudaError_t srpc_tensor_map_2d(CUtensorMap* m, const void* ptr, uint64_t inner, uint64_t outer, uint64_t row_stride_bytes,
                                uint32_t box_inner, uint32_t box_outer) {

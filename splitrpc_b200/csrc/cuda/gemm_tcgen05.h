@@ -56,6 +56,12 @@ bool srpc_gemm_2sm_eligible(int M, int N, int K, const GemmEpilogue& ep);
 cudaError_t srpc_gemm_bf16_2sm(const void* A, int lda, const void* B, int ldb, int M, int N, int K, int bn,
                                const GemmEpilogue& ep, uint32_t* status, cudaStream_t stream);
 
+// Leaves `n` SMs out of the grids of the persistent kernels (see num_sms in gemm_persistent.cu); takes effect for
+// launches (and graph captures) made afterwards.  srpc_gemm_grid_sms returns the SM count the grids are sized for.
+void srpc_gemm_reserve_sms(int n);
+int srpc_gemm_grid_sms();
+int srpc_gemm_reserved_sms();
+
 // Phase time stamps (ns, %globaltimer) of block 0 of the last persistent launch; returns 0 unless the library was
 // built with -DSRPC_GEMM_TRACE.  Slots: 0 entry, 1 set-up done, 2 first loads issued, 3 first operands landed,
 // 4 first tile's MMAs issued, 5 first accumulator ready, 6 first tile's store issued, 7 last epilogue done,

@@ -16,6 +16,7 @@
 #include <thread>
 
 #include "../host/p2p_rpc_sg_engine.h"
+#include "gemm_tcgen05.h"
 #include "sg_kernels.cuh"
 
 namespace {
@@ -23,18 +24,23 @@ namespace {
 class P2pRpcSgGpuEngine : public P2pRpcSgEngine {
   int copy_type_;
   // Blocks per copy kernel.  A list whose sources sit in host memory is bound by the PCIe link and needs only enough
-  // loads in flight to cover its latency; a small grid then leaves the SMs to the model's kernels that run beside
-  // it (48 blocks measured best for a ResNet-50 batch; 16 to 296 all reach the same copy rate).  Lists that read
-  // device memory get four blocks per SM.  P2P_RPC_SG_BLOCKS overrides both.
+  // loads in flight to cover its latency.  When the model's persistent kernels leave r SMs out of their grids
+  // (srpc_gemm_reserve_sms), the copy runs as r blocks of 1024 threads (written -r): twelve reach the link rate, and
+  // the model beside it runs as fast as alone (measured: ResNet-50 graph 1.68 ms with the copy, 1.63 ms alone, against
+  // 1.98 ms when the copy's 48 blocks of 256 threads each hold an SM that a persistent kernel counts on).  Lists
+  // that read device memory get four blocks of 256 threads per SM.  P2P_RPC_SG_BLOCKS overrides both
+  // (negative = 1024-thread blocks).
   int n_blocks_ = readEnvInfo<int>("P2P_RPC_SG_BLOCKS", 0);
   int blocks_for(const SgItem& first) const {
-    if (n_blocks_ > 0) return n_blocks_;
+    if (n_blocks_ != 0) return n_blocks_;
     cudaPointerAttributes a{};
     if (cudaPointerGetAttributes(&a, (const void*)first.src) != cudaSuccess) {
       (void)cudaGetLastError();
       return 0;
     }
-    return a.type == cudaMemoryTypeHost ? 48 : 0;
+    if (a.type != cudaMemoryTypeHost) return 0;
+    const int r = srpc_gemm_reserved_sms();
+    return r > 0 ? -r : 48;
   }
   cudaStream_t stream_ = nullptr;
   SgItem* h_items_ = nullptr;  // pinned staging of the copy list

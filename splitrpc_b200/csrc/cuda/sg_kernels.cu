@@ -57,8 +57,18 @@ __device__ __forceinline__ void copy_chunk_simt(const uint8_t* src, uint8_t* dst
     uint32_t nv = body >> 4;
     const uint4* s4 = reinterpret_cast<const uint4*>(s);
     uint4* d4 = reinterpret_cast<uint4*>(d);
-    for (uint32_t i = t; i < nv; i += nthr) d4[i] = s4[i];
-    for (uint32_t i = (nv << 4) + t; i < body; i += nthr) d[i] = s[i];
+    // four independent 16-byte loads in flight per thread: a host-memory source answers after microseconds, and with
+    // one load per thread a few blocks cannot keep the PCIe link busy
+    uint32_t i = t;
+    for (; i + 3 * nthr < nv; i += 4 * nthr) {
+      const uint4 a = s4[i], b = s4[i + nthr], c = s4[i + 2 * nthr], e = s4[i + 3 * nthr];
+      d4[i] = a;
+      d4[i + nthr] = b;
+      d4[i + 2 * nthr] = c;
+      d4[i + 3 * nthr] = e;
+    }
+    for (; i < nv; i += nthr) d4[i] = s4[i];
+    for (uint32_t i2 = (nv << 4) + t; i2 < body; i2 += nthr) d[i2] = s[i2];
   } else if (((uintptr_t)s & 3) == 0) {
     uint32_t nv = body >> 2;
     const uint32_t* s1 = reinterpret_cast<const uint32_t*>(s);
@@ -70,10 +80,15 @@ __device__ __forceinline__ void copy_chunk_simt(const uint8_t* src, uint8_t* dst
   }
 }
 
-__global__ void __launch_bounds__(256) sg_copy_simt(const SgItem* __restrict__ items, uint32_t n_items, uint32_t n_chunks) {
-  for (uint32_t c = blockIdx.x; c < n_chunks; c += gridDim.x) {
+// Groups of 256 threads take chunks in turn.  Launched with 256 threads per block (many blocks: device and peer
+// sources) or with 1024 (four groups per block: a few "fat" blocks reach the PCIe rate for host sources and occupy
+// only as many SMs).
+__global__ void __launch_bounds__(1024) sg_copy_simt(const SgItem* __restrict__ items, uint32_t n_items, uint32_t n_chunks) {
+  const uint32_t groups = blockDim.x >> 8;
+  const uint32_t g = blockIdx.x * groups + (threadIdx.x >> 8), ng = gridDim.x * groups;
+  for (uint32_t c = g; c < n_chunks; c += ng) {
     ChunkRef r = chunk_ref(items, n_items, c);
-    copy_chunk_simt(r.src, r.dst, r.len, threadIdx.x, blockDim.x);
+    copy_chunk_simt(r.src, r.dst, r.len, threadIdx.x & 255u, 256u);
   }
 }
 
@@ -245,6 +260,27 @@ __global__ void __launch_bounds__(256) sg_persistent(SgCtrl* ctrl, uint32_t* cou
 
 }  // namespace
 
+// The copy kernels run beside the model's kernels, whose blocks need (almost) all of an SM's shared memory.  An SM
+// keeps its L1 / shared-memory split while any block is resident, so a copy block that was placed on an SM set up
+// for a large L1 keeps the big-tile kernels off that SM until it leaves.  Asking for the largest shared-memory
+// carve-out (the copies stream and gain nothing from L1) lets both kinds of block share an SM.
+template <typename K>
+static void prefer_max_shared(K kernel) {
+  cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+}
+static void sg_kernel_setup() {
+  static bool done = false;
+  if (done) return;
+  static const int on = [] { const char* e = getenv("P2P_RPC_SG_MAX_SHARED"); return e ? atoi(e) : 1; }();
+  if (on) {
+    prefer_max_shared(sg_copy_simt);
+    prefer_max_shared(sg_cast_bf16);
+    prefer_max_shared(sg_persistent);
+  }
+  (void)cudaGetLastError();
+  done = true;
+}
+
 static int clamp_blocks(int n_blocks, uint32_t n_chunks) {
   if (n_blocks <= 0) n_blocks = 148 * 4;
   if ((uint32_t)n_blocks > n_chunks) n_blocks = (int)n_chunks;
@@ -254,6 +290,7 @@ static int clamp_blocks(int n_blocks, uint32_t n_chunks) {
 cudaError_t sg_launch_copy(const SgItem* d_items, uint32_t n_items, uint32_t n_chunks, int impl, int n_blocks,
                            cudaStream_t stream) {
   if (n_items == 0 || n_chunks == 0) return cudaSuccess;
+  sg_kernel_setup();
   if (impl == SG_IMPL_BULK) {
     static bool attr_set = false;
     size_t smem = (size_t)BULK_STAGES * SG_CHUNK;
@@ -264,6 +301,9 @@ cudaError_t sg_launch_copy(const SgItem* d_items, uint32_t n_items, uint32_t n_c
     }
     int nb = clamp_blocks(n_blocks > 0 ? n_blocks : 148, n_chunks);
     sg_copy_bulk<<<nb, BULK_THREADS, smem, stream>>>(d_items, n_items, n_chunks, nullptr);
+  } else if (n_blocks < 0) {  // -n "fat" blocks of 1024 threads
+    const uint32_t want = (uint32_t)(-n_blocks), most = (n_chunks + 3) / 4;
+    sg_copy_simt<<<want < most ? want : most, 1024, 0, stream>>>(d_items, n_items, n_chunks);
   } else {
     sg_copy_simt<<<clamp_blocks(n_blocks, n_chunks), 256, 0, stream>>>(d_items, n_items, n_chunks);
   }
@@ -273,11 +313,13 @@ cudaError_t sg_launch_copy(const SgItem* d_items, uint32_t n_items, uint32_t n_c
 cudaError_t sg_launch_cast_bf16(const SgItem* d_items, uint32_t n_items, uint32_t n_chunks, float scale, float shift,
                                 int n_blocks, cudaStream_t stream) {
   if (n_items == 0 || n_chunks == 0) return cudaSuccess;
+  sg_kernel_setup();
   sg_cast_bf16<<<clamp_blocks(n_blocks, n_chunks), 256, 0, stream>>>(d_items, n_items, n_chunks, scale, shift);
   return cudaGetLastError();
 }
 
 cudaError_t sg_launch_persistent(SgCtrl* d_ctrl, uint32_t* d_counter, int n_blocks, cudaStream_t stream) {
+  sg_kernel_setup();
   sg_persistent<<<n_blocks, 256, 0, stream>>>(d_ctrl, d_counter);
   return cudaGetLastError();
 }
