@@ -34,8 +34,15 @@ struct AttSmem {
   static constexpr int K_BYTES = SEQ * 128;           // SEQ rows x 64 bf16
   static constexpr int VT_BYTES = (SEQ / 64) * 64 * 128;  // SEQ/64 atoms of 64 rows x 64 keys
   static constexpr int P_BYTES = (SEQ / 64) * QT * 128;   // SEQ/64 atoms of 128 rows x 64 keys
-  static constexpr int TOTAL = Q_BYTES + K_BYTES + VT_BYTES + P_BYTES;
-  static constexpr int TMEM_COLS = (SEQ + HD) <= 256 ? 256 : 512;
+  // With a single query tile (SEQ == 128) Q and K are dead once the scores exist, and the scores are dead once P is
+  // written: P takes the place of Q|K in shared memory and the output accumulator the place of the scores in tensor
+  // memory.  48 KB and 128 columns per CTA let four CTAs share an SM, so every (sequence, head) of a 32 x 12 batch is
+  // resident at once and the SM interleaves their load -> MMA -> softmax -> MMA chains.
+  static constexpr bool ALIAS = SEQ == QT;
+  static constexpr int P_OFFSET = ALIAS ? 0 : Q_BYTES + K_BYTES + VT_BYTES;
+  static constexpr int TOTAL = ALIAS ? Q_BYTES + K_BYTES + VT_BYTES : Q_BYTES + K_BYTES + VT_BYTES + P_BYTES;
+  static constexpr int TMEM_COLS = ALIAS ? 128 : ((SEQ + HD) <= 256 ? 256 : 512);
+  static_assert(!ALIAS || P_BYTES <= Q_BYTES + K_BYTES, "P must fit over Q and K");
 };
 
 template <int SEQ>
@@ -49,7 +56,7 @@ attention_tc(const __grid_constant__ CUtensorMap tmap_qk, const __grid_constant_
   uint8_t* sQ = smem;
   uint8_t* sK = sQ + L::Q_BYTES;
   uint8_t* sVT = sK + L::K_BYTES;
-  uint8_t* sP = sVT + L::VT_BYTES;
+  uint8_t* sP = smem + L::P_OFFSET;
   __shared__ __align__(8) uint64_t bar_kv, bar_q, bar_s, bar_p, bar_o;
   __shared__ uint32_t tmem_base_smem;
   __shared__ uint32_t s_error;
@@ -78,7 +85,7 @@ attention_tc(const __grid_constant__ CUtensorMap tmap_qk, const __grid_constant_
   __syncthreads();
   ptx::tc_fence_after();
   const uint32_t tmem_s = tmem_base_smem;          // scores: columns [0, SEQ)
-  const uint32_t tmem_o = tmem_base_smem + SEQ;    // output: columns [SEQ, SEQ+64)
+  const uint32_t tmem_o = tmem_base_smem + (L::ALIAS ? 0 : SEQ);  // output: columns [SEQ, SEQ+64), or over the scores
 
   if (warp == 4) {
     if (ptx::elect_one()) {

@@ -74,6 +74,12 @@ struct TileParams {
   // earlier tiles are still in their epilogue; the epilogue then adds the accumulator to it in place.  Plain loads
   // of the residual from the epilogue threads leave each of them waiting a full DRAM round trip per tile.
   int res_tma;
+  // Row-tap reuse (stride-1 convolutions, patch width a multiple of 8): one A box per (filter column, channel block)
+  // holds the patch rows with their halo (ph + r - 1 image rows), and the r filter rows are r groups of MMAs whose A
+  // descriptors start fr * pw rows further into that box: a third of the loads (and of the round trips that pace a
+  // short-tile k loop) for a 3 x 3 filter.  num_kb then counts load groups (s * cblocks); panel_kb counts all k-blocks.
+  int reuse;
+  int panel_kb;
 };
 
 __device__ __forceinline__ float gelu_f(float x) { return ptx::gelu_erf_fast(x); }
@@ -158,8 +164,7 @@ template <int BN, int STAGES, int OB>
 __global__ void __launch_bounds__(Threads<BN>::TOTAL, 1)
 gemm_conv_persistent(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                      const __grid_constant__ CUtensorMap tmap_out, const __grid_constant__ CUtensorMap tmap_res, TileParams p,
-                     GemmEpilogue ep, int use_tma_store_mode, uint32_t* status) {
-  const int use_tma_store = use_tma_store_mode == 1 ? 1 : 0;
+                     GemmEpilogue ep, int use_tma_store, uint32_t* status) {
   constexpr int A_BYTES = BM * BK * 2;
   constexpr int B_BYTES = BN * BK * 2;
   constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
@@ -176,10 +181,11 @@ gemm_conv_persistent(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   __shared__ __align__(8) uint64_t empty_bar[MAX_STAGES];
   __shared__ __align__(8) uint64_t bpanel_bar;
   // Streaming: STAGES stages of {A tile, B tile}.  B-stationary: the B panel (num_kb tiles) first, then a ring of A tiles.
-  const int panel_bytes = p.b_stationary ? p.num_kb * B_BYTES : 0;
-  int nst_calc = p.b_stationary ? (STAGES * STAGE_BYTES - panel_bytes) / A_BYTES : STAGES;
+  const int panel_bytes = p.b_stationary ? p.panel_kb * B_BYTES : 0;
+  const int b_per_stage = p.b_stationary ? 0 : (p.reuse ? p.r : 1);  // B tiles that travel with every A box
+  const int a_stride = A_BYTES + b_per_stage * B_BYTES;
+  int nst_calc = (STAGES * STAGE_BYTES - panel_bytes) / a_stride;
   const int nst = nst_calc > MAX_STAGES ? MAX_STAGES : nst_calc;
-  const int a_stride = p.b_stationary ? A_BYTES : STAGE_BYTES;
   uint8_t* a_ring = smem + panel_bytes;
   // Four TMEM accumulators: up to four tiles can be between "MMA issued" and "accumulator read back", which hides
   // the commit -> wake-up -> tcgen05.ld -> release round trip of short (few k-block) tiles.
@@ -224,7 +230,7 @@ gemm_conv_persistent(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   uint32_t pr_ph = 0;
   bool pr_more = true;
   auto produce = [&](int budget) {
-    const uint32_t b_tx = p.b_stationary ? 0u : (uint32_t)B_BYTES;
+    const uint32_t b_tx = (uint32_t)(b_per_stage * B_BYTES);
     TileCoord tc;
     while (pr_more && budget > 0) {
       if (!get_tile(p, pr_j, &tc) || *(volatile uint32_t*)&s_error != 0) {
@@ -241,6 +247,15 @@ gemm_conv_persistent(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         if (p.mode == 0) {
           ptx::mbar_expect_tx(&full_bar[pr_s], (uint32_t)A_BYTES + b_tx);
           ptx::tma_load_2d(sa, &tmap_a, &full_bar[pr_s], pr_kb * BK, tc.m_idx * BM);
+        } else if (p.reuse) {
+          // load group (fs, cb): the box covers filter rows 0 .. r-1 at once
+          ptx::mbar_expect_tx(&full_bar[pr_s], p.a_box_bytes + b_tx);
+          const int fs = pr_kb / p.cblocks, cb = pr_kb - fs * p.cblocks;
+          tma_load_4d_box(sa, &tmap_a, &full_bar[pr_s], cb * BK, tc.w0 + fs - p.pad, tc.h0 - p.pad, tc.img0);
+          if (!p.b_stationary)
+            for (int fr = 0; fr < p.r; fr++)
+              ptx::tma_load_2d(sa + A_BYTES + fr * B_BYTES, &tmap_b, &full_bar[pr_s], ((fr * p.s + fs) * p.cblocks + cb) * BK,
+                               tc.n_idx * BN);
         } else {
           ptx::mbar_expect_tx(&full_bar[pr_s], p.a_box_bytes + b_tx);
           const int tap = pr_kb / p.cblocks, cb = pr_kb - tap * p.cblocks;
@@ -248,7 +263,7 @@ gemm_conv_persistent(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
           tma_load_4d_box(sa, &tmap_a, &full_bar[pr_s], cb * BK, tc.w0 * p.stride + fs - p.pad,
                           tc.h0 * p.stride + fr - p.pad, tc.img0);
         }
-        if (!p.b_stationary) ptx::tma_load_2d(sa + A_BYTES, &tmap_b, &full_bar[pr_s], pr_kb * BK, tc.n_idx * BN);
+        if (!p.b_stationary && !p.reuse) ptx::tma_load_2d(sa + A_BYTES, &tmap_b, &full_bar[pr_s], pr_kb * BK, tc.n_idx * BN);
         if (pr_j == 0 && pr_kb == 0) GEMM_TRACE(2);
         if (++pr_s == nst) {
           pr_s = 0;
@@ -265,7 +280,7 @@ gemm_conv_persistent(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     TileCoord tc;
     if (p.b_stationary && get_tile(p, 0, &tc)) {
       ptx::mbar_expect_tx(&bpanel_bar, (uint32_t)panel_bytes);
-      for (int kb = 0; kb < p.num_kb; kb++)
+      for (int kb = 0; kb < p.panel_kb; kb++)
         ptx::tma_load_2d(smem + (size_t)kb * B_BYTES, &tmap_b, &bpanel_bar, kb * BK, tc.n_idx * BN);
     }
     produce(nst < 2 ? nst : 2);  // more would hold thread 0 (and with it the set-up barrier) behind a full TMA queue
@@ -314,11 +329,25 @@ gemm_conv_persistent(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
           ptx::tc_fence_after();
           if (j == 0 && kb == 0) GEMM_TRACE(3);
           const uint32_t sa = ptx::smem_u32(a_ring + (size_t)s * a_stride);
-          const uint32_t sb = p.b_stationary ? ptx::smem_u32(smem + (size_t)kb * B_BYTES) : sa + A_BYTES;
+          if (p.reuse) {
+            const int fs = kb / p.cblocks, cb = kb - fs * p.cblocks;
+            for (int fr = 0; fr < p.r; fr++) {
+              const uint32_t sa_fr = sa + (uint32_t)(fr * p.pw * 128);  // fr image rows further into the box
+              const uint32_t sb = p.b_stationary
+                                      ? ptx::smem_u32(smem + (size_t)((fr * p.s + fs) * p.cblocks + cb) * B_BYTES)
+                                      : sa + A_BYTES + fr * B_BYTES;
 #pragma unroll
-          for (int k = 0; k < BK / UMMA_K; k++)
-            ptx::umma_bf16(d_tmem, ptx::umma_desc_sw128(sa + k * UMMA_K * 2), ptx::umma_desc_sw128(sb + k * UMMA_K * 2), idesc,
-                           (kb | k) != 0 ? 1u : 0u);
+              for (int k = 0; k < BK / UMMA_K; k++)
+                ptx::umma_bf16(d_tmem, ptx::umma_desc_sw128(sa_fr + k * UMMA_K * 2), ptx::umma_desc_sw128(sb + k * UMMA_K * 2),
+                               idesc, (kb | fr | k) != 0 ? 1u : 0u);
+            }
+          } else {
+            const uint32_t sb = p.b_stationary ? ptx::smem_u32(smem + (size_t)kb * B_BYTES) : sa + A_BYTES;
+#pragma unroll
+            for (int k = 0; k < BK / UMMA_K; k++)
+              ptx::umma_bf16(d_tmem, ptx::umma_desc_sw128(sa + k * UMMA_K * 2), ptx::umma_desc_sw128(sb + k * UMMA_K * 2), idesc,
+                             (kb | k) != 0 ? 1u : 0u);
+          }
           ptx::umma_commit(&empty_bar[s]);
           if (++s == nst) {
             s = 0;
@@ -399,12 +428,6 @@ gemm_conv_persistent(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       }
       ptx::tc_fence_after();
       if (j == 0 && et == 0) GEMM_TRACE(5);
-      if (use_tma_store_mode == 5) {  // experiment: release the accumulator without reading it
-        ptx::tc_fence_before();
-        __syncwarp();
-        if (lane == 0) ptx::mbar_arrive(&tmem_empty_bar[acc]);
-        continue;
-      }
       uint32_t r[LEAN ? 32 : CPW];
       const uint32_t t_addr = tmem_base + acc * ACC_STRIDE + ((uint32_t)(warp_q * 32) << 16) + (uint32_t)cbase;
       if (!LEAN) {
@@ -415,10 +438,6 @@ gemm_conv_persistent(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         ptx::tc_fence_before();
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive(&tmem_empty_bar[acc]);
-      }
-      if (!LEAN && use_tma_store_mode == 4) {  // experiment: read the accumulator, do nothing with it
-        if (r[0] == 0x7fc12345u) reinterpret_cast<uint32_t*>(ep.out)[0] = r[1];
-        continue;
       }
       uint8_t* sbuf = stage_out + (size_t)(local % OB) * OUT_BYTES;
       if (use_tma_store && !res_tma) {
@@ -508,18 +527,6 @@ gemm_conv_persistent(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
             for (int t = 0; t < 4; t++) h[t] = __floats2bfloat162_rn(v[j * 8 + 2 * t], v[j * 8 + 2 * t + 1]);
             *reinterpret_cast<uint4*>(half + (((chunk0 + j) ^ (row & 7)) << 4)) = q;
           }
-        } else if (use_tma_store_mode == 3 && row_ok && col0 + 32 <= p.N) {
-          __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(ep.out) + row_off * ep.ldo + col0;
-#pragma unroll
-          for (int j = 0; j < 4; j++) {
-            uint4 q;
-            __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&q);
-#pragma unroll
-            for (int t = 0; t < 4; t++) h[t] = __floats2bfloat162_rn(v[j * 8 + 2 * t], v[j * 8 + 2 * t + 1]);
-            *reinterpret_cast<uint4*>(op + j * 8) = q;
-          }
-        } else if (use_tma_store_mode == 2) {
-          if (v[0] == 1.2345e30f) reinterpret_cast<float*>(ep.out)[0] = v[1];  // experiment: compute, never store
         } else if (row_ok && col0 < p.N) {
           if (ep.out_fp32) {
             float* op = reinterpret_cast<float*>(ep.out) + row_off * ep.ldo + col0;
@@ -682,7 +689,7 @@ cudaError_t launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorM
   static const int allow_bs = [] { const char* e = getenv("SPLITRPC_GEMM_BSTAT"); return e ? atoi(e) : 1; }();
   // The panel may take the ring's memory as long as three A stages remain (a 3x3 convolution over 64 channels keeps its
   // nine 8 KB filter taps resident: otherwise every CTA re-reads the same few L2 lines for every tile).
-  const int panel = p.num_kb * BN * BK * 2, ring = STAGES * (BM * BK * 2 + BN * BK * 2);
+  const int panel = p.panel_kb * BN * BK * 2, ring = STAGES * (BM * BK * 2 + BN * BK * 2);
   const bool panel_fits = p.mode == 1 ? panel + 3 * BM * BK * 2 <= ring : p.num_kb <= (BN >= 192 ? 2 : 4);
   if (allow_bs && panel_fits && p.tiles_n <= num_sms()) {
     const int per_n = std::min(num_sms() / p.tiles_n, p.tiles_m);
@@ -698,9 +705,17 @@ cudaError_t launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorM
 
 cudaError_t dispatch(int bn, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& to, const CUtensorMap& tr,
                      const TileParams& p, const GemmEpilogue& ep, int use_tma_store, uint32_t* status, cudaStream_t st) {
-  if (bn == 64) return launch<64, 6, OUT_BUFS>(ta, tb, to, tr, p, ep, use_tma_store, status, st);
+  // Long k loops run at (round trip MMA done -> stage free -> TMA -> stage full) / (stages): give them the staging
+  // buffers' memory as extra stages.  Short k loops are bound by the output stream and keep three staging buffers.
+  static const int allow_deep = [] { const char* e = getenv("SPLITRPC_GEMM_DEEP"); return e ? atoi(e) : 1; }();
+  const bool deep = allow_deep && !p.res_tma && p.panel_kb >= 8;
+  if (bn == 64) {
+    if (deep) return launch<64, 8, 1>(ta, tb, to, tr, p, ep, use_tma_store, status, st);
+    return launch<64, 6, OUT_BUFS>(ta, tb, to, tr, p, ep, use_tma_store, status, st);
+  }
   if (bn == 256) return launch<256, 3, 1>(ta, tb, to, tr, p, ep, use_tma_store, status, st);
   if (bn == 192) return launch<192, 4, 1>(ta, tb, to, tr, p, ep, use_tma_store, status, st);
+  if (deep) return launch<128, 6, 1>(ta, tb, to, tr, p, ep, use_tma_store, status, st);
   return launch<128, 4, OUT_BUFS>(ta, tb, to, tr, p, ep, use_tma_store, status, st);
 }
 
@@ -781,11 +796,6 @@ cudaError_t srpc_gemm_bf16_v2(const void* A, int lda, const void* B, int ldb, in
   if ((lda % 8) || (ldb % 8) || (K % 8) || ((uintptr_t)A & 15) || ((uintptr_t)B & 15)) return cudaErrorInvalidValue;
   if (ep.bias && ((uintptr_t)ep.bias & 15)) return cudaErrorInvalidValue;
   int use_tma_store = (!ep.out_fp32 && (ep.ldo % 8) == 0 && ((uintptr_t)ep.out & 15) == 0) ? 1 : 0;
-  if (use_tma_store) {
-    // Epilogue store path: 1 = staged TMA store (default), 3 = 16-byte vector stores straight from registers.
-    static const int mode = [] { const char* e = getenv("SPLITRPC_GEMM_STORE"); return e ? atoi(e) : 1; }();
-    if (mode >= 2 && mode <= 5) use_tma_store = mode;
-  }
   static const int allow_res_tma = [] { const char* e = getenv("SPLITRPC_GEMM_RES_TMA"); return e ? atoi(e) : 1; }();
   // Short-K shapes are bound by memory and gain from the prefetched residual; with a long K the plain residual loads of
   // the epilogue hide behind the next tile's MMAs and the tile width matters more.
@@ -803,6 +813,7 @@ cudaError_t srpc_gemm_bf16_v2(const void* A, int lda, const void* B, int ldb, in
   p.N = N;
   p.K = K;
   p.num_kb = (K + BK - 1) / BK;
+  p.panel_kb = p.num_kb;
   p.tiles_m = (M + BM - 1) / BM;
   p.tiles_n = (N + bn - 1) / bn;
   CUtensorMap ta, tb, to;
@@ -860,16 +871,32 @@ cudaError_t srpc_conv_bf16_tma(const void* in, const void* weight, const ConvSha
   p.s = cs.s;
   p.cblocks = cs.cin / BK;
   p.num_kb = cs.r * cs.s * p.cblocks;
+  p.panel_kb = p.num_kb;
   p.stride = cs.stride;
   p.pad = cs.pad;
-  pick_patch(cs.ow, cs.oh, cs.n, &p.pw, &p.ph, &p.pn);
+  // Row-tap reuse: 8-pixel-wide patches, so that a step of one image row inside the box is 1024 bytes (one swizzle
+  // atom) and the shifted A descriptors stay aligned; the box (ph + r - 1 rows) must fit the 128-row A slot.
+  static const int allow_reuse = [] { const char* e = getenv("SPLITRPC_CONV_REUSE"); return e ? atoi(e) : 1; }();
+  const bool reuse = allow_reuse && cs.stride == 1 && cs.r >= 2 && cs.r <= 4 && cs.ow >= 14 && cs.oh >= 8;
+  int bn;
+  if (reuse) {
+    p.reuse = 1;
+    p.pw = 8;
+    p.ph = std::min(cs.oh, 16 - (cs.r - 1));
+    p.pn = 1;
+    p.num_kb = cs.s * p.cblocks;  // load groups
+  } else {
+    pick_patch(cs.ow, cs.oh, cs.n, &p.pw, &p.ph, &p.pn);
+  }
   p.rows_used = p.pw * p.ph * p.pn;
   p.tiles_w = (cs.ow + p.pw - 1) / p.pw;
   p.tiles_h = (cs.oh + p.ph - 1) / p.ph;
   p.tiles_m = p.tiles_w * p.tiles_h * ((cs.n + p.pn - 1) / p.pn);
-  const int bn = pick_bn(cs.cout, p.tiles_m, p.num_kb, true);
+  if (reuse) bn = cs.cout <= 64 ? 64 : 128;  // r B tiles travel with every A box: wider tiles leave too few stages
+  else bn = pick_bn(cs.cout, p.tiles_m, p.num_kb, true);
   p.tiles_n = (cs.cout + bn - 1) / bn;
-  p.a_box_bytes = (uint32_t)p.rows_used * 128u;
+  const int box_rows = reuse ? p.ph + cs.r - 1 : p.ph * cs.stride;
+  p.a_box_bytes = reuse ? (uint32_t)(box_rows * p.pw) * 128u : (uint32_t)p.rows_used * 128u;
   CUtensorMap ta, tb, to;
   {
     const uint64_t pix = cs.in_pix_stride ? (uint64_t)cs.in_pix_stride : (uint64_t)cs.cin;
@@ -878,7 +905,7 @@ cudaError_t srpc_conv_bf16_tma(const void* in, const void* weight, const ConvSha
     if ((pix % 8) || (rowst % 8) || (imgst % 8)) return cudaErrorInvalidValue;
     uint64_t dims[4] = {(uint64_t)cs.cin, (uint64_t)cs.w, (uint64_t)cs.h, (uint64_t)cs.n};
     uint64_t st[3] = {pix * 2, rowst * 2, imgst * 2};
-    uint32_t box[4] = {BK, (uint32_t)(p.pw * cs.stride), (uint32_t)(p.ph * cs.stride), (uint32_t)p.pn};
+    uint32_t box[4] = {BK, (uint32_t)(p.pw * cs.stride), (uint32_t)box_rows, (uint32_t)p.pn};
     uint32_t es[4] = {1, (uint32_t)cs.stride, (uint32_t)cs.stride, 1};
     if (box[1] > 256 || box[2] > 256) return cudaErrorInvalidValue;
     cudaError_t e = get_map(&ta, in, 4, dims, st, box, es);

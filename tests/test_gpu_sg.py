@@ -47,6 +47,39 @@ def test_sg_copy_matches_reference(C, torch_cuda, impl, align):
     assert torch.equal(dst, ref)
 
 
+@pytest.mark.parametrize("n_blocks", [-1, -3, -12, 5])
+def test_sg_copy_fat_blocks(C, torch_cuda, n_blocks):
+    """Negative block counts run 1024-thread blocks (four chunk groups each); unaligned items take the byte paths."""
+    torch = torch_cuda
+    rng = np.random.default_rng(11)
+    for align in (True, False):
+        src, dst, ref, items = _random_list(torch, rng, 53, 90000, align)
+        C.sg_copy(items, 0, n_blocks)
+        torch.cuda.synchronize()
+        assert torch.equal(dst, ref)
+
+
+def test_persistent_grid_leaves_reserved_sms(C, torch_cuda):
+    """gemm_reserve_sms shrinks the persistent grids; results do not change."""
+    torch = torch_cuda
+    from splitrpc_b200 import ops
+
+    a = (torch.randn(1024, 512, device="cuda") * 0.3).bfloat16()
+    b = (torch.randn(768, 512, device="cuda") * 0.3).bfloat16()
+    full = C.gemm_grid_sms() + C.gemm_reserved_sms()
+    try:
+        C.gemm_reserve_sms(12)
+        assert C.gemm_grid_sms() == full - 12 and C.gemm_reserved_sms() == 12
+        got = ops.gemm(a, b)
+    finally:
+        C.gemm_reserve_sms(0)
+    want = ops.gemm(a, b)
+    ops.check_status()
+    assert torch.equal(got, want)
+    ref = a.float() @ b.float().t()
+    assert ((got.float() - ref).norm() / ref.norm()).item() < 1e-2
+
+
 def test_sg_copy_from_mapped_host_memory(C, torch_cuda):
     torch = torch_cuda
     host = torch.randint(0, 256, (1 << 20,), dtype=torch.uint8).pin_memory()
