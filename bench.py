@@ -154,7 +154,11 @@ def device_timed(srv, steps: int, warmup: int):
         if i >= n_sets:
             sg_stream.wait_event(done[i - n_sets])  # the window's previous batch has been answered
         # PCIe-bound: a few 1024-thread blocks on the SMs that the model's persistent kernels leave free
-        _C.sg_list_launch(lists[w], 0, -srv.reserve_sms if srv.reserve_sms > 0 else 48, sg_stream.cuda_stream)
+        gb = -srv.reserve_sms if srv.reserve_sms > 0 else 48
+        if srv.fused_ingress:  # gather + deserialise in one kernel, as the server's engine does
+            _C.sg_list_launch_stem_s2d(lists[w], req_base, req, srv.ingress["mean"], srv.ingress["inv_std"], gb, sg_stream.cuda_stream)
+        else:
+            _C.sg_list_launch(lists[w], 0, gb, sg_stream.cuda_stream)
         gathered[i].record(sg_stream)
         stream.wait_event(gathered[i])
         # the stub is re-pointed in stream order, as the stream-armed server mode does

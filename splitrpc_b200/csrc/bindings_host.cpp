@@ -461,6 +461,18 @@ PYBIND11_MODULE(_C, m) {
         auto* mp = a.info->app_rr_pool->rr_mem_pool;
         return py::make_tuple((uintptr_t)mp->get_req_addr_range(), mp->get_req_addr_pool_size(), mp->is_double_mapped());
       })
+      // Gathers into this app's request ring deserialise ResNet images on the way (fp32 CHW -> normalised bf16
+      // space-to-depth, see sg_kernels.cuh); an empty mean list switches back to plain copies.  The caller zeroes the
+      // ring once before the first request.
+      .def("set_ingress_stem_s2d",
+           [](AppHolder& a, std::vector<float> mean, std::vector<float> inv_std) {
+             auto* mp = a.info->app_rr_pool->rr_mem_pool;
+             if (mean.empty()) return a.engine->set_gather_transform(SG_TRANSFORM_NONE, 0, 0, nullptr) == 0;
+             if (mean.size() != 3 || inv_std.size() != 3) throw std::invalid_argument("mean / inv_std need 3 values");
+             float params[6] = {mean[0], mean[1], mean[2], inv_std[0], inv_std[1], inv_std[2]};
+             return a.engine->set_gather_transform(SG_TRANSFORM_STEM_S2D, (uint64_t)(uintptr_t)mp->get_req_addr_range(),
+                                                   (uint32_t)a.info->app_rr_pool->req_size, params) == 0;
+           })
       .def_property_readonly("resp_ring", [](AppHolder& a) {
         auto* mp = a.info->app_rr_pool->rr_mem_pool;
         return py::make_tuple((uintptr_t)mp->get_resp_addr_range(), mp->get_resp_addr_pool_size(), mp->is_double_mapped());

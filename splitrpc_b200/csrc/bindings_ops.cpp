@@ -53,11 +53,23 @@ void bind_ops(py::module_& m) {
           check(srpc_sg_cast_list(items, scale, shift, n_blocks, (cudaStream_t)stream), "sg_cast_bf16");
         },
         py::arg("items"), py::arg("scale") = 1.0f, py::arg("shift") = 0.0f, py::arg("n_blocks") = 0, py::arg("stream") = 0);
+  m.def("memset_async", [](uintptr_t dst, int value, size_t n, uintptr_t stream) {
+    check(cudaMemsetAsync((void*)dst, value, n, (cudaStream_t)stream), "memset_async");
+  });
   m.def("memcpy_async", [](uintptr_t dst, uintptr_t src, size_t n, uintptr_t stream) {
     check(cudaMemcpyAsync((void*)dst, (const void*)src, n, cudaMemcpyDefault, (cudaStream_t)stream), "memcpy_async");
   });
   m.def("sg_list_create", &srpc_sg_list_create);
   m.def("sg_list_destroy", &srpc_sg_list_destroy);
+  m.def("sg_list_launch_stem_s2d",
+        [](uintptr_t h, uintptr_t ring_base, uint32_t slot_bytes, std::vector<float> mean, std::vector<float> inv_std, int n_blocks,
+           uintptr_t stream) {
+          if (mean.size() != 3 || inv_std.size() != 3) throw std::invalid_argument("mean / inv_std need 3 values");
+          check(srpc_sg_list_launch_stem_s2d(h, ring_base, slot_bytes, mean.data(), inv_std.data(), n_blocks, (cudaStream_t)stream),
+                "sg_list_launch_stem_s2d");
+        },
+        py::arg("handle"), py::arg("ring_base"), py::arg("slot_bytes"), py::arg("mean"), py::arg("inv_std"), py::arg("n_blocks") = 0,
+        py::arg("stream") = 0);
   m.def("sg_list_launch",
         [](uintptr_t h, int impl, int n_blocks, uintptr_t stream) {
           check(srpc_sg_list_launch(h, impl, n_blocks, (cudaStream_t)stream), "sg_list_launch");
@@ -83,11 +95,14 @@ void bind_ops(py::module_& m) {
   m.def("conv_bf16",
         [](uintptr_t in, uintptr_t w, int n, int h, int wd, int cin, int cout, int r, int s, int stride, int pad,
            uintptr_t out, uintptr_t bias, uintptr_t residual, int act, uintptr_t status, uintptr_t stream, int impl,
-           long pix_stride, long row_stride, long img_stride) {
+           long pix_stride, long row_stride, long img_stride, uintptr_t in_stub, long ring_slots, unsigned int slot_bytes) {
           ConvShape cs{n, h, wd, cin, cout, r, s, stride, pad, (h + 2 * pad - r) / stride + 1, (wd + 2 * pad - s) / stride + 1};
           cs.in_pix_stride = pix_stride;
           cs.in_row_stride = row_stride;
           cs.in_img_stride = img_stride;
+          cs.in_stub = (const void*)in_stub;
+          cs.in_ring_slots = ring_slots;
+          cs.in_slot_bytes = slot_bytes;
           if ((pix_stride || row_stride || img_stride) && impl == 1)
             throw std::invalid_argument("conv_bf16: input strides need the TMA implementation");
           GemmEpilogue ep = make_ep(out, cout, false, bias, residual, cout, act);
@@ -97,14 +112,15 @@ void bind_ops(py::module_& m) {
         py::arg("input"), py::arg("weight"), py::arg("n"), py::arg("h"), py::arg("w"), py::arg("cin"), py::arg("cout"),
         py::arg("r"), py::arg("s"), py::arg("stride"), py::arg("pad"), py::arg("out"), py::arg("bias") = 0,
         py::arg("residual") = 0, py::arg("act") = 0, py::arg("status") = 0, py::arg("stream") = 0, py::arg("impl") = 2,
-        py::arg("pix_stride") = 0, py::arg("row_stride") = 0, py::arg("img_stride") = 0);
+        py::arg("pix_stride") = 0, py::arg("row_stride") = 0, py::arg("img_stride") = 0, py::arg("in_stub") = 0,
+        py::arg("ring_slots") = 0, py::arg("slot_bytes") = 0);
 
   m.def("gemm_reserve_sms", [](int n) { srpc_gemm_reserve_sms(n); }, py::arg("n"));
   m.def("gemm_grid_sms", []() { return srpc_gemm_grid_sms(); });
   m.def("gemm_reserved_sms", []() { return srpc_gemm_reserved_sms(); });
   m.def("gemm_trace", [](bool two_sm) {
-    unsigned long long t[12] = {0};
-    int n = two_sm ? srpc_gemm2_trace_read(t, 12) : srpc_gemm_trace_read(t, 10);
+    unsigned long long t[16] = {0};
+    int n = two_sm ? srpc_gemm2_trace_read(t, 12) : srpc_gemm_trace_read(t, 16);
     std::vector<uint64_t> v(t, t + n);
     return v;
   }, py::arg("two_sm") = false);

@@ -80,6 +80,12 @@ struct TileParams {
   // short-tile k loop) for a 3 x 3 filter.  num_kb then counts load groups (s * cblocks); panel_kb counts all k-blocks.
   int reuse;
   int panel_kb;
+  // Input that lives in a request ring (convolution mode): the tensor map covers the whole ring, one "image" per slot,
+  // and the batch starts at the slot that the app stub's request pointer names when the kernel runs, so one captured
+  // graph serves every ring position.  in_stub == nullptr: the input starts at image 0.
+  const void* in_stub;
+  unsigned long long in_ring_base;
+  unsigned int in_slot_bytes;
 };
 
 __device__ __forceinline__ float gelu_f(float x) { return ptx::gelu_erf_fast(x); }
@@ -229,6 +235,9 @@ gemm_conv_persistent(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   int pr_s = 0, pr_j = 0, pr_kb = 0;
   uint32_t pr_ph = 0;
   bool pr_more = true;
+  int img_off = 0;
+  if (threadIdx.x == 0 && p.in_stub)
+    img_off = (int)((*reinterpret_cast<const unsigned long long*>(p.in_stub) - p.in_ring_base) / p.in_slot_bytes);
   auto produce = [&](int budget) {
     const uint32_t b_tx = (uint32_t)(b_per_stage * B_BYTES);
     TileCoord tc;
@@ -251,7 +260,7 @@ gemm_conv_persistent(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
           // load group (fs, cb): the box covers filter rows 0 .. r-1 at once
           ptx::mbar_expect_tx(&full_bar[pr_s], p.a_box_bytes + b_tx);
           const int fs = pr_kb / p.cblocks, cb = pr_kb - fs * p.cblocks;
-          tma_load_4d_box(sa, &tmap_a, &full_bar[pr_s], cb * BK, tc.w0 + fs - p.pad, tc.h0 - p.pad, tc.img0);
+          tma_load_4d_box(sa, &tmap_a, &full_bar[pr_s], cb * BK, tc.w0 + fs - p.pad, tc.h0 - p.pad, tc.img0 + img_off);
           if (!p.b_stationary)
             for (int fr = 0; fr < p.r; fr++)
               ptx::tma_load_2d(sa + A_BYTES + fr * B_BYTES, &tmap_b, &full_bar[pr_s], ((fr * p.s + fs) * p.cblocks + cb) * BK,
@@ -261,7 +270,7 @@ gemm_conv_persistent(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
           const int tap = pr_kb / p.cblocks, cb = pr_kb - tap * p.cblocks;
           const int fr = tap / p.s, fs = tap - fr * p.s;
           tma_load_4d_box(sa, &tmap_a, &full_bar[pr_s], cb * BK, tc.w0 * p.stride + fs - p.pad,
-                          tc.h0 * p.stride + fr - p.pad, tc.img0);
+                          tc.h0 * p.stride + fr - p.pad, tc.img0 + img_off);
         }
         if (!p.b_stationary && !p.reuse) ptx::tma_load_2d(sa + A_BYTES, &tmap_b, &full_bar[pr_s], pr_kb * BK, tc.n_idx * BN);
         if (pr_j == 0 && pr_kb == 0) GEMM_TRACE(2);
@@ -416,6 +425,7 @@ gemm_conv_persistent(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
 #pragma unroll
         for (int j = 0; j < CPW / 8; j++) resq[j] = __ldg(reinterpret_cast<const uint4*>(rp) + j);
       }
+      if (j == 5 && et == 0) GEMM_TRACE(10);
       float* bias_s = s_bias[local & 1u];
       if (ep.bias && et < BN) bias_s[et] = (n0 + et < p.N) ? __ldg(ep.bias + n0 + et) : 0.f;
       // Each thread's wait is bounded; the vote makes the outcome uniform so that no
@@ -428,6 +438,7 @@ gemm_conv_persistent(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       }
       ptx::tc_fence_after();
       if (j == 0 && et == 0) GEMM_TRACE(5);
+      if (j == 5 && et == 0) GEMM_TRACE(11);
       uint32_t r[LEAN ? 32 : CPW];
       const uint32_t t_addr = tmem_base + acc * ACC_STRIDE + ((uint32_t)(warp_q * 32) << 16) + (uint32_t)cbase;
       if (!LEAN) {
@@ -439,6 +450,7 @@ gemm_conv_persistent(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive(&tmem_empty_bar[acc]);
       }
+      if (j == 5 && et == 0) GEMM_TRACE(12);
       uint8_t* sbuf = stage_out + (size_t)(local % OB) * OUT_BYTES;
       if (use_tma_store && !res_tma) {
         // The store issued OB tiles ago must have finished reading this staging buffer.  (With the residual in the
@@ -541,9 +553,11 @@ gemm_conv_persistent(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
           }
         }
       }
+      if (j == 5 && et == 0) GEMM_TRACE(13);
       if (use_tma_store) {
         ptx::fence_proxy_async_smem();
         named_bar_sync(1, EPI_THREADS);
+        if (j == 5 && et == 0) GEMM_TRACE(14);
         if (et == 0) {
 #pragma unroll
           for (int hcol = 0; hcol < BN / 64; hcol++) {
@@ -560,6 +574,7 @@ gemm_conv_persistent(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
             ptx::bulk_wait_read<(OB > RES_DIST ? OB - RES_DIST : 0)>();
             load_residual(j + RES_DIST);
           }
+          if (j == 5) GEMM_TRACE(15);
         }
       }
     }
@@ -903,8 +918,12 @@ cudaError_t srpc_conv_bf16_tma(const void* in, const void* weight, const ConvSha
     const uint64_t rowst = cs.in_row_stride ? (uint64_t)cs.in_row_stride : (uint64_t)cs.w * pix;
     const uint64_t imgst = cs.in_img_stride ? (uint64_t)cs.in_img_stride : (uint64_t)cs.h * rowst;
     if ((pix % 8) || (rowst % 8) || (imgst % 8)) return cudaErrorInvalidValue;
-    uint64_t dims[4] = {(uint64_t)cs.cin, (uint64_t)cs.w, (uint64_t)cs.h, (uint64_t)cs.n};
+    if (cs.in_stub && (cs.in_ring_slots < cs.n || !cs.in_slot_bytes || imgst * 2 != cs.in_slot_bytes)) return cudaErrorInvalidValue;
+    uint64_t dims[4] = {(uint64_t)cs.cin, (uint64_t)cs.w, (uint64_t)cs.h, (uint64_t)(cs.in_stub ? cs.in_ring_slots : cs.n)};
     uint64_t st[3] = {pix * 2, rowst * 2, imgst * 2};
+    p.in_stub = cs.in_stub;
+    p.in_ring_base = (unsigned long long)(uintptr_t)in;
+    p.in_slot_bytes = cs.in_slot_bytes;
     uint32_t box[4] = {BK, (uint32_t)(p.pw * cs.stride), (uint32_t)box_rows, (uint32_t)p.pn};
     uint32_t es[4] = {1, (uint32_t)cs.stride, (uint32_t)cs.stride, 1};
     if (box[1] > 256 || box[2] > 256) return cudaErrorInvalidValue;

@@ -35,6 +35,12 @@ struct ConvShape {
   // stride smaller than cin makes neighbouring pixels overlap: a window of several narrow pixels is then read as one
   // 64-channel pixel without being copied first (TMA path only; every stride a multiple of 8 elements).
   long in_pix_stride = 0, in_row_stride = 0, in_img_stride = 0;
+  // Input inside a request ring (TMA path): `in` is the ring base, in_ring_slots images of in_slot_bytes each are
+  // addressable (both mappings of a double-mapped ring), and the batch starts at the slot that *(uint8_t**)in_stub
+  // points to when the kernel runs.  in_img_stride must then equal in_slot_bytes / 2.
+  const void* in_stub = nullptr;
+  long in_ring_slots = 0;
+  unsigned int in_slot_bytes = 0;
 };
 
 // D[M,N] = A[M,K] . B[N,K]^T, bf16 operands (row strides lda/ldb elements, multiples of 8), fp32 accumulation.

@@ -18,3 +18,6 @@ cudaError_t srpc_sg_cast_list(const std::vector<SgTuple>& items, float scale, fl
 uintptr_t srpc_sg_list_create(const std::vector<SgTuple>& items);
 void srpc_sg_list_destroy(uintptr_t handle);
 cudaError_t srpc_sg_list_launch(uintptr_t handle, int impl, int n_blocks, cudaStream_t stream);
+// The same list run through the fused gather + ResNet-stem deserialisation kernel (see sg_kernels.cuh).
+cudaError_t srpc_sg_list_launch_stem_s2d(uintptr_t handle, uint64_t ring_base, uint32_t slot_bytes, const float mean[3],
+                                         const float inv_std[3], int n_blocks, cudaStream_t stream);

@@ -113,7 +113,11 @@ class P2pRpcSgGpuEngine : public P2pRpcSgEngine {
     return 0;
   }
 
-  int submit(uint32_t n) {
+  // Optional transform applied by gathers (not by scatters): see set_gather_transform.
+  bool has_transform_ = false;
+  SgStemS2d transform_{};
+
+  int submit(uint32_t n, bool gather = false) {
     if (n == 0) return 0;
     counters.items += n;
     for (uint32_t i = 0; i < n; i++) counters.bytes += h_items_[i].len;
@@ -130,8 +134,12 @@ class P2pRpcSgGpuEngine : public P2pRpcSgEngine {
       default: {
         uint32_t chunks = sg_assign_chunks(h_items_, n);
         e = cudaMemcpyAsync(d_items_, h_items_, n * sizeof(SgItem), cudaMemcpyHostToDevice, stream_);
-        if (e == cudaSuccess)
-          e = sg_launch_copy(d_items_, n, chunks, copy_type_ == 3 ? SG_IMPL_BULK : SG_IMPL_SIMT, blocks_for(h_items_[0]), stream_);
+        if (e == cudaSuccess) {
+          if (gather && has_transform_)
+            e = sg_launch_stem_s2d(d_items_, n, chunks, transform_, blocks_for(h_items_[0]), stream_);
+          else
+            e = sg_launch_copy(d_items_, n, chunks, copy_type_ == 3 ? SG_IMPL_BULK : SG_IMPL_SIMT, blocks_for(h_items_[0]), stream_);
+        }
         if (e == cudaSuccess) e = cudaStreamSynchronize(stream_);
       }
     }
@@ -197,12 +205,12 @@ class P2pRpcSgGpuEngine : public P2pRpcSgEngine {
     for (int i = 0; i < n; i++) {
       gather_skbs(rrs[i]->payload_sk_bufs, rrs[i]->payload_bufs, stubs[i]->req);
       if (!append(rrs[i]->payload_sk_bufs, &ni)) {
-        rc |= submit(ni);
+        rc |= submit(ni, true);
         ni = 0;
         append(rrs[i]->payload_sk_bufs, &ni);
       }
     }
-    rc |= submit(ni);
+    rc |= submit(ni, true);
     counters.gathers += (uint64_t)n;
     PROF_STOP(Gather);
     return rc;
@@ -232,6 +240,21 @@ class P2pRpcSgGpuEngine : public P2pRpcSgEngine {
     uint32_t ni = 0;
     if (!append(skb, &ni)) return -4;
     return submit(ni);
+  }
+  int set_gather_transform(int kind, uint64_t ring_base, uint32_t slot_bytes, const float* params) override {
+    if (kind == 0) {
+      has_transform_ = false;
+      return 0;
+    }
+    if (kind != SG_TRANSFORM_STEM_S2D || copy_type_ != 2 || !params) return -1;
+    transform_.ring_base = ring_base;
+    transform_.slot_bytes = slot_bytes;
+    for (int i = 0; i < 3; i++) {
+      transform_.mean[i] = params[i];
+      transform_.inv_std[i] = params[3 + i];
+    }
+    has_transform_ = true;
+    return 0;
   }
   const char* name() const override { return "gpu"; }
 };
@@ -284,6 +307,13 @@ cudaError_t srpc_sg_list_launch(uintptr_t handle, int impl, int n_blocks, cudaSt
   auto* h = reinterpret_cast<SgListHandle*>(handle);
   if (!h) return cudaErrorInvalidValue;
   return sg_launch_copy(h->d_items, h->n, h->chunks, impl, n_blocks, stream);
+}
+cudaError_t srpc_sg_list_launch_stem_s2d(uintptr_t handle, uint64_t ring_base, uint32_t slot_bytes, const float mean[3],
+                                         const float inv_std[3], int n_blocks, cudaStream_t stream) {
+  auto* h = reinterpret_cast<SgListHandle*>(handle);
+  if (!h) return cudaErrorInvalidValue;
+  SgStemS2d tr{ring_base, slot_bytes, {mean[0], mean[1], mean[2]}, {inv_std[0], inv_std[1], inv_std[2]}};
+  return sg_launch_stem_s2d(h->d_items, h->n, h->chunks, tr, n_blocks, stream);
 }
 cudaError_t srpc_sg_copy_list(const std::vector<SgTuple>& items, int impl, int n_blocks, cudaStream_t stream) {
   uintptr_t h = srpc_sg_list_create(items);

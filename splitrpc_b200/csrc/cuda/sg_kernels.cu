@@ -197,6 +197,70 @@ __global__ void __launch_bounds__(256) sg_cast_bf16(const SgItem* __restrict__ i
   }
 }
 
+// Gather fused with the deserialisation of a ResNet request: the fragments of an fp32 3 x 224 x 224 image are read
+// where the NIC put them and written, normalised and cast to bf16, in the space-to-depth layout that the stem
+// convolution reads through TMA (see stem_s2d in nn_kernels.cu for the layout).  The copy list is the ordinary one:
+// an item's destination address says which ring slot and which byte offset of the request the bytes belong to, so
+// fragments may arrive split and in any order.  The slot then holds the [115][115][16] bf16 tensor (423,200 bytes,
+// less than the 602,112-byte request it replaces); border pixels and padding channels are never written and keep
+// the zeros the ring was created with.
+__global__ void __launch_bounds__(1024) sg_stem_s2d(const SgItem* __restrict__ items, uint32_t n_items, uint32_t n_chunks,
+                                                    SgStemS2d tr) {
+  const uint32_t groups = blockDim.x >> 8;
+  const uint32_t g = blockIdx.x * groups + (threadIdx.x >> 8), ng = gridDim.x * groups;
+  const uint32_t t = threadIdx.x & 255u;
+  for (uint32_t c = g; c < n_chunks; c += ng) {
+    const uint32_t it = find_item(items, n_items, c);
+    const uint64_t off = (uint64_t)(c - items[it].first_chunk) * SG_CHUNK;
+    const uint32_t left = items[it].len - (uint32_t)off;
+    const uint32_t len = left < SG_CHUNK ? left : SG_CHUNK;
+    const uint8_t* src = reinterpret_cast<const uint8_t*>(items[it].src + off);
+    const uint64_t rel = items[it].dst + off - tr.ring_base;
+    const uint64_t slot = rel / tr.slot_bytes;
+    const uint32_t req_off = (uint32_t)(rel - slot * tr.slot_bytes);
+    __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(tr.ring_base + slot * tr.slot_bytes);
+    if ((req_off | len | (uint32_t)(uintptr_t)src) & 3u) continue;  // requests are whole floats
+    const uint32_t e0 = req_off >> 2, n = len >> 2;
+    auto put = [&](uint32_t e, float v) {
+      if (e >= 3u * 224u * 224u) return;
+      const uint32_t ch = e / 50176u, rem = e - ch * 50176u;
+      const uint32_t iy = rem / 224u, ix = rem - iy * 224u;
+      const uint32_t py = iy + 3u, px = ix + 3u;
+      const float m = ch == 0 ? tr.mean[0] : (ch == 1 ? tr.mean[1] : tr.mean[2]);
+      const float s = ch == 0 ? tr.inv_std[0] : (ch == 1 ? tr.inv_std[1] : tr.inv_std[2]);
+      out[((py >> 1) * 115u + (px >> 1)) * 16u + (py & 1u) * 8u + (px & 1u) * 3u + ch] = __float2bfloat16((v - m) * s);
+    };
+    if ((((uintptr_t)src) & 15) == 0) {
+      const uint32_t nv = n >> 2;
+      const float4* s4 = reinterpret_cast<const float4*>(src);
+      uint32_t i = t;
+      for (; i + 3 * 256 < nv; i += 4 * 256) {  // four loads in flight per thread, as in the plain copy
+        const float4 a = s4[i], b = s4[i + 256], d = s4[i + 512], f = s4[i + 768];
+        const float4 q[4] = {a, b, d, f};
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+          const uint32_t e = e0 + 4u * (i + 256u * k);
+          put(e, q[k].x);
+          put(e + 1, q[k].y);
+          put(e + 2, q[k].z);
+          put(e + 3, q[k].w);
+        }
+      }
+      for (; i < nv; i += 256) {
+        const float4 a = s4[i];
+        const uint32_t e = e0 + 4u * i;
+        put(e, a.x);
+        put(e + 1, a.y);
+        put(e + 2, a.z);
+        put(e + 3, a.w);
+      }
+      for (uint32_t j = (nv << 2) + t; j < n; j += 256) put(e0 + j, reinterpret_cast<const float*>(src)[j]);
+    } else {
+      for (uint32_t j = t; j < n; j += 256) put(e0 + j, reinterpret_cast<const float*>(src)[j]);
+    }
+  }
+}
+
 // Resident engine.  Each block polls the doorbell; a new sequence number means
 // the item list is valid.  Blocks never wait for one another: each finishes its
 // share, and the block that brings the arrival counter to gridDim.x * seq
@@ -315,6 +379,25 @@ cudaError_t sg_launch_cast_bf16(const SgItem* d_items, uint32_t n_items, uint32_
   if (n_items == 0 || n_chunks == 0) return cudaSuccess;
   sg_kernel_setup();
   sg_cast_bf16<<<clamp_blocks(n_blocks, n_chunks), 256, 0, stream>>>(d_items, n_items, n_chunks, scale, shift);
+  return cudaGetLastError();
+}
+
+cudaError_t sg_launch_stem_s2d(const SgItem* d_items, uint32_t n_items, uint32_t n_chunks, const SgStemS2d& tr, int n_blocks,
+                               cudaStream_t stream) {
+  if (n_items == 0 || n_chunks == 0) return cudaSuccess;
+  if (!tr.ring_base || !tr.slot_bytes || (tr.slot_bytes & 15u)) return cudaErrorInvalidValue;
+  static bool setup = false;
+  if (!setup) {
+    prefer_max_shared(sg_stem_s2d);
+    (void)cudaGetLastError();
+    setup = true;
+  }
+  if (n_blocks < 0) {
+    const uint32_t want = (uint32_t)(-n_blocks), most = (n_chunks + 3) / 4;
+    sg_stem_s2d<<<want < most ? want : most, 1024, 0, stream>>>(d_items, n_items, n_chunks, tr);
+  } else {
+    sg_stem_s2d<<<clamp_blocks(n_blocks, n_chunks), 256, 0, stream>>>(d_items, n_items, n_chunks, tr);
+  }
   return cudaGetLastError();
 }
 

@@ -44,6 +44,16 @@ cudaError_t sg_launch_copy(const SgItem* d_items, uint32_t n_items, uint32_t n_c
 // computing (x - shift) * scale on the way.
 cudaError_t sg_launch_cast_bf16(const SgItem* d_items, uint32_t n_items, uint32_t n_chunks, float scale, float shift,
                                 int n_blocks, cudaStream_t stream);
+// Gather fused with the ResNet stem's deserialisation (fp32 CHW fragments -> normalised bf16 space-to-depth tensor in
+// the ring slot).  ring_base / slot_bytes describe the request ring that the items' destinations point into.
+struct SgStemS2d {
+  uint64_t ring_base;
+  uint32_t slot_bytes;
+  float mean[3];
+  float inv_std[3];
+};
+cudaError_t sg_launch_stem_s2d(const SgItem* d_items, uint32_t n_items, uint32_t n_chunks, const SgStemS2d& tr, int n_blocks,
+                               cudaStream_t stream);
 // Persistent engine: `counter` is a zero-initialised device word.
 cudaError_t sg_launch_persistent(SgCtrl* d_ctrl, uint32_t* d_counter, int n_blocks, cudaStream_t stream);
 

@@ -106,6 +106,8 @@ struct SgCounters {
   uint64_t gathers = 0, scatters = 0, items = 0, bytes = 0, timeouts = 0;
 };
 
+enum { SG_TRANSFORM_NONE = 0, SG_TRANSFORM_STEM_S2D = 1 };
+
 class P2pRpcSgEngine {
  public:
   int num_instances = 1;
@@ -142,6 +144,16 @@ class P2pRpcSgEngine {
     int rc = 0;
     for (int i = 0; i < n; i++) rc |= scatter(rrs[i], stubs[i]);
     return rc;
+  }
+  // Makes gathers transform the payload on the way into the ring instead of copying it (GPU engine, copy type 2).
+  // kind 0 = plain copy; SG_TRANSFORM_STEM_S2D = fp32 CHW image -> normalised bf16 space-to-depth tensor, params =
+  // {mean[3], inv_std[3]}.  ring_base / slot_bytes describe the request ring.  Returns 0 when the engine supports it.
+  virtual int set_gather_transform(int kind, uint64_t ring_base, uint32_t slot_bytes, const float* params) {
+    (void)kind;
+    (void)ring_base;
+    (void)slot_bytes;
+    (void)params;
+    return -1;
   }
   // Executes an already built copy list.  Engines that cannot copy (zero copy) return -1.
   virtual int copy_list(const p2p_sk_buf* skb) {

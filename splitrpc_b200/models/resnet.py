@@ -91,7 +91,8 @@ class ResNet50:
             if ds:
                 self.buf[name + ".ds"] = torch.empty((nb, ho, ho, width * 4), dtype=bf, device=dev)
             h = ho
-        self.kernels_per_forward = 3 + sum(3 + (1 if b[4] else 0) for b in self.blocks) + 3
+        self.kernels_per_forward = self._kernels_per_forward_base = 3 + sum(3 + (1 if b[4] else 0) for b in self.blocks) + 3
+        self.ingress_ring = None
 
     # ------------------------------------------------------------------ forward
     def _conv1x1(self, x, name, out, act, residual=None):
@@ -104,6 +105,14 @@ class ResNet50:
                  out=out.view(n * h * w, cout))
         return out
 
+    def enable_fused_ingress(self, ring_base: int, ring_slots: int, slot_bytes: int) -> dict:
+        """Tells the model that the scatter-gather engine deserialises requests on the way into the ring (fp32 CHW ->
+        normalised bf16 space-to-depth, one tensor per ring slot).  ``forward(d_stub=...)`` then starts at the stem
+        convolution, which reads the ring through one tensor map.  Returns the transform's parameters."""
+        self.ingress_ring = (ring_base, ring_slots, slot_bytes)
+        self.kernels_per_forward = self._kernels_per_forward_base - 1
+        return {"mean": list(self.mean), "inv_std": list(self.inv_std)}
+
     def forward(self, batch: int, x: torch.Tensor | None = None, d_stub: int = 0, out: torch.Tensor | None = None,
                 flag_ptr: int = 0, flag_value: int = 0, counter: torch.Tensor | None = None) -> torch.Tensor:
         """Launches the whole network for ``batch`` images on the current stream.
@@ -113,8 +122,13 @@ class ResNet50:
         """
         p, b = self.params, self.buf
         nb = batch
-        ops.stem_s2d(b["s2d"], nb, x=x, d_stub=d_stub, mean=self.mean, inv_std=self.inv_std)
-        ops.stem_conv(b["s2d"], p["stem.w_s2d"], nb, bias=p["stem.b"], act="relu", out=b["stem"][:nb])
+        if self.ingress_ring is not None and x is None:
+            # the gather already wrote the normalised space-to-depth tensors into the ring slots
+            ops.stem_conv(None, p["stem.w_s2d"], nb, bias=p["stem.b"], act="relu", out=b["stem"][:nb], ring=self.ingress_ring,
+                          d_stub=d_stub)
+        else:
+            ops.stem_s2d(b["s2d"], nb, x=x, d_stub=d_stub, mean=self.mean, inv_std=self.inv_std)
+            ops.stem_conv(b["s2d"], p["stem.w_s2d"], nb, bias=p["stem.b"], act="relu", out=b["stem"][:nb])
         cur = ops.maxpool3x3s2(b["stem"][:nb], out=b["pool"][:nb])
         for name, cin, width, s, ds in self.blocks:
             t1 = self._conv1x1(cur, name + ".c1", b[name + ".t1"][:nb], "relu")

@@ -133,11 +133,23 @@ def stem_weight_s2d(w: torch.Tensor) -> torch.Tensor:
     return w2.view(cout, 4, 1, 64).to(torch.bfloat16).contiguous()
 
 
-def stem_conv(s2d: torch.Tensor, w2: torch.Tensor, batch: int, bias: torch.Tensor | None = None, act: str | None = "relu",
-              out: torch.Tensor | None = None) -> torch.Tensor:
-    """The 7x7/2 stem as a 4x1-tap convolution over overlapping 64-channel windows of ``stem_s2d``'s output."""
-    assert s2d.dtype == torch.bfloat16 and s2d.is_contiguous() and s2d.numel() >= batch * 115 * 115 * 16
+def stem_conv(s2d: torch.Tensor | None, w2: torch.Tensor, batch: int, bias: torch.Tensor | None = None, act: str | None = "relu",
+              out: torch.Tensor | None = None, ring: tuple[int, int, int] | None = None, d_stub: int = 0) -> torch.Tensor:
+    """The 7x7/2 stem as a 4x1-tap convolution over overlapping 64-channel windows of ``stem_s2d``'s output.
+
+    With ``ring=(base, slots, slot_bytes)`` and ``d_stub`` the space-to-depth tensors are read out of a request ring
+    instead (one per slot, written by the fused gather ``sg_list_launch_stem_s2d``); the batch starts at the slot
+    that the stub's request pointer names when the kernel runs."""
     cout = w2.shape[0]
+    if ring is not None:
+        base, slots, slot_bytes = ring
+        assert d_stub and slot_bytes % 16 == 0 and slot_bytes >= 115 * 115 * 16 * 2
+        assert tuple(w2.shape) == (cout, 4, 1, 64) and w2.dtype == torch.bfloat16 and w2.is_contiguous()
+        assert out is not None and out.is_contiguous() and out.numel() >= batch * 112 * 112 * cout
+        _C.conv_bf16(base, w2.data_ptr(), batch, 115, 112, 64, cout, 4, 1, 1, 0, out.data_ptr(), _ptr(bias), 0, ACT[act],
+                     status_word().data_ptr(), _stream(), 2, 16, 115 * 16, slot_bytes // 2, d_stub, slots, slot_bytes)
+        return out
+    assert s2d.dtype == torch.bfloat16 and s2d.is_contiguous() and s2d.numel() >= batch * 115 * 115 * 16
     assert tuple(w2.shape) == (cout, 4, 1, 64) and w2.dtype == torch.bfloat16 and w2.is_contiguous()
     if out is None:
         out = torch.empty((batch, 112, 112, cout), dtype=torch.bfloat16, device=s2d.device)

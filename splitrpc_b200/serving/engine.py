@@ -18,7 +18,8 @@ MTU = 8192
 
 class ModelServer:
     def __init__(self, model, device: int = 0, max_batch: int = 64, server_mode: int = 2, copy_type: int = 2,
-                 outstanding: int | None = None, pool_size: int | None = None, batch_sizes=None, reserve_sms: int = 12):
+                 outstanding: int | None = None, pool_size: int | None = None, batch_sizes=None, reserve_sms: int = 12,
+                 fused_ingress: bool = True):
         """``reserve_sms``: SMs that the model's persistent kernels leave out of their grids, for the scatter-gather
         kernel that pulls the next batch out of host memory while the current one is computed.  A persistent kernel
         counts on one block per SM: with a foreign block on only a few SMs it takes twice as long (ResNet-50 graph
@@ -37,6 +38,19 @@ class ModelServer:
         self.app = _C.make_graph_app(device, self.req_size, self.resp_size, self.pool_size, max_batch, "gpu", copy_type)
         self.stream = torch.cuda.ExternalStream(self.app.work_stream, device=torch.device("cuda", device))
         self.batch_sizes = list(batch_sizes) if batch_sizes else list(range(1, max_batch + 1))
+        # Fused ingress: the gather that pulls a request's fragments into the ring also deserialises them for the
+        # model's first layer (models that offer enable_fused_ingress; GPU engine with one kernel per list).
+        self.fused_ingress = False
+        if fused_ingress and copy_type == 2 and hasattr(model, "enable_fused_ingress"):
+            base, nbytes, doubled = self.app.req_ring
+            slots = nbytes * (2 if doubled else 1) // self.req_size
+            tr = model.enable_fused_ingress(base, slots, self.req_size)
+            _C.memset_async(base, 0, nbytes, self.app.work_stream)  # borders and padding channels stay zero for good
+            self.stream.synchronize()
+            if not self.app.set_ingress_stem_s2d(tr["mean"], tr["inv_std"]):
+                raise RuntimeError("the scatter-gather engine does not support the fused ingress transform")
+            self.fused_ingress = True
+            self.ingress = tr
         self._capture()
         self.server = _C.Server(self.server_port, req_size=self.req_size, resp_size=self.resp_size, server_mode=server_mode,
                                 max_batch=max_batch, rr_pool_size=max(1023, 4 * self.outstanding), gather_burst=max_batch)

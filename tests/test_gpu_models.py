@@ -137,13 +137,46 @@ def test_bert_matches_fp32_reference(torch_cuda):
     torch.testing.assert_close(out, ref, rtol=5e-2, atol=3e-2)
 
 
-def test_model_server_end_to_end_resnet(torch_cuda):
+def test_fused_gather_deserialise_matches_stem_s2d(torch_cuda):
+    """The gather that writes normalised space-to-depth tensors into ring slots against stem_s2d on the raw bytes;
+    fragments are given out of order and split at odd (4-byte aligned) places."""
+    torch = torch_cuda
+    from splitrpc_b200 import _C, ops
+
+    n, req = 3, 3 * 224 * 224 * 4
+    slot_bytes = req
+    img = torch.randn(n, 3, 224, 224, device="cuda")
+    raw = img.view(torch.uint8).reshape(n, req)
+    ring = torch.zeros(8 * slot_bytes, dtype=torch.uint8, device="cuda")
+    mean, inv = (0.1, 0.2, 0.3), (2.0, 3.0, 4.0)
+    items = []
+    cuts = [0, 8192, 8192 + 4, 100000, 100000 + 16388, 300004, req]
+    for r in range(n):
+        slot = 2 + r  # the batch sits in slots 2..4
+        for a, b in reversed(list(zip(cuts[:-1], cuts[1:]))):
+            items.append((raw[r].data_ptr() + a, ring.data_ptr() + slot * slot_bytes + a, b - a))
+    h = _C.sg_list_create(items)
+    _C.sg_list_launch_stem_s2d(h, ring.data_ptr(), slot_bytes, list(mean), list(inv), -2, torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    _C.sg_list_destroy(h)
+    want = torch.zeros(n, 115, 115, 16, dtype=torch.bfloat16, device="cuda")
+    ops.stem_s2d(want, n, x=img, mean=mean, inv_std=inv)
+    torch.cuda.synchronize()
+    got = torch.stack([ring[(2 + r) * slot_bytes:(2 + r) * slot_bytes + 115 * 115 * 32].view(torch.bfloat16).view(115, 115, 16)
+                       for r in range(n)])
+    assert torch.equal(got, want)
+    assert int(ring[:2 * slot_bytes].max()) == 0 and int(ring[5 * slot_bytes:].max()) == 0
+
+
+@pytest.mark.parametrize("fused_ingress", [True, False])
+def test_model_server_end_to_end_resnet(torch_cuda, fused_ingress):
     torch = torch_cuda
     from splitrpc_b200.models import ResNet50
     from splitrpc_b200.serving import ModelServer
 
     m = ResNet50(device=0, max_batch=8)
-    srv = ModelServer(m, device=0, max_batch=8, outstanding=16)
+    srv = ModelServer(m, device=0, max_batch=8, outstanding=16, fused_ingress=fused_ingress)
+    assert srv.fused_ingress == fused_ingress
     with srv:
         cli = srv.client(total=48, warmup=0, payload="normal", verify=True, n_payloads=4)
         assert cli.run_closed_loop(16)
