@@ -839,10 +839,11 @@ cudaError_t srpc_gemm_bf16_v2(const void* A, int lda, const void* B, int ldb, in
   if (ep.bias && ((uintptr_t)ep.bias & 15)) return cudaErrorInvalidValue;
   int use_tma_store = (!ep.out_fp32 && (ep.ldo % 8) == 0 && ((uintptr_t)ep.out & 15) == 0) ? 1 : 0;
   static const int allow_res_tma = [] { const char* e = getenv("SPLITRPC_GEMM_RES_TMA"); return e ? atoi(e) : 1; }();
+  static const int res_tma_max_k = [] { const char* e = getenv("SPLITRPC_GEMM_RES_TMA_MAXK"); return e ? atoi(e) : 512; }();
   // Short-K shapes are bound by memory and gain from the prefetched residual; with a long K the plain residual loads of
   // the epilogue hide behind the next tile's MMAs and the tile width matters more.
   const bool res_tma = allow_res_tma && use_tma_store == 1 && ep.residual && (ep.ldr % 8) == 0 &&
-                       ((uintptr_t)ep.residual & 15) == 0 && K <= 512;
+                       ((uintptr_t)ep.residual & 15) == 0 && K <= res_tma_max_k;
   // The residual ring lives in the output staging buffers, which the wide tiles have only one of.
   bool two_sm = false;
   const int bn = res_tma ? (N <= 64 ? 64 : 128)
