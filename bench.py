@@ -311,42 +311,51 @@ def run_tp(args, rank: int, world: int, local_rank: int) -> dict:
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     sampler = ClockSampler(local_rank)
 
-    def one_step(i, e2e):
-        if e2e:
-            ids_dev.copy_(ids_host[i % n_sets], non_blocking=True)  # host -> device copy of the step's inputs
+    def one_step(i):
         graph.replay()
-        if e2e:
-            probs_host.copy_(probs, non_blocking=True)              # device -> host read of the result
 
     results = {}
     with torch.cuda.stream(stream):
-        for mode in ("device", "e2e"):
-            for i in range(warm):
-                one_step(i, mode == "e2e")
-            stream.synchronize()
-            dist.barrier()
-            if mode == "device":
-                sampler.start()
-            evs = []
-            for i in range(args.steps):
-                if mode == "device":
-                    flush.zero_()
-                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                e0.record(stream)
-                one_step(i, mode == "e2e")
-                e1.record(stream)
-                evs.append((e0, e1))
-                if mode == "e2e":
-                    stream.synchronize()  # the client waits for the result before it sends the next batch
-            stream.synchronize()
-            dist.barrier()
-            t = torch.tensor([sum(a.elapsed_time(b) for a, b in evs)], device=dev, dtype=torch.float64)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            results[mode] = float(t.item())
+        for i in range(warm):
+            one_step(i)
+        stream.synchronize()
+        dist.barrier()
+        sampler.start()
+        evs = []
+        for i in range(args.steps):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            one_step(i)
+            e1.record(stream)
+            evs.append((e0, e1))
+        stream.synchronize()
+        dist.barrier()
+        t = torch.tensor([sum(a.elapsed_time(b) for a, b in evs)], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        results["device"] = float(t.item())
+    # ---- end to end: closed-loop clients -> RPC front end on rank 0 -> control broadcast -> TP graph on every rank
+    from splitrpc_b200.serving.tp_server import TensorParallelServer
+
+    srv = TensorParallelServer(model, outstanding=2 * B)
+    n_req, n_warm = B * args.steps, B * warm
+    stats = torch.zeros(4, dtype=torch.float64, device=dev)
+    if rank == 0:
+        with srv:
+            cli = srv.client(total=n_req + n_warm, warmup=n_warm, payload="ids", n_payloads=2 * B, send_by_reference=True)
+            ok = cli.run_closed_loop(2 * B)
+            st = cli.post_process()
+        if ok:
+            stats[0], stats[1], stats[2] = st.get("throughput_est", 0.0), st.get("p50_sojournTime_us", 0.0), st.get("p99_sojournTime_us", 0.0)
+        stats[3] = srv.served_batches
+    else:
+        srv.serve_forever()
+    dist.barrier()
+    dist.broadcast(stats, src=0)
+    e2e_rps, e2e_p50, e2e_p99, e2e_batches = (float(v) for v in stats)
     clocks = sampler.stop()
     ops.check_status()
     value = B * args.steps / (results["device"] / 1e3)
-    e2e = B * args.steps / (results["e2e"] / 1e3)
     res = {
         "metric": "req/s (tensor-parallel batch serving, device-timed, max over ranks)", "value": round(value, 1),
         "unit": "req/s", "n_gpus": world, "steps": args.steps, "warmup": warm, "ms_per_step": round(results["device"] / args.steps, 4),
@@ -356,9 +365,12 @@ def run_tp(args, rank: int, world: int, local_rank: int) -> dict:
                    "step": "one batch of 16 sequences through the tensor-parallel CUDA graph on all ranks",
                    "l2": "256 MiB buffer written between timed iterations", "weights": "random init"},
         "clocks": clocks,
-        "e2e": {"value": round(e2e, 1), "unit": "req/s", "h2d_bytes_per_step": B * S * 4, "d2h_bytes_per_step": B * 2 * 4,
-                "path": "pinned host ids -> cudaMemcpyAsync -> TP graph on every rank -> probabilities copied back to pinned host",
-                "note": "the batch is handed to the model API directly; the RPC front end serves tensor-parallel groups on rank 0 only"},
+        "e2e": {"value": round(e2e_rps, 1), "unit": "req/s", "h2d_bytes_per_step": B * S * 4, "d2h_bytes_per_step": B * 16,
+                "p50_us": round(e2e_p50, 1), "p99_us": round(e2e_p99, 1),
+                "mean_batch": round((n_req + n_warm) / max(1.0, e2e_batches), 2), "outstanding": 2 * B,
+                "path": "loadgen (ids in pinned host memory, sent by reference) -> loopback NIC -> native server on rank 0 "
+                        "(reassembly, dynamic batching, SG kernel pulls the ids over PCIe) -> control broadcast to the "
+                        "peers -> TP graph on every rank -> probabilities to the pinned transmit arena -> client"},
         "gpu_launches": model.kernels_per_forward * args.steps,
     }
     dist.barrier()

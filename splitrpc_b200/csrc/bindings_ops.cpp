@@ -56,6 +56,11 @@ void bind_ops(py::module_& m) {
   m.def("memset_async", [](uintptr_t dst, int value, size_t n, uintptr_t stream) {
     check(cudaMemsetAsync((void*)dst, value, n, (cudaStream_t)stream), "memset_async");
   });
+  m.def("memcpy2d_async", [](uintptr_t dst, size_t dpitch, uintptr_t src, size_t spitch, size_t width, size_t height,
+                             uintptr_t stream) {
+    check(cudaMemcpy2DAsync((void*)dst, dpitch, (const void*)src, spitch, width, height, cudaMemcpyDefault, (cudaStream_t)stream),
+          "memcpy2d_async");
+  });
   m.def("memcpy_async", [](uintptr_t dst, uintptr_t src, size_t n, uintptr_t stream) {
     check(cudaMemcpyAsync((void*)dst, (const void*)src, n, cudaMemcpyDefault, (cudaStream_t)stream), "memcpy_async");
   });

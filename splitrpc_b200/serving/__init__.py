@@ -7,6 +7,14 @@ from .. import _C
 from .engine import ModelServer  # noqa: F401
 
 
+def __getattr__(name):
+    if name == "TensorParallelServer":  # needs torch.distributed; imported on first use
+        from .tp_server import TensorParallelServer
+
+        return TensorParallelServer
+    raise AttributeError(name)
+
+
 def lenet5_random_weights(seed: int = 0) -> list[np.ndarray]:
     """Random-init LeNet-5 parameters in the order the native apps expect."""
     rng = np.random.default_rng(seed)

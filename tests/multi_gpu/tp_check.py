@@ -64,6 +64,37 @@ def check_bert_tp(rank, world, dev):
     dist.barrier()
 
 
+def check_tp_server(rank, world, dev):
+    """Requests through the RPC front end of rank 0, every rank stepping the tensor-parallel graph; responses against
+    a single-GPU evaluation of the same weights on the same token ids."""
+    import numpy as np
+
+    from splitrpc_b200.serving.tp_server import TensorParallelServer
+
+    cfg = BertConfig(layers=2, hidden=512, heads=8, ffn=2048)
+    B, S = 2 * world, 128
+    tp_model = BertClassifierTP(cfg, seq=S, device=dev.index, batch=B, seed=5, n_copy=4)
+    srv = TensorParallelServer(tp_model, outstanding=2 * B)
+    if rank == 0:
+        total = 6 * B + 1  # the last batch is a short one
+        with srv:
+            cli = srv.client(total=total, warmup=0, payload="ids", n_payloads=4, verify=True)  # verify keeps the responses
+            assert cli.run_closed_loop(2 * B), "closed loop did not finish"
+            assert cli.received == total
+        ref_model = BertClassifier(cfg, seq=S, device=dev.index, max_batch=B, seed=5)
+        for k in (0, 3, total - 1):
+            ids = torch.from_numpy(np.frombuffer(cli.payload(k % 4), dtype=np.int32).copy()).view(1, S).to(dev)
+            out = torch.zeros(1, 2, device=dev)
+            ref_model.forward(1, ids=ids, out=out)
+            torch.cuda.synchronize()
+            got = torch.from_numpy(np.frombuffer(cli.response(k), dtype=np.float32).copy())[:2]
+            torch.testing.assert_close(got, out[0].cpu(), rtol=5e-2, atol=5e-2)
+    else:
+        assert srv.serve_forever() >= 6
+    ops.check_status()
+    dist.barrier()
+
+
 def check_cross_gpu_sg(rank, world, dev):
     """Rank k pulls 8 KB fragments out of rank 0's arena into its own buffer and pushes an echo back into rank 0."""
     frag, n_frag = 8192, 64
@@ -90,6 +121,7 @@ def main():
     check_cross_gpu_sg(rank, world, dev)
     check_fused_linear(rank, world, dev)
     check_bert_tp(rank, world, dev)
+    check_tp_server(rank, world, dev)
     torch.cuda.synchronize()
     dist.barrier()
     if rank == 0:
