@@ -45,7 +45,11 @@ struct AttSmem {
   static_assert(!ALIAS || P_BYTES <= Q_BYTES + K_BYTES, "P must fit over Q and K");
 };
 
-template <int SEQ>
+// VMN = true: V is read in place from the fused Q|K|V projection ([tokens, 3*hidden], V in the last third).  A V tile
+// is then [keys, 64] with the head dimension contiguous, i.e. an MN-major B operand of the second product: same
+// 128-byte-swizzled shared-memory tile and descriptor, "B is MN-major" in the instruction descriptor, and a step of 16
+// keys along K is 2048 bytes (two 8-row groups) instead of 32.  No transposed copy of V and no separate V GEMM.
+template <int SEQ, bool VMN>
 __global__ void __launch_bounds__(ATT_THREADS)
 attention_tc(const __grid_constant__ CUtensorMap tmap_qk, const __grid_constant__ CUtensorMap tmap_vt,
              __nv_bfloat16* __restrict__ out, int ld_out, const float* __restrict__ v_bias, int hidden, float scale_log2e,
@@ -93,10 +97,15 @@ attention_tc(const __grid_constant__ CUtensorMap tmap_qk, const __grid_constant_
       ptx::mbar_expect_tx(&bar_kv, L::K_BYTES + L::VT_BYTES);
       for (int nb = 0; nb < SEQ / 128; nb++)
         ptx::tma_load_2d(sK + nb * 128 * 128, &tmap_qk, &bar_kv, hidden + head * HD, tok0 + nb * 128);
-      for (int a = 0; a < SEQ / 64; a++) ptx::tma_load_2d(sVT + a * 64 * 128, &tmap_vt, &bar_kv, tok0 + a * 64, head * HD);
+      if constexpr (VMN) {
+        for (int nb = 0; nb < SEQ / 128; nb++)
+          ptx::tma_load_2d(sVT + nb * 128 * 128, &tmap_qk, &bar_kv, 2 * hidden + head * HD, tok0 + nb * 128);
+      } else {
+        for (int a = 0; a < SEQ / 64; a++) ptx::tma_load_2d(sVT + a * 64 * 128, &tmap_vt, &bar_kv, tok0 + a * 64, head * HD);
+      }
       bool ok = ptx::mbar_wait(&bar_kv, 0);
       const uint32_t idesc_s = ptx::umma_idesc_bf16(QT, 128);
-      const uint32_t idesc_o = ptx::umma_idesc_bf16(QT, HD);
+      const uint32_t idesc_o = ptx::umma_idesc_bf16(QT, HD) | (VMN ? (1u << 16) : 0u);  // bit 16: B is MN-major
       for (int qt = 0; qt < NQT && ok; qt++) {
         const uint32_t ph = (uint32_t)qt & 1u;
         // Q tile (the previous tile's score MMAs have completed: bar_s was awaited by the softmax warps and
@@ -118,8 +127,9 @@ attention_tc(const __grid_constant__ CUtensorMap tmap_qk, const __grid_constant_
         const uint32_t p_addr = ptx::smem_u32(sP), vt_addr = ptx::smem_u32(sVT);
         for (int kk = 0; kk < SEQ / 16; kk++) {
           const int atom = kk >> 2, sub = kk & 3;
-          ptx::umma_bf16(tmem_o, ptx::umma_desc_sw128(p_addr + atom * QT * 128 + sub * 32),
-                         ptx::umma_desc_sw128(vt_addr + atom * 64 * 128 + sub * 32), idesc_o, kk != 0 ? 1u : 0u);
+          const uint32_t v_desc_addr = VMN ? vt_addr + kk * 2048 : vt_addr + atom * 64 * 128 + sub * 32;
+          ptx::umma_bf16(tmem_o, ptx::umma_desc_sw128(p_addr + atom * QT * 128 + sub * 32), ptx::umma_desc_sw128(v_desc_addr),
+                         idesc_o, kk != 0 ? 1u : 0u);
         }
         ptx::umma_commit(&bar_o);
       }
@@ -232,18 +242,18 @@ cudaError_t encode(CUtensorMap* m, const void* ptr, uint64_t inner, uint64_t out
   return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
 }
 
-template <int SEQ>
+template <int SEQ, bool VMN>
 cudaError_t launch(const CUtensorMap& tqk, const CUtensorMap& tvt, void* out, int ld_out, const float* v_bias, int hidden,
                    int batch, int heads, uint32_t* status, cudaStream_t s) {
   static bool attr = false;
   const int smem = AttSmem<SEQ>::TOTAL + 1024;
   if (!attr) {
-    cudaError_t e = cudaFuncSetAttribute(attention_tc<SEQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaError_t e = cudaFuncSetAttribute(attention_tc<SEQ, VMN>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
     attr = true;
   }
   const float scale_log2e = 0.125f * 1.4426950408889634f;
-  attention_tc<SEQ><<<dim3(heads, batch), ATT_THREADS, smem, s>>>(tqk, tvt, (__nv_bfloat16*)out, ld_out, v_bias, hidden,
+  attention_tc<SEQ, VMN><<<dim3(heads, batch), ATT_THREADS, smem, s>>>(tqk, tvt, (__nv_bfloat16*)out, ld_out, v_bias, hidden,
                                                                   scale_log2e, status);
   return cudaGetLastError();
 }
@@ -254,14 +264,21 @@ cudaError_t nn_attention_tc(const void* qk, int ld_qk, const void* vt, int ld_vt
                             int batch, int seq, int heads, uint32_t* status, cudaStream_t s) {
   const int hidden = heads * HD;
   const int tokens = batch * seq;
-  if ((ld_qk % 8) || (ld_vt % 8) || (ld_out % 8) || ((uintptr_t)qk & 15) || ((uintptr_t)vt & 15) || ((uintptr_t)out & 15))
-    return cudaErrorInvalidValue;
+  if ((ld_qk % 8) || (ld_out % 8) || ((uintptr_t)qk & 15) || ((uintptr_t)out & 15)) return cudaErrorInvalidValue;
   CUtensorMap tqk, tvt;
+  if (!vt) {  // V in place: qk is the [tokens, 3*hidden] output of the fused Q|K|V projection
+    cudaError_t e = encode(&tqk, qk, (uint64_t)3 * hidden, (uint64_t)tokens, (uint64_t)ld_qk * 2, 64, 128);
+    if (e != cudaSuccess) return e;
+    if (seq == 128) return launch<128, true>(tqk, tqk, out, ld_out, v_bias, hidden, batch, heads, status, s);
+    if (seq == 384) return launch<384, true>(tqk, tqk, out, ld_out, v_bias, hidden, batch, heads, status, s);
+    return cudaErrorInvalidValue;
+  }
+  if ((ld_vt % 8) || ((uintptr_t)vt & 15)) return cudaErrorInvalidValue;
   cudaError_t e = encode(&tqk, qk, (uint64_t)2 * hidden, (uint64_t)tokens, (uint64_t)ld_qk * 2, 64, 128);
   if (e != cudaSuccess) return e;
   e = encode(&tvt, vt, (uint64_t)tokens, (uint64_t)hidden, (uint64_t)ld_vt * 2, 64, 64);
   if (e != cudaSuccess) return e;
-  if (seq == 128) return launch<128>(tqk, tvt, out, ld_out, v_bias, hidden, batch, heads, status, s);
-  if (seq == 384) return launch<384>(tqk, tvt, out, ld_out, v_bias, hidden, batch, heads, status, s);
+  if (seq == 128) return launch<128, false>(tqk, tvt, out, ld_out, v_bias, hidden, batch, heads, status, s);
+  if (seq == 384) return launch<384, false>(tqk, tvt, out, ld_out, v_bias, hidden, batch, heads, status, s);
   return cudaErrorInvalidValue;
 }

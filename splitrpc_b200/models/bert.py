@@ -71,13 +71,12 @@ class BertClassifier:
         T = max_batch * seq
         self.buf = {
             "x": torch.empty((T, H), dtype=bf, device=dev), "qkv": torch.empty((T, 3 * H), dtype=bf, device=dev),
-            "vt": torch.empty((H, T), dtype=bf, device=dev),
             "ctx": torch.empty((T, H), dtype=bf, device=dev), "attn": torch.empty((T, H), dtype=bf, device=dev),
             "x1": torch.empty((T, H), dtype=bf, device=dev), "ffn": torch.empty((T, F), dtype=bf, device=dev),
             "y": torch.empty((T, H), dtype=bf, device=dev), "pooled": torch.empty((max_batch, H), dtype=bf, device=dev),
             "logits": torch.empty((max_batch, 8), dtype=torch.float32, device=dev),
         }
-        self.kernels_per_forward = 1 + (8 if attention == "tensor_core" else 7) * cfg.layers + 3
+        self.kernels_per_forward = 1 + 7 * cfg.layers + 3
 
     def forward(self, batch: int, ids: torch.Tensor | None = None, d_stub: int = 0, out: torch.Tensor | None = None,
                 flag_ptr: int = 0, flag_value: int = 0, counter: torch.Tensor | None = None) -> torch.Tensor:
@@ -89,13 +88,9 @@ class BertClassifier:
         for l in range(cfg.layers):
             q = f"l{l}."
             if self.attention == "tensor_core":
-                H = cfg.hidden
-                # Q|K projection, then V^T = Wv . x^T with swapped operands (already K-major for P.V); the V bias
-                # is added to the attention output.
-                ops.gemm(x, p[q + "qkv.w"][: 2 * H], bias=p[q + "qkv.b"][: 2 * H], out=qkv[:, : 2 * H])
-                vt = b["vt"][:, :T] if T == b["vt"].shape[1] else b["vt"].view(-1)[: H * T].view(H, T)
-                ops.gemm(p[q + "qkv.w"][2 * H:], x, out=vt)
-                ops.attention_tc(qkv[:, : 2 * H], vt, batch, S, cfg.heads, v_bias=p[q + "qkv.b"][2 * H:], out=ctx)
+                # one fused Q|K|V projection; the attention kernel reads V in place (MN-major operand of P.V)
+                ops.gemm(x, p[q + "qkv.w"], bias=p[q + "qkv.b"], out=qkv)
+                ops.attention_tc_qkv(qkv, batch, S, cfg.heads, out=ctx)
             else:
                 ops.gemm(x, p[q + "qkv.w"], bias=p[q + "qkv.b"], out=qkv)
                 ops.attention_d64(qkv, batch, S, cfg.heads, out=ctx)

@@ -41,10 +41,9 @@ class BertClassifierTP:
         for l in range(cfg.layers):
             q = f"l{l}."
             w, bq = fp[q + "qkv.w"], fp[q + "qkv.b"]
-            p[q + "qk.w"] = torch.cat([w[:H][sl], w[H:2 * H][sl]]).contiguous()
-            p[q + "qk.b"] = torch.cat([bq[:H][sl], bq[H:2 * H][sl]]).contiguous()
-            p[q + "v.w"] = w[2 * H:][sl].contiguous()
-            p[q + "v.b"] = bq[2 * H:][sl].contiguous()
+            # this rank's heads of Q, K and V as one [3*Hl, H] projection (Q | K | V thirds)
+            p[q + "qkv.w"] = torch.cat([w[:H][sl], w[H:2 * H][sl], w[2 * H:][sl]]).contiguous()
+            p[q + "qkv.b"] = torch.cat([bq[:H][sl], bq[H:2 * H][sl], bq[2 * H:][sl]]).contiguous()
             p[q + "o.w"] = fp[q + "o.w"][:, sl].contiguous()
             p[q + "o.b"] = fp[q + "o.b"]
             p[q + "f1.w"] = fp[q + "f1.w"][r * Fl:(r + 1) * Fl].contiguous()
@@ -59,11 +58,11 @@ class BertClassifierTP:
         self.T = T
         self.tpc = TensorParallel(T, H, self.device, n_copy=n_copy, group=group)
         bf, dev = torch.bfloat16, self.device
-        self.buf = {"qk": torch.empty((T, 2 * Hl), dtype=bf, device=dev), "vt": torch.empty((Hl, T), dtype=bf, device=dev),
+        self.buf = {"qkv": torch.empty((T, 3 * Hl), dtype=bf, device=dev),
                     "ctx": torch.empty((T, Hl), dtype=bf, device=dev), "ffn": torch.empty((T, Fl), dtype=bf, device=dev),
                     "pooled": torch.empty((batch, H), dtype=bf, device=dev),
                     "logits": torch.empty((batch, 8), dtype=torch.float32, device=dev)}
-        self.kernels_per_forward = 3 + 8 * cfg.layers + 5
+        self.kernels_per_forward = 3 + 7 * cfg.layers + 5
 
     def forward(self, ids: torch.Tensor, out: torch.Tensor | None = None, d_stub: int = 0) -> torch.Tensor:
         """``ids``: int32 ``[batch, seq]`` (identical on every rank).  Returns fp32 logits ``[batch, num_labels]``."""
@@ -77,9 +76,8 @@ class BertClassifierTP:
         for l in range(cfg.layers):
             q = f"l{l}."
             e = l + 1
-            t.ag_gemm("A", p[q + "qk.w"], e, bias=p[q + "qk.b"], out=b["qk"])
-            ops.gemm(p[q + "v.w"], t.gathered["A"], out=b["vt"])  # V^T from the gathered activations
-            ops.attention_tc(b["qk"], b["vt"], B, S, self.heads_local, v_bias=p[q + "v.b"], out=b["ctx"])
+            t.ag_gemm("A", p[q + "qkv.w"], e, bias=p[q + "qkv.b"], out=b["qkv"])
+            ops.attention_tc_qkv(b["qkv"], B, S, self.heads_local, out=b["ctx"])  # V in place, no transposed copy
             t.gemm_rs(b["ctx"], p[q + "o.w"], "RS1", e)
             t.ln_reduce("RS1", e, p[q + "o.b"], t.shard("A"), p[q + "ln1.g"], p[q + "ln1.b"], out=t.shard("B"), signal=("B", e))
             t.ag_gemm("B", p[q + "f1.w"], e, bias=p[q + "f1.b"], act="gelu", out=b["ffn"])

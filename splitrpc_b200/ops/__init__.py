@@ -223,6 +223,19 @@ def attention_d64(qkv: torch.Tensor, batch: int, seq: int, heads: int, out: torc
     return out
 
 
+def attention_tc_qkv(qkv: torch.Tensor, batch: int, seq: int, heads: int, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Tensor-core attention (head dim 64, all-ones mask) straight from the fused projection ``[tokens, 3*hidden]``
+    (Q | K | V, biases included): V is used in place as an MN-major operand, no transposed copy.  Returns
+    ``[tokens, hidden]`` bf16."""
+    hidden = heads * 64
+    assert qkv.dtype == torch.bfloat16 and qkv.stride(1) == 1 and qkv.shape == (batch * seq, 3 * hidden)
+    if out is None:
+        out = torch.empty((batch * seq, hidden), dtype=torch.bfloat16, device=qkv.device)
+    _C.attention_tc(qkv.data_ptr(), qkv.stride(0), 0, 0, out.data_ptr(), out.stride(0), 0, batch, seq, heads,
+                    status_word().data_ptr(), _stream())
+    return out
+
+
 def attention_tc(qk: torch.Tensor, vt: torch.Tensor, batch: int, seq: int, heads: int, v_bias: torch.Tensor | None = None,
                  out: torch.Tensor | None = None) -> torch.Tensor:
     """Tensor-core attention (head dim 64, all-ones mask).

@@ -89,6 +89,22 @@ def test_attention_matches_pytorch(torch_cuda, seq, heads):
 
 
 @pytest.mark.parametrize("seq,heads", [(128, 12), (384, 16)])
+def test_tensor_core_attention_with_v_in_place(torch_cuda, seq, heads):
+    """V read in place from the fused Q|K|V buffer (MN-major operand of the second product)."""
+    torch = torch_cuda
+    from splitrpc_b200 import ops
+
+    B, H = 3, heads * 64
+    qkv = (torch.randn(B * seq, 3 * H, device="cuda") * 0.6).bfloat16()
+    out = ops.attention_tc_qkv(qkv, B, seq, heads)
+    torch.cuda.synchronize()
+    ops.check_status()
+    q, k, v = (t.float().view(B, seq, heads, 64).transpose(1, 2) for t in qkv.split(H, dim=1))
+    ref = (torch.softmax(q @ k.transpose(-1, -2) / 8.0, -1) @ v).transpose(1, 2).reshape(B * seq, H)
+    torch.testing.assert_close(out.float(), ref, rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("seq,heads", [(128, 12), (384, 16)])
 def test_tensor_core_attention_matches_pytorch(torch_cuda, seq, heads):
     torch = torch_cuda
     from splitrpc_b200 import ops
