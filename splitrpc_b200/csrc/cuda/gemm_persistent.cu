@@ -58,6 +58,22 @@ struct Threads {
   static constexpr int TOTAL = 64 + EPI + 32;  // + the store warp
 };
 
+// Division by a launch-time constant as multiply-high + shift (dividends below 2^24): every thread of every role
+// decodes a tile index per tile, and with small tiles the hardware divisions were a quarter of a microsecond per tile.
+struct FastDiv {
+  uint32_t mul, shr, d;
+};
+static inline FastDiv make_fastdiv(uint32_t d) {
+  FastDiv f;
+  f.d = d ? d : 1;
+  uint32_t l = 0;
+  while ((1u << l) < f.d) l++;
+  f.shr = l;
+  f.mul = (uint32_t)((((uint64_t)1 << 32) * (((uint64_t)1 << l) - f.d)) / f.d + 1);
+  return f;
+}
+__device__ __forceinline__ uint32_t fdiv(const FastDiv& f, uint32_t n) { return (__umulhi(f.mul, n) + n) >> f.shr; }
+
 struct TileParams {
   int mode;          // 0 GEMM, 1 convolution
   int M, N, K;       // GEMM view (M = rows, N = columns)
@@ -85,6 +101,7 @@ struct TileParams {
   // short-tile k loop) for a 3 x 3 filter.  num_kb then counts load groups (s * cblocks); panel_kb counts all k-blocks.
   int reuse;
   int panel_kb;
+  FastDiv fd_tiles_n, fd_group, fd_tiles_w, fd_tiles_h;  // filled in by launch()
   // Input that lives in a request ring (convolution mode): the tensor map covers the whole ring, one "image" per slot,
   // and the batch starts at the slot that the app stub's request pointer names when the kernel runs, so one captured
   // graph serves every ring position.  in_stub == nullptr: the input starts at image 0.
@@ -141,8 +158,9 @@ struct TileCoord {
 __device__ __forceinline__ bool get_tile(const TileParams& p, int j, TileCoord* out) {
   TileCoord t;
   if (p.b_stationary) {
-    t.n_idx = (int)blockIdx.x % p.tiles_n;
-    t.m_idx = (int)blockIdx.x / p.tiles_n + j * p.ctas_per_n;
+    const uint32_t q = fdiv(p.fd_tiles_n, blockIdx.x);
+    t.n_idx = (int)(blockIdx.x - q * (uint32_t)p.tiles_n);
+    t.m_idx = (int)q + j * p.ctas_per_n;
     if (t.m_idx >= p.tiles_m) return false;
   } else {
     const int tile = (int)blockIdx.x + j * (int)gridDim.x;
@@ -151,18 +169,23 @@ __device__ __forceinline__ bool get_tile(const TileParams& p, int j, TileCoord* 
     // B blocks they share are read from DRAM once and then hit in L2.
     constexpr int GROUP_M = 8;
     const int per_group = GROUP_M * p.tiles_n;
-    const int g = tile / per_group, in_g = tile - g * per_group;
+    const int g = (int)fdiv(p.fd_group, (uint32_t)tile), in_g = tile - g * per_group;
     const int m_first = g * GROUP_M;
     const int gm = (p.tiles_m - m_first) < GROUP_M ? (p.tiles_m - m_first) : GROUP_M;
-    t.m_idx = m_first + in_g % gm;
-    t.n_idx = in_g / gm;
+    if (gm == GROUP_M) {
+      t.m_idx = m_first + (in_g & (GROUP_M - 1));
+      t.n_idx = in_g >> 3;
+    } else {  // last, shorter group
+      t.m_idx = m_first + in_g % gm;
+      t.n_idx = in_g / gm;
+    }
   }
   t.w0 = t.h0 = t.img0 = 0;
   if (p.mode == 1) {
-    int tw = t.m_idx % p.tiles_w;
-    int rest = t.m_idx / p.tiles_w;
-    int th = rest % p.tiles_h;
-    int ti = rest / p.tiles_h;
+    const int rest = (int)fdiv(p.fd_tiles_w, (uint32_t)t.m_idx);
+    const int tw = t.m_idx - rest * p.tiles_w;
+    const int ti = (int)fdiv(p.fd_tiles_h, (uint32_t)rest);
+    const int th = rest - ti * p.tiles_h;
     t.w0 = tw * p.pw;
     t.h0 = th * p.ph;
     t.img0 = ti * p.pn;
@@ -396,6 +419,14 @@ gemm_conv_persistent(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     const bool vec_res = !res_tma && ep.residual && ((ep.ldr & 7) == 0) && (((uintptr_t)ep.residual & 15) == 0);
     uint32_t local = 0;
     TileCoord tc;
+    // Position of this thread's row inside a convolution patch (the same for every tile).
+    int pw_i = 0, ph_i = 0, pn_i = 0;
+    if (p.mode == 1) {
+      const int rest = row / p.pw;
+      pw_i = row - rest * p.pw;
+      pn_i = rest / p.ph;
+      ph_i = rest - pn_i * p.ph;
+    }
     for (int j = 0; get_tile(p, j, &tc); j++, local++) {
       const uint32_t acc = local & (ACC - 1);
       // Where this thread's row lives in the output.
@@ -406,8 +437,6 @@ gemm_conv_persistent(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         row_ok = m < p.M;
         row_off = (size_t)m;
       } else {
-        const int pw_i = row % p.pw, rest = row / p.pw;
-        const int ph_i = rest % p.ph, pn_i = rest / p.ph;
         const int x = tc.w0 + pw_i, y = tc.h0 + ph_i, img = tc.img0 + pn_i;
         row_ok = row < p.rows_used && x < p.ow && y < p.oh && img < p.nimg;
         row_off = ((size_t)img * p.oh + y) * p.ow + x;
@@ -728,6 +757,10 @@ cudaError_t launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorM
   int grid = std::min(tiles, num_sms());
   p.b_stationary = 0;
   p.ctas_per_n = 0;
+  p.fd_tiles_n = make_fastdiv((uint32_t)p.tiles_n);
+  p.fd_group = make_fastdiv((uint32_t)(8 * p.tiles_n));  // GROUP_M row blocks x all column blocks (see get_tile)
+  p.fd_tiles_w = make_fastdiv((uint32_t)(p.tiles_w > 0 ? p.tiles_w : 1));
+  p.fd_tiles_h = make_fastdiv((uint32_t)(p.tiles_h > 0 ? p.tiles_h : 1));
   static const int allow_bs = [] { const char* e = getenv("SPLITRPC_GEMM_BSTAT"); return e ? atoi(e) : 1; }();
   // The panel may take the ring's memory as long as three A stages remain (a 3x3 convolution over 64 channels keeps its
   // nine 8 KB filter taps resident: otherwise every CTA re-reads the same few L2 lines for every tile).
