@@ -100,7 +100,8 @@ void bind_ops(py::module_& m) {
   m.def("conv_bf16",
         [](uintptr_t in, uintptr_t w, int n, int h, int wd, int cin, int cout, int r, int s, int stride, int pad,
            uintptr_t out, uintptr_t bias, uintptr_t residual, int act, uintptr_t status, uintptr_t stream, int impl,
-           long pix_stride, long row_stride, long img_stride, uintptr_t in_stub, long ring_slots, unsigned int slot_bytes) {
+           long pix_stride, long row_stride, long img_stride, uintptr_t in_stub, long ring_slots, unsigned int slot_bytes,
+           uintptr_t in2, int h2, int w2, int cin2, int stride2) {
           ConvShape cs{n, h, wd, cin, cout, r, s, stride, pad, (h + 2 * pad - r) / stride + 1, (wd + 2 * pad - s) / stride + 1};
           cs.in_pix_stride = pix_stride;
           cs.in_row_stride = row_stride;
@@ -108,6 +109,12 @@ void bind_ops(py::module_& m) {
           cs.in_stub = (const void*)in_stub;
           cs.in_ring_slots = ring_slots;
           cs.in_slot_bytes = slot_bytes;
+          cs.in2 = (const void*)in2;
+          cs.h2 = h2;
+          cs.w2 = w2;
+          cs.cin2 = cin2;
+          cs.stride2 = stride2;
+          if (in2 && impl == 1) throw std::invalid_argument("conv_bf16: a second input needs the TMA implementation");
           if ((pix_stride || row_stride || img_stride) && impl == 1)
             throw std::invalid_argument("conv_bf16: input strides need the TMA implementation");
           GemmEpilogue ep = make_ep(out, cout, false, bias, residual, cout, act);
@@ -118,7 +125,8 @@ void bind_ops(py::module_& m) {
         py::arg("r"), py::arg("s"), py::arg("stride"), py::arg("pad"), py::arg("out"), py::arg("bias") = 0,
         py::arg("residual") = 0, py::arg("act") = 0, py::arg("status") = 0, py::arg("stream") = 0, py::arg("impl") = 2,
         py::arg("pix_stride") = 0, py::arg("row_stride") = 0, py::arg("img_stride") = 0, py::arg("in_stub") = 0,
-        py::arg("ring_slots") = 0, py::arg("slot_bytes") = 0);
+        py::arg("ring_slots") = 0, py::arg("slot_bytes") = 0, py::arg("in2") = 0, py::arg("h2") = 0, py::arg("w2") = 0,
+        py::arg("cin2") = 0, py::arg("stride2") = 1);
 
   m.def("gemm_reserve_sms", [](int n) { srpc_gemm_reserve_sms(n); }, py::arg("n"));
   m.def("gemm_grid_sms", []() { return srpc_gemm_grid_sms(); });

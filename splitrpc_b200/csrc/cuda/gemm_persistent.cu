@@ -108,6 +108,8 @@ struct TileParams {
   const void* in_stub;
   unsigned long long in_ring_base;
   unsigned int in_slot_bytes;
+  // two-input 1x1 convolution: k-blocks from kb_split on come from the second input (pixel stride2, no padding)
+  int kb_split, stride2;
 };
 
 __device__ __forceinline__ float gelu_f(float x) { return ptx::gelu_erf_fast(x); }
@@ -304,10 +306,16 @@ gemm_conv_persistent(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
                                tc.n_idx * BN);
         } else {
           ptx::mbar_expect_tx(&full_bar[pr_s], p.a_box_bytes + b_tx);
-          const int tap = pr_kb / p.cblocks, cb = pr_kb - tap * p.cblocks;
-          const int fr = tap / p.s, fs = tap - fr * p.s;
-          tma_load_4d_box(sa, &tmap_a, &full_bar[pr_s], cb * BK, tc.w0 * p.stride + fs - p.pad,
-                          tc.h0 * p.stride + fr - p.pad, tc.img0 + img_off);
+          if (pr_kb >= p.kb_split) {
+            // second input of a two-input 1x1 convolution (its map travels in the residual map's place)
+            tma_load_4d_box(sa, &tmap_res, &full_bar[pr_s], (pr_kb - p.kb_split) * BK, tc.w0 * p.stride2, tc.h0 * p.stride2,
+                            tc.img0);
+          } else {
+            const int tap = pr_kb / p.cblocks, cb = pr_kb - tap * p.cblocks;
+            const int fr = tap / p.s, fs = tap - fr * p.s;
+            tma_load_4d_box(sa, &tmap_a, &full_bar[pr_s], cb * BK, tc.w0 * p.stride + fs - p.pad,
+                            tc.h0 * p.stride + fr - p.pad, tc.img0 + img_off);
+          }
         }
         if (!p.b_stationary && !p.reuse) ptx::tma_load_2d(sa + A_BYTES, &tmap_b, &full_bar[pr_s], pr_kb * BK, tc.n_idx * BN);
         if (pr_j == 0 && pr_kb == 0) GEMM_TRACE(2);
@@ -947,6 +955,17 @@ cudaError_t srpc_conv_bf16_tma(const void* in, const void* weight, const ConvSha
   p.s = cs.s;
   p.cblocks = cs.cin / BK;
   p.num_kb = cs.r * cs.s * p.cblocks;
+  p.kb_split = p.num_kb;
+  p.stride2 = 1;
+  if (cs.in2) {
+    // out = act(W1 . in + W2 . in2(strided) + bias): the weight rows hold [W1 | W2]
+    if (cs.r != 1 || cs.s != 1 || cs.pad != 0 || cs.in_stub || cs.cin2 % BK || cs.stride2 < 1 || ((uintptr_t)cs.in2 & 15))
+      return cudaErrorInvalidValue;
+    if ((cs.h2 - 1) / cs.stride2 + 1 != cs.oh || (cs.w2 - 1) / cs.stride2 + 1 != cs.ow) return cudaErrorInvalidValue;
+    p.K += cs.cin2;
+    p.num_kb += cs.cin2 / BK;
+    p.stride2 = cs.stride2;
+  }
   p.panel_kb = p.num_kb;
   p.stride = cs.stride;
   p.pad = cs.pad;
@@ -991,6 +1010,16 @@ cudaError_t srpc_conv_bf16_tma(const void* in, const void* weight, const ConvSha
     cudaError_t e = get_map(&ta, in, 4, dims, st, box, es);
     if (e != cudaSuccess) return e;
   }
+  CUtensorMap ta2 = ta;
+  if (cs.in2) {
+    uint64_t dims[4] = {(uint64_t)cs.cin2, (uint64_t)cs.w2, (uint64_t)cs.h2, (uint64_t)cs.n};
+    uint64_t st[3] = {(uint64_t)cs.cin2 * 2, (uint64_t)cs.w2 * cs.cin2 * 2, (uint64_t)cs.h2 * cs.w2 * cs.cin2 * 2};
+    uint32_t box[4] = {BK, (uint32_t)(p.pw * cs.stride2), (uint32_t)(p.ph * cs.stride2), (uint32_t)p.pn};
+    uint32_t es[4] = {1, (uint32_t)cs.stride2, (uint32_t)cs.stride2, 1};
+    if (box[1] > 256 || box[2] > 256) return cudaErrorInvalidValue;
+    cudaError_t e2 = get_map(&ta2, cs.in2, 4, dims, st, box, es);
+    if (e2 != cudaSuccess) return e2;
+  }
   cudaError_t e = map_2d(&tb, weight, (uint64_t)p.K, (uint64_t)cs.cout, (uint64_t)p.K * 2, BK, (uint32_t)bn);
   if (e != cudaSuccess) return e;
   {
@@ -1004,5 +1033,5 @@ cudaError_t srpc_conv_bf16_tma(const void* in, const void* weight, const ConvSha
   GemmEpilogue ep2 = ep;
   ep2.ldo = cs.cout;
   if (ep2.residual) ep2.ldr = cs.cout;
-  return dispatch(bn, ta, tb, to, ta, p, ep2, 1, status, stream);
+  return dispatch(bn, ta, tb, to, ta2, p, ep2, 1, status, stream);
 }

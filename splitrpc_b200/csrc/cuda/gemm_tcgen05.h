@@ -41,6 +41,11 @@ struct ConvShape {
   const void* in_stub = nullptr;
   long in_ring_slots = 0;
   unsigned int in_slot_bytes = 0;
+  // Second input of a two-input 1x1 convolution (TMA path, r = s = 1, pad = 0): dense NHWC [n, h2, w2, cin2] sampled
+  // every stride2 pixels; the filter rows are then [cout][cin + cin2] and out = act(W1 . in + W2 . in2 + bias).  A
+  // bottleneck's last convolution and its projection shortcut become one kernel this way.
+  const void* in2 = nullptr;
+  int h2 = 0, w2 = 0, cin2 = 0, stride2 = 1;
 };
 
 // D[M,N] = A[M,K] . B[N,K]^T, bf16 operands (row strides lda/ldb elements, multiples of 8), fp32 accumulation.

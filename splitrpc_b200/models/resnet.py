@@ -31,9 +31,13 @@ class ResNet50:
     req_size = REQ_BYTES
     resp_size = RESP_BYTES
 
-    def __init__(self, device: int = 0, max_batch: int = 64, seed: int = 0, normalize: bool = False):
+    def __init__(self, device: int = 0, max_batch: int = 64, seed: int = 0, normalize: bool = False,
+                 fuse_shortcut: bool = True):
         self.device = torch.device("cuda", device)
         self.max_batch = max_batch
+        # projection shortcuts computed inside the block's last convolution (one two-input kernel) instead of a kernel
+        # of their own whose output is read back as the residual
+        self.fuse_shortcut = fuse_shortcut
         self.mean = ops.IMAGENET_MEAN if normalize else (0.0, 0.0, 0.0)
         self.inv_std = ops.IMAGENET_INV_STD if normalize else (1.0, 1.0, 1.0)
         g = torch.Generator(device="cpu").manual_seed(seed)
@@ -66,6 +70,11 @@ class ResNet50:
                 ds = bi == 0
                 if ds:
                     conv(name + ".ds", width * 4, cin, 1, gain=0.5)
+                    # last convolution and projection shortcut as one two-input kernel: weights side by side, biases added
+                    pr = self.params
+                    pr[name + ".c3ds.w"] = torch.cat([pr[name + ".c3.w"].view(width * 4, width),
+                                                      pr[name + ".ds.w"].view(width * 4, cin)], dim=1).contiguous()
+                    pr[name + ".c3ds.b"] = pr[name + ".c3.b"] + pr[name + ".ds.b"]
                 self.blocks.append((name, cin, width, s, ds))
                 cin = width * 4
         self.params["fc.w"] = (torch.randn((1000, 2048), generator=g) * math.sqrt(1.0 / 2048)).to(self.device, torch.bfloat16)
@@ -88,10 +97,11 @@ class ResNet50:
             self.buf[name + ".t1"] = torch.empty((nb, h, h, width), dtype=bf, device=dev)
             self.buf[name + ".t2"] = torch.empty((nb, ho, ho, width), dtype=bf, device=dev)
             self.buf[name + ".out"] = torch.empty((nb, ho, ho, width * 4), dtype=bf, device=dev)
-            if ds:
+            if ds and not self.fuse_shortcut:
                 self.buf[name + ".ds"] = torch.empty((nb, ho, ho, width * 4), dtype=bf, device=dev)
             h = ho
-        self.kernels_per_forward = self._kernels_per_forward_base = 3 + sum(3 + (1 if b[4] else 0) for b in self.blocks) + 3
+        per_ds = 0 if self.fuse_shortcut else 1
+        self.kernels_per_forward = self._kernels_per_forward_base = 3 + sum(3 + (per_ds if b[4] else 0) for b in self.blocks) + 3
         self.ingress_ring = None
 
     # ------------------------------------------------------------------ forward
@@ -134,6 +144,10 @@ class ResNet50:
             t1 = self._conv1x1(cur, name + ".c1", b[name + ".t1"][:nb], "relu")
             t2 = ops.conv2d_nhwc(t1, p[name + ".c2.w"], bias=p[name + ".c2.b"], stride=s, pad=1, act="relu",
                                  out=b[name + ".t2"][:nb])
+            if ds and self.fuse_shortcut:
+                cur = ops.conv1x1_dual(t2, cur, p[name + ".c3ds.w"], bias=p[name + ".c3ds.b"], stride2=s, act="relu",
+                                       out=b[name + ".out"][:nb])
+                continue
             if ds:
                 if s == 1:
                     idn = self._conv1x1(cur, name + ".ds", b[name + ".ds"][:nb], None)

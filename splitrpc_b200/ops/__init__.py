@@ -87,6 +87,25 @@ def conv2d_nhwc(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = No
     return out
 
 
+def conv1x1_dual(x1: torch.Tensor, x2: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, stride2: int = 1,
+                 act: str | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """``act(W1 . x1 + W2 . x2[:, ::stride2, ::stride2] + bias)`` in one kernel: two 1x1 convolutions that share their
+    output pixels (a bottleneck's last convolution and its projection shortcut).  ``w`` is ``[Cout, C1 + C2]``."""
+    assert x1.is_cuda and x1.dtype == x2.dtype == w.dtype == torch.bfloat16
+    assert x1.is_contiguous() and x2.is_contiguous() and w.is_contiguous()
+    n, oh, ow, c1 = x1.shape
+    n2, h2, w2, c2 = x2.shape
+    cout = w.shape[0]
+    assert n == n2 and w.numel() == cout * (c1 + c2) and c1 % 64 == 0 and c2 % 64 == 0 and cout % 8 == 0
+    assert (h2 - 1) // stride2 + 1 == oh and (w2 - 1) // stride2 + 1 == ow
+    if out is None:
+        out = torch.empty((n, oh, ow, cout), dtype=torch.bfloat16, device=x1.device)
+    assert out.is_contiguous() and out.shape == (n, oh, ow, cout)
+    _C.conv_bf16(x1.data_ptr(), w.data_ptr(), n, oh, ow, c1, cout, 1, 1, 1, 0, out.data_ptr(), _ptr(bias), 0, ACT[act],
+                 status_word().data_ptr(), _stream(), 2, in2=x2.data_ptr(), h2=h2, w2=w2, cin2=c2, stride2=stride2)
+    return out
+
+
 def sg_copy(items, impl: int = 0, n_blocks: int = 0) -> None:
     """Runs a copy list ``[(src_addr, dst_addr, nbytes)]`` on the current stream and waits for it."""
     _C.sg_copy(list(items), impl, n_blocks, _stream())

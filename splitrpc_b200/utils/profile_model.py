@@ -44,6 +44,11 @@ def _work(name, args, kwargs, out):
         oh, ow = out.shape[1], out.shape[2]
         by = 2 * (x.numel() + w.numel() + out.numel()) + (2 * out.numel() if kwargs.get("residual") is not None else 0)
         return 2.0 * n * oh * ow * cout * r * s * cin, by, f"{n}x{h}x{wd}x{cin}->{cout} k{r} s{kwargs.get('stride', 1)}"
+    if name == "conv1x1_dual":
+        x1, x2, w = args[0], args[1], args[2]
+        st = kwargs.get("stride2", 1)
+        by = 2 * (x1.numel() + x2.numel() // (st * st) + w.numel() + out.numel())
+        return 2.0 * out.numel() * w.shape[1], by, f"{tuple(x1.shape)}+{tuple(x2.shape)}/s{st}->{w.shape[0]}"
     if name == "stem_s2d":
         batch = args[1]
         return 0.0, batch * (3 * 224 * 224 * 4 + 115 * 115 * 16 * 2), f"b{batch}"
@@ -89,7 +94,7 @@ def main():
 
     records = []
     if not args.no_events:
-        for name in ("gemm", "conv2d_nhwc", "stem_im2col", "stem_s2d", "stem_conv", "maxpool3x3s2", "global_avgpool", "softmax_response", "layernorm",
+        for name in ("gemm", "conv2d_nhwc", "conv1x1_dual", "stem_im2col", "stem_s2d", "stem_conv", "maxpool3x3s2", "global_avgpool", "softmax_response", "layernorm",
                      "bert_embed_ln", "attention_d64"):
             fn = getattr(ops, name)
 

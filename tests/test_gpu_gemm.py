@@ -78,6 +78,23 @@ def test_gelu_epilogue_matches_erf_definition(env):
     assert (out - ref).abs().max().item() < 2e-6
 
 
+@pytest.mark.parametrize("n,oh,c1,h2,c2,cout,stride2", [(2, 56, 64, 56, 64, 256, 1), (3, 28, 128, 56, 256, 512, 2),
+                                                        (2, 14, 256, 28, 512, 1024, 2), (5, 7, 512, 14, 1024, 2048, 2)])
+def test_two_input_pointwise_conv(env, n, oh, c1, h2, c2, cout, stride2):
+    """Last bottleneck convolution + projection shortcut as one kernel vs the two convolutions in fp32."""
+    torch, ops = env
+    x1 = (torch.randn(n, oh, oh, c1, device="cuda") * 0.5).bfloat16()
+    x2 = (torch.randn(n, h2, h2, c2, device="cuda") * 0.5).bfloat16()
+    w1 = (torch.randn(cout, c1, device="cuda") * 0.1).bfloat16()
+    w2 = (torch.randn(cout, c2, device="cuda") * 0.1).bfloat16()
+    bias = torch.randn(cout, device="cuda")
+    out = ops.conv1x1_dual(x1, x2, torch.cat([w1, w2], dim=1).contiguous(), bias=bias, stride2=stride2, act="relu")
+    ops.check_status()
+    ref = x1.float() @ w1.float().t() + x2[:, ::stride2, ::stride2].float() @ w2.float().t() + bias
+    assert out.shape == ref.shape
+    assert _rel_err(torch, out, torch.relu(ref)) < 1e-2
+
+
 @pytest.mark.parametrize("n,h,cin,cout,r,stride,pad", [(2, 56, 64, 64, 3, 1, 1), (4, 28, 128, 128, 3, 1, 1),
                                                        (2, 56, 256, 128, 1, 2, 0), (3, 14, 256, 256, 3, 1, 1),
                                                        (2, 7, 512, 512, 3, 1, 1), (2, 56, 64, 256, 1, 1, 0),
