@@ -242,6 +242,11 @@ void bind_ops(py::module_& m) {
   m.def("global_avgpool", [](uintptr_t in, uintptr_t out, int n, int hw, int c, uintptr_t stream) {
     check(nn_global_avgpool((const void*)in, (void*)out, n, hw, c, (cudaStream_t)stream), "global_avgpool");
   });
+  m.def("fc_skinny", [](uintptr_t a, int lda, uintptr_t w, int ldw, uintptr_t bias, uintptr_t out, int ldo, int M, int N, int K,
+                        uintptr_t stream) {
+    check(nn_fc_skinny((const void*)a, lda, (const void*)w, ldw, (const float*)bias, (float*)out, ldo, M, N, K, (cudaStream_t)stream),
+          "fc_skinny");
+  });
   m.def("softmax_response",
         [](uintptr_t logits, int rows, int n, int ld, uintptr_t d_stub, uintptr_t direct_out, size_t resp_stride,
            bool write_argmax, uintptr_t counter, uintptr_t flag, uint32_t flag_value, uintptr_t stream) {

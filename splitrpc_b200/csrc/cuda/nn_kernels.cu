@@ -116,7 +116,9 @@ __global__ void __launch_bounds__(256) stem_s2d(const g_params* stub, const floa
   }
 }
 
-// 3x3 stride-2 pad-1 max pooling, NHWC bf16, 8 channels per thread.
+// 3x3 stride-2 pad-1 max pooling, NHWC bf16, 8 channels per thread.  Window positions outside the image are clamped
+// to the nearest pixel inside (a duplicate does not change a maximum), so the nine 16-byte loads of a thread carry no
+// branches and are all in flight together.
 __global__ void __launch_bounds__(256) maxpool3x3s2(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out,
                                                     int n, int h, int w, int c) {
   const int oh = (h + 2 - 3) / 2 + 1, ow = (w + 2 - 3) / 2 + 1, cv = c / 8;
@@ -127,45 +129,162 @@ __global__ void __launch_bounds__(256) maxpool3x3s2(const __nv_bfloat16* __restr
     const int ox = (int)(p % ow);
     p /= ow;
     const int oy = (int)(p % oh), b = (int)(p / oh);
-    float m[8];
+    uint4 q[9];
 #pragma unroll
-    for (int j = 0; j < 8; j++) m[j] = -FLT_MAX;
     for (int dy = 0; dy < 3; dy++) {
-      const int iy = oy * 2 - 1 + dy;
-      if (iy < 0 || iy >= h) continue;
-      for (int dx = 0; dx < 3; dx++) {
-        const int ix = ox * 2 - 1 + dx;
-        if (ix < 0 || ix >= w) continue;
-        uint4 q = *reinterpret_cast<const uint4*>(in + (((size_t)b * h + iy) * w + ix) * c + cc * 8);
-        const __nv_bfloat162* hq = reinterpret_cast<const __nv_bfloat162*>(&q);
+      const int iy = min(max(oy * 2 - 1 + dy, 0), h - 1);
 #pragma unroll
-        for (int t = 0; t < 4; t++) {
-          float2 f = __bfloat1622float2(hq[t]);
-          m[2 * t] = fmaxf(m[2 * t], f.x);
-          m[2 * t + 1] = fmaxf(m[2 * t + 1], f.y);
-        }
+      for (int dx = 0; dx < 3; dx++) {
+        const int ix = min(max(ox * 2 - 1 + dx, 0), w - 1);
+        q[dy * 3 + dx] = __ldg(reinterpret_cast<const uint4*>(in + (((size_t)b * h + iy) * w + ix) * c + cc * 8));
       }
+    }
+    __nv_bfloat162 m[4];
+    {
+      const __nv_bfloat162* h0 = reinterpret_cast<const __nv_bfloat162*>(&q[0]);
+#pragma unroll
+      for (int t = 0; t < 4; t++) m[t] = h0[t];
+    }
+#pragma unroll
+    for (int k = 1; k < 9; k++) {
+      const __nv_bfloat162* hq = reinterpret_cast<const __nv_bfloat162*>(&q[k]);
+#pragma unroll
+      for (int t = 0; t < 4; t++) m[t] = __hmax2(m[t], hq[t]);
     }
     uint4 o;
     __nv_bfloat162* ho = reinterpret_cast<__nv_bfloat162*>(&o);
 #pragma unroll
-    for (int t = 0; t < 4; t++) ho[t] = __floats2bfloat162_rn(m[2 * t], m[2 * t + 1]);
+    for (int t = 0; t < 4; t++) ho[t] = m[t];
     *reinterpret_cast<uint4*>(out + (((size_t)b * oh + oy) * ow + ox) * c + cc * 8) = o;
   }
 }
 
-// Global average pooling NHWC -> [n, c]; one block per image, threads over channels.
+// Global average pooling NHWC -> [n, c]; block (x = channel chunk of 512, y = image), two channels per thread, the
+// pixel loop unrolled so that several loads are in flight.
 __global__ void __launch_bounds__(256) global_avgpool(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out,
                                                       int hw, int c) {
-  const int b = blockIdx.x;
-  for (int ch = threadIdx.x * 2; ch < c; ch += blockDim.x * 2) {
-    float s0 = 0.f, s1 = 0.f;
-    for (int p = 0; p < hw; p++) {
-      float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(in + ((size_t)b * hw + p) * c + ch));
+  const int b = blockIdx.y, ch = (blockIdx.x * 256 + threadIdx.x) * 2;
+  if (ch >= c) return;
+  const __nv_bfloat16* src = in + (size_t)b * hw * c + ch;
+  float s0 = 0.f, s1 = 0.f;
+  int p = 0;
+  for (; p + 7 <= hw; p += 7) {
+    __nv_bfloat162 v[7];
+#pragma unroll
+    for (int j = 0; j < 7; j++) v[j] = *reinterpret_cast<const __nv_bfloat162*>(src + (size_t)(p + j) * c);
+#pragma unroll
+    for (int j = 0; j < 7; j++) {
+      float2 f = __bfloat1622float2(v[j]);
       s0 += f.x;
       s1 += f.y;
     }
-    *reinterpret_cast<__nv_bfloat162*>(out + (size_t)b * c + ch) = __floats2bfloat162_rn(s0 / hw, s1 / hw);
+  }
+  for (; p < hw; p++) {
+    float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(src + (size_t)p * c));
+    s0 += f.x;
+    s1 += f.y;
+  }
+  *reinterpret_cast<__nv_bfloat162*>(out + (size_t)b * c + ch) = __floats2bfloat162_rn(s0 / hw, s1 / hw);
+}
+
+// Skinny fully connected layer: out[m, n] = sum_k a[m, k] * w[n, k] + bias[n] for a handful of rows, fp32 output.  A
+// tensor-core tile would be 128 rows x 64 columns: with 64 rows that leaves 16 CTAs each walking all of K.  Here a
+// block owns FC_NB output columns and FC_ROWS rows: the weight rows are staged in shared memory as fp32 once (two
+// planes of float4 per column, so that the sixteen k-slices a warp reads together are contiguous), thread
+// (row pair, kq) walks every sixteenth 8-element slice of its two rows of `a` with the next slice's loads in flight, and
+// the sixteen partial sums of a row meet through shuffles.
+constexpr int FC_NB = 8, FC_ROWS = 32;
+__global__ void __launch_bounds__(256, 2) fc_skinny(const __nv_bfloat16* __restrict__ a, int lda, const __nv_bfloat16* __restrict__ w,
+                                                 int ldw, const float* __restrict__ bias, float* __restrict__ out, int ldo, int M,
+                                                 int N, int K) {
+  extern __shared__ __align__(16) float4 s_w[];  // [FC_NB][2][K/8]
+  const int n0 = blockIdx.x * FC_NB, kvn = K / 8;
+  for (int base = 0; base < FC_NB * kvn; base += 256 * 8) {
+    uint4 q[8];  // eight loads in flight per thread: the weights usually come from DRAM
+#pragma unroll
+    for (int u = 0; u < 8; u++) {
+      const int i = base + u * 256 + threadIdx.x, col = i / kvn, kv = i - col * kvn;
+      q[u] = make_uint4(0, 0, 0, 0);
+      if (i < FC_NB * kvn && n0 + col < N) q[u] = __ldg(reinterpret_cast<const uint4*>(w + (size_t)(n0 + col) * ldw + kv * 8));
+    }
+#pragma unroll
+    for (int u = 0; u < 8; u++) {
+      const int i = base + u * 256 + threadIdx.x, col = i / kvn, kv = i - col * kvn;
+      const __nv_bfloat162* hq = reinterpret_cast<const __nv_bfloat162*>(&q[u]);
+      const float2 f0 = __bfloat1622float2(hq[0]), f1 = __bfloat1622float2(hq[1]), f2 = __bfloat1622float2(hq[2]),
+                   f3 = __bfloat1622float2(hq[3]);
+      if (i < FC_NB * kvn) {
+        s_w[(col * 2) * kvn + kv] = make_float4(f0.x, f0.y, f1.x, f1.y);
+        s_w[(col * 2 + 1) * kvn + kv] = make_float4(f2.x, f2.y, f3.x, f3.y);
+      }
+    }
+  }
+  __syncthreads();
+  const int kq = threadIdx.x & 15;
+  const int row0 = blockIdx.y * FC_ROWS + (threadIdx.x >> 4) * 2;
+  // rows past M read row M-1 again (their results are not stored): no branch inside the loop
+  const __nv_bfloat16* ar0 = a + (size_t)min(row0, M - 1) * lda;
+  const __nv_bfloat16* ar1 = a + (size_t)min(row0 + 1, M - 1) * lda;
+  // packed fp32 FMAs (two per instruction): lane x of an accumulator sums the even k, lane y the odd k
+  float2 acc0[FC_NB], acc1[FC_NB];
+#pragma unroll
+  for (int j = 0; j < FC_NB; j++) acc0[j] = acc1[j] = make_float2(0.f, 0.f);
+  auto step = [&](const uint4& c0, const uint4& c1, int kv) {
+    float2 x0[4], x1[4];
+    const __nv_bfloat162* h0 = reinterpret_cast<const __nv_bfloat162*>(&c0);
+    const __nv_bfloat162* h1 = reinterpret_cast<const __nv_bfloat162*>(&c1);
+#pragma unroll
+    for (int t = 0; t < 4; t++) {
+      x0[t] = __bfloat1622float2(h0[t]);
+      x1[t] = __bfloat1622float2(h1[t]);
+    }
+#pragma unroll
+    for (int j = 0; j < FC_NB; j++) {
+      const float4 w0 = s_w[(j * 2) * kvn + kv], w1 = s_w[(j * 2 + 1) * kvn + kv];
+      const float2 wa = make_float2(w0.x, w0.y), wb = make_float2(w0.z, w0.w), wc = make_float2(w1.x, w1.y),
+                   wd = make_float2(w1.z, w1.w);
+      acc0[j] = __ffma2_rn(x0[0], wa, acc0[j]);
+      acc1[j] = __ffma2_rn(x1[0], wa, acc1[j]);
+      acc0[j] = __ffma2_rn(x0[1], wb, acc0[j]);
+      acc1[j] = __ffma2_rn(x1[1], wb, acc1[j]);
+      acc0[j] = __ffma2_rn(x0[2], wc, acc0[j]);
+      acc1[j] = __ffma2_rn(x1[2], wc, acc1[j]);
+      acc0[j] = __ffma2_rn(x0[3], wd, acc0[j]);
+      acc1[j] = __ffma2_rn(x1[3], wd, acc1[j]);
+    }
+  };
+  auto load = [&](const __nv_bfloat16* r, int kv) {
+    return kv < kvn ? __ldg(reinterpret_cast<const uint4*>(r + kv * 8)) : make_uint4(0, 0, 0, 0);
+  };
+  // two slices per trip, the next trip's four loads issued before this trip's arithmetic
+  uint4 qa0 = load(ar0, kq), qa1 = load(ar1, kq), qb0 = load(ar0, kq + 16), qb1 = load(ar1, kq + 16);
+  for (int kv = kq; kv < kvn; kv += 32) {
+    const uint4 ca0 = qa0, ca1 = qa1, cb0 = qb0, cb1 = qb1;
+    qa0 = load(ar0, kv + 32);
+    qa1 = load(ar1, kv + 32);
+    qb0 = load(ar0, kv + 48);
+    qb1 = load(ar1, kv + 48);
+    step(ca0, ca1, kv);
+    if (kv + 16 < kvn) step(cb0, cb1, kv + 16);
+  }
+  float s0[FC_NB], s1[FC_NB];
+#pragma unroll
+  for (int j = 0; j < FC_NB; j++) {
+    s0[j] = acc0[j].x + acc0[j].y;
+    s1[j] = acc1[j].x + acc1[j].y;
+#pragma unroll
+    for (int d = 1; d < 16; d <<= 1) {
+      s0[j] += __shfl_xor_sync(0xffffffffu, s0[j], d);
+      s1[j] += __shfl_xor_sync(0xffffffffu, s1[j], d);
+    }
+  }
+  // lane kq stores column kq & 7 of row kq >> 3
+#pragma unroll
+  for (int j = 0; j < FC_NB; j++) {
+    if ((kq & 7) == j && n0 + j < N) {
+      const int row = row0 + (kq >> 3);
+      if (row < M) out[(size_t)row * ldo + n0 + j] = ((kq >> 3) ? s1[j] : s0[j]) + (bias ? bias[n0 + j] : 0.f);
+    }
   }
 }
 
@@ -453,7 +572,21 @@ cudaError_t nn_maxpool3x3s2(const void* in, void* out, int n, int h, int w, int 
 }
 cudaError_t nn_global_avgpool(const void* in, void* out, int n, int hw, int c, cudaStream_t s) {
   if (c % 2) return cudaErrorInvalidValue;
-  global_avgpool<<<n, 256, 0, s>>>((const __nv_bfloat16*)in, (__nv_bfloat16*)out, hw, c);
+  global_avgpool<<<dim3((c + 511) / 512, n), 256, 0, s>>>((const __nv_bfloat16*)in, (__nv_bfloat16*)out, hw, c);
+  return cudaGetLastError();
+}
+cudaError_t nn_fc_skinny(const void* a, int lda, const void* w, int ldw, const float* bias, float* out, int ldo, int M, int N, int K,
+                         cudaStream_t s) {
+  const size_t smem = (size_t)FC_NB * K * sizeof(float);
+  if (K % 8 || lda % 8 || ldw % 8 || (((uintptr_t)a | (uintptr_t)w) & 15) || smem > 200 * 1024 || M <= 0) return cudaErrorInvalidValue;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(fc_skinny, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    if (e != cudaSuccess) return e;
+    attr_set = true;
+  }
+  fc_skinny<<<dim3((N + FC_NB - 1) / FC_NB, (M + FC_ROWS - 1) / FC_ROWS), 256, smem, s>>>((const __nv_bfloat16*)a, lda, (const __nv_bfloat16*)w,
+                                                                          ldw, bias, out, ldo, M, N, K);
   return cudaGetLastError();
 }
 cudaError_t nn_softmax_response(const float* logits, int rows, int n, int ld, const void* d_stub, void* direct_out,

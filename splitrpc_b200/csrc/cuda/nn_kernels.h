@@ -14,6 +14,10 @@ cudaError_t nn_stem_s2d(const void* d_stub, const float* direct_in, int batch, v
                         const float inv_std[3], cudaStream_t s);
 cudaError_t nn_maxpool3x3s2(const void* in, void* out, int n, int h, int w, int c, cudaStream_t s);
 cudaError_t nn_global_avgpool(const void* in, void* out, int n, int hw, int c, cudaStream_t s);
+// out[M, N] (fp32) = a[M, K] . w[N, K]^T + bias for a few rows (SIMT, weights staged in shared memory): the shape where a
+// 128-row tensor-core tile leaves most of the GPU idle.  K a multiple of 8 up to 6400; lda, ldw multiples of 8.
+cudaError_t nn_fc_skinny(const void* a, int lda, const void* w, int ldw, const float* bias, float* out, int ldo, int M, int N, int K,
+                         cudaStream_t s);
 cudaError_t nn_softmax_response(const float* logits, int rows, int n, int ld, const void* d_stub, void* direct_out,
                                 size_t resp_stride, int write_argmax, uint32_t* counter, uint32_t* flag, uint32_t flag_value,
                                 cudaStream_t s);

@@ -158,7 +158,10 @@ class ResNet50:
                 idn = cur
             cur = self._conv1x1(t2, name + ".c3", b[name + ".out"][:nb], "relu", residual=idn)
         avg = ops.global_avgpool(cur, out=b["avg"][:nb])
-        ops.gemm(avg, p["fc.w"], bias=p["fc.b"], out=b["logits"][:nb])
+        if nb <= 64:
+            ops.fc_skinny(avg, p["fc.w"], bias=p["fc.b"], out=b["logits"][:nb])
+        else:
+            ops.gemm(avg, p["fc.w"], bias=p["fc.b"], out=b["logits"][:nb])
         ops.softmax_response(b["logits"][:nb], nb, out=out, d_stub=0 if out is not None else d_stub, resp_stride=RESP_BYTES,
                              counter=counter, flag_ptr=flag_ptr, flag_value=flag_value)
         return b["logits"][:nb]

@@ -69,6 +69,22 @@ def gemm(a: torch.Tensor, b: torch.Tensor, bias: torch.Tensor | None = None, res
     return out
 
 
+def fc_skinny(a: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """``a @ w.T + bias`` in fp32 for a handful of rows (``a`` ``[M,K]``, ``w`` ``[N,K]`` bf16): the classifier head of a
+    batch, where a 128-row tensor-core tile would leave most SMs without work."""
+    assert a.is_cuda and a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.stride(1) == 1 and w.stride(1) == 1
+    M, K = a.shape
+    N = w.shape[0]
+    assert w.shape[1] == K
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.float32, device=a.device)
+    assert out.dtype == torch.float32 and out.shape == (M, N) and out.stride(1) == 1
+    if bias is not None:
+        assert bias.dtype == torch.float32 and bias.numel() == N
+    _C.fc_skinny(a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(0), _ptr(bias), out.data_ptr(), out.stride(0), M, N, K, _stream())
+    return out
+
+
 def conv2d_nhwc(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, residual: torch.Tensor | None = None,
                 stride: int = 1, pad: int = 0, act: str | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
     """Convolution of an NHWC bf16 tensor with ``[Cout, R, S, Cin]`` bf16 filters (Cin a multiple of 64)."""

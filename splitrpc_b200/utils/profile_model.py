@@ -31,7 +31,7 @@ def _peaks():
 
 def _work(name, args, kwargs, out):
     """Algorithmic (flops, bytes) of one op call."""
-    if name == "gemm":
+    if name in ("gemm", "fc_skinny"):
         a, b = args[0], args[1]
         M, K = a.shape
         N = b.shape[0]
@@ -94,7 +94,7 @@ def main():
 
     records = []
     if not args.no_events:
-        for name in ("gemm", "conv2d_nhwc", "conv1x1_dual", "stem_im2col", "stem_s2d", "stem_conv", "maxpool3x3s2", "global_avgpool", "softmax_response", "layernorm",
+        for name in ("gemm", "fc_skinny", "conv2d_nhwc", "conv1x1_dual", "stem_im2col", "stem_s2d", "stem_conv", "maxpool3x3s2", "global_avgpool", "softmax_response", "layernorm",
                      "bert_embed_ln", "attention_d64"):
             fn = getattr(ops, name)
 

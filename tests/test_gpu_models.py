@@ -24,6 +24,16 @@ def test_nn_layers_match_pytorch(torch_cuda):
     assert torch.equal(ops.maxpool3x3s2(x).float(), ref)
     y = torch.randn(4, 7, 7, 2048, device="cuda").bfloat16()
     torch.testing.assert_close(ops.global_avgpool(y).float(), y.float().mean((1, 2)), rtol=1e-2, atol=1e-2)
+    x = torch.randn(2, 13, 9, 72, device="cuda").bfloat16()  # odd sizes: clamped windows on every border
+    ref = F.max_pool2d(x.float().permute(0, 3, 1, 2), 3, 2, 1).permute(0, 2, 3, 1)
+    assert torch.equal(ops.maxpool3x3s2(x).float(), ref)
+    y = torch.randn(3, 5, 5, 640, device="cuda").bfloat16()
+    torch.testing.assert_close(ops.global_avgpool(y).float(), y.float().mean((1, 2)), rtol=1e-2, atol=1e-2)
+    for m_rows, n_cols, k in ((64, 1000, 2048), (5, 10, 512), (130, 77, 256)):
+        a = torch.randn(m_rows, k, device="cuda").bfloat16()
+        w = (torch.randn(n_cols, k, device="cuda") * 0.05).bfloat16()
+        bias = torch.randn(n_cols, device="cuda")
+        torch.testing.assert_close(ops.fc_skinny(a, w, bias=bias), a.float() @ w.float().t() + bias, rtol=1e-3, atol=1e-3)
     h = torch.randn(300, 768, device="cuda").bfloat16()
     r = torch.randn(300, 768, device="cuda").bfloat16()
     g, b = torch.randn(768, device="cuda"), torch.randn(768, device="cuda")
