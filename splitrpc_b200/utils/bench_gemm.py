@@ -23,6 +23,7 @@ def main():
     ap.add_argument("--n", type=int, default=8192)
     ap.add_argument("--k", type=int, default=8192)
     ap.add_argument("--conv", default=None)
+    ap.add_argument("--dual", default=None, help="two-input 1x1 convolution: n,oh,c1,h2,c2,cout,stride2")
     ap.add_argument("--residual", action="store_true")
     ap.add_argument("--act", default=None)
     ap.add_argument("--iters", type=int, default=20)
@@ -32,7 +33,27 @@ def main():
     args = ap.parse_args()
     torch.cuda.set_device(0)
     hbm, tf, tag = _peaks()
-    if args.conv:
+    if args.dual:
+        n, oh, c1, h2, c2, cout, s2 = (int(v) for v in args.dual.split(","))
+        x1 = (torch.randn(n, oh, oh, c1, device="cuda") * 0.5).bfloat16()
+        x2 = (torch.randn(n, h2, h2, c2, device="cuda") * 0.5).bfloat16()
+        w1 = (torch.randn(cout, c1, device="cuda") * 0.1).bfloat16()
+        w2 = (torch.randn(cout, c2, device="cuda") * 0.1).bfloat16()
+        wt = torch.cat([w1, w2], dim=1).contiguous()
+        bias = torch.randn(cout, device="cuda")
+        out = torch.empty(n, oh, oh, cout, dtype=torch.bfloat16, device="cuda")
+        fn = lambda: ops.conv1x1_dual(x1, x2, wt, bias=bias, stride2=s2, act=args.act, out=out)
+        if args.library:
+            import torch.nn.functional as F
+
+            torch.backends.cudnn.benchmark = True
+            x1l, x2l, bl = x1.permute(0, 3, 1, 2), x2.permute(0, 3, 1, 2), bias.bfloat16()
+            w1l, w2l = w1.view(cout, c1, 1, 1), w2.view(cout, c2, 1, 1)
+            fn = lambda: torch.relu_(F.conv2d(x1l, w1l, bl).add_(F.conv2d(x2l, w2l, None, s2)))
+        flops = 2.0 * n * oh * oh * cout * (c1 + c2)
+        nbytes = 2 * (x1.numel() + x2.numel() // (s2 * s2) + wt.numel() + out.numel())
+        desc = f"two-input 1x1 conv {args.dual}"
+    elif args.conv:
         n, h, w, cin, cout, k, s, pad = (int(v) for v in args.conv.split(","))
         x = (torch.randn(n, h, w, cin, device="cuda") * 0.5).bfloat16()
         wt = (torch.randn(cout, k, k, cin, device="cuda") * 0.1).bfloat16()
@@ -112,7 +133,7 @@ def main():
             times.append(e0.elapsed_time(e1))
     ops.check_status()
     if args.library:
-        desc = "library " + desc + " (bias only, no activation or residual)"
+        desc = "library " + desc + (" (two convolutions + add + ReLU)" if args.dual else " (bias only, no activation or residual)")
     times.sort()
     ms = times[len(times) // 2]
     print(f"{desc}{' +res' if args.residual else ''}: median {ms * 1e3:.1f} us  {flops / ms / 1e9:.1f} TFLOP/s "
