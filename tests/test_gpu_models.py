@@ -131,12 +131,13 @@ def test_tensor_core_attention_matches_pytorch(torch_cuda, seq, heads):
     torch.testing.assert_close(out.float(), ref, rtol=2e-2, atol=2e-2)
 
 
-def test_resnet50_matches_fp32_reference(torch_cuda):
+@pytest.mark.parametrize("fuse_shortcut", [True, False])
+def test_resnet50_matches_fp32_reference(torch_cuda, fuse_shortcut):
     torch = torch_cuda
     from splitrpc_b200 import ops
     from splitrpc_b200.models import ResNet50
 
-    m = ResNet50(device=0, max_batch=4)
+    m = ResNet50(device=0, max_batch=4, fuse_shortcut=fuse_shortcut)
     x = torch.randn(3, 3, 224, 224, device="cuda")
     out = torch.zeros(3, 1000, device="cuda")
     logits = m.forward(3, x=x, out=out)
