@@ -41,10 +41,10 @@ class P2pRpcRr {
 
   explicit P2pRpcRr(const p2p_rpc_conn_info* tmpl = nullptr, size_t max_payload = 0)
       : max_payload_size(max_payload),
-        transport_mbufs(new p2p_hbufs),
-        hdr_bufs(new p2p_hbufs),
-        payload_bufs(new p2p_bufs),
-        payload_sk_bufs(new p2p_sk_buf) {
+        transport_mbufs(new p2p_hbufs()),
+        hdr_bufs(new p2p_hbufs()),
+        payload_bufs(new p2p_bufs()),
+        payload_sk_bufs(new p2p_sk_buf()) {
     if (tmpl) _client_conn_info = *tmpl;
     clear_bufs();
   }
@@ -58,6 +58,15 @@ class P2pRpcRr {
   P2pRpcRr& operator=(const P2pRpcRr&) = delete;
 
   void clear_bufs() {
+    // Entries that were in use go back to zero, so that an index nobody filled can never be read as a stale
+    // pointer or length.
+    for (uint16_t i = 0; i < transport_mbufs->num_items; i++) transport_mbufs->burst_items[i] = 0;
+    for (uint16_t i = 0; i < hdr_bufs->num_items; i++) hdr_bufs->burst_items[i] = 0;
+    for (uint16_t i = 0; i < payload_bufs->num_items; i++) {
+      payload_bufs->burst_items[i] = 0;
+      payload_bufs->item_size[i] = 0;
+    }
+    n_frags_ = 0;
     transport_mbufs->num_items = 0;
     hdr_bufs->num_items = 0;
     payload_bufs->num_items = 0;
@@ -81,18 +90,30 @@ class P2pRpcRr {
   }
 
   // Places a received fragment at its sequence number.  Returns false (and leaves
-  // the record untouched) for an out-of-range or repeated sequence number.
+  // the record untouched) for an out-of-range or repeated sequence number and for
+  // an empty fragment of a non-empty request.
   bool rr_emplace_mbuf(uintptr_t mbuf, uintptr_t hdr, uintptr_t payload, size_t size, int seq_num) {
     if (seq_num < 0 || seq_num >= MAX_BI_SIZE) return false;
+    if (size == 0 && max_payload_size > 0) return false;
     if ((size_t)seq_num >= seen_.size()) seen_.resize((size_t)seq_num + 1, 0);
     if (seen_[seq_num]) return false;
     seen_[seq_num] = 1;
     place(mbuf, hdr, payload, size, (uint16_t)seq_num);
     payload_size += size;
+    n_frags_++;
     return true;
   }
 
-  bool is_rr_ready() const { return payload_size == max_payload_size; }
+  // Ready = every byte of the fixed-size request has arrived AND the fragments
+  // fill indices 0..n-1 without a hole.  The byte count alone is not enough: a
+  // fragment with a skipped sequence number raises num_items past an index that
+  // nobody filled, and a copy list built from that index would be garbage.
+  bool is_rr_ready() const { return payload_size == max_payload_size && n_frags_ == payload_bufs->num_items; }
+  // All the bytes are there (or more) but the sequence numbers leave a hole: the
+  // sender broke the framing rule and the record can never become ready.
+  bool is_rr_malformed() const {
+    return payload_size > max_payload_size || (payload_size == max_payload_size && n_frags_ != payload_bufs->num_items);
+  }
 
   void rr_print_bufs() const {
     std::printf("rr %p token=%lu: %u fragments, %zu/%zu bytes\n", (const void*)this, (unsigned long)req_token,
@@ -102,6 +123,7 @@ class P2pRpcRr {
 
  private:
   std::vector<uint8_t> seen_;
+  uint16_t n_frags_ = 0;  // distinct fragments accepted since clear_bufs()
   void place(uintptr_t mbuf, uintptr_t hdr, uintptr_t payload, size_t size, uint16_t idx) {
     transport_mbufs->burst_items[idx] = mbuf;
     hdr_bufs->burst_items[idx] = hdr;

@@ -89,8 +89,9 @@ class SplitRpcServer {
         if (rr->is_rr_ready()) {
           rr_pool_.mark_rx_ready_rr(rr);
           stats_.rx_reqs++;
-        } else if (rr->payload_size > rr->max_payload_size) {
-          // More bytes than the app's request size: protocol violation, drop.
+        } else if (rr->is_rr_malformed()) {
+          // More bytes than the app's request size, or all the bytes with a hole in the sequence numbers:
+          // protocol violation, drop the whole request.
           release_rr_rx(rr);
           rr_pool_.drop_partial(rr);
           stats_.dropped_pkts++;

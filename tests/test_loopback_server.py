@@ -137,6 +137,15 @@ def test_zero_token_and_bad_sequence_packets_are_dropped(C, mtu1k):
         assert cli.received == 0 and ss["dropped_pkts"] == ss["rx_pkts"] > 0 and ss["rx_reqs"] == 0
 
 
+def test_in_range_sequence_gap_never_reaches_the_engine(C, mtu1k):
+    """A single-fragment request stamped with sequence number 3 has all its bytes but leaves indices 0..2 unfilled:
+    the server must drop it instead of building a copy list from them (CPU engine only)."""
+    ok, cli, st, ss, ws = _serve(C, "echo", 1024, 1024, 20, 0, 1, "echo", outstanding=2, mtu_slots=1024,
+                                 faults=dict(force_seq=3), drain_ns=200_000_000)
+    assert cli.received == 0 and ss["rx_reqs"] == 0 and ws["num_req"] == 0
+    assert ss["dropped_pkts"] == ss["rx_pkts"] > 0
+
+
 def test_replica_marked_down_is_skipped_by_steering(C, mtu1k):
     sp, cp = C.make_loopback_pair(1024, 2048)
     apps = [C.make_app("echo", -1, 1024, 1024, [], 128, 1, 4) for _ in range(3)]

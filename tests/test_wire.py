@@ -96,6 +96,38 @@ def test_reassembly_out_of_order_duplicates_and_bad_packets(C):
     assert r.expire(0) == 1 and r.partial == 0
 
 
+def test_reassembly_needs_every_sequence_number(C):
+    """The byte count alone does not complete a request: sequence numbers must fill 0..n-1 without a hole."""
+    ctmpl = C.client_conn_template(CLIENT_URI)
+    payload = bytes(np.random.default_rng(3).integers(0, 256, 4096, dtype=np.uint8))
+    # one fragment that carries all 4096 bytes but claims sequence number 3: indices 0..2 were never filled
+    hdr, body = C.build_fragments(ctmpl, 77, payload, 4096)[0]
+    bad = bytearray(hdr)
+    struct.pack_into("<H", bad, 58, 3)
+    r = C.Reassembler(4096)
+    assert r.feed(bytes(bad), body) is None and r.partial == 1
+    assert r.expire(0) == 1
+    # sequence numbers 0, 2, 3 whose sizes add up to the request size (the middle one is oversized)
+    r = C.Reassembler(4096)
+    f = C.build_fragments(ctmpl, 78, payload, 1024)
+
+    def with_seq(h, seq):
+        b = bytearray(h)
+        struct.pack_into("<H", b, 58, seq)
+        return bytes(b)
+
+    assert r.feed(f[0][0], payload[:1024]) is None
+    assert r.feed(with_seq(f[2][0], 2), payload[1024:3072]) is None
+    assert r.feed(with_seq(f[3][0], 3), payload[3072:]) is None  # 4096 bytes are in, index 1 is a hole
+    assert r.partial == 1 and r.counters["rx_ready"] == 0
+    # an empty fragment of a non-empty request is refused
+    assert r.feed(with_seq(f[1][0], 1), b"") is None and r.counters["dropped_dup"] >= 1
+    # a well-formed request on the same pool still completes after the malformed ones
+    for h, b in C.build_fragments(ctmpl, 79, payload, 1024):
+        out = r.feed(h, b)
+    assert out is not None and out[1] == payload
+
+
 def test_copy_list_coalesces_adjacent_fragments(C):
     base = 1 << 20
     frags = [(base, 8192), (base + 8192, 8192), (base + 3 * 8192, 8192), (base + 4 * 8192, 100)]
