@@ -1,0 +1,70 @@
+"""Builds the reference arm's native library, ``baseline/_ref/libsplitrpc_ref.so``.
+
+The original project is a CMake tree whose server needs DPDK, gdrcopy, verbs, ONNX Runtime/TensorRT and an spdlog
+submodule that its repository snapshot does not contain, so it cannot be installed as a whole.  What builds offline is
+its scatter-gather engine: ``src/transport/g_copy_ng.cu`` and the headers it includes are compiled UNMODIFIED from the
+original tree (``--src``, default ``/root/reference/src``) for sm_100a, with two stand-in headers (``spdlog/spdlog.h``:
+no-op logging; ``gdrapi.h``: declarations only) and ``ref_harness/ref_driver.cu``, which exports C symbols that call
+the original's ``gather_skbs`` / ``scatter_skbs`` / ``sg_on_gpu`` / ``WaitForAppRunComplete``.  The output directory is
+git-ignored.  On a machine without the original tree an already built library is used as is.
+"""
+from __future__ import annotations
+
+import argparse
+import hashlib
+import shutil
+import subprocess
+import sys
+from pathlib import Path
+
+HERE = Path(__file__).resolve().parent
+OUT = HERE / "_ref"
+LIB = OUT / "libsplitrpc_ref.so"
+GENCODE = ["-gencode", "arch=compute_100a,code=sm_100a"]
+
+
+def _nvcc() -> str:
+    for cand in (shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
+        if cand and Path(cand).exists():
+            return cand
+    raise RuntimeError("nvcc not found")
+
+
+def build(src: str = "/root/reference/src", force: bool = False) -> Path | None:
+    """Returns the library path, or None when it neither exists nor can be built."""
+    srcdir = Path(src)
+    units = [srcdir / "transport" / "g_copy_ng.cu", HERE / "ref_harness" / "ref_driver.cu"]
+    if not units[0].exists():
+        return LIB if LIB.exists() else None
+    OUT.mkdir(exist_ok=True)
+    key = hashlib.sha256(b"".join(u.read_bytes() for u in units)).hexdigest()
+    stamp = OUT / "build.stamp"
+    if LIB.exists() and stamp.exists() and stamp.read_text() == key and not force:
+        return LIB
+    inc = [f"-I{srcdir}", f"-I{srcdir / 'utils'}", f"-I{srcdir / 'utils' / 'nv_helpers'}", f"-I{srcdir / 'transport'}",
+           f"-I{HERE / 'ref_harness' / 'shims'}"]
+    flags = GENCODE + ["-O3", "-std=c++17", "-rdc=true", "-lineinfo", "-w", "-Xcompiler", "-fPIC"]
+    objs = []
+    for u in units:
+        o = OUT / (u.stem + ".o")
+        r = subprocess.run([_nvcc(), "-c", str(u), "-o", str(o)] + flags + inc, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError(f"reference build failed for {u}:\n{r.stderr[-4000:]}")
+        objs.append(str(o))
+    # g_copy_ng.cu has one kernel that calls the device runtime (device-side cudaMemcpyAsync), hence -rdc and cudadevrt
+    r = subprocess.run([_nvcc(), "-shared", "-o", str(LIB)] + objs + GENCODE + ["-cudart", "static", "-lcudadevrt"],
+                       capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"reference link failed:\n{r.stderr[-4000:]}")
+    stamp.write_text(key)
+    return LIB
+
+
+if __name__ == "__main__":
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--src", default="/root/reference/src")
+    ap.add_argument("--force", action="store_true")
+    a = ap.parse_args()
+    p = build(a.src, a.force)
+    print(p if p else "unavailable: no original tree and no prebuilt library")
+    sys.exit(0 if p else 1)

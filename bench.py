@@ -378,10 +378,15 @@ def run_tp(args, rank: int, world: int, local_rank: int) -> dict:
     return res
 
 
-def run_reference(args) -> dict:
-    return {"impl": "reference", "unavailable": "the original server needs DPDK 21.08, gdrcopy, libibverbs/rdmacm, ONNX "
-            "Runtime + TensorRT and a spdlog submodule, none of which exist offline on this image; it has no setup.py/pyproject "
-            "so the pip install into baseline/_ref fails"}
+def run_reference(args, rank: int, world: int, local_rank: int) -> dict:
+    """The original's data path, re-hosted: see baseline/reference_arm.py.  Imports nothing of this package."""
+    sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "baseline"))
+    try:
+        import reference_arm
+
+        return reference_arm.run(args, rank, world, local_rank, CONFIGS[args.config])
+    except Exception as e:  # noqa: BLE001 - the arm must answer with one JSON line and exit 0
+        return {"impl": "reference", "unavailable": f"reference arm failed: {type(e).__name__}: {str(e)[:300]}"}
 
 
 def main():
@@ -396,8 +401,9 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
+        res = run_reference(args, rank, world, local_rank)
         if rank == 0:
-            print(json.dumps(run_reference(args)), flush=True)
+            print(json.dumps(res), flush=True)
         return
     res = run_tp(args, rank, world, local_rank) if args.config == "bert_large_tp" else run_ours(args, rank, world, local_rank)
     if rank == 0:

@@ -11,8 +11,11 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <unistd.h>
+
 #include <mutex>
 #include <string>
+#include <vector>
 
 #include "../host/p2p_rpc_app.h"
 #include "driver_api.h"
@@ -59,6 +62,8 @@ const SrpcDriverApi* srpc_driver_api() {
     get("cuStreamWriteValue32", (void**)&api.StreamWriteValue32);
     get("cuTensorMapEncodeTiled", (void**)&api.TensorMapEncodeTiled);
     get("cuDeviceGetAttribute", (void**)&api.DeviceGetAttribute);
+    get("cuMemExportToShareableHandle", (void**)&api.MemExportToShareableHandle);
+    get("cuMemImportFromShareableHandle", (void**)&api.MemImportFromShareableHandle);
     api.ok = api.MemCreate && api.MemMap && api.StreamWaitValue32 && api.TensorMapEncodeTiled;
   });
   return &api;
@@ -69,7 +74,35 @@ struct RingImpl {
   CUdeviceptr va;
   size_t cap;
   bool vmm;
+  bool shareable;  // created with a POSIX file descriptor handle type, so it can be exported
 };
+
+// Maps `handle` twice back to back and grants access to `owner` and (optionally) to every device that can reach it.
+static int map_ring_twice(const SrpcDriverApi* d, RingImpl* impl, size_t cap, size_t gran, int owner, bool peer_access,
+                          int only_dev) {
+  CUresult r = d->MemAddressReserve(&impl->va, 2 * cap, gran, 0, 0);
+  if (r != CUDA_SUCCESS) return fail_drv("cuMemAddressReserve", r);
+  DRV(d->MemMap(impl->va, cap, 0, impl->handle, 0));
+  DRV(d->MemMap(impl->va + cap, cap, 0, impl->handle, 0));
+  std::vector<CUmemAccessDesc> acc;
+  int ndev = 0;
+  cudaGetDeviceCount(&ndev);
+  for (int p = 0; p < ndev; p++) {
+    int can = (p == owner);
+    if (only_dev >= 0) can = (p == only_dev);
+    else if (p != owner && peer_access) cudaDeviceCanAccessPeer(&can, p, owner);
+    if (!can) continue;
+    CUmemAccessDesc a = {};
+    a.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
+    a.location.id = p;
+    a.flags = CU_MEM_ACCESS_FLAGS_PROT_READWRITE;
+    acc.push_back(a);
+  }
+  DRV(d->MemSetAccess(impl->va, 2 * cap, acc.data(), acc.size()));
+  impl->cap = cap;
+  impl->vmm = true;
+  return 0;
+}
 
 static int d_device_count() {
   int n = 0;
@@ -134,31 +167,19 @@ static int d_ring_alloc(int dev, size_t min_bytes, bool peer_access, SrpcRingMem
     DRV(d->MemGetAllocationGranularity(&gran, &prop, CU_MEM_ALLOC_GRANULARITY_MINIMUM));
     size_t cap = (min_bytes + gran - 1) / gran * gran;
     if (cap == 0) cap = gran;
-    DRV(d->MemCreate(&impl->handle, cap, &prop, 0));
-    CUresult r = d->MemAddressReserve(&impl->va, 2 * cap, gran, 0, 0);
-    if (r != CUDA_SUCCESS) {
+    // Ask for an allocation that can be handed to another process as a file descriptor; fall back to a private one.
+    prop.requestedHandleTypes = CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR;
+    impl->shareable = true;
+    if (d->MemCreate(&impl->handle, cap, &prop, 0) != CUDA_SUCCESS) {
+      prop.requestedHandleTypes = CU_MEM_HANDLE_TYPE_NONE;
+      impl->shareable = false;
+      DRV(d->MemCreate(&impl->handle, cap, &prop, 0));
+    }
+    if (map_ring_twice(d, impl, cap, gran, dev, peer_access, -1) != 0) {
       d->MemRelease(impl->handle);
       delete impl;
-      return fail_drv("cuMemAddressReserve", r);
+      return -1;
     }
-    DRV(d->MemMap(impl->va, cap, 0, impl->handle, 0));
-    DRV(d->MemMap(impl->va + cap, cap, 0, impl->handle, 0));
-    // Grant access to the owner and to every peer that can address it.
-    int ndev = d_device_count();
-    std::vector<CUmemAccessDesc> acc;
-    for (int p = 0; p < ndev; p++) {
-      int can = (p == dev);
-      if (p != dev && peer_access) cudaDeviceCanAccessPeer(&can, p, dev);
-      if (!can) continue;
-      CUmemAccessDesc a = {};
-      a.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
-      a.location.id = p;
-      a.flags = CU_MEM_ACCESS_FLAGS_PROT_READWRITE;
-      acc.push_back(a);
-    }
-    DRV(d->MemSetAccess(impl->va, 2 * cap, acc.data(), acc.size()));
-    impl->cap = cap;
-    impl->vmm = true;
     out->base = (void*)impl->va;
     out->capacity = cap;
     out->double_mapped = true;
@@ -191,6 +212,61 @@ static int d_ring_free(SrpcRingMem* m) {
   delete impl;
   m->impl = nullptr;
   m->base = nullptr;
+  return 0;
+}
+
+static int d_ring_export(const SrpcRingMem* m, int* fd) {
+  const RingImpl* impl = static_cast<const RingImpl*>(m->impl);
+  const SrpcDriverApi* d = srpc_driver_api();
+  if (!impl || !impl->vmm || !impl->shareable || !d->MemExportToShareableHandle)
+    return fail_drv("ring is not shareable", CUDA_ERROR_NOT_SUPPORTED);
+  int out = -1;
+  DRV(d->MemExportToShareableHandle(&out, impl->handle, CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR, 0));
+  *fd = out;
+  return 0;
+}
+
+// The physical memory stays on the exporting process's GPU; this process maps it and lets `dev` address it over
+// NVLink.  The descriptor is closed here: the mapping keeps the allocation alive.
+static int d_ring_import(int dev, int fd, size_t cap, SrpcRingMem* out) {
+  RT(cudaSetDevice(dev));
+  RT(cudaFree(0));
+  const SrpcDriverApi* d = srpc_driver_api();
+  if (!d->ok || !d->MemImportFromShareableHandle) return fail_drv("cuMemImportFromShareableHandle unavailable", CUDA_ERROR_NOT_SUPPORTED);
+  RingImpl* impl = new RingImpl{};
+  CUresult r = d->MemImportFromShareableHandle(&impl->handle, (void*)(uintptr_t)fd, CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR);
+  close(fd);
+  if (r != CUDA_SUCCESS) {
+    delete impl;
+    return fail_drv("cuMemImportFromShareableHandle", r);
+  }
+  CUmemAllocationProp prop = {};
+  prop.type = CU_MEM_ALLOCATION_TYPE_PINNED;
+  prop.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
+  prop.location.id = dev;
+  size_t gran = 0;
+  DRV(d->MemGetAllocationGranularity(&gran, &prop, CU_MEM_ALLOC_GRANULARITY_MINIMUM));
+  if (map_ring_twice(d, impl, cap, gran, dev, false, dev) != 0) {
+    d->MemRelease(impl->handle);
+    delete impl;
+    return -1;
+  }
+  impl->shareable = false;
+  out->base = (void*)impl->va;
+  out->capacity = cap;
+  out->double_mapped = true;
+  out->impl = impl;
+  out->fd = -1;
+  return 0;
+}
+
+static int d_host_register(void* p, size_t bytes, void** dptr) {
+  RT(cudaHostRegister(p, bytes, cudaHostRegisterMapped | cudaHostRegisterPortable));
+  RT(cudaHostGetDevicePointer(dptr, p, 0));
+  return 0;
+}
+static int d_host_unregister(void* p) {
+  RT(cudaHostUnregister(p));
   return 0;
 }
 
@@ -231,7 +307,8 @@ extern "C" const SrpcDeviceOps* srpc_cuda_ops() {
   static const SrpcDeviceOps ops = {
       d_device_count, d_set_device,  d_stream_create, d_stream_destroy,    d_stream_sync, d_stream_query, d_wait32,
       d_write32,      d_event_create, d_event_destroy, d_ring_alloc,        d_ring_free,   d_host_alloc_mapped,
-      d_host_free,    d_dev_alloc,    d_dev_free,      d_memcpy_async,      d_memset_async, d_graph_launch, d_last_error};
+      d_host_free,    d_dev_alloc,    d_dev_free,      d_memcpy_async,      d_memset_async, d_graph_launch, d_last_error,
+      d_ring_export,  d_ring_import,  d_host_register, d_host_unregister};
   return &ops;
 }
 

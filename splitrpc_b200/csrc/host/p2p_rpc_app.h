@@ -78,6 +78,18 @@ struct SrpcRingMem {
   size_t capacity = 0;       // bytes of physical ring (mapping covers 2x when double_mapped)
   bool double_mapped = false;
   void* impl = nullptr;      // backend bookkeeping
+  int fd = -1;               // host rings: the memfd behind the mapping (kept open so the ring can be exported)
+};
+
+// Host memory that several processes map (a memfd) and that, on a GPU build, every one of them registers with CUDA, so
+// that the CPU threads and the GPUs of all those processes address the same words: slot doorbells, response
+// destinations, transmit arenas.  `dev` is this process's device-side address of `host`.
+struct SrpcSharedMem {
+  void* host = nullptr;
+  void* dev = nullptr;
+  size_t bytes = 0;
+  int fd = -1;
+  bool registered = false;
 };
 
 struct SrpcDeviceOps {
@@ -101,6 +113,14 @@ struct SrpcDeviceOps {
   int (*memset_async)(void* dst, int v, size_t n, cudaStream_t s);
   int (*graph_launch)(cudaGraphExec_t g, cudaStream_t s);
   const char* (*last_error)();
+  // Sharing with another process on the same machine.  ring_export returns a file descriptor for the physical
+  // allocation of a ring made by ring_alloc (the caller closes it); ring_import maps such an allocation (twice, like
+  // its owner does) into this process and gives `dev` read/write access to it.  host_register pins an existing host
+  // mapping (a memfd that the peer process maps too) and returns its device-side address.
+  int (*ring_export)(const SrpcRingMem* m, int* fd);
+  int (*ring_import)(int dev, int fd, size_t capacity, SrpcRingMem* out);
+  int (*host_register)(void* p, size_t bytes, void** dptr);
+  int (*host_unregister)(void* p);
 };
 
 // Implemented by the CUDA half; returns nullptr when the library was built
@@ -136,7 +156,24 @@ static inline bool srpc_host_ring_alloc(size_t min_bytes, SrpcRingMem* out) {
   }
   void* a = mmap(va, cap, PROT_READ | PROT_WRITE, MAP_SHARED | MAP_FIXED, fd, 0);
   void* b = mmap((uint8_t*)va + cap, cap, PROT_READ | PROT_WRITE, MAP_SHARED | MAP_FIXED, fd, 0);
-  close(fd);
+  if (a == MAP_FAILED || b == MAP_FAILED) {
+    close(fd);
+    munmap(va, 2 * cap);
+    return false;
+  }
+  out->base = va;
+  out->capacity = cap;
+  out->double_mapped = true;
+  out->impl = nullptr;
+  out->fd = fd;
+  return true;
+}
+// Maps a host ring that another process created (its memfd arrived over a control channel).  Takes ownership of fd.
+static inline bool srpc_host_ring_import(int fd, size_t cap, SrpcRingMem* out) {
+  void* va = mmap(nullptr, 2 * cap, PROT_NONE, MAP_PRIVATE | MAP_ANONYMOUS, -1, 0);
+  if (va == MAP_FAILED) return false;
+  void* a = mmap(va, cap, PROT_READ | PROT_WRITE, MAP_SHARED | MAP_FIXED, fd, 0);
+  void* b = mmap((uint8_t*)va + cap, cap, PROT_READ | PROT_WRITE, MAP_SHARED | MAP_FIXED, fd, 0);
   if (a == MAP_FAILED || b == MAP_FAILED) {
     munmap(va, 2 * cap);
     return false;
@@ -145,37 +182,125 @@ static inline bool srpc_host_ring_alloc(size_t min_bytes, SrpcRingMem* out) {
   out->capacity = cap;
   out->double_mapped = true;
   out->impl = nullptr;
+  out->fd = fd;
   return true;
 }
 static inline void srpc_host_ring_free(SrpcRingMem* m) {
   if (m->base) munmap(m->base, 2 * m->capacity);
+  if (m->fd >= 0) close(m->fd);
   m->base = nullptr;
+  m->fd = -1;
 }
 
-// Request ring, response ring and per-slot state words of one app.
+// Shared host memory: create (memfd) or import (an fd that arrived from the creator), then optionally register it
+// with CUDA.  `with_cuda` needs the CUDA half of the library.
+static inline bool srpc_shm_map(int fd, size_t bytes, bool with_cuda, SrpcSharedMem* out) {
+  void* p = mmap(nullptr, bytes, PROT_READ | PROT_WRITE, MAP_SHARED, fd, 0);
+  if (p == MAP_FAILED) return false;
+  out->host = out->dev = p;
+  out->bytes = bytes;
+  out->fd = fd;
+  out->registered = false;
+  if (with_cuda) {
+    const SrpcDeviceOps* ops = srpc_cuda_ops();
+    void* d = nullptr;
+    if (!ops || ops->host_register(p, bytes, &d) != 0) {
+      munmap(p, bytes);
+      out->host = out->dev = nullptr;
+      return false;
+    }
+    out->dev = d;
+    out->registered = true;
+  }
+  return true;
+}
+static inline bool srpc_shm_create(size_t min_bytes, bool with_cuda, SrpcSharedMem* out) {
+  size_t page = (size_t)sysconf(_SC_PAGESIZE);
+  size_t bytes = (min_bytes + page - 1) / page * page;
+  int fd = memfd_create("splitrpc_shm", 0);
+  if (fd < 0) return false;
+  if (ftruncate(fd, (off_t)bytes) != 0 || !srpc_shm_map(fd, bytes, with_cuda, out)) {
+    close(fd);
+    return false;
+  }
+  return true;
+}
+// Takes ownership of fd on success.
+static inline bool srpc_shm_import(int fd, size_t bytes, bool with_cuda, SrpcSharedMem* out) {
+  return srpc_shm_map(fd, bytes, with_cuda, out);
+}
+static inline void srpc_shm_free(SrpcSharedMem* m) {
+  if (!m->host) return;
+  if (m->registered)
+    if (const SrpcDeviceOps* ops = srpc_cuda_ops()) ops->host_unregister(m->host);
+  munmap(m->host, m->bytes);
+  if (m->fd >= 0) close(m->fd);
+  *m = SrpcSharedMem{};
+}
+
+// What one process tells another about the rings of an app so that the other can produce into them: three file
+// descriptors (request ring, response ring, control block) and the geometry.  This is the NVLink-era form of the three
+// remotely writable memory regions {address, length, key} that the original's batched server registers and hands to
+// its SmartNIC proxy (reference src/splitrpc_rdma_transport/gpu_rdma_batched_server.cc:326-352).
+struct AppRrPoolExport {
+  int req_fd = -1, resp_fd = -1, ctl_fd = -1;
+  uint64_t req_capacity = 0, resp_capacity = 0, ctl_bytes = 0;
+  uint32_t pool_size = 0;
+  int32_t owner_device = -1;
+  uint64_t req_size = 0, resp_size = 0;
+};
+
+// Request ring, response ring and per-slot control words of one app.
 // On a GPU the rings are CUDA virtual-memory allocations mapped twice (and made
-// accessible to every peer GPU when `peer_access` is set); the state words live
-// in mapped pinned host memory so that the host can poll them and a GPU stream
-// (or a peer GPU) can wait on or write them.
+// accessible to every peer GPU when `peer_access` is set); the control block lives
+// in mapped pinned host memory so that the host can poll it and a GPU stream
+// (or a peer GPU) can wait on or write it.  The control block holds, per slot, the
+// 32-bit state word (the doorbell) and a 64-bit response destination: the offset
+// in the ingress transmit arena where the serving side stores the slot's response
+// (kNoTxOffset = the response stays in the response ring).
+// A pool is either the owner of its memory or a mirror of a pool that another
+// process owns (import constructor): the mirror maps the same rings and the same
+// control block, which is what lets a producer in another process fill slots and
+// ring doorbells without the owner's CPU.
 class P2pRpcAppRrMemPool {
   int device_id_;
   SrpcRingMem req_{}, resp_{};
+  SrpcSharedMem ctl_{};
   volatile uint32_t* h_doorbells_ = nullptr;
   volatile uint32_t* d_doorbells_ = nullptr;
+  volatile uint64_t* h_tx_off_ = nullptr;
+  volatile uint64_t* d_tx_off_ = nullptr;
   size_t n_doorbells_ = 0;
+  bool mirror_ = false;
+  bool ctl_plain_ = false;  // control block from host_alloc_mapped / posix_memalign instead of a memfd
+
+  static size_t ctl_layout(size_t n, size_t* tx_off_at) {
+    size_t a = (n * sizeof(uint32_t) + 63) / 64 * 64;
+    *tx_off_at = a;
+    return a + n * sizeof(uint64_t);
+  }
+  void bind_ctl(void* h, void* d) {
+    size_t at = 0;
+    ctl_layout(n_doorbells_, &at);
+    h_doorbells_ = (volatile uint32_t*)h;
+    d_doorbells_ = (volatile uint32_t*)d;
+    h_tx_off_ = (volatile uint64_t*)((uint8_t*)h + at);
+    d_tx_off_ = (volatile uint64_t*)((uint8_t*)d + at);
+  }
 
  public:
+  static constexpr uint64_t kNoTxOffset = ~0ull;
+
   P2pRpcAppRrMemPool(int pool_size, int device_id, size_t req_size, size_t resp_size, bool peer_access = true)
       : device_id_(device_id), n_doorbells_((size_t)pool_size) {
     size_t req_bytes = (size_t)pool_size * req_size, resp_bytes = (size_t)pool_size * resp_size;
+    size_t at = 0, ctl_bytes = ctl_layout(n_doorbells_, &at);
     if (device_id < 0) {
       if (!srpc_host_ring_alloc(req_bytes, &req_) || !srpc_host_ring_alloc(resp_bytes, &resp_)) {
         srpc_log(SRPC_LOG_ERROR, "host ring allocation failed (%zu + %zu bytes)", req_bytes, resp_bytes);
         std::abort();
       }
-      void* p = nullptr;
-      if (posix_memalign(&p, 64, n_doorbells_ * sizeof(uint32_t)) != 0) std::abort();
-      h_doorbells_ = d_doorbells_ = (volatile uint32_t*)p;
+      if (!srpc_shm_create(ctl_bytes, false, &ctl_)) std::abort();
     } else {
       const SrpcDeviceOps* ops = srpc_require_cuda("a GPU request ring");
       if (ops->ring_alloc(device_id, req_bytes, peer_access, &req_) != 0 ||
@@ -183,24 +308,92 @@ class P2pRpcAppRrMemPool {
         srpc_log(SRPC_LOG_ERROR, "GPU ring allocation failed: %s", ops->last_error());
         std::abort();
       }
-      void *h = nullptr, *d = nullptr;
-      if (ops->host_alloc_mapped(n_doorbells_ * sizeof(uint32_t), &h, &d) != 0) std::abort();
-      h_doorbells_ = (volatile uint32_t*)h;
-      d_doorbells_ = (volatile uint32_t*)d;
+      ops->set_device(device_id);
+      if (!srpc_shm_create(ctl_bytes, true, &ctl_)) {
+        // No memfd or no registration of foreign mappings: a private pinned block (the pool cannot be exported).
+        void *h = nullptr, *d = nullptr;
+        if (ops->host_alloc_mapped(ctl_bytes, &h, &d) != 0) std::abort();
+        ctl_.host = h;
+        ctl_.dev = d;
+        ctl_.bytes = ctl_bytes;
+        ctl_plain_ = true;
+      }
     }
-    for (size_t i = 0; i < n_doorbells_; i++) h_doorbells_[i] = APP_RR_STATUS::FREE;
+    bind_ctl(ctl_.host, ctl_.dev);
+    for (size_t i = 0; i < n_doorbells_; i++) {
+      h_doorbells_[i] = APP_RR_STATUS::FREE;
+      h_tx_off_[i] = kNoTxOffset;
+    }
   }
+
+  // Mirror of a pool owned by another process.  `device_id` is the device whose kernels will write the rings (the
+  // ingress GPU), or -1 when the CPU does.  Takes ownership of the descriptors in `ex`.
+  P2pRpcAppRrMemPool(const AppRrPoolExport& ex, int device_id) : device_id_(device_id), n_doorbells_(ex.pool_size), mirror_(true) {
+    bool ok;
+    if (ex.owner_device < 0) {
+      ok = srpc_host_ring_import(ex.req_fd, ex.req_capacity, &req_) && srpc_host_ring_import(ex.resp_fd, ex.resp_capacity, &resp_);
+    } else {
+      const SrpcDeviceOps* ops = srpc_require_cuda("importing a GPU request ring");
+      ok = device_id >= 0 && ops->ring_import(device_id, ex.req_fd, ex.req_capacity, &req_) == 0 &&
+           ops->ring_import(device_id, ex.resp_fd, ex.resp_capacity, &resp_) == 0;
+      if (!ok) srpc_log(SRPC_LOG_ERROR, "ring import failed: %s", ops->last_error());
+    }
+    if (ok && device_id >= 0) srpc_require_cuda("importing a control block")->set_device(device_id);
+    ok = ok && srpc_shm_import(ex.ctl_fd, ex.ctl_bytes, device_id >= 0, &ctl_);
+    if (!ok) {
+      srpc_log(SRPC_LOG_ERROR, "could not map the rings of a remote app");
+      n_doorbells_ = 0;
+      return;
+    }
+    bind_ctl(ctl_.host, ctl_.dev);
+  }
+
   ~P2pRpcAppRrMemPool() {
-    if (device_id_ < 0) {
+    const SrpcDeviceOps* ops = srpc_cuda_ops();
+    bool gpu_rings = mirror_ ? (req_.impl != nullptr) : device_id_ >= 0;
+    if (!gpu_rings) {
       srpc_host_ring_free(&req_);
       srpc_host_ring_free(&resp_);
-      free((void*)h_doorbells_);
-    } else if (const SrpcDeviceOps* ops = srpc_cuda_ops()) {
+    } else if (ops) {
       ops->ring_free(&req_);
       ops->ring_free(&resp_);
-      ops->host_free((void*)h_doorbells_);
+    }
+    if (ctl_plain_) {
+      if (ops) ops->host_free(ctl_.host);
+    } else {
+      srpc_shm_free(&ctl_);
     }
   }
+  P2pRpcAppRrMemPool(const P2pRpcAppRrMemPool&) = delete;
+
+  bool ok() const { return n_doorbells_ > 0 && req_.base && resp_.base; }
+  bool is_mirror() const { return mirror_; }
+  bool exportable() const { return !mirror_ && !ctl_plain_ && ctl_.fd >= 0; }
+  // Fills `ex` with freshly duplicated descriptors (the caller sends and closes them).  false when this pool cannot
+  // be shared (no memfd-backed control block, or the driver refused to export the rings).
+  bool export_to(AppRrPoolExport* ex, size_t req_size, size_t resp_size) const {
+    if (!exportable()) return false;
+    ex->ctl_fd = dup(ctl_.fd);
+    ex->ctl_bytes = ctl_.bytes;
+    if (device_id_ < 0) {
+      ex->req_fd = dup(req_.fd);
+      ex->resp_fd = dup(resp_.fd);
+    } else {
+      const SrpcDeviceOps* ops = srpc_require_cuda("ring export");
+      if (ops->ring_export(&req_, &ex->req_fd) != 0 || ops->ring_export(&resp_, &ex->resp_fd) != 0) {
+        srpc_log(SRPC_LOG_ERROR, "ring export failed: %s", ops->last_error());
+        return false;
+      }
+    }
+    ex->req_capacity = req_.capacity;
+    ex->resp_capacity = resp_.capacity;
+    ex->pool_size = (uint32_t)n_doorbells_;
+    ex->owner_device = device_id_;
+    ex->req_size = req_size;
+    ex->resp_size = resp_size;
+    return ex->ctl_fd >= 0 && ex->req_fd >= 0 && ex->resp_fd >= 0;
+  }
+
   void* get_req_addr_range() const { return req_.base; }
   void* get_resp_addr_range() const { return resp_.base; }
   size_t get_req_addr_pool_size() const { return req_.capacity; }
@@ -208,6 +401,8 @@ class P2pRpcAppRrMemPool {
   bool is_double_mapped() const { return req_.double_mapped && resp_.double_mapped; }
   volatile uint32_t* get_doorbells_host() const { return h_doorbells_; }
   volatile uint32_t* get_doorbells_device() const { return d_doorbells_; }
+  volatile uint64_t* get_tx_offsets_host() const { return h_tx_off_; }
+  volatile uint64_t* get_tx_offsets_device() const { return d_tx_off_; }
 };
 
 // ------------------------------------------------------------------ app slots
@@ -217,6 +412,7 @@ class P2pRpcAppRr {
   g_params* d_stub = nullptr;
   volatile uint32_t* h_state = nullptr;
   volatile uint32_t* d_state = nullptr;
+  volatile uint64_t* h_tx_off = nullptr;  // where the serving side stores this slot's response (offset in the transmit arena)
   size_t req_size = 0, resp_size = 0;
   void* rpc_rr = nullptr;  // transport-side record this slot currently serves
   int rr_idx = 0;
@@ -235,19 +431,35 @@ class P2pRpcAppRrPool {
   int device_id_;
   g_params* h_stubs_ = nullptr;
   g_params* d_stubs_ = nullptr;
-  P2pRpcTring *req_pool_, *resp_pool_;
+  P2pRpcTring *req_pool_ = nullptr, *resp_pool_ = nullptr;
   size_t pi_idx_ = 0;
   bool stubs_mapped_ = false;
 
  public:
   size_t req_size, resp_size;
-  P2pRpcAppRr* rr_pool;
-  P2pRpcAppRrMemPool* rr_mem_pool;
+  P2pRpcAppRr* rr_pool = nullptr;
+  P2pRpcAppRrMemPool* rr_mem_pool = nullptr;
 
   P2pRpcAppRrPool(int pool_size, int device_id, size_t _req_size, size_t _resp_size)
       : pool_size_(pool_size), device_id_(device_id), req_size(_req_size), resp_size(_resp_size) {
-    rr_pool = new P2pRpcAppRr[pool_size];
     rr_mem_pool = new P2pRpcAppRrMemPool(pool_size, device_id, req_size, resp_size);
+    bind();
+  }
+  // Producer-side mirror of a pool that another process owns: same slots, same ring arithmetic, the addresses are this
+  // process's mappings of the owner's rings (the original's SmartNIC-side pool mirrors the host's ring addresses the
+  // same way, reference src/splitrpc_rdma_transport/p2p_rpc_bf_rr_pool.h:13-60).
+  P2pRpcAppRrPool(const AppRrPoolExport& ex, int device_id)
+      : pool_size_((int)ex.pool_size), device_id_(device_id), req_size(ex.req_size), resp_size(ex.resp_size) {
+    rr_mem_pool = new P2pRpcAppRrMemPool(ex, device_id);
+    if (rr_mem_pool->ok()) bind();
+  }
+  bool ok() const { return rr_mem_pool && rr_mem_pool->ok() && rr_pool; }
+
+ private:
+  void bind() {
+    const int pool_size = pool_size_;
+    const int device_id = device_id_;
+    rr_pool = new P2pRpcAppRr[pool_size];
     req_pool_ = new P2pRpcTring(rr_mem_pool->get_req_addr_range(), rr_mem_pool->get_req_addr_pool_size());
     resp_pool_ = new P2pRpcTring(rr_mem_pool->get_resp_addr_range(), rr_mem_pool->get_resp_addr_pool_size());
     if (device_id >= 0) {
@@ -271,11 +483,14 @@ class P2pRpcAppRrPool {
       r.d_stub = &d_stubs_[i];
       r.h_state = &hs[i];
       r.d_state = &ds[i];
+      r.h_tx_off = &rr_mem_pool->get_tx_offsets_host()[i];
       r.h_stub->req = nullptr;
       r.h_stub->resp = nullptr;
       r.rr_idx = i;
     }
   }
+
+ public:
   ~P2pRpcAppRrPool() {
     delete req_pool_;
     delete resp_pool_;
