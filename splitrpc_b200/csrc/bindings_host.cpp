@@ -67,10 +67,32 @@ ArenaMem make_arena(const std::string& kind, size_t bytes) {
     m.host = (uint8_t*)h;
     m.dev = (uint8_t*)d;
     m.bytes = bytes;
+    m.gpu_visible = true;
     m.release = [ops, h] { ops->host_free(h); };
     return m;
   }
-  throw std::invalid_argument("arena kind must be 'malloc' or 'pinned'");
+  if (kind == "shm" || kind == "shm_pinned") {
+    // A memfd mapping that other processes can map too; "shm_pinned" also registers it with CUDA so that GPUs (of
+    // every process that registers its own mapping) can read and write it.
+    auto* sm = new SrpcSharedMem;
+    if (!srpc_shm_create(bytes, kind == "shm_pinned", sm)) {
+      delete sm;
+      throw std::runtime_error("shared arena: memfd mapping or CUDA registration failed");
+    }
+    std::memset(sm->host, 0, sm->bytes);
+    ArenaMem m;
+    m.host = (uint8_t*)sm->host;
+    m.dev = (uint8_t*)sm->dev;
+    m.bytes = bytes;
+    m.fd = sm->fd;
+    m.gpu_visible = sm->registered;
+    m.release = [sm] {
+      srpc_shm_free(sm);
+      delete sm;
+    };
+    return m;
+  }
+  throw std::invalid_argument("arena kind must be 'malloc', 'pinned', 'shm' or 'shm_pinned'");
 }
 
 // ---- apps
@@ -190,7 +212,14 @@ std::shared_ptr<AppHolder> make_graph_app(int device, size_t req_size, size_t re
 struct ServerHolder {
   PortHolder port;
   std::vector<std::shared_ptr<AppHolder>> apps;
+  std::vector<std::unique_ptr<NvlRemoteReplica>> remotes;  // outlive the server's threads (declared before `server`)
   std::unique_ptr<SplitRpcServer> server;
+};
+
+// A batched server and the app it serves.
+struct BatchedServerHolder {
+  std::shared_ptr<AppHolder> app;
+  std::unique_ptr<NvlBatchedServer> server;
 };
 
 struct ClientHolder {
@@ -489,6 +518,20 @@ PYBIND11_MODULE(_C, m) {
              srpc_graph_app_set(a.graph_internal, batch, exec);
            })
       .def("sync", [](AppHolder& a) { return a.info->app_ctx->WaitForAppRunComplete(); })
+      // Device address of the app's response-push block: kernels given it store responses where the ingress asked
+      // for them and complete the slots themselves once the server has enabled that (see RespPushCtx).
+      .def_property_readonly("d_push", [](AppHolder& a) { return (uintptr_t)a.info->app_ctx->d_push; })
+      // Tells the worker that the app's own kernels take d_push (no separate push kernel is queued behind them).
+      .def("set_self_push", [](AppHolder& a, bool on) { a.info->app_ctx->self_push = on; })
+      .def_property_readonly("completion_by_device", [](AppHolder& a) { return a.info->completion_by_device; })
+      // Writes the slot index of the batch's first request into the push block (stand-alone timing loops; the server's
+      // workers do this themselves).
+      .def("set_first_slot", [](AppHolder& a, uint32_t slot) {
+        a.info->app_ctx->h_push->first_slot = slot;
+        std::atomic_thread_fence(std::memory_order_seq_cst);
+      })
+      .def_property_readonly("pool_size", [](AppHolder& a) { return a.info->app_rr_pool->get_pool_size(); })
+      .def_property_readonly("exportable", [](AppHolder& a) { return a.info->app_rr_pool->rr_mem_pool->exportable(); })
       // Points the app's stub at explicit addresses (default: the start of both rings),
       // e.g. before a warm-up run or a stand-alone timing loop.
       .def("set_stub",
@@ -561,7 +604,7 @@ PYBIND11_MODULE(_C, m) {
   py::class_<ServerHolder, std::shared_ptr<ServerHolder>>(m, "Server")
       .def(py::init([](PortHolder port, const std::string& uri, size_t req_size, size_t resp_size, int server_mode,
                        int max_batch, int zerocopy, int rr_pool_size, uint64_t reassembly_timeout_ns, int steer_policy,
-                       int gather_burst) {
+                       int gather_burst, int device_completion) {
              auto h = std::make_shared<ServerHolder>();
              ServerConfig c;
              if (!uri.empty()) c.server_uri = uri;
@@ -574,17 +617,60 @@ PYBIND11_MODULE(_C, m) {
              c.reassembly_timeout_ns = reassembly_timeout_ns;
              c.steer_policy = steer_policy;
              c.gather_burst = gather_burst;
+             c.device_completion = device_completion;
              h->port = port;
              h->server.reset(new SplitRpcServer(port.port, c));
              return h;
            }),
            py::arg("port"), py::arg("uri") = "", py::arg("req_size") = 1024, py::arg("resp_size") = 1024,
            py::arg("server_mode") = 2, py::arg("max_batch") = 1, py::arg("zerocopy") = 0, py::arg("rr_pool_size") = 1023,
-           py::arg("reassembly_timeout_ns") = 200000000ull, py::arg("steer_policy") = 0, py::arg("gather_burst") = 64)
+           py::arg("reassembly_timeout_ns") = 200000000ull, py::arg("steer_policy") = 0, py::arg("gather_burst") = 64,
+           py::arg("device_completion") = 1)
       .def("add_replica",
            [](ServerHolder& s, std::shared_ptr<AppHolder> app) {
              s.apps.push_back(app);
              return s.server->add_replica(app->info.get(), app->engine.get());
+           })
+      // Adds a replica served by a BatchedServer in another process (usually another GPU): connects to its control
+      // socket, performs the ALLOC handshake (this server's transmit arena travels with it when it is a shared
+      // mapping), maps the replica's rings and doorbells, and creates the engine that fills them from
+      // `ingress_device` (-1: CPU engine, rings in host memory only).
+      .def("add_remote_replica",
+           [](ServerHolder& s, const std::string& path, uint32_t func_id, int ingress_device, int copy_type, int timeout_ms) {
+             std::string err;
+             std::unique_ptr<NvlRemoteReplica> r;
+             {
+               py::gil_scoped_release rel;
+               r = NvlRemoteReplica::connect(path, func_id, ingress_device, copy_type, s.server->tx_arena(), timeout_ms, &err);
+             }
+             if (!r) throw std::runtime_error("add_remote_replica: " + err);
+             int idx = s.server->add_remote_replica(r.get());
+             s.remotes.push_back(std::move(r));
+             return idx;
+           },
+           py::arg("path"), py::arg("func_id") = 1234, py::arg("ingress_device") = -1, py::arg("copy_type") = 2,
+           py::arg("timeout_ms") = 10000)
+      .def("remote_info",
+           [](ServerHolder& s, int remote_idx) {
+             const buf_mon_rr& i = s.remotes.at((size_t)remote_idx)->info();
+             py::dict d;
+             d["queue_size"] = i.queue_size;
+             d["req_size"] = i.req_size;
+             d["resp_size"] = i.resp_size;
+             d["device_id"] = i.device_id;
+             d["server_mode"] = i.server_mode;
+             d["max_batch"] = i.max_batch;
+             d["device_completes"] = i.device_completes;
+             d["transform_kind"] = i.transform.kind;
+             return d;
+           })
+      // Sends RELEASE to every remote replica (their servers stop their workers and listen again).
+      .def("release_remotes",
+           [](ServerHolder& s) {
+             py::gil_scoped_release rel;
+             int ok = 0;
+             for (auto& r : s.remotes) ok += r->release() ? 1 : 0;
+             return ok;
            })
       .def("start", [](ServerHolder& s) { s.server->start(); })
       .def("stop", [](ServerHolder& s) {
@@ -605,12 +691,14 @@ PYBIND11_MODULE(_C, m) {
              d["ring_full"] = st.ring_full;
              d["tx_alloc_fail"] = st.tx_alloc_fail;
              d["sg_errors"] = st.sg_errors;
+             d["replicas_lost"] = st.replicas_lost;
              py::list reps;
              for (auto& r : st.replicas) {
                py::dict rd;
                rd["steered"] = r.steered;
                rd["completed"] = r.completed;
                rd["ring_full"] = r.ring_full;
+               rd["pushed"] = r.pushed;
                reps.append(rd);
              }
              d["replicas"] = reps;
@@ -618,6 +706,50 @@ PYBIND11_MODULE(_C, m) {
            })
       .def("worker_stats", [](ServerHolder& s, int replica) {
         WorkerStats w = s.server->worker_stats(replica);
+        py::dict d;
+        d["num_req"] = w.num_req;
+        d["num_batches"] = w.num_batches;
+        d["wait_timeouts"] = w.wait_timeouts;
+        d["batch_hist"] = w.batch_hist;
+        d["work_ns"] = w.work_ns;
+        return d;
+      });
+
+  // ---- batched server: serves one app to a producer in another process (see nvl_batched_server.h)
+  py::class_<BatchedServerHolder, std::shared_ptr<BatchedServerHolder>>(m, "BatchedServer")
+      .def(py::init([](std::shared_ptr<AppHolder> app, const std::string& path, uint32_t func_id, int server_mode, int max_batch) {
+             auto h = std::make_shared<BatchedServerHolder>();
+             if (!app->info->app_rr_pool->rr_mem_pool->exportable())
+               throw std::runtime_error("BatchedServer: this app's rings cannot be shared with another process");
+             h->app = app;
+             h->server.reset(new NvlBatchedServer(app->info.get(), path, func_id, server_mode, max_batch));
+             return h;
+           }),
+           py::arg("app"), py::arg("path"), py::arg("func_id") = 1234, py::arg("server_mode") = 2, py::arg("max_batch") = 1)
+      .def("set_ingress_stem_s2d",
+           [](BatchedServerHolder& b, std::vector<float> mean, std::vector<float> inv_std) {
+             if (mean.size() != 3 || inv_std.size() != 3) throw std::invalid_argument("mean / inv_std need 3 values");
+             float p[6] = {mean[0], mean[1], mean[2], inv_std[0], inv_std[1], inv_std[2]};
+             b.server->set_ingress_transform(SG_TRANSFORM_STEM_S2D, p);
+           })
+      .def("start", [](BatchedServerHolder& b) {
+        if (!b.server->start()) throw std::runtime_error("BatchedServer: cannot listen on the control socket path");
+      })
+      .def("stop", [](BatchedServerHolder& b) {
+        py::gil_scoped_release rel;
+        b.server->stop();
+      })
+      .def_property_readonly("serving", [](BatchedServerHolder& b) { return b.server->serving(); })
+      .def("counters", [](BatchedServerHolder& b) {
+        py::dict d;
+        d["allocs"] = b.server->counters.allocs.load();
+        d["releases"] = b.server->counters.releases.load();
+        d["peers_lost"] = b.server->counters.peers_lost.load();
+        d["refused"] = b.server->counters.refused.load();
+        return d;
+      })
+      .def("worker_stats", [](BatchedServerHolder& b) {
+        WorkerStats w = b.server->worker_stats();
         py::dict d;
         d["num_req"] = w.num_req;
         d["num_batches"] = w.num_batches;

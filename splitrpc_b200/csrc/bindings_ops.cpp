@@ -249,15 +249,15 @@ void bind_ops(py::module_& m) {
   });
   m.def("softmax_response",
         [](uintptr_t logits, int rows, int n, int ld, uintptr_t d_stub, uintptr_t direct_out, size_t resp_stride,
-           bool write_argmax, uintptr_t counter, uintptr_t flag, uint32_t flag_value, uintptr_t stream) {
+           bool write_argmax, uintptr_t counter, uintptr_t flag, uint32_t flag_value, uintptr_t stream, uintptr_t d_push) {
           check(nn_softmax_response((const float*)logits, rows, n, ld, (const void*)d_stub, (void*)direct_out, resp_stride,
                                     write_argmax ? 1 : 0, (uint32_t*)counter, (uint32_t*)flag, flag_value,
-                                    (cudaStream_t)stream),
+                                    (cudaStream_t)stream, (const void*)d_push),
                 "softmax_response");
         },
         py::arg("logits"), py::arg("rows"), py::arg("n"), py::arg("ld"), py::arg("d_stub") = 0, py::arg("direct_out") = 0,
         py::arg("resp_stride") = 0, py::arg("write_argmax") = false, py::arg("counter") = 0, py::arg("flag") = 0,
-        py::arg("flag_value") = 0, py::arg("stream") = 0);
+        py::arg("flag_value") = 0, py::arg("stream") = 0, py::arg("d_push") = 0);
   m.def("layernorm",
         [](uintptr_t x, uintptr_t residual, uintptr_t gamma, uintptr_t beta, uintptr_t y, int rows, int hidden, float eps,
            uintptr_t stream) {

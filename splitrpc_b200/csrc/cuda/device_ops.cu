@@ -19,6 +19,7 @@
 
 #include "../host/p2p_rpc_app.h"
 #include "driver_api.h"
+#include "sg_kernels.cuh"
 
 static thread_local std::string g_last_error;
 
@@ -153,7 +154,7 @@ static int d_event_destroy(cudaEvent_t e) {
   return 0;
 }
 
-static int d_ring_alloc(int dev, size_t min_bytes, bool peer_access, SrpcRingMem* out) {
+static int d_ring_alloc(int dev, size_t min_bytes, size_t slot_bytes, bool peer_access, SrpcRingMem* out) {
   RT(cudaSetDevice(dev));
   RT(cudaFree(0));  // make sure the primary context exists before driver calls
   const SrpcDriverApi* d = srpc_driver_api();
@@ -165,8 +166,7 @@ static int d_ring_alloc(int dev, size_t min_bytes, bool peer_access, SrpcRingMem
     prop.location.id = dev;
     size_t gran = 0;
     DRV(d->MemGetAllocationGranularity(&gran, &prop, CU_MEM_ALLOC_GRANULARITY_MINIMUM));
-    size_t cap = (min_bytes + gran - 1) / gran * gran;
-    if (cap == 0) cap = gran;
+    size_t cap = srpc_ring_capacity(min_bytes, slot_bytes, gran);
     // Ask for an allocation that can be handed to another process as a file descriptor; fall back to a private one.
     prop.requestedHandleTypes = CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR;
     impl->shareable = true;
@@ -301,6 +301,10 @@ static int d_graph_launch(cudaGraphExec_t g, cudaStream_t s) {
   RT(cudaGraphLaunch(g, s));
   return 0;
 }
+static int d_resp_push(const void* d_stub, const void* d_push, int n, cudaStream_t s) {
+  RT(sg_launch_resp_push(d_stub, d_push, n, s));
+  return 0;
+}
 static const char* d_last_error() { return g_last_error.c_str(); }
 
 extern "C" const SrpcDeviceOps* srpc_cuda_ops() {
@@ -308,7 +312,7 @@ extern "C" const SrpcDeviceOps* srpc_cuda_ops() {
       d_device_count, d_set_device,  d_stream_create, d_stream_destroy,    d_stream_sync, d_stream_query, d_wait32,
       d_write32,      d_event_create, d_event_destroy, d_ring_alloc,        d_ring_free,   d_host_alloc_mapped,
       d_host_free,    d_dev_alloc,    d_dev_free,      d_memcpy_async,      d_memset_async, d_graph_launch, d_last_error,
-      d_ring_export,  d_ring_import,  d_host_register, d_host_unregister};
+      d_ring_export,  d_ring_import,  d_host_register, d_host_unregister,   d_resp_push};
   return &ops;
 }
 

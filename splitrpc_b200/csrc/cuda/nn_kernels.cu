@@ -12,6 +12,7 @@
 #include "../host/p2p_rpc_app.h"
 #include "nn_kernels.h"
 #include "ptx.cuh"
+#include "resp_push.cuh"
 
 namespace {
 
@@ -294,15 +295,22 @@ __global__ void __launch_bounds__(256, 2) fc_skinny(const __nv_bfloat16* __restr
 // argmax class as int32.  When `flag` is set, the block that finishes last
 // publishes `flag_value` with a system-scope release store: the response is in
 // place (possibly in a peer GPU's or the host's memory) before the flag is seen.
+// With a response-push block (`push`, see resp_push.cuh) each row goes straight to
+// the place the producer named for its slot (the ingress transmit arena, in another
+// process's pinned memory or on a peer GPU) and the row's block completes the slot.
 __global__ void __launch_bounds__(256) softmax_response(const float* __restrict__ logits, int n, int ld, const g_params* stub,
                                                         uint8_t* direct_out, size_t resp_stride, int write_argmax,
-                                                        uint32_t* counter, volatile uint32_t* flag, uint32_t flag_value) {
+                                                        uint32_t* counter, volatile uint32_t* flag, uint32_t flag_value,
+                                                        const RespPushCtx* push) {
   __shared__ float sh[32];
   __shared__ float s_max, s_sum;
   __shared__ int s_arg;
   const int row = blockIdx.x;
   const float* x = logits + (size_t)row * ld;
   uint8_t* base = (direct_out ? direct_out : stub->resp) + (size_t)row * resp_stride;
+  RespPushTarget target{base, nullptr};
+  if (!direct_out) target = resp_push_target(push, (uint32_t)row, base);
+  base = target.dst;
   float m = -FLT_MAX;
   int am = 0;
   for (int i = threadIdx.x; i < n; i += blockDim.x)
@@ -344,6 +352,10 @@ __global__ void __launch_bounds__(256) softmax_response(const float* __restrict_
   float* o = reinterpret_cast<float*>(base);
   for (int i = threadIdx.x; i < n; i += blockDim.x) o[i] = __expf(x[i] - mx) * inv;
   if (write_argmax && threadIdx.x == 0) reinterpret_cast<int*>(base)[n] = s_arg;
+  if (target.state) {
+    __syncthreads();
+    if (threadIdx.x == 0) resp_push_complete(target);
+  }
   if (flag) {
     __threadfence_system();
     __syncthreads();
@@ -591,10 +603,10 @@ cudaError_t nn_fc_skinny(const void* a, int lda, const void* w, int ldw, const f
 }
 cudaError_t nn_softmax_response(const float* logits, int rows, int n, int ld, const void* d_stub, void* direct_out,
                                 size_t resp_stride, int write_argmax, uint32_t* counter, uint32_t* flag, uint32_t flag_value,
-                                cudaStream_t s) {
+                                cudaStream_t s, const void* d_push) {
   if (rows <= 0) return cudaSuccess;
   softmax_response<<<rows, 256, 0, s>>>(logits, n, ld, (const g_params*)d_stub, (uint8_t*)direct_out, resp_stride,
-                                        write_argmax, counter, flag, flag_value);
+                                        write_argmax, counter, flag, flag_value, (const RespPushCtx*)d_push);
   return cudaGetLastError();
 }
 cudaError_t nn_layernorm(const void* x, const void* residual, const float* gamma, const float* beta, void* y, int rows,

@@ -20,7 +20,7 @@ cudaError_t nn_fc_skinny(const void* a, int lda, const void* w, int ldw, const f
                          cudaStream_t s);
 cudaError_t nn_softmax_response(const float* logits, int rows, int n, int ld, const void* d_stub, void* direct_out,
                                 size_t resp_stride, int write_argmax, uint32_t* counter, uint32_t* flag, uint32_t flag_value,
-                                cudaStream_t s);
+                                cudaStream_t s, const void* d_push = nullptr);
 cudaError_t nn_layernorm(const void* x, const void* residual, const float* gamma, const float* beta, void* y, int rows,
                          int hidden, float eps, cudaStream_t s);
 cudaError_t nn_bert_embed_ln(const void* d_stub, const int* direct_ids, size_t req_stride, int batch, int seq, const void* word,

@@ -1,0 +1,35 @@
+// Device side of "the serving GPU answers by itself": where a response goes and how its slot is completed.
+//
+// A kernel that produces the response of request `row` of the running batch asks resp_push_target() for the
+// destination (the producer's transmit arena when the producer named an offset for the slot, otherwise the response
+// ring) and, after all its stores, has ONE thread call resp_push_complete(), which publishes WORK_COMPLETE in the
+// slot's state word with a system-scope release store.  The arena may be pinned host memory of another process or a
+// peer GPU's memory; the fence before the store makes the bytes visible there before the state is.
+// In the original this hand-off takes a host thread, a SEND_WITH_IMM and an RDMA READ per response (reference
+// src/splitrpc_rdma_transport/gpu_rdma_batched_server.cc:441-458, gpu_dpdk_rdma_proxy_handler.cc:249-296).
+#pragma once
+
+#include "../host/p2p_rpc_app.h"
+#include "ptx.cuh"
+
+struct RespPushTarget {
+  uint8_t* dst;
+  volatile uint32_t* state;  // nullptr: completion is left to the host
+};
+
+__device__ __forceinline__ RespPushTarget resp_push_target(const RespPushCtx* ctx, uint32_t row, uint8_t* ring_dst) {
+  RespPushTarget t{ring_dst, nullptr};
+  if (!ctx || ctx->enabled == 0 || ctx->pool_size == 0) return t;
+  const uint32_t slot = (ctx->first_slot + row) % ctx->pool_size;
+  const uint64_t off = ctx->tx_off[slot];
+  if (ctx->tx_base && off != ~0ull && off + ctx->resp_size <= ctx->tx_bytes) t.dst = reinterpret_cast<uint8_t*>(ctx->tx_base + off);
+  t.state = ctx->states + slot;
+  return t;
+}
+
+// Call from one thread, after a __syncthreads() that follows every store of the response by the block.
+__device__ __forceinline__ void resp_push_complete(const RespPushTarget& t) {
+  if (!t.state) return;
+  __threadfence_system();
+  ptx::st_release_sys(t.state, (uint32_t)APP_RR_STATUS::WORK_COMPLETE);
+}

@@ -43,8 +43,26 @@ class P2pRpcSgGpuEngine : public P2pRpcSgEngine {
     return r > 0 ? -r : 48;
   }
   cudaStream_t stream_ = nullptr;
-  SgItem* h_items_ = nullptr;  // pinned staging of the copy list
-  SgItem* d_items_ = nullptr;
+
+  // Submission slots.  A synchronous call uses slot 0 and waits; calls that finish by themselves (gather_batch_notify)
+  // rotate through all of them, so the host builds list k+1 while the kernel of list k still runs.  Per slot: the copy
+  // list and the doorbell addresses in pinned host memory, their device copies, and the arrival counter of the launch.
+  static constexpr int kSlots = 4;
+  static constexpr uint32_t kMaxBells = 1024;
+  struct Slot {
+    SgItem* h_items = nullptr;
+    uint64_t* h_bells = nullptr;
+    SgItem* d_items = nullptr;
+    uint64_t* d_bells = nullptr;
+    uint32_t* d_counter = nullptr;
+    uint32_t ticket = 0;  // last submission that used this slot
+  } slots_[kSlots];
+  SgItem* h_items_ = nullptr;  // = slots_[cur_].h_items while a list is being built
+  int cur_ = 0;
+  volatile uint32_t* h_done_ = nullptr;  // mapped: sequence number of the newest finished asynchronous submission
+  uint32_t* d_done_ = nullptr;
+  uint32_t ticket_ = 0;
+
   SgCtrl* h_ctrl_ = nullptr;   // persistent mode control block (mapped)
   SgCtrl* d_ctrl_ = nullptr;
   uint32_t* d_counter_ = nullptr;
@@ -53,23 +71,33 @@ class P2pRpcSgGpuEngine : public P2pRpcSgEngine {
   int persistent_blocks_ = 16;
   uint64_t wait_budget_ns_ = 2000000000ull;
 
-  bool ensure_resident() {
-    if (resident_ && h_ctrl_->exited == 0) return true;
-    if (resident_) {
-      // Some blocks have left after their idle limit; wait for the rest, then re-arm.
-      uint64_t t0 = getCurNs();
-      while (h_ctrl_->exited < (uint32_t)persistent_blocks_) {
-        if (getCurNs() - t0 > wait_budget_ns_) return false;
-        std::this_thread::yield();
-      }
-      cudaStreamSynchronize(stream_);
+  // ---- resident kernel (copy type 1)
+  // Stops the resident kernel: asks every block to leave, waits (bounded) until all have, and only then lets the
+  // stream drain.  The doorbell is never moved backwards; a sequence number that was rung but not served stays
+  // consumed, and the list is submitted again under a new one.
+  bool stop_resident() {
+    if (!resident_) return true;
+    __atomic_store_n(&h_ctrl_->exit_flag, 1u, __ATOMIC_RELEASE);
+    uint64_t t0 = getCurNs();
+    while (__atomic_load_n(&h_ctrl_->exited, __ATOMIC_ACQUIRE) < (uint32_t)persistent_blocks_) {
+      if (getCurNs() - t0 > wait_budget_ns_) return false;
+      std::this_thread::yield();
     }
+    cudaStreamSynchronize(stream_);
+    resident_ = false;
+    return true;
+  }
+
+  bool ensure_resident() {
+    if (resident_ && __atomic_load_n(&h_ctrl_->exited, __ATOMIC_ACQUIRE) == 0) return true;
+    if (!stop_resident()) return false;  // some blocks have left after their idle limit: collect the rest, then re-arm
     h_ctrl_->exited = 0;
     h_ctrl_->exit_flag = 0;
     h_ctrl_->error = 0;
     h_ctrl_->done = seq_;
     h_ctrl_->doorbell = seq_;
     std::atomic_thread_fence(std::memory_order_seq_cst);
+    // every block has left: the arrival counter of a half-served submission can be cleared safely
     cudaMemsetAsync(d_counter_, 0, sizeof(uint32_t), stream_);
     if (sg_launch_persistent(d_ctrl_, d_counter_, persistent_blocks_, stream_) != cudaSuccess) return false;
     resident_ = true;
@@ -79,35 +107,41 @@ class P2pRpcSgGpuEngine : public P2pRpcSgEngine {
   int submit_persistent(const SgItem* items, uint32_t n) {
     for (uint32_t off = 0; off < n; off += SG_PERSISTENT_ITEMS) {
       uint32_t m = n - off < SG_PERSISTENT_ITEMS ? n - off : SG_PERSISTENT_ITEMS;
-      for (int attempt = 0; attempt < 2; attempt++) {
+      bool served = false;
+      for (int attempt = 0; attempt < 2 && !served; attempt++) {
         if (!ensure_resident()) return -2;
         SgItem* dst = const_cast<SgItem*>(h_ctrl_->items);
         std::memcpy(dst, items + off, m * sizeof(SgItem));
         h_ctrl_->n_items = m;
         h_ctrl_->n_chunks = sg_assign_chunks(dst, m);
         std::atomic_thread_fence(std::memory_order_release);
-        uint32_t s = seq_ + 1;
+        const uint32_t s = ++seq_;
         __atomic_store_n(&h_ctrl_->doorbell, s, __ATOMIC_RELEASE);
         uint64_t t0 = getCurNs();
-        bool done = false, gone = false;
-        while (!(done = (__atomic_load_n(&h_ctrl_->done, __ATOMIC_ACQUIRE) == s))) {
-          if (h_ctrl_->exited != 0) {
+        bool gone = false;
+        for (;;) {
+          if (__atomic_load_n(&h_ctrl_->done, __ATOMIC_ACQUIRE) == s) {
+            served = true;
+            break;
+          }
+          if (__atomic_load_n(&h_ctrl_->exited, __ATOMIC_ACQUIRE) != 0) {
             gone = true;
             break;
           }
           if (getCurNs() - t0 > wait_budget_ns_) break;
         }
-        if (done) {
-          seq_ = s;
-          break;
-        }
-        // The kernel left between the residency check and the doorbell (or the
-        // wait ran out): take the doorbell back and try once more on a fresh launch.
-        __atomic_store_n(&h_ctrl_->doorbell, seq_, __ATOMIC_RELEASE);
-        if (!gone || attempt == 1) {
+        if (served) break;
+        // Blocks left between the residency check and the doorbell (idle limit), or the wait ran out.  Either way the
+        // kernel is stopped completely before anything else happens; the copies it may have made are idempotent.
+        if (!stop_resident()) return -2;
+        if (!gone) {
           counters.timeouts++;
           return -1;
         }
+      }
+      if (!served) {
+        counters.timeouts++;
+        return -1;
       }
     }
     return 0;
@@ -117,31 +151,48 @@ class P2pRpcSgGpuEngine : public P2pRpcSgEngine {
   bool has_transform_ = false;
   SgStemS2d transform_{};
 
-  int submit(uint32_t n, bool gather = false) {
-    if (n == 0) return 0;
+  static bool reached(uint32_t done, uint32_t ticket) { return (int32_t)(done - ticket) >= 0; }
+
+  // Makes slot `k` safe to overwrite: the asynchronous submission that used it last has finished.
+  bool wait_slot_free(int k) {
+    const uint32_t t = slots_[k].ticket;
+    if (t == 0) return true;
+    uint64_t t0 = getCurNs();
+    while (!reached(__atomic_load_n(h_done_, __ATOMIC_ACQUIRE), t)) {
+      if (getCurNs() - t0 > wait_budget_ns_) return false;
+    }
+    return true;
+  }
+  bool begin_list() {
+    if (!wait_slot_free(cur_)) return false;
+    h_items_ = slots_[cur_].h_items;
+    return true;
+  }
+
+  // Launches the list built in the current slot.  notify == nullptr: waits for it (synchronous calls).
+  int submit(uint32_t n, bool gather, const SgNotify* notify) {
+    if (n == 0 && !notify) return 0;
+    Slot& sl = slots_[cur_];
     counters.items += n;
     for (uint32_t i = 0; i < n; i++) counters.bytes += h_items_[i].len;
     cudaError_t e = cudaSuccess;
-    switch (copy_type_) {
-      case 0:
-        for (uint32_t i = 0; i < n && e == cudaSuccess; i++)
-          e = cudaMemcpyAsync((void*)h_items_[i].dst, (const void*)h_items_[i].src, h_items_[i].len, cudaMemcpyDefault,
-                              stream_);
-        if (e == cudaSuccess) e = cudaStreamSynchronize(stream_);
-        break;
-      case 1:
-        return submit_persistent(h_items_, n);
-      default: {
-        uint32_t chunks = sg_assign_chunks(h_items_, n);
-        e = cudaMemcpyAsync(d_items_, h_items_, n * sizeof(SgItem), cudaMemcpyHostToDevice, stream_);
-        if (e == cudaSuccess) {
-          if (gather && has_transform_)
-            e = sg_launch_stem_s2d(d_items_, n, chunks, transform_, blocks_for(h_items_[0]), stream_);
-          else
-            e = sg_launch_copy(d_items_, n, chunks, copy_type_ == 3 ? SG_IMPL_BULK : SG_IMPL_SIMT, blocks_for(h_items_[0]), stream_);
-        }
-        if (e == cudaSuccess) e = cudaStreamSynchronize(stream_);
+    if (copy_type_ == 0 && !notify) {
+      for (uint32_t i = 0; i < n && e == cudaSuccess; i++)
+        e = cudaMemcpyAsync((void*)h_items_[i].dst, (const void*)h_items_[i].src, h_items_[i].len, cudaMemcpyDefault, stream_);
+      if (e == cudaSuccess) e = cudaStreamSynchronize(stream_);
+    } else if (copy_type_ == 1 && !notify) {
+      return submit_persistent(h_items_, n);
+    } else {
+      uint32_t chunks = sg_assign_chunks(h_items_, n);
+      e = cudaMemcpyAsync(sl.d_items, h_items_, n * sizeof(SgItem), cudaMemcpyHostToDevice, stream_);
+      if (e == cudaSuccess) {
+        const int impl = (copy_type_ == 3 && !notify) ? SG_IMPL_BULK : SG_IMPL_SIMT;
+        if (gather && has_transform_)
+          e = sg_launch_stem_s2d(sl.d_items, n, chunks, transform_, blocks_for(h_items_[0]), stream_, notify);
+        else
+          e = sg_launch_copy(sl.d_items, n, chunks, impl, blocks_for(h_items_[0]), stream_, notify);
       }
+      if (e == cudaSuccess && !notify) e = cudaStreamSynchronize(stream_);
     }
     if (e != cudaSuccess) {
       srpc_log(SRPC_LOG_ERROR, "GPU scatter-gather failed: %s", cudaGetErrorString(e));
@@ -168,8 +219,20 @@ class P2pRpcSgGpuEngine : public P2pRpcSgEngine {
     device_id = dev;
     cudaSetDevice(dev);
     cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking);
-    cudaHostAlloc(&h_items_, sizeof(SgItem) * SG_MAX_ITEMS, cudaHostAllocDefault);
-    cudaMalloc(&d_items_, sizeof(SgItem) * SG_MAX_ITEMS);
+    for (Slot& sl : slots_) {
+      cudaHostAlloc(&sl.h_items, sizeof(SgItem) * SG_MAX_ITEMS, cudaHostAllocDefault);
+      cudaHostAlloc(&sl.h_bells, sizeof(uint64_t) * kMaxBells, cudaHostAllocDefault);
+      cudaMalloc(&sl.d_items, sizeof(SgItem) * SG_MAX_ITEMS);
+      cudaMalloc(&sl.d_bells, sizeof(uint64_t) * kMaxBells);
+      cudaMalloc(&sl.d_counter, sizeof(uint32_t));
+      cudaMemset(sl.d_counter, 0, sizeof(uint32_t));
+    }
+    h_items_ = slots_[0].h_items;
+    void* h = nullptr;
+    cudaHostAlloc(&h, 64, cudaHostAllocMapped | cudaHostAllocPortable);
+    std::memset(h, 0, 64);
+    h_done_ = (volatile uint32_t*)h;
+    cudaHostGetDevicePointer((void**)&d_done_, h, 0);
     if (copy_type_ == 1) {
       cudaHostAlloc(&h_ctrl_, sizeof(SgCtrl), cudaHostAllocMapped | cudaHostAllocPortable);
       std::memset(h_ctrl_, 0, sizeof(SgCtrl));
@@ -181,14 +244,18 @@ class P2pRpcSgGpuEngine : public P2pRpcSgEngine {
   }
   ~P2pRpcSgGpuEngine() override {
     cudaSetDevice(device_id);
-    if (resident_) {
-      __atomic_store_n(&h_ctrl_->exit_flag, 1u, __ATOMIC_RELEASE);
-      cudaStreamSynchronize(stream_);
-    }
+    stop_resident();
+    cudaStreamSynchronize(stream_);
     if (h_ctrl_) cudaFreeHost(h_ctrl_);
     if (d_counter_) cudaFree(d_counter_);
-    cudaFree(d_items_);
-    cudaFreeHost(h_items_);
+    for (Slot& sl : slots_) {
+      cudaFree(sl.d_items);
+      cudaFree(sl.d_bells);
+      cudaFree(sl.d_counter);
+      cudaFreeHost(sl.h_items);
+      cudaFreeHost(sl.h_bells);
+    }
+    cudaFreeHost((void*)h_done_);
     cudaStreamDestroy(stream_);
   }
 
@@ -200,46 +267,104 @@ class P2pRpcSgGpuEngine : public P2pRpcSgEngine {
   int gather_batch(P2pRpcRr** rrs, g_params** stubs, int n) override {
     PROF_START(Gather);
     cudaSetDevice(device_id);
+    if (!begin_list()) return -1;
     uint32_t ni = 0;
     int rc = 0;
     for (int i = 0; i < n; i++) {
       gather_skbs(rrs[i]->payload_sk_bufs, rrs[i]->payload_bufs, stubs[i]->req);
       if (!append(rrs[i]->payload_sk_bufs, &ni)) {
-        rc |= submit(ni, true);
+        rc |= submit(ni, true, nullptr);
         ni = 0;
         append(rrs[i]->payload_sk_bufs, &ni);
       }
     }
-    rc |= submit(ni, true);
+    rc |= submit(ni, true, nullptr);
     counters.gathers += (uint64_t)n;
     PROF_STOP(Gather);
     return rc;
   }
 
+  // Gather that finishes by itself: one launch (per SG_MAX_ITEMS items) whose last block stores `state_value` into the
+  // d_states words and then publishes the ticket.  Nothing here waits for the GPU, except for a submission slot to
+  // come free when kSlots submissions are already in flight.
+  int64_t gather_batch_notify(P2pRpcRr** rrs, g_params** stubs, volatile uint32_t** h_states, volatile uint32_t** d_states,
+                              int n, uint32_t state_value) override {
+    (void)h_states;
+    if (n <= 0 || (uint32_t)n > kMaxBells) return -4;
+    PROF_START(Gather);
+    cudaSetDevice(device_id);
+    int rc = 0;
+    int first = 0;
+    uint32_t ticket = 0;
+    while (first < n && rc == 0) {
+      cur_ = (cur_ + 1) % kSlots;
+      if (!begin_list()) {
+        counters.timeouts++;
+        return -1;
+      }
+      Slot& sl = slots_[cur_];
+      uint32_t ni = 0;
+      int i = first;
+      for (; i < n; i++) {
+        gather_skbs(rrs[i]->payload_sk_bufs, rrs[i]->payload_bufs, stubs[i]->req);
+        const uint32_t before = ni;
+        if (!append(rrs[i]->payload_sk_bufs, &ni)) {
+          ni = before;  // this request goes into the next launch
+          if (i == first) return -4;  // a single request with more runs than a launch can hold
+          break;
+        }
+        sl.h_bells[i - first] = (uint64_t)(uintptr_t)d_states[i];
+      }
+      const uint32_t nb = (uint32_t)(i - first);
+      ticket = ++ticket_;
+      if (ticket == 0) ticket = ++ticket_;  // 0 means "slot never used"
+      sl.ticket = ticket;
+      cudaError_t e = cudaMemcpyAsync(sl.d_bells, sl.h_bells, nb * sizeof(uint64_t), cudaMemcpyHostToDevice, stream_);
+      if (e != cudaSuccess) return -3;
+      SgNotify nt;
+      nt.counter = sl.d_counter;
+      nt.bells = sl.d_bells;
+      nt.n_bells = nb;
+      nt.bell_value = state_value;
+      nt.done_word = d_done_;
+      nt.done_value = ticket;
+      rc = submit(ni, true, &nt);
+      first = i;
+    }
+    counters.gathers += (uint64_t)n;
+    PROF_STOP(Gather);
+    return rc == 0 ? (int64_t)ticket : (int64_t)rc;
+  }
+  bool ticket_done(int64_t ticket) override {
+    return ticket <= 0 || reached(__atomic_load_n(h_done_, __ATOMIC_ACQUIRE), (uint32_t)ticket);
+  }
+
   int scatter_batch(P2pRpcRr** rrs, g_params** stubs, int n) override {
     PROF_START(Scatter);
     cudaSetDevice(device_id);
+    if (!begin_list()) return -1;
     uint32_t ni = 0;
     int rc = 0;
     for (int i = 0; i < n; i++) {
       if (rrs[i]->payload_bufs->num_items == 0) continue;
       scatter_skbs(rrs[i]->payload_sk_bufs, rrs[i]->payload_bufs, stubs[i]->resp);
       if (!append(rrs[i]->payload_sk_bufs, &ni)) {
-        rc |= submit(ni);
+        rc |= submit(ni, false, nullptr);
         ni = 0;
         append(rrs[i]->payload_sk_bufs, &ni);
       }
     }
-    rc |= submit(ni);
+    rc |= submit(ni, false, nullptr);
     counters.scatters += (uint64_t)n;
     PROF_STOP(Scatter);
     return rc;
   }
   int copy_list(const p2p_sk_buf* skb) override {
     cudaSetDevice(device_id);
+    if (!begin_list()) return -1;
     uint32_t ni = 0;
     if (!append(skb, &ni)) return -4;
-    return submit(ni);
+    return submit(ni, false, nullptr);
   }
   int set_gather_transform(int kind, uint64_t ring_base, uint32_t slot_bytes, const float* params) override {
     if (kind == 0) {

@@ -13,7 +13,10 @@
 //                    it back with a system-scope release store)
 // All waits are bounded; a wait that runs out sets an error word and the kernel
 // returns after draining its own outstanding copies.
+#include <mutex>
+
 #include "ptx.cuh"
+#include "resp_push.cuh"
 #include "sg_kernels.cuh"
 
 namespace {
@@ -80,16 +83,54 @@ __device__ __forceinline__ void copy_chunk_simt(const uint8_t* src, uint8_t* dst
   }
 }
 
+// Epilogue shared by the copy kernels: see SgNotify.  Every thread fences its own stores at system scope before the
+// block arrives; the block that arrives last has therefore seen (through the counter) that all bytes of the launch are
+// visible to the peer GPU or the host, and only then rings the bells.
+__device__ __forceinline__ void sg_notify_epilogue(const SgNotify& nt) {
+  if (!nt.counter) return;
+  __shared__ uint32_t s_last;
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const uint32_t prev = atomicAdd(nt.counter, 1u);
+    s_last = (prev + 1 == gridDim.x) ? 1u : 0u;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  if (threadIdx.x == 0) atomicExch(nt.counter, 0u);
+  __threadfence_system();
+  for (uint32_t i = threadIdx.x; i < nt.n_bells; i += blockDim.x)
+    ptx::st_release_sys(reinterpret_cast<volatile uint32_t*>(nt.bells[i]), nt.bell_value);
+  __syncthreads();
+  if (threadIdx.x == 0 && nt.done_word) {
+    __threadfence_system();
+    ptx::st_release_sys(nt.done_word, nt.done_value);
+  }
+}
+
 // Groups of 256 threads take chunks in turn.  Launched with 256 threads per block (many blocks: device and peer
 // sources) or with 1024 (four groups per block: a few "fat" blocks reach the PCIe rate for host sources and occupy
 // only as many SMs).
-__global__ void __launch_bounds__(1024) sg_copy_simt(const SgItem* __restrict__ items, uint32_t n_items, uint32_t n_chunks) {
+__global__ void __launch_bounds__(1024) sg_copy_simt(const SgItem* __restrict__ items, uint32_t n_items, uint32_t n_chunks,
+                                                     SgNotify notify) {
   const uint32_t groups = blockDim.x >> 8;
   const uint32_t g = blockIdx.x * groups + (threadIdx.x >> 8), ng = gridDim.x * groups;
   for (uint32_t c = g; c < n_chunks; c += ng) {
     ChunkRef r = chunk_ref(items, n_items, c);
     copy_chunk_simt(r.src, r.dst, r.len, threadIdx.x & 255u, 256u);
   }
+  sg_notify_epilogue(notify);
+}
+
+// One block per response of the batch: copy it from the response ring to where the producer wants it (when that is
+// somewhere else) and complete the slot.
+__global__ void __launch_bounds__(256) resp_push_kernel(const g_params* __restrict__ stub, const RespPushCtx* __restrict__ ctx) {
+  const uint32_t row = blockIdx.x;
+  uint8_t* src = stub->resp + (size_t)row * ctx->resp_size;
+  const RespPushTarget t = resp_push_target(ctx, row, src);
+  if (t.dst != src) copy_chunk_simt(src, t.dst, ctx->resp_size, threadIdx.x, blockDim.x);
+  __syncthreads();
+  if (threadIdx.x == 0) resp_push_complete(t);
 }
 
 __device__ __forceinline__ bool bulk_ok(const ChunkRef& r) {
@@ -205,7 +246,7 @@ __global__ void __launch_bounds__(256) sg_cast_bf16(const SgItem* __restrict__ i
 // less than the 602,112-byte request it replaces); border pixels and padding channels are never written and keep
 // the zeros the ring was created with.
 __global__ void __launch_bounds__(1024) sg_stem_s2d(const SgItem* __restrict__ items, uint32_t n_items, uint32_t n_chunks,
-                                                    SgStemS2d tr) {
+                                                    SgStemS2d tr, SgNotify notify) {
   const uint32_t groups = blockDim.x >> 8;
   const uint32_t g = blockIdx.x * groups + (threadIdx.x >> 8), ng = gridDim.x * groups;
   const uint32_t t = threadIdx.x & 255u;
@@ -259,14 +300,16 @@ __global__ void __launch_bounds__(1024) sg_stem_s2d(const SgItem* __restrict__ i
       for (uint32_t j = t; j < n; j += 256) put(e0 + j, reinterpret_cast<const float*>(src)[j]);
     }
   }
+  sg_notify_epilogue(notify);
 }
 
-// Resident engine.  Each block polls the doorbell; a new sequence number means
-// the item list is valid.  Blocks never wait for one another: each finishes its
-// share, and the block that brings the arrival counter to gridDim.x * seq
-// publishes `done`.
+// Resident engine.  Each block polls the control block; a doorbell ahead of the block's own sequence number (compared
+// as a signed difference, so a block can never mistake an older or equal value for new work) means the item list is
+// valid.  The exit flag and the idle limit are looked at on every poll, before the doorbell, so a block always leaves
+// within one poll of being asked to, whatever the doorbell says.  Blocks never wait for one another: each finishes its
+// share, and the block that brings the arrival counter to gridDim.x publishes `done`.
 __global__ void __launch_bounds__(256) sg_persistent(SgCtrl* ctrl, uint32_t* counter) {
-  __shared__ uint32_t s_cmd;
+  __shared__ uint32_t s_cmd, s_seq;
   __shared__ SgItem s_items[SG_PERSISTENT_ITEMS];
   uint32_t seen = ctrl->done;  // submissions up to `done` were served by an earlier launch
   uint64_t last = ptx::globaltimer_ns();
@@ -275,13 +318,14 @@ __global__ void __launch_bounds__(256) sg_persistent(SgCtrl* ctrl, uint32_t* cou
     if (threadIdx.x == 0) {
       uint32_t cmd = 0;  // 0 keep polling, 1 work, 2 leave
       for (int spin = 0; spin < 4096; spin++) {
-        uint32_t db = ptx::ld_acquire_sys(&ctrl->doorbell);
-        if (db != seen) {
-          cmd = 1;
-          break;
-        }
         if (ptx::ld_relaxed_sys(&ctrl->exit_flag) || ptx::globaltimer_ns() - last > idle_limit) {
           cmd = 2;
+          break;
+        }
+        const uint32_t db = ptx::ld_acquire_sys(&ctrl->doorbell);
+        if ((int32_t)(db - seen) > 0) {
+          s_seq = db;
+          cmd = 1;
           break;
         }
         __nanosleep(200);
@@ -289,11 +333,11 @@ __global__ void __launch_bounds__(256) sg_persistent(SgCtrl* ctrl, uint32_t* cou
       s_cmd = cmd;
     }
     __syncthreads();
-    uint32_t cmd = s_cmd;
+    const uint32_t cmd = s_cmd, seq = s_seq;
     __syncthreads();
     if (cmd == 2) break;
     if (cmd == 0) continue;
-    seen++;
+    seen = seq;
     uint32_t n_items = ctrl->n_items, n_chunks = ctrl->n_chunks;
     if (n_items > SG_PERSISTENT_ITEMS) n_items = SG_PERSISTENT_ITEMS;
     // One pass over PCIe brings the list into shared memory; lookups stay on chip.
@@ -332,17 +376,26 @@ template <typename K>
 static void prefer_max_shared(K kernel) {
   cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
 }
-static void sg_kernel_setup() {
-  static bool done = false;
-  if (done) return;
-  static const int on = [] { const char* e = getenv("P2P_RPC_SG_MAX_SHARED"); return e ? atoi(e) : 1; }();
-  if (on) {
-    prefer_max_shared(sg_copy_simt);
-    prefer_max_shared(sg_cast_bf16);
-    prefer_max_shared(sg_persistent);
-  }
-  (void)cudaGetLastError();
-  done = true;
+// Function attributes belong to a device: the set-up runs once per device (the engines of a multi-GPU server live in
+// one process and launch from several threads).  Returns the error of the shared-memory opt-in of the bulk kernel.
+static constexpr int kMaxDevices = 64;
+static cudaError_t sg_kernel_setup() {
+  static std::once_flag once[kMaxDevices];
+  static cudaError_t result[kMaxDevices];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+  std::call_once(once[dev], [dev] {
+    static const int on = [] { const char* e = getenv("P2P_RPC_SG_MAX_SHARED"); return e ? atoi(e) : 1; }();
+    if (on) {
+      prefer_max_shared(sg_copy_simt);
+      prefer_max_shared(sg_cast_bf16);
+      prefer_max_shared(sg_persistent);
+      prefer_max_shared(sg_stem_s2d);
+    }
+    (void)cudaGetLastError();
+    result[dev] = cudaFuncSetAttribute(sg_copy_bulk, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)((size_t)BULK_STAGES * SG_CHUNK));
+  });
+  return result[dev];
 }
 
 static int clamp_blocks(int n_blocks, uint32_t n_chunks) {
@@ -352,25 +405,28 @@ static int clamp_blocks(int n_blocks, uint32_t n_chunks) {
 }
 
 cudaError_t sg_launch_copy(const SgItem* d_items, uint32_t n_items, uint32_t n_chunks, int impl, int n_blocks,
-                           cudaStream_t stream) {
+                           cudaStream_t stream, const SgNotify* notify) {
   if (n_items == 0 || n_chunks == 0) return cudaSuccess;
-  sg_kernel_setup();
+  const cudaError_t bulk_attr = sg_kernel_setup();
+  const SgNotify nt = notify ? *notify : SgNotify{};
+  if (impl == SG_IMPL_BULK && nt.counter) return cudaErrorNotSupported;  // the bulk pipeline has no doorbell epilogue
   if (impl == SG_IMPL_BULK) {
-    static bool attr_set = false;
+    if (bulk_attr != cudaSuccess) return bulk_attr;
     size_t smem = (size_t)BULK_STAGES * SG_CHUNK;
-    if (!attr_set) {
-      cudaError_t e = cudaFuncSetAttribute(sg_copy_bulk, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-      if (e != cudaSuccess) return e;
-      attr_set = true;
-    }
     int nb = clamp_blocks(n_blocks > 0 ? n_blocks : 148, n_chunks);
     sg_copy_bulk<<<nb, BULK_THREADS, smem, stream>>>(d_items, n_items, n_chunks, nullptr);
   } else if (n_blocks < 0) {  // -n "fat" blocks of 1024 threads
     const uint32_t want = (uint32_t)(-n_blocks), most = (n_chunks + 3) / 4;
-    sg_copy_simt<<<want < most ? want : most, 1024, 0, stream>>>(d_items, n_items, n_chunks);
+    sg_copy_simt<<<want < most ? want : most, 1024, 0, stream>>>(d_items, n_items, n_chunks, nt);
   } else {
-    sg_copy_simt<<<clamp_blocks(n_blocks, n_chunks), 256, 0, stream>>>(d_items, n_items, n_chunks);
+    sg_copy_simt<<<clamp_blocks(n_blocks, n_chunks), 256, 0, stream>>>(d_items, n_items, n_chunks, nt);
   }
+  return cudaGetLastError();
+}
+
+cudaError_t sg_launch_resp_push(const void* d_stub, const void* d_push, int n, cudaStream_t stream) {
+  if (n <= 0) return cudaSuccess;
+  resp_push_kernel<<<n, 256, 0, stream>>>((const g_params*)d_stub, (const RespPushCtx*)d_push);
   return cudaGetLastError();
 }
 
@@ -383,20 +439,16 @@ cudaError_t sg_launch_cast_bf16(const SgItem* d_items, uint32_t n_items, uint32_
 }
 
 cudaError_t sg_launch_stem_s2d(const SgItem* d_items, uint32_t n_items, uint32_t n_chunks, const SgStemS2d& tr, int n_blocks,
-                               cudaStream_t stream) {
+                               cudaStream_t stream, const SgNotify* notify) {
   if (n_items == 0 || n_chunks == 0) return cudaSuccess;
   if (!tr.ring_base || !tr.slot_bytes || (tr.slot_bytes & 15u)) return cudaErrorInvalidValue;
-  static bool setup = false;
-  if (!setup) {
-    prefer_max_shared(sg_stem_s2d);
-    (void)cudaGetLastError();
-    setup = true;
-  }
+  const SgNotify nt = notify ? *notify : SgNotify{};
+  sg_kernel_setup();
   if (n_blocks < 0) {
     const uint32_t want = (uint32_t)(-n_blocks), most = (n_chunks + 3) / 4;
-    sg_stem_s2d<<<want < most ? want : most, 1024, 0, stream>>>(d_items, n_items, n_chunks, tr);
+    sg_stem_s2d<<<want < most ? want : most, 1024, 0, stream>>>(d_items, n_items, n_chunks, tr, nt);
   } else {
-    sg_stem_s2d<<<clamp_blocks(n_blocks, n_chunks), 256, 0, stream>>>(d_items, n_items, n_chunks, tr);
+    sg_stem_s2d<<<clamp_blocks(n_blocks, n_chunks), 256, 0, stream>>>(d_items, n_items, n_chunks, tr, nt);
   }
   return cudaGetLastError();
 }

@@ -37,9 +37,28 @@ struct SgCtrl {
 
 enum SgImpl { SG_IMPL_SIMT = 0, SG_IMPL_BULK = 1 };
 
+// Optional epilogue of a copy launch: when the last block has finished (arrival counter), it stores `bell_value` into
+// each of the n_bells 32-bit words whose addresses are listed in `bells`, then `done_value` into `done_word`, all with
+// system-scope release stores that follow a system-scope fence.  The words may live in mapped host memory or in
+// another GPU's memory: this is how a gather rings the doorbells of the slots it filled (payload first, doorbell
+// second, the order the original gets from chaining an RDMA WRITE of the payload with one of the doorbell, reference
+// src/splitrpc_rdma_transport/p2p_rpc_bf_rr_pool.h:107-152) without a host thread in between.  counter == nullptr: no
+// epilogue.  The counter must be zero at launch; the last block leaves it at zero.
+struct SgNotify {
+  uint32_t* counter = nullptr;
+  const uint64_t* bells = nullptr;  // device-readable list of addresses
+  uint32_t n_bells = 0;
+  uint32_t bell_value = 0;
+  uint32_t* done_word = nullptr;
+  uint32_t done_value = 0;
+};
+
 // One launch over a copy list that the device can read (device or mapped memory).
 cudaError_t sg_launch_copy(const SgItem* d_items, uint32_t n_items, uint32_t n_chunks, int impl, int n_blocks,
-                           cudaStream_t stream);
+                           cudaStream_t stream, const SgNotify* notify = nullptr);
+// Stores the responses of a batch where the producer asked for them and completes their slots (see resp_push.cuh):
+// one block per response.  d_stub / d_push are the device views of the app's stub and RespPushCtx.
+cudaError_t sg_launch_resp_push(const void* d_stub, const void* d_push, int n, cudaStream_t stream);
 // fp32 -> bf16 gather: every item copies len/4 floats to len/4 bf16 values,
 // computing (x - shift) * scale on the way.
 cudaError_t sg_launch_cast_bf16(const SgItem* d_items, uint32_t n_items, uint32_t n_chunks, float scale, float shift,
@@ -53,7 +72,7 @@ struct SgStemS2d {
   float inv_std[3];
 };
 cudaError_t sg_launch_stem_s2d(const SgItem* d_items, uint32_t n_items, uint32_t n_chunks, const SgStemS2d& tr, int n_blocks,
-                               cudaStream_t stream);
+                               cudaStream_t stream, const SgNotify* notify = nullptr);
 // Persistent engine: `counter` is a zero-initialised device word.
 cudaError_t sg_launch_persistent(SgCtrl* d_ctrl, uint32_t* d_counter, int n_blocks, cudaStream_t stream);
 

@@ -50,6 +50,25 @@ static constexpr uint32_t APP_DOORBELL_EXIT = 3u;       // asks a resident kerne
 
 enum APP_RR_STATUS : uint32_t { FREE = 0, RX_COMPLETE = 1, WORK_COMPLETE = 2, TX_COMPLETE = 3 };
 
+// What the serving side needs to answer a slot by itself: for the batch whose first slot is `first_slot`, request r
+// belongs to slot (first_slot + r) % pool_size; its response goes to tx_base + tx_off[slot] (unless tx_off is
+// kNoTxOffset: then it stays in the response ring) and states[slot] becomes WORK_COMPLETE with a system-scope release
+// store once the bytes are written.  The block sits in memory that kernels read when they run (mapped pinned memory),
+// so graphs captured before the transmit arena is known pick the values up later.  enabled == 0: kernels leave
+// completion to the host.  This replaces the original's "host sends SEND_WITH_IMM(slot), proxy RDMA-READs the
+// response" exchange (reference src/splitrpc_rdma_transport/gpu_rdma_batched_server.cc:441-458) by stores from the
+// GPU that computed the response.
+struct RespPushCtx {
+  uint64_t tx_base;                 // device-side address of the ingress transmit arena in the serving process
+  uint64_t tx_bytes;
+  const volatile uint64_t* tx_off;  // per slot, device view
+  volatile uint32_t* states;        // per slot, device view
+  uint32_t pool_size;
+  uint32_t resp_size;
+  uint32_t enabled;
+  uint32_t first_slot;              // written by the worker with the stub, before every run
+};
+
 // ------------------------------------------------------------------ tring
 // Bump-pointer address generator over a ring-shaped address range (reference
 // src/p2p_rpc_tring.h:10-34): get_next(n) returns the current address and
@@ -103,7 +122,9 @@ struct SrpcDeviceOps {
   int (*stream_write_value32)(cudaStream_t s, volatile uint32_t* d_addr, uint32_t value);
   int (*event_create)(cudaEvent_t* e);
   int (*event_destroy)(cudaEvent_t e);
-  int (*ring_alloc)(int dev, size_t min_bytes, bool peer_access, SrpcRingMem* out);
+  // Capacity = min_bytes rounded up to a multiple of both the allocation granularity and slot_bytes, so that the
+  // ring's address generator wraps on a slot boundary and every slot starts at a multiple of slot_bytes.
+  int (*ring_alloc)(int dev, size_t min_bytes, size_t slot_bytes, bool peer_access, SrpcRingMem* out);
   int (*ring_free)(SrpcRingMem* m);
   int (*host_alloc_mapped)(size_t bytes, void** host_ptr, void** dev_ptr);
   int (*host_free)(void* host_ptr);
@@ -121,6 +142,9 @@ struct SrpcDeviceOps {
   int (*ring_import)(int dev, int fd, size_t capacity, SrpcRingMem* out);
   int (*host_register)(void* p, size_t bytes, void** dptr);
   int (*host_unregister)(void* p);
+  // Queues, on `s`, the kernel that stores the `n` responses of the window at *d_stub where *d_push says and marks
+  // their slots WORK_COMPLETE (see RespPushCtx).
+  int (*resp_push)(const void* d_stub, const void* d_push, int n, cudaStream_t s);
 };
 
 // Implemented by the CUDA half; returns nullptr when the library was built
@@ -140,9 +164,19 @@ static inline const SrpcDeviceOps* srpc_require_cuda(const char* what) {
 static inline size_t find_lcm(size_t a, size_t b) { return a / std::gcd(a, b) * b; }
 
 // Host ring mapped twice back to back with memfd + MAP_FIXED.
-static inline bool srpc_host_ring_alloc(size_t min_bytes, SrpcRingMem* out) {
+// Ring capacity: min_bytes rounded up to a multiple of lcm(granularity, slot_bytes).  A ring that wrapped in the
+// middle of a slot would still give contiguous windows (double mapping), but slots would stop being aligned to
+// slot_bytes after the first lap, and kernels that address the ring by slot index would read the wrong bytes.
+static inline size_t srpc_ring_capacity(size_t min_bytes, size_t slot_bytes, size_t gran) {
+  size_t unit = slot_bytes ? find_lcm(gran, slot_bytes) : gran;
+  if (unit > ((size_t)4 << 30)) unit = gran;  // pathological slot size: keep the plain rounding
+  size_t cap = (min_bytes + unit - 1) / unit * unit;
+  return cap ? cap : unit;
+}
+
+static inline bool srpc_host_ring_alloc(size_t min_bytes, size_t slot_bytes, SrpcRingMem* out) {
   size_t page = (size_t)sysconf(_SC_PAGESIZE);
-  size_t cap = (min_bytes + page - 1) / page * page;
+  size_t cap = srpc_ring_capacity(min_bytes, slot_bytes, page);
   int fd = memfd_create("splitrpc_ring", 0);
   if (fd < 0) return false;
   if (ftruncate(fd, (off_t)cap) != 0) {
@@ -296,15 +330,15 @@ class P2pRpcAppRrMemPool {
     size_t req_bytes = (size_t)pool_size * req_size, resp_bytes = (size_t)pool_size * resp_size;
     size_t at = 0, ctl_bytes = ctl_layout(n_doorbells_, &at);
     if (device_id < 0) {
-      if (!srpc_host_ring_alloc(req_bytes, &req_) || !srpc_host_ring_alloc(resp_bytes, &resp_)) {
+      if (!srpc_host_ring_alloc(req_bytes, req_size, &req_) || !srpc_host_ring_alloc(resp_bytes, resp_size, &resp_)) {
         srpc_log(SRPC_LOG_ERROR, "host ring allocation failed (%zu + %zu bytes)", req_bytes, resp_bytes);
         std::abort();
       }
       if (!srpc_shm_create(ctl_bytes, false, &ctl_)) std::abort();
     } else {
       const SrpcDeviceOps* ops = srpc_require_cuda("a GPU request ring");
-      if (ops->ring_alloc(device_id, req_bytes, peer_access, &req_) != 0 ||
-          ops->ring_alloc(device_id, resp_bytes, peer_access, &resp_) != 0) {
+      if (ops->ring_alloc(device_id, req_bytes, req_size, peer_access, &req_) != 0 ||
+          ops->ring_alloc(device_id, resp_bytes, resp_size, peer_access, &resp_) != 0) {
         srpc_log(SRPC_LOG_ERROR, "GPU ring allocation failed: %s", ops->last_error());
         std::abort();
       }
@@ -559,6 +593,9 @@ class MetaAppCtx {
   cudaGraphExec_t instance = nullptr;
   uint64_t wait_budget_ns = 2000000000ull;  // bound on every host-side spin
   int last_status = 0;                      // 0 ok, -1 a bounded wait ran out
+  RespPushCtx* h_push = nullptr;            // response-push block (host view / device view), see RespPushCtx
+  RespPushCtx* d_push = nullptr;
+  bool self_push = false;                   // the app's own kernels store responses and completions (fused epilogue)
 
   // Makes the work stream wait until *d_state == value.
   void AppRrRunNotify(volatile uint32_t* d_state, int value) {

@@ -40,7 +40,14 @@ class P2pRpcAppInfo {
   uint32_t* door_bells = nullptr;
   uint32_t* d_door_bells = nullptr;
   bool init_ok = false;
-  uint64_t consumer_seq = 0;  // slots consumed by the stream-armed worker since the pool was initialised
+  uint64_t consumer_seq = 0;  // slots consumed by the worker since the pool was initialised
+  // The slots are filled by a producer that does not bind them through this pool's get_next() (another process that
+  // mirrors the rings): window addresses then come from the ring arithmetic, not from the slots' stubs.
+  bool use_window_stub = false;
+  // The serving side stores every response where the producer asked for it and marks the slot WORK_COMPLETE itself
+  // (from the app's last kernel, a push kernel behind it, or the CPU app's thread); the worker loops then leave the
+  // slot states alone.  See RespPushCtx.
+  bool completion_by_device = false;
 
   // `internal` is stored in app_ctx->app_ctx_internal before app_init runs, so a
   // callback set can be shared by several instances with different state.
@@ -68,18 +75,24 @@ class P2pRpcAppInfo {
       ops->event_create(&app_ctx->work_complete);
       // One allocation holds the stub and the doorbell; both are read by kernels
       // (indirect stub, persistent doorbell) and written by the host.
+      // One allocation: stub at 0, doorbell at 128, response-push block at 256.
       void *h = nullptr, *d = nullptr;
-      ops->host_alloc_mapped(256, &h, &d);
+      ops->host_alloc_mapped(512, &h, &d);
       h_stubs = (g_params*)h;
       d_stubs = (g_params*)d;
       door_bells = (uint32_t*)((uint8_t*)h + 128);
       d_door_bells = (uint32_t*)((uint8_t*)d + 128);
+      app_ctx->h_push = (RespPushCtx*)((uint8_t*)h + 256);
+      app_ctx->d_push = (RespPushCtx*)((uint8_t*)d + 256);
     } else {
       void* p = nullptr;
-      if (posix_memalign(&p, 64, 256) != 0) std::abort();
+      if (posix_memalign(&p, 64, 512) != 0) std::abort();
+      std::memset(p, 0, 512);
       h_stubs = d_stubs = (g_params*)p;
       door_bells = d_door_bells = (uint32_t*)((uint8_t*)p + 128);
+      app_ctx->h_push = app_ctx->d_push = (RespPushCtx*)((uint8_t*)p + 256);
     }
+    std::memset(app_ctx->h_push, 0, sizeof(RespPushCtx));
     app_ctx->h_stub = h_stubs;
     app_ctx->d_stub = d_stubs;
     app_ctx->door_bell = door_bells;
@@ -107,6 +120,52 @@ class P2pRpcAppInfo {
     delete app_rr_pool;
   }
   P2pRpcAppInfo(const P2pRpcAppInfo&) = delete;
+
+  // Turns on completion by the serving side.  tx_base / tx_bytes describe the producer's transmit arena as THIS
+  // process addresses it from the app's device (a device-side address on a GPU, a host address on the CPU device);
+  // tx_base == 0 keeps responses in the response ring and only moves the state store to the serving side.
+  void enable_device_completion(uint64_t tx_base, uint64_t tx_bytes) {
+    RespPushCtx* p = app_ctx->h_push;
+    P2pRpcAppRrMemPool* mp = app_rr_pool->rr_mem_pool;
+    p->tx_base = tx_base;
+    p->tx_bytes = tx_base ? tx_bytes : 0;
+    p->tx_off = mp->get_tx_offsets_device();
+    p->states = mp->get_doorbells_device();
+    p->pool_size = (uint32_t)rr_pool_size;
+    p->resp_size = (uint32_t)resp_size;
+    p->first_slot = 0;
+    std::atomic_thread_fence(std::memory_order_release);
+    p->enabled = 1;
+    std::atomic_thread_fence(std::memory_order_seq_cst);
+    completion_by_device = true;
+  }
+  void disable_device_completion() {
+    completion_by_device = false;
+    app_ctx->h_push->enabled = 0;
+    std::atomic_thread_fence(std::memory_order_seq_cst);
+  }
+
+  // Stores the responses of the batch that just ran (app_ctx->curr_batch_size requests from slot h_push->first_slot on)
+  // and completes their slots, unless the app's own kernels do that.  On a GPU this queues one kernel behind the app
+  // on the work stream; on the CPU device it copies here.
+  void push_responses() {
+    if (!completion_by_device || app_ctx->self_push) return;
+    RespPushCtx* p = app_ctx->h_push;
+    const int n = app_ctx->curr_batch_size;
+    if (device_id >= 0) {
+      const SrpcDeviceOps* ops = srpc_require_cuda("response push");
+      if (ops->resp_push(app_ctx->d_stub, app_ctx->d_push, n, app_ctx->work_stream) != 0)
+        srpc_log(SRPC_LOG_ERROR, "response push failed: %s", ops->last_error());
+      return;
+    }
+    for (int r = 0; r < n; r++) {
+      uint32_t slot = (p->first_slot + (uint32_t)r) % p->pool_size;
+      uint64_t off = p->tx_off[slot];
+      if (p->tx_base && off != P2pRpcAppRrMemPool::kNoTxOffset && off + p->resp_size <= p->tx_bytes)
+        std::memcpy((void*)(uintptr_t)(p->tx_base + off), app_ctx->h_stub->resp + (size_t)r * p->resp_size, p->resp_size);
+      __atomic_store_n(&p->states[slot], (uint32_t)APP_RR_STATUS::WORK_COMPLETE, __ATOMIC_RELEASE);
+    }
+  }
 };
 
 struct WorkerStats {
@@ -174,9 +233,12 @@ class P2pRpcAsyncAppServer {
   // Points the app's stub at slot rr_idx and starts the app; does not wait.
   void do_work(int appIdx, int rr_idx) {
     P2pRpcAppInfo* a = all_apps[appIdx];
-    *a->app_ctx->h_stub = *a->app_rr_pool->get_app_rr(rr_idx)->h_stub;
+    *a->app_ctx->h_stub = a->use_window_stub ? a->app_rr_pool->window_stub(a->consumer_seq)
+                                             : *a->app_rr_pool->get_app_rr(rr_idx)->h_stub;
+    a->app_ctx->h_push->first_slot = (uint32_t)rr_idx;
     std::atomic_thread_fence(std::memory_order_release);
     a->app_run(a->app_ctx);
+    a->push_responses();
   }
   bool do_sync(int appIdx) {
     P2pRpcAppInfo* a = all_apps[appIdx];
@@ -200,6 +262,7 @@ class P2pRpcAsyncAppServer {
     P2pRpcAppRrPool* pool = a->app_rr_pool;
     const int n = a->rr_pool_size;
     int ci = 0, si = 0, win = 0;
+    a->consumer_seq = 0;
     IdleBackoff backoff;
     while (!should_stop()) {
       if (load_state(pool->get_app_rr(ci)->h_state) != APP_RR_STATUS::RX_COMPLETE) {
@@ -211,13 +274,15 @@ class P2pRpcAsyncAppServer {
       if (++win < a->app_ctx->curr_batch_size) continue;
       uint64_t t0 = getCurNs();
       bool ok = do_work_sync(appIdx, si);
-      for (int i = si; i != ci; i = (i + 1) % n) store_state(pool->get_app_rr(i)->h_state, APP_RR_STATUS::WORK_COMPLETE);
+      if (!a->completion_by_device)
+        for (int i = si; i != ci; i = (i + 1) % n) store_state(pool->get_app_rr(i)->h_state, APP_RR_STATUS::WORK_COMPLETE);
       {
         std::lock_guard<std::mutex> g(stats_mu_);
         note_batch(appIdx, win, getCurNs() - t0);
         if (!ok) stats_[appIdx].wait_timeouts++;
       }
       num_req.fetch_add((uint64_t)win);
+      a->consumer_seq += (uint64_t)win;
       si = ci;
       win = 0;
       update_batch_size(appIdx);
@@ -229,6 +294,7 @@ class P2pRpcAsyncAppServer {
     P2pRpcAppRrPool* pool = a->app_rr_pool;
     const int n = a->rr_pool_size;
     int ci = 0, si = 0, win = 0;
+    a->consumer_seq = 0;
     IdleBackoff backoff;
     while (!should_stop()) {
       while (win < max_batch_size && load_state(pool->get_app_rr(ci)->h_state) == APP_RR_STATUS::RX_COMPLETE) {
@@ -242,13 +308,15 @@ class P2pRpcAsyncAppServer {
       backoff.busy();
       uint64_t t0 = getCurNs();
       bool ok = do_batch_work_sync(appIdx, si, win);
-      for (int i = si; i != ci; i = (i + 1) % n) store_state(pool->get_app_rr(i)->h_state, APP_RR_STATUS::WORK_COMPLETE);
+      if (!a->completion_by_device)
+        for (int i = si; i != ci; i = (i + 1) % n) store_state(pool->get_app_rr(i)->h_state, APP_RR_STATUS::WORK_COMPLETE);
       {
         std::lock_guard<std::mutex> g(stats_mu_);
         note_batch(appIdx, win, getCurNs() - t0);
         if (!ok) stats_[appIdx].wait_timeouts++;
       }
       num_req.fetch_add((uint64_t)win);
+      a->consumer_seq += (uint64_t)win;
       win = 0;
       si = ci;
     }
@@ -264,10 +332,13 @@ class P2pRpcAsyncAppServer {
     // The window may not have been bound by its producer yet: take its addresses
     // from the ring arithmetic, not from the slot.
     *c->h_stub = a->app_rr_pool->window_stub(a->consumer_seq);
-    (void)start_rr_idx;
+    c->h_push->first_slot = (uint32_t)start_rr_idx;
     std::atomic_thread_fence(std::memory_order_seq_cst);
     c->AppRrRunNotify(a->app_rr_pool->get_app_rr(last_rr_idx)->d_state, APP_RR_STATUS::RX_COMPLETE);
-    if (c->last_status == 0 || c->device_id >= 0) a->app_run(c);
+    if (c->last_status == 0 || c->device_id >= 0) {
+      a->app_run(c);
+      a->push_responses();
+    }
     c->AppCompleteNotify(1U);
   }
 
@@ -302,7 +373,7 @@ class P2pRpcAsyncAppServer {
       backoff.busy();
       int bs = c->curr_batch_size;
       for (int i = 0; i < bs; i++) {
-        store_state(pool->get_app_rr(ci)->h_state, APP_RR_STATUS::WORK_COMPLETE);
+        if (!a->completion_by_device) store_state(pool->get_app_rr(ci)->h_state, APP_RR_STATUS::WORK_COMPLETE);
         ci = (ci + 1) % n;
       }
       {

@@ -114,6 +114,7 @@ class P2pRpcSgEngine {
   int device_id = -1;
   uint16_t app_queue_length = 0;
   SgCounters counters;
+  int64_t sync_ticket_ = 0;
   PROF_DECL(Gather);
   PROF_DECL(Scatter);
 
@@ -144,6 +145,23 @@ class P2pRpcSgEngine {
     int rc = 0;
     for (int i = 0; i < n; i++) rc |= scatter(rrs[i], stubs[i]);
     return rc;
+  }
+  // Gather that completes the slots by itself: once every byte of the n requests is in place, `state_value` is stored
+  // (release) into each request's slot state, and the returned ticket (> 0) turns "done" (ticket_done).  The caller
+  // must keep the fragments alive until then.  The GPU engine does all of this in one kernel launch without waiting
+  // (d_states: the state words as the engine's GPU addresses them); this default does it synchronously on the calling
+  // thread (h_states).  Negative return: failure, no state was stored.
+  virtual int64_t gather_batch_notify(P2pRpcRr** rrs, g_params** stubs, volatile uint32_t** h_states,
+                                      volatile uint32_t** d_states, int n, uint32_t state_value) {
+    (void)d_states;
+    int rc = gather_batch(rrs, stubs, n);
+    if (rc != 0) return rc < 0 ? rc : -1;
+    for (int i = 0; i < n; i++) __atomic_store_n(h_states[i], state_value, __ATOMIC_RELEASE);
+    return ++sync_ticket_;
+  }
+  virtual bool ticket_done(int64_t ticket) {
+    (void)ticket;
+    return true;
   }
   // Makes gathers transform the payload on the way into the ring instead of copying it (GPU engine, copy type 2).
   // kind 0 = plain copy; SG_TRANSFORM_STEM_S2D = fp32 CHW image -> normalised bf16 space-to-depth tensor, params =

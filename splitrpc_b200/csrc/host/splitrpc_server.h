@@ -11,8 +11,10 @@
 // pointers to the engines.
 #pragma once
 
+#include <deque>
 #include <thread>
 
+#include "nvl_batched_server.h"
 #include "p2p_rpc_async_app_server.h"
 #include "p2p_rpc_sg_engine.h"
 #include "transport.h"
@@ -27,28 +29,43 @@ struct ServerConfig {
   uint64_t reassembly_timeout_ns = 200000000ull;
   int steer_policy = 0;     // 0 = round robin in runs of max_batch, 1 = least outstanding
   int gather_burst = 64;    // requests per scatter-gather submission
+  // 1 = let the serving side store single-fragment responses straight into the transmit arena and complete the slot
+  // itself (see RespPushCtx) wherever the arena is reachable from the app's device; 0 = host-driven scatter.
+  int device_completion = 1;
 };
 
 struct ReplicaStats {
-  uint64_t steered = 0, completed = 0, ring_full = 0;
+  uint64_t steered = 0, completed = 0, ring_full = 0, pushed = 0;
 };
 
 struct ServerStats {
   uint64_t rx_pkts = 0, rx_reqs = 0, tx_resps = 0, tx_pkts = 0, dropped_pkts = 0, expired = 0, ring_full = 0,
-           tx_alloc_fail = 0, sg_errors = 0;
+           tx_alloc_fail = 0, sg_errors = 0, replicas_lost = 0;
   std::vector<ReplicaStats> replicas;
 };
 
 class SplitRpcServer {
+  // A replica is a slot ring plus the engine that fills it.  Local: the app lives in this process and a worker thread
+  // of this server runs it.  Remote: the ring belongs to a batched server in another process (another GPU); this
+  // process holds a mirror of its slot pool and an engine on the ingress GPU that writes into it over NVLink.
   struct Replica {
     P2pRpcAppInfo* app = nullptr;
+    P2pRpcAppRrPool* pool = nullptr;
     P2pRpcSgEngine* engine = nullptr;
+    NvlRemoteReplica* remote = nullptr;
+    bool device_completes = false;         // responses and WORK_COMPLETE arrive without this process's help
     int app_idx = -1;
     int tx_idx = 0;                        // next slot whose response goes out
     std::atomic<int> outstanding{0};
     std::atomic<bool> down{false};         // steering skips a replica marked down
     ReplicaStats stats;
     std::thread worker;
+  };
+  // A gather that the engine finishes by itself: the receive buffers go back to the port once its ticket is done.
+  struct Inflight {
+    P2pRpcSgEngine* engine;
+    int64_t ticket;
+    std::vector<uint32_t> rx_slots;
   };
 
   Transport* port_;
@@ -62,12 +79,13 @@ class SplitRpcServer {
   std::atomic<bool> running_{false};
   struct LiveStats {
     std::atomic<uint64_t> rx_pkts{0}, rx_reqs{0}, tx_resps{0}, tx_pkts{0}, dropped_pkts{0}, expired{0}, ring_full{0},
-        tx_alloc_fail{0}, sg_errors{0};
+        tx_alloc_fail{0}, sg_errors{0}, replicas_lost{0};
   } stats_;
   int rr_cursor_ = 0, rr_run_ = 0;
-  // Per transport record: the packets it holds (for release) — indexed through
-  // transport_mbufs as slot+1 so that 0 means "none".
   size_t resp_frags_;
+  TxArenaInfo tx_info_{};
+  bool have_tx_info_ = false;
+  std::deque<Inflight> inflight_;
 
   void rx_loop() {
     std::vector<SrpcPkt> pkts(1024);
@@ -115,6 +133,33 @@ class SplitRpcServer {
       rr->transport_mbufs->burst_items[i] = 0;
     }
   }
+  // Moves the receive-buffer handles of a record into `out` (they are released later, when the gather is done).
+  static void take_rx_slots(P2pRpcRr* rr, std::vector<uint32_t>* out) {
+    for (size_t i = 0; i < rr->transport_mbufs->num_items; i++) {
+      uintptr_t h = rr->transport_mbufs->burst_items[i];
+      if (h) out->push_back((uint32_t)(h - 1));
+      rr->transport_mbufs->burst_items[i] = 0;
+    }
+  }
+  void release_rx_slots(const std::vector<uint32_t>& slots) {
+    SrpcPkt p;
+    for (uint32_t s : slots) {
+      p.slot = s;
+      port_->release_rx(&p, 1);
+    }
+  }
+  void reap_inflight(bool wait_all) {
+    uint64_t t0 = getCurNs();
+    while (!inflight_.empty()) {
+      Inflight& f = inflight_.front();
+      if (!f.engine->ticket_done(f.ticket)) {
+        if (!wait_all || getCurNs() - t0 > 2000000000ull) return;
+        continue;
+      }
+      release_rx_slots(f.rx_slots);
+      inflight_.pop_front();
+    }
+  }
 
   int pick_replica() {
     int n = (int)replicas_.size();
@@ -146,10 +191,8 @@ class SplitRpcServer {
     return -1;
   }
 
-  // Prepares the response side of a record: transmit buffers + reply headers.
-  bool prepare_tx(P2pRpcRr* rr) {
-    std::vector<SrpcPkt> tx(resp_frags_);
-    if (!port_->alloc_tx(tx.data(), (int)resp_frags_)) return false;
+  // Response side of a record, part 2: reply headers + buffer list over transmit buffers that were reserved before.
+  void fill_tx(P2pRpcRr* rr, const SrpcPkt* tx) {
     rr->clear_bufs();
     size_t left = cfg_.resp_size, mtu = rpc_mtu();
     for (size_t i = 0; i < resp_frags_; i++) {
@@ -158,7 +201,31 @@ class SplitRpcServer {
       fill_frag_hdr(tx[i].hdr, &rr->_client_conn_info, rr->req_token, (uint16_t)i, (uint16_t)len, true);
       rr->rr_append_mbuf((uintptr_t)tx[i].slot + 1, (uintptr_t)tx[i].hdr, (uintptr_t)tx[i].payload, len);
     }
-    return true;
+  }
+
+  void send_response(P2pRpcRr* rr) {
+    std::vector<SrpcPkt> tx(rr->transport_mbufs->num_items);
+    for (size_t k = 0; k < tx.size(); k++) {
+      tx[k].slot = (uint32_t)(rr->transport_mbufs->burst_items[k] - 1);
+      tx[k].hdr = (p2p_rpc_hdr*)rr->hdr_bufs->burst_items[k];
+      tx[k].payload = (uint8_t*)rr->payload_bufs->burst_items[k];
+      tx[k].len = (uint32_t)rr->payload_bufs->item_size[k];
+    }
+    if (!tx.empty()) stats_.tx_pkts += (uint64_t)port_->tx_burst(tx.data(), (int)tx.size());
+    stats_.tx_resps++;
+    rr_pool_.reap_rr(rr);
+  }
+
+  void check_remote_replicas() {
+    for (auto& rp : replicas_) {
+      Replica& rep = *rp;
+      if (!rep.remote || rep.down.load()) continue;
+      if (!rep.remote->alive()) {
+        rep.down.store(true);
+        stats_.replicas_lost++;
+        srpc_log(SRPC_LOG_WARN, "a remote replica closed its control connection: steering now skips it");
+      }
+    }
   }
 
   void shunter_loop() {
@@ -166,9 +233,15 @@ class SplitRpcServer {
     std::vector<P2pRpcRr*> rrs((size_t)burst);
     std::vector<g_params*> stubs((size_t)burst);
     std::vector<P2pRpcAppRr*> slots((size_t)burst);
+    std::vector<volatile uint32_t*> h_states((size_t)burst), d_states((size_t)burst);
+    std::vector<SrpcPkt> tx((size_t)burst * resp_frags_);
+    std::vector<uint8_t> tx_ok((size_t)burst);
+    std::vector<P2pRpcRr*> s_rrs;
+    std::vector<g_params*> s_stubs;
     P2pRpcRr* pending = nullptr;  // a ready request that found its replica's ring full
     IdleBackoff backoff;
     bool did_work = true;
+    uint64_t last_alive_check = getCurNs();
     while (!quit_.load(std::memory_order_acquire)) {
       if (did_work) backoff.busy();
       else backoff.empty();
@@ -179,6 +252,7 @@ class SplitRpcServer {
         P2pRpcRr* rr = pending ? pending : rr_pool_.get_next_rx_ready_rr();
         if (!rr) break;
         int t = pending ? rr->steer_target : pick_replica();
+        if (t >= 0 && replicas_[t]->down.load()) t = pick_replica();  // its replica went down while it waited
         pending = nullptr;
         if (t < 0) {  // every replica is down: drop the request
           release_rr_rx(rr);
@@ -193,7 +267,7 @@ class SplitRpcServer {
         }
         Replica& rep = *replicas_[t];
         // The next producer slot is bound to ring addresses only once it is free.
-        P2pRpcAppRrPool* arp = rep.app->app_rr_pool;
+        P2pRpcAppRrPool* arp = rep.pool;
         P2pRpcAppRr* slot = arp->get_app_rr((int)arp->producer_index());
         if (__atomic_load_n(slot->h_state, __ATOMIC_ACQUIRE) != APP_RR_STATUS::FREE) {
           rep.stats.ring_full++;
@@ -206,6 +280,8 @@ class SplitRpcServer {
         rrs[nb] = rr;
         stubs[nb] = slot->h_stub;
         slots[nb] = slot;
+        h_states[nb] = slot->h_state;
+        d_states[nb] = slot->d_state;
         slot->rpc_rr = rr;
         rr->app_rr_idx = slot->rr_idx;
         nb++;
@@ -213,25 +289,46 @@ class SplitRpcServer {
       if (nb > 0) {
         did_work = true;
         Replica& rep = *replicas_[target];
-        int rc = rep.engine->gather_batch(rrs.data(), stubs.data(), nb);
-        if (rc != 0) stats_.sg_errors++;
-        for (int i = 0; i < nb; i++) {
-          if (!cfg_.zerocopy) {
-            release_rr_rx(rrs[i]);
-            if (!prepare_tx(rrs[i])) stats_.tx_alloc_fail++;
+        Inflight fl{rep.engine, 0, {}};
+        if (!cfg_.zerocopy) {
+          // Transmit buffers first: the serving side reads a slot's response destination as soon as it sees the
+          // doorbell, so the destination has to be in place before the gather (which rings the doorbell) is launched.
+          for (int i = 0; i < nb; i++) {
+            take_rx_slots(rrs[i], &fl.rx_slots);
+            tx_ok[i] = port_->alloc_tx(&tx[(size_t)i * resp_frags_], (int)resp_frags_) ? 1 : 0;
+            if (!tx_ok[i]) stats_.tx_alloc_fail++;
+            uint64_t off = P2pRpcAppRrMemPool::kNoTxOffset;
+            if (rep.device_completes && tx_ok[i] && resp_frags_ == 1) off = port_->tx_arena_offset(tx[(size_t)i * resp_frags_]);
+            __atomic_store_n(slots[i]->h_tx_off, off, __ATOMIC_RELEASE);
           }
-          __atomic_store_n(slots[i]->h_state, (uint32_t)APP_RR_STATUS::RX_COMPLETE, __ATOMIC_RELEASE);
+        }
+        int64_t ticket = rep.engine->gather_batch_notify(rrs.data(), stubs.data(), h_states.data(), d_states.data(), nb,
+                                                         (uint32_t)APP_RR_STATUS::RX_COMPLETE);
+        if (ticket < 0) {
+          // Nothing was stored into the slot states.  Hand the slots to the consumer anyway (it will answer with
+          // whatever the ring holds) rather than stall the ring: the error is counted and logged by the engine.
+          stats_.sg_errors++;
+          for (int i = 0; i < nb; i++) __atomic_store_n(h_states[i], (uint32_t)APP_RR_STATUS::RX_COMPLETE, __ATOMIC_RELEASE);
+        }
+        fl.ticket = ticket;
+        if (!cfg_.zerocopy) {
+          for (int i = 0; i < nb; i++) {
+            if (tx_ok[i]) fill_tx(rrs[i], &tx[(size_t)i * resp_frags_]);
+            else rrs[i]->clear_bufs();
+          }
+          inflight_.push_back(std::move(fl));
         }
         rep.outstanding.fetch_add(nb);
         rep.stats.steered += (uint64_t)nb;
       }
+      if (!inflight_.empty()) reap_inflight(false);
       // ---- TX half: finished slots -> responses
       for (auto& rep_ptr : replicas_) {
         Replica& rep = *rep_ptr;
-        int nt = 0;
-        const int pool_n = rep.app->app_rr_pool->get_pool_size();
+        int nt = 0, n_scatter = 0;
+        const int pool_n = rep.pool->get_pool_size();
         while (nt < burst) {
-          P2pRpcAppRr* slot = rep.app->app_rr_pool->get_app_rr((rep.tx_idx + nt) % pool_n);
+          P2pRpcAppRr* slot = rep.pool->get_app_rr((rep.tx_idx + nt) % pool_n);
           if (__atomic_load_n(slot->h_state, __ATOMIC_ACQUIRE) != APP_RR_STATUS::WORK_COMPLETE) break;
           if (!slot->rpc_rr) break;  // completed without ever being filled: leave it to the worker's accounting
           rrs[nt] = (P2pRpcRr*)slot->rpc_rr;
@@ -244,31 +341,45 @@ class SplitRpcServer {
         if (cfg_.zerocopy) {
           send_zerocopy(rep, rrs.data(), slots.data(), nt);
         } else {
-          int rc = rep.engine->scatter_batch(rrs.data(), stubs.data(), nt);
-          if (rc != 0) stats_.sg_errors++;
+          // Responses that the serving side already stored in the transmit arena only need sending; the others are
+          // fetched from the response ring by the engine (for a remote replica: a read over NVLink).
+          s_rrs.clear();
+          s_stubs.clear();
           for (int i = 0; i < nt; i++) {
-            P2pRpcRr* rr = rrs[i];
-            std::vector<SrpcPkt> tx(rr->transport_mbufs->num_items);
-            for (size_t k = 0; k < tx.size(); k++) {
-              tx[k].slot = (uint32_t)(rr->transport_mbufs->burst_items[k] - 1);
-              tx[k].hdr = (p2p_rpc_hdr*)rr->hdr_bufs->burst_items[k];
-              tx[k].payload = (uint8_t*)rr->payload_bufs->burst_items[k];
-              tx[k].len = (uint32_t)rr->payload_bufs->item_size[k];
+            bool pushed = rep.device_completes &&
+                          __atomic_load_n(slots[i]->h_tx_off, __ATOMIC_ACQUIRE) != P2pRpcAppRrMemPool::kNoTxOffset;
+            if (pushed) {
+              rep.stats.pushed++;
+            } else {
+              s_rrs.push_back(rrs[i]);
+              s_stubs.push_back(stubs[i]);
+              n_scatter++;
             }
-            stats_.tx_pkts += (uint64_t)port_->tx_burst(tx.data(), (int)tx.size());
-            stats_.tx_resps++;
-            rr_pool_.reap_rr(rr);
           }
+          if (n_scatter > 0) {
+            int rc = rep.engine->scatter_batch(s_rrs.data(), s_stubs.data(), n_scatter);
+            if (rc != 0) stats_.sg_errors++;
+          }
+          for (int i = 0; i < nt; i++) send_response(rrs[i]);
         }
         for (int i = 0; i < nt; i++) {
           slots[i]->rpc_rr = nullptr;
+          __atomic_store_n(slots[i]->h_tx_off, P2pRpcAppRrMemPool::kNoTxOffset, __ATOMIC_RELAXED);
           __atomic_store_n(slots[i]->h_state, (uint32_t)APP_RR_STATUS::FREE, __ATOMIC_RELEASE);
         }
         rep.tx_idx = (rep.tx_idx + nt) % pool_n;
         rep.outstanding.fetch_sub(nt);
         rep.stats.completed += (uint64_t)nt;
       }
+      if (!did_work) {
+        uint64_t now = getCurNs();
+        if (now - last_alive_check > 20000000ull) {
+          last_alive_check = now;
+          check_remote_replicas();
+        }
+      }
     }
+    reap_inflight(true);
   }
 
   // Zero-copy replies: the app answered in the receive buffer; build the reply
@@ -292,6 +403,7 @@ class SplitRpcServer {
  public:
   SplitRpcServer(Transport* port, const ServerConfig& cfg)
       : port_(port), cfg_(cfg), rr_pool_(cfg.rr_pool_size), resp_frags_(num_fragments(cfg.resp_size, rpc_mtu())) {
+    have_tx_info_ = port_->tx_arena_info(&tx_info_);
     server_conn_ = initialize_src_conn_info(cfg.server_uri);
     rr_pool_.setup_and_init_rr_pool(server_conn_, cfg.req_size);
   }
@@ -300,17 +412,41 @@ class SplitRpcServer {
     release_conn_info(server_conn_);
   }
 
-  // Adds a replica: an app instance (its own slot ring) and the engine that
+  // Adds a local replica: an app instance (its own slot ring) and the engine that
   // fills that ring.  Returns the replica index.
   int add_replica(P2pRpcAppInfo* app, P2pRpcSgEngine* engine) {
     auto r = std::make_unique<Replica>();
     r->app = app;
+    r->pool = app->app_rr_pool;
     r->engine = engine;
     r->app_idx = app_server_.register_app(app);
     app->app_rr_pool->init_pool();
+    // Completion by the serving side: possible when responses fit one fragment and the app's device can store into
+    // the transmit arena (any host arena for a CPU app; a pinned/registered one for a GPU app).
+    if (cfg_.device_completion && !cfg_.zerocopy && resp_frags_ == 1 && have_tx_info_) {
+      if (app->device_id < 0) {
+        app->enable_device_completion((uint64_t)(uintptr_t)tx_info_.host_base, tx_info_.bytes);
+        r->device_completes = true;
+      } else if (tx_info_.gpu_visible) {
+        app->enable_device_completion((uint64_t)(uintptr_t)tx_info_.dev_base, tx_info_.bytes);
+        r->device_completes = true;
+      }
+    }
     replicas_.push_back(std::move(r));
     return (int)replicas_.size() - 1;
   }
+  // Adds a replica that is served by a batched server in another process.  The caller keeps `remote` alive.
+  int add_remote_replica(NvlRemoteReplica* remote) {
+    auto r = std::make_unique<Replica>();
+    r->remote = remote;
+    r->pool = remote->pool();
+    r->engine = remote->engine();
+    r->device_completes = remote->device_completes();
+    replicas_.push_back(std::move(r));
+    return (int)replicas_.size() - 1;
+  }
+  const TxArenaInfo* tx_arena() const { return have_tx_info_ ? &tx_info_ : nullptr; }
+  size_t num_replicas() const { return replicas_.size(); }
   P2pRpcAsyncAppServer& app_server() { return app_server_; }
   P2pRpcRRPool& rr_pool() { return rr_pool_; }
   void mark_replica_down(int idx, bool down) { replicas_[idx]->down.store(down); }
@@ -321,6 +457,7 @@ class SplitRpcServer {
     app_server_.reset_quit();
     for (auto& rp : replicas_) {
       Replica* r = rp.get();
+      if (!r->app) continue;  // remote replicas run their own worker
       r->app->app_ctx->curr_batch_size = cfg_.max_batch;
       r->app->app_ctx->next_batch_size = cfg_.max_batch;
       r->worker = std::thread([this, r] {
@@ -349,9 +486,15 @@ class SplitRpcServer {
     ServerStats s;
     s.rx_pkts = stats_.rx_pkts; s.rx_reqs = stats_.rx_reqs; s.tx_resps = stats_.tx_resps; s.tx_pkts = stats_.tx_pkts;
     s.dropped_pkts = stats_.dropped_pkts; s.expired = stats_.expired; s.ring_full = stats_.ring_full;
-    s.tx_alloc_fail = stats_.tx_alloc_fail; s.sg_errors = stats_.sg_errors;
+    s.tx_alloc_fail = stats_.tx_alloc_fail; s.sg_errors = stats_.sg_errors; s.replicas_lost = stats_.replicas_lost;
     for (auto& rp : replicas_) s.replicas.push_back(rp->stats);
     return s;
   }
-  WorkerStats worker_stats(int replica) { return app_server_.stats(replicas_[replica]->app_idx); }
+  WorkerStats worker_stats(int replica) {
+    Replica& r = *replicas_[replica];
+    if (r.app) return app_server_.stats(r.app_idx);
+    WorkerStats w;  // remote: ask its server
+    if (r.remote) r.remote->query_stats(&w.num_req, &w.num_batches);
+    return w;
+  }
 };

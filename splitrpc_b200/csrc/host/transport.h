@@ -44,6 +44,19 @@ struct ArenaMem {
   uint8_t* dev = nullptr;
   size_t bytes = 0;
   std::function<void()> release;  // frees the memory when the arena dies
+  int fd = -1;                    // memfd behind the mapping when other processes may map the arena too
+  bool gpu_visible = false;       // `dev` is an address that this process's GPUs can read and write
+};
+
+// A port's transmit arena seen as one region that a serving GPU (of this or of another process) stores responses
+// into: the stand-in for a NIC's registered transmit ring.
+struct TxArenaInfo {
+  uint8_t* host_base = nullptr;
+  uint8_t* dev_base = nullptr;
+  size_t bytes = 0;
+  size_t slot_bytes = 0;
+  int fd = -1;
+  bool gpu_visible = false;
 };
 
 static inline ArenaMem make_malloc_arena(size_t bytes) {
@@ -86,6 +99,8 @@ class PktArena {
   uint8_t* host_ptr(uint32_t slot) const { return mem_.host + (size_t)slot * slot_bytes_; }
   uint8_t* dev_ptr(uint32_t slot) const { return mem_.dev + (size_t)slot * slot_bytes_; }
   p2p_rpc_hdr* hdr_ptr(uint32_t slot) const { return &hdrs_[slot]; }
+  int fd() const { return mem_.fd; }
+  bool gpu_visible() const { return mem_.gpu_visible; }
   uint8_t* to_dev(const uint8_t* host) const { return mem_.dev + (host - mem_.host); }
   uint8_t* to_host(const uint8_t* dev) const { return mem_.host + (dev - mem_.dev); }
 
@@ -138,6 +153,16 @@ class Transport {
   virtual uint8_t* tx_host_ptr(const SrpcPkt& p) const { return p.payload; }
   // Host-view address of the payload buffer of receive slot `slot`.
   virtual uint8_t* rx_host_ptr(uint32_t slot) const = 0;
+  // Describes the transmit arena; false when the port has none that others could write into.
+  virtual bool tx_arena_info(TxArenaInfo* out) const {
+    (void)out;
+    return false;
+  }
+  // Byte offset of a transmit buffer (from alloc_tx) inside the transmit arena.
+  virtual uint64_t tx_arena_offset(const SrpcPkt& p) const {
+    (void)p;
+    return ~0ull;
+  }
 };
 
 // ------------------------------------------------------------------ loopback
@@ -334,6 +359,16 @@ class LoopbackPort : public Transport {
     return p.slot == kExternalSlot ? p.payload : rx_arena_->to_dev(p.payload);
   }
   uint8_t* tx_host_ptr(const SrpcPkt& p) const override { return tx_arena_->to_host(p.payload); }
+  bool tx_arena_info(TxArenaInfo* out) const override {
+    out->host_base = tx_arena_->host_base();
+    out->dev_base = tx_arena_->dev_base();
+    out->bytes = tx_arena_->bytes();
+    out->slot_bytes = tx_arena_->slot_bytes();
+    out->fd = tx_arena_->fd();
+    out->gpu_visible = tx_arena_->gpu_visible();
+    return true;
+  }
+  uint64_t tx_arena_offset(const SrpcPkt& p) const override { return (uint64_t)p.slot * tx_arena_->slot_bytes(); }
   uint8_t* rx_host_ptr(uint32_t slot) const override { return rx_arena_->host_ptr(slot); }
   const char* name() const override { return "loopback"; }
 };
@@ -475,6 +510,16 @@ class UdpPort : public Transport {
     for (int i = 0; i < n; i++) s += send_one(&hdrs[i], payloads[i], lens[i]);
     return s;
   }
+  bool tx_arena_info(TxArenaInfo* out) const override {
+    out->host_base = tx_arena_->host_base();
+    out->dev_base = tx_arena_->dev_base();
+    out->bytes = tx_arena_->bytes();
+    out->slot_bytes = tx_arena_->slot_bytes();
+    out->fd = tx_arena_->fd();
+    out->gpu_visible = tx_arena_->gpu_visible();
+    return true;
+  }
+  uint64_t tx_arena_offset(const SrpcPkt& p) const override { return (uint64_t)p.slot * tx_arena_->slot_bytes(); }
   uint8_t* rx_host_ptr(uint32_t slot) const override { return rx_arena_->host_ptr(slot); }
   const char* name() const override { return "udp"; }
 };

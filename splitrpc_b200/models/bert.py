@@ -79,7 +79,7 @@ class BertClassifier:
         self.kernels_per_forward = 1 + 7 * cfg.layers + 3
 
     def forward(self, batch: int, ids: torch.Tensor | None = None, d_stub: int = 0, out: torch.Tensor | None = None,
-                flag_ptr: int = 0, flag_value: int = 0, counter: torch.Tensor | None = None) -> torch.Tensor:
+                flag_ptr: int = 0, flag_value: int = 0, counter: torch.Tensor | None = None, d_push: int = 0) -> torch.Tensor:
         cfg, p, b, S = self.cfg, self.params, self.buf, self.seq
         T = batch * S
         x, qkv, ctx, attn, x1, ffn, y = (b[k][:T] for k in ("x", "qkv", "ctx", "attn", "x1", "ffn", "y"))
@@ -104,7 +104,7 @@ class BertClassifier:
         ops.gemm(b["pooled"][:batch], p["cls.w"], bias=p["cls.b"], out=b["logits"][:batch])
         logits = b["logits"][:batch, : cfg.num_labels]
         ops.softmax_response(logits, batch, out=out, d_stub=0 if out is not None else d_stub, resp_stride=self.resp_size,
-                             counter=counter, flag_ptr=flag_ptr, flag_value=flag_value)
+                             counter=counter, flag_ptr=flag_ptr, flag_value=flag_value, d_push=0 if out is not None else d_push)
         return logits
 
     __call__ = forward

@@ -124,11 +124,13 @@ class ResNet50:
         return {"mean": list(self.mean), "inv_std": list(self.inv_std)}
 
     def forward(self, batch: int, x: torch.Tensor | None = None, d_stub: int = 0, out: torch.Tensor | None = None,
-                flag_ptr: int = 0, flag_value: int = 0, counter: torch.Tensor | None = None) -> torch.Tensor:
+                flag_ptr: int = 0, flag_value: int = 0, counter: torch.Tensor | None = None, d_push: int = 0) -> torch.Tensor:
         """Launches the whole network for ``batch`` images on the current stream.
 
         Input: fp32 ``[batch,3,224,224]`` tensor ``x`` or the request window behind ``d_stub``.
-        Output: fp32 softmax rows in ``out`` (``[batch,1000]``) or the response window behind ``d_stub``.
+        Output: fp32 softmax rows in ``out`` (``[batch,1000]``) or the response window behind ``d_stub``; with ``d_push``
+        (the app's response-push block) the last kernel stores each row where the ingress asked for it and completes
+        the row's slot.
         """
         p, b = self.params, self.buf
         nb = batch
@@ -163,7 +165,7 @@ class ResNet50:
         else:
             ops.gemm(avg, p["fc.w"], bias=p["fc.b"], out=b["logits"][:nb])
         ops.softmax_response(b["logits"][:nb], nb, out=out, d_stub=0 if out is not None else d_stub, resp_stride=RESP_BYTES,
-                             counter=counter, flag_ptr=flag_ptr, flag_value=flag_value)
+                             counter=counter, flag_ptr=flag_ptr, flag_value=flag_value, d_push=0 if out is not None else d_push)
         return b["logits"][:nb]
 
     __call__ = forward

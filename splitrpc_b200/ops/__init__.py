@@ -213,14 +213,18 @@ def global_avgpool(x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Te
 
 def softmax_response(logits: torch.Tensor, rows: int, out: torch.Tensor | None = None, d_stub: int = 0,
                      resp_stride: int | None = None, write_argmax: bool = False, counter: torch.Tensor | None = None,
-                     flag_ptr: int = 0, flag_value: int = 0) -> None:
-    """Row softmax of fp32 logits written as fp32 into response slots (``out`` or the stub's response window)."""
+                     flag_ptr: int = 0, flag_value: int = 0, d_push: int = 0) -> None:
+    """Row softmax of fp32 logits written as fp32 into response slots (``out`` or the stub's response window).
+
+    ``d_push``: device address of the app's response-push block (``App.d_push``).  When the server has enabled
+    completion by the serving side, every row is stored where the ingress asked for it (its transmit arena) and the
+    row's slot is marked complete by this kernel; otherwise the block is inert and the row goes to the response ring."""
     assert logits.dtype == torch.float32 and logits.stride(1) == 1
     n = logits.shape[1]
     if resp_stride is None:
         resp_stride = (n + (1 if write_argmax else 0)) * 4
     _C.softmax_response(logits.data_ptr(), rows, n, logits.stride(0), d_stub, _ptr(out), resp_stride, write_argmax,
-                        _ptr(counter), flag_ptr, flag_value, _stream())
+                        _ptr(counter), flag_ptr, flag_value, _stream(), d_push)
 
 
 def layernorm(x: torch.Tensor, gamma: torch.Tensor, beta: torch.Tensor, residual: torch.Tensor | None = None,
