@@ -531,6 +531,27 @@ PYBIND11_MODULE(_C, m) {
         std::atomic_thread_fence(std::memory_order_seq_cst);
       })
       .def_property_readonly("pool_size", [](AppHolder& a) { return a.info->app_rr_pool->get_pool_size(); })
+      // Slot-level access for stand-alone timing loops and tests (the server's threads do all of this themselves):
+      // device-side address of the slot state words, state and response destination of one slot, and a reset of the
+      // whole ring (every slot FREE, no destinations, ring addresses from the start).
+      .def_property_readonly("states_dev", [](AppHolder& a) { return (uintptr_t)a.info->app_rr_pool->rr_mem_pool->get_doorbells_device(); })
+      .def_property_readonly("d_first_slot", [](AppHolder& a) { return (uintptr_t)&a.info->app_ctx->d_push->first_slot; })
+      .def("slot_state", [](AppHolder& a, int i) { return (uint32_t)__atomic_load_n(a.info->app_rr_pool->get_app_rr(i)->h_state, __ATOMIC_ACQUIRE); })
+      .def("set_slot_state", [](AppHolder& a, int i, uint32_t v) { __atomic_store_n(a.info->app_rr_pool->get_app_rr(i)->h_state, v, __ATOMIC_RELEASE); })
+      .def("set_tx_off", [](AppHolder& a, int i, uint64_t off) { __atomic_store_n(a.info->app_rr_pool->get_app_rr(i)->h_tx_off, off, __ATOMIC_RELEASE); })
+      .def("reset_slots", [](AppHolder& a) {
+        P2pRpcAppRrPool* pool = a.info->app_rr_pool;
+        pool->init_pool();
+        a.info->consumer_seq = 0;
+        for (int i = 0; i < pool->get_pool_size(); i++) {
+          __atomic_store_n(pool->get_app_rr(i)->h_tx_off, P2pRpcAppRrMemPool::kNoTxOffset, __ATOMIC_RELAXED);
+          __atomic_store_n(pool->get_app_rr(i)->h_state, (uint32_t)APP_RR_STATUS::FREE, __ATOMIC_RELEASE);
+        }
+      })
+      // Completion by the serving side, set up by hand (the server does this in add_replica): responses go to
+      // tx_base + the slot's offset, tx_base being this process's device-side address of the transmit arena.
+      .def("enable_device_completion", [](AppHolder& a, uintptr_t tx_base, uint64_t tx_bytes) { a.info->enable_device_completion(tx_base, tx_bytes); })
+      .def("disable_device_completion", [](AppHolder& a) { a.info->disable_device_completion(); })
       .def_property_readonly("exportable", [](AppHolder& a) { return a.info->app_rr_pool->rr_mem_pool->exportable(); })
       // Points the app's stub at explicit addresses (default: the start of both rings),
       // e.g. before a warm-up run or a stand-alone timing loop.
@@ -650,6 +671,35 @@ PYBIND11_MODULE(_C, m) {
            },
            py::arg("path"), py::arg("func_id") = 1234, py::arg("ingress_device") = -1, py::arg("copy_type") = 2,
            py::arg("timeout_ms") = 10000)
+      // Transmit arena of the server's port: (host base, device base, bytes, slot bytes).
+      .def_property_readonly("tx_arena", [](ServerHolder& s) -> py::tuple {
+        const TxArenaInfo* t = s.server->tx_arena();
+        if (!t) return py::make_tuple((uintptr_t)0, (uintptr_t)0, (size_t)0, (size_t)0);
+        return py::make_tuple((uintptr_t)t->host_base, (uintptr_t)t->dev_base, (size_t)t->bytes, (size_t)t->slot_bytes);
+      })
+      // This process's mapping of a remote replica's rings and slot words (addresses are valid on the ingress GPU).
+      .def("remote_rings",
+           [](ServerHolder& s, int remote_idx) {
+             P2pRpcAppRrPool* pool = s.remotes.at((size_t)remote_idx)->pool();
+             P2pRpcAppRrMemPool* mp = pool->rr_mem_pool;
+             py::dict d;
+             d["req_base"] = (uintptr_t)mp->get_req_addr_range();
+             d["req_capacity"] = mp->get_req_addr_pool_size();
+             d["resp_base"] = (uintptr_t)mp->get_resp_addr_range();
+             d["resp_capacity"] = mp->get_resp_addr_pool_size();
+             d["states_dev"] = (uintptr_t)mp->get_doorbells_device();
+             d["pool_size"] = pool->get_pool_size();
+             return d;
+           })
+      .def("remote_slot_state", [](ServerHolder& s, int remote_idx, int slot) {
+        return (uint32_t)__atomic_load_n(s.remotes.at((size_t)remote_idx)->pool()->get_app_rr(slot)->h_state, __ATOMIC_ACQUIRE);
+      })
+      .def("remote_set_slot_state", [](ServerHolder& s, int remote_idx, int slot, uint32_t v) {
+        __atomic_store_n(s.remotes.at((size_t)remote_idx)->pool()->get_app_rr(slot)->h_state, v, __ATOMIC_RELEASE);
+      })
+      .def("remote_set_tx_off", [](ServerHolder& s, int remote_idx, int slot, uint64_t off) {
+        __atomic_store_n(s.remotes.at((size_t)remote_idx)->pool()->get_app_rr(slot)->h_tx_off, off, __ATOMIC_RELEASE);
+      })
       .def("remote_info",
            [](ServerHolder& s, int remote_idx) {
              const buf_mon_rr& i = s.remotes.at((size_t)remote_idx)->info();

@@ -9,6 +9,7 @@
 #include "cuda/gemm_tp.h"
 #include "cuda/nn_kernels.h"
 #include "cuda/ops_api.h"
+#include "host/p2p_rpc_app.h"
 #include "cuda/parity_kernels.h"
 
 namespace py = pybind11;
@@ -64,22 +65,36 @@ void bind_ops(py::module_& m) {
   m.def("memcpy_async", [](uintptr_t dst, uintptr_t src, size_t n, uintptr_t stream) {
     check(cudaMemcpyAsync((void*)dst, (const void*)src, n, cudaMemcpyDefault, (cudaStream_t)stream), "memcpy_async");
   });
-  m.def("sg_list_create", &srpc_sg_list_create);
+  m.def("sg_list_create", &srpc_sg_list_create, py::arg("items"), py::arg("bells") = std::vector<uint64_t>{});
   m.def("sg_list_destroy", &srpc_sg_list_destroy);
   m.def("sg_list_launch_stem_s2d",
         [](uintptr_t h, uintptr_t ring_base, uint32_t slot_bytes, std::vector<float> mean, std::vector<float> inv_std, int n_blocks,
-           uintptr_t stream) {
+           uintptr_t stream, uint32_t bell_value, uintptr_t done_word, uint32_t done_value) {
           if (mean.size() != 3 || inv_std.size() != 3) throw std::invalid_argument("mean / inv_std need 3 values");
-          check(srpc_sg_list_launch_stem_s2d(h, ring_base, slot_bytes, mean.data(), inv_std.data(), n_blocks, (cudaStream_t)stream),
+          check(srpc_sg_list_launch_stem_s2d(h, ring_base, slot_bytes, mean.data(), inv_std.data(), n_blocks, (cudaStream_t)stream,
+                                             bell_value, done_word, done_value),
                 "sg_list_launch_stem_s2d");
         },
         py::arg("handle"), py::arg("ring_base"), py::arg("slot_bytes"), py::arg("mean"), py::arg("inv_std"), py::arg("n_blocks") = 0,
-        py::arg("stream") = 0);
+        py::arg("stream") = 0, py::arg("bell_value") = 0, py::arg("done_word") = 0, py::arg("done_value") = 0);
   m.def("sg_list_launch",
-        [](uintptr_t h, int impl, int n_blocks, uintptr_t stream) {
-          check(srpc_sg_list_launch(h, impl, n_blocks, (cudaStream_t)stream), "sg_list_launch");
+        [](uintptr_t h, int impl, int n_blocks, uintptr_t stream, uint32_t bell_value, uintptr_t done_word, uint32_t done_value) {
+          check(srpc_sg_list_launch(h, impl, n_blocks, (cudaStream_t)stream, bell_value, done_word, done_value), "sg_list_launch");
         },
-        py::arg("handle"), py::arg("impl") = 0, py::arg("n_blocks") = 0, py::arg("stream") = 0);
+        py::arg("handle"), py::arg("impl") = 0, py::arg("n_blocks") = 0, py::arg("stream") = 0, py::arg("bell_value") = 0,
+        py::arg("done_word") = 0, py::arg("done_value") = 0);
+  // Stream-ordered doorbell operations on a 32-bit word that the device can address (mapped host memory or device
+  // memory): the stream waits until the word equals `value` / writes `value` once everything queued before has finished.
+  m.def("stream_wait32", [](uintptr_t stream, uintptr_t addr, uint32_t value) {
+    const SrpcDeviceOps* o = srpc_cuda_ops();
+    if (!o || o->stream_wait_value32((cudaStream_t)stream, (volatile uint32_t*)addr, value) != 0)
+      throw std::runtime_error(std::string("stream_wait32: ") + (o ? o->last_error() : "no CUDA"));
+  });
+  m.def("stream_write32", [](uintptr_t stream, uintptr_t addr, uint32_t value) {
+    const SrpcDeviceOps* o = srpc_cuda_ops();
+    if (!o || o->stream_write_value32((cudaStream_t)stream, (volatile uint32_t*)addr, value) != 0)
+      throw std::runtime_error(std::string("stream_write32: ") + (o ? o->last_error() : "no CUDA"));
+  });
 
   // ---- tensor-core GEMM / convolution
   m.attr("ACT_NONE") = (int)GEMM_ACT_NONE;

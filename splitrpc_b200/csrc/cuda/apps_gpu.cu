@@ -387,6 +387,18 @@ GpuAppHandle srpc_make_gpu_app(const char* name, int device_id, size_t req_size,
   if (cudaGetDeviceCount(&n) != cudaSuccess || device_id >= n) return h;
   std::string nm(name);
   if (nm != "echo" && nm != "vec_add" && nm != "matmul" && nm != "lenet5" && nm != "lenet_ref" && nm != "lstm") return h;
+  {
+    // Load the app kernels before a work stream can be parked on a doorbell (see sg_preload_kernels).
+    cudaSetDevice(device_id);
+    cudaFuncAttributes fa;
+    (void)cudaFuncGetAttributes(&fa, echo_kernel);
+    (void)cudaFuncGetAttributes(&fa, vec_add_kernel);
+    (void)cudaFuncGetAttributes(&fa, vec_add_resident);
+    (void)cudaFuncGetAttributes(&fa, mm_kernel);
+    (void)cudaFuncGetAttributes(&fa, lenet5_kernel);
+    srpc_parity_preload();
+    (void)cudaGetLastError();
+  }
   GpuAppState* s = new GpuAppState;
   s->name = nm;
   s->req_size = req_size;

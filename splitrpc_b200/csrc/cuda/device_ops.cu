@@ -116,6 +116,7 @@ static int d_set_device(int dev) {
 }
 static int d_stream_create(int dev, cudaStream_t* s) {
   RT(cudaSetDevice(dev));
+  sg_preload_kernels();  // every GPU app context passes here before its stream can be armed on a doorbell
   RT(cudaStreamCreateWithFlags(s, cudaStreamNonBlocking));
   return 0;
 }

@@ -18,3 +18,7 @@ cudaError_t srpc_lenet_ref(const void* d_stub, const void* direct_in, float* dir
 size_t srpc_lstm_scratch_bytes(int max_clusters);
 cudaError_t srpc_lstm(const void* d_stub, const float* direct_in, float* direct_out, const float* weights, float* scratch,
                       int max_clusters, int batch, float forget_bias, cudaStream_t s);
+
+// Loads this file's kernels on the current device, so that none of them is loaded lazily at a first launch that
+// happens while a stream is parked on a doorbell.
+void srpc_parity_preload();

@@ -218,6 +218,7 @@ class P2pRpcSgGpuEngine : public P2pRpcSgEngine {
   P2pRpcSgGpuEngine(int dev, int copy_type) : copy_type_(copy_type) {
     device_id = dev;
     cudaSetDevice(dev);
+    sg_preload_kernels();
     cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking);
     for (Slot& sl : slots_) {
       cudaHostAlloc(&sl.h_items, sizeof(SgItem) * SG_MAX_ITEMS, cudaHostAllocDefault);
@@ -289,7 +290,9 @@ class P2pRpcSgGpuEngine : public P2pRpcSgEngine {
   // come free when kSlots submissions are already in flight.
   int64_t gather_batch_notify(P2pRpcRr** rrs, g_params** stubs, volatile uint32_t** h_states, volatile uint32_t** d_states,
                               int n, uint32_t state_value) override {
-    (void)h_states;
+    // Only the launch-per-submission mode has a doorbell epilogue; DMA copies, the resident kernel and the bulk
+    // pipeline keep their own way of submitting and complete the slots from the host.
+    if (copy_type_ != 2) return P2pRpcSgEngine::gather_batch_notify(rrs, stubs, h_states, d_states, n, state_value);
     if (n <= 0 || (uint32_t)n > kMaxBells) return -4;
     PROF_START(Gather);
     cudaSetDevice(device_id);
@@ -397,7 +400,9 @@ extern "C" P2pRpcSgEngine* srpc_make_gpu_sg_engine(int device_id, int copy_type)
 
 struct SgListHandle {
   SgItem* d_items = nullptr;
-  uint32_t n = 0, chunks = 0;
+  uint64_t* d_bells = nullptr;  // optional: addresses of the doorbell words that a launch rings when it has finished
+  uint32_t* d_counter = nullptr;
+  uint32_t n = 0, chunks = 0, n_bells = 0;
 };
 
 static std::vector<SgItem> to_items(const std::vector<SgTuple>& in, uint32_t* chunks) {
@@ -411,13 +416,20 @@ static std::vector<SgItem> to_items(const std::vector<SgTuple>& in, uint32_t* ch
   return v;
 }
 
-uintptr_t srpc_sg_list_create(const std::vector<SgTuple>& items) {
+uintptr_t srpc_sg_list_create(const std::vector<SgTuple>& items, const std::vector<uint64_t>& bells) {
   auto* h = new SgListHandle;
   std::vector<SgItem> v = to_items(items, &h->chunks);
   h->n = (uint32_t)v.size();
-  if (cudaMalloc(&h->d_items, sizeof(SgItem) * (v.size() + 1)) != cudaSuccess ||
-      cudaMemcpy(h->d_items, v.data(), sizeof(SgItem) * v.size(), cudaMemcpyHostToDevice) != cudaSuccess) {
-    delete h;
+  h->n_bells = (uint32_t)bells.size();
+  bool ok = cudaMalloc(&h->d_items, sizeof(SgItem) * (v.size() + 1)) == cudaSuccess &&
+            cudaMemcpy(h->d_items, v.data(), sizeof(SgItem) * v.size(), cudaMemcpyHostToDevice) == cudaSuccess;
+  if (ok && !bells.empty()) {
+    ok = cudaMalloc(&h->d_bells, sizeof(uint64_t) * bells.size()) == cudaSuccess &&
+         cudaMemcpy(h->d_bells, bells.data(), sizeof(uint64_t) * bells.size(), cudaMemcpyHostToDevice) == cudaSuccess &&
+         cudaMalloc(&h->d_counter, sizeof(uint32_t)) == cudaSuccess && cudaMemset(h->d_counter, 0, sizeof(uint32_t)) == cudaSuccess;
+  }
+  if (!ok) {
+    srpc_sg_list_destroy((uintptr_t)h);
     return 0;
   }
   return (uintptr_t)h;
@@ -426,30 +438,50 @@ void srpc_sg_list_destroy(uintptr_t handle) {
   auto* h = reinterpret_cast<SgListHandle*>(handle);
   if (!h) return;
   cudaFree(h->d_items);
+  if (h->d_bells) cudaFree(h->d_bells);
+  if (h->d_counter) cudaFree(h->d_counter);
   delete h;
 }
-cudaError_t srpc_sg_list_launch(uintptr_t handle, int impl, int n_blocks, cudaStream_t stream) {
+// bell_value != 0 on a list created with bells: the launch's last block stores bell_value into every bell, then
+// done_value into *done_word (when given); see SgNotify.
+static SgNotify list_notify(const SgListHandle* h, uint32_t bell_value, uintptr_t done_word, uint32_t done_value) {
+  SgNotify nt;
+  if (h->d_bells && bell_value != 0) {
+    nt.counter = h->d_counter;
+    nt.bells = h->d_bells;
+    nt.n_bells = h->n_bells;
+    nt.bell_value = bell_value;
+    nt.done_word = reinterpret_cast<uint32_t*>(done_word);
+    nt.done_value = done_value;
+  }
+  return nt;
+}
+cudaError_t srpc_sg_list_launch(uintptr_t handle, int impl, int n_blocks, cudaStream_t stream, uint32_t bell_value,
+                                uintptr_t done_word, uint32_t done_value) {
   auto* h = reinterpret_cast<SgListHandle*>(handle);
   if (!h) return cudaErrorInvalidValue;
-  return sg_launch_copy(h->d_items, h->n, h->chunks, impl, n_blocks, stream);
+  const SgNotify nt = list_notify(h, bell_value, done_word, done_value);
+  return sg_launch_copy(h->d_items, h->n, h->chunks, impl, n_blocks, stream, nt.counter ? &nt : nullptr);
 }
 cudaError_t srpc_sg_list_launch_stem_s2d(uintptr_t handle, uint64_t ring_base, uint32_t slot_bytes, const float mean[3],
-                                         const float inv_std[3], int n_blocks, cudaStream_t stream) {
+                                         const float inv_std[3], int n_blocks, cudaStream_t stream, uint32_t bell_value,
+                                         uintptr_t done_word, uint32_t done_value) {
   auto* h = reinterpret_cast<SgListHandle*>(handle);
   if (!h) return cudaErrorInvalidValue;
   SgStemS2d tr{ring_base, slot_bytes, {mean[0], mean[1], mean[2]}, {inv_std[0], inv_std[1], inv_std[2]}};
-  return sg_launch_stem_s2d(h->d_items, h->n, h->chunks, tr, n_blocks, stream);
+  const SgNotify nt = list_notify(h, bell_value, done_word, done_value);
+  return sg_launch_stem_s2d(h->d_items, h->n, h->chunks, tr, n_blocks, stream, nt.counter ? &nt : nullptr);
 }
 cudaError_t srpc_sg_copy_list(const std::vector<SgTuple>& items, int impl, int n_blocks, cudaStream_t stream) {
-  uintptr_t h = srpc_sg_list_create(items);
+  uintptr_t h = srpc_sg_list_create(items, {});
   if (!h) return cudaErrorMemoryAllocation;
-  cudaError_t e = srpc_sg_list_launch(h, impl, n_blocks, stream);
+  cudaError_t e = srpc_sg_list_launch(h, impl, n_blocks, stream, 0, 0, 0);
   if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
   srpc_sg_list_destroy(h);
   return e;
 }
 cudaError_t srpc_sg_cast_list(const std::vector<SgTuple>& items, float scale, float shift, int n_blocks, cudaStream_t stream) {
-  uintptr_t hh = srpc_sg_list_create(items);
+  uintptr_t hh = srpc_sg_list_create(items, {});
   if (!hh) return cudaErrorMemoryAllocation;
   auto* h = reinterpret_cast<SgListHandle*>(hh);
   cudaError_t e = sg_launch_cast_bf16(h->d_items, h->n, h->chunks, scale, shift, n_blocks, stream);

@@ -385,6 +385,16 @@ static cudaError_t sg_kernel_setup() {
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
   std::call_once(once[dev], [dev] {
+    // Load every kernel of this file now.  With lazy module loading a kernel is loaded at its first launch, and that
+    // load can wait for the device to go idle; a work stream that is already parked on a doorbell (stream-armed mode)
+    // never goes idle until the very gather that is trying to launch has run, so the first launch would deadlock.
+    cudaFuncAttributes fa;
+    (void)cudaFuncGetAttributes(&fa, sg_copy_simt);
+    (void)cudaFuncGetAttributes(&fa, sg_copy_bulk);
+    (void)cudaFuncGetAttributes(&fa, sg_cast_bf16);
+    (void)cudaFuncGetAttributes(&fa, sg_stem_s2d);
+    (void)cudaFuncGetAttributes(&fa, sg_persistent);
+    (void)cudaFuncGetAttributes(&fa, resp_push_kernel);
     static const int on = [] { const char* e = getenv("P2P_RPC_SG_MAX_SHARED"); return e ? atoi(e) : 1; }();
     if (on) {
       prefer_max_shared(sg_copy_simt);
@@ -424,8 +434,11 @@ cudaError_t sg_launch_copy(const SgItem* d_items, uint32_t n_items, uint32_t n_c
   return cudaGetLastError();
 }
 
+void sg_preload_kernels() { (void)sg_kernel_setup(); }
+
 cudaError_t sg_launch_resp_push(const void* d_stub, const void* d_push, int n, cudaStream_t stream) {
   if (n <= 0) return cudaSuccess;
+  sg_kernel_setup();
   resp_push_kernel<<<n, 256, 0, stream>>>((const g_params*)d_stub, (const RespPushCtx*)d_push);
   return cudaGetLastError();
 }

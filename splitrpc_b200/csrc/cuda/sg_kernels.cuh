@@ -73,6 +73,9 @@ struct SgStemS2d {
 };
 cudaError_t sg_launch_stem_s2d(const SgItem* d_items, uint32_t n_items, uint32_t n_chunks, const SgStemS2d& tr, int n_blocks,
                                cudaStream_t stream, const SgNotify* notify = nullptr);
+// Loads this file's kernels on the current device (idempotent).  Call it before any stream of the device may be parked
+// on a doorbell: a kernel's first launch can otherwise block behind that stream (lazy module loading).
+void sg_preload_kernels();
 // Persistent engine: `counter` is a zero-initialised device word.
 cudaError_t sg_launch_persistent(SgCtrl* d_ctrl, uint32_t* d_counter, int n_blocks, cudaStream_t stream);
 

@@ -6,6 +6,7 @@
 
 #include <cuda_runtime.h>
 
+#include <atomic>
 #include <cstdio>
 #include <mutex>
 
@@ -18,21 +19,23 @@ namespace {
 static __device__ __align__(256) SgItem g_noalloc_items[SRPC_NOALLOC_MAX_ITEMS];
 
 constexpr int kMaxDevices = 64;
-SgItem* g_dev_list[kMaxDevices];  // device address of g_noalloc_items per device, filled on first use
+std::atomic<SgItem*> g_dev_list[kMaxDevices];  // device address of g_noalloc_items per device, filled on first use
 std::mutex g_setup_mu;
 
-// Set-up, once per device, with that device current.
+// Set-up, once per device, with that device current.  After the first call a device costs one atomic load here: the
+// threads this entry point is for must not queue up behind a lock on every copy.
 SgItem* list_address(int dev) {
+  if (SgItem* p = g_dev_list[dev].load(std::memory_order_acquire)) return p;
   std::lock_guard<std::mutex> g(g_setup_mu);
-  if (g_dev_list[dev]) return g_dev_list[dev];
+  if (SgItem* p = g_dev_list[dev].load(std::memory_order_acquire)) return p;
   void* p = nullptr;
   cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_items);
   if (e != cudaSuccess || !p) {
     std::fprintf(stderr, "srpc_sg_copy_noalloc: cudaGetSymbolAddress failed on device %d: %s\n", dev, cudaGetErrorString(e));
     return nullptr;
   }
-  g_dev_list[dev] = static_cast<SgItem*>(p);
-  return g_dev_list[dev];
+  g_dev_list[dev].store(static_cast<SgItem*>(p), std::memory_order_release);
+  return static_cast<SgItem*>(p);
 }
 
 }  // namespace
@@ -45,6 +48,13 @@ extern "C" int srpc_sg_copy_noalloc(const uint64_t* src, const uint64_t* dst, co
     return -1;
   }
   if (!src || !dst || !len) return -2;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(st, &cap) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return -4;
+  }
+  if (cap != cudaStreamCaptureStatusNone) return -5;  // a captured upload would read this stack frame at replay time
   int dev = -1;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return -3;
   SgItem* d_list = list_address(dev);
@@ -59,7 +69,6 @@ extern "C" int srpc_sg_copy_noalloc(const uint64_t* src, const uint64_t* dst, co
     items[i].first_chunk = 0;
   }
   const uint32_t chunks = sg_assign_chunks(items, n);
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
   // Pageable source: the runtime stages it before returning, so `items` may leave scope.
   if (cudaMemcpyAsync(d_list, items, sizeof(SgItem) * n, cudaMemcpyHostToDevice, st) != cudaSuccess) return -4;
   if (sg_launch_copy(d_list, n, chunks, SG_IMPL_SIMT, 0, st) != cudaSuccess) return -4;

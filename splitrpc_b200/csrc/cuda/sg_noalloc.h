@@ -26,12 +26,20 @@ extern "C" {
 // on `stream` (a cudaStream_t; null = the default stream) of the current device.
 // The arrays are host arrays; the addresses in them are device-visible addresses
 // (device memory, mapped pinned host memory or peer memory).  The call returns
-// after the launch has been queued; it does not wait for the copy.
+// once the list has been handed to the runtime and the kernel has been queued;
+// it does not wait for the copy itself.  The list is uploaded from this thread's
+// stack, i.e. from pageable memory, which the runtime stages before returning
+// and may do synchronously with the host; the caller's arrays can be reused as
+// soon as the call returns.
 //
 // Nothing is allocated: no cudaMalloc/cudaFree, no allocating library routine.
 // The first call on each device looks up the device address of the built-in list
-// array (cudaGetSymbolAddress with that device current) and keeps it; make that
-// first call outside any stream capture.
+// array (cudaGetSymbolAddress with that device current) and keeps it.
+//
+// Never call this while `stream` is being captured into a CUDA graph, neither the
+// first time nor later: the upload would be recorded as a copy from a stack frame
+// that is gone when the graph runs.  The call checks for an active capture and
+// refuses (-5) without touching the stream.
 //
 // All calls on a device share the one list array, and it keeps the previous
 // call's list until the next call overwrites it.  Two calls whose GPU work may
@@ -43,6 +51,7 @@ extern "C" {
 //   -2  a null array with n > 0, or a zero-length / over-4-GiB item
 //   -3  no usable CUDA device, or the set-up lookup failed
 //   -4  the list upload or the launch failed (see cudaGetLastError on the caller's runtime)
+//   -5  `stream` is being captured into a graph
 int srpc_sg_copy_noalloc(const uint64_t* src, const uint64_t* dst, const uint64_t* len, uint32_t n, void* stream);
 
 #ifdef __cplusplus

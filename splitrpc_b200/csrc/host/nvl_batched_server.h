@@ -3,7 +3,8 @@
 // NvlBatchedServer is the NVLink counterpart of the original's host-side batched GPU server (reference
 // src/splitrpc_rdma_transport/gpu_rdma_batched_server.cc:229-487): it owns one app with its request ring, response
 // ring and per-slot doorbells, answers a buf_mon ALLOC by exposing those three regions to the producer, then runs one
-// of the three worker modes (0 fixed batch, 1 stream armed, 2 dynamic batching) over the slots.  The producer (the
+// of the three worker modes (0 fixed batch, 1 stream armed, 2 dynamic batching) over the slots (a negative mode starts
+// no worker: the embedding program consumes the slots itself).  The producer (the
 // ingress process, the role of the original's SmartNIC proxy) fills slots and rings their doorbells from ITS side:
 // payload stores followed by a release store of RX_COMPLETE into the slot's state word, both issued by the ingress
 // GPU's gather kernel, so this server's CPU is not involved in a request's arrival.  Completion goes the other way
@@ -60,6 +61,7 @@ class NvlBatchedServer {
     app_->app_ctx->next_batch_size = max_batch_;
     app_server_.reset_quit();
     serving_.store(true);
+    if (server_mode_ < 0) return;  // the embedder runs the app itself (timing loops, tests)
     worker_ = std::thread([this] {
       switch (server_mode_) {
         case 1: app_server_.async_worker_loop(app_idx_); break;

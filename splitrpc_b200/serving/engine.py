@@ -1,9 +1,18 @@
 """Model serving engine: a model built from this library's kernels behind the native server.
 
-``ModelServer`` owns the loopback transport (pinned receive/transmit arenas the GPU
-maps), a graph app whose CUDA graphs hold the model's forward pass for every batch
-size, and the native server threads.  Python is only involved in building and
-capturing; the request hot path is native code and GPU kernels.
+Two roles, one per process:
+
+``ModelServer``   the ingress.  Owns the loopback transport (receive/transmit arenas in pinned host memory that
+                  the GPUs map), the native server threads (header parsing, reassembly, flow steering) and,
+                  unless ``local_replica=False``, one replica of the model on its own GPU.  Replicas on other
+                  GPUs are added with ``add_remote(path)``: the scatter-gather kernel of the ingress GPU then
+                  writes their request rings over NVLink and rings their slot doorbells itself.
+``ModelReplica``  a replica on another GPU (another process): the model's graphs behind a batched server that
+                  hands its rings and doorbells to the ingress (``buf_mon`` ALLOC handshake) and runs the worker.
+
+In both, the model's last kernel stores each response into the ingress transmit arena and completes the slot, so
+neither a scatter kernel nor a host thread sits between the result and the (emulated) NIC.  Python is only involved
+in building and capturing; the request hot path is native code and GPU kernels.
 """
 from __future__ import annotations
 
@@ -14,26 +23,20 @@ import torch
 from .. import _C
 
 MTU = 8192
+FUNC_ID = 1234
 
 
-class ModelServer:
-    def __init__(self, model, device: int = 0, max_batch: int = 64, server_mode: int = 2, copy_type: int = 2,
-                 outstanding: int | None = None, pool_size: int | None = None, batch_sizes=None, reserve_sms: int = 12,
-                 fused_ingress: bool = True):
-        """``reserve_sms``: SMs that the model's persistent kernels leave out of their grids, for the scatter-gather
-        kernel that pulls the next batch out of host memory while the current one is computed.  A persistent kernel
-        counts on one block per SM: with a foreign block on only a few SMs it takes twice as long (ResNet-50 graph
-        1.98 ms instead of 1.63 ms), with twelve SMs set aside it runs at 1.68 ms beside the copy."""
+class _GraphModelApp:
+    """A graph app for ``model`` on ``device``: rings, fused ingress set-up, one captured graph per batch size."""
+
+    def __init__(self, model, device: int, max_batch: int, copy_type: int, pool_size: int | None, batch_sizes,
+                 reserve_sms: int, fused_ingress: bool):
         self.model, self.device, self.max_batch = model, device, max_batch
         self.reserve_sms = reserve_sms
         _C.gemm_reserve_sms(reserve_sms)  # process-wide; must precede the graph captures below
         self.req_size, self.resp_size = model.req_size, model.resp_size
         _C.set_rpc_mtu(MTU)
         torch.cuda.set_device(device)
-        self.outstanding = outstanding or 2 * max_batch
-        frags = math.ceil(self.req_size / MTU) + math.ceil(self.resp_size / MTU)
-        n_slots = max(1024, 2 * self.outstanding * frags)
-        self.server_port, self.client_port = _C.make_loopback_pair(MTU, n_slots, "pinned")
         self.pool_size = pool_size or max(256, 4 * max_batch)
         self.app = _C.make_graph_app(device, self.req_size, self.resp_size, self.pool_size, max_batch, "gpu", copy_type)
         self.stream = torch.cuda.ExternalStream(self.app.work_stream, device=torch.device("cuda", device))
@@ -41,36 +44,68 @@ class ModelServer:
         # Fused ingress: the gather that pulls a request's fragments into the ring also deserialises them for the
         # model's first layer (models that offer enable_fused_ingress; GPU engine with one kernel per list).
         self.fused_ingress = False
+        self.ingress = None
         if fused_ingress and copy_type == 2 and hasattr(model, "enable_fused_ingress"):
             base, nbytes, doubled = self.app.req_ring
             slots = nbytes * (2 if doubled else 1) // self.req_size
-            tr = model.enable_fused_ingress(base, slots, self.req_size)
+            self.ingress = model.enable_fused_ingress(base, slots, self.req_size)
             _C.memset_async(base, 0, nbytes, self.app.work_stream)  # borders and padding channels stay zero for good
             self.stream.synchronize()
-            if not self.app.set_ingress_stem_s2d(tr["mean"], tr["inv_std"]):
-                raise RuntimeError("the scatter-gather engine does not support the fused ingress transform")
             self.fused_ingress = True
-            self.ingress = tr
         self._capture()
-        self.server = _C.Server(self.server_port, req_size=self.req_size, resp_size=self.resp_size, server_mode=server_mode,
-                                max_batch=max_batch, rr_pool_size=max(1023, 4 * self.outstanding), gather_burst=max_batch)
-        self.server.add_replica(self.app)
-        self._running = False
 
     def _capture(self) -> None:
-        """Warm-up run, then one captured graph per batch size; kernels read the ring through the stub."""
+        """Warm-up run, then one captured graph per batch size.  Kernels read the ring through the stub and the
+        response destinations through the push block, so one graph serves every ring position and every producer."""
         self.app.set_stub()
+        kw = dict(d_stub=self.app.d_stub, d_push=self.app.d_push)
         with torch.cuda.stream(self.stream):
-            self.model.forward(min(2, self.max_batch), d_stub=self.app.d_stub)
+            self.model.forward(min(2, self.max_batch), **kw)
         self.stream.synchronize()
         for bs in self.batch_sizes:
             with torch.cuda.stream(self.stream):
                 self.app.capture_begin()
                 try:
-                    self.model.forward(bs, d_stub=self.app.d_stub)
+                    self.model.forward(bs, **kw)
                 finally:
                     self.app.capture_end(bs)
         self.stream.synchronize()
+        self.app.set_self_push(True)  # the graphs' last kernel stores responses and completes slots
+
+
+class ModelServer(_GraphModelApp):
+    def __init__(self, model, device: int = 0, max_batch: int = 64, server_mode: int = 2, copy_type: int = 2,
+                 outstanding: int | None = None, pool_size: int | None = None, batch_sizes=None, reserve_sms: int = 12,
+                 fused_ingress: bool = True, n_replicas: int = 1, steer_policy: int = 0, device_completion: bool = True):
+        """``reserve_sms``: SMs that the model's persistent kernels leave out of their grids, for the scatter-gather
+        kernel that pulls the next batch out of host memory while the current one is computed.  A persistent kernel
+        counts on one block per SM: with a foreign block on only a few SMs it takes twice as long (ResNet-50 graph
+        1.98 ms instead of 1.63 ms), with twelve SMs set aside it runs at 1.68 ms beside the copy.
+
+        ``n_replicas``: how many replicas this ingress will feed in total (sizes the arenas and the request pool)."""
+        super().__init__(model, device, max_batch, copy_type, pool_size, batch_sizes, reserve_sms, fused_ingress)
+        self.copy_type = copy_type
+        self.outstanding = outstanding or 2 * max_batch * n_replicas
+        frags = math.ceil(self.req_size / MTU) + math.ceil(self.resp_size / MTU)
+        n_slots = max(1024, 2 * self.outstanding * frags)
+        # "shm_pinned": pinned and GPU-mapped like a NIC's registered rings, and a shared mapping, so that replicas
+        # in other processes can register the transmit arena with their GPUs and store responses into it
+        self.server_port, self.client_port = _C.make_loopback_pair(MTU, n_slots, "shm_pinned")
+        if self.fused_ingress and not self.app.set_ingress_stem_s2d(self.ingress["mean"], self.ingress["inv_std"]):
+            raise RuntimeError("the scatter-gather engine does not support the fused ingress transform")
+        self.server = _C.Server(self.server_port, req_size=self.req_size, resp_size=self.resp_size, server_mode=server_mode,
+                                max_batch=max_batch, rr_pool_size=max(1023, 4 * self.outstanding), gather_burst=max_batch,
+                                steer_policy=steer_policy, device_completion=1 if device_completion else 0)
+        self.server.add_replica(self.app)
+        self.n_remote = 0
+        self._running = False
+
+    def add_remote(self, path: str, timeout_ms: int = 60000) -> int:
+        """Connects to the ``ModelReplica`` listening at ``path`` and adds it to flow steering."""
+        idx = self.server.add_remote_replica(path, func_id=FUNC_ID, ingress_device=self.device, copy_type=self.copy_type,
+                                             timeout_ms=timeout_ms)
+        self.n_remote += 1
+        return idx
 
     def start(self) -> None:
         if not self._running:
@@ -81,10 +116,38 @@ class ModelServer:
         if self._running:
             self.server.stop()
             self._running = False
+        if self.n_remote:
+            self.server.release_remotes()
+            self.n_remote = 0
 
     def client(self, total: int, warmup: int, payload: str, verify: bool = False, **kw):
         return _C.Client(self.client_port, req_size=self.req_size, resp_size=self.resp_size, total=total, warmup=warmup,
                          payload=payload, verify=verify, **kw)
+
+    def __enter__(self):
+        self.start()
+        return self
+
+    def __exit__(self, *exc):
+        self.stop()
+
+
+class ModelReplica(_GraphModelApp):
+    """One replica of ``model`` on ``device`` for an ingress in another process (see ``ModelServer.add_remote``)."""
+
+    def __init__(self, model, path: str, device: int = 0, max_batch: int = 64, server_mode: int = 2, copy_type: int = 2,
+                 pool_size: int | None = None, batch_sizes=None, reserve_sms: int = 0, fused_ingress: bool = True):
+        super().__init__(model, device, max_batch, copy_type, pool_size, batch_sizes, reserve_sms, fused_ingress)
+        self.path = path
+        self.batched = _C.BatchedServer(self.app, path, func_id=FUNC_ID, server_mode=server_mode, max_batch=max_batch)
+        if self.fused_ingress:
+            self.batched.set_ingress_stem_s2d(self.ingress["mean"], self.ingress["inv_std"])
+
+    def start(self) -> None:
+        self.batched.start()
+
+    def stop(self) -> None:
+        self.batched.stop()
 
     def __enter__(self):
         self.start()

@@ -1,4 +1,5 @@
-"""Multi-GPU checks (fused tensor-parallel kernels, cross-GPU scatter-gather); skipped with fewer than 2 GPUs."""
+"""Multi-GPU checks (fused tensor-parallel kernels, cross-GPU scatter-gather, single-ingress serving across
+processes); skipped with fewer than 2 GPUs.  The world size follows the number of GPUs (largest power of two, at most 8)."""
 import os
 import subprocess
 import sys
@@ -8,16 +9,31 @@ import pytest
 pytestmark = pytest.mark.gpu
 
 
-def test_tensor_parallel_and_cross_gpu_paths():
+def _world():
     import torch
 
     n = torch.cuda.device_count()
     if n < 2:
         pytest.skip("needs at least 2 GPUs")
-    world = 2
-    script = os.path.join(os.path.dirname(os.path.abspath(__file__)), "multi_gpu", "tp_check.py")
+    w = 2
+    while w * 2 <= min(n, 8):
+        w *= 2
+    return w
+
+
+def _torchrun(script, world, port):
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "multi_gpu", script)
     env = dict(os.environ, NCCL_NVLS_ENABLE="0", TORCH_SYMM_MEM_DISABLE_MULTICAST="1")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr",
-           "127.0.0.1", "--master-port", "29533", script]
-    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+           "127.0.0.1", "--master-port", str(port), path]
+    return subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=900)
+
+
+def test_tensor_parallel_and_cross_gpu_paths():
+    r = _torchrun("tp_check.py", _world(), 29533)
     assert r.returncode == 0 and "MULTI_GPU_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+
+
+def test_single_ingress_serving_across_gpus():
+    r = _torchrun("ingress_check.py", _world(), 29534)
+    assert r.returncode == 0 and "INGRESS_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]

@@ -53,3 +53,29 @@ def test_no_alloc_copy_matches_regular_entry_point(C):
     too_many = [(src.data_ptr(), got.data_ptr(), 16)] * 1025
     assert _call(lib, too_many) == -1
     assert _call(lib, []) == 0
+    # malformed lists: a zero-length item, null arrays
+    assert _call(lib, [(src.data_ptr(), got.data_ptr(), 0)]) == -2
+    null = ctypes.POINTER(ctypes.c_uint64)()
+    assert lib.srpc_sg_copy_noalloc(null, null, null, ctypes.c_uint32(3), ctypes.c_void_p(0)) == -2
+    # exactly the largest list, on a stream of the caller's
+    n = 1024
+    src2 = torch.randint(0, 256, (n * 48,), dtype=torch.uint8, device="cuda")
+    ref2, got2 = torch.zeros_like(src2), torch.zeros_like(src2)
+    full_ref = [(src2.data_ptr() + 48 * i, ref2.data_ptr() + 48 * i, 33 + i % 15) for i in range(n)]
+    full_new = [(s_, got2.data_ptr() + (d_ - ref2.data_ptr()), l_) for s_, d_, l_ in full_ref]
+    C.sg_copy(full_ref[:512], 0)
+    C.sg_copy(full_ref[512:], 0)
+    user = torch.cuda.Stream()
+    user.wait_stream(torch.cuda.current_stream())
+    assert _call(lib, full_new, user.cuda_stream) == 0
+    user.synchronize()
+    torch.cuda.synchronize()
+    assert torch.equal(got2, ref2)
+    # a stream that is being captured is refused, and the capture stays usable
+    cap_stream = torch.cuda.Stream()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=cap_stream):
+        assert _call(lib, full_new[:4], cap_stream.cuda_stream) == -5
+        got2.add_(0)
+    g.replay()
+    torch.cuda.synchronize()
