@@ -114,6 +114,26 @@ int ref_scatter_batch(void* engine, uint64_t src, uint64_t resp_size, uint64_t d
   return 0;
 }
 
+// Scatters `n_req` multi-fragment responses: response r (resp_size bytes at src + r * resp_size) goes into
+// `frags_per_resp` transmit buffers of `frag_len` bytes (the last one `last_len`) that sit `frag_stride` bytes apart
+// from dst + r * resp_stride on.
+int ref_scatter_batch_frags(void* engine, uint64_t src, uint64_t resp_size, uint64_t dst, uint64_t resp_stride, uint64_t frag_stride,
+                            uint32_t frag_len, uint32_t last_len, int frags_per_resp, int n_req) {
+  RefEngine* e = (RefEngine*)engine;
+  cudaSetDevice(e->device);
+  for (int r = 0; r < n_req; r++) {
+    e->bufs->num_items = (uint16_t)frags_per_resp;
+    for (int f = 0; f < frags_per_resp; f++) {
+      e->bufs->burst_items[f] = (uintptr_t)(dst + (uint64_t)r * resp_stride + (uint64_t)f * frag_stride);
+      e->bufs->item_size[f] = f == frags_per_resp - 1 ? last_len : frag_len;
+    }
+    scatter_skbs(e->skb, e->bufs, (uint8_t*)(uintptr_t)(src + (uint64_t)r * resp_size));
+    if (!upload_stub(e->scatter_ctx, e->skb) || sg_on_gpu(e->scatter_ctx, e->skb) != 1) return r + 1;
+    e->scatter_ctx->WaitForAppRunComplete();
+  }
+  return 0;
+}
+
 // Number of copy items the original's list builder makes of one such request (shows whether fragments coalesced).
 int ref_items_per_request(void* engine, uint64_t src, uint64_t frag_stride, uint32_t frag_len, uint32_t last_len, int frags_per_req) {
   RefEngine* e = (RefEngine*)engine;

@@ -58,6 +58,9 @@ def load_library():
     lib.ref_scatter_batch.restype = ctypes.c_int
     lib.ref_scatter_batch.argtypes = [ctypes.c_void_p, ctypes.c_uint64, ctypes.c_uint64, ctypes.c_uint64, ctypes.c_uint64,
                                       ctypes.c_int]
+    lib.ref_scatter_batch_frags.restype = ctypes.c_int
+    lib.ref_scatter_batch_frags.argtypes = [ctypes.c_void_p, ctypes.c_uint64, ctypes.c_uint64, ctypes.c_uint64, ctypes.c_uint64,
+                                            ctypes.c_uint64, ctypes.c_uint32, ctypes.c_uint32, ctypes.c_int, ctypes.c_int]
     lib.ref_items_per_request.restype = ctypes.c_int
     lib.ref_items_per_request.argtypes = [ctypes.c_void_p, ctypes.c_uint64, ctypes.c_uint64, ctypes.c_uint32, ctypes.c_uint32,
                                           ctypes.c_int]
@@ -294,11 +297,83 @@ class Pipeline:
         self.lib.ref_engine_destroy(self.engine)
 
 
+def run_echo(lib, args, rank, world, local_rank):
+    """Echo sweep on the original's copy path: per request gather (list builder + CopyKernel + sync), the echo app's
+    device-to-device cudaMemcpyAsync (src/apps/echo_rpc_bench.cc:25-36) + sync per batch, per response scatter + sync.
+    The original serves one GPU; with N > 1 every rank runs this by itself and the rates are summed."""
+    import torch
+
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("gloo")
+    copy_type = int(os.environ.get("SPLITRPC_REF_COPY_TYPE", "2"))
+    engine = lib.ref_engine_create(local_rank, copy_type)
+    dev = torch.device("cuda", local_rank)
+    stride = MTU + MBUF_GAP
+    sweep = []
+    for size in [1 << k for k in range(6, 23)]:
+        frags = (size + MTU - 1) // MTU
+        last = size - (frags - 1) * MTU
+        frag_len = min(MTU, size)
+        batch = 64 if size <= (1 << 18) else (16 if size <= (1 << 20) else 8)
+        rx = torch.randint(0, 256, (batch * frags * stride,), dtype=torch.uint8).pin_memory()
+        tx = torch.zeros(batch * frags * stride, dtype=torch.uint8).pin_memory()
+        req_ring = torch.zeros(batch * size, dtype=torch.uint8, device=dev)
+        resp_ring = torch.zeros(batch * size, dtype=torch.uint8, device=dev)
+        n_batches = int(max(3, min(200, 0.3 * 13e9 / (batch * max(size, 4096)))))
+
+        def one_batch():
+            rc = lib.ref_gather_batch(engine, rx.data_ptr(), frags * stride, stride, frag_len, last, frags, req_ring.data_ptr(), size, batch)
+            resp_ring.copy_(req_ring, non_blocking=True)
+            torch.cuda.synchronize()
+            rc |= lib.ref_scatter_batch_frags(engine, resp_ring.data_ptr(), size, tx.data_ptr(), frags * stride, stride, frag_len, last, frags, batch)
+            if rc:
+                raise RuntimeError("original copy engine failed")
+
+        one_batch()
+        t0 = time.perf_counter()
+        for _ in range(n_batches):
+            one_batch()
+        wall = time.perf_counter() - t0
+        ok = all(bool(torch.equal(tx[f * stride:f * stride + (frag_len if f < frags - 1 else last)],
+                                  rx[f * stride:f * stride + (frag_len if f < frags - 1 else last)])) for f in range(min(frags, 3)))
+        rps = batch * n_batches / wall
+        sweep.append({"bytes": size, "fragments": frags, "batch": batch, "req_s": round(rps, 1), "gather_gbs": round(rps * size / 1e9, 3),
+                      "verified": ok})
+    lib.ref_engine_destroy(engine)
+    if dist:
+        import torch.distributed as dist2
+
+        for s in sweep:
+            t = torch.tensor([s["req_s"], s["gather_gbs"]], dtype=torch.float64)
+            dist2.all_reduce(t)
+            s["req_s"], s["gather_gbs"] = round(float(t[0]), 1), round(float(t[1]), 3)
+        dist2.barrier()
+        dist2.destroy_process_group()
+    best = max(sweep, key=lambda s: s["gather_gbs"])
+    return {"metric": "payload GB/s gathered into GPU batch buffers and echoed (best size of the sweep), end to end", "value": best["gather_gbs"],
+            "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": None, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "uint8", "data": "synthetic", "impl": "reference",
+            "reference_class": "re-hosted original copy path (g_copy_ng.cu, unmodified) + its echo app's device memcpy; host clock",
+            "config": {"model": "echo, 64 B - 4 MB payloads in 8 KB fragments", "global_batch": None, "seq_len": None,
+                       "parallelism": f"dp{world}, one independent copy engine per GPU" if world > 1 else "dp1",
+                       "copy_type": copy_type},
+            "sweep": sweep, "all_verified": all(s["verified"] for s in sweep)}
+
+
 def run(args, rank, world, local_rank, cfg):
     """Returns the JSON dict of the reference arm (or an ``unavailable`` dict)."""
     lib, why = load_library()
     if lib is None:
         return {"impl": "reference", "unavailable": why}
+    if args.config == "lenet5":
+        return {"impl": "reference", "unavailable": "the original has no CPU device: its LeNet is a set of generated GPU kernels "
+                "behind the DPDK server, so the GPU-less plumbing configuration has no counterpart to run"}
+    if args.config == "echo":
+        return run_echo(lib, args, rank, world, local_rank)
     if args.config == "bert_large_tp":
         return {"impl": "reference", "unavailable": "the original has no multi-GPU path at all (no NCCL, no peer copies); its "
                 "library stand-in for tensor parallelism (NCCL all-gather / reduce-scatter + cuBLAS) is timed per operation by "

@@ -1,25 +1,29 @@
-"""Headline benchmark: requests/s of dynamic-batched model serving, per GPU replica.
+"""Headline benchmark: requests/s of dynamic-batched model serving behind ONE ingress.
 
-    python bench.py --gpus N --steps K --warmup W [--config resnet50|bert_base|lenet5|echo]
+    python bench.py --gpus N --steps K --warmup W [--config resnet50|bert_base|bert_large_tp|lenet5|echo]
+                    [--impl ours|reference] [--slo-ms 10]
 
-One process per GPU (launched under torchrun for N > 1; RANK/LOCAL_RANK/WORLD_SIZE
-come from the environment).  Every rank serves one data-parallel replica of the
-model on its GPU.  A "step" is one full batch (``max_batch`` requests) through
-the serving path.  Two numbers are produced:
+One process per GPU (launched under torchrun for N > 1; RANK/LOCAL_RANK/WORLD_SIZE come from the environment).
+Rank 0 is the ingress: it owns the loopback transport (an emulated NIC that DMA-writes into pinned host rings which
+GPU 0 maps), parses headers, reassembles and steers.  Every rank serves one data-parallel replica of the model on its
+GPU; the replicas of ranks > 0 sit behind batched servers that handed their request rings and slot doorbells to rank 0.
+A "step" is one full batch (``max_batch`` requests) per GPU.  Numbers:
 
-* ``value``: device-timed.  K steps of {scatter-gather kernel that pulls the
-  batch's 8 KB fragments out of the pinned receive arena into the request ring,
-  the model's CUDA graph, the response scatter kernel into the pinned transmit
-  arena}, bracketed by CUDA events on the serving stream, max over ranks.
-* ``e2e``: the same metric through the public serving API: the load generator
-  sends fragmented requests over the loopback transport (an emulated NIC that
-  DMA-writes into pinned host rings), the native server reassembles, gathers,
-  batches dynamically, runs the graphs and sends responses, and the client
-  receives them on the host.  The host->device bytes are the request fragments
-  the GPU pulls from pinned memory; the device->host bytes are the responses.
+* ``value`` (device-timed, single ingress): K steps of {GPU 0's scatter-gather kernel pulls a batch's 8 KB fragments
+  out of the pinned arena, deserialises them, stores them into the serving GPU's request ring (over NVLink for
+  replicas on other GPUs) and rings the slot doorbells; the serving GPU's stream, parked on the last doorbell, runs
+  the model's CUDA graph, whose last kernel stores the responses into the ingress transmit arena and completes the
+  slots}.  No host thread takes part between the first doorbell and the last completion.  Timed with CUDA events on
+  every rank's serving stream, max over ranks.
+* ``e2e``: the same metric through the public serving API: the load generator sends fragmented requests over the
+  loopback transport, the native server reassembles, steers, gathers; the replicas batch dynamically and answer; the
+  client receives the responses on the host.  Host->device bytes are the request fragments GPU 0 pulls from pinned
+  memory; device->host bytes are the responses.  Run for about two seconds, with the payloads handed over by
+  reference (registered buffers) and, for comparison, copied into the receive arena by the emulated DMA.
+* ``ingress_per_gpu``: the earlier arrangement, every GPU with its own transport, server and load generator (N
+  independent single-GPU servers), device-timed and end to end, as a second, labelled number.
 
-Rank 0 prints one JSON line.  ``--impl reference`` reports why the original
-server cannot run here.
+Rank 0 prints one JSON line.  ``--impl reference`` runs the original's data path (see baseline/reference_arm.py).
 """
 from __future__ import annotations
 
@@ -29,6 +33,7 @@ import os
 import statistics
 import subprocess
 import sys
+import tempfile
 import threading
 import time
 
@@ -40,7 +45,14 @@ CONFIGS = {
     "bert_base": dict(model="BERT-base bf16 classifier, seq 128 int32 ids", max_batch=32, payload="ids", seq=128),
     "bert_large_tp": dict(model="BERT-large bf16 classifier, seq 384 int32 ids, tensor parallel over all GPUs",
                           max_batch=16, payload="ids", seq=384),
+    "lenet5": dict(model="LeNet-5 fp32 on the CPU device, 1x28x28 fp32 requests (3136 B, one fragment)", max_batch=32,
+                   payload="uniform", seq=None),
+    "echo": dict(model="echo / scatter-gather microbenchmark, 64 B - 4 MB payloads in 8 KB fragments", max_batch=64,
+                 payload="echo", seq=None),
 }
+RX_COMPLETE, WORK_COMPLETE = 1, 2
+PCIE_GBS = 55.0      # measured rate of one large pinned-host -> GPU copy on these machines
+NVLINK_GBS = 770.0   # measured peer copy rate per direction
 
 
 class ClockSampler:
@@ -64,7 +76,28 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.samples.append([f.strip() for f in line.split(",")])
+            self.samples.append((time.perf_counter(), [f.strip() for f in line.split(",")]))
+
+    def mark(self) -> float:
+        return time.perf_counter()
+
+    def summary(self, t_from: float | None = None, t_to: float | None = None) -> dict:
+        sm, mx, pw, reasons = [], 0, [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for t, s in list(self.samples):
+            if (t_from is not None and t < t_from) or (t_to is not None and t > t_to):
+                continue
+            try:
+                sm.append(float(s[0]))
+                mx = max(mx, float(s[1]))
+                pw.append(float(s[2]))
+                for n, v in zip(names, s[3:7]):
+                    if v.lower().startswith("active"):
+                        reasons.add(n)
+            except (ValueError, IndexError):
+                continue
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx or None, "reasons": sorted(reasons),
+                "samples": len(sm), "power_w_max": max(pw) if pw else None}
 
     def stop(self) -> dict:
         if self.proc:
@@ -73,19 +106,7 @@ class ClockSampler:
                 self.proc.wait(timeout=2)
             except subprocess.TimeoutExpired:
                 self.proc.kill()
-        sm, mx, reasons = [], 0, set()
-        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
-        for s in self.samples:
-            try:
-                sm.append(float(s[0]))
-                mx = max(mx, float(s[1]))
-                for n, v in zip(names, s[3:7]):
-                    if v.lower().startswith("active"):
-                        reasons.add(n)
-            except (ValueError, IndexError):
-                continue
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx or None, "reasons": sorted(reasons),
-                "samples": len(sm)}
+        return self.summary()
 
 
 def build_model(config: str, device: int):
@@ -93,54 +114,155 @@ def build_model(config: str, device: int):
         from splitrpc_b200.models import ResNet50
 
         return ResNet50(device=device, max_batch=CONFIGS[config]["max_batch"])
-    if config == "lenet5":
-        raise SystemExit("lenet5 is served by the built-in app: see tests/test_gpu_sg.py and serving.smoke_test")
     if config == "bert_base":
         from splitrpc_b200.models import BertClassifier, BERT_BASE
 
         return BertClassifier(BERT_BASE, seq=128, device=device, max_batch=CONFIGS[config]["max_batch"])
-    raise SystemExit(f"unknown config {config}")
+    raise SystemExit(f"unknown model config {config}")
 
 
-def device_timed(srv, steps: int, warmup: int):
-    """K steps of gather -> graph -> response scatter, timed with CUDA events on the serving stream.
+def sock_path(rank: int) -> str:
+    return os.path.join(tempfile.gettempdir(), f"splitrpc_bench_{os.environ.get('MASTER_PORT', str(os.getpid()))}_{rank}.sock")
 
-    The step is issued the way the server issues it: the gather of batch i+1 runs on the scatter-gather stream while
-    the model graph of batch i runs on the work stream, over two windows of the request/response rings.  The timed
-    region starts with both streams idle and ends when the last response scatter has finished, so it contains K
-    gathers, K graphs, K scatters and K L2 flushes.
-    """
+
+# ----------------------------------------------------------------------------------------------- device-timed
+def device_timed_single_ingress(node, rank: int, world: int, steps: int, warmup: int, barrier, payload_kind: str):
+    """K steps of the doorbell-driven pipeline described in the module docstring.  ``node`` is the ModelServer (rank 0,
+    remotes already added, server not started) or the ModelReplica (ranks > 0, batched server without a worker).
+    Returns this rank's CUDA-event time for the K steps in ms and the number of kernels it launched in them."""
     import torch
 
     from splitrpc_b200 import _C
 
-    app, nb = srv.app, srv.max_batch
-    req, resp = srv.req_size, srv.resp_size
-    mtu = 8192
-    n_sets = 2
-    # Two batches worth of fragments in pinned, GPU-mapped host memory, one per ring window.
+    app, nb, req, resp = node.app, node.max_batch, node.req_size, node.resp_size
+    dev = torch.device("cuda", node.device)
+    # three ring windows per replica: one being computed, one gathered and waiting, one being gathered
+    n_sets, mtu, total = 3, 8192, warmup + steps
+    stream = node.stream
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    req_base, resp_base = app.req_ring[0], app.resp_ring[0]
+    if rank == 0:
+        app.reset_slots()
+    launches = 0
+    produce = None
+    lists = []
+    if rank == 0:
+        srv = node.server
+        _, tx_dev, tx_bytes, tx_slot = srv.tx_arena
+        assert world * n_sets * nb * tx_slot <= tx_bytes, "transmit arena too small for the timing loop"
+        pinned = torch.empty(n_sets * world * nb * req, dtype=torch.uint8).pin_memory()
+        if payload_kind == "ids":
+            pinned.view(torch.int32).random_(0, 30522)
+        else:
+            pinned.view(torch.float32).normal_()
+        sg_streams = [torch.cuda.Stream(device=dev) for _ in range(world)]  # one per replica: no head-of-line blocking
+        rings = [dict(req_base=req_base, states_dev=app.states_dev)] + [srv.remote_rings(r - 1) for r in range(1, world)]
+        for r in range(world):
+            per_w = []
+            for w in range(n_sets):
+                items, bells = [], []
+                for j in range(nb):
+                    src = pinned.data_ptr() + ((w * world + r) * nb + j) * req
+                    dst = rings[r]["req_base"] + (w * nb + j) * req
+                    off = 0
+                    while off < req:  # one item per 8 KB fragment, as the reassembly delivers them
+                        ln = min(mtu, req - off)
+                        items.append((src + off, dst + off, ln))
+                        off += ln
+                    bells.append(rings[r]["states_dev"] + 4 * (w * nb + j))
+                    tx_off = ((r * n_sets + w) * nb + j) * tx_slot
+                    if r == 0:
+                        app.set_tx_off(w * nb + j, tx_off)
+                    else:
+                        srv.remote_set_tx_off(r - 1, w * nb + j, tx_off)
+                per_w.append(_C.sg_list_create(items, bells))
+            lists.append(per_w)
+        gb = -node.reserve_sms if node.reserve_sms > 0 else 48  # PCIe-bound: a few fat blocks on the reserved SMs
+
+        def produce(i):
+            w = i % n_sets
+            for r in range(world):
+                sg = sg_streams[r].cuda_stream
+                if i >= n_sets:  # the replica has consumed what this window held n_sets steps ago
+                    _C.stream_wait32(sg, rings[r]["states_dev"] + 4 * (w * nb + nb - 1), WORK_COMPLETE)
+                if node.fused_ingress:  # gather + deserialise + doorbells in one kernel, as the server's engine does
+                    _C.sg_list_launch_stem_s2d(lists[r][w], rings[r]["req_base"], req, node.ingress["mean"], node.ingress["inv_std"],
+                                               gb, sg, bell_value=RX_COMPLETE)
+                else:
+                    _C.sg_list_launch(lists[r][w], 0, gb, sg, bell_value=RX_COMPLETE)
+            return world
+
+    def consume(i):
+        w = i % n_sets
+        st = stream.cuda_stream
+        _C.stream_wait32(st, app.states_dev + 4 * (w * nb + nb - 1), RX_COMPLETE)
+        # re-point the stub (request / response window) and the window's first slot in stream order
+        _C.stream_write64(st, app.d_stub, req_base + w * nb * req)
+        _C.stream_write64(st, app.d_stub + 8, resp_base + w * nb * resp)
+        _C.stream_write32(st, app.d_first_slot, w * nb)
+        app.launch(nb)  # the graph; its last kernel stores the responses into rank 0's arena and completes the slots
+        with torch.cuda.stream(stream):
+            flush.zero_()  # L2 flush between iterations (inside the timed region)
+        return node.model.kernels_per_forward
+
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with torch.cuda.stream(stream):
+        flush.zero_()  # loads the fill kernel before the stream is first parked on a doorbell
+    stream.synchronize()
+    for i in range(warmup):
+        if produce:
+            produce(i)
+        consume(i)
+    stream.synchronize()
+    barrier()
+    t0.record(stream)
+    for i in range(warmup, total):
+        if produce:
+            launches += produce(i)
+        launches += consume(i)
+    t1.record(stream)
+    stream.synchronize()
+    torch.cuda.synchronize()
+    ms = t0.elapsed_time(t1)
+    barrier()
+    ok = all(app.slot_state(s) == WORK_COMPLETE for s in range(n_sets * nb))
+    for per_w in lists:
+        for h in per_w:
+            _C.sg_list_destroy(h)
+    if not ok:
+        raise RuntimeError("device-timed loop: a slot was not completed by the serving GPU")
+    return ms, launches
+
+
+def device_timed_per_gpu(srv, steps: int, warmup: int):
+    """The independent arrangement: this GPU gathers its own batches from its own pinned arena (gather of batch i+1 on
+    a second stream beside the graph of batch i), runs the graph, whose last kernel stores the responses into the
+    transmit arena.  CUDA events on the serving stream."""
+    import torch
+
+    from splitrpc_b200 import _C
+
+    app, nb, req, resp = srv.app, srv.max_batch, srv.req_size, srv.resp_size
+    mtu, n_sets = 8192, 2
     pinned = torch.empty(n_sets * nb * req, dtype=torch.uint8).pin_memory()
-    pinned.random_(0, 256) if req < 4096 else pinned.view(torch.float32).normal_()
-    if srv.model.__class__.__name__ == "BertClassifier":
-        pinned.view(torch.int32).random_(0, 30522)
-    tx = torch.empty(n_sets * nb * max(resp, 16), dtype=torch.uint8).pin_memory()
-    req_base, _, _ = app.req_ring
-    resp_base, _, _ = app.resp_ring
-    stubs = torch.empty(n_sets, 2, dtype=torch.int64).pin_memory()  # (request window, response window) per set
-    lists, out_lists = [], []
+    pinned.view(torch.float32).normal_() if req >= 4096 else pinned.view(torch.int32).random_(0, 30522)
+    req_base, resp_base = app.req_ring[0], app.resp_ring[0]
+    _, tx_dev, tx_bytes, tx_slot = srv.server.tx_arena
+    app.reset_slots()
+    stubs = torch.empty(n_sets, 2, dtype=torch.int64).pin_memory()
+    first = torch.empty(n_sets, dtype=torch.int32).pin_memory()
+    lists = []
     for s in range(n_sets):
         items = []
         for r in range(nb):
             off = 0
-            while off < req:  # one item per 8 KB fragment, as the reassembly delivers them
+            while off < req:
                 ln = min(mtu, req - off)
                 items.append((pinned.data_ptr() + (s * nb + r) * req + off, req_base + (s * nb + r) * req + off, ln))
                 off += ln
+            app.set_tx_off(s * nb + r, (s * nb + r) * tx_slot)
         lists.append(_C.sg_list_create(items))
-        out_lists.append(_C.sg_list_create(
-            [(resp_base + (s * nb + r) * resp, tx.data_ptr() + (s * nb + r) * resp, resp) for r in range(nb)]))
-        stubs[s, 0] = req_base + s * nb * req
-        stubs[s, 1] = resp_base + s * nb * resp
+        stubs[s, 0], stubs[s, 1], first[s] = req_base + s * nb * req, resp_base + s * nb * resp, s * nb
     stream = srv.stream
     sg_stream = torch.cuda.Stream(device=srv.device)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=f"cuda:{srv.device}")
@@ -148,25 +270,24 @@ def device_timed(srv, steps: int, warmup: int):
     gathered = [torch.cuda.Event() for _ in range(total)]
     done = [torch.cuda.Event() for _ in range(total)]
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    gb = -srv.reserve_sms if srv.reserve_sms > 0 else 48
 
     def step(i):
         w = i % n_sets
         if i >= n_sets:
-            sg_stream.wait_event(done[i - n_sets])  # the window's previous batch has been answered
-        # PCIe-bound: a few 1024-thread blocks on the SMs that the model's persistent kernels leave free
-        gb = -srv.reserve_sms if srv.reserve_sms > 0 else 48
-        if srv.fused_ingress:  # gather + deserialise in one kernel, as the server's engine does
+            sg_stream.wait_event(done[i - n_sets])
+        if srv.fused_ingress:
             _C.sg_list_launch_stem_s2d(lists[w], req_base, req, srv.ingress["mean"], srv.ingress["inv_std"], gb, sg_stream.cuda_stream)
         else:
             _C.sg_list_launch(lists[w], 0, gb, sg_stream.cuda_stream)
         gathered[i].record(sg_stream)
         stream.wait_event(gathered[i])
-        # the stub is re-pointed in stream order, as the stream-armed server mode does
-        _C.memcpy_async(app.d_stub, stubs[w].data_ptr(), 16, stream.cuda_stream)
+        _C.stream_write64(stream.cuda_stream, app.d_stub, int(stubs[w, 0]))
+        _C.stream_write64(stream.cuda_stream, app.d_stub + 8, int(stubs[w, 1]))
+        _C.stream_write32(stream.cuda_stream, app.d_first_slot, int(first[w]))
         app.launch(nb)
-        _C.sg_list_launch(out_lists[w], 0, 0, stream.cuda_stream)
         with torch.cuda.stream(stream):
-            flush.zero_()  # L2 flush between iterations (inside the timed region)
+            flush.zero_()
         done[i].record(stream)
 
     for i in range(warmup):
@@ -180,19 +301,65 @@ def device_timed(srv, steps: int, warmup: int):
     t1.record(stream)
     stream.synchronize()
     sg_stream.synchronize()
-    app.set_stub()
-    ms_total = t0.elapsed_time(t1)
-    for h in lists + out_lists:
+    ms = t0.elapsed_time(t1)
+    app.reset_slots()
+    for h in lists:
         _C.sg_list_destroy(h)
-    return [ms_total / steps] * steps
+    return ms
+
+
+# ----------------------------------------------------------------------------------------------- end to end
+def closed_loop(srv, n_req: int, n_warm: int, outstanding: int, payload: str, by_reference: bool) -> dict:
+    cli = srv.client(total=n_req + n_warm, warmup=n_warm, payload=payload, n_payloads=min(outstanding, 256),
+                     send_by_reference=by_reference)
+    t0 = time.perf_counter()
+    ok = cli.run_closed_loop(outstanding)
+    wall = time.perf_counter() - t0
+    st = cli.post_process()
+    return {"ok": bool(ok), "rps": st.get("throughput_est", 0.0) if ok else 0.0, "p50_us": st.get("p50_sojournTime_us", 0.0),
+            "p99_us": st.get("p99_sojournTime_us", 0.0), "requests": n_req, "seconds": round(wall, 3), "received": int(cli.received)}
+
+
+class PerGpuIngress:
+    """A per-GPU ingress around the already captured app of a ModelReplica (second, labelled number of the bench)."""
+
+    def __init__(self, rep, outstanding: int):
+        import math
+
+        from splitrpc_b200 import _C
+
+        self.app, self.model, self.device, self.max_batch = rep.app, rep.model, rep.device, rep.max_batch
+        self.stream, self.req_size, self.resp_size = rep.stream, rep.req_size, rep.resp_size
+        self.fused_ingress, self.ingress, self.reserve_sms = rep.fused_ingress, rep.ingress, rep.reserve_sms
+        self.app.reset_slots()
+        frags = math.ceil(self.req_size / 8192) + math.ceil(self.resp_size / 8192)
+        self.server_port, self.client_port = _C.make_loopback_pair(8192, max(1024, 2 * outstanding * frags), "shm_pinned")
+        if self.fused_ingress:
+            self.app.set_ingress_stem_s2d(self.ingress["mean"], self.ingress["inv_std"])
+        self.server = _C.Server(self.server_port, req_size=self.req_size, resp_size=self.resp_size, server_mode=2,
+                                max_batch=self.max_batch, rr_pool_size=max(1023, 4 * outstanding), gather_burst=self.max_batch)
+        self.server.add_replica(self.app)
+
+    def start(self):
+        self.server.start()
+
+    def stop(self):
+        self.server.stop()
+
+    def client(self, total, warmup, payload, **kw):
+        from splitrpc_b200 import _C
+
+        return _C.Client(self.client_port, req_size=self.req_size, resp_size=self.resp_size, total=total, warmup=warmup,
+                         payload=payload, verify=False, **kw)
 
 
 def run_ours(args, rank: int, world: int, local_rank: int) -> dict:
     import torch
 
     from splitrpc_b200 import ops
-    from splitrpc_b200.serving import ModelServer
+    from splitrpc_b200.serving import ModelReplica, ModelServer
 
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     cfg = CONFIGS[args.config]
     nb = cfg["max_batch"]
     torch.cuda.set_device(local_rank)
@@ -201,78 +368,151 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> dict:
         import torch.distributed as dist
 
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    warm = max(args.warmup, 3)
     model = build_model(args.config, local_rank)
-    outstanding = 3 * nb  # closed-loop depth: one batch running, one being gathered, one in the clients' hands
-    srv = ModelServer(model, device=local_rank, max_batch=nb, server_mode=2, copy_type=2, outstanding=outstanding)
+    # closed-loop depth per replica: one batch running, one being gathered, one in the clients' hands
+    outstanding = 3 * nb * world
+    pool = max(256, 4 * nb)
 
     def barrier():
+        torch.cuda.synchronize()
         if dist:
             dist.barrier()
-        torch.cuda.synchronize()
 
-    # ---- device-timed
+    def allmax(v: float) -> float:
+        t = torch.tensor([v], device="cuda", dtype=torch.float64)
+        if dist:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def allsum(v: float) -> float:
+        t = torch.tensor([v], device="cuda", dtype=torch.float64)
+        if dist:
+            dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        return float(t.item())
+
+    # ---- roles: rank 0 = ingress + replica, the others = replicas behind batched servers
+    if rank == 0:
+        node = ModelServer(model, device=local_rank, max_batch=nb, server_mode=2, copy_type=2, outstanding=outstanding,
+                           pool_size=pool, n_replicas=world)
+    else:
+        node = ModelReplica(model, sock_path(rank), device=local_rank, max_batch=nb, server_mode=-1, pool_size=pool,
+                            reserve_sms=12)
+        node.start()
     barrier()
+    if rank == 0:
+        for r in range(1, world):
+            node.add_remote(sock_path(r))
+    barrier()
+
+    # ---- device-timed, single ingress
     sampler = ClockSampler(local_rank)
     sampler.start()
-    ms = device_timed(srv, args.steps, max(args.warmup, 3))
-    barrier()
-    total_ms = sum(ms)
-    t = torch.tensor([total_ms], device="cuda", dtype=torch.float64)
-    if dist:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    max_total_ms = float(t.item())
+    m0 = sampler.mark()
+    ms, launches = device_timed_single_ingress(node, rank, world, args.steps, warm, barrier, cfg["payload"])
+    m1 = sampler.mark()
+    max_ms = allmax(ms)
+    total_launches = int(allsum(launches))
     ops.check_status()
-    value = world * nb * args.steps / (max_total_ms / 1e3)
+    value = world * nb * args.steps / (max_ms / 1e3)
 
-    # ---- end to end through the public API
+    # ---- end to end through the public API, single ingress
+    if rank == 0:
+        node.stop()  # releases the worker-less batched servers
     barrier()
-    n_req = nb * args.steps
-    n_warm = nb * max(args.warmup, 3)
-    srv.start()
-    # Requests are sent by reference: the payload pool sits in pinned, GPU-mapped host memory (as a NIC's registered
-    # buffers would) and only headers + descriptors cross the emulated wire; the GPU pulls every fragment of every
-    # request out of that host memory each step.
-    cli = srv.client(total=n_req + n_warm, warmup=n_warm, payload=cfg["payload"], n_payloads=outstanding, send_by_reference=True)
+    if rank > 0:
+        node.serve(server_mode=2)
+        node.start()
     barrier()
-    ok = cli.run_closed_loop(outstanding)
-    st = cli.post_process()
+    e2e = {}
+    n_req = int(min(400000, max(nb * args.steps * world, args.e2e_seconds * value)))
+    n_warm = max(nb * warm * world, n_req // 20)
+    m2 = m3 = sampler.mark()
+    if rank == 0:
+        node.new_server(server_mode=2, outstanding=outstanding, n_replicas=world)
+        for r in range(1, world):
+            node.add_remote(sock_path(r))
+        node.start()
+        m2 = sampler.mark()
+        e2e["ref"] = closed_loop(node, n_req, n_warm, outstanding, cfg["payload"], True)
+        m3 = sampler.mark()
+        st = node.server.stats()
+        ws = [node.server.worker_stats(i) for i in range(world)]
+        e2e["copy"] = closed_loop(node, max(nb * world * 4, n_req // 4), max(nb, n_warm // 4), outstanding, cfg["payload"], False)
+        e2e["pushed"] = sum(r["pushed"] for r in st["replicas"])
+        e2e["steered"] = [r["steered"] for r in st["replicas"]]
+        e2e["sg_errors"] = st["sg_errors"]
+        hist = ws[0]["batch_hist"]
+        e2e["mean_batch_replica0"] = sum(k * v for k, v in hist.items()) / max(1, sum(hist.values()))
+        e2e["batches"] = [w["num_batches"] for w in ws]
+        node.stop()
+    barrier()
+    clocks_e2e = sampler.summary(m2, m3)
+    if rank > 0:
+        node.stop()
+
+    # ---- the independent arrangement (every GPU its own ingress), as a second number
+    per_gpu = None
+    if world > 1:
+        if rank == 0:
+            srv2 = node
+            srv2.new_server(server_mode=2, outstanding=3 * nb, n_replicas=1)
+        else:
+            srv2 = PerGpuIngress(node, outstanding=3 * nb)
+        barrier()
+        ms2 = allmax(device_timed_per_gpu(srv2, args.steps, warm))
+        barrier()
+        srv2.start()
+        r2 = closed_loop(srv2, max(nb * args.steps, int(0.5 * value / world)), nb * warm, 3 * nb, cfg["payload"], True)
+        srv2.stop()
+        per_gpu = {"value": round(world * nb * args.steps / (ms2 / 1e3), 1), "ms_per_step": round(ms2 / args.steps, 4),
+                   "e2e": round(allsum(r2["rps"]), 1), "e2e_p99_us": round(allmax(r2["p99_us"]), 1),
+                   "parallelism": f"dp{world}, one ingress (transport, server, load generator) per GPU"}
     clocks = sampler.stop()
-    ws = srv.server.worker_stats(0)
-    srv.stop()
-    e2e_rps = st.get("throughput_est", 0.0) if ok else 0.0
-    t2 = torch.tensor([e2e_rps, st.get("p50_sojournTime_us", 0.0), st.get("p99_sojournTime_us", 0.0)], device="cuda",
-                      dtype=torch.float64)
-    if dist:
-        s = t2.clone()
-        dist.all_reduce(s, op=dist.ReduceOp.SUM)
-        m = t2.clone()
-        dist.all_reduce(m, op=dist.ReduceOp.MAX)
-        e2e_total, p50, p99 = float(s[0]), float(m[1]), float(m[2])
-    else:
-        e2e_total, p50, p99 = float(t2[0]), float(t2[1]), float(t2[2])
-    hist = ws["batch_hist"]
-    mean_bs = sum(k * v for k, v in hist.items()) / max(1, sum(hist.values()))
-    launches_per_step = 2 + model.kernels_per_forward
-    wns = ws["work_ns"][len(ws["work_ns"]) // 4:]
-    work_ms = sum(wns) / max(1, len(wns)) / 1e6  # host-observed graph launch + wait per batch on the worker thread
-    result = {
-        "metric": "req/s (dynamic batching, device-timed, max over ranks)", "value": round(value, 1), "unit": "req/s",
-        "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(max_total_ms / args.steps, 4),
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "impl": "splitrpc_b200",
-        "config": {"model": cfg["model"], "global_batch": nb * world, "seq_len": cfg["seq"], "parallelism": f"dp{world}",
-                   "step": f"one batch of {nb} requests per GPU: gather fragments from pinned host arena + model graph + response scatter; the gather of batch i+1 overlaps the graph of batch i on a second stream, as in the server",
-                   "l2": "256 MiB buffer written between iterations, inside the timed region; inputs alternate between two pinned host sets",
-                   "weights": "random init"},
-        "clocks": clocks,
-        "e2e": {"value": round(e2e_total, 1), "unit": "req/s", "h2d_bytes_per_step": nb * srv.req_size,
-                "d2h_bytes_per_step": nb * srv.resp_size, "p50_us": round(p50, 1), "p99_us": round(p99, 1),
-                "mean_batch": round(mean_bs, 2), "worker_ms_per_batch": round(work_ms, 3), "requests": n_req, "outstanding": outstanding,
-                "path": "loadgen (fragments in pinned host memory, sent by reference) -> loopback NIC -> native server "
-                        "(reassembly, steering, dynamic batching) -> SG kernel pulls fragments over PCIe -> CUDA graph -> "
-                        "SG kernel writes responses to the pinned transmit arena -> client"},
-        "gpu_launches": launches_per_step * args.steps,
-    }
+    clocks_dev = sampler.summary(m0, m1)
+
+    result = None
+    if rank == 0:
+        ref, cp = e2e["ref"], e2e["copy"]
+        req_bytes, resp_bytes = node.req_size, node.resp_size
+        ingress_cap = PCIE_GBS * 1e9 / req_bytes  # requests/s that one ingress can pull over GPU 0's PCIe link
+        sm_e2e = clocks_e2e.get("sm_mhz") or 0
+        result = {
+            "metric": "req/s (dynamic batching, device-timed, max over ranks)", "value": round(value, 1), "unit": "req/s",
+            "n_gpus": world, "steps": args.steps, "warmup": warm, "ms_per_step": round(max_ms / args.steps, 4),
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "impl": "splitrpc_b200",
+            "config": {"model": cfg["model"], "global_batch": nb * world, "seq_len": cfg["seq"],
+                       "parallelism": f"dp{world}, single ingress" if world > 1 else "dp1",
+                       "step": f"one batch of {nb} requests per GPU: GPU 0 gathers the fragments from the pinned host arena "
+                               "into the serving GPU's ring (NVLink for the other GPUs) and rings the slot doorbells; the serving "
+                               "stream waits on the doorbell and replays the model graph, whose last kernel stores the responses "
+                               "into the ingress transmit arena and completes the slots",
+                       "l2": "256 MiB buffer written between iterations, inside the timed region; inputs alternate between two pinned host sets",
+                       "weights": "random init"},
+            "clocks": {**clocks_dev, "whole_run": clocks},
+            "roofline": {"ingress_pcie_req_s": round(ingress_cap, 0), "value_over_ingress_cap": round(value / ingress_cap, 3),
+                         "note": f"one ingress pulls every request over GPU 0's PCIe link ({PCIE_GBS} GB/s measured): "
+                                 f"{req_bytes} B per request; the NVLink hop ({NVLINK_GBS} GB/s measured per direction) is not the limit"},
+            "e2e": {"value": round(ref["rps"], 1), "unit": "req/s", "h2d_bytes_per_step": nb * world * req_bytes,
+                    "d2h_bytes_per_step": nb * world * resp_bytes, "p50_us": round(ref["p50_us"], 1), "p99_us": round(ref["p99_us"], 1),
+                    "slo_ms": args.slo_ms, "slo_met": bool(ref["ok"] and ref["p99_us"] <= args.slo_ms * 1e3),
+                    "requests": ref["requests"], "seconds": ref["seconds"], "outstanding": outstanding,
+                    "sm_mhz_median": clocks_e2e.get("sm_mhz"), "reasons": clocks_e2e.get("reasons"),
+                    "value_at_max_clock": round(ref["rps"] * 1965.0 / sm_e2e, 1) if sm_e2e else None,
+                    "copy_mode": {"value": round(cp["rps"], 1), "p50_us": round(cp["p50_us"], 1), "p99_us": round(cp["p99_us"], 1),
+                                  "requests": cp["requests"], "note": "the emulated NIC DMA writes every fragment into the receive arena (CPU memcpy by the client thread)"},
+                    "responses_pushed_by_serving_gpu": e2e["pushed"], "steered": e2e["steered"], "sg_errors": e2e["sg_errors"],
+                    "mean_batch_replica0": round(e2e["mean_batch_replica0"], 2), "batches": e2e["batches"],
+                    "path": "loadgen (fragments in pinned host memory, sent by reference) -> loopback NIC -> native server on rank 0 "
+                            "(reassembly, steering) -> GPU 0 gather kernel pulls the fragments over PCIe, writes the serving GPU's ring "
+                            "and rings its doorbells -> worker (dynamic batching) -> CUDA graph -> last kernel stores the responses into "
+                            "the pinned transmit arena and completes the slots -> client"},
+            "gpu_launches": total_launches,
+        }
+        if per_gpu:
+            result["ingress_per_gpu"] = per_gpu
+    barrier()
     if dist:
         dist.destroy_process_group()
     return result
@@ -294,12 +534,8 @@ def run_tp(args, rank: int, world: int, local_rank: int) -> dict:
     model = BertClassifierTP(BERT_LARGE, seq=S, device=local_rank, batch=B)
     dev = torch.device("cuda", local_rank)
     warm = max(args.warmup, 3)
-    n_sets = 4
-    ids_host = [torch.randint(0, 30522, (B, S), dtype=torch.int32, generator=torch.Generator().manual_seed(i)).pin_memory()
-                for i in range(n_sets)]
     ids_dev = torch.zeros((B, S), dtype=torch.int32, device=dev)
     probs = torch.zeros((B, 2), dtype=torch.float32, device=dev)
-    probs_host = torch.zeros((B, 2), dtype=torch.float32).pin_memory()
     stream = torch.cuda.Stream(device=dev)
     with torch.cuda.stream(stream):
         model.forward(ids_dev, out=probs)  # warm-up outside capture (sets kernel attributes)
@@ -310,14 +546,10 @@ def run_tp(args, rank: int, world: int, local_rank: int) -> dict:
             model.forward(ids_dev, out=probs)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     sampler = ClockSampler(local_rank)
-
-    def one_step(i):
-        graph.replay()
-
     results = {}
     with torch.cuda.stream(stream):
         for i in range(warm):
-            one_step(i)
+            graph.replay()
         stream.synchronize()
         dist.barrier()
         sampler.start()
@@ -326,7 +558,7 @@ def run_tp(args, rank: int, world: int, local_rank: int) -> dict:
             flush.zero_()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record(stream)
-            one_step(i)
+            graph.replay()
             e1.record(stream)
             evs.append((e0, e1))
         stream.synchronize()
@@ -378,6 +610,45 @@ def run_tp(args, rank: int, world: int, local_rank: int) -> dict:
     return res
 
 
+def run_lenet5_cpu(args) -> dict:
+    """Plumbing configuration that needs no GPU: LeNet-5 on the CPU device behind the loopback transport."""
+    import numpy as np
+
+    from splitrpc_b200 import _C
+    from splitrpc_b200.serving import lenet5_random_weights
+
+    cfg = CONFIGS["lenet5"]
+    nb = cfg["max_batch"]
+    _C.set_rpc_mtu(8192)
+    w = lenet5_random_weights()
+    sp, cp = _C.make_loopback_pair(8192, 4096)
+    app = _C.make_app("lenet5", -1, 3136, 40, w, 256, 1, nb, "cpu")
+    srv = _C.Server(sp, req_size=3136, resp_size=40, server_mode=2, max_batch=nb)
+    srv.add_replica(app)
+    srv.start()
+    n_req, n_warm = nb * args.steps * 8, nb * max(args.warmup, 3)
+    cli = _C.Client(cp, req_size=3136, resp_size=40, total=n_req + n_warm, warmup=n_warm, payload="uniform", verify=True)
+    t0 = time.perf_counter()
+    ok = cli.run_closed_loop(48)
+    wall = time.perf_counter() - t0
+    st = cli.post_process()
+    ws = srv.worker_stats(0)
+    srv.stop()
+    x = np.frombuffer(cli.payload(3), dtype=np.float32)
+    oracle_ok = bool(np.allclose(np.frombuffer(cli.response(3), dtype=np.float32), _C.cpu_lenet5(w, x)[0], rtol=1e-4, atol=1e-5))
+    hist = ws["batch_hist"]
+    rps = st.get("throughput_est", 0.0) if ok else 0.0
+    return {"metric": "req/s (dynamic batching, CPU device, host clock)", "value": round(rps, 1), "unit": "req/s", "n_gpus": 0,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(1e3 * nb / rps, 4) if rps else None,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp32", "data": "synthetic", "impl": "splitrpc_b200",
+            "config": {"model": cfg["model"], "global_batch": nb, "seq_len": None, "parallelism": "cpu"},
+            "e2e": {"value": round(rps, 1), "unit": "req/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
+                    "p50_us": round(st.get("p50_sojournTime_us", 0.0), 1), "p99_us": round(st.get("p99_sojournTime_us", 0.0), 1),
+                    "requests": n_req, "seconds": round(wall, 3), "oracle_match": oracle_ok,
+                    "mean_batch": round(sum(k * v for k, v in hist.items()) / max(1, sum(hist.values())), 2)},
+            "gpu_launches": 0}
+
+
 def run_reference(args, rank: int, world: int, local_rank: int) -> dict:
     """The original's data path, re-hosted: see baseline/reference_arm.py.  Imports nothing of this package."""
     sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "baseline"))
@@ -396,17 +667,25 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--config", default="resnet50", choices=sorted(CONFIGS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--slo-ms", type=float, default=10.0, help="p99 latency objective of the end-to-end phase")
+    ap.add_argument("--e2e-seconds", type=float, default=2.0, help="target length of the end-to-end phase")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         res = run_reference(args, rank, world, local_rank)
-        if rank == 0:
-            print(json.dumps(res), flush=True)
-        return
-    res = run_tp(args, rank, world, local_rank) if args.config == "bert_large_tp" else run_ours(args, rank, world, local_rank)
-    if rank == 0:
+    elif args.config == "lenet5":
+        res = run_lenet5_cpu(args) if rank == 0 else None
+    elif args.config == "echo":
+        from splitrpc_b200.utils.bench_echo import run_echo
+
+        res = run_echo(args, rank, world, local_rank)
+    elif args.config == "bert_large_tp":
+        res = run_tp(args, rank, world, local_rank)
+    else:
+        res = run_ours(args, rank, world, local_rank)
+    if rank == 0 and res is not None:
         print(json.dumps(res), flush=True)
 
 

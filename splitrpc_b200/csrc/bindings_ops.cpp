@@ -30,6 +30,8 @@ static GemmEpilogue make_ep(uintptr_t out, int ldo, bool out_fp32, uintptr_t bia
   return ep;
 }
 
+extern "C" int srpc_stream_write64(cudaStream_t s, uint64_t* addr, uint64_t v);
+
 void bind_ops(py::module_& m) {
   m.def("device_caps", [](int dev) {
     int vmm = 0, memops = 0, gdr = 0, maj = 0, min = 0, nsm = 0;
@@ -89,6 +91,11 @@ void bind_ops(py::module_& m) {
     const SrpcDeviceOps* o = srpc_cuda_ops();
     if (!o || o->stream_wait_value32((cudaStream_t)stream, (volatile uint32_t*)addr, value) != 0)
       throw std::runtime_error(std::string("stream_wait32: ") + (o ? o->last_error() : "no CUDA"));
+  });
+  m.def("stream_write64", [](uintptr_t stream, uintptr_t addr, uint64_t value) {
+    const SrpcDeviceOps* o = srpc_cuda_ops();
+    if (!o || srpc_stream_write64((cudaStream_t)stream, (uint64_t*)addr, value) != 0)
+      throw std::runtime_error(std::string("stream_write64: ") + (o ? o->last_error() : "no CUDA"));
   });
   m.def("stream_write32", [](uintptr_t stream, uintptr_t addr, uint32_t value) {
     const SrpcDeviceOps* o = srpc_cuda_ops();

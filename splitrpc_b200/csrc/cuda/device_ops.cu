@@ -61,6 +61,7 @@ const SrpcDriverApi* srpc_driver_api() {
     get("cuMemGetAllocationGranularity", (void**)&api.MemGetAllocationGranularity);
     get("cuStreamWaitValue32", (void**)&api.StreamWaitValue32);
     get("cuStreamWriteValue32", (void**)&api.StreamWriteValue32);
+    get("cuStreamWriteValue64", (void**)&api.StreamWriteValue64);
     get("cuTensorMapEncodeTiled", (void**)&api.TensorMapEncodeTiled);
     get("cuDeviceGetAttribute", (void**)&api.DeviceGetAttribute);
     get("cuMemExportToShareableHandle", (void**)&api.MemExportToShareableHandle);
@@ -144,6 +145,12 @@ static int d_write32(cudaStream_t s, volatile uint32_t* addr, uint32_t v) {
   const SrpcDriverApi* d = srpc_driver_api();
   if (!d->StreamWriteValue32) return fail_drv("cuStreamWriteValue32 unavailable", CUDA_ERROR_NOT_SUPPORTED);
   DRV(d->StreamWriteValue32((CUstream)s, (CUdeviceptr)(uintptr_t)addr, v, CU_STREAM_WRITE_VALUE_DEFAULT));
+  return 0;
+}
+extern "C" int srpc_stream_write64(cudaStream_t s, uint64_t* addr, uint64_t v) {
+  const SrpcDriverApi* d = srpc_driver_api();
+  if (!d->StreamWriteValue64) return fail_drv("cuStreamWriteValue64 unavailable", CUDA_ERROR_NOT_SUPPORTED);
+  DRV(d->StreamWriteValue64((CUstream)s, (CUdeviceptr)(uintptr_t)addr, v, CU_STREAM_WRITE_VALUE_DEFAULT));
   return 0;
 }
 static int d_event_create(cudaEvent_t* e) {

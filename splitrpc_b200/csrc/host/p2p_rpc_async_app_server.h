@@ -296,10 +296,23 @@ class P2pRpcAsyncAppServer {
     int ci = 0, si = 0, win = 0;
     a->consumer_seq = 0;
     IdleBackoff backoff;
+    // A gather rings the doorbells of a whole burst of slots "at once", but the stores land one after the other: a
+    // worker that looks in between would cut the burst into two small batches.  After the first ready slot it therefore
+    // lingers for a few microseconds while the window is not full and slots keep arriving (P2P_RPC_BATCH_LINGER_US).
+    const uint64_t linger_ns = (uint64_t)readEnvInfo<uint64_t>("P2P_RPC_BATCH_LINGER_US", 10) * 1000ull;
     while (!should_stop()) {
-      while (win < max_batch_size && load_state(pool->get_app_rr(ci)->h_state) == APP_RR_STATUS::RX_COMPLETE) {
-        win++;
-        ci = (ci + 1) % n;
+      uint64_t last_arrival = 0;
+      for (;;) {
+        bool grew = false;
+        while (win < max_batch_size && load_state(pool->get_app_rr(ci)->h_state) == APP_RR_STATUS::RX_COMPLETE) {
+          win++;
+          ci = (ci + 1) % n;
+          grew = true;
+        }
+        if (win == 0 || win >= max_batch_size || linger_ns == 0) break;
+        uint64_t now = getCurNs();
+        if (grew) last_arrival = now;
+        else if (now - last_arrival > linger_ns) break;
       }
       if (win == 0) {
         backoff.empty();

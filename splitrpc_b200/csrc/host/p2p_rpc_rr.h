@@ -179,8 +179,14 @@ class P2pRpcRRPool {
       ctr_.dropped_zero_token++;
       return nullptr;
     }
+    // The fragments of a request mostly arrive back to back: remember the last record and skip the hash lookup.
+    if (last_rr_ && last_token_ == token) return last_rr_;
     auto it = cache_.find(token);
-    if (it != cache_.end()) return it->second;
+    if (it != cache_.end()) {
+      last_token_ = token;
+      last_rr_ = it->second;
+      return it->second;
+    }
     P2pRpcRr* rr = alloc_rr();
     if (!rr) return nullptr;
     rr->req_token = token;
@@ -188,6 +194,8 @@ class P2pRpcRRPool {
     rr->first_frag_ns = getCurNs();
     set_conn_info(&rr->_client_conn_info, hdr);
     cache_.emplace(token, rr);
+    last_token_ = token;
+    last_rr_ = rr;
     return rr;
   }
 
@@ -208,6 +216,7 @@ class P2pRpcRRPool {
   }
 
   void mark_rx_ready_rr(P2pRpcRr* rr) {
+    forget(rr);
     cache_.erase(rr->req_token);
     rr->rr_state = RR_READY;
     ctr_.rx_ready++;
@@ -253,6 +262,7 @@ class P2pRpcRRPool {
     for (auto it = cache_.begin(); it != cache_.end();) {
       P2pRpcRr* rr = it->second;
       if (now_ns - rr->first_frag_ns > timeout_ns) {
+        forget(rr);
         if (release) release(rr);
         it = cache_.erase(it);
         reap_rr(rr);
@@ -267,6 +277,7 @@ class P2pRpcRRPool {
 
   // Receive-thread only.  Forgets a partially received request.
   void drop_partial(P2pRpcRr* rr) {
+    forget(rr);
     cache_.erase(rr->req_token);
     reap_rr(rr);
   }
@@ -290,6 +301,11 @@ class P2pRpcRRPool {
     return rr;
   }
 
+  void forget(const P2pRpcRr* rr) {
+    if (last_rr_ == rr) last_rr_ = nullptr;
+  }
+  uint64_t last_token_ = 0;       // receive thread only: the record the previous fragment belonged to
+  P2pRpcRr* last_rr_ = nullptr;
   int pool_size_;
   int max_records_ = 1 << 16;
   size_t req_size_ = 0;

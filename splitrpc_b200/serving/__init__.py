@@ -4,7 +4,7 @@ from __future__ import annotations
 import numpy as np
 
 from .. import _C
-from .engine import ModelServer  # noqa: F401
+from .engine import ModelReplica, ModelServer  # noqa: F401
 
 
 def __getattr__(name):

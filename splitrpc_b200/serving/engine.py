@@ -3,8 +3,8 @@
 Two roles, one per process:
 
 ``ModelServer``   the ingress.  Owns the loopback transport (receive/transmit arenas in pinned host memory that
-                  the GPUs map), the native server threads (header parsing, reassembly, flow steering) and,
-                  unless ``local_replica=False``, one replica of the model on its own GPU.  Replicas on other
+                  the GPUs map), the native server threads (header parsing, reassembly, flow steering) and
+                  one replica of the model on its own GPU.  Replicas on other
                   GPUs are added with ``add_remote(path)``: the scatter-gather kernel of the ingress GPU then
                   writes their request rings over NVLink and rings their slot doorbells itself.
 ``ModelReplica``  a replica on another GPU (another process): the model's graphs behind a batched server that
@@ -85,7 +85,20 @@ class ModelServer(_GraphModelApp):
         ``n_replicas``: how many replicas this ingress will feed in total (sizes the arenas and the request pool)."""
         super().__init__(model, device, max_batch, copy_type, pool_size, batch_sizes, reserve_sms, fused_ingress)
         self.copy_type = copy_type
-        self.outstanding = outstanding or 2 * max_batch * n_replicas
+        self.server = None
+        self.n_remote = 0
+        self._running = False
+        self.new_server(server_mode=server_mode, outstanding=outstanding, n_replicas=n_replicas, steer_policy=steer_policy,
+                        device_completion=device_completion)
+
+    def new_server(self, server_mode: int = 2, outstanding: int | None = None, n_replicas: int = 1, steer_policy: int = 0,
+                   device_completion: bool = True) -> None:
+        """(Re)creates the transport and the native server around the already captured model: a fresh loopback link, a
+        fresh request pool, this GPU's replica added.  Remote replicas of an earlier server are released first."""
+        self.stop()
+        self.server = None
+        self.app.reset_slots()
+        self.outstanding = outstanding or 2 * self.max_batch * n_replicas
         frags = math.ceil(self.req_size / MTU) + math.ceil(self.resp_size / MTU)
         n_slots = max(1024, 2 * self.outstanding * frags)
         # "shm_pinned": pinned and GPU-mapped like a NIC's registered rings, and a shared mapping, so that replicas
@@ -94,11 +107,10 @@ class ModelServer(_GraphModelApp):
         if self.fused_ingress and not self.app.set_ingress_stem_s2d(self.ingress["mean"], self.ingress["inv_std"]):
             raise RuntimeError("the scatter-gather engine does not support the fused ingress transform")
         self.server = _C.Server(self.server_port, req_size=self.req_size, resp_size=self.resp_size, server_mode=server_mode,
-                                max_batch=max_batch, rr_pool_size=max(1023, 4 * self.outstanding), gather_burst=max_batch,
-                                steer_policy=steer_policy, device_completion=1 if device_completion else 0)
+                                max_batch=self.max_batch, rr_pool_size=max(1023, 4 * self.outstanding),
+                                gather_burst=self.max_batch, steer_policy=steer_policy,
+                                device_completion=1 if device_completion else 0)
         self.server.add_replica(self.app)
-        self.n_remote = 0
-        self._running = False
 
     def add_remote(self, path: str, timeout_ms: int = 60000) -> int:
         """Connects to the ``ModelReplica`` listening at ``path`` and adds it to flow steering."""
@@ -133,13 +145,23 @@ class ModelServer(_GraphModelApp):
 
 
 class ModelReplica(_GraphModelApp):
-    """One replica of ``model`` on ``device`` for an ingress in another process (see ``ModelServer.add_remote``)."""
+    """One replica of ``model`` on ``device`` for an ingress in another process (see ``ModelServer.add_remote``).
+
+    ``server_mode``: 0 fixed batch, 1 stream armed, 2 dynamic batching; negative = no worker (the caller consumes the
+    slots itself, e.g. a timing loop)."""
 
     def __init__(self, model, path: str, device: int = 0, max_batch: int = 64, server_mode: int = 2, copy_type: int = 2,
                  pool_size: int | None = None, batch_sizes=None, reserve_sms: int = 0, fused_ingress: bool = True):
         super().__init__(model, device, max_batch, copy_type, pool_size, batch_sizes, reserve_sms, fused_ingress)
         self.path = path
-        self.batched = _C.BatchedServer(self.app, path, func_id=FUNC_ID, server_mode=server_mode, max_batch=max_batch)
+        self.batched = None
+        self.serve(server_mode)
+
+    def serve(self, server_mode: int = 2) -> None:
+        """(Re)creates the batched server in the given worker mode; call ``start()`` afterwards."""
+        if self.batched is not None:
+            self.batched.stop()
+        self.batched = _C.BatchedServer(self.app, self.path, func_id=FUNC_ID, server_mode=server_mode, max_batch=self.max_batch)
         if self.fused_ingress:
             self.batched.set_ingress_stem_s2d(self.ingress["mean"], self.ingress["inv_std"])
 
