@@ -393,8 +393,12 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> dict:
 
     # ---- roles: rank 0 = ingress + replica, the others = replicas behind batched servers
     if rank == 0:
+        # The ingress GPU gathers for every replica.  The gather that also deserialises ResNet images needs about 24 SMs
+        # to run at the PCIe rate (12 are enough when it only feeds its own replica), so with more than one replica the
+        # model kernels of GPU 0 leave 24 SMs to it.
         node = ModelServer(model, device=local_rank, max_batch=nb, server_mode=2, copy_type=2, outstanding=outstanding,
-                           pool_size=pool, n_replicas=world)
+                           pool_size=pool, n_replicas=world, reserve_sms=12 if world == 1 else 24,
+                           steer_policy=0 if world == 1 else 1)
     else:
         node = ModelReplica(model, sock_path(rank), device=local_rank, max_batch=nb, server_mode=-1, pool_size=pool,
                             reserve_sms=12)
@@ -429,7 +433,7 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> dict:
     n_warm = max(nb * warm * world, n_req // 20)
     m2 = m3 = sampler.mark()
     if rank == 0:
-        node.new_server(server_mode=2, outstanding=outstanding, n_replicas=world)
+        node.new_server(server_mode=2, outstanding=outstanding, n_replicas=world, steer_policy=0 if world == 1 else 1)
         for r in range(1, world):
             node.add_remote(sock_path(r))
         node.start()

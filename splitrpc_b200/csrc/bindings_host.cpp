@@ -8,6 +8,7 @@
 #include "cuda/apps_gpu.h"
 #include "host/apps_cpu.h"
 #include "host/loadgen.h"
+#include "host/p2p_rpc_compat.h"
 #include "host/splitrpc_server.h"
 
 namespace py = pybind11;
@@ -866,6 +867,86 @@ PYBIND11_MODULE(_C, m) {
       .def_property_readonly("received", [](ClientHolder& c) { return c.client->received(); })
       .def_property_readonly("verify_failures", [](ClientHolder& c) { return c.client->verify_failures(); })
       .def_property_readonly("bad_tokens", [](ClientHolder& c) { return c.client->bad_tokens(); });
+
+  // ---- the original's older public types (BufItemPool, first-generation records, socket records): exercised here so
+  // that their behaviour is pinned by a test without exposing every method to Python.
+  m.def("compat_selftest", [](int device) {
+    py::dict d;
+    // typed pool: host memory, and memory that a GPU addresses too
+    uint32_t* hp = BufItemPool<uint32_t>::create_buf_item_pool(16, -1);
+    d["host_pool"] = hp != nullptr && BufItemPool<uint32_t>::get_dev_ptr(hp) == hp && hp[15] == 0;
+    BufItemPool<uint32_t>::delete_buf_item_pool(hp);
+    d["host_pool_forgotten"] = BufItemPool<uint32_t>::get_dev_ptr(hp) == nullptr;
+    if (device >= 0) {
+      g_params* gp = BufItemPool<g_params>::create_buf_item_pool(4, device);
+      d["mapped_pool"] = gp != nullptr && BufItemPool<g_params>::get_dev_ptr(gp) != nullptr;
+      if (gp) BufItemPool<g_params>::delete_buf_item_pool(gp, device);
+    }
+    // first-generation record + pool
+    p2p_rpc_conn_info* conn = initialize_src_conn_info("b8:ce:f6:cc:6a:52,192.168.25.1,50051");
+    {
+      p2p_rpc_v1::P2pRpcRRPool pool(8);
+      pool.setup_and_init_rr_pool(conn, 256, 64, -1);
+      p2p_rpc_hdr h{};
+      h.req_token = 99;
+      p2p_rpc_rr* a = pool.get_rr(&h);
+      p2p_rpc_rr* b = pool.get_rr(&h);
+      rr_merge_req_mbuf(a, 1, 2, 3, 100, 1);
+      rr_merge_req_mbuf(a, 4, 5, 6, 156, 0);
+      d["v1_same_token_same_rr"] = a != nullptr && a == b;
+      d["v1_merge"] = a->payload_bufs->num_items == 2 && a->req_size == 256 && a->payload_bufs->burst_items[1] == 3 &&
+                      a->payload_bufs->item_size[0] == 156 && a->req_payload != nullptr && a->max_resp_size == 64;
+      p2p_rpc_rr* c = rr_clone_alloc(a);
+      d["v1_clone"] = c->max_req_size == 256 && c->payload_bufs->num_items == 0;
+      rr_base_free(c);
+      pool.reap_rr(a);
+      d["v1_reaped"] = pool.num_free() == 8 && a->req_size == 0 && a->payload_bufs->num_items == 0;
+      int taken = 0;
+      while (pool.consume_rr()) taken++;
+      d["v1_exhausts"] = taken == 8 && pool.consume_rr() == nullptr;
+    }
+    release_conn_info(conn);
+    // socket record + pool: a 2500-byte request through datagram buffers and back
+    {
+      size_t old_mtu = rpc_mtu();
+      set_rpc_mtu(1024);
+      UdpRrPool pool(4);
+      pool.setup_and_init_rr_pool(2500, 40);
+      UdpRpcHdr uh{};
+      uh.req_token = 7;
+      UdpRr* rr = pool.get_rr(&uh);
+      for (size_t i = 0; i < 2500; i++) rr->req_payload[i] = (uint8_t)(i * 13);
+      rr->alloc_req_bufs();
+      size_t put = rr->req_to_bufs();
+      const UdpRpcHdr* first = (const UdpRpcHdr*)rr->req_bufs->burst_items[0];
+      const UdpRpcHdr* last = (const UdpRpcHdr*)rr->req_bufs->burst_items[2];
+      d["udp_fragments"] = rr->req_bufs->num_items == 3 && put == 2500 && first->req_token == 7 && last->seq_num == 2 &&
+                           rr->req_bufs->item_size[2] == UDP_RPC_HEADER_LEN + 452;
+      std::vector<uint8_t> keep(rr->req_payload, rr->req_payload + 2500);
+      std::memset(rr->req_payload, 0, 2500);
+      size_t got = rr->bufs_to_req();
+      d["udp_roundtrip"] = got == 2500 && std::memcmp(keep.data(), rr->req_payload, 2500) == 0;
+      // reassembly bookkeeping by sequence number
+      UdpRr other(2500, 40);
+      other.rr_merge_req_buf(rr->req_bufs->burst_items[2], rr->req_bufs->item_size[2], 2);
+      other.rr_merge_req_buf(rr->req_bufs->burst_items[0], rr->req_bufs->item_size[0], 0);
+      bool before = other.is_req_ready();
+      other.rr_merge_req_buf(rr->req_bufs->burst_items[1], rr->req_bufs->item_size[1], 1);
+      d["udp_ready"] = !before && other.is_req_ready();
+      other.req_bufs->num_items = 0;  // the buffers belong to rr
+      pool.mark_process_rr(rr);
+      UdpRr* nx = nullptr;
+      d["udp_queues"] = pool.get_next_rx_ready_rr(&nx) == 1 && nx == rr && pool.consume_process_rr() == nullptr;
+      pool.mark_ready_rr(rr);
+      d["udp_ready_queue"] = pool.consume_ready_rr() == rr;
+      pool.reap_rr(rr);
+      int taken = 0;
+      while (pool.consume_rr()) taken++;
+      d["udp_exhausts"] = taken == 4;
+      set_rpc_mtu(old_mtu);
+    }
+    return d;
+  }, py::arg("device") = -1);
 
   // ---- arrival processes
   m.def("arrival_schedule", [](double rate, int cov, uint64_t n, uint64_t seed) {

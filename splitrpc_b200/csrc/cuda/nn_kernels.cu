@@ -307,10 +307,15 @@ __global__ void __launch_bounds__(256) softmax_response(const float* __restrict_
   __shared__ int s_arg;
   const int row = blockIdx.x;
   const float* x = logits + (size_t)row * ld;
-  uint8_t* base = (direct_out ? direct_out : stub->resp) + (size_t)row * resp_stride;
-  RespPushTarget target{base, nullptr};
-  if (!direct_out) target = resp_push_target(push, (uint32_t)row, base);
-  base = target.dst;
+  // One thread reads the stub and the push block (mapped host memory: every read is a PCIe round trip) for the block.
+  __shared__ RespPushTarget s_target;
+  if (threadIdx.x == 0) {
+    uint8_t* b = (direct_out ? direct_out : stub->resp) + (size_t)row * resp_stride;
+    s_target = (!direct_out && push) ? resp_push_target(push, (uint32_t)row, b) : RespPushTarget{b, nullptr};
+  }
+  __syncthreads();
+  const RespPushTarget target = s_target;
+  uint8_t* base = target.dst;
   float m = -FLT_MAX;
   int am = 0;
   for (int i = threadIdx.x; i < n; i += blockDim.x)

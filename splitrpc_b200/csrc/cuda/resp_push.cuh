@@ -17,6 +17,10 @@ struct RespPushTarget {
   volatile uint32_t* state;  // nullptr: completion is left to the host
 };
 
+// The push block, the slots' destinations and their state words live in host memory that several processes map: a
+// read costs a PCIe round trip.  Call this from ONE thread per response and hand the result to the others through
+// shared memory (resp_push_target_block does that); thousands of threads reading it at once cost more than the
+// softmax they belong to.
 __device__ __forceinline__ RespPushTarget resp_push_target(const RespPushCtx* ctx, uint32_t row, uint8_t* ring_dst) {
   RespPushTarget t{ring_dst, nullptr};
   if (!ctx || ctx->enabled == 0 || ctx->pool_size == 0) return t;
@@ -25,6 +29,15 @@ __device__ __forceinline__ RespPushTarget resp_push_target(const RespPushCtx* ct
   if (ctx->tx_base && off != ~0ull && off + ctx->resp_size <= ctx->tx_bytes) t.dst = reinterpret_cast<uint8_t*>(ctx->tx_base + off);
   t.state = ctx->states + slot;
   return t;
+}
+
+// Block-wide form: thread 0 looks the target up, everybody gets it.  Contains __syncthreads(): call it from all
+// threads of the block, outside divergent code.
+__device__ __forceinline__ RespPushTarget resp_push_target_block(const RespPushCtx* ctx, uint32_t row, uint8_t* ring_dst) {
+  __shared__ RespPushTarget s_target;
+  if (threadIdx.x == 0) s_target = resp_push_target(ctx, row, ring_dst);
+  __syncthreads();
+  return s_target;
 }
 
 // Call from one thread, after a __syncthreads() that follows every store of the response by the block.

@@ -70,7 +70,14 @@ __device__ __forceinline__ void copy_chunk_simt(const uint8_t* src, uint8_t* dst
       d4[i + 2 * nthr] = c;
       d4[i + 3 * nthr] = e;
     }
-    for (; i < nv; i += nthr) d4[i] = s4[i];
+    if (i < nv) {  // fewer than four full rounds left (e.g. one 8 KB fragment): still issue every load before any store
+      const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+      const bool p1 = i + nthr < nv, p2 = i + 2 * nthr < nv;
+      const uint4 a = s4[i], b = p1 ? s4[i + nthr] : z, c = p2 ? s4[i + 2 * nthr] : z;
+      d4[i] = a;
+      if (p1) d4[i + nthr] = b;
+      if (p2) d4[i + 2 * nthr] = c;
+    }
     for (uint32_t i2 = (nv << 4) + t; i2 < body; i2 += nthr) d[i2] = s[i2];
   } else if (((uintptr_t)s & 3) == 0) {
     uint32_t nv = body >> 2;
@@ -126,9 +133,16 @@ __global__ void __launch_bounds__(1024) sg_copy_simt(const SgItem* __restrict__ 
 // somewhere else) and complete the slot.
 __global__ void __launch_bounds__(256) resp_push_kernel(const g_params* __restrict__ stub, const RespPushCtx* __restrict__ ctx) {
   const uint32_t row = blockIdx.x;
-  uint8_t* src = stub->resp + (size_t)row * ctx->resp_size;
-  const RespPushTarget t = resp_push_target(ctx, row, src);
-  if (t.dst != src) copy_chunk_simt(src, t.dst, ctx->resp_size, threadIdx.x, blockDim.x);
+  __shared__ uint8_t* s_src;
+  __shared__ uint32_t s_len;
+  if (threadIdx.x == 0) {  // the stub and the push block are read once per block (host memory)
+    s_len = ctx->resp_size;
+    s_src = stub->resp + (size_t)row * s_len;
+  }
+  __syncthreads();
+  uint8_t* src = s_src;
+  const RespPushTarget t = resp_push_target_block(ctx, row, src);
+  if (t.dst != src) copy_chunk_simt(src, t.dst, s_len, threadIdx.x, blockDim.x);
   __syncthreads();
   if (threadIdx.x == 0) resp_push_complete(t);
 }

@@ -1,0 +1,437 @@
+// Public types of the original's client-side and socket-side API, kept so that code written against them compiles
+// against this library: the typed buffer pool, the first-generation request/response record with its pool, and the
+// kernel-UDP record with its pool.  They are thin: storage and queues come from this library's own pieces (mapped
+// pinned memory instead of gdrcopy, MpmcRing instead of DPDK rings / moodycamel queues), every loop is bounded and the
+// pools are safe to use from several threads where the originals note that they are not.
+//
+//   BufItemPool<T>            reference src/p2p_buf_pool.h:12-78
+//   p2p_rpc_rr + rr_* helpers reference src/p2p_rpc_rr.h:13-223
+//   p2p_rpc_v1::P2pRpcRRPool  reference src/p2p_rpc_rr_pool.h:54-184 (same class name as the current pool in the
+//                             original, which keeps the two in different headers; here the older one has a namespace)
+//   UdpRpcHdr, UdpRr, UdpRrPool   reference src/udp_rr.h:23-446
+#pragma once
+
+#include <netinet/in.h>
+
+#include <mutex>
+#include <unordered_map>
+#include <vector>
+
+#include "mpmc_ring.h"
+#include "p2p_rpc.h"
+#include "p2p_rpc_app.h"
+
+// ------------------------------------------------------------------ typed buffer pool
+// type -1: plain host memory.  type >= 0: memory that both the CPU and GPU `type` address (the original maps GPU
+// memory into the CPU with gdrcopy; here it is mapped pinned host memory, which serves the same purpose for stubs and
+// doorbells).  get_dev_ptr() returns the device-side address of a pool (the host address for host pools).
+template <class T>
+class BufItemPool {
+  struct Info {
+    T* dev = nullptr;
+    size_t num = 0;
+    bool mapped = false;
+  };
+  static std::unordered_map<T*, Info>& table() {
+    static std::unordered_map<T*, Info> t;
+    return t;
+  }
+  static std::mutex& mu() {
+    static std::mutex m;
+    return m;
+  }
+
+ public:
+  static T* create_buf_item_pool(int num, int type = -1) {
+    if (num <= 0) return nullptr;
+    Info info;
+    info.num = (size_t)num;
+    T* h = nullptr;
+    if (type >= 0) {
+      const SrpcDeviceOps* ops = srpc_cuda_ops();
+      void *hp = nullptr, *dp = nullptr;
+      if (!ops || ops->set_device(type) != 0 || ops->host_alloc_mapped(sizeof(T) * (size_t)num, &hp, &dp) != 0) return nullptr;
+      h = static_cast<T*>(hp);
+      info.dev = static_cast<T*>(dp);
+      info.mapped = true;
+    } else {
+      void* p = nullptr;
+      if (posix_memalign(&p, 64, sizeof(T) * (size_t)num) != 0) return nullptr;
+      h = static_cast<T*>(p);
+      info.dev = h;
+    }
+    std::memset((void*)h, 0, sizeof(T) * (size_t)num);
+    std::lock_guard<std::mutex> g(mu());
+    table()[h] = info;
+    return h;
+  }
+  static void delete_buf_item_pool(T* h, int type = -1) {
+    (void)type;
+    Info info;
+    {
+      std::lock_guard<std::mutex> g(mu());
+      auto it = table().find(h);
+      if (it == table().end()) return;
+      info = it->second;
+      table().erase(it);
+    }
+    if (info.mapped) {
+      if (const SrpcDeviceOps* ops = srpc_cuda_ops()) ops->host_free(h);
+    } else {
+      free((void*)h);
+    }
+  }
+  static T* get_dev_ptr(T* h) {
+    std::lock_guard<std::mutex> g(mu());
+    auto it = table().find(h);
+    return it == table().end() ? nullptr : it->second.dev;
+  }
+};
+
+// ------------------------------------------------------------------ first-generation record
+enum RR_STATUS : uint32_t { RR_V1_UNUSED = 0, RR_V1_INUSE = 1 };
+
+struct p2p_rpc_rr {
+  uint64_t req_token = 0;
+  uint8_t *req_payload = nullptr, *resp_payload = nullptr;
+  size_t req_size = 0, resp_size = 0;
+  size_t max_req_size = 0, max_resp_size = 0;
+  int req_device_id = -2, resp_device_id = -2;
+  volatile uint32_t* state = nullptr;
+  uint32_t rr_state = RR_V1_UNUSED;
+  p2p_rpc_conn_info _client_conn_info{};
+  p2p_hbufs* transport_mbufs = nullptr;
+  p2p_hbufs* hdr_bufs = nullptr;
+  p2p_bufs* payload_bufs = nullptr;
+  p2p_sk_buf* payload_sk_bufs = nullptr;
+};
+
+static inline p2p_rpc_rr* rr_base_alloc() {
+  p2p_rpc_rr* rr = new p2p_rpc_rr;
+  rr->transport_mbufs = new p2p_hbufs();
+  rr->hdr_bufs = new p2p_hbufs();
+  rr->payload_bufs = new p2p_bufs();
+  rr->payload_sk_bufs = new p2p_sk_buf();
+  return rr;
+}
+static inline void rr_base_free(p2p_rpc_rr* rr) {
+  if (!rr) return;
+  delete rr->transport_mbufs;
+  delete rr->hdr_bufs;
+  delete rr->payload_bufs;
+  delete rr->payload_sk_bufs;
+  delete rr;
+}
+static inline p2p_rpc_rr* rr_proto_alloc(const p2p_rpc_conn_info* conn, size_t req_size, size_t resp_size) {
+  p2p_rpc_rr* rr = rr_base_alloc();
+  rr->max_req_size = req_size;
+  rr->max_resp_size = resp_size;
+  if (conn) rr->_client_conn_info = *conn;
+  return rr;
+}
+static inline p2p_rpc_rr* rr_clone_alloc(const p2p_rpc_rr* src) {
+  p2p_rpc_rr* rr = rr_proto_alloc(&src->_client_conn_info, src->max_req_size, src->max_resp_size);
+  rr->req_device_id = src->req_device_id;
+  rr->resp_device_id = src->resp_device_id;
+  return rr;
+}
+// Places one buffer at index `idx` of the record's three parallel lists.  Out-of-range indices are ignored.
+static inline void rr_merge_mbuf(p2p_rpc_rr* rr, uintptr_t transport_mbuf, uintptr_t hdr_buf, uintptr_t payload_buf, size_t item_size,
+                                 int idx) {
+  if (idx < 0 || idx >= MAX_BI_SIZE) return;
+  rr->transport_mbufs->burst_items[idx] = transport_mbuf;
+  rr->hdr_bufs->burst_items[idx] = hdr_buf;
+  rr->payload_bufs->burst_items[idx] = payload_buf;
+  rr->payload_bufs->item_size[idx] = item_size;
+  const uint16_t n = (uint16_t)(idx + 1);
+  if (rr->transport_mbufs->num_items < n) rr->transport_mbufs->num_items = n;
+  if (rr->hdr_bufs->num_items < n) rr->hdr_bufs->num_items = n;
+  if (rr->payload_bufs->num_items < n) rr->payload_bufs->num_items = n;
+}
+static inline void rr_append_req_mbuf(p2p_rpc_rr* rr, uintptr_t m, uintptr_t h, uintptr_t p, size_t sz) {
+  rr->req_size += sz;
+  rr_merge_mbuf(rr, m, h, p, sz, rr->transport_mbufs->num_items);
+}
+static inline void rr_append_resp_mbuf(p2p_rpc_rr* rr, uintptr_t m, uintptr_t h, uintptr_t p, size_t sz) {
+  rr->resp_size += sz;
+  rr_merge_mbuf(rr, m, h, p, sz, rr->transport_mbufs->num_items);
+}
+static inline void rr_merge_req_mbuf(p2p_rpc_rr* rr, uintptr_t m, uintptr_t h, uintptr_t p, size_t sz, int seq_num) {
+  rr->req_size += sz;
+  rr_merge_mbuf(rr, m, h, p, sz, seq_num);
+}
+static inline void rr_merge_resp_mbuf(p2p_rpc_rr* rr, uintptr_t m, uintptr_t h, uintptr_t p, size_t sz, int seq_num) {
+  rr->resp_size += sz;
+  rr_merge_mbuf(rr, m, h, p, sz, seq_num);
+}
+static inline void rr_clear_bufs(p2p_rpc_rr* rr) {
+  rr->transport_mbufs->num_items = rr->hdr_bufs->num_items = rr->payload_bufs->num_items = 0;
+  rr->payload_sk_bufs->num_items = 0;
+  rr->req_size = rr->resp_size = 0;
+}
+static inline void rr_print_bufs(const p2p_rpc_rr* rr) {
+  std::printf("rr %p token=%lu: %u buffers\n", (const void*)rr, (unsigned long)rr->req_token, (unsigned)rr->payload_bufs->num_items);
+  print_bufs(rr->payload_bufs);
+}
+
+namespace p2p_rpc_v1 {
+
+// Pool of first-generation records that also owns each record's request and response payload memory: host memory
+// (device id -1), memory a GPU can address (device id >= 0, mapped pinned) or none (-2).
+class P2pRpcRRPool {
+  int pool_size_;
+  std::unordered_map<uint64_t, p2p_rpc_rr*> rr_cache_;
+  MpmcRing<p2p_rpc_rr*> free_;
+  std::vector<p2p_rpc_rr*> rr_pool_;
+  std::mutex mu_;
+
+  static uint8_t* alloc_mem(size_t n, int dev) {
+    if (dev == -2 || n == 0) return nullptr;
+    return BufItemPool<uint8_t>::create_buf_item_pool((int)n, dev);
+  }
+
+ public:
+  explicit P2pRpcRRPool(int pool_size = 1023) : pool_size_(pool_size), free_((size_t)1 << 12) {}
+  ~P2pRpcRRPool() {
+    for (p2p_rpc_rr* rr : rr_pool_) {
+      if (rr->req_payload) BufItemPool<uint8_t>::delete_buf_item_pool(rr->req_payload);
+      if (rr->resp_payload) BufItemPool<uint8_t>::delete_buf_item_pool(rr->resp_payload);
+      rr_base_free(rr);
+    }
+  }
+  int get_pool_size() const { return pool_size_; }
+  std::vector<p2p_rpc_rr*>& get_rr_pool() { return rr_pool_; }
+
+  void setup_and_init_rr_pool(const p2p_rpc_conn_info* src_conn_info, size_t req_size, size_t resp_size, int device_id) {
+    for (int i = 0; i < pool_size_; i++) {
+      p2p_rpc_rr* rr = rr_proto_alloc(src_conn_info, req_size, resp_size);
+      rr->req_payload = alloc_mem(req_size, device_id);
+      rr->resp_payload = alloc_mem(resp_size, device_id);
+      rr->req_device_id = rr->resp_device_id = device_id;
+      rr_pool_.push_back(rr);
+      free_.push(rr);
+    }
+  }
+  // Record of the header's token; a new one is taken from the free ring.  nullptr when the pool is exhausted.
+  p2p_rpc_rr* get_rr(p2p_rpc_hdr* rpc_hdr) {
+    std::lock_guard<std::mutex> g(mu_);
+    auto it = rr_cache_.find(rpc_hdr->req_token);
+    if (it != rr_cache_.end()) return it->second;
+    p2p_rpc_rr* rr = nullptr;
+    if (!free_.pop(rr)) return nullptr;
+    rr->req_token = rpc_hdr->req_token;
+    rr->rr_state = RR_V1_INUSE;
+    set_conn_info(&rr->_client_conn_info, rpc_hdr);
+    rr_cache_[rr->req_token] = rr;
+    return rr;
+  }
+  p2p_rpc_rr* consume_rr() {
+    p2p_rpc_rr* rr = nullptr;
+    if (!free_.pop(rr)) return nullptr;
+    rr->rr_state = RR_V1_INUSE;
+    return rr;
+  }
+  void reap_rr(p2p_rpc_rr* rr) {
+    {
+      std::lock_guard<std::mutex> g(mu_);
+      rr_cache_.erase(rr->req_token);
+    }
+    rr_clear_bufs(rr);
+    rr->req_token = 0;
+    rr->rr_state = RR_V1_UNUSED;
+    free_.push(rr);
+  }
+  size_t num_free() const { return free_.size(); }
+};
+
+}  // namespace p2p_rpc_v1
+
+// ------------------------------------------------------------------ kernel-UDP records
+// UdpRpcHdr, the datagram header of the socket path, is defined with the wire format (p2p_rpc.h).
+static constexpr size_t UDP_RPC_HEADER_LEN = sizeof(UdpRpcHdr);
+static inline uint64_t get_req_token(const UdpRpcHdr* h) { return h->req_token; }
+static inline uint16_t get_seq_num(const UdpRpcHdr* h) { return h->seq_num; }
+
+enum UDP_RR_STATES : uint32_t { UDP_RR_CREATE, UDP_RR_PROCESS, UDP_RR_READY, UDP_RR_FINISH, UDP_RR_UNUSED };
+
+// One RPC on the socket path.  A request or response is held twice: as one contiguous payload and as a list of
+// datagram buffers (header + up to MTU payload bytes each); req_to_bufs / bufs_to_req and resp_to_bufs / bufs_to_resp
+// convert between the two.
+class UdpRr {
+  static void alloc_bufs(p2p_bufs* b, size_t total) {
+    const size_t mtu = rpc_mtu();
+    size_t n = num_fragments(total, mtu), left = total;
+    if (n > MAX_BI_SIZE) n = MAX_BI_SIZE;
+    b->num_items = (uint16_t)n;
+    for (size_t i = 0; i < n; i++) {
+      size_t len = left < mtu ? left : mtu;
+      left -= len;
+      b->burst_items[i] = (uintptr_t) new uint8_t[UDP_RPC_HEADER_LEN + len];
+      b->item_size[i] = UDP_RPC_HEADER_LEN + len;
+    }
+  }
+  static void release_bufs(p2p_bufs* b) {
+    for (size_t i = 0; i < b->num_items; i++) delete[] (uint8_t*)b->burst_items[i];
+    b->num_items = 0;
+  }
+  static size_t payload_to_bufs(const uint8_t* payload, size_t size, p2p_bufs* b, uint64_t token) {
+    size_t off = 0;
+    for (size_t i = 0; i < b->num_items && off < size; i++) {
+      uint8_t* buf = (uint8_t*)b->burst_items[i];
+      UdpRpcHdr* h = (UdpRpcHdr*)buf;
+      std::memset(h, 0, sizeof(*h));
+      h->req_token = token;
+      h->seq_num = (uint16_t)i;
+      size_t len = b->item_size[i] - UDP_RPC_HEADER_LEN;
+      if (len > size - off) len = size - off;
+      std::memcpy(buf + UDP_RPC_HEADER_LEN, payload + off, len);
+      off += len;
+    }
+    return off;
+  }
+  static size_t bufs_to_payload(const p2p_bufs* b, uint8_t* payload, size_t cap) {
+    size_t off = 0;
+    for (size_t i = 0; i < b->num_items; i++) {
+      size_t len = b->item_size[i] - UDP_RPC_HEADER_LEN;
+      if (off + len > cap) len = cap - off;
+      std::memcpy(payload + off, (const uint8_t*)b->burst_items[i] + UDP_RPC_HEADER_LEN, len);
+      off += len;
+    }
+    return off;
+  }
+
+ public:
+  uint64_t req_token = 0;
+  size_t rr_idx = 0;
+  uint8_t *req_payload = nullptr, *resp_payload = nullptr;
+  size_t req_size = 0, resp_size = 0;
+  int req_device_id = -1, resp_device_id = -1;
+  size_t max_req_size, max_resp_size;
+  p2p_bufs* req_bufs;
+  p2p_bufs* resp_bufs;
+  uint32_t rr_state = UDP_RR_CREATE;
+  sockaddr_in si_server{}, si_other{};
+  int my_sock = -1;
+
+  explicit UdpRr(size_t _max_req_size = 0, size_t _max_resp_size = 0)
+      : max_req_size(_max_req_size), max_resp_size(_max_resp_size), req_bufs(new p2p_bufs()), resp_bufs(new p2p_bufs()) {}
+  ~UdpRr() {
+    release_req_bufs();
+    release_resp_bufs();
+    delete req_bufs;
+    delete resp_bufs;
+  }
+  UdpRr(const UdpRr&) = delete;
+
+  void alloc_req_bufs() { alloc_bufs(req_bufs, max_req_size); }
+  void alloc_resp_bufs() { alloc_bufs(resp_bufs, max_resp_size); }
+  void release_req_bufs() { release_bufs(req_bufs); }
+  void release_resp_bufs() { release_bufs(resp_bufs); }
+  // Records a received datagram (header + payload, `item_size` bytes in all) at its sequence number.
+  void rr_merge_req_buf(uintptr_t buf, size_t item_size, int seq_num) {
+    if (seq_num < 0 || seq_num >= MAX_BI_SIZE || item_size < UDP_RPC_HEADER_LEN) return;
+    req_bufs->burst_items[seq_num] = buf;
+    req_bufs->item_size[seq_num] = item_size;
+    if (req_bufs->num_items < seq_num + 1) req_bufs->num_items = (uint16_t)(seq_num + 1);
+    req_size += item_size - UDP_RPC_HEADER_LEN;
+  }
+  void rr_merge_resp_buf(uintptr_t buf, size_t item_size, int seq_num) {
+    if (seq_num < 0 || seq_num >= MAX_BI_SIZE || item_size < UDP_RPC_HEADER_LEN) return;
+    resp_bufs->burst_items[seq_num] = buf;
+    resp_bufs->item_size[seq_num] = item_size;
+    if (resp_bufs->num_items < seq_num + 1) resp_bufs->num_items = (uint16_t)(seq_num + 1);
+    resp_size += item_size - UDP_RPC_HEADER_LEN;
+  }
+  size_t req_to_bufs() { return payload_to_bufs(req_payload, max_req_size, req_bufs, req_token); }
+  size_t bufs_to_req() { return bufs_to_payload(req_bufs, req_payload, max_req_size); }
+  size_t resp_to_bufs() { return payload_to_bufs(resp_payload, max_resp_size, resp_bufs, req_token); }
+  size_t bufs_to_resp() { return bufs_to_payload(resp_bufs, resp_payload, max_resp_size); }
+  bool is_req_ready() const { return req_size == max_req_size; }
+  bool is_resp_ready() const { return resp_size == max_resp_size; }
+};
+
+// Pool of socket-path records over one request arena and one response arena (its own, or the caller's: the original's
+// SmartNIC proxy hands in a registered staging region).  Records move free -> (by token) in process -> process queue
+// -> ready queue -> free.
+class UdpRrPool {
+  std::unordered_map<uint64_t, UdpRr*> rr_cache_;
+  std::vector<UdpRr*> rr_pool_;
+  int pool_size_;
+  size_t req_size_ = 0, resp_size_ = 0;
+  uint8_t *req_arena_internal_ = nullptr, *resp_arena_internal_ = nullptr;
+  MpmcRing<UdpRr*> ready_, process_, free_;
+  std::mutex mu_;
+
+ public:
+  explicit UdpRrPool(int pool_size = MAX_WI_SIZE - 1)
+      : pool_size_(pool_size), ready_((size_t)1 << 12), process_((size_t)1 << 12), free_((size_t)1 << 12) {}
+  ~UdpRrPool() {
+    for (UdpRr* rr : rr_pool_) delete rr;
+    delete[] req_arena_internal_;
+    delete[] resp_arena_internal_;
+  }
+  UdpRr** get_rr_pool() { return rr_pool_.data(); }
+  int get_pool_size() const { return pool_size_; }
+
+  void setup_and_init_rr_pool_with_preallocation(uint8_t* req_arena, size_t req_size, uint8_t* resp_arena, size_t resp_size) {
+    req_size_ = req_size;
+    resp_size_ = resp_size;
+    for (int i = 0; i < pool_size_; i++) {
+      UdpRr* rr = new UdpRr(req_size, resp_size);
+      rr->req_payload = req_arena + (size_t)i * req_size;
+      rr->resp_payload = resp_arena + (size_t)i * resp_size;
+      rr->rr_state = UDP_RR_UNUSED;
+      rr->rr_idx = (size_t)i;
+      rr_pool_.push_back(rr);
+      free_.push(rr);
+    }
+  }
+  void setup_and_init_rr_pool(size_t req_size, size_t resp_size) {
+    req_arena_internal_ = new uint8_t[req_size * (size_t)pool_size_]();
+    resp_arena_internal_ = new uint8_t[resp_size * (size_t)pool_size_]();
+    setup_and_init_rr_pool_with_preallocation(req_arena_internal_, req_size, resp_arena_internal_, resp_size);
+  }
+  // nullptr when no record is free (the original spins forever here).
+  UdpRr* consume_rr() {
+    UdpRr* rr = nullptr;
+    return free_.pop(rr) ? rr : nullptr;
+  }
+  UdpRr* get_rr(const UdpRpcHdr* hdr) {
+    std::lock_guard<std::mutex> g(mu_);
+    auto it = rr_cache_.find(hdr->req_token);
+    if (it != rr_cache_.end()) return it->second;
+    UdpRr* rr = consume_rr();
+    if (!rr) return nullptr;
+    rr->req_token = hdr->req_token;
+    rr->rr_state = UDP_RR_PROCESS;
+    rr->req_size = rr->resp_size = 0;
+    rr_cache_[rr->req_token] = rr;
+    return rr;
+  }
+  void reap_rr(UdpRr* rr) {
+    rr->req_token = 0;
+    rr->rr_state = UDP_RR_UNUSED;
+    free_.push(rr);
+  }
+  void mark_process_rr(UdpRr* rr) {
+    {
+      std::lock_guard<std::mutex> g(mu_);
+      rr_cache_.erase(rr->req_token);
+    }
+    rr->rr_state = UDP_RR_READY;
+    process_.push(rr);
+  }
+  UdpRr* consume_process_rr() {
+    UdpRr* rr = nullptr;
+    return process_.pop(rr) ? rr : nullptr;
+  }
+  void mark_ready_rr(UdpRr* rr) { ready_.push(rr); }
+  UdpRr* consume_ready_rr() {
+    UdpRr* rr = nullptr;
+    return ready_.pop(rr) ? rr : nullptr;
+  }
+  int get_next_rx_ready_rr(UdpRr** next_rr) {
+    *next_rr = consume_process_rr();
+    return *next_rr ? 1 : 0;
+  }
+};

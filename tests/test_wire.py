@@ -171,3 +171,9 @@ def test_multi_tensor_pack_list(C):
         for bi in range(batch):
             assert np.array_equal(o[bi * s:(bi + 1) * s], req[off:off + s])
         off += s
+
+
+def test_older_public_types(C):
+    """BufItemPool, the first-generation record and pool, UdpRr / UdpRrPool keep the original's names and behaviour."""
+    res = C.compat_selftest(-1)
+    assert res and all(res.values()), res
