@@ -957,6 +957,23 @@ PYBIND11_MODULE(_C, m) {
     return t;
   });
 
+  // ---- model files in the original's formats
+  m.def("load_lenet_ref_weights", [](const std::string& dataset_dir) {
+    std::vector<std::vector<float>> w;
+    if (!load_lenet_ref_weights(dataset_dir, &w)) throw std::runtime_error("cannot read data/lenet/data{2,0,1,3}.dat under " + dataset_dir);
+    std::vector<py::array_t<float>> out;
+    for (auto& v : w) out.emplace_back(py::array_t<float>((ssize_t)v.size(), v.data()));
+    return out;
+  });
+  m.def("load_lstm_constants", [](const std::string& dir, const std::string& manifest, int layers, int H) {
+    std::vector<std::vector<float>> w;
+    std::string err = load_lstm_constant_dir(dir, manifest, layers, H, &w);
+    if (!err.empty()) throw std::runtime_error("load_lstm_constants: " + err);
+    std::vector<py::array_t<float>> out;
+    for (auto& v : w) out.emplace_back(py::array_t<float>((ssize_t)v.size(), v.data()));
+    return out;
+  }, py::arg("dir"), py::arg("manifest"), py::arg("layers") = 8, py::arg("H") = 256);
+
   // ---- CPU oracles callable on numpy arrays
   m.def("cpu_lenet5", [](const std::vector<py::array_t<float, py::array::c_style | py::array::forcecast>>& weights,
                          py::array_t<float, py::array::c_style | py::array::forcecast> x) {

@@ -9,6 +9,7 @@
 #include "cuda/gemm_tp.h"
 #include "cuda/nn_kernels.h"
 #include "cuda/ops_api.h"
+#include "host/p2p_rpc.h"
 #include "host/p2p_rpc_app.h"
 #include "cuda/parity_kernels.h"
 
@@ -237,6 +238,33 @@ void bind_ops(py::module_& m) {
         py::arg("stream"), py::arg("epoch_base"), py::arg("sig_flags") = std::vector<uintptr_t>{}, py::arg("sig_epoch") = 0,
         py::arg("done_count") = 0);
 
+  // GPU header processor: handle = g_pp_setup(device, launch_type); g_pp_do(handle, [addresses], clear_sockperf);
+  // g_pp_stop(handle).
+  m.def("g_pp_setup", [](int device, int launch_type) {
+    pp_handler_ctx* c = setup_g_pp(device, launch_type);
+    if (!c) throw std::runtime_error("setup_g_pp failed");
+    return (uintptr_t)c;
+  }, py::arg("device") = 0, py::arg("launch_type") = -1);
+  m.def("g_pp_do", [](uintptr_t h, const std::vector<uint64_t>& hdr_addrs, bool clear_sockperf) {
+    auto bufs = std::make_unique<p2p_hbufs>();
+    if (hdr_addrs.size() > MAX_BI_SIZE) throw std::invalid_argument("at most 1024 headers per burst");
+    bufs->num_items = (uint16_t)hdr_addrs.size();
+    for (size_t i = 0; i < hdr_addrs.size(); i++) bufs->burst_items[i] = hdr_addrs[i];
+    py::gil_scoped_release rel;
+    return do_g_pp((pp_handler_ctx*)h, bufs.get(), clear_sockperf ? 1 : 0);
+  }, py::arg("handle"), py::arg("hdr_addrs"), py::arg("clear_sockperf") = false);
+  m.def("g_pp_counters", [](uintptr_t h) {
+    uint64_t b, r, t;
+    int lt;
+    g_pp_counters((pp_handler_ctx*)h, &b, &r, &t, &lt);
+    py::dict d;
+    d["bursts"] = b;
+    d["rearmed"] = r;
+    d["timeouts"] = t;
+    d["launch_type"] = lt;
+    return d;
+  });
+  m.def("g_pp_stop", [](uintptr_t h) { stop_g_pp((pp_handler_ctx*)h); });
   m.def("swap_hdrs", [](uintptr_t hdr_ptrs, uintptr_t hdrs_contig, int n, bool clear_sockperf, uintptr_t stream) {
     check(srpc_swap_hdrs((void* const*)hdr_ptrs, (void*)hdrs_contig, n, clear_sockperf ? 1 : 0, (cudaStream_t)stream), "swap_hdrs");
   });

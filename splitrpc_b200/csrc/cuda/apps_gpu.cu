@@ -23,6 +23,7 @@
 #include "apps_gpu.h"
 #include "parity_kernels.h"
 #include "ptx.cuh"
+#include "resp_push.cuh"
 
 namespace {
 
@@ -76,7 +77,7 @@ __device__ __forceinline__ void vec_add_body(const uint8_t* req, uint8_t* resp, 
     uint8_t* d = resp + (size_t)b * resp_size;
     if (vec) {
       for (size_t i = tid; i < n / 16; i += nth) {
-        uint4 v = reinterpret_cast<const uint4*>(s)[i];
+        uint4 v = __ldcg(reinterpret_cast<const uint4*>(s) + i);  // not through L1: a resident kernel re-reads ring addresses
         v.x = add1_bytes(v.x);
         v.y = add1_bytes(v.y);
         v.z = add1_bytes(v.z);
@@ -84,7 +85,7 @@ __device__ __forceinline__ void vec_add_body(const uint8_t* req, uint8_t* resp, 
         reinterpret_cast<uint4*>(d)[i] = v;
       }
     } else {
-      for (size_t i = tid; i < n; i += nth) d[i] = (uint8_t)(s[i] + 1);
+      for (size_t i = tid; i < n; i += nth) d[i] = (uint8_t)(__ldcg(s + i) + 1);
     }
   }
 }
@@ -94,71 +95,30 @@ __global__ void vec_add_kernel(const g_params* stub, size_t req_size, size_t res
                (size_t)gridDim.x * blockDim.x, blockIdx.y, gridDim.y);
 }
 
-// Resident vec_add: one block; waits (bounded) for the doorbell to hold a batch
-// size, serves the batch, answers 2.
-__global__ void vec_add_resident(const g_params* stub, volatile uint32_t* door_bell, size_t req_size, size_t resp_size,
-                                 uint64_t idle_ns, uint32_t* status) {
-  __shared__ uint32_t s_batch, s_leave;
-  uint64_t last = ptx::globaltimer_ns();
-  for (;;) {
-    if (threadIdx.x == 0) {
-      uint32_t batch = 0, leave = 0;
-      for (int spin = 0; spin < 4096; spin++) {
-        const uint32_t v = ptx::ld_acquire_sys(door_bell);
-        if (v == APP_DOORBELL_EXIT || ptx::globaltimer_ns() - last > idle_ns) {
-          leave = 1;  // exit request or idle limit
-          break;
-        }
-        if (v != APP_DOORBELL_IDLE && (v & APP_DOORBELL_START)) {
-          batch = v & ~APP_DOORBELL_START;
-          break;
-        }
-        __nanosleep(200);
-      }
-      s_batch = batch;
-      s_leave = leave;
-    }
-    __syncthreads();
-    const uint32_t batch = s_batch, leave = s_leave;
-    __syncthreads();
-    if (leave) break;
-    if (batch == 0) continue;
-    // The stub lives in mapped host memory and changes between batches while this
-    // kernel stays resident: read it with system-scope loads, never from a cache.
-    g_params p;
-    p.req = reinterpret_cast<uint8_t*>(ptx::ld_relaxed_sys_u64(reinterpret_cast<const uint64_t*>(stub)));
-    p.resp = reinterpret_cast<uint8_t*>(ptx::ld_relaxed_sys_u64(reinterpret_cast<const uint64_t*>(stub) + 1));
-    __threadfence();  // drop request-ring lines an earlier lap may have left in L1
-    vec_add_body(p.req, p.resp, req_size, resp_size, (int)batch, threadIdx.x, blockDim.x, 0, 1);
-    __threadfence_system();
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      ptx::st_release_sys(door_bell, 2u);
-      last = ptx::globaltimer_ns();
-    }
-    __syncthreads();
-  }
-  if (threadIdx.x == 0) ptx::st_release_sys(status, 1u);
-}
-
 // C = A.B for one small square fp32 problem per block (d <= 128).
-__global__ void mm_kernel(const g_params* stub, size_t req_size, size_t resp_size, int d, int batch) {
-  extern __shared__ float sm[];
-  for (int b = blockIdx.x; b < batch; b += gridDim.x) {
-    const float* A = reinterpret_cast<const float*>(stub->req + (size_t)b * req_size);
+// Requests are read with cache-global loads: a resident kernel serves many batches out of the same ring addresses
+// and must not see an earlier lap's bytes in its L1.
+__device__ __forceinline__ void mm_body(const uint8_t* req, uint8_t* resp, size_t req_size, size_t resp_size, int d, int batch,
+                                        int b0, int nb, float* sm) {
+  for (int b = b0; b < batch; b += nb) {
+    const float* A = reinterpret_cast<const float*>(req + (size_t)b * req_size);
     const float* B = A + (size_t)d * d;
-    float* C = reinterpret_cast<float*>(stub->resp + (size_t)b * resp_size);
+    float* C = reinterpret_cast<float*>(resp + (size_t)b * resp_size);
     float* sB = sm;  // B staged in shared memory (<= 64 KB)
-    for (int i = threadIdx.x; i < d * d; i += blockDim.x) sB[i] = B[i];
+    for (int i = threadIdx.x; i < d * d; i += blockDim.x) sB[i] = __ldcg(B + i);
     __syncthreads();
     for (int o = threadIdx.x; o < d * d; o += blockDim.x) {
       int i = o / d, j = o % d;
       float acc = 0.f;
-      for (int k = 0; k < d; k++) acc += A[i * d + k] * sB[k * d + j];
+      for (int k = 0; k < d; k++) acc += __ldcg(A + i * d + k) * sB[k * d + j];
       C[o] = acc;
     }
     __syncthreads();
   }
+}
+__global__ void mm_kernel(const g_params* stub, size_t req_size, size_t resp_size, int d, int batch) {
+  extern __shared__ float sm[];
+  mm_body(stub->req, stub->resp, req_size, resp_size, d, batch, blockIdx.x, gridDim.x, sm);
 }
 
 // LeNet-5, whole network in one kernel, one image per block (256 threads).
@@ -167,7 +127,7 @@ struct LeNetW {
   const float *c1w, *c1b, *c2w, *c2b, *f1w, *f1b, *f2w, *f2b, *f3w, *f3b;
 };
 
-__global__ void __launch_bounds__(256) lenet5_kernel(const g_params* stub, LeNetW w, int batch) {
+__device__ __forceinline__ void lenet5_body(const uint8_t* req, uint8_t* resp, const LeNetW& w, int batch, int b0, int nb) {
   __shared__ float x[28 * 28];
   __shared__ float p1[6 * 14 * 14];
   __shared__ float p2[16 * 5 * 5];
@@ -181,11 +141,11 @@ __global__ void __launch_bounds__(256) lenet5_kernel(const g_params* stub, LeNet
   for (int i = t; i < 6; i += 256) wc1[150 + i] = w.c1b[i];
   for (int i = t; i < 2400; i += 256) wc2[i] = w.c2w[i];
   for (int i = t; i < 16; i += 256) wc2[2400 + i] = w.c2b[i];
-  for (int b = blockIdx.x; b < batch; b += gridDim.x) {
-    const float* in = reinterpret_cast<const float*>(stub->req + (size_t)b * LENET5_REQ_BYTES);
-    float* out = reinterpret_cast<float*>(stub->resp + (size_t)b * LENET5_RESP_BYTES);
+  for (int b = b0; b < batch; b += nb) {
+    const float* in = reinterpret_cast<const float*>(req + (size_t)b * LENET5_REQ_BYTES);
+    float* out = reinterpret_cast<float*>(resp + (size_t)b * LENET5_RESP_BYTES);
     __syncthreads();
-    for (int i = t; i < 784; i += 256) x[i] = in[i];
+    for (int i = t; i < 784; i += 256) x[i] = __ldcg(in + i);  // not through L1: see mm_body
     __syncthreads();
     // conv1 (pad 2) + relu + 2x2 maxpool fused: each thread makes pooled outputs
     for (int o = t; o < 6 * 14 * 14; o += 256) {
@@ -261,6 +221,70 @@ __global__ void __launch_bounds__(256) lenet5_kernel(const g_params* stub, LeNet
   }
 }
 
+__global__ void __launch_bounds__(256) lenet5_kernel(const g_params* stub, LeNetW w, int batch) {
+  lenet5_body(stub->req, stub->resp, w, batch, blockIdx.x, gridDim.x);
+}
+
+// Resident ("persistent thread") form of an app, launch type 3 of the original (reference
+// src/apps/lenet/lenet_vanilla.cu:371-443, src/apps/mm.cu:60-86, src/apps/vec_add/vector_add.cu:63-90): one block stays
+// on the GPU, waits (bounded, with an idle limit after which it leaves and the host re-arms it) for the doorbell to
+// hold a batch size, serves the batch, answers 2.  KIND selects the body.
+enum { RESIDENT_VEC_ADD = 0, RESIDENT_MATMUL = 1, RESIDENT_LENET5 = 2 };
+struct ResidentArgs {
+  size_t req_size, resp_size;
+  int dim;
+  LeNetW w;
+};
+template <int KIND>
+__global__ void app_resident(const g_params* stub, volatile uint32_t* door_bell, ResidentArgs a, uint64_t idle_ns, uint32_t* status,
+                             const RespPushCtx* push) {
+  extern __shared__ float dyn_sm[];
+  __shared__ uint32_t s_batch, s_leave;
+  uint64_t last = ptx::globaltimer_ns();
+  for (;;) {
+    if (threadIdx.x == 0) {
+      uint32_t batch = 0, leave = 0;
+      for (int spin = 0; spin < 4096; spin++) {
+        const uint32_t v = ptx::ld_acquire_sys(door_bell);
+        if (v == APP_DOORBELL_EXIT || ptx::globaltimer_ns() - last > idle_ns) {
+          leave = 1;  // exit request or idle limit
+          break;
+        }
+        if (v != APP_DOORBELL_IDLE && (v & APP_DOORBELL_START)) {
+          batch = v & ~APP_DOORBELL_START;
+          break;
+        }
+        __nanosleep(200);
+      }
+      s_batch = batch;
+      s_leave = leave;
+    }
+    __syncthreads();
+    const uint32_t batch = s_batch, leave = s_leave;
+    __syncthreads();
+    if (leave) break;
+    if (batch == 0) continue;
+    // The stub lives in mapped host memory and changes between batches while this
+    // kernel stays resident: read it with system-scope loads, never from a cache.
+    uint8_t* req = reinterpret_cast<uint8_t*>(ptx::ld_relaxed_sys_u64(reinterpret_cast<const uint64_t*>(stub)));
+    uint8_t* resp = reinterpret_cast<uint8_t*>(ptx::ld_relaxed_sys_u64(reinterpret_cast<const uint64_t*>(stub) + 1));
+    if (KIND == RESIDENT_VEC_ADD) vec_add_body(req, resp, a.req_size, a.resp_size, (int)batch, threadIdx.x, blockDim.x, 0, 1);
+    else if (KIND == RESIDENT_MATMUL) mm_body(req, resp, a.req_size, a.resp_size, a.dim, (int)batch, 0, 1, dyn_sm);
+    else lenet5_body(req, resp, a.w, (int)batch, 0, 1);
+    __threadfence_system();
+    __syncthreads();
+    // This kernel owns its stream for good, so nothing can be queued behind it: it stores the responses where the
+    // producer wants them and completes the slots itself (inert unless the server enabled that).
+    resp_push_rows_block(push, resp, (uint32_t)a.resp_size, (int)batch);
+    if (threadIdx.x == 0) {
+      ptx::st_release_sys(door_bell, 2u);
+      last = ptx::globaltimer_ns();
+    }
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) ptx::st_release_sys(status, 1u);
+}
+
 // ------------------------------------------------------------------ launch
 LeNetW lenet_w(const GpuAppState* s) {
   const float* b = s->d_weights;
@@ -300,20 +324,22 @@ int gpu_app_init(AppCtx* c) {
     srpc_log(SRPC_LOG_ERROR, "launch type 2 (device-side launch + device-side sync) is not available on sm_100");
     return 0;
   }
-  if (c->launch_type == 3 && s->name != "vec_add") {
-    srpc_log(SRPC_LOG_WARN, "resident launch type is implemented for vec_add only; using kernel launches");
-    c->launch_type = 1;
+  if (c->launch_type == 3 && s->name != "vec_add" && s->name != "matmul" && s->name != "lenet5") {
+    srpc_log(SRPC_LOG_ERROR, "resident launch type (3) exists for vec_add, matmul and lenet5; app '%s' has none", s->name.c_str());
+    return 0;
   }
   cudaSetDevice(c->device_id);
   if (s->name == "matmul") {
     if (!s->dim) s->dim = mm_dim_from_req(s->req_size);
     if (s->dim > 128) return 0;
     cudaFuncSetAttribute(mm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 128 * 4);
+    cudaFuncSetAttribute(app_resident<RESIDENT_MATMUL>, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 128 * 4);
   }
   if (s->name == "lstm") {
     if (cudaMalloc(&s->d_scratch, srpc_lstm_scratch_bytes(s->lstm_clusters)) != cudaSuccess) return 0;
   }
   if (c->launch_type == 3) {
+    c->self_push = true;  // the resident kernel stores responses and completes slots itself
     cudaHostAlloc(&s->h_pt_status, 4, cudaHostAllocMapped);
     cudaHostGetDevicePointer((void**)&s->d_pt_status, s->h_pt_status, 0);
     *s->h_pt_status = 1;  // not running yet
@@ -331,8 +357,16 @@ int gpu_app_run(AppCtx* c) {
       *s->h_pt_status = 0;
       c->ResetAppRunStatus();
       std::atomic_thread_fence(std::memory_order_seq_cst);
-      vec_add_resident<<<1, 1024, 0, c->work_stream>>>(c->d_stub, c->d_door_bell, s->req_size, s->resp_size, s->idle_ns,
-                                                       s->d_pt_status);
+      ResidentArgs a{s->req_size, s->resp_size, s->dim, LeNetW{}};
+      if (s->name == "vec_add") {
+        app_resident<RESIDENT_VEC_ADD><<<1, 1024, 0, c->work_stream>>>(c->d_stub, c->d_door_bell, a, s->idle_ns, s->d_pt_status, c->d_push);
+      } else if (s->name == "matmul") {
+        app_resident<RESIDENT_MATMUL><<<1, 256, (size_t)s->dim * s->dim * 4, c->work_stream>>>(c->d_stub, c->d_door_bell, a,
+                                                                                               s->idle_ns, s->d_pt_status, c->d_push);
+      } else {
+        a.w = lenet_w(s);
+        app_resident<RESIDENT_LENET5><<<1, 256, 0, c->work_stream>>>(c->d_stub, c->d_door_bell, a, s->idle_ns, s->d_pt_status, c->d_push);
+      }
     }
     c->NotifyAppRunStart();
     return cudaGetLastError() == cudaSuccess;
@@ -393,7 +427,9 @@ GpuAppHandle srpc_make_gpu_app(const char* name, int device_id, size_t req_size,
     cudaFuncAttributes fa;
     (void)cudaFuncGetAttributes(&fa, echo_kernel);
     (void)cudaFuncGetAttributes(&fa, vec_add_kernel);
-    (void)cudaFuncGetAttributes(&fa, vec_add_resident);
+    (void)cudaFuncGetAttributes(&fa, app_resident<RESIDENT_VEC_ADD>);
+    (void)cudaFuncGetAttributes(&fa, app_resident<RESIDENT_MATMUL>);
+    (void)cudaFuncGetAttributes(&fa, app_resident<RESIDENT_LENET5>);
     (void)cudaFuncGetAttributes(&fa, mm_kernel);
     (void)cudaFuncGetAttributes(&fa, lenet5_kernel);
     srpc_parity_preload();

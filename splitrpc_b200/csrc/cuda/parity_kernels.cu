@@ -16,6 +16,7 @@
 #include "../host/p2p_rpc.h"
 #include "../host/p2p_rpc_app.h"
 #include "parity_kernels.h"
+#include "ptx.cuh"
 
 namespace cg = cooperative_groups;
 
@@ -37,6 +38,67 @@ __global__ void swap_hdrs_contig_kernel(p2p_rpc_hdr* hdrs, int n, int clear_sock
   p2p_rpc_hdr* h = hdrs + i;
   swap_eth_hdr(h);
   if (clear_sockperf) set_sockperf_header(h);
+  add_udp_cksum(h);
+}
+
+// Resident header processor (launch type 2 of the GPU header-processing API): one block stays on the GPU and serves
+// bursts of header pointers that the host posts in a mapped control block.  The doorbell is a sequence number, every
+// poll also looks at the exit flag and the idle limit, and a burst is acknowledged by publishing its number in `done`.
+__global__ void __launch_bounds__(1024) persistent_swap_hdrs(pp_params* stub, volatile uint32_t* door_bell, volatile uint32_t* done,
+                                                             volatile uint32_t* exit_flag, volatile uint32_t* exited,
+                                                             uint64_t idle_ns) {
+  __shared__ uint32_t s_cmd, s_seq, s_n;
+  uint32_t seen = *done;
+  uint64_t last = ptx::globaltimer_ns();
+  for (;;) {
+    if (threadIdx.x == 0) {
+      uint32_t cmd = 0;
+      for (int spin = 0; spin < 4096; spin++) {
+        if (ptx::ld_relaxed_sys(exit_flag) || ptx::globaltimer_ns() - last > idle_ns) {
+          cmd = 2;
+          break;
+        }
+        const uint32_t db = ptx::ld_acquire_sys(door_bell);
+        if ((int32_t)(db - seen) > 0) {
+          s_seq = db;
+          s_n = ptx::ld_relaxed_sys(reinterpret_cast<const volatile uint32_t*>(&stub->num_items));
+          cmd = 1;
+          break;
+        }
+        __nanosleep(200);
+      }
+      s_cmd = cmd;
+    }
+    __syncthreads();
+    const uint32_t cmd = s_cmd, seq = s_seq;
+    uint32_t n = s_n;
+    __syncthreads();
+    if (cmd == 2) break;
+    if (cmd == 0) continue;
+    seen = seq;
+    if (n > MAX_BI_SIZE) n = MAX_BI_SIZE;
+    for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) {
+      p2p_rpc_hdr* h = reinterpret_cast<p2p_rpc_hdr*>(ptx::ld_relaxed_sys_u64(reinterpret_cast<const uint64_t*>(&stub->hdr_ptrs[i])));
+      swap_eth_hdr(h);
+      if (stub->clear_sockperf) set_sockperf_header(h);
+      add_udp_cksum(h);
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      ptx::st_release_sys(done, seen);
+      last = ptx::globaltimer_ns();
+    }
+  }
+  if (threadIdx.x == 0) ptx::st_release_sys(exited, 1u);
+}
+
+__global__ void swap_hdrs_stub_kernel(const pp_params* stub) {
+  const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= stub->num_items) return;
+  p2p_rpc_hdr* h = reinterpret_cast<p2p_rpc_hdr*>(stub->hdr_ptrs[i]);
+  swap_eth_hdr(h);
+  if (stub->clear_sockperf) set_sockperf_header(h);
   add_udp_cksum(h);
 }
 
@@ -211,8 +273,136 @@ cudaError_t srpc_lenet_ref(const void* d_stub, const void* direct_in, float* dir
   return cudaGetLastError();
 }
 
+// ------------------------------------------------------------------ GPU header-processing API
+struct pp_handler_ctx {
+  pp_params* h_stub = nullptr;  // mapped pinned: the burst the host posts
+  pp_params* d_stub = nullptr;
+  volatile uint32_t* h_words = nullptr;  // [0] doorbell, [1] done, [2] exit flag, [3] exited
+  uint32_t* d_words = nullptr;
+  cudaStream_t g_stream = nullptr;
+  uint8_t launch_type = 0;  // 0 none, 1 one kernel launch per burst, 2 resident kernel
+  int device = 0;
+  uint32_t seq = 0;
+  bool resident = false;
+  uint64_t idle_ns = 200000000ull, wait_ns = 2000000000ull;
+  uint64_t bursts = 0, rearmed = 0, timeouts = 0;
+};
+
+static bool g_pp_stop_resident(pp_handler_ctx* c) {
+  if (!c->resident) return true;
+  __atomic_store_n(&c->h_words[2], 1u, __ATOMIC_RELEASE);
+  const uint64_t t0 = getCurNs();
+  while (__atomic_load_n(&c->h_words[3], __ATOMIC_ACQUIRE) == 0) {
+    if (getCurNs() - t0 > c->wait_ns) return false;
+  }
+  cudaStreamSynchronize(c->g_stream);
+  c->resident = false;
+  return true;
+}
+static bool g_pp_ensure_resident(pp_handler_ctx* c) {
+  if (c->resident && __atomic_load_n(&c->h_words[3], __ATOMIC_ACQUIRE) == 0) return true;
+  if (!g_pp_stop_resident(c)) return false;  // it left after its idle limit: collect it, then launch again
+  if (c->bursts) c->rearmed++;
+  c->h_words[0] = c->seq;
+  c->h_words[1] = c->seq;
+  c->h_words[2] = 0;
+  c->h_words[3] = 0;
+  std::atomic_thread_fence(std::memory_order_seq_cst);
+  persistent_swap_hdrs<<<1, 1024, 0, c->g_stream>>>(c->d_stub, c->d_words, c->d_words + 1, c->d_words + 2, c->d_words + 3, c->idle_ns);
+  if (cudaGetLastError() != cudaSuccess) return false;
+  c->resident = true;
+  return true;
+}
+
+pp_handler_ctx* setup_g_pp(int device, int launch_type) {
+  if (launch_type < 0) launch_type = (int)readEnvInfo<uint16_t>("P2P_RPC_G_PP_LAUNCH_TYPE", 2);
+  if (cudaSetDevice(device) != cudaSuccess) return nullptr;
+  srpc_parity_preload();
+  pp_handler_ctx* c = new pp_handler_ctx;
+  c->device = device;
+  c->launch_type = (uint8_t)((launch_type == 1 || launch_type == 2) ? launch_type : 0);
+  c->idle_ns = (uint64_t)readEnvInfo<uint64_t>("P2P_RPC_G_PP_IDLE_MS", 200) * 1000000ull;
+  void *h = nullptr, *w = nullptr;
+  if (cudaStreamCreateWithFlags(&c->g_stream, cudaStreamNonBlocking) != cudaSuccess ||
+      cudaHostAlloc(&h, sizeof(pp_params), cudaHostAllocMapped | cudaHostAllocPortable) != cudaSuccess ||
+      cudaHostAlloc(&w, 64, cudaHostAllocMapped | cudaHostAllocPortable) != cudaSuccess) {
+    delete c;
+    return nullptr;
+  }
+  std::memset(h, 0, sizeof(pp_params));
+  std::memset(w, 0, 64);
+  c->h_stub = (pp_params*)h;
+  c->h_words = (volatile uint32_t*)w;
+  cudaHostGetDevicePointer((void**)&c->d_stub, h, 0);
+  cudaHostGetDevicePointer((void**)&c->d_words, w, 0);
+  if (c->launch_type == 2 && !g_pp_ensure_resident(c)) c->launch_type = 1;
+  return c;
+}
+
+int do_g_pp(pp_handler_ctx* c, const p2p_hbufs* h_wi, int clear_sockperf) {
+  if (!c || c->launch_type == 0 || !h_wi || h_wi->num_items == 0) return 0;
+  cudaSetDevice(c->device);
+  const uint32_t n = h_wi->num_items;
+  for (uint32_t i = 0; i < n; i++) c->h_stub->hdr_ptrs[i] = h_wi->burst_items[i];
+  c->h_stub->num_items = n;
+  c->h_stub->clear_sockperf = (uint32_t)clear_sockperf;
+  std::atomic_thread_fence(std::memory_order_release);
+  c->bursts++;
+  if (c->launch_type == 2) {
+    for (int attempt = 0; attempt < 2; attempt++) {
+      if (!g_pp_ensure_resident(c)) return -2;
+      const uint32_t s = ++c->seq;
+      __atomic_store_n(&c->h_words[0], s, __ATOMIC_RELEASE);
+      const uint64_t t0 = getCurNs();
+      bool gone = false;
+      for (;;) {
+        if (__atomic_load_n(&c->h_words[1], __ATOMIC_ACQUIRE) == s) return 0;
+        if (__atomic_load_n(&c->h_words[3], __ATOMIC_ACQUIRE) != 0) {
+          gone = true;
+          break;
+        }
+        if (getCurNs() - t0 > c->wait_ns) break;
+      }
+      // it left (idle limit) around the doorbell, or the wait ran out: stop it for good before anything else.  A header
+      // swap is not idempotent, so the burst is only repeated when the kernel left without having touched it.
+      const bool served = __atomic_load_n(&c->h_words[1], __ATOMIC_ACQUIRE) == s;
+      if (!g_pp_stop_resident(c)) return -2;
+      if (served || __atomic_load_n(&c->h_words[1], __ATOMIC_ACQUIRE) == s) return 0;
+      if (!gone) {
+        c->timeouts++;
+        return -1;
+      }
+    }
+    c->timeouts++;
+    return -1;
+  }
+  swap_hdrs_stub_kernel<<<(n + 255) / 256, 256, 0, c->g_stream>>>(c->d_stub);
+  if (cudaGetLastError() != cudaSuccess) return -3;
+  return cudaStreamSynchronize(c->g_stream) == cudaSuccess ? 0 : -3;
+}
+
+void g_pp_counters(const pp_handler_ctx* c, uint64_t* bursts, uint64_t* rearmed, uint64_t* timeouts, int* launch_type) {
+  *bursts = c->bursts;
+  *rearmed = c->rearmed;
+  *timeouts = c->timeouts;
+  *launch_type = c->launch_type;
+}
+
+void stop_g_pp(pp_handler_ctx* c) {
+  if (!c) return;
+  cudaSetDevice(c->device);
+  g_pp_stop_resident(c);
+  cudaStreamSynchronize(c->g_stream);
+  cudaStreamDestroy(c->g_stream);
+  cudaFreeHost(c->h_stub);
+  cudaFreeHost((void*)c->h_words);
+  delete c;
+}
+
 void srpc_parity_preload() {
   cudaFuncAttributes fa;
+  (void)cudaFuncGetAttributes(&fa, persistent_swap_hdrs);
+  (void)cudaFuncGetAttributes(&fa, swap_hdrs_stub_kernel);
   (void)cudaFuncGetAttributes(&fa, swap_hdrs_kernel);
   (void)cudaFuncGetAttributes(&fa, swap_hdrs_contig_kernel);
   (void)cudaFuncGetAttributes(&fa, lenet_ref_kernel);

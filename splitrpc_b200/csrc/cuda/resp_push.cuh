@@ -21,7 +21,9 @@ struct RespPushTarget {
 // read costs a PCIe round trip.  Call this from ONE thread per response and hand the result to the others through
 // shared memory (resp_push_target_block does that); thousands of threads reading it at once cost more than the
 // softmax they belong to.
-__device__ __forceinline__ RespPushTarget resp_push_target(const RespPushCtx* ctx, uint32_t row, uint8_t* ring_dst) {
+__device__ __forceinline__ RespPushTarget resp_push_target(const RespPushCtx* ctx_, uint32_t row, uint8_t* ring_dst) {
+  // volatile: a resident kernel looks at the block once per batch and must see what the host wrote since the last one
+  const volatile RespPushCtx* ctx = ctx_;
   RespPushTarget t{ring_dst, nullptr};
   if (!ctx || ctx->enabled == 0 || ctx->pool_size == 0) return t;
   const uint32_t slot = (ctx->first_slot + row) % ctx->pool_size;
@@ -38,6 +40,24 @@ __device__ __forceinline__ RespPushTarget resp_push_target_block(const RespPushC
   if (threadIdx.x == 0) s_target = resp_push_target(ctx, row, ring_dst);
   __syncthreads();
   return s_target;
+}
+
+// Stores the `batch` responses that one block has just produced at resp (resp_size apart) and completes their slots,
+// one after the other.  For kernels that serve a whole batch with one block (resident apps).  Call from all threads.
+__device__ __forceinline__ void resp_push_rows_block(const RespPushCtx* ctx, uint8_t* resp, uint32_t resp_size, int batch) {
+  if (!ctx) return;
+  for (int r = 0; r < batch; r++) {
+    uint8_t* src = resp + (size_t)r * resp_size;
+    const RespPushTarget t = resp_push_target_block(ctx, (uint32_t)r, src);
+    if (t.dst != src)
+      for (uint32_t i = threadIdx.x; i < resp_size; i += blockDim.x) t.dst[i] = src[i];
+    __syncthreads();
+    if (threadIdx.x == 0 && t.state) {
+      __threadfence_system();
+      ptx::st_release_sys(t.state, (uint32_t)APP_RR_STATUS::WORK_COMPLETE);
+    }
+    __syncthreads();
+  }
 }
 
 // Call from one thread, after a __syncthreads() that follows every store of the response by the block.

@@ -18,6 +18,7 @@
 #include <cmath>
 #include <cstring>
 #include <fstream>
+#include <sstream>
 #include <string>
 #include <vector>
 
@@ -189,6 +190,61 @@ static inline bool load_lenet_ref_weights(const std::string& dataset_dir, std::v
     if ((size_t)f.gcount() != counts[i] * 4) return false;
   }
   return true;
+}
+
+// Reads the LSTM's weights from the original's per-constant files: <dir>/Constant_<id>_0.bin, raw fp32, one file per
+// tensor (64 matrices of H x H, 32 vectors of H for the 8-layer model; reference
+// src/apps/nnfusion_lstm/nnfusion_rt.cu:13884-13896 and the Constant/ directory beside it).  Which constant is which
+// tensor is a property of the exported graph, not of the file format, so it comes from a manifest: one line per tensor,
+//     <layer> <W|U|b> <gate: i|g|f|o> <constant id> [T]
+// W multiplies the layer's input, U its previous hidden state; T marks a matrix stored [in][out] (the layout a
+// Dot(x, M) node consumes), which is transposed into the [out][in] rows used here.  Lines starting with # are
+// comments.  Output: per layer W[4][H][H], U[4][H][H], b[4][H] in gate order i, g, f, o (what the apps take).
+// Returns an empty string on success, else what went wrong.
+static inline std::string load_lstm_constant_dir(const std::string& dir, const std::string& manifest_path, int layers, int H,
+                                                 std::vector<std::vector<float>>* out) {
+  std::ifstream mf(manifest_path);
+  if (!mf) return "cannot open manifest " + manifest_path;
+  out->assign((size_t)3 * layers, {});
+  for (int l = 0; l < layers; l++) {
+    (*out)[3 * l].assign((size_t)4 * H * H, 0.f);
+    (*out)[3 * l + 1].assign((size_t)4 * H * H, 0.f);
+    (*out)[3 * l + 2].assign((size_t)4 * H, 0.f);
+  }
+  std::vector<uint8_t> seen((size_t)layers * 12, 0);
+  std::string line;
+  int line_no = 0;
+  std::vector<float> buf;
+  while (std::getline(mf, line)) {
+    line_no++;
+    if (line.empty() || line[0] == '#') continue;
+    std::istringstream ss(line);
+    int layer = -1, id = -1;
+    std::string kind, gate, flag;
+    if (!(ss >> layer >> kind >> gate >> id)) return "manifest line " + std::to_string(line_no) + ": expected <layer> <W|U|b> <gate> <id>";
+    ss >> flag;
+    const int k = kind == "W" ? 0 : (kind == "U" ? 1 : (kind == "b" ? 2 : -1));
+    const int g = gate == "i" ? 0 : (gate == "g" ? 1 : (gate == "f" ? 2 : (gate == "o" ? 3 : -1)));
+    if (layer < 0 || layer >= layers || k < 0 || g < 0 || id < 0) return "manifest line " + std::to_string(line_no) + ": bad field";
+    const size_t count = k == 2 ? (size_t)H : (size_t)H * H;
+    const std::string path = dir + "/Constant_" + std::to_string(id) + "_0.bin";
+    std::ifstream f(path, std::ios::binary);
+    if (!f) return "missing " + path;
+    buf.resize(count);
+    f.read(reinterpret_cast<char*>(buf.data()), (std::streamsize)(count * 4));
+    if ((size_t)f.gcount() != count * 4) return path + " is shorter than " + std::to_string(count * 4) + " bytes";
+    float* dst = (*out)[3 * layer + k].data() + (size_t)g * count;
+    if (k < 2 && flag == "T") {
+      for (int o = 0; o < H; o++)
+        for (int i = 0; i < H; i++) dst[(size_t)o * H + i] = buf[(size_t)i * H + o];
+    } else {
+      std::memcpy(dst, buf.data(), count * 4);
+    }
+    seen[(size_t)layer * 12 + (size_t)k * 4 + g] = 1;
+  }
+  for (size_t i = 0; i < seen.size(); i++)
+    if (!seen[i]) return "manifest does not name layer " + std::to_string(i / 12) + " tensor " + std::to_string((i % 12) / 4) + " gate " + std::to_string(i % 4);
+  return "";
 }
 
 // ---- LSTM cell math of the stacked 8-layer x 8-step, hidden 256 model

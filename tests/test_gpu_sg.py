@@ -162,10 +162,12 @@ def test_gpu_async_stream_armed_mode(C, torch_cuda, mtu8k):
     assert set(ws["batch_hist"]) == {4}
 
 
-def test_gpu_lenet5_matches_cpu_oracle(C, torch_cuda, mtu8k):
+@pytest.mark.parametrize("launch_type", [1, 3, 4])
+def test_gpu_lenet5_matches_cpu_oracle(C, torch_cuda, mtu8k, launch_type):
+    """Kernel launch per batch, resident kernel behind the doorbell (launch type 3), CUDA graph."""
     w = lenet5_weights()
-    ok, cli, st, ss, ws, sg = _serve_gpu(C, "lenet5", 3136, 40, 400, 2, 32, "uniform", 2, 4, weights=w, outstanding=64)
-    assert ok and cli.received == 400
+    ok, cli, st, ss, ws, sg = _serve_gpu(C, "lenet5", 3136, 40, 400, 2, 32, "uniform", 2, launch_type, weights=w, outstanding=64)
+    assert ok and cli.received == 400 and ws["wait_timeouts"] == 0
     for i in (0, 100, 399):
         x = np.frombuffer(cli.payload(i % 16), dtype=np.float32)
         ref = C.cpu_lenet5(w, x)[0]
@@ -173,9 +175,11 @@ def test_gpu_lenet5_matches_cpu_oracle(C, torch_cuda, mtu8k):
         np.testing.assert_allclose(got, ref, rtol=1e-4, atol=1e-5)
 
 
-def test_gpu_matmul(C, torch_cuda, mtu8k):
+@pytest.mark.parametrize("launch_type", [1, 3])
+def test_gpu_matmul(C, torch_cuda, mtu8k, launch_type):
     sp, cp = C.make_loopback_pair(8192, 1024, "pinned")
-    app = C.make_app("matmul", 0, 32768, 16384, [], 64, 1, 2, "gpu", 2)
+    app = C.make_app("matmul", 0, 32768, 16384, [], 64, launch_type, 2, "gpu", 2)
+    assert app.init_ok
     srv = C.Server(sp, req_size=32768, resp_size=16384, server_mode=2, max_batch=2)
     srv.add_replica(app)
     srv.start()
@@ -186,6 +190,13 @@ def test_gpu_matmul(C, torch_cuda, mtu8k):
     a, b = req[:4096].reshape(64, 64), req[4096:].reshape(64, 64)
     got = np.frombuffer(cli.response(5), dtype=np.float32).reshape(64, 64)
     np.testing.assert_allclose(got, a @ b, rtol=1e-4, atol=1e-4)
+
+
+def test_resident_launch_type_is_refused_where_it_does_not_exist(C, torch_cuda):
+    """Launch type 3 exists for vec_add, matmul and lenet5; asking for it elsewhere fails the app's init instead of
+    silently running something else."""
+    app = C.make_app("echo", 0, 1024, 1024, [], 64, 3, 1, "gpu", 2)
+    assert not app.init_ok
 
 
 def test_local_bench_gpu(C, torch_cuda):
@@ -205,6 +216,62 @@ def test_gpu_header_swap_matches_host(C, torch_cuda):
     got = dev.cpu().numpy().tobytes()
     for i in (0, 77, 299):
         assert got[i * 64:(i + 1) * 64] == C.swap_header(hdrs[i])
+
+
+@pytest.mark.parametrize("launch_type", [1, 2])
+def test_gpu_header_processor_api(C, torch_cuda, launch_type, monkeypatch):
+    """setup_g_pp / do_g_pp / stop_g_pp: per-burst launches and the resident kernel, which leaves after its idle limit
+    and is started again by the next burst."""
+    import time
+
+    torch = torch_cuda
+    monkeypatch.setenv("P2P_RPC_G_PP_IDLE_MS", "5")
+    uri = "b8:ce:f6:cc:6a:53,192.168.25.2,50052,b8:ce:f6:cc:6a:52,192.168.25.1,50051"
+    tmpl = C.client_conn_template(uri)
+    h = C.g_pp_setup(0, launch_type)
+    try:
+        for burst in range(3):
+            n = (5, 300, 1024)[burst]
+            hdrs = [C.build_fragments(tmpl, 5000 + 7 * burst + i, bytes(64 + (i % 50)), 1024)[0][0] for i in range(n)]
+            dev = torch.tensor(np.frombuffer(b"".join(hdrs), dtype=np.uint8).copy(), device="cuda")
+            addrs = [dev.data_ptr() + 64 * i for i in range(n)]
+            assert C.g_pp_do(h, addrs, burst == 1) == 0
+            torch.cuda.synchronize()
+            got = dev.cpu().numpy().tobytes()
+            for i in (0, n // 2, n - 1):
+                want = C.swap_header(hdrs[i])
+                if burst == 1:  # the sockperf word's low half is cleared: compare the routing part only
+                    assert got[i * 64:i * 64 + 42] == want[:42]
+                else:
+                    assert got[i * 64:(i + 1) * 64] == want
+            time.sleep(0.05)  # longer than the idle limit: the resident kernel leaves
+        ctr = C.g_pp_counters(h)
+        assert ctr["bursts"] == 3 and ctr["timeouts"] == 0 and ctr["launch_type"] == launch_type
+        if launch_type == 2:
+            assert ctr["rearmed"] >= 1
+    finally:
+        C.g_pp_stop(h)
+
+
+def test_resident_copy_engine_leaves_when_idle_and_is_rearmed(C, torch_cuda, mtu8k, monkeypatch):
+    """Copy type 1: the resident copy kernel leaves after P2P_RPC_SG_IDLE_MS without work; the next gather starts it
+    again and is served correctly."""
+    import time
+
+    monkeypatch.setenv("P2P_RPC_SG_IDLE_MS", "5")
+    sp, cp = C.make_loopback_pair(8192, 2048, "pinned")
+    app = C.make_app("echo", 0, 40000, 40000, [], 256, 1, 8, "gpu", 1)
+    srv = C.Server(sp, req_size=40000, resp_size=40000, server_mode=2, max_batch=8)
+    srv.add_replica(app)
+    srv.start()
+    try:
+        for rnd in range(3):
+            cli = C.Client(cp, req_size=40000, resp_size=40000, total=24, warmup=0, payload="echo", verify=True, seed=rnd + 1)
+            assert cli.run_closed_loop(4) and cli.received == 24 and cli.verify_failures == 0
+            time.sleep(0.06)  # idle for much longer than the limit
+        assert app.sg_counters["timeouts"] == 0 and srv.stats()["sg_errors"] == 0
+    finally:
+        srv.stop()
 
 
 def test_gpu_lenet_ref_and_lstm_match_cpu_oracles(C, torch_cuda, mtu8k):

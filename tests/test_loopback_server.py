@@ -195,3 +195,60 @@ def test_local_bench_cpu(C):
     app = C.make_app("vec_add", -1, 1024, 1024, [], 64, 1, 1)
     ns, outs = C.local_bench(app, 50, 2)
     assert len(ns) == 50 and all(n > 0 for n in ns)
+
+
+def test_model_files_in_the_original_formats(C, mtu8k, tmp_path):
+    """LeNet: four raw fp32 blobs under data/lenet/; LSTM: one Constant_<id>_0.bin per tensor plus a manifest."""
+    rng = np.random.default_rng(4)
+    shapes = {"data2.dat": (20, 1, 5, 5), "data0.dat": (50, 20, 5, 5), "data1.dat": (10, 1250), "data3.dat": (10,)}
+    d = tmp_path / "data" / "lenet"
+    d.mkdir(parents=True)
+    w = {}
+    for name, shape in shapes.items():
+        w[name] = (rng.standard_normal(shape) * 0.1).astype(np.float32)
+        w[name].tofile(d / name)
+    got = C.load_lenet_ref_weights(str(tmp_path))
+    for arr, name in zip(got, ("data2.dat", "data0.dat", "data1.dat", "data3.dat")):
+        assert np.array_equal(arr, w[name].ravel())
+    # the loaded weights serve the reference-format LeNet: uint8 images in, 10 probabilities out
+    sp, cp = C.make_loopback_pair(8192, 512)
+    app = C.make_app("lenet_ref", -1, 784, 40, got, 64, 1, 4, "cpu")
+    srv = C.Server(sp, req_size=784, resp_size=40, server_mode=2, max_batch=4)
+    srv.add_replica(app)
+    srv.start()
+    cli = C.Client(cp, req_size=784, resp_size=40, total=12, warmup=0, payload="echo", verify=True)
+    assert cli.run_closed_loop(4) and cli.received == 12
+    srv.stop()
+    assert abs(float(np.frombuffer(cli.response(3), dtype=np.float32).sum()) - 1.0) < 1e-4
+    with pytest.raises(RuntimeError):
+        C.load_lenet_ref_weights(str(tmp_path / "nowhere"))
+
+    # LSTM: 2 layers, hidden 8 for the test; ids shuffled, matrices stored [in][out] (flag T) as a Dot node wants them
+    L, H = 2, 8
+    cdir = tmp_path / "Constant"
+    cdir.mkdir()
+    ids = list(rng.permutation(200)[: L * 12])
+    lines, want = ["# layer kind gate id [T]"], []
+    k = 0
+    for layer in range(L):
+        Wm, Um = (rng.standard_normal((4, H, H)).astype(np.float32) for _ in range(2))
+        b = rng.standard_normal((4, H)).astype(np.float32)
+        for kind, t in (("W", Wm), ("U", Um), ("b", b)):
+            for g, gate in enumerate("igfo"):
+                cid = int(ids[k]); k += 1
+                if kind == "b":
+                    t[g].tofile(cdir / f"Constant_{cid}_0.bin")
+                    lines.append(f"{layer} {kind} {gate} {cid}")
+                else:
+                    np.ascontiguousarray(t[g].T).tofile(cdir / f"Constant_{cid}_0.bin")
+                    lines.append(f"{layer} {kind} {gate} {cid} T")
+        want += [Wm.ravel(), Um.ravel(), b.ravel()]
+    (tmp_path / "lstm.manifest").write_text("\n".join(lines) + "\n")
+    got = C.load_lstm_constants(str(cdir), str(tmp_path / "lstm.manifest"), L, H)
+    assert len(got) == 3 * L and all(np.array_equal(a, b_) for a, b_ in zip(got, want))
+    x = rng.standard_normal((3, H)).astype(np.float32)
+    y = C.cpu_lstm(got, x, L, 3, H)
+    assert y.shape == (H,) and np.all(np.isfinite(y)) and float(np.abs(y).max()) <= 1.0
+    (tmp_path / "short.manifest").write_text("\n".join(lines[:5]) + "\n")
+    with pytest.raises(RuntimeError):
+        C.load_lstm_constants(str(cdir), str(tmp_path / "short.manifest"), L, H)
