@@ -191,6 +191,7 @@ void bind_ops(py::module_& m) {
         py::arg("gathered") = 0, py::arg("src_ready") = 0, py::arg("rs") = 0, py::arg("dst") = std::vector<uintptr_t>{},
         py::arg("dst_flag") = std::vector<uintptr_t>{}, py::arg("owner_count") = 0, py::arg("status") = 0,
         py::arg("stream") = 0, py::arg("epoch_base") = 0);
+  m.def("tp_set_wait_ns", [](uint64_t ns) { check(srpc_tp_set_wait_ns(ns), "tp_set_wait_ns"); });
   m.def("tp_wait", [](uintptr_t flags, int n, uint32_t epoch, uintptr_t epoch_base, uintptr_t status, uintptr_t stream) {
     check(srpc_tp_wait((const uint32_t*)flags, n, epoch, (const uint32_t*)epoch_base, (uint32_t*)status, (cudaStream_t)stream),
           "tp_wait");

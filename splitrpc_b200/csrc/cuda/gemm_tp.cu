@@ -542,6 +542,11 @@ __global__ void tp_wait_kernel(const uint32_t* flags, int n, uint32_t epoch, con
   }
 }
 
+// Sets the bound of the flag waits of every kernel in this file on the current device.
+cudaError_t srpc_tp_set_wait_ns(uint64_t ns) {
+  return cudaMemcpyToSymbol(tpdev::g_flag_wait_ns, &ns, sizeof(ns));
+}
+
 cudaError_t srpc_tp_wait(const uint32_t* flags, int n, uint32_t epoch, const uint32_t* epoch_base, uint32_t* status,
                          cudaStream_t stream) {
   tp_wait_kernel<<<1, 32, 0, stream>>>(flags, n, epoch, epoch_base, status);

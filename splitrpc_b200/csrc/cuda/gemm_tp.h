@@ -72,3 +72,7 @@ cudaError_t srpc_tp_begin(const uint32_t* flags, int n, uint32_t* epoch_base, ui
 // *word += delta, stream ordered (advances the step-number base between forward passes).
 cudaError_t srpc_tp_bump(uint32_t* word, uint32_t delta, cudaStream_t stream);
 cudaError_t srpc_layernorm_reduce(const TpReduce& rd, int rows, uint32_t* status, cudaStream_t stream);
+
+// Bound (ns) of the flag waits of the tensor-parallel kernels on the current device (default 2 s).  A wait that runs
+// out sets GEMM_ERR_TP_SRC_WAIT in the status word and the kernel returns; nothing traps or spins on.
+cudaError_t srpc_tp_set_wait_ns(uint64_t ns);

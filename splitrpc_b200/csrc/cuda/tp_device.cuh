@@ -7,7 +7,10 @@
 
 namespace tpdev {
 
-constexpr uint64_t FLAG_WAIT_NS = 2000000000ull;
+// Upper bound of every flag wait, in nanoseconds.  A run-time value (srpc_tp_set_wait_ns) so that a test can let a wait
+// run out within milliseconds; the default is two seconds.
+__device__ uint64_t g_flag_wait_ns = 2000000000ull;
+#define FLAG_WAIT_NS (tpdev::g_flag_wait_ns)
 
 // Bounded wait until *flag >= epoch (flags only ever grow).
 __device__ __forceinline__ bool wait_flag_gpu(const uint32_t* flag, uint32_t epoch) {

@@ -13,6 +13,7 @@
 
 #include <cmath>
 #include <iomanip>
+#include <map>
 #include <thread>
 #include <unordered_map>
 

@@ -1,0 +1,171 @@
+// Stand-alone exercise of the host core (no Python, no CUDA) for sanitizer builds:
+//
+//   g++ -std=c++17 -O1 -g -fsanitize=thread            -pthread -I splitrpc_b200/csrc selftest_main.cpp -o selftest_tsan
+//   g++ -std=c++17 -O1 -g -fsanitize=address,undefined -pthread -I splitrpc_b200/csrc selftest_main.cpp -o selftest_asan
+//
+// It runs the real server threads (receive, shunter, workers), the CPU scatter-gather engine, CPU apps, the load
+// generator with host-side fault injection, and a replica behind a batched server reached over the control socket
+// (ALLOC handshake, rings and doorbells shared through memfds, responses pushed by the serving side), all in one
+// process, and exits non-zero when a reply is wrong or missing.  The original has no such harness; its host code is
+// only ever run on the full testbed.
+#include <cstdio>
+#include <string>
+
+#include "host/apps_cpu.h"
+#include "host/loadgen.h"
+#include "host/splitrpc_server.h"
+
+// The CUDA half is absent from this build.
+extern "C" const SrpcDeviceOps* srpc_cuda_ops() { return nullptr; }
+extern "C" P2pRpcSgEngine* srpc_make_gpu_sg_engine(int, int) { return nullptr; }
+
+namespace {
+
+struct Link {
+  std::unique_ptr<LoopbackPort> server, client;
+};
+
+ArenaMem shm_arena(size_t bytes) {
+  auto* sm = new SrpcSharedMem;
+  if (!srpc_shm_create(bytes, false, sm)) std::abort();
+  ArenaMem m;
+  m.host = m.dev = (uint8_t*)sm->host;
+  m.bytes = bytes;
+  m.fd = sm->fd;
+  m.release = [sm] {
+    srpc_shm_free(sm);
+    delete sm;
+  };
+  return m;
+}
+
+Link make_link(size_t slot, size_t n) {
+  Link l;
+  l.server.reset(new LoopbackPort(shm_arena(slot * n), shm_arena(slot * n), slot));
+  l.client.reset(new LoopbackPort(make_malloc_arena(slot * n), make_malloc_arena(slot * n), slot));
+  LoopbackPort::connect(l.server.get(), l.client.get());
+  return l;
+}
+
+std::unique_ptr<P2pRpcAppInfo> make_cpu_app(AppRunCB run, size_t req, size_t resp, int pool, int batch) {
+  auto* st = new CpuAppState;
+  st->req_size = req;
+  st->resp_size = resp;
+  return std::unique_ptr<P2pRpcAppInfo>(new P2pRpcAppInfo(cpu_app_noop, run, [](AppCtx* c) {
+    delete cpu_state(c);
+    c->app_ctx_internal = nullptr;
+    return 1;
+  }, cpu_app_noop, -1, req, resp, pool, st, 1, batch));
+}
+
+int fails = 0;
+void expect(bool ok, const char* what) {
+  std::printf("%s  %s\n", ok ? "ok  " : "FAIL", what);
+  if (!ok) fails++;
+}
+
+// Echo through every worker mode, with duplicated and reordered fragments on the wire.
+void scenario_modes() {
+  set_rpc_mtu(1024);
+  for (int mode = 0; mode < 3; mode++) {
+    Link l = make_link(1024, 2048);
+    LoopbackFaults f;
+    f.duplicate = 0.05;
+    f.reorder = 0.2;
+    f.seed = 7;
+    l.client->set_faults(f);
+    auto app = make_cpu_app(cpu_echo_run, 4096, 1024, 64, mode == 2 ? 4 : 1);
+    P2pRpcSgCpuEngine engine;
+    ServerConfig sc;
+    sc.req_size = 4096;
+    sc.resp_size = 1024;
+    sc.server_mode = mode;
+    sc.max_batch = mode == 2 ? 4 : 1;
+    SplitRpcServer srv(l.server.get(), sc);
+    srv.add_replica(app.get(), &engine);
+    srv.start();
+    ClientConfig cc;
+    cc.req_size = 4096;
+    cc.resp_size = 1024;
+    cc.total_requests = 300;
+    cc.num_warmup = 0;
+    cc.verify = true;
+    P2pRpcAppClient cli(l.client.get(), cc, echo_fill, echo_check);
+    cli.PreProcessRequests();
+    bool ok = cli.run_closed_loop(6);
+    srv.stop();
+    expect(ok && cli.received() == 300 && cli.verify_failures() == 0, mode == 0 ? "echo, sync worker" : (mode == 1 ? "echo, armed worker" : "echo, dynamic batching"));
+  }
+}
+
+// One local replica plus one replica behind a batched server (control socket, shared rings), least-outstanding steering.
+void scenario_remote(const std::string& sock) {
+  set_rpc_mtu(1024);
+  auto remote_app = make_cpu_app(cpu_vec_add_run, 2048, 1024, 64, 4);
+  NvlBatchedServer bs(remote_app.get(), sock, 55, 2, 4);
+  expect(bs.start(), "batched server listens");
+  Link l = make_link(1024, 2048);
+  auto local_app = make_cpu_app(cpu_vec_add_run, 2048, 1024, 64, 4);
+  P2pRpcSgCpuEngine engine;
+  ServerConfig sc;
+  sc.req_size = 2048;
+  sc.resp_size = 1024;
+  sc.server_mode = 2;
+  sc.max_batch = 4;
+  sc.steer_policy = 1;
+  {
+    SplitRpcServer srv(l.server.get(), sc);
+    srv.add_replica(local_app.get(), &engine);
+    std::string err;
+    auto remote = NvlRemoteReplica::connect(sock, 55, -1, 2, srv.tx_arena(), 3000, &err);
+    expect(remote != nullptr, "ALLOC handshake");
+    if (!remote) return;
+    srv.add_remote_replica(remote.get());
+    srv.start();
+    ClientConfig cc;
+    cc.req_size = 2048;
+    cc.resp_size = 1024;
+    cc.total_requests = 400;
+    cc.num_warmup = 0;
+    cc.verify = true;
+    P2pRpcAppClient cli(l.client.get(), cc, vec_add_fill, vec_add_check);
+    cli.PreProcessRequests();
+    bool ok = cli.run_closed_loop(12);
+    ServerStats st = srv.stats();
+    srv.stop();
+    expect(ok && cli.received() == 400 && cli.verify_failures() == 0, "vec_add over a local and a remote replica");
+    expect(st.replicas.size() == 2 && st.replicas[0].steered > 0 && st.replicas[1].steered > 0, "both replicas served");
+    expect(st.replicas[1].pushed == st.replicas[1].completed, "remote responses were pushed by the serving side");
+    expect(remote->release(), "RELEASE");
+  }
+  bs.stop();
+  expect(bs.counters.allocs == 1 && bs.counters.releases == 1 && bs.counters.peers_lost == 0, "batched server counters");
+}
+
+// A producer that vanishes without RELEASE.
+void scenario_lost_peer(const std::string& sock) {
+  auto app = make_cpu_app(cpu_echo_run, 1024, 1024, 64, 4);
+  NvlBatchedServer bs(app.get(), sock, 56, 2, 4);
+  bs.start();
+  {
+    std::string err;
+    auto remote = NvlRemoteReplica::connect(sock, 56, -1, 2, nullptr, 3000, &err);
+    expect(remote != nullptr && bs.serving(), "producer connected");
+  }  // the connection closes here
+  uint64_t t0 = getCurNs();
+  while (bs.serving() && getCurNs() - t0 < 3000000000ull) usleep(1000);
+  expect(!bs.serving() && bs.counters.peers_lost == 1, "server noticed the lost producer");
+  bs.stop();
+}
+
+}  // namespace
+
+int main(int argc, char** argv) {
+  std::string dir = argc > 1 ? argv[1] : "/tmp";
+  srpc_set_log_level(SRPC_LOG_ERROR);
+  scenario_modes();
+  scenario_remote(dir + "/srpc_selftest_a.sock");
+  scenario_lost_peer(dir + "/srpc_selftest_b.sock");
+  std::printf("%s\n", fails ? "SELFTEST FAILED" : "SELFTEST OK");
+  return fails ? 1 : 0;
+}

@@ -58,7 +58,9 @@ class SplitRpcServer {
     int tx_idx = 0;                        // next slot whose response goes out
     std::atomic<int> outstanding{0};
     std::atomic<bool> down{false};         // steering skips a replica marked down
-    ReplicaStats stats;
+    struct {
+      std::atomic<uint64_t> steered{0}, completed{0}, ring_full{0}, pushed{0};  // written by the shunter, read by stats()
+    } stats;
     std::thread worker;
   };
   // A gather that the engine finishes by itself: the receive buffers go back to the port once its ticket is done.
@@ -487,7 +489,14 @@ class SplitRpcServer {
     s.rx_pkts = stats_.rx_pkts; s.rx_reqs = stats_.rx_reqs; s.tx_resps = stats_.tx_resps; s.tx_pkts = stats_.tx_pkts;
     s.dropped_pkts = stats_.dropped_pkts; s.expired = stats_.expired; s.ring_full = stats_.ring_full;
     s.tx_alloc_fail = stats_.tx_alloc_fail; s.sg_errors = stats_.sg_errors; s.replicas_lost = stats_.replicas_lost;
-    for (auto& rp : replicas_) s.replicas.push_back(rp->stats);
+    for (auto& rp : replicas_) {
+      ReplicaStats r;
+      r.steered = rp->stats.steered.load(std::memory_order_relaxed);
+      r.completed = rp->stats.completed.load(std::memory_order_relaxed);
+      r.ring_full = rp->stats.ring_full.load(std::memory_order_relaxed);
+      r.pushed = rp->stats.pushed.load(std::memory_order_relaxed);
+      s.replicas.push_back(r);
+    }
     return s;
   }
   WorkerStats worker_stats(int replica) {
