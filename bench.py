@@ -442,6 +442,8 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> dict:
         m3 = sampler.mark()
         st = node.server.stats()
         ws = [node.server.worker_stats(i) for i in range(world)]
+        lat = sorted(node.server.device_latency_ns())
+        e2e["dev_lat"] = [lat[round(q * (len(lat) - 1))] / 1e3 if lat else None for q in (0.5, 0.99)] + [len(lat)]
         e2e["copy"] = closed_loop(node, max(nb * world * 4, n_req // 4), max(nb, n_warm // 4), outstanding, cfg["payload"], False)
         e2e["pushed"] = sum(r["pushed"] for r in st["replicas"])
         e2e["steered"] = [r["steered"] for r in st["replicas"]]
@@ -506,6 +508,9 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> dict:
                     "value_at_max_clock": round(ref["rps"] * 1965.0 / sm_e2e, 1) if sm_e2e else None,
                     "copy_mode": {"value": round(cp["rps"], 1), "p50_us": round(cp["p50_us"], 1), "p99_us": round(cp["p99_us"], 1),
                                   "requests": cp["requests"], "note": "the emulated NIC DMA writes every fragment into the receive arena (CPU memcpy by the client thread)"},
+                    "device_timed_latency": {"p50_us": e2e["dev_lat"][0], "p99_us": e2e["dev_lat"][1], "samples": e2e["dev_lat"][2],
+                                             "span": "the gather rings the slot's doorbell -> the serving GPU has stored the response "
+                                                     "(each stamped with the nanosecond timer of the GPU that did it)"},
                     "responses_pushed_by_serving_gpu": e2e["pushed"], "steered": e2e["steered"], "sg_errors": e2e["sg_errors"],
                     "mean_batch_replica0": round(e2e["mean_batch_replica0"], 2), "batches": e2e["batches"],
                     "path": "loadgen (fragments in pinned host memory, sent by reference) -> loopback NIC -> native server on rank 0 "

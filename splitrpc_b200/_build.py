@@ -63,7 +63,9 @@ def _obj_for(src: Path, hdr_digest: str, verbose_ptxas: bool) -> tuple[Path, lis
     is_cu = src.suffix == ".cu"
     # SPLITRPC_NVCC_EXTRA: extra nvcc flags for a one-off build, e.g. -DSRPC_GEMM_TRACE (phase time stamps in the GEMM)
     extra = os.environ.get("SPLITRPC_NVCC_EXTRA", "").split()
-    flags = (NVCC_FLAGS + extra + (["-Xptxas", "-v"] if verbose_ptxas else [])) if is_cu else CXX_FLAGS
+    # SPLITRPC_PROFILE=1: per-stage host timers and NVTX ranges on the server threads (-DPROFILE_MODE)
+    prof = ["-DPROFILE_MODE"] if os.environ.get("SPLITRPC_PROFILE") == "1" else []
+    flags = (NVCC_FLAGS + extra + prof + (["-Xptxas", "-v"] if verbose_ptxas else [])) if is_cu else CXX_FLAGS + prof
     key = hashlib.sha256((src.read_text() + hdr_digest + " ".join(flags)).encode()).hexdigest()[:16]
     obj = BUILD / f"{src.stem}.{key}.o"
     if is_cu:

@@ -755,6 +755,9 @@ PYBIND11_MODULE(_C, m) {
              d["replicas"] = reps;
              return d;
            })
+      // Device-timed latency samples (ns): doorbell rung by the gather -> response stored by the serving side.
+      .def("device_latency_ns", [](ServerHolder& s) { return s.server->device_latency_ns(); })
+      .def("clear_device_latency", [](ServerHolder& s) { s.server->clear_device_latency(); })
       .def("worker_stats", [](ServerHolder& s, int replica) {
         WorkerStats w = s.server->worker_stats(replica);
         py::dict d;

@@ -311,7 +311,7 @@ __global__ void __launch_bounds__(256) softmax_response(const float* __restrict_
   __shared__ RespPushTarget s_target;
   if (threadIdx.x == 0) {
     uint8_t* b = (direct_out ? direct_out : stub->resp) + (size_t)row * resp_stride;
-    s_target = (!direct_out && push) ? resp_push_target(push, (uint32_t)row, b) : RespPushTarget{b, nullptr};
+    s_target = (!direct_out && push) ? resp_push_target(push, (uint32_t)row, b) : RespPushTarget{b, nullptr, nullptr};
   }
   __syncthreads();
   const RespPushTarget target = s_target;

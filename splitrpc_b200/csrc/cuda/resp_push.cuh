@@ -15,6 +15,7 @@
 struct RespPushTarget {
   uint8_t* dst;
   volatile uint32_t* state;  // nullptr: completion is left to the host
+  volatile uint64_t* stamp;  // where the completion time goes (may be nullptr)
 };
 
 // The push block, the slots' destinations and their state words live in host memory that several processes map: a
@@ -24,12 +25,13 @@ struct RespPushTarget {
 __device__ __forceinline__ RespPushTarget resp_push_target(const RespPushCtx* ctx_, uint32_t row, uint8_t* ring_dst) {
   // volatile: a resident kernel looks at the block once per batch and must see what the host wrote since the last one
   const volatile RespPushCtx* ctx = ctx_;
-  RespPushTarget t{ring_dst, nullptr};
+  RespPushTarget t{ring_dst, nullptr, nullptr};
   if (!ctx || ctx->enabled == 0 || ctx->pool_size == 0) return t;
   const uint32_t slot = (ctx->first_slot + row) % ctx->pool_size;
   const uint64_t off = ctx->tx_off[slot];
   if (ctx->tx_base && off != ~0ull && off + ctx->resp_size <= ctx->tx_bytes) t.dst = reinterpret_cast<uint8_t*>(ctx->tx_base + off);
   t.state = ctx->states + slot;
+  t.stamp = ctx->stamps ? ctx->stamps + 2 * slot + 1 : nullptr;
   return t;
 }
 
@@ -42,6 +44,14 @@ __device__ __forceinline__ RespPushTarget resp_push_target_block(const RespPushC
   return s_target;
 }
 
+// Call from one thread, after a __syncthreads() that follows every store of the response by the block.
+__device__ __forceinline__ void resp_push_complete(const RespPushTarget& t) {
+  if (!t.state) return;
+  if (t.stamp) *t.stamp = ptx::globaltimer_ns();
+  __threadfence_system();
+  ptx::st_release_sys(t.state, (uint32_t)APP_RR_STATUS::WORK_COMPLETE);
+}
+
 // Stores the `batch` responses that one block has just produced at resp (resp_size apart) and completes their slots,
 // one after the other.  For kernels that serve a whole batch with one block (resident apps).  Call from all threads.
 __device__ __forceinline__ void resp_push_rows_block(const RespPushCtx* ctx, uint8_t* resp, uint32_t resp_size, int batch) {
@@ -52,17 +62,7 @@ __device__ __forceinline__ void resp_push_rows_block(const RespPushCtx* ctx, uin
     if (t.dst != src)
       for (uint32_t i = threadIdx.x; i < resp_size; i += blockDim.x) t.dst[i] = src[i];
     __syncthreads();
-    if (threadIdx.x == 0 && t.state) {
-      __threadfence_system();
-      ptx::st_release_sys(t.state, (uint32_t)APP_RR_STATUS::WORK_COMPLETE);
-    }
+    if (threadIdx.x == 0) resp_push_complete(t);
     __syncthreads();
   }
-}
-
-// Call from one thread, after a __syncthreads() that follows every store of the response by the block.
-__device__ __forceinline__ void resp_push_complete(const RespPushTarget& t) {
-  if (!t.state) return;
-  __threadfence_system();
-  ptx::st_release_sys(t.state, (uint32_t)APP_RR_STATUS::WORK_COMPLETE);
 }

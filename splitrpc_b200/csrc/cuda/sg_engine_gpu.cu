@@ -331,6 +331,10 @@ class P2pRpcSgGpuEngine : public P2pRpcSgEngine {
       nt.bell_value = state_value;
       nt.done_word = d_done_;
       nt.done_value = ticket;
+      if (d_states_base_ && d_stamps_base_) {
+        nt.states_base = (uint64_t)(uintptr_t)d_states_base_;
+        nt.stamps_base = (uint64_t)(uintptr_t)d_stamps_base_;
+      }
       rc = submit(ni, true, &nt);
       first = i;
     }

@@ -106,8 +106,14 @@ __device__ __forceinline__ void sg_notify_epilogue(const SgNotify& nt) {
   if (!s_last) return;
   if (threadIdx.x == 0) atomicExch(nt.counter, 0u);
   __threadfence_system();
-  for (uint32_t i = threadIdx.x; i < nt.n_bells; i += blockDim.x)
+  const uint64_t now = nt.stamps_base ? ptx::globaltimer_ns() : 0ull;
+  for (uint32_t i = threadIdx.x; i < nt.n_bells; i += blockDim.x) {
+    if (nt.stamps_base) {
+      const uint64_t slot = (nt.bells[i] - nt.states_base) >> 2;
+      *reinterpret_cast<volatile uint64_t*>(nt.stamps_base + 16 * slot) = now;
+    }
     ptx::st_release_sys(reinterpret_cast<volatile uint32_t*>(nt.bells[i]), nt.bell_value);
+  }
   __syncthreads();
   if (threadIdx.x == 0 && nt.done_word) {
     __threadfence_system();

@@ -51,6 +51,10 @@ struct SgNotify {
   uint32_t bell_value = 0;
   uint32_t* done_word = nullptr;
   uint32_t done_value = 0;
+  // When set: the bells are the state words of one slot ring that starts at states_base, and the time at which they
+  // are rung (this GPU's nanosecond timer) goes into stamps_base[2 * slot] for each of them.
+  uint64_t states_base = 0;
+  uint64_t stamps_base = 0;
 };
 
 // One launch over a copy list that the device can read (device or mapped memory).

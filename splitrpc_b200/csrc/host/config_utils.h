@@ -229,6 +229,24 @@ static inline void print_stat(const std::string& key, const std::vector<uint64_t
 #define PROF_PRINT(label, name) ((void)0)
 #endif
 
+// NVTX ranges on the host threads (receive, shunter, worker), compiled in with -DPROFILE_MODE like the timers above
+// (reference src/utils/time_utils.h:16-38).  NVTX 3 is header-only; without a profiler attached the calls are no-ops.
+#if defined(PROFILE_MODE) && defined(__has_include)
+#if __has_include(<nvtx3/nvToolsExt.h>)
+#include <nvtx3/nvToolsExt.h>
+#define SRPC_HAVE_NVTX 1
+#endif
+#endif
+#ifdef SRPC_HAVE_NVTX
+#define NVTX_R(name) nvtxRangePushA(name)
+#define NVTX_P() nvtxRangePop()
+#define NVTX_M(name) nvtxMarkA(name)
+#else
+#define NVTX_R(name) ((void)0)
+#define NVTX_P() ((void)0)
+#define NVTX_M(name) ((void)0)
+#endif
+
 // Seeded xorshift generator used by payload generators and arrival processes so
 // that every run with the same P2P_RPC_RANDOM_SEED produces the same bytes.
 struct SrpcRng {

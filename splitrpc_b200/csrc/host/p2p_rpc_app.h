@@ -63,6 +63,7 @@ struct RespPushCtx {
   uint64_t tx_bytes;
   const volatile uint64_t* tx_off;  // per slot, device view
   volatile uint32_t* states;        // per slot, device view
+  volatile uint64_t* stamps;        // per slot {doorbell rung, response stored} device timer values (ns), device view
   uint32_t pool_size;
   uint32_t resp_size;
   uint32_t enabled;
@@ -304,22 +305,28 @@ class P2pRpcAppRrMemPool {
   volatile uint32_t* d_doorbells_ = nullptr;
   volatile uint64_t* h_tx_off_ = nullptr;
   volatile uint64_t* d_tx_off_ = nullptr;
+  volatile uint64_t* h_stamps_ = nullptr;  // per slot: [0] when the gather rang the doorbell, [1] when the response was stored
+  volatile uint64_t* d_stamps_ = nullptr;
   size_t n_doorbells_ = 0;
   bool mirror_ = false;
   bool ctl_plain_ = false;  // control block from host_alloc_mapped / posix_memalign instead of a memfd
 
-  static size_t ctl_layout(size_t n, size_t* tx_off_at) {
+  static size_t ctl_layout(size_t n, size_t* tx_off_at, size_t* stamps_at = nullptr) {
     size_t a = (n * sizeof(uint32_t) + 63) / 64 * 64;
     *tx_off_at = a;
-    return a + n * sizeof(uint64_t);
+    size_t b = a + n * sizeof(uint64_t);
+    if (stamps_at) *stamps_at = b;
+    return b + 2 * n * sizeof(uint64_t);
   }
   void bind_ctl(void* h, void* d) {
-    size_t at = 0;
-    ctl_layout(n_doorbells_, &at);
+    size_t at = 0, st = 0;
+    ctl_layout(n_doorbells_, &at, &st);
     h_doorbells_ = (volatile uint32_t*)h;
     d_doorbells_ = (volatile uint32_t*)d;
     h_tx_off_ = (volatile uint64_t*)((uint8_t*)h + at);
     d_tx_off_ = (volatile uint64_t*)((uint8_t*)d + at);
+    h_stamps_ = (volatile uint64_t*)((uint8_t*)h + st);
+    d_stamps_ = (volatile uint64_t*)((uint8_t*)d + st);
   }
 
  public:
@@ -357,6 +364,7 @@ class P2pRpcAppRrMemPool {
     for (size_t i = 0; i < n_doorbells_; i++) {
       h_doorbells_[i] = APP_RR_STATUS::FREE;
       h_tx_off_[i] = kNoTxOffset;
+      h_stamps_[2 * i] = h_stamps_[2 * i + 1] = 0;
     }
   }
 
@@ -437,6 +445,8 @@ class P2pRpcAppRrMemPool {
   volatile uint32_t* get_doorbells_device() const { return d_doorbells_; }
   volatile uint64_t* get_tx_offsets_host() const { return h_tx_off_; }
   volatile uint64_t* get_tx_offsets_device() const { return d_tx_off_; }
+  volatile uint64_t* get_stamps_host() const { return h_stamps_; }
+  volatile uint64_t* get_stamps_device() const { return d_stamps_; }
 };
 
 // ------------------------------------------------------------------ app slots
@@ -447,6 +457,7 @@ class P2pRpcAppRr {
   volatile uint32_t* h_state = nullptr;
   volatile uint32_t* d_state = nullptr;
   volatile uint64_t* h_tx_off = nullptr;  // where the serving side stores this slot's response (offset in the transmit arena)
+  volatile uint64_t* h_stamps = nullptr;  // [0] doorbell rung, [1] response stored: timer values of whoever did it (ns)
   size_t req_size = 0, resp_size = 0;
   void* rpc_rr = nullptr;  // transport-side record this slot currently serves
   int rr_idx = 0;
@@ -518,6 +529,7 @@ class P2pRpcAppRrPool {
       r.h_state = &hs[i];
       r.d_state = &ds[i];
       r.h_tx_off = &rr_mem_pool->get_tx_offsets_host()[i];
+      r.h_stamps = &rr_mem_pool->get_stamps_host()[2 * i];
       r.h_stub->req = nullptr;
       r.h_stub->resp = nullptr;
       r.rr_idx = i;

@@ -131,6 +131,7 @@ class P2pRpcAppInfo {
     p->tx_bytes = tx_base ? tx_bytes : 0;
     p->tx_off = mp->get_tx_offsets_device();
     p->states = mp->get_doorbells_device();
+    p->stamps = mp->get_stamps_device();
     p->pool_size = (uint32_t)rr_pool_size;
     p->resp_size = (uint32_t)resp_size;
     p->first_slot = 0;
@@ -163,6 +164,7 @@ class P2pRpcAppInfo {
       uint64_t off = p->tx_off[slot];
       if (p->tx_base && off != P2pRpcAppRrMemPool::kNoTxOffset && off + p->resp_size <= p->tx_bytes)
         std::memcpy((void*)(uintptr_t)(p->tx_base + off), app_ctx->h_stub->resp + (size_t)r * p->resp_size, p->resp_size);
+      p->stamps[2 * slot + 1] = getCurNs();
       __atomic_store_n(&p->states[slot], (uint32_t)APP_RR_STATUS::WORK_COMPLETE, __ATOMIC_RELEASE);
     }
   }
@@ -237,8 +239,10 @@ class P2pRpcAsyncAppServer {
                                              : *a->app_rr_pool->get_app_rr(rr_idx)->h_stub;
     a->app_ctx->h_push->first_slot = (uint32_t)rr_idx;
     std::atomic_thread_fence(std::memory_order_release);
+    NVTX_R("AppRun");
     a->app_run(a->app_ctx);
     a->push_responses();
+    NVTX_P();
   }
   bool do_sync(int appIdx) {
     P2pRpcAppInfo* a = all_apps[appIdx];

@@ -115,6 +115,8 @@ class P2pRpcSgEngine {
   uint16_t app_queue_length = 0;
   SgCounters counters;
   int64_t sync_ticket_ = 0;
+  volatile uint32_t *h_states_base_ = nullptr, *d_states_base_ = nullptr;
+  volatile uint64_t *h_stamps_base_ = nullptr, *d_stamps_base_ = nullptr;
   PROF_DECL(Gather);
   PROF_DECL(Scatter);
 
@@ -156,8 +158,21 @@ class P2pRpcSgEngine {
     (void)d_states;
     int rc = gather_batch(rrs, stubs, n);
     if (rc != 0) return rc < 0 ? rc : -1;
-    for (int i = 0; i < n; i++) __atomic_store_n(h_states[i], state_value, __ATOMIC_RELEASE);
+    const uint64_t now = getCurNs();
+    for (int i = 0; i < n; i++) {
+      if (h_states_base_ && h_stamps_base_) h_stamps_base_[2 * (h_states[i] - h_states_base_)] = now;
+      __atomic_store_n(h_states[i], state_value, __ATOMIC_RELEASE);
+    }
     return ++sync_ticket_;
+  }
+  // Tells the engine where the slot ring it fills keeps its state words and its time stamps (host view and the view of
+  // the engine's device), so that a gather can record when it rang each doorbell.  Optional.
+  virtual void set_stamp_layout(volatile uint32_t* h_states_base, volatile uint64_t* h_stamps_base, volatile uint32_t* d_states_base,
+                                volatile uint64_t* d_stamps_base) {
+    h_states_base_ = h_states_base;
+    h_stamps_base_ = h_stamps_base;
+    d_states_base_ = d_states_base;
+    d_stamps_base_ = d_stamps_base;
   }
   virtual bool ticket_done(int64_t ticket) {
     (void)ticket;

@@ -88,6 +88,8 @@ class SplitRpcServer {
   TxArenaInfo tx_info_{};
   bool have_tx_info_ = false;
   std::deque<Inflight> inflight_;
+  std::mutex lat_mu_;
+  std::vector<uint64_t> device_latency_ns_;  // per pushed response: doorbell rung -> response stored (device timers)
 
   void rx_loop() {
     std::vector<SrpcPkt> pkts(1024);
@@ -97,6 +99,7 @@ class SplitRpcServer {
       int n = port_->rx_burst(pkts.data(), (int)pkts.size());
       if (n > 0) backoff.busy();
       else backoff.empty();
+      if (n > 0) NVTX_R("rx_burst");
       for (int i = 0; i < n; i++) {
         SrpcPkt& p = pkts[i];
         stats_.rx_pkts++;
@@ -117,6 +120,7 @@ class SplitRpcServer {
           stats_.dropped_pkts++;
         }
       }
+      if (n > 0) NVTX_P();
       uint64_t now = getCurNs();
       if (now - last_sweep > cfg_.reassembly_timeout_ns / 4 + 1) {
         last_sweep = now;
@@ -290,6 +294,7 @@ class SplitRpcServer {
       }
       if (nb > 0) {
         did_work = true;
+        NVTX_R("gather");
         Replica& rep = *replicas_[target];
         Inflight fl{rep.engine, 0, {}};
         if (!cfg_.zerocopy) {
@@ -322,6 +327,7 @@ class SplitRpcServer {
         }
         rep.outstanding.fetch_add(nb);
         rep.stats.steered += (uint64_t)nb;
+        NVTX_P();
       }
       if (!inflight_.empty()) reap_inflight(false);
       // ---- TX half: finished slots -> responses
@@ -340,6 +346,7 @@ class SplitRpcServer {
         }
         if (nt == 0) continue;
         did_work = true;
+        NVTX_R("tx");
         if (cfg_.zerocopy) {
           send_zerocopy(rep, rrs.data(), slots.data(), nt);
         } else {
@@ -352,6 +359,12 @@ class SplitRpcServer {
                           __atomic_load_n(slots[i]->h_tx_off, __ATOMIC_ACQUIRE) != P2pRpcAppRrMemPool::kNoTxOffset;
             if (pushed) {
               rep.stats.pushed++;
+              // doorbell rung -> response stored, on the timers of the devices that did it
+              const uint64_t t_rx = slots[i]->h_stamps[0], t_done = slots[i]->h_stamps[1];
+              if (t_rx && t_done > t_rx && t_done - t_rx < 60000000000ull) {
+                std::lock_guard<std::mutex> g(lat_mu_);
+                if (device_latency_ns_.size() < ((size_t)1 << 21)) device_latency_ns_.push_back(t_done - t_rx);
+              }
             } else {
               s_rrs.push_back(rrs[i]);
               s_stubs.push_back(stubs[i]);
@@ -366,12 +379,14 @@ class SplitRpcServer {
         }
         for (int i = 0; i < nt; i++) {
           slots[i]->rpc_rr = nullptr;
+          slots[i]->h_stamps[0] = slots[i]->h_stamps[1] = 0;
           __atomic_store_n(slots[i]->h_tx_off, P2pRpcAppRrMemPool::kNoTxOffset, __ATOMIC_RELAXED);
           __atomic_store_n(slots[i]->h_state, (uint32_t)APP_RR_STATUS::FREE, __ATOMIC_RELEASE);
         }
         rep.tx_idx = (rep.tx_idx + nt) % pool_n;
         rep.outstanding.fetch_sub(nt);
         rep.stats.completed += (uint64_t)nt;
+        NVTX_P();
       }
       if (!did_work) {
         uint64_t now = getCurNs();
@@ -434,6 +449,10 @@ class SplitRpcServer {
         r->device_completes = true;
       }
     }
+    {
+      P2pRpcAppRrMemPool* mp = app->app_rr_pool->rr_mem_pool;
+      engine->set_stamp_layout(mp->get_doorbells_host(), mp->get_stamps_host(), mp->get_doorbells_device(), mp->get_stamps_device());
+    }
     replicas_.push_back(std::move(r));
     return (int)replicas_.size() - 1;
   }
@@ -444,6 +463,10 @@ class SplitRpcServer {
     r->pool = remote->pool();
     r->engine = remote->engine();
     r->device_completes = remote->device_completes();
+    {
+      P2pRpcAppRrMemPool* mp = r->pool->rr_mem_pool;
+      r->engine->set_stamp_layout(mp->get_doorbells_host(), mp->get_stamps_host(), mp->get_doorbells_device(), mp->get_stamps_device());
+    }
     replicas_.push_back(std::move(r));
     return (int)replicas_.size() - 1;
   }
@@ -498,6 +521,16 @@ class SplitRpcServer {
       s.replicas.push_back(r);
     }
     return s;
+  }
+  // Device-timed service latency of the responses that the serving side pushed: from the moment the gather rang the
+  // slot's doorbell to the moment the response was stored, both stamped by the GPUs (or CPU threads) that did it.
+  std::vector<uint64_t> device_latency_ns() {
+    std::lock_guard<std::mutex> g(lat_mu_);
+    return device_latency_ns_;
+  }
+  void clear_device_latency() {
+    std::lock_guard<std::mutex> g(lat_mu_);
+    device_latency_ns_.clear();
   }
   WorkerStats worker_stats(int replica) {
     Replica& r = *replicas_[replica];

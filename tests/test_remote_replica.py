@@ -68,7 +68,9 @@ def test_remote_replica_serves_echo_in_every_worker_mode(C, mtu1k, tmp_path, mod
         assert cli.run_closed_loop(6)
         st = srv.stats()
         ws = srv.worker_stats(0)  # asked from the remote server over the control channel
+        lat = srv.device_latency_ns()  # doorbell rung (ingress side) -> response stored (serving side), per request
         srv.stop()
+        assert len(lat) == 120 and min(lat) > 0 and max(lat) < 5_000_000_000
         assert cli.received == 120 and cli.verify_failures == 0
         # every response was stored into the ingress transmit arena by the serving process, none was fetched
         assert st["replicas"][0]["pushed"] == 120 and st["sg_errors"] == 0
