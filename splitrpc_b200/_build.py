@@ -76,8 +76,25 @@ def _obj_for(src: Path, hdr_digest: str, verbose_ptxas: bool) -> tuple[Path, lis
 
 
 def build(force: bool = False, verbose: bool = False, verbose_ptxas: bool = False) -> Path:
-    """Compiles what changed and links ``_C``; returns the path of the library."""
+    """Compiles what changed and links ``_C``; returns the path of the library.
+
+    Safe to call from several processes at once (one rank per GPU importing the package at the same time): a file lock
+    serialises them, the winner builds, the others find the result up to date; the library is linked under a temporary
+    name and moved into place atomically, so no process ever maps a half-written file."""
+    import fcntl
+
     BUILD.mkdir(exist_ok=True)
+    with open(BUILD / ".lock", "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        try:
+            if not force and not verbose_ptxas and up_to_date():
+                return TARGET
+            return _build_locked(force, verbose, verbose_ptxas)
+        finally:
+            fcntl.flock(lock, fcntl.LOCK_UN)
+
+
+def _build_locked(force: bool, verbose: bool, verbose_ptxas: bool) -> Path:
     hdr = _headers_digest()
     jobs = [_obj_for(s, hdr, verbose_ptxas) for s in sources()]
     todo = [(o, c) for o, c in jobs if force or not o.exists()]
@@ -98,14 +115,17 @@ def build(force: bool = False, verbose: bool = False, verbose_ptxas: bool = Fals
             list(ex.map(run, todo))
     objs = [o for o, _ in jobs]
     stamp = BUILD / "link.stamp"
-    link_key = hashlib.sha256(" ".join(str(o) for o in objs).encode()).hexdigest()
+    link_key = hashlib.sha256(" ".join(o.name for o in objs).encode()).hexdigest()  # names, not paths: the tree may move
     if force or todo or not TARGET.exists() or not stamp.exists() or stamp.read_text() != link_key:
-        cmd = [_nvcc(), "-shared", "-o", str(TARGET)] + [str(o) for o in objs] + GENCODE + ["-cudart", "static", "-lpthread", "-ldl", "-lrt"]
+        tmp = TARGET.with_name(TARGET.name + f".tmp{os.getpid()}")
+        cmd = [_nvcc(), "-shared", "-o", str(tmp)] + [str(o) for o in objs] + GENCODE + ["-cudart", "static", "-lpthread", "-ldl", "-lrt"]
         if verbose:
             print(" ".join(cmd), flush=True)
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
+            tmp.unlink(missing_ok=True)
             raise RuntimeError(f"link failed: {' '.join(cmd)}\n{r.stdout}\n{r.stderr}")
+        os.replace(tmp, TARGET)
         stamp.write_text(link_key)
         # drop objects of older source versions
         keep = {o.name for o in objs}
@@ -116,10 +136,15 @@ def build(force: bool = False, verbose: bool = False, verbose_ptxas: bool = Fals
 
 
 def up_to_date() -> bool:
+    """True when the library exists and was linked from the objects of the current sources, headers and flags."""
     if not TARGET.exists():
         return False
     hdr = _headers_digest()
-    return all(_obj_for(s, hdr, False)[0].exists() for s in sources())
+    objs = [_obj_for(s, hdr, False)[0] for s in sources()]
+    if not all(o.exists() for o in objs):
+        return False
+    stamp = BUILD / "link.stamp"
+    return stamp.exists() and stamp.read_text() == hashlib.sha256(" ".join(o.name for o in objs).encode()).hexdigest()
 
 
 if __name__ == "__main__":
