@@ -713,6 +713,8 @@ PYBIND11_MODULE(_C, m) {
              d["max_batch"] = i.max_batch;
              d["device_completes"] = i.device_completes;
              d["transform_kind"] = i.transform.kind;
+             d["timer_offset_ns"] = i.timer_offset_ns;
+             d["stamp_skew_ns"] = s.remotes.at((size_t)remote_idx)->stamp_skew_ns();
              return d;
            })
       // Sends RELEASE to every remote replica (their servers stop their workers and listen again).

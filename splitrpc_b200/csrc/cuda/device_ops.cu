@@ -313,6 +313,63 @@ static int d_resp_push(const void* d_stub, const void* d_push, int n, cudaStream
   RT(sg_launch_resp_push(d_stub, d_push, n, s));
   return 0;
 }
+// One thread writes the device timer into a mapped host word; the host notes its own clock the moment the word
+// arrives (the write takes about a microsecond to cross PCIe).  The smallest of a few tries is the least delayed.
+__global__ void timer_probe_kernel(volatile unsigned long long* out) {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  *out = t;
+  __threadfence_system();
+}
+static int d_timer_offset_ns(int dev, int64_t* offset) {
+  int prev = 0;
+  RT(cudaGetDevice(&prev));
+  RT(cudaSetDevice(dev));
+  volatile unsigned long long* w = nullptr;
+  cudaError_t e = cudaHostAlloc((void**)&w, 64, cudaHostAllocMapped);
+  if (e != cudaSuccess) {
+    cudaSetDevice(prev);
+    RT(e);
+  }
+  unsigned long long* dw = nullptr;
+  cudaStream_t s = nullptr;
+  int rc = 0;
+  if (cudaHostGetDevicePointer((void**)&dw, (void*)w, 0) != cudaSuccess || cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking) != cudaSuccess) rc = -1;
+  int64_t best = 0;
+  uint64_t best_wait = ~0ull;
+  for (int i = 0; rc == 0 && i < 6; i++) {
+    *w = 0;
+    const uint64_t t0 = getCurNs();
+    timer_probe_kernel<<<1, 1, 0, s>>>(dw);
+    if (cudaGetLastError() != cudaSuccess) {
+      rc = -1;
+      break;
+    }
+    uint64_t t1 = t0;
+    while (*w == 0 && (t1 = getCurNs()) - t0 < 2000000000ull) {
+    }
+    if (*w == 0) {
+      rc = -1;
+      break;
+    }
+    t1 = getCurNs();
+    cudaStreamSynchronize(s);
+    // the first tries include the kernel's load; a short host wait means the stamp is fresh
+    if (i >= 1 && t1 - t0 < best_wait) {
+      best_wait = t1 - t0;
+      best = (int64_t)*w - (int64_t)t1;
+    }
+  }
+  if (s) cudaStreamDestroy(s);
+  cudaFreeHost((void*)w);
+  cudaSetDevice(prev);
+  if (rc != 0) {
+    g_last_error = "timer_offset_ns: probe failed";
+    return rc;
+  }
+  *offset = best;
+  return 0;
+}
 static const char* d_last_error() { return g_last_error.c_str(); }
 
 extern "C" const SrpcDeviceOps* srpc_cuda_ops() {
@@ -320,7 +377,8 @@ extern "C" const SrpcDeviceOps* srpc_cuda_ops() {
       d_device_count, d_set_device,  d_stream_create, d_stream_destroy,    d_stream_sync, d_stream_query, d_wait32,
       d_write32,      d_event_create, d_event_destroy, d_ring_alloc,        d_ring_free,   d_host_alloc_mapped,
       d_host_free,    d_dev_alloc,    d_dev_free,      d_memcpy_async,      d_memset_async, d_graph_launch, d_last_error,
-      d_ring_export,  d_ring_import,  d_host_register, d_host_unregister,   d_resp_push};
+      d_ring_export,  d_ring_import,  d_host_register, d_host_unregister,   d_resp_push,
+      d_timer_offset_ns};
   return &ops;
 }
 

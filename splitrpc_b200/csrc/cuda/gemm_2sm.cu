@@ -19,11 +19,22 @@
 //              stores; each warp releases the accumulator by arriving on the LEADER's "accumulator empty" barrier.
 // Every mbarrier wait is bounded; on a timeout the CTA records an error code and winds down; both CTAs always reach
 // the two cluster barriers (after set-up and before tensor memory is freed).  All operands live in this GPU's memory.
+//
+// Tensor-parallel variant (template flag TP, entry point srpc_gemm_tp_2sm): the same pair tiles with
+//   all-gather   copier clusters appended to the grid pull the peers' row shards of A over NVLink into this GPU's
+//                gathered buffer (bulk copies through shared memory, no multicast) and publish each 128-row block; the
+//                producer of a CTA waits (bounded) for the block its tile needs.  Tiles are ordered so that the rows
+//                this rank already holds come first.
+//   reduce-scatter  the epilogue stores the staged bf16 tile with 16-byte stores into the slot this rank owns in the
+//                memory of the rank that owns the rows (its own slot for its own rows), fences, counts the tile and,
+//                when the last tile for an owner is through, publishes the step number there.  Rows owned by peers
+//                come first, so that their transfer overlaps the rest of the GEMM.
 #include <algorithm>
 #include <cstdlib>
 
 #include "gemm_tcgen05.h"
 #include "ptx.cuh"
+#include "tp_device.cuh"
 
 cudaError_t srpc_tensor_map_2d(CUtensorMap* m, const void* ptr, uint64_t inner, uint64_t outer, uint64_t row_stride_bytes,
                                uint32_t box_inner, uint32_t box_outer);
@@ -83,31 +94,48 @@ struct PairTile {
   int m2, n;  // 256-row block, 256-column block
 };
 
+struct TileOrder {
+  int clusters;  // clusters that compute tiles (the grid may hold copier clusters after them)
+  int tiles_m2, tiles_n;
+  int group_m;   // 256-row blocks per group
+  int m_rot2;    // rotation of the 256-row blocks (tensor-parallel: which rank's rows come first)
+};
+
 // j-th tile of this cluster, grouped so that tiles in flight share A and B blocks in L2.
-__device__ __forceinline__ bool pair_tile(int j, int tiles_m2, int tiles_n, PairTile* out) {
-  const int tile = (int)(blockIdx.x >> 1) + j * (int)(gridDim.x >> 1);
-  if (tile >= tiles_m2 * tiles_n) return false;
-  constexpr int GROUP_M = 4;
-  const int per_group = GROUP_M * tiles_n;
+__device__ __forceinline__ bool pair_tile(int j, const TileOrder& o, PairTile* out) {
+  const int tile = (int)(blockIdx.x >> 1) + j * o.clusters;
+  if (tile >= o.tiles_m2 * o.tiles_n) return false;
+  const int per_group = o.group_m * o.tiles_n;
   const int g = tile / per_group, in_g = tile - g * per_group;
-  const int m_first = g * GROUP_M;
-  const int gm = (tiles_m2 - m_first) < GROUP_M ? (tiles_m2 - m_first) : GROUP_M;
-  out->m2 = m_first + in_g % gm;
+  const int m_first = g * o.group_m;
+  const int gm = (o.tiles_m2 - m_first) < o.group_m ? (o.tiles_m2 - m_first) : o.group_m;
+  int m2 = m_first + in_g % gm + o.m_rot2;
+  if (m2 >= o.tiles_m2) m2 -= o.tiles_m2;
+  out->m2 = m2;
   out->n = in_g / gm;
   return true;
 }
 
-template <int BN>
+template <int BN, bool TP>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(Cfg<BN>::THREADS, 1)
 gemm_2sm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                const __grid_constant__ CUtensorMap tmap_out, int M, int N, int K, int tiles_m2, int tiles_n, GemmEpilogue ep,
-                uint32_t* status) {
+                const __grid_constant__ CUtensorMap tmap_out, int M, int N, int K, const TileOrder order, GemmEpilogue ep,
+                uint32_t* status, const TpParams tp_in) {
   constexpr int B_BYTES = Cfg<BN>::B_BYTES, STAGE_BYTES = Cfg<BN>::STAGE_BYTES, STAGES = Cfg<BN>::STAGES;
   constexpr int EPI_THREADS = Cfg<BN>::EPI_THREADS, ACC_STRIDE = Cfg<BN>::ACC_STRIDE, TMEM_COLS = Cfg<BN>::TMEM_COLS;
   constexpr int PASSES = Cfg<BN>::PASSES, PASS_COLS = Cfg<BN>::PASS_COLS;
   constexpr int CH = PASS_COLS / 32 / (EPI_THREADS / 128);  // 32-column chunks per warp and pass
   (void)B_BYTES;
   extern __shared__ __align__(1024) uint8_t smem[];
+  TpParams tp = tp_in;
+  if constexpr (TP) {
+    if (tp.epoch_base) tp.epoch += *tp.epoch_base;
+    if ((int)(blockIdx.x >> 1) >= order.clusters) {
+      // Copier CTA: neither of the pair takes part in the cluster barriers below, nor holds tensor memory.
+      tpdev::copier(tp, (int)blockIdx.x - 2 * order.clusters, smem, status);
+      return;
+    }
+  }
   uint8_t* stage_out = smem + (size_t)STAGES * STAGE_BYTES;
   __shared__ __align__(8) uint64_t full_bar[STAGES];   // used in the leader only
   __shared__ __align__(8) uint64_t empty_bar[STAGES];
@@ -159,9 +187,22 @@ gemm_2sm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     int s = 0;
     uint32_t ph = 0;
     PairTile t;
-    for (int j = 0; layout_ok && pair_tile(j, tiles_m2, tiles_n, &t) && *(volatile uint32_t*)&s_error == 0; j++) {
+    for (int j = 0; layout_ok && pair_tile(j, order, &t) && *(volatile uint32_t*)&s_error == 0; j++) {
       const int row0 = (t.m2 * 2 + (int)rank) * BM;
       const int brow0 = t.n * BN + (int)rank * (BN / 2);
+      if constexpr (TP) {
+        if (tp.mblock_ready) {
+          // Rows of a peer arrive through the copier clusters of this launch, one 128-row block at a time.
+          const int m_idx = t.m2 * 2 + (int)rank;
+          if (m_idx / tp.mblocks_per_rank != tp.rank) {
+            if (!tpdev::wait_flag_gpu(tp.mblock_ready + m_idx, tp.epoch)) {
+              atomicExch(&s_error, GEMM_ERR_TP_BLOCK_WAIT);
+              break;
+            }
+            ptx::fence_proxy_async_all();  // the copier's writes -> this thread's TMA reads
+          }
+        }
+      }
       for (int kb = 0; kb < num_kb; kb++) {
         if (!ptx::mbar_wait(&empty_bar[s], ph ^ 1u)) {
           atomicExch(&s_error, GEMM_ERR_PRODUCER_WAIT);
@@ -186,7 +227,7 @@ gemm_2sm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       int s = 0;
       uint32_t ph = 0, local = 0;
       PairTile t;
-      for (int j = 0; layout_ok && pair_tile(j, tiles_m2, tiles_n, &t) && *(volatile uint32_t*)&s_error == 0; j++, local++) {
+      for (int j = 0; layout_ok && pair_tile(j, order, &t) && *(volatile uint32_t*)&s_error == 0; j++, local++) {
         const uint32_t acc = local & 1u;
         if (!ptx::mbar_wait(&tmem_empty_bar[acc], ((local >> 1) & 1u) ^ 1u)) {
           atomicExch(&s_error, GEMM_ERR_MMA_WAIT);
@@ -231,7 +272,9 @@ gemm_2sm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     const bool vec_res = ep.residual && ((ep.ldr & 7) == 0) && (((uintptr_t)ep.residual & 15) == 0);
     uint32_t local = 0;
     PairTile t;
-    for (int j = 0; layout_ok && pair_tile(j, tiles_m2, tiles_n, &t); j++, local++) {
+    bool peer_store = false;
+    if constexpr (TP) peer_store = tp.rs != 0;
+    for (int j = 0; layout_ok && pair_tile(j, order, &t); j++, local++) {
       const uint32_t acc = local & 1u;
       const int row0 = (t.m2 * 2 + (int)rank) * BM;
       const int m = row0 + row;
@@ -249,7 +292,7 @@ gemm_2sm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
 #pragma unroll
       for (int pass = 0; pass < PASSES; pass++) {
         // The previous store must have finished reading the staging buffer.
-        if (et == 0) ptx::bulk_wait_read<0>();
+        if (et == 0 && !peer_store) ptx::bulk_wait_read<0>();
         named_bar_sync(1, EPI_THREADS);
 #pragma unroll
         for (int ch = 0; ch < CH; ch++) {
@@ -318,6 +361,40 @@ gemm_2sm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
             *reinterpret_cast<uint4*>(half + (((chunk0 + q) ^ (row & 7)) << 4)) = o;
           }
         }
+        if constexpr (TP) {
+          if (peer_store) {
+            // The tile goes to the slot this rank owns on the rank that owns these rows (rows per rank are a multiple
+            // of 128, so a CTA's half tile has one owner).
+            named_bar_sync(1, EPI_THREADS);
+            const int m_idx = t.m2 * 2 + (int)rank;
+            const int owner = m_idx / tp.mblocks_per_rank;
+            const int local_m0 = (m_idx - owner * tp.mblocks_per_rank) * BM;
+            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(tp.dst[owner]);
+            constexpr int SEGS = PASS_COLS / 8;  // 16-byte segments per row of this pass
+#pragma unroll 4
+            for (int q = et; q < BM * SEGS; q += EPI_THREADS) {
+              const int rr = q / SEGS, seg = q - rr * SEGS;
+              const int col = n0 + pass * PASS_COLS + seg * 8;
+              if (col < N) {
+                const uint8_t* src = stage_out + (size_t)(seg >> 3) * OUT_HALF_BYTES + (size_t)rr * 128 + (((seg & 7) ^ (rr & 7)) << 4);
+                *reinterpret_cast<uint4*>(dst + (size_t)(local_m0 + rr) * ep.ldo + col) = *reinterpret_cast<const uint4*>(src);
+              }
+            }
+            if (pass == PASSES - 1) {
+              __threadfence_system();  // this thread's stores of every pass have reached the owner
+              named_bar_sync(1, EPI_THREADS);
+              if (et == 0) {
+                const uint32_t done = atomicAdd(tp.owner_count + owner, 1u) + 1u;
+                if (done == (uint32_t)tp.tiles_per_owner) {
+                  atomicExch(tp.owner_count + owner, 0u);
+                  __threadfence_system();
+                  ptx::st_release_sys(tp.dst_flag[owner], tp.epoch);
+                }
+              }
+            }
+            continue;
+          }
+        }
         ptx::fence_proxy_async_smem();
         named_bar_sync(1, EPI_THREADS);
         if (et == 0) {
@@ -352,13 +429,13 @@ gemm_2sm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
 }
 
 
-template <int BN>
-cudaError_t launch_2sm(const void* A, int lda, const void* B, int ldb, int M, int N, int K, const GemmEpilogue& ep,
-                       uint32_t* status, cudaStream_t stream) {
+// Clusters of two CTAs that can be resident at once (queried once per instantiation).
+template <int BN, bool TP>
+cudaError_t max_clusters_2sm(int* out) {
   using C = Cfg<BN>;
   static int max_clusters = 0;
   if (!max_clusters) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_2sm_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+    cudaError_t e = cudaFuncSetAttribute(gemm_2sm_kernel<BN, TP>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
     if (e != cudaSuccess) return e;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(2 * 74);
@@ -372,21 +449,74 @@ cudaError_t launch_2sm(const void* A, int lda, const void* B, int ldb, int M, in
     cfg.attrs = &attr;
     cfg.numAttrs = 1;
     int n = 0;
-    e = cudaOccupancyMaxActiveClusters(&n, gemm_2sm_kernel<BN>, &cfg);
+    e = cudaOccupancyMaxActiveClusters(&n, gemm_2sm_kernel<BN, TP>, &cfg);
     if (e != cudaSuccess) return e;
     if (n < 1) return cudaErrorInvalidConfiguration;
     max_clusters = n;
   }
+  *out = max_clusters;
+  return cudaSuccess;
+}
+
+template <int BN>
+cudaError_t launch_2sm(const void* A, int lda, const void* B, int ldb, int M, int N, int K, const GemmEpilogue& ep,
+                       uint32_t* status, cudaStream_t stream) {
+  using C = Cfg<BN>;
+  int max_clusters = 0;
+  cudaError_t e = max_clusters_2sm<BN, false>(&max_clusters);
+  if (e != cudaSuccess) return e;
   CUtensorMap ta, tb, to;
-  cudaError_t e = srpc_tensor_map_2d(&ta, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda * 2, BK, BM);
+  e = srpc_tensor_map_2d(&ta, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda * 2, BK, BM);
   if (e != cudaSuccess) return e;
   e = srpc_tensor_map_2d(&tb, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb * 2, BK, BN / 2);
   if (e != cudaSuccess) return e;
   e = srpc_tensor_map_2d(&to, ep.out, (uint64_t)N, (uint64_t)M, (uint64_t)ep.ldo * 2, 64, BM);
   if (e != cudaSuccess) return e;
-  const int tiles_m2 = (M + 2 * BM - 1) / (2 * BM), tiles_n = (N + BN - 1) / BN;
-  const int clusters = std::min(tiles_m2 * tiles_n, std::min(max_clusters, srpc_gemm_grid_sms() / 2));
-  gemm_2sm_kernel<BN><<<2 * clusters, C::THREADS, C::SMEM_BYTES, stream>>>(ta, tb, to, M, N, K, tiles_m2, tiles_n, ep, status);
+  TileOrder o;
+  o.tiles_m2 = (M + 2 * BM - 1) / (2 * BM);
+  o.tiles_n = (N + BN - 1) / BN;
+  o.clusters = std::min(o.tiles_m2 * o.tiles_n, std::min(max_clusters, srpc_gemm_grid_sms() / 2));
+  o.group_m = 4;
+  o.m_rot2 = 0;
+  gemm_2sm_kernel<BN, false><<<2 * o.clusters, C::THREADS, C::SMEM_BYTES, stream>>>(ta, tb, to, M, N, K, o, ep, status, TpParams{});
+  return cudaGetLastError();
+}
+
+// Tensor-parallel launch: `tp` arrives with mblocks_per_rank / mblock_bytes filled in and an even n_copy.
+template <int BN>
+cudaError_t launch_2sm_tp(const void* A, int lda, const void* B, int ldb, int M, int N, int K, const GemmEpilogue& ep,
+                          TpParams tp, uint32_t* status, cudaStream_t stream) {
+  using C = Cfg<BN>;
+  static_assert(C::SMEM_BYTES >= tpdev::COPY_SLOTS * tpdev::COPY_CHUNK, "the copier's ring lives in the operand stages");
+  int max_clusters = 0;
+  cudaError_t e = max_clusters_2sm<BN, true>(&max_clusters);
+  if (e != cudaSuccess) return e;
+  max_clusters = std::min(max_clusters, srpc_gemm_grid_sms() / 2);
+  const int copy_clusters = tp.n_copy / 2;
+  if (max_clusters - copy_clusters < 1) return cudaErrorInvalidValue;
+  CUtensorMap ta, tb, to;
+  e = srpc_tensor_map_2d(&ta, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda * 2, BK, BM);
+  if (e != cudaSuccess) return e;
+  e = srpc_tensor_map_2d(&tb, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb * 2, BK, BN / 2);
+  if (e != cudaSuccess) return e;
+  if (!tp.rs) {
+    e = srpc_tensor_map_2d(&to, ep.out, (uint64_t)N, (uint64_t)M, (uint64_t)ep.ldo * 2, 64, BM);
+    if (e != cudaSuccess) return e;
+  } else {
+    to = ta;  // never used: the epilogue stores to the owners' slots
+  }
+  TileOrder o;
+  o.tiles_m2 = M / (2 * BM);
+  o.tiles_n = (N + BN - 1) / BN;
+  o.clusters = std::min(o.tiles_m2 * o.tiles_n, max_clusters - copy_clusters);
+  const int m2_per_rank = tp.mblocks_per_rank / 2;
+  o.group_m = 1;
+  for (int g = 2; g <= 4; g++)
+    if (m2_per_rank % g == 0) o.group_m = g;  // groups never straddle two ranks' rows
+  // all-gather: own rows first (they are here already); reduce-scatter: own rows last (the peers' cross NVLink)
+  o.m_rot2 = (tp.rs ? (tp.rank + 1) % tp.tp : tp.rank) * m2_per_rank;
+  tp.tiles_per_owner = tp.mblocks_per_rank * o.tiles_n;
+  gemm_2sm_kernel<BN, true><<<2 * (o.clusters + copy_clusters), C::THREADS, C::SMEM_BYTES, stream>>>(ta, tb, to, M, N, K, o, ep, status, tp);
   return cudaGetLastError();
 }
 
@@ -421,3 +551,31 @@ cudaError_t srpc_gemm_bf16_2sm(const void* A, int lda, const void* B, int ldb, i
   if (bn == 128) return launch_2sm<128>(A, lda, B, ldb, M, N, K, ep, status, stream);
   return cudaErrorInvalidValue;
 }
+
+// Tensor-parallel entry point (see gemm_tp.h).  Takes the shapes where a rank's rows are whole 256-row pair tiles.
+bool srpc_gemm_tp_2sm_eligible(int M, int N, int K, const GemmEpilogue& ep, const TpParams& tp) {
+  static const int allow = [] { const char* e = getenv("SPLITRPC_TP_2SM"); return e ? atoi(e) : 1; }();
+  if (!allow || tp.tp < 1 || N < 128 || (N % 8) || K < 64 || ep.out_fp32 || (ep.ldo % 8)) return false;
+  if (ep.bias && ((uintptr_t)ep.bias & 15)) return false;
+  if (!tp.rs && ((uintptr_t)ep.out & 15)) return false;
+  return M % (2 * BM * tp.tp) == 0;
+}
+
+cudaError_t srpc_gemm_tp_2sm(const void* A, int lda, const void* B, int ldb, int M, int N, int K, const GemmEpilogue& ep,
+                             const TpParams& tp_in, uint32_t* status, cudaStream_t stream) {
+  if (!srpc_gemm_tp_2sm_eligible(M, N, K, ep, tp_in)) return cudaErrorInvalidValue;
+  TpParams tp = tp_in;
+  tp.mblocks_per_rank = (M / BM) / tp.tp;
+  tp.m_rot = 0;
+  tp.mblock_bytes = (size_t)BM * lda * 2;
+  tp.n_copy = tp.mblock_ready ? (tp.n_copy + 1) & ~1 : 0;
+  if (tp.rs)
+    for (int o = 0; o < tp.tp; o++)
+      if ((uintptr_t)tp.dst[o] & 15) return cudaErrorInvalidValue;
+  const int bn = (N % 256 == 0) ? 256 : ((N % 192 == 0) ? 192 : (N % 128 == 0 ? 128 : (N >= 1024 ? 256 : 128)));
+  if (bn == 256) return launch_2sm_tp<256>(A, lda, B, ldb, M, N, K, ep, tp, status, stream);
+  if (bn == 192) return launch_2sm_tp<192>(A, lda, B, ldb, M, N, K, ep, tp, status, stream);
+  return launch_2sm_tp<128>(A, lda, B, ldb, M, N, K, ep, tp, status, stream);
+}
+
+cudaError_t srpc_gemm_tp_2sm_set_wait_ns(uint64_t ns) { return tpdev::set_wait_ns_here(ns); }

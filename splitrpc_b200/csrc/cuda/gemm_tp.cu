@@ -494,6 +494,7 @@ cudaError_t srpc_gemm_tp(const void* A, int lda, const void* B, int ldb, int M, 
   if ((lda % 8) || (ldb % 8) || (K % 8) || ((uintptr_t)A & 15) || ((uintptr_t)B & 15) || (ep.ldo % 8)) return cudaErrorInvalidValue;
   TpParams tp = tp_in;
   if (tp.tp < 1 || tp.tp > TP_MAX_RANKS || (M / BM) % tp.tp != 0) return cudaErrorInvalidValue;
+  if (srpc_gemm_tp_2sm_eligible(M, N, K, ep, tp)) return srpc_gemm_tp_2sm(A, lda, B, ldb, M, N, K, ep, tp, status, stream);
   tp.mblocks_per_rank = (M / BM) / tp.tp;
   tp.m_rot = tp.rank * tp.mblocks_per_rank;
   tp.mblock_bytes = (size_t)BM * lda * 2;
@@ -544,7 +545,8 @@ __global__ void tp_wait_kernel(const uint32_t* flags, int n, uint32_t epoch, con
 
 // Sets the bound of the flag waits of every kernel in this file on the current device.
 cudaError_t srpc_tp_set_wait_ns(uint64_t ns) {
-  return cudaMemcpyToSymbol(tpdev::g_flag_wait_ns, &ns, sizeof(ns));
+  cudaError_t e = tpdev::set_wait_ns_here(ns);
+  return e != cudaSuccess ? e : srpc_gemm_tp_2sm_set_wait_ns(ns);
 }
 
 cudaError_t srpc_tp_wait(const uint32_t* flags, int n, uint32_t epoch, const uint32_t* epoch_base, uint32_t* status,

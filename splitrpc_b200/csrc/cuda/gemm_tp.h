@@ -62,6 +62,12 @@ struct TpReduce {
 // finished tiles are stored into the owners' slots instead of ep.out (ep.ldo = row stride of a slot).
 cudaError_t srpc_gemm_tp(const void* A, int lda, const void* B, int ldb, int M, int N, int K, const GemmEpilogue& ep,
                          const TpParams& tp, uint32_t* status, cudaStream_t stream);
+// The same operation on 256-row tiles computed by CTA pairs (tcgen05 cta_group::2); srpc_gemm_tp forwards the shapes
+// that srpc_gemm_tp_2sm_eligible accepts (rows per rank a multiple of 256, N >= 128) unless SPLITRPC_TP_2SM=0.
+bool srpc_gemm_tp_2sm_eligible(int M, int N, int K, const GemmEpilogue& ep, const TpParams& tp);
+cudaError_t srpc_gemm_tp_2sm(const void* A, int lda, const void* B, int ldb, int M, int N, int K, const GemmEpilogue& ep,
+                             const TpParams& tp, uint32_t* status, cudaStream_t stream);
+cudaError_t srpc_gemm_tp_2sm_set_wait_ns(uint64_t ns);
 cudaError_t srpc_tp_signal(const TpSignal& sig, cudaStream_t stream);
 // Stream-ordered bounded wait until flags[0..n) >= epoch (+ *epoch_base); a timeout sets *status.
 cudaError_t srpc_tp_wait(const uint32_t* flags, int n, uint32_t epoch, const uint32_t* epoch_base, uint32_t* status,

@@ -8,9 +8,11 @@
 namespace tpdev {
 
 // Upper bound of every flag wait, in nanoseconds.  A run-time value (srpc_tp_set_wait_ns) so that a test can let a wait
-// run out within milliseconds; the default is two seconds.
-__device__ uint64_t g_flag_wait_ns = 2000000000ull;
+// run out within milliseconds; the default is two seconds.  Every translation unit that includes this header has its
+// own copy of the word and sets it through set_wait_ns_here().
+static __device__ uint64_t g_flag_wait_ns = 2000000000ull;
 #define FLAG_WAIT_NS (tpdev::g_flag_wait_ns)
+static inline cudaError_t set_wait_ns_here(uint64_t ns) { return cudaMemcpyToSymbol(g_flag_wait_ns, &ns, sizeof(ns)); }
 
 // Bounded wait until *flag >= epoch (flags only ever grow).
 __device__ __forceinline__ bool wait_flag_gpu(const uint32_t* flag, uint32_t epoch) {

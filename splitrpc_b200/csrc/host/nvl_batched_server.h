@@ -123,6 +123,11 @@ class NvlBatchedServer {
     rep.resp_buf = {(uint64_t)(uintptr_t)app_->app_rr_pool->rr_mem_pool->get_resp_addr_range(), ex.resp_capacity, 1, 0};
     rep.ctl_buf = {(uint64_t)(uintptr_t)app_->app_rr_pool->rr_mem_pool->get_doorbells_host(), ex.ctl_bytes, 2, 0};
     rep.transform = transform_;
+    rep.timer_offset_ns = 0;  // a CPU app stamps with the steady clock itself
+    if (app_->device_id >= 0) {
+      const SrpcDeviceOps* ops = srpc_cuda_ops();
+      if (ops && ops->timer_offset_ns) ops->timer_offset_ns(app_->device_id, &rep.timer_offset_ns);
+    }
     bool ok = ch.send_msg(&rep, sizeof(rep), out_fds, 3);
     for (int f : out_fds) ::close(f);
     if (!ok) stop_worker();
@@ -243,6 +248,7 @@ class NvlRemoteReplica {
   std::unique_ptr<P2pRpcAppRrPool> pool_;
   std::unique_ptr<P2pRpcSgEngine> engine_;
   buf_mon_rr info_{};
+  int64_t stamp_skew_ns_ = 0;
   std::mutex mu_;
 
  public:
@@ -305,8 +311,18 @@ class NvlRemoteReplica {
                                          (uint64_t)(uintptr_t)r->pool_->rr_mem_pool->get_req_addr_range(),
                                          (uint32_t)ex.req_size, r->info_.transform.params) != 0)
       return fail("the engine cannot apply the server's ingress transform");
+    // Doorbell stamps come from the ingress device's timer, completion stamps from the serving device's.
+    int64_t ingress_offset = 0;
+    if (dev >= 0) {
+      const SrpcDeviceOps* ops = srpc_cuda_ops();
+      if (ops && ops->timer_offset_ns) ops->timer_offset_ns(dev, &ingress_offset);
+    }
+    r->stamp_skew_ns_ = r->info_.timer_offset_ns - ingress_offset;
     return r;
   }
+  // (completion stamp - doorbell stamp) exceeds the true latency by this much: the two stamps come from different
+  // devices' timers.
+  int64_t stamp_skew_ns() const { return stamp_skew_ns_; }
 
   P2pRpcAppRrPool* pool() { return pool_.get(); }
   P2pRpcSgEngine* engine() { return engine_.get(); }

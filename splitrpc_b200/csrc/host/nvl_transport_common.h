@@ -58,6 +58,7 @@ struct buf_mon_rr {
   nvl_buffer_attr tx_arena;                    // request
   nvl_ingress_transform transform;             // reply
   uint64_t stat_served = 0, stat_batches = 0;  // BUF_MON_STATS reply
+  int64_t timer_offset_ns = 0;  // reply: the serving device's stamp timer minus the machine's steady clock
 };
 
 // Per-request notification (host path, kept for parity with the original's SEND_WITH_IMM of a slot index; the

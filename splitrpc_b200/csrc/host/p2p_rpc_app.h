@@ -146,6 +146,10 @@ struct SrpcDeviceOps {
   // Queues, on `s`, the kernel that stores the `n` responses of the window at *d_stub where *d_push says and marks
   // their slots WORK_COMPLETE (see RespPushCtx).
   int (*resp_push)(const void* d_stub, const void* d_push, int n, cudaStream_t s);
+  // Device `dev`'s nanosecond timer (what its kernels stamp slots with) minus this machine's steady clock, measured
+  // now.  The timers of two GPUs differ by an arbitrary amount; a latency that starts on one GPU and ends on another
+  // is the difference of the stamps minus the difference of these offsets.
+  int (*timer_offset_ns)(int dev, int64_t* offset);
 };
 
 // Implemented by the CUDA half; returns nullptr when the library was built
@@ -553,10 +557,18 @@ class P2pRpcAppRrPool {
   int get_device_id() const { return device_id_; }
   P2pRpcAppRr* get_app_rr_pool() { return rr_pool; }
   P2pRpcAppRr* get_app_rr(int idx) { return (idx >= 0 && idx < pool_size_) ? &rr_pool[idx] : nullptr; }
+  // Start of a serving session: the rings rewind and every slot is FREE with no transmit offset and no stamps
+  // (whatever an earlier session left behind, e.g. a window that was armed when its server stopped).
   void init_pool() {
     pi_idx_ = 0;
     req_pool_->reset();
     resp_pool_->reset();
+    for (int i = 0; i < pool_size_; i++) {
+      P2pRpcAppRr* r = &rr_pool[i];
+      if (r->h_stamps) r->h_stamps[0] = r->h_stamps[1] = 0;
+      if (r->h_tx_off) __atomic_store_n(r->h_tx_off, P2pRpcAppRrMemPool::kNoTxOffset, __ATOMIC_RELAXED);
+      if (r->h_state) __atomic_store_n(r->h_state, (uint32_t)APP_RR_STATUS::FREE, __ATOMIC_RELEASE);
+    }
   }
   size_t producer_index() const { return pi_idx_; }
 

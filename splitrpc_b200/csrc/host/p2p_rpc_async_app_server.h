@@ -406,11 +406,18 @@ class P2pRpcAsyncAppServer {
     }
     if (armed && c->device_id >= 0) {
       // Let the armed stream run through: mark the awaited slot ready, then wait
-      // (bounded by the stream sync) for the queued work to drain.
+      // (bounded by the stream sync) for the queued work to drain.  The window
+      // holds no requests, so the kernels must neither store responses nor
+      // complete its slots: the push block is read when they run, switch it off.
       int last = (ci + c->curr_batch_size - 1) % n;
+      const uint32_t push_was = c->h_push->enabled;
+      c->h_push->enabled = 0;
+      std::atomic_thread_fence(std::memory_order_seq_cst);
       store_state(pool->get_app_rr(last)->h_state, APP_RR_STATUS::RX_COMPLETE);
       c->WaitForAppRunComplete();
       store_state(pool->get_app_rr(last)->h_state, APP_RR_STATUS::FREE);
+      c->h_push->enabled = push_was;
+      c->ResetAppRunStatus();
     }
   }
 };

@@ -54,6 +54,7 @@ class SplitRpcServer {
     P2pRpcSgEngine* engine = nullptr;
     NvlRemoteReplica* remote = nullptr;
     bool device_completes = false;         // responses and WORK_COMPLETE arrive without this process's help
+    int64_t stamp_skew_ns = 0;             // serving device's stamp timer minus the gather device's
     int app_idx = -1;
     int tx_idx = 0;                        // next slot whose response goes out
     std::atomic<int> outstanding{0};
@@ -361,9 +362,10 @@ class SplitRpcServer {
               rep.stats.pushed++;
               // doorbell rung -> response stored, on the timers of the devices that did it
               const uint64_t t_rx = slots[i]->h_stamps[0], t_done = slots[i]->h_stamps[1];
-              if (t_rx && t_done > t_rx && t_done - t_rx < 60000000000ull) {
+              const int64_t lat = (int64_t)(t_done - t_rx) - rep.stamp_skew_ns;
+              if (t_rx && t_done && lat > 0 && lat < 60000000000ll) {
                 std::lock_guard<std::mutex> g(lat_mu_);
-                if (device_latency_ns_.size() < ((size_t)1 << 21)) device_latency_ns_.push_back(t_done - t_rx);
+                if (device_latency_ns_.size() < ((size_t)1 << 21)) device_latency_ns_.push_back((uint64_t)lat);
               }
             } else {
               s_rrs.push_back(rrs[i]);
@@ -463,6 +465,7 @@ class SplitRpcServer {
     r->pool = remote->pool();
     r->engine = remote->engine();
     r->device_completes = remote->device_completes();
+    r->stamp_skew_ns = remote->stamp_skew_ns();
     {
       P2pRpcAppRrMemPool* mp = r->pool->rr_mem_pool;
       r->engine->set_stamp_layout(mp->get_doorbells_host(), mp->get_stamps_host(), mp->get_doorbells_device(), mp->get_stamps_device());

@@ -22,7 +22,10 @@ def env():
     return torch, _C, ops
 
 
-@pytest.mark.parametrize("T,K,N,tp", [(512, 256, 384, 2), (1024, 1024, 512, 4), (2048, 512, 2048, 2)])
+# Rows per rank that are a multiple of 256 run on CTA pairs (256-row tiles, 128 / 192 / 256 columns wide), the others
+# on the one-SM kernel.
+@pytest.mark.parametrize("T,K,N,tp", [(512, 256, 384, 2), (1024, 1024, 512, 4), (2048, 512, 2048, 2), (768, 256, 384, 2),
+                                      (6144, 1024, 1536, 2), (6144, 1024, 512, 8), (2048, 512, 640, 4)])
 def test_all_gather_gemm_emulated_ranks(env, T, K, N, tp):
     torch, C, ops = env
     rows = T // tp
@@ -49,7 +52,8 @@ def test_all_gather_gemm_emulated_ranks(env, T, K, N, tp):
         assert all(int(mblock[m]) == 5 for m in remote)
 
 
-@pytest.mark.parametrize("T,Kl,N,tp", [(512, 256, 384, 2), (1024, 512, 1024, 4), (2048, 2048, 1024, 2)])
+@pytest.mark.parametrize("T,Kl,N,tp", [(512, 256, 384, 2), (1024, 512, 1024, 4), (2048, 2048, 1024, 2), (768, 256, 384, 2),
+                                       (6144, 512, 1024, 2), (6144, 128, 1024, 8), (2048, 256, 640, 4)])
 def test_gemm_reduce_scatter_emulated_ranks(env, T, Kl, N, tp):
     torch, C, ops = env
     rows = T // tp
