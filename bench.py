@@ -196,14 +196,13 @@ def device_timed_single_ingress(node, rank: int, world: int, steps: int, warmup:
         w = i % n_sets
         st = stream.cuda_stream
         _C.stream_wait32(st, app.states_dev + 4 * (w * nb + nb - 1), RX_COMPLETE)
-        # re-point the stub (request / response window) and the window's first slot in stream order
-        _C.stream_write64(st, app.d_stub, req_base + w * nb * req)
-        _C.stream_write64(st, app.d_stub + 8, resp_base + w * nb * resp)
-        _C.stream_write32(st, app.d_first_slot, w * nb)
+        # re-point what the graph's kernels read (request / response window, first slot, where each response goes) in
+        # stream order: one small kernel behind the doorbell wait, as the stream-armed worker queues it
+        app.stage_window(req_base + w * nb * req, resp_base + w * nb * resp, w * nb, nb, armed=True)
         app.launch(nb)  # the graph; its last kernel stores the responses into rank 0's arena and completes the slots
         with torch.cuda.stream(stream):
             flush.zero_()  # L2 flush between iterations (inside the timed region)
-        return node.model.kernels_per_forward
+        return node.model.kernels_per_forward + 1  # + the window update
 
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with torch.cuda.stream(stream):
@@ -282,9 +281,7 @@ def device_timed_per_gpu(srv, steps: int, warmup: int):
             _C.sg_list_launch(lists[w], 0, gb, sg_stream.cuda_stream)
         gathered[i].record(sg_stream)
         stream.wait_event(gathered[i])
-        _C.stream_write64(stream.cuda_stream, app.d_stub, int(stubs[w, 0]))
-        _C.stream_write64(stream.cuda_stream, app.d_stub + 8, int(stubs[w, 1]))
-        _C.stream_write32(stream.cuda_stream, app.d_first_slot, int(first[w]))
+        app.stage_window(int(stubs[w, 0]), int(stubs[w, 1]), int(first[w]), nb)
         app.launch(nb)
         with torch.cuda.stream(stream):
             flush.zero_()

@@ -530,7 +530,21 @@ PYBIND11_MODULE(_C, m) {
       .def("set_first_slot", [](AppHolder& a, uint32_t slot) {
         a.info->app_ctx->h_push->first_slot = slot;
         std::atomic_thread_fence(std::memory_order_seq_cst);
+        a.info->stage_window((int)slot, 0, false);
       })
+      // Stream-ordered update of what the next batch's kernels read (stand-alone timing loops; the server's workers do
+      // this themselves): the stub points at req / resp, the batch of `batch` requests starts at `first_slot`.  With
+      // `armed` the transmit offsets are read from the slot table when the update runs (queue it behind the doorbell
+      // wait), otherwise they are taken from the table now.
+      .def("stage_window",
+           [](AppHolder& a, uintptr_t req, uintptr_t resp, int first_slot, int batch, bool armed) {
+             a.info->app_ctx->h_stub->req = (uint8_t*)req;
+             a.info->app_ctx->h_stub->resp = (uint8_t*)resp;
+             a.info->app_ctx->h_push->first_slot = (uint32_t)first_slot;
+             std::atomic_thread_fence(std::memory_order_seq_cst);
+             a.info->stage_window(first_slot, batch, armed);
+           },
+           py::arg("req"), py::arg("resp"), py::arg("first_slot"), py::arg("batch"), py::arg("armed") = false)
       .def_property_readonly("pool_size", [](AppHolder& a) { return a.info->app_rr_pool->get_pool_size(); })
       // Slot-level access for stand-alone timing loops and tests (the server's threads do all of this themselves):
       // device-side address of the slot state words, state and response destination of one slot, and a reset of the
@@ -562,6 +576,7 @@ PYBIND11_MODULE(_C, m) {
              a.info->app_ctx->h_stub->req = req ? (uint8_t*)req : (uint8_t*)mp->get_req_addr_range();
              a.info->app_ctx->h_stub->resp = resp ? (uint8_t*)resp : (uint8_t*)mp->get_resp_addr_range();
              std::atomic_thread_fence(std::memory_order_seq_cst);
+             a.info->stage_window((int)a.info->app_ctx->h_push->first_slot, 0, false);
            },
            py::arg("req") = 0, py::arg("resp") = 0)
       // Runs the app once for `batch` requests at the current stub without waiting.

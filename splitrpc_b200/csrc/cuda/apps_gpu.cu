@@ -358,14 +358,15 @@ int gpu_app_run(AppCtx* c) {
       c->ResetAppRunStatus();
       std::atomic_thread_fence(std::memory_order_seq_cst);
       ResidentArgs a{s->req_size, s->resp_size, s->dim, LeNetW{}};
+      // a resident kernel polls the host-mapped stub and push block (nothing is queued behind it to update a copy)
       if (s->name == "vec_add") {
-        app_resident<RESIDENT_VEC_ADD><<<1, 1024, 0, c->work_stream>>>(c->d_stub, c->d_door_bell, a, s->idle_ns, s->d_pt_status, c->d_push);
+        app_resident<RESIDENT_VEC_ADD><<<1, 1024, 0, c->work_stream>>>(c->d_stub_mapped, c->d_door_bell, a, s->idle_ns, s->d_pt_status, c->d_push_mapped);
       } else if (s->name == "matmul") {
-        app_resident<RESIDENT_MATMUL><<<1, 256, (size_t)s->dim * s->dim * 4, c->work_stream>>>(c->d_stub, c->d_door_bell, a,
-                                                                                               s->idle_ns, s->d_pt_status, c->d_push);
+        app_resident<RESIDENT_MATMUL><<<1, 256, (size_t)s->dim * s->dim * 4, c->work_stream>>>(c->d_stub_mapped, c->d_door_bell, a,
+                                                                                               s->idle_ns, s->d_pt_status, c->d_push_mapped);
       } else {
         a.w = lenet_w(s);
-        app_resident<RESIDENT_LENET5><<<1, 256, 0, c->work_stream>>>(c->d_stub, c->d_door_bell, a, s->idle_ns, s->d_pt_status, c->d_push);
+        app_resident<RESIDENT_LENET5><<<1, 256, 0, c->work_stream>>>(c->d_stub_mapped, c->d_door_bell, a, s->idle_ns, s->d_pt_status, c->d_push_mapped);
       }
     }
     c->NotifyAppRunStart();

@@ -313,6 +313,11 @@ static int d_resp_push(const void* d_stub, const void* d_push, int n, cudaStream
   RT(sg_launch_resp_push(d_stub, d_push, n, s));
   return 0;
 }
+static int d_window_params(void* block, const g_params* stub, const RespPushCtx* ctx, const uint64_t* offsets, int n,
+                           const uint32_t* live_enabled, cudaStream_t s) {
+  RT(sg_launch_window_params(block, stub, ctx, offsets, n, live_enabled, s));
+  return 0;
+}
 // One thread writes the device timer into a mapped host word; the host notes its own clock the moment the word
 // arrives (the write takes about a microsecond to cross PCIe).  The smallest of a few tries is the least delayed.
 __global__ void timer_probe_kernel(volatile unsigned long long* out) {
@@ -378,7 +383,7 @@ extern "C" const SrpcDeviceOps* srpc_cuda_ops() {
       d_write32,      d_event_create, d_event_destroy, d_ring_alloc,        d_ring_free,   d_host_alloc_mapped,
       d_host_free,    d_dev_alloc,    d_dev_free,      d_memcpy_async,      d_memset_async, d_graph_launch, d_last_error,
       d_ring_export,  d_ring_import,  d_host_register, d_host_unregister,   d_resp_push,
-      d_timer_offset_ns};
+      d_timer_offset_ns, d_window_params};
   return &ops;
 }
 

@@ -28,7 +28,8 @@ __device__ __forceinline__ RespPushTarget resp_push_target(const RespPushCtx* ct
   RespPushTarget t{ring_dst, nullptr, nullptr};
   if (!ctx || ctx->enabled == 0 || ctx->pool_size == 0) return t;
   const uint32_t slot = (ctx->first_slot + row) % ctx->pool_size;
-  const uint64_t off = ctx->tx_off[slot];
+  const uint64_t* win = ctx->tx_window;
+  const uint64_t off = win ? win[row] : ctx->tx_off[slot];
   if (ctx->tx_base && off != ~0ull && off + ctx->resp_size <= ctx->tx_bytes) t.dst = reinterpret_cast<uint8_t*>(ctx->tx_base + off);
   t.state = ctx->states + slot;
   t.stamp = ctx->stamps ? ctx->stamps + 2 * slot + 1 : nullptr;

@@ -153,6 +153,38 @@ __global__ void __launch_bounds__(256) resp_push_kernel(const g_params* __restri
   if (threadIdx.x == 0) resp_push_complete(t);
 }
 
+// Rewrites an app's parameter block (stub, push block, transmit offsets of the batch) in the GPU's own memory.  The
+// stub and the push block arrive as launch arguments; the offsets either with them or, when the host could not know
+// them at launch time (a window armed ahead of its requests), from the per-slot table in host memory, all rows at
+// once so that the reads overlap.
+struct WindowParams {
+  g_params stub;
+  RespPushCtx ctx;
+  uint8_t* block;
+  const volatile uint32_t* live_enabled;
+  int n;
+  int fetch;
+  uint64_t off[APP_PARAM_INLINE_MAX];
+};
+__global__ void __launch_bounds__(128) window_params_kernel(const __grid_constant__ WindowParams p) {
+  uint64_t* win = reinterpret_cast<uint64_t*>(p.block + APP_PARAM_WINDOW_OFFSET);
+  uint32_t live = 1;
+  if (threadIdx.x == 0 && p.live_enabled) live = *p.live_enabled;
+  for (int r = threadIdx.x; r < p.n; r += blockDim.x) {
+    uint64_t v = ~0ull;
+    if (!p.fetch) v = p.off[r];
+    else if (p.ctx.tx_off && p.ctx.pool_size) v = p.ctx.tx_off[(p.ctx.first_slot + (uint32_t)r) % p.ctx.pool_size];
+    win[r] = v;
+  }
+  if (threadIdx.x == 0) {
+    RespPushCtx c = p.ctx;
+    c.tx_window = p.n > 0 ? win : nullptr;
+    if (live == 0) c.enabled = 0;
+    *reinterpret_cast<g_params*>(p.block) = p.stub;
+    *reinterpret_cast<RespPushCtx*>(p.block + APP_PARAM_PUSH_OFFSET) = c;
+  }
+}
+
 __device__ __forceinline__ bool bulk_ok(const ChunkRef& r) {
   return ((((uintptr_t)r.src) | ((uintptr_t)r.dst) | (uintptr_t)r.len) & 15) == 0 && r.len > 0;
 }
@@ -415,6 +447,7 @@ static cudaError_t sg_kernel_setup() {
     (void)cudaFuncGetAttributes(&fa, sg_stem_s2d);
     (void)cudaFuncGetAttributes(&fa, sg_persistent);
     (void)cudaFuncGetAttributes(&fa, resp_push_kernel);
+    (void)cudaFuncGetAttributes(&fa, window_params_kernel);
     static const int on = [] { const char* e = getenv("P2P_RPC_SG_MAX_SHARED"); return e ? atoi(e) : 1; }();
     if (on) {
       prefer_max_shared(sg_copy_simt);
@@ -460,6 +493,24 @@ cudaError_t sg_launch_resp_push(const void* d_stub, const void* d_push, int n, c
   if (n <= 0) return cudaSuccess;
   sg_kernel_setup();
   resp_push_kernel<<<n, 256, 0, stream>>>((const g_params*)d_stub, (const RespPushCtx*)d_push);
+  return cudaGetLastError();
+}
+
+cudaError_t sg_launch_window_params(void* block, const g_params* stub, const RespPushCtx* ctx, const uint64_t* offsets, int n,
+                                    const uint32_t* live_enabled, cudaStream_t stream) {
+  if (!block || !stub || !ctx || n < 0) return cudaErrorInvalidValue;
+  if (offsets ? n > APP_PARAM_INLINE_MAX : n > APP_PARAM_WINDOW_MAX) return cudaErrorInvalidValue;
+  sg_kernel_setup();
+  WindowParams p;
+  p.stub = *stub;
+  p.ctx = *ctx;
+  p.block = (uint8_t*)block;
+  p.live_enabled = live_enabled;
+  p.n = n;
+  p.fetch = offsets ? 0 : 1;
+  if (offsets)
+    for (int i = 0; i < n; i++) p.off[i] = offsets[i];
+  window_params_kernel<<<1, 128, 0, stream>>>(p);
   return cudaGetLastError();
 }
 

@@ -63,6 +63,11 @@ cudaError_t sg_launch_copy(const SgItem* d_items, uint32_t n_items, uint32_t n_c
 // Stores the responses of a batch where the producer asked for them and completes their slots (see resp_push.cuh):
 // one block per response.  d_stub / d_push are the device views of the app's stub and RespPushCtx.
 cudaError_t sg_launch_resp_push(const void* d_stub, const void* d_push, int n, cudaStream_t stream);
+// See SrpcDeviceOps::window_params.
+struct g_params;
+struct RespPushCtx;
+cudaError_t sg_launch_window_params(void* block, const g_params* stub, const RespPushCtx* ctx, const uint64_t* offsets, int n,
+                                    const uint32_t* live_enabled, cudaStream_t stream);
 // fp32 -> bf16 gather: every item copies len/4 floats to len/4 bf16 values,
 // computing (x - shift) * scale on the way.
 cudaError_t sg_launch_cast_bf16(const SgItem* d_items, uint32_t n_items, uint32_t n_chunks, float scale, float shift,

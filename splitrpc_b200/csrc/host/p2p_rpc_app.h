@@ -68,7 +68,19 @@ struct RespPushCtx {
   uint32_t resp_size;
   uint32_t enabled;
   uint32_t first_slot;              // written by the worker with the stub, before every run
+  // Optional: the transmit offsets of the running batch, request r at tx_window[r], already looked up and placed in
+  // the serving GPU's own memory (see SrpcDeviceOps::window_params).  nullptr: kernels read tx_off[slot].
+  const uint64_t* tx_window;
 };
+
+// A GPU app's kernels take the stub and the push block from a small block in the GPU's own memory, laid out as
+// below and rewritten in stream order before every batch.  (A read of mapped host memory by a kernel crosses PCIe;
+// a kernel whose every block does a dozen of them spends longer on that than on its work.)
+static constexpr size_t APP_PARAM_BLOCK_BYTES = 4096;
+static constexpr size_t APP_PARAM_PUSH_OFFSET = 64;     // RespPushCtx
+static constexpr size_t APP_PARAM_WINDOW_OFFSET = 256;  // tx_window[]
+static constexpr int APP_PARAM_WINDOW_MAX = (int)((APP_PARAM_BLOCK_BYTES - APP_PARAM_WINDOW_OFFSET) / 8);
+static constexpr int APP_PARAM_INLINE_MAX = 112;        // offsets that fit the kernel's argument space
 
 // ------------------------------------------------------------------ tring
 // Bump-pointer address generator over a ring-shaped address range (reference
@@ -150,6 +162,13 @@ struct SrpcDeviceOps {
   // now.  The timers of two GPUs differ by an arbitrary amount; a latency that starts on one GPU and ends on another
   // is the difference of the stamps minus the difference of these offsets.
   int (*timer_offset_ns)(int dev, int64_t* offset);
+  // Queues, on `s`, a one-block kernel that rewrites the parameter block `block` (device memory, see
+  // APP_PARAM_BLOCK_BYTES) with *stub, *ctx and the transmit offsets of a batch of `n` requests: `offsets[0..n)` when
+  // `offsets` is given (n <= APP_PARAM_INLINE_MAX; the values travel in the launch), otherwise read from
+  // ctx->tx_off[(first_slot + r) % pool_size] when the kernel runs (n <= APP_PARAM_WINDOW_MAX).  `live_enabled`
+  // (optional, device view of a host word): a zero found there when the kernel runs switches the push off.
+  int (*window_params)(void* block, const g_params* stub, const RespPushCtx* ctx, const uint64_t* offsets, int n,
+                       const uint32_t* live_enabled, cudaStream_t s);
 };
 
 // Implemented by the CUDA half; returns nullptr when the library was built
@@ -619,6 +638,11 @@ class MetaAppCtx {
   int last_status = 0;                      // 0 ok, -1 a bounded wait ran out
   RespPushCtx* h_push = nullptr;            // response-push block (host view / device view), see RespPushCtx
   RespPushCtx* d_push = nullptr;
+  // On a GPU, d_stub and d_push point into a parameter block in the GPU's own memory that P2pRpcAppInfo::stage_window
+  // rewrites in stream order before every batch; the mapped host copies below are what resident kernels poll.
+  T* d_stub_mapped = nullptr;
+  RespPushCtx* d_push_mapped = nullptr;
+  uint8_t* param_block = nullptr;
   bool self_push = false;                   // the app's own kernels store responses and completions (fused epilogue)
 
   // Makes the work stream wait until *d_state == value.

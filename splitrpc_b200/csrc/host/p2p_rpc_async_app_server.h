@@ -84,6 +84,13 @@ class P2pRpcAppInfo {
       d_door_bells = (uint32_t*)((uint8_t*)d + 128);
       app_ctx->h_push = (RespPushCtx*)((uint8_t*)h + 256);
       app_ctx->d_push = (RespPushCtx*)((uint8_t*)d + 256);
+      // What kernels read: a copy of both in the GPU's own memory, rewritten by stage_window() before every batch.
+      void* blk = nullptr;
+      if (ops->window_params && ops->dev_alloc(device_id, APP_PARAM_BLOCK_BYTES, &blk) == 0 && blk) {
+        ops->memset_async(blk, 0, APP_PARAM_BLOCK_BYTES, app_ctx->work_stream);
+        ops->stream_sync(app_ctx->work_stream);
+        app_ctx->param_block = (uint8_t*)blk;
+      }
     } else {
       void* p = nullptr;
       if (posix_memalign(&p, 64, 512) != 0) std::abort();
@@ -94,7 +101,12 @@ class P2pRpcAppInfo {
     }
     std::memset(app_ctx->h_push, 0, sizeof(RespPushCtx));
     app_ctx->h_stub = h_stubs;
-    app_ctx->d_stub = d_stubs;
+    app_ctx->d_stub = app_ctx->d_stub_mapped = d_stubs;
+    app_ctx->d_push_mapped = app_ctx->d_push;
+    if (app_ctx->param_block) {
+      app_ctx->d_stub = (g_params*)app_ctx->param_block;
+      app_ctx->d_push = (RespPushCtx*)(app_ctx->param_block + APP_PARAM_PUSH_OFFSET);
+    }
     app_ctx->door_bell = door_bells;
     app_ctx->d_door_bell = d_door_bells;
     app_ctx->h_stub->req = nullptr;
@@ -111,6 +123,7 @@ class P2pRpcAppInfo {
         ops->stream_sync(app_ctx->work_stream);
         ops->stream_destroy(app_ctx->work_stream);
         ops->event_destroy(app_ctx->work_complete);
+        if (app_ctx->param_block) ops->dev_free(app_ctx->param_block);
         ops->host_free(h_stubs);
       }
     } else {
@@ -135,15 +148,43 @@ class P2pRpcAppInfo {
     p->pool_size = (uint32_t)rr_pool_size;
     p->resp_size = (uint32_t)resp_size;
     p->first_slot = 0;
+    p->tx_window = nullptr;
     std::atomic_thread_fence(std::memory_order_release);
     p->enabled = 1;
     std::atomic_thread_fence(std::memory_order_seq_cst);
     completion_by_device = true;
+    stage_window(0, 0, false);
   }
   void disable_device_completion() {
     completion_by_device = false;
     app_ctx->h_push->enabled = 0;
     std::atomic_thread_fence(std::memory_order_seq_cst);
+    stage_window(0, 0, false);
+  }
+
+  // Makes the kernels of the next batch see the current stub and push block: on a GPU, queues the kernel that
+  // rewrites the parameter block in the GPU's memory (in stream order, so batches already queued keep theirs).
+  // `batch` requests starting at slot `first_slot`; their transmit offsets travel with the launch when the slots are
+  // already filled (`armed` false), otherwise the kernel reads them from the slot table when it runs, which is after
+  // the doorbell wait that the caller has queued before it.
+  void stage_window(int first_slot, int batch, bool armed) {
+    AppCtx* c = app_ctx;
+    if (device_id < 0 || !c->param_block || c->launch_type == 3) return;  // resident kernels poll the mapped copies
+    const SrpcDeviceOps* ops = srpc_require_cuda("parameter block");
+    RespPushCtx ctx = *c->h_push;
+    ctx.first_slot = (uint32_t)first_slot;
+    uint64_t offs[APP_PARAM_INLINE_MAX];
+    const uint64_t* inline_offs = nullptr;
+    int n = (completion_by_device && ctx.enabled) ? batch : 0;
+    if (n > APP_PARAM_WINDOW_MAX) n = 0;  // kernels fall back to the slot table
+    if (n > 0 && !armed && n <= APP_PARAM_INLINE_MAX) {
+      for (int r = 0; r < n; r++)
+        offs[r] = __atomic_load_n(app_rr_pool->get_app_rr((first_slot + r) % rr_pool_size)->h_tx_off, __ATOMIC_ACQUIRE);
+      inline_offs = offs;
+    }
+    const uint32_t* live = armed ? &c->d_push_mapped->enabled : nullptr;
+    if (ops->window_params(c->param_block, c->h_stub, &ctx, inline_offs, n, live, c->work_stream) != 0)
+      srpc_log(SRPC_LOG_ERROR, "parameter block update failed: %s", ops->last_error());
   }
 
   // Stores the responses of the batch that just ran (app_ctx->curr_batch_size requests from slot h_push->first_slot on)
@@ -240,6 +281,7 @@ class P2pRpcAsyncAppServer {
     a->app_ctx->h_push->first_slot = (uint32_t)rr_idx;
     std::atomic_thread_fence(std::memory_order_release);
     NVTX_R("AppRun");
+    a->stage_window(rr_idx, a->app_ctx->curr_batch_size, false);
     a->app_run(a->app_ctx);
     a->push_responses();
     NVTX_P();
@@ -353,6 +395,7 @@ class P2pRpcAsyncAppServer {
     std::atomic_thread_fence(std::memory_order_seq_cst);
     c->AppRrRunNotify(a->app_rr_pool->get_app_rr(last_rr_idx)->d_state, APP_RR_STATUS::RX_COMPLETE);
     if (c->last_status == 0 || c->device_id >= 0) {
+      a->stage_window(start_rr_idx, c->curr_batch_size, true);  // runs after the doorbell wait
       a->app_run(c);
       a->push_responses();
     }
