@@ -111,6 +111,16 @@ static int d_device_count() {
   if (cudaGetDeviceCount(&n) != cudaSuccess) return 0;
   return n;
 }
+__global__ void timer_probe_kernel(volatile unsigned long long* out);
+struct TimerProbe;
+static TimerProbe* timer_probe_for(int dev);
+static void preload_own_kernels() {
+  cudaFuncAttributes fa;
+  (void)cudaFuncGetAttributes(&fa, timer_probe_kernel);
+  int dev = 0;
+  if (cudaGetDevice(&dev) == cudaSuccess) (void)timer_probe_for(dev);
+  (void)cudaGetLastError();
+}
 static int d_set_device(int dev) {
   RT(cudaSetDevice(dev));
   return 0;
@@ -118,6 +128,7 @@ static int d_set_device(int dev) {
 static int d_stream_create(int dev, cudaStream_t* s) {
   RT(cudaSetDevice(dev));
   sg_preload_kernels();  // every GPU app context passes here before its stream can be armed on a doorbell
+  preload_own_kernels();
   RT(cudaStreamCreateWithFlags(s, cudaStreamNonBlocking));
   return 0;
 }
@@ -326,47 +337,61 @@ __global__ void timer_probe_kernel(volatile unsigned long long* out) {
   *out = t;
   __threadfence_system();
 }
+// The probe's mapped word and stream are made once per device, when the device's first app context is set up:
+// allocating or freeing pinned memory synchronises the device, and a device whose work stream is parked on a doorbell
+// (or that runs a collective that waits for the very process that asked for this measurement) never gets there.
+struct TimerProbe {
+  volatile unsigned long long* w = nullptr;
+  unsigned long long* dw = nullptr;
+  cudaStream_t s = nullptr;
+};
+static TimerProbe* timer_probe_for(int dev) {
+  static std::mutex mu;
+  static TimerProbe probes[64];
+  if (dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> g(mu);
+  TimerProbe& p = probes[dev];
+  if (!p.w) {
+    void* h = nullptr;
+    if (cudaHostAlloc(&h, 64, cudaHostAllocMapped) != cudaSuccess) return nullptr;
+    if (cudaHostGetDevicePointer((void**)&p.dw, h, 0) != cudaSuccess || cudaStreamCreateWithFlags(&p.s, cudaStreamNonBlocking) != cudaSuccess) {
+      cudaFreeHost(h);
+      return nullptr;
+    }
+    p.w = (volatile unsigned long long*)h;
+  }
+  return &p;
+}
 static int d_timer_offset_ns(int dev, int64_t* offset) {
   int prev = 0;
   RT(cudaGetDevice(&prev));
   RT(cudaSetDevice(dev));
-  volatile unsigned long long* w = nullptr;
-  cudaError_t e = cudaHostAlloc((void**)&w, 64, cudaHostAllocMapped);
-  if (e != cudaSuccess) {
-    cudaSetDevice(prev);
-    RT(e);
-  }
-  unsigned long long* dw = nullptr;
-  cudaStream_t s = nullptr;
-  int rc = 0;
-  if (cudaHostGetDevicePointer((void**)&dw, (void*)w, 0) != cudaSuccess || cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking) != cudaSuccess) rc = -1;
+  TimerProbe* p = timer_probe_for(dev);
+  int rc = p ? 0 : -1;
   int64_t best = 0;
   uint64_t best_wait = ~0ull;
   for (int i = 0; rc == 0 && i < 6; i++) {
-    *w = 0;
+    *p->w = 0;
     const uint64_t t0 = getCurNs();
-    timer_probe_kernel<<<1, 1, 0, s>>>(dw);
+    timer_probe_kernel<<<1, 1, 0, p->s>>>(p->dw);
     if (cudaGetLastError() != cudaSuccess) {
       rc = -1;
       break;
     }
     uint64_t t1 = t0;
-    while (*w == 0 && (t1 = getCurNs()) - t0 < 2000000000ull) {
+    while (*p->w == 0 && (t1 = getCurNs()) - t0 < 500000000ull) {
     }
-    if (*w == 0) {
+    if (*p->w == 0) {
       rc = -1;
       break;
     }
     t1 = getCurNs();
-    cudaStreamSynchronize(s);
-    // the first tries include the kernel's load; a short host wait means the stamp is fresh
+    // the first try includes start-up costs; a short host wait means the stamp is fresh
     if (i >= 1 && t1 - t0 < best_wait) {
       best_wait = t1 - t0;
-      best = (int64_t)*w - (int64_t)t1;
+      best = (int64_t)*p->w - (int64_t)t1;
     }
   }
-  if (s) cudaStreamDestroy(s);
-  cudaFreeHost((void*)w);
   cudaSetDevice(prev);
   if (rc != 0) {
     g_last_error = "timer_offset_ns: probe failed";

@@ -95,6 +95,13 @@ class NvlBatchedServer {
     AppRrPoolExport ex;
     if (!app_->app_rr_pool->rr_mem_pool->export_to(&ex, app_->req_size, app_->resp_size)) return refuse(-3);
     int out_fds[3] = {ex.req_fd, ex.resp_fd, ex.ctl_fd};
+    // Measured before the worker starts: once a work stream is parked on a doorbell nothing new may be loaded or run
+    // to completion on this GPU on the host's behalf.
+    rep.timer_offset_ns = 0;  // a CPU app stamps with the steady clock itself
+    if (app_->device_id >= 0) {
+      const SrpcDeviceOps* ops = srpc_cuda_ops();
+      if (ops && ops->timer_offset_ns) ops->timer_offset_ns(app_->device_id, &rep.timer_offset_ns);
+    }
     // The producer's transmit arena, if it sent one: responses are stored there by this side.
     uint64_t tx_base = 0, tx_bytes = 0;
     if (n_fds >= 1 && req.tx_arena.length > 0) {
@@ -123,11 +130,6 @@ class NvlBatchedServer {
     rep.resp_buf = {(uint64_t)(uintptr_t)app_->app_rr_pool->rr_mem_pool->get_resp_addr_range(), ex.resp_capacity, 1, 0};
     rep.ctl_buf = {(uint64_t)(uintptr_t)app_->app_rr_pool->rr_mem_pool->get_doorbells_host(), ex.ctl_bytes, 2, 0};
     rep.transform = transform_;
-    rep.timer_offset_ns = 0;  // a CPU app stamps with the steady clock itself
-    if (app_->device_id >= 0) {
-      const SrpcDeviceOps* ops = srpc_cuda_ops();
-      if (ops && ops->timer_offset_ns) ops->timer_offset_ns(app_->device_id, &rep.timer_offset_ns);
-    }
     bool ok = ch.send_msg(&rep, sizeof(rep), out_fds, 3);
     for (int f : out_fds) ::close(f);
     if (!ok) stop_worker();

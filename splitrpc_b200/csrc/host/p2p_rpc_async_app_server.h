@@ -171,6 +171,7 @@ class P2pRpcAppInfo {
     AppCtx* c = app_ctx;
     if (device_id < 0 || !c->param_block || c->launch_type == 3) return;  // resident kernels poll the mapped copies
     const SrpcDeviceOps* ops = srpc_require_cuda("parameter block");
+    ops->set_device(device_id);  // callers include threads that never touched this GPU (a control-socket thread)
     RespPushCtx ctx = *c->h_push;
     ctx.first_slot = (uint32_t)first_slot;
     uint64_t offs[APP_PARAM_INLINE_MAX];
