@@ -447,12 +447,25 @@ PYBIND11_MODULE(_C, m) {
           auto cli = std::make_shared<LoopbackPort>(make_malloc_arena(slot_bytes * n_slots),
                                                     make_malloc_arena(slot_bytes * n_slots), slot_bytes);
           LoopbackPort::connect(srv.get(), cli.get());
+          // Buffers that the client fills and hands over by reference are made of the same kind of memory as the
+          // server's receive arena (so a shared arena comes with shared by-reference buffers).
+          if (server_mem != "malloc") srv->set_region_factory([server_mem](size_t bytes) { return make_arena(server_mem, bytes); });
           // Each port keeps the other alive, since it delivers into its arenas.
           auto both = std::make_shared<std::pair<std::shared_ptr<LoopbackPort>, std::shared_ptr<LoopbackPort>>>(srv, cli);
           PortHolder s{srv.get(), both}, c{cli.get(), both};
           return py::make_tuple(s, c);
         },
         py::arg("slot_bytes"), py::arg("n_slots") = 4096, py::arg("server_mem") = "malloc");
+  // A buffer of the receiving port's kind of memory that the sender fills and hands over by reference: returns
+  // (host address, device address, bytes, index among the receiving port's payload regions).
+  m.def("alloc_dma_region", [](PortHolder& sender, size_t bytes) {
+    DmaRegion r;
+    if (!sender.port->alloc_dma_region(bytes, &r)) throw std::runtime_error("this port has no shareable by-reference memory");
+    auto* lp = dynamic_cast<LoopbackPort*>(sender.port);
+    DmaRegion all[NVL_MAX_REGIONS];
+    int n = lp && lp->peer() ? lp->peer()->dma_regions(all, NVL_MAX_REGIONS) : 0;
+    return py::make_tuple((uintptr_t)r.host_base, (uintptr_t)r.dev_base, (size_t)r.bytes, n - 1);
+  });
   m.def("set_loopback_faults",
         [](PortHolder& p, double drop, double dup, double reorder, double truncate, bool zero_token, int force_seq,
            uint64_t seed) {
@@ -673,12 +686,13 @@ PYBIND11_MODULE(_C, m) {
       // mapping), maps the replica's rings and doorbells, and creates the engine that fills them from
       // `ingress_device` (-1: CPU engine, rings in host memory only).
       .def("add_remote_replica",
-           [](ServerHolder& s, const std::string& path, uint32_t func_id, int ingress_device, int copy_type, int timeout_ms) {
+           [](ServerHolder& s, const std::string& path, uint32_t func_id, int ingress_device, int copy_type, int timeout_ms, bool pull) {
              std::string err;
              std::unique_ptr<NvlRemoteReplica> r;
              {
                py::gil_scoped_release rel;
-               r = NvlRemoteReplica::connect(path, func_id, ingress_device, copy_type, s.server->tx_arena(), timeout_ms, &err);
+               r = NvlRemoteReplica::connect(path, func_id, ingress_device, copy_type, s.server->tx_arena(), timeout_ms, &err,
+                                             pull ? s.server->port() : nullptr);
              }
              if (!r) throw std::runtime_error("add_remote_replica: " + err);
              int idx = s.server->add_remote_replica(r.get());
@@ -686,7 +700,7 @@ PYBIND11_MODULE(_C, m) {
              return idx;
            },
            py::arg("path"), py::arg("func_id") = 1234, py::arg("ingress_device") = -1, py::arg("copy_type") = 2,
-           py::arg("timeout_ms") = 10000)
+           py::arg("timeout_ms") = 10000, py::arg("pull") = false)
       // Transmit arena of the server's port: (host base, device base, bytes, slot bytes).
       .def_property_readonly("tx_arena", [](ServerHolder& s) -> py::tuple {
         const TxArenaInfo* t = s.server->tx_arena();
@@ -728,6 +742,7 @@ PYBIND11_MODULE(_C, m) {
              d["max_batch"] = i.max_batch;
              d["device_completes"] = i.device_completes;
              d["transform_kind"] = i.transform.kind;
+             d["pull"] = i.pull;
              d["timer_offset_ns"] = i.timer_offset_ns;
              d["stamp_skew_ns"] = s.remotes.at((size_t)remote_idx)->stamp_skew_ns();
              return d;
@@ -794,6 +809,7 @@ PYBIND11_MODULE(_C, m) {
                throw std::runtime_error("BatchedServer: this app's rings cannot be shared with another process");
              h->app = app;
              h->server.reset(new NvlBatchedServer(app->info.get(), path, func_id, server_mode, max_batch));
+             h->server->set_pull_engine(app->engine.get());  // a producer may ask this side to fetch requests itself
              return h;
            }),
            py::arg("app"), py::arg("path"), py::arg("func_id") = 1234, py::arg("server_mode") = 2, py::arg("max_batch") = 1)
@@ -802,7 +818,25 @@ PYBIND11_MODULE(_C, m) {
              if (mean.size() != 3 || inv_std.size() != 3) throw std::invalid_argument("mean / inv_std need 3 values");
              float p[6] = {mean[0], mean[1], mean[2], inv_std[0], inv_std[1], inv_std[2]};
              b.server->set_ingress_transform(SG_TRANSFORM_STEM_S2D, p);
+             // and on this side's own engine, which does the gathers when the producer only describes requests
+             auto* mp = b.app->info->app_rr_pool->rr_mem_pool;
+             b.app->engine->set_gather_transform(SG_TRANSFORM_STEM_S2D, (uint64_t)(uintptr_t)mp->get_req_addr_range(),
+                                                 (uint32_t)b.app->info->req_size, p);
            })
+      .def_property_readonly("pulling", [](BatchedServerHolder& b) { return b.server->pulling(); })
+      .def("pull_stats", [](BatchedServerHolder& b) {
+        py::dict d;
+        d["pulled"] = b.server->pulled();
+        d["errors"] = b.server->pull_errors();
+        return d;
+      })
+      // (base, bytes) of the producer's payload regions as this side's device addresses them (pull mode).
+      .def("regions", [](BatchedServerHolder& b) {
+        py::list l;
+        uint64_t base = 0, bytes = 0;
+        for (int i = 0; b.server->region(i, &base, &bytes); i++) l.append(py::make_tuple((uintptr_t)base, (size_t)bytes));
+        return l;
+      })
       .def("start", [](BatchedServerHolder& b) {
         if (!b.server->start()) throw std::runtime_error("BatchedServer: cannot listen on the control socket path");
       })

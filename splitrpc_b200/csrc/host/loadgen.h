@@ -333,7 +333,12 @@ class P2pRpcAppClient {
   void PreProcessRequests() {
     payloads_.resize((size_t)cfg_.n_payloads);
     payload_ptrs_.resize((size_t)cfg_.n_payloads);
-    if (cfg_.send_by_reference) {
+    DmaRegion region;
+    if (cfg_.send_by_reference && port_->alloc_dma_region(((cfg_.req_size + 255) / 256 * 256) * (size_t)cfg_.n_payloads, &region)) {
+      // memory of the receiving port: it can share it with the processes that serve its requests
+      size_t stride = (cfg_.req_size + 255) / 256 * 256;
+      for (int i = 0; i < cfg_.n_payloads; i++) payload_ptrs_[i] = region.host_base + (size_t)i * stride;
+    } else if (cfg_.send_by_reference) {
       const SrpcDeviceOps* ops = srpc_cuda_ops();
       void *h = nullptr, *d = nullptr;
       size_t stride = (cfg_.req_size + 255) / 256 * 256;

@@ -22,6 +22,8 @@
 // flow steering skips it.  No GPU is involved in detecting either.
 #pragma once
 
+#include <deque>
+#include <functional>
 #include <thread>
 
 #include "nvl_transport_common.h"
@@ -46,6 +48,80 @@ class NvlBatchedServer {
   std::atomic<bool> quit_{false};
   std::atomic<bool> serving_{false};
   SrpcSharedMem tx_arena_{};
+  // Pull mode: the producer's payload regions as this process maps them, the engine that fetches from them (this
+  // app's own scatter-gather engine) and the thread that turns described slots into gathers.
+  P2pRpcSgEngine* pull_engine_ = nullptr;
+  SrpcSharedMem regions_[NVL_MAX_REGIONS];
+  std::atomic<int> n_regions_{0};  // entries below it never change while the fetch thread runs
+  std::thread puller_;
+  std::atomic<bool> pull_quit_{false};
+  bool pull_ = false;
+  std::atomic<uint64_t> pulled_{0}, pull_errors_{0};
+
+  // Fetch thread: takes described slots in ring order, builds their copy lists from the descriptors and hands them
+  // to the engine, whose kernel (or memcpy) marks each slot RX_COMPLETE when its bytes are in the ring.
+  void pull_loop() {
+    P2pRpcAppRrPool* pool = app_->app_rr_pool;
+    P2pRpcAppRrMemPool* mp = pool->rr_mem_pool;
+    const int n = pool->get_pool_size();
+    const int burst = max_batch_ > 0 ? max_batch_ : 1;
+    const bool gpu = app_->device_id >= 0;
+    if (gpu) srpc_require_cuda("pull thread")->set_device(app_->device_id);
+    std::vector<std::unique_ptr<P2pRpcRr>> rr((size_t)n);
+    for (auto& r : rr) r.reset(new P2pRpcRr(nullptr, app_->req_size));
+    std::vector<g_params> stubs((size_t)n);
+    std::vector<P2pRpcRr*> rp((size_t)burst);
+    std::vector<g_params*> sp((size_t)burst);
+    std::vector<volatile uint32_t*> hs((size_t)burst), ds((size_t)burst);
+    int pi = 0;
+    uint64_t seq = 0;
+    IdleBackoff backoff;
+    while (!pull_quit_.load(std::memory_order_acquire)) {
+      int k = 0;
+      while (k < burst && __atomic_load_n(pool->get_app_rr((pi + k) % n)->h_state, __ATOMIC_ACQUIRE) == (uint32_t)APP_RR_STATUS::RX_DESCRIBED) k++;
+      if (k == 0) {
+        backoff.empty();
+        continue;
+      }
+      backoff.busy();
+      bool ok = true;
+      for (int j = 0; j < k; j++) {
+        const int slot = (pi + j) % n;
+        const SrpcSlotDesc* d = mp->get_slot_desc(slot);
+        P2pRpcRr* r = rr[(size_t)slot].get();
+        r->clear_bufs();
+        const uint32_t nf = d->n_frags;
+        if (nf == 0 || nf > mp->desc_per_slot() || nf > MAX_BI_SIZE) ok = false;
+        for (uint32_t f = 0; ok && f < nf; f++) {
+          const uint32_t region = (uint32_t)(d->frag[f].where >> 56);
+          const uint64_t off = d->frag[f].where & ((1ull << 56) - 1);
+          if (region >= (uint32_t)n_regions_.load(std::memory_order_acquire) || off + d->frag[f].len > regions_[region].bytes) {
+            ok = false;
+            break;
+          }
+          const uint8_t* base = (const uint8_t*)(gpu ? regions_[region].dev : regions_[region].host);
+          r->payload_bufs->burst_items[f] = (uintptr_t)(base + off);
+          r->payload_bufs->item_size[f] = d->frag[f].len;
+        }
+        r->payload_bufs->num_items = ok ? (uint16_t)nf : 0;
+        stubs[(size_t)slot] = pool->window_stub(seq + (uint64_t)j);
+        rp[(size_t)j] = r;
+        sp[(size_t)j] = &stubs[(size_t)slot];
+        hs[(size_t)j] = pool->get_app_rr(slot)->h_state;
+        ds[(size_t)j] = pool->get_app_rr(slot)->d_state;
+      }
+      int64_t ticket = ok ? pull_engine_->gather_batch_notify(rp.data(), sp.data(), hs.data(), ds.data(), k, (uint32_t)APP_RR_STATUS::RX_COMPLETE) : -1;
+      if (ticket < 0) {
+        // Hand the slots on anyway (the app answers with whatever the ring holds) rather than stall the ring.
+        pull_errors_++;
+        srpc_log(SRPC_LOG_ERROR, "pull: could not fetch %d described request(s)", k);
+        for (int j = 0; j < k; j++) __atomic_store_n(hs[(size_t)j], (uint32_t)APP_RR_STATUS::RX_COMPLETE, __ATOMIC_RELEASE);
+      }
+      pulled_ += (uint64_t)k;
+      pi = (pi + k) % n;
+      seq += (uint64_t)k;
+    }
+  }
 
   void start_worker() {
     P2pRpcAppRrPool* pool = app_->app_rr_pool;
@@ -61,6 +137,12 @@ class NvlBatchedServer {
     app_->app_ctx->next_batch_size = max_batch_;
     app_server_.reset_quit();
     serving_.store(true);
+    if (pull_) {
+      P2pRpcAppRrMemPool* mp = pool->rr_mem_pool;
+      pull_engine_->set_stamp_layout(mp->get_doorbells_host(), mp->get_stamps_host(), mp->get_doorbells_device(), mp->get_stamps_device());
+      pull_quit_.store(false);
+      puller_ = std::thread([this] { pull_loop(); });
+    }
     if (server_mode_ < 0) return;  // the embedder runs the app itself (timing loops, tests)
     worker_ = std::thread([this] {
       switch (server_mode_) {
@@ -72,11 +154,26 @@ class NvlBatchedServer {
   }
   void stop_worker() {
     if (!serving_.exchange(false)) return;
+    pull_quit_.store(true, std::memory_order_release);
+    if (puller_.joinable()) puller_.join();
     app_server_.quit();
     if (worker_.joinable()) worker_.join();
     app_->disable_device_completion();
     app_->use_window_stub = false;
     srpc_shm_free(&tx_arena_);
+    for (int i = 0; i < n_regions_.load(); i++) srpc_shm_free(&regions_[i]);
+    n_regions_.store(0);
+    pull_ = false;
+  }
+  bool add_region(int fd, uint64_t bytes) {
+    const int at = n_regions_.load();
+    if (at >= NVL_MAX_REGIONS) return false;
+    if (app_->device_id >= 0) srpc_require_cuda("pull regions")->set_device(app_->device_id);
+    SrpcSharedMem m;
+    if (!srpc_shm_import(fd, bytes, app_->device_id >= 0, &m)) return false;
+    regions_[at] = m;
+    n_regions_.store(at + 1, std::memory_order_release);
+    return true;
   }
 
   bool handle_alloc(NvlCtrlChannel& ch, const buf_mon_rr& req, int* fds, int n_fds) {
@@ -104,6 +201,7 @@ class NvlBatchedServer {
     }
     // The producer's transmit arena, if it sent one: responses are stored there by this side.
     uint64_t tx_base = 0, tx_bytes = 0;
+    int next_fd = 0;
     if (n_fds >= 1 && req.tx_arena.length > 0) {
       if (srpc_shm_import(fds[0], req.tx_arena.length, app_->device_id >= 0, &tx_arena_)) {
         tx_base = (uint64_t)(uintptr_t)tx_arena_.dev;
@@ -112,10 +210,29 @@ class NvlBatchedServer {
         ::close(fds[0]);
         srpc_log(SRPC_LOG_WARN, "batched server: could not map the producer's transmit arena; responses stay in the ring");
       }
-      for (int i = 1; i < n_fds; i++) ::close(fds[i]);
-    } else {
-      for (int i = 0; i < n_fds; i++) ::close(fds[i]);
+      next_fd = 1;
     }
+    // Pull mode: map the producer's payload regions (all of them, or the mode stays off).
+    pull_ = false;
+    if (req.pull && pull_engine_ && req.n_regions > 0 && req.n_regions <= (uint32_t)NVL_MAX_REGIONS && next_fd + (int)req.n_regions <= n_fds) {
+      bool ok = true;
+      for (uint32_t i = 0; i < req.n_regions; i++) {
+        if (!ok || !add_region(fds[next_fd], req.region_bytes[i])) {
+          ::close(fds[next_fd]);
+          ok = false;
+        }
+        next_fd++;
+      }
+      if (!ok) {
+        srpc_log(SRPC_LOG_WARN, "batched server: could not map the producer's payload regions; it will push instead");
+        for (int i = 0; i < n_regions_.load(); i++) srpc_shm_free(&regions_[i]);
+        n_regions_.store(0);
+      }
+      pull_ = ok;
+    }
+    for (int i = next_fd; i < n_fds; i++) ::close(fds[i]);
+    rep.pull = pull_ ? 1u : 0u;
+    rep.tx_arena.length = tx_bytes;  // 0: this side could not map the arena, responses stay in the response ring
     app_->enable_device_completion(tx_base, tx_bytes);
     start_worker();
     rep.status = 0;
@@ -140,8 +257,8 @@ class NvlBatchedServer {
   // Handles one message of the connected producer.  Returns false when the connection is over.
   bool serve_one(NvlCtrlChannel& ch) {
     buf_mon_rr msg{};
-    int fds[4], n_fds = 0;
-    int r = ch.recv_msg(&msg, sizeof(msg), fds, 4, &n_fds, 0);
+    int fds[NVL_MAX_FDS], n_fds = 0;
+    int r = ch.recv_msg(&msg, sizeof(msg), fds, NVL_MAX_FDS, &n_fds, 0);
     if (r == 0) return true;
     if (r < 0) {  // the producer went away (without RELEASE if it was still being served)
       if (serving_.load()) counters.peers_lost++;
@@ -157,6 +274,19 @@ class NvlBatchedServer {
       rep.func_id = func_id_;
       fill_stats(&rep);
       ch.send_msg(&rep, sizeof(rep));
+    } else if (msg.type == BUF_MON_REGION) {
+      buf_mon_rr rep{};
+      rep.type = BUF_MON_REGION;
+      rep.func_id = func_id_;
+      rep.status = -1;
+      if (pull_ && n_fds >= 1 && add_region(fds[0], msg.region_bytes[0])) {
+        rep.status = 0;
+        rep.n_regions = (uint32_t)n_regions_.load();
+        for (int i = 1; i < n_fds; i++) ::close(fds[i]);
+      } else {
+        for (int i = 0; i < n_fds; i++) ::close(fds[i]);
+      }
+      ch.send_msg(&rep, sizeof(rep));
     } else if (msg.type == BUF_MON_STATS) {
       buf_mon_rr rep{};
       rep.type = BUF_MON_STATS;
@@ -170,8 +300,8 @@ class NvlBatchedServer {
   void refuse_connection(int fd) {
     NvlCtrlChannel ch(fd);
     buf_mon_rr msg{};
-    int fds[4], n_fds = 0;
-    if (ch.recv_msg(&msg, sizeof(msg), fds, 4, &n_fds, 200) == 1) {
+    int fds[NVL_MAX_FDS], n_fds = 0;
+    if (ch.recv_msg(&msg, sizeof(msg), fds, NVL_MAX_FDS, &n_fds, 200) == 1) {
       for (int i = 0; i < n_fds; i++) ::close(fds[i]);
       buf_mon_rr rep{};
       rep.type = msg.type;
@@ -215,6 +345,20 @@ class NvlBatchedServer {
   }
   ~NvlBatchedServer() { stop(); }
 
+  // Engine that fetches described requests (pull mode): normally the app's own scatter-gather engine, with the
+  // ingress transform, if any, already set on it.  Without one the server only accepts pushed requests.
+  void set_pull_engine(P2pRpcSgEngine* e) { pull_engine_ = e; }
+  bool pulling() const { return pull_; }
+  uint64_t pulled() const { return pulled_.load(); }
+  uint64_t pull_errors() const { return pull_errors_.load(); }
+  // Device-side (host-side on the CPU device) base address and size of the producer's i-th payload region.
+  bool region(int i, uint64_t* base, uint64_t* bytes) const {
+    if (i < 0 || i >= n_regions_.load(std::memory_order_acquire)) return false;
+    *base = (uint64_t)(uintptr_t)(app_->device_id >= 0 ? regions_[i].dev : regions_[i].host);
+    *bytes = regions_[i].bytes;
+    return true;
+  }
+
   // Producers must deserialise into this app's request ring with this transform (see SG_TRANSFORM_*).
   void set_ingress_transform(uint32_t kind, const float* params6) {
     transform_.kind = kind;
@@ -242,13 +386,133 @@ class NvlBatchedServer {
   WorkerStats worker_stats() { return app_server_.stats(app_idx_); }
 };
 
+// Ingress side of pull mode: a "gather" only writes where the request's fragments are into the slot's descriptor
+// block and marks the slot RX_DESCRIBED; the serving side moves the bytes.  A ticket is done when the serving side has
+// taken all its requests out of the regions (their slots have left RX_DESCRIBED), which is when the receive buffers can
+// be reused.  Responses that the serving side did not push are fetched by `fetch` (the engine that maps the rings).
+class P2pRpcSgDescribeEngine : public P2pRpcSgEngine {
+  P2pRpcAppRrMemPool* mp_;
+  std::vector<DmaRegion> regions_;
+  P2pRpcSgEngine* fetch_;
+  bool dev_addr_;  // fragment addresses arrive as the ingress GPU sees them (otherwise as the host does)
+  struct Pending {
+    int64_t ticket;
+    std::vector<uint32_t> slots;
+  };
+  std::deque<Pending> pending_;
+  int64_t ticket_ = 0;
+  std::vector<SrpcFragDesc> tmp_;
+  // Regions can appear after the handshake (a sender's by-reference buffer): `list_` re-reads the port's regions,
+  // `announce_` shares a new one with the serving side.
+  std::function<int(DmaRegion*, int)> list_;
+  std::function<bool(const DmaRegion&)> announce_;
+
+  bool refresh_regions() {
+    if (!list_ || !announce_) return false;
+    DmaRegion all[NVL_MAX_REGIONS];
+    const int n = list_(all, NVL_MAX_REGIONS);
+    bool grew = false;
+    for (int i = (int)regions_.size(); i < n; i++) {
+      if (all[i].fd < 0 || !announce_(all[i])) return grew;
+      regions_.push_back(all[i]);
+      grew = true;
+    }
+    return grew;
+  }
+  bool locate(uintptr_t addr, size_t len, uint64_t* where) {
+    return locate_known(addr, len, where) || (refresh_regions() && locate_known(addr, len, where));
+  }
+  bool locate_known(uintptr_t addr, size_t len, uint64_t* where) const {
+    for (size_t r = 0; r < regions_.size(); r++) {
+      const uintptr_t base = (uintptr_t)(dev_addr_ ? regions_[r].dev_base : regions_[r].host_base);
+      if (addr >= base && addr + len <= base + regions_[r].bytes) {
+        *where = ((uint64_t)r << 56) | (uint64_t)(addr - base);
+        return true;
+      }
+    }
+    return false;
+  }
+
+ public:
+  P2pRpcSgDescribeEngine(P2pRpcAppRrMemPool* mp, const DmaRegion* regions, int n_regions, P2pRpcSgEngine* fetch, bool dev_addr)
+      : mp_(mp), regions_(regions, regions + n_regions), fetch_(fetch), dev_addr_(dev_addr) {}
+  void set_region_source(std::function<int(DmaRegion*, int)> list, std::function<bool(const DmaRegion&)> announce) {
+    list_ = std::move(list);
+    announce_ = std::move(announce);
+  }
+  const char* name() const override { return "describe"; }
+  int gather(P2pRpcRr*, g_params*) override { return -1; }  // only the notifying batch form exists
+  int scatter(P2pRpcRr* rr, g_params* stub) override { return fetch_ ? fetch_->scatter(rr, stub) : -1; }
+  int scatter_batch(P2pRpcRr** rrs, g_params** stubs, int n) override { return fetch_ ? fetch_->scatter_batch(rrs, stubs, n) : -1; }
+  int copy_list(const p2p_sk_buf* skb) override { return fetch_ ? fetch_->copy_list(skb) : -1; }
+
+  int64_t gather_batch_notify(P2pRpcRr** rrs, g_params** stubs, volatile uint32_t** h_states, volatile uint32_t** d_states, int n,
+                              uint32_t state_value) override {
+    (void)stubs;
+    (void)d_states;
+    (void)state_value;
+    const uint32_t cap = mp_->desc_per_slot();
+    volatile uint32_t* base = mp_->get_doorbells_host();
+    Pending pend;
+    for (int i = 0; i < n; i++) {
+      const p2p_bufs* fr = rrs[i]->payload_bufs;
+      tmp_.clear();
+      uintptr_t run_end = 0;
+      uint32_t dst = 0;
+      for (size_t f = 0; f < fr->num_items; f++) {
+        const uintptr_t src = fr->burst_items[f];
+        const size_t len = fr->item_size[f];
+        if (!tmp_.empty() && src == run_end && (uint64_t)tmp_.back().len + len <= 0xFFFFFFFFull) {
+          tmp_.back().len += (uint32_t)len;  // still inside one region: the run started there and is contiguous
+        } else {
+          SrpcFragDesc d{0, (uint32_t)len, dst};
+          if (!locate(src, len, &d.where)) {
+            srpc_log(SRPC_LOG_ERROR, "describe: a fragment lies outside the shared regions");
+            return -5;
+          }
+          tmp_.push_back(d);
+        }
+        run_end = src + len;
+        dst += (uint32_t)len;
+      }
+      // a merged run must not leave its region
+      for (const SrpcFragDesc& d : tmp_) {
+        const uint32_t r = (uint32_t)(d.where >> 56);
+        if ((d.where & ((1ull << 56) - 1)) + d.len > regions_[r].bytes) return -5;
+      }
+      if (tmp_.empty() || tmp_.size() > cap) return -4;
+      const uint32_t slot = (uint32_t)(h_states[i] - base);
+      SrpcSlotDesc* sd = mp_->get_slot_desc((int)slot);
+      for (size_t k = 0; k < tmp_.size(); k++) sd->frag[k] = tmp_[k];
+      sd->n_frags = (uint32_t)tmp_.size();
+      pend.slots.push_back(slot);
+    }
+    std::atomic_thread_fence(std::memory_order_release);
+    for (int i = 0; i < n; i++) __atomic_store_n(h_states[i], (uint32_t)APP_RR_STATUS::RX_DESCRIBED, __ATOMIC_RELEASE);
+    pend.ticket = ++ticket_;
+    pending_.push_back(std::move(pend));
+    counters.gathers += (uint64_t)n;
+    return ticket_;
+  }
+  bool ticket_done(int64_t ticket) override {
+    volatile uint32_t* base = mp_->get_doorbells_host();
+    while (!pending_.empty() && pending_.front().ticket <= ticket) {
+      for (uint32_t s : pending_.front().slots)
+        if (__atomic_load_n(base + s, __ATOMIC_ACQUIRE) == (uint32_t)APP_RR_STATUS::RX_DESCRIBED) return false;
+      pending_.pop_front();
+    }
+    return true;
+  }
+};
+
 // GPU engine factory of the CUDA half (null without CUDA).
 extern "C" P2pRpcSgEngine* srpc_make_gpu_sg_engine(int device_id, int copy_type);
 
 class NvlRemoteReplica {
   NvlCtrlChannel ch_;
   std::unique_ptr<P2pRpcAppRrPool> pool_;
-  std::unique_ptr<P2pRpcSgEngine> engine_;
+  std::unique_ptr<P2pRpcSgEngine> engine_;           // what the server's shunter drives
+  std::unique_ptr<P2pRpcSgEngine> fetch_engine_;     // pull mode: the engine that maps the rings (response fetches)
   buf_mon_rr info_{};
   int64_t stamp_skew_ns_ = 0;
   std::mutex mu_;
@@ -258,7 +522,11 @@ class NvlRemoteReplica {
   // whose kernels will fill the rings (-1: the CPU engine; only for rings in host memory).  `tx`: this process's
   // transmit arena (may be null or unshareable: responses then stay in the response ring and are fetched from there).
   static std::unique_ptr<NvlRemoteReplica> connect(const std::string& path, uint32_t func_id, int ingress_device, int copy_type,
-                                                   const TxArenaInfo* tx, int timeout_ms, std::string* err) {
+                                                   const TxArenaInfo* tx, int timeout_ms, std::string* err,
+                                                   const Transport* pull_from = nullptr) {
+    // Pull mode: `pull_from` is the port whose received payloads the server should fetch by itself.
+    DmaRegion regions[NVL_MAX_REGIONS];
+    const int n_regions = pull_from ? pull_from->dma_regions(regions, NVL_MAX_REGIONS) : 0;
     auto fail = [&](const std::string& m) {
       if (err) *err = m;
       return std::unique_ptr<NvlRemoteReplica>();
@@ -276,9 +544,22 @@ class NvlRemoteReplica {
       tx_fd = tx->fd;
       req.tx_arena = {(uint64_t)(uintptr_t)tx->host_base, tx->bytes, 0, 0};
     }
-    if (!r->ch_.send_msg(&req, sizeof(req), tx_fd >= 0 ? &tx_fd : nullptr, tx_fd >= 0 ? 1 : 0)) return fail("ALLOC send failed");
-    int fds[4], n_fds = 0;
-    if (r->ch_.recv_msg(&r->info_, sizeof(r->info_), fds, 4, &n_fds, timeout_ms) != 1) return fail("no ALLOC reply");
+    // Pull mode is asked for when every region can be mapped by another process.
+    int out_fds[NVL_MAX_FDS], n_out = 0;
+    if (tx_fd >= 0) out_fds[n_out++] = tx_fd;
+    bool want_pull = n_regions > 0 && n_regions <= NVL_MAX_REGIONS;
+    for (int i = 0; want_pull && i < n_regions; i++) want_pull = regions[i].fd >= 0 && regions[i].bytes > 0;
+    if (want_pull) {
+      req.pull = 1;
+      req.n_regions = (uint32_t)n_regions;
+      for (int i = 0; i < n_regions; i++) {
+        req.region_bytes[i] = regions[i].bytes;
+        out_fds[n_out++] = regions[i].fd;
+      }
+    }
+    if (!r->ch_.send_msg(&req, sizeof(req), n_out ? out_fds : nullptr, n_out)) return fail("ALLOC send failed");
+    int fds[NVL_MAX_FDS], n_fds = 0;
+    if (r->ch_.recv_msg(&r->info_, sizeof(r->info_), fds, NVL_MAX_FDS, &n_fds, timeout_ms) != 1) return fail("no ALLOC reply");
     if (r->info_.status != 0 || n_fds != 3) {
       for (int i = 0; i < n_fds; i++) ::close(fds[i]);
       return fail("ALLOC refused, status " + std::to_string(r->info_.status));
@@ -320,6 +601,16 @@ class NvlRemoteReplica {
       if (ops && ops->timer_offset_ns) ops->timer_offset_ns(dev, &ingress_offset);
     }
     r->stamp_skew_ns_ = r->info_.timer_offset_ns - ingress_offset;
+    if (r->info_.pull) {
+      // The server fetches by itself: the shunter only describes.  Both stamps then come from the serving device.
+      r->fetch_engine_ = std::move(r->engine_);
+      auto* de = new P2pRpcSgDescribeEngine(r->pool_->rr_mem_pool, regions, n_regions, r->fetch_engine_.get(), ingress_device >= 0);
+      NvlRemoteReplica* self = r.get();
+      de->set_region_source([pull_from](DmaRegion* out, int max) { return pull_from->dma_regions(out, max); },
+                            [self](const DmaRegion& reg) { return self->add_region(reg); });
+      r->engine_.reset(de);
+      r->stamp_skew_ns_ = 0;
+    }
     return r;
   }
   // (completion stamp - doorbell stamp) exceeds the true latency by this much: the two stamps come from different
@@ -330,6 +621,9 @@ class NvlRemoteReplica {
   P2pRpcSgEngine* engine() { return engine_.get(); }
   const buf_mon_rr& info() const { return info_; }
   bool device_completes() const { return info_.device_completes != 0; }
+  bool pulls() const { return info_.pull != 0; }
+  // The serving side stores single-fragment responses straight into this process's transmit arena.
+  bool pushes_responses() const { return info_.device_completes != 0 && info_.tx_arena.length > 0; }
 
   // false once the server has closed the control connection (it exited or was killed).
   bool alive() {
@@ -351,6 +645,19 @@ class NvlRemoteReplica {
     *served = m.stat_served;
     *batches = m.stat_batches;
     return true;
+  }
+  // Shares one more payload region with the server (pull mode).
+  bool add_region(const DmaRegion& reg, int timeout_ms = 3000) {
+    std::lock_guard<std::mutex> g(mu_);
+    if (!ch_.ok() || reg.fd < 0) return false;
+    buf_mon_rr m{};
+    m.type = BUF_MON_REGION;
+    m.func_id = info_.func_id;
+    m.n_regions = 1;
+    m.region_bytes[0] = reg.bytes;
+    int fd = reg.fd;
+    if (!ch_.send_msg(&m, sizeof(m), &fd, 1)) return false;
+    return ch_.recv_msg(&m, sizeof(m), nullptr, 0, nullptr, timeout_ms) == 1 && m.type == BUF_MON_REGION && m.status == 0;
   }
   // Tells the server to stop its worker and forget this producer.
   bool release(int timeout_ms = 3000) {

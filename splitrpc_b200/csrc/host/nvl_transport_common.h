@@ -22,7 +22,9 @@
 
 #include "p2p_rpc_app.h"
 
-enum buf_mon_type : uint32_t { BUF_MON_ALLOC = 1, BUF_MON_RELEASE = 2, BUF_MON_STATS = 3 };
+// BUF_MON_REGION: one more payload region of a producer that is already being served in pull mode (its descriptor
+// travels with the message, its size in region_bytes[0]); the reply carries status 0 and the region's index.
+enum buf_mon_type : uint32_t { BUF_MON_ALLOC = 1, BUF_MON_RELEASE = 2, BUF_MON_STATS = 3, BUF_MON_REGION = 4 };
 enum req_mon_type : uint32_t { REQ_MON_COMPLETE = 1 };
 
 // One shareable region.  `stag` is the position of its descriptor among the descriptors that travel with the message
@@ -44,6 +46,8 @@ struct nvl_ingress_transform {
 // ALLOC request: proxy -> server.  Carries the proxy's transmit arena (descriptor 0) when responses are to be stored
 // there by the serving GPU.  ALLOC reply: server -> proxy with the three regions of the app's slot ring (descriptors
 // 0..2 = request ring, response ring, control block).
+static constexpr int NVL_MAX_REGIONS = 8;
+static constexpr int NVL_MAX_FDS = 12;
 struct buf_mon_rr {
   uint32_t type = 0;
   uint32_t func_id = 0;
@@ -59,6 +63,13 @@ struct buf_mon_rr {
   nvl_ingress_transform transform;             // reply
   uint64_t stat_served = 0, stat_batches = 0;  // BUF_MON_STATS reply
   int64_t timer_offset_ns = 0;  // reply: the serving device's stamp timer minus the machine's steady clock
+  // Pull mode.  Request: pull = 1 and the host memory regions in which the producer's received payloads lie (their
+  // descriptors follow the transmit arena's in the message); the producer will only DESCRIBE requests (fragment list
+  // in the slot's descriptor block, state RX_DESCRIBED) and the serving side fetches the bytes over its own link to
+  // host memory.  Reply: pull = 1 when the server mapped the regions and runs a fetch thread; 0 = push as usual.
+  uint32_t pull = 0;
+  uint32_t n_regions = 0;
+  uint64_t region_bytes[NVL_MAX_REGIONS] = {};
 };
 
 // Per-request notification (host path, kept for parity with the original's SEND_WITH_IMM of a slot index; the

@@ -48,7 +48,28 @@ static constexpr uint32_t APP_DOORBELL_RUN_DONE = 1u;   // written from the stre
 static constexpr uint32_t APP_DOORBELL_PT_DONE = 2u;    // written by a resident kernel after a batch
 static constexpr uint32_t APP_DOORBELL_EXIT = 3u;       // asks a resident kernel to leave
 
-enum APP_RR_STATUS : uint32_t { FREE = 0, RX_COMPLETE = 1, WORK_COMPLETE = 2, TX_COMPLETE = 3 };
+// RX_DESCRIBED: the slot's request has not been moved yet; its fragment list sits in the slot's descriptor block and
+// the serving side fetches the bytes itself (over its own link to host memory), then marks the slot RX_COMPLETE.
+enum APP_RR_STATUS : uint32_t { FREE = 0, RX_COMPLETE = 1, WORK_COMPLETE = 2, TX_COMPLETE = 3, RX_DESCRIBED = 4 };
+
+// Where the fragments of a described request are: `where` = region index << 56 | byte offset inside that region (the
+// regions are the host memory ranges that the producer shared at ALLOC time: its receive arena and the buffers that
+// senders hand over by reference); the bytes go to request offset dst_off.
+struct SrpcFragDesc {
+  uint64_t where;
+  uint32_t len;
+  uint32_t dst_off;
+};
+struct SrpcSlotDesc {
+  uint32_t n_frags;
+  uint32_t pad_[3];
+  SrpcFragDesc frag[1];  // desc_per_slot entries follow
+};
+static inline uint32_t srpc_desc_per_slot(size_t req_size) {
+  size_t n = req_size / 1024 + 3;
+  return (uint32_t)(n > 1024 ? 1024 : n);
+}
+static inline size_t srpc_desc_stride(size_t req_size) { return 16 + (size_t)srpc_desc_per_slot(req_size) * sizeof(SrpcFragDesc); }
 
 // What the serving side needs to answer a slot by itself: for the batch whose first slot is `first_slot`, request r
 // belongs to slot (first_slot + r) % pool_size; its response goes to tx_base + tx_off[slot] (unless tx_off is
@@ -333,17 +354,23 @@ class P2pRpcAppRrMemPool {
   size_t n_doorbells_ = 0;
   bool mirror_ = false;
   bool ctl_plain_ = false;  // control block from host_alloc_mapped / posix_memalign instead of a memfd
+  size_t req_size_ = 0;
+  uint8_t* h_desc_ = nullptr;  // per slot: SrpcSlotDesc (host view; only the hosts of both sides touch it)
 
-  static size_t ctl_layout(size_t n, size_t* tx_off_at, size_t* stamps_at = nullptr) {
+  // states | transmit offsets | stamps | fragment descriptors
+  static size_t ctl_layout(size_t n, size_t req_size, size_t* tx_off_at, size_t* stamps_at = nullptr, size_t* desc_at = nullptr) {
     size_t a = (n * sizeof(uint32_t) + 63) / 64 * 64;
     *tx_off_at = a;
     size_t b = a + n * sizeof(uint64_t);
     if (stamps_at) *stamps_at = b;
-    return b + 2 * n * sizeof(uint64_t);
+    size_t c = (b + 2 * n * sizeof(uint64_t) + 63) / 64 * 64;
+    if (desc_at) *desc_at = c;
+    return c + n * srpc_desc_stride(req_size);
   }
   void bind_ctl(void* h, void* d) {
-    size_t at = 0, st = 0;
-    ctl_layout(n_doorbells_, &at, &st);
+    size_t at = 0, st = 0, ds = 0;
+    ctl_layout(n_doorbells_, req_size_, &at, &st, &ds);
+    h_desc_ = (uint8_t*)h + ds;
     h_doorbells_ = (volatile uint32_t*)h;
     d_doorbells_ = (volatile uint32_t*)d;
     h_tx_off_ = (volatile uint64_t*)((uint8_t*)h + at);
@@ -356,9 +383,9 @@ class P2pRpcAppRrMemPool {
   static constexpr uint64_t kNoTxOffset = ~0ull;
 
   P2pRpcAppRrMemPool(int pool_size, int device_id, size_t req_size, size_t resp_size, bool peer_access = true)
-      : device_id_(device_id), n_doorbells_((size_t)pool_size) {
+      : device_id_(device_id), n_doorbells_((size_t)pool_size), req_size_(req_size) {
     size_t req_bytes = (size_t)pool_size * req_size, resp_bytes = (size_t)pool_size * resp_size;
-    size_t at = 0, ctl_bytes = ctl_layout(n_doorbells_, &at);
+    size_t at = 0, ctl_bytes = ctl_layout(n_doorbells_, req_size_, &at);
     if (device_id < 0) {
       if (!srpc_host_ring_alloc(req_bytes, req_size, &req_) || !srpc_host_ring_alloc(resp_bytes, resp_size, &resp_)) {
         srpc_log(SRPC_LOG_ERROR, "host ring allocation failed (%zu + %zu bytes)", req_bytes, resp_bytes);
@@ -393,8 +420,20 @@ class P2pRpcAppRrMemPool {
 
   // Mirror of a pool owned by another process.  `device_id` is the device whose kernels will write the rings (the
   // ingress GPU), or -1 when the CPU does.  Takes ownership of the descriptors in `ex`.
-  P2pRpcAppRrMemPool(const AppRrPoolExport& ex, int device_id) : device_id_(device_id), n_doorbells_(ex.pool_size), mirror_(true) {
+  P2pRpcAppRrMemPool(const AppRrPoolExport& ex, int device_id)
+      : device_id_(device_id), n_doorbells_(ex.pool_size), mirror_(true), req_size_(ex.req_size) {
     bool ok;
+    {
+      size_t at = 0;
+      if (ctl_layout(n_doorbells_, req_size_, &at) > ex.ctl_bytes) {  // the owner's mapping is rounded up to pages
+        srpc_log(SRPC_LOG_ERROR, "control block of a remote app is smaller than its layout");
+        ::close(ex.req_fd);
+        ::close(ex.resp_fd);
+        ::close(ex.ctl_fd);
+        n_doorbells_ = 0;
+        return;
+      }
+    }
     if (ex.owner_device < 0) {
       ok = srpc_host_ring_import(ex.req_fd, ex.req_capacity, &req_) && srpc_host_ring_import(ex.resp_fd, ex.resp_capacity, &resp_);
     } else {
@@ -466,6 +505,8 @@ class P2pRpcAppRrMemPool {
   bool is_double_mapped() const { return req_.double_mapped && resp_.double_mapped; }
   volatile uint32_t* get_doorbells_host() const { return h_doorbells_; }
   volatile uint32_t* get_doorbells_device() const { return d_doorbells_; }
+  SrpcSlotDesc* get_slot_desc(int slot) const { return (SrpcSlotDesc*)(h_desc_ + (size_t)slot * srpc_desc_stride(req_size_)); }
+  uint32_t desc_per_slot() const { return srpc_desc_per_slot(req_size_); }
   volatile uint64_t* get_tx_offsets_host() const { return h_tx_off_; }
   volatile uint64_t* get_tx_offsets_device() const { return d_tx_off_; }
   volatile uint64_t* get_stamps_host() const { return h_stamps_; }

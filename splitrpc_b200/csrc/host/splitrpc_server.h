@@ -55,6 +55,7 @@ class SplitRpcServer {
     NvlRemoteReplica* remote = nullptr;
     bool device_completes = false;         // responses and WORK_COMPLETE arrive without this process's help
     int64_t stamp_skew_ns = 0;             // serving device's stamp timer minus the gather device's
+    bool can_push = true;                  // the serving side can reach the transmit arena
     int app_idx = -1;
     int tx_idx = 0;                        // next slot whose response goes out
     std::atomic<int> outstanding{0};
@@ -306,7 +307,7 @@ class SplitRpcServer {
             tx_ok[i] = port_->alloc_tx(&tx[(size_t)i * resp_frags_], (int)resp_frags_) ? 1 : 0;
             if (!tx_ok[i]) stats_.tx_alloc_fail++;
             uint64_t off = P2pRpcAppRrMemPool::kNoTxOffset;
-            if (rep.device_completes && tx_ok[i] && resp_frags_ == 1) off = port_->tx_arena_offset(tx[(size_t)i * resp_frags_]);
+            if (rep.device_completes && rep.can_push && tx_ok[i] && resp_frags_ == 1) off = port_->tx_arena_offset(tx[(size_t)i * resp_frags_]);
             __atomic_store_n(slots[i]->h_tx_off, off, __ATOMIC_RELEASE);
           }
         }
@@ -466,6 +467,7 @@ class SplitRpcServer {
     r->engine = remote->engine();
     r->device_completes = remote->device_completes();
     r->stamp_skew_ns = remote->stamp_skew_ns();
+    r->can_push = remote->pushes_responses();
     {
       P2pRpcAppRrMemPool* mp = r->pool->rr_mem_pool;
       r->engine->set_stamp_layout(mp->get_doorbells_host(), mp->get_stamps_host(), mp->get_doorbells_device(), mp->get_stamps_device());
@@ -474,6 +476,7 @@ class SplitRpcServer {
     return (int)replicas_.size() - 1;
   }
   const TxArenaInfo* tx_arena() const { return have_tx_info_ ? &tx_info_ : nullptr; }
+  Transport* port() const { return port_; }
   size_t num_replicas() const { return replicas_.size(); }
   P2pRpcAsyncAppServer& app_server() { return app_server_; }
   P2pRpcRRPool& rr_pool() { return rr_pool_; }

@@ -18,8 +18,10 @@
 #include <netinet/in.h>
 #include <sys/socket.h>
 
+#include <atomic>
 #include <functional>
 #include <memory>
+#include <mutex>
 
 #include "mpmc_ring.h"
 #include "p2p_rpc.h"
@@ -125,10 +127,34 @@ class PktArena {
   }
 };
 
+// A range of host memory in which the payloads of received packets may lie (the receive arena, or a buffer that a
+// sender hands over by reference), as this process and its GPUs address it.  fd >= 0: a memfd that another process
+// can map too, which is what lets a replica in another process fetch a request's fragments by itself.
+struct DmaRegion {
+  uint8_t* host_base = nullptr;
+  uint8_t* dev_base = nullptr;
+  size_t bytes = 0;
+  int fd = -1;
+  bool gpu_visible = false;
+};
+
 class Transport {
  public:
   TransportCounters counters;
   virtual ~Transport() = default;
+  // Receiving side: the regions received payloads can be in (region 0 is the receive arena).  Returns how many.
+  virtual int dma_regions(DmaRegion* out, int max) const {
+    (void)out;
+    (void)max;
+    return 0;
+  }
+  // Sending side: memory whose contents tx_ref() can hand to the peer without a copy and that the peer can share with
+  // other processes.  false: the port has none (the caller uses memory of its own).
+  virtual bool alloc_dma_region(size_t bytes, DmaRegion* out) {
+    (void)bytes;
+    (void)out;
+    return false;
+  }
   // Receives up to `max` packets; never blocks.
   virtual int rx_burst(SrpcPkt* out, int max) = 0;
   // Hands buffers of received packets back to the port.
@@ -195,6 +221,12 @@ class LoopbackPort : public Transport {
   LoopbackFaults faults_;  // applied to packets this port SENDS
   SrpcRng rng_;
   std::mutex tx_mu_;
+  // Buffers that the peer's senders fill and hand over by reference (they belong to the port that receives them).
+  std::function<ArenaMem(size_t)> region_factory_;
+  static constexpr int kMaxRefRegions = 7;
+  std::unique_ptr<ArenaMem> ref_regions_[kMaxRefRegions];
+  std::atomic<int> n_ref_regions_{0};  // entries below it never change: readers need no lock
+  std::mutex region_mu_;
 
   // The emulated DMA: place one packet into the peer's receive arena.
   bool deliver(const p2p_rpc_hdr* hdr, const uint8_t* payload_host, uint32_t len, uint32_t slot) {
@@ -275,14 +307,49 @@ class LoopbackPort : public Transport {
         tx_arena_(new PktArena(std::move(tx_mem), slot_bytes)),
         rx_ring_(ring_depth) {}
 
+  ~LoopbackPort() override {
+    for (int i = 0; i < n_ref_regions_.load(); i++)
+      if (ref_regions_[i]->release) ref_regions_[i]->release();
+  }
   static void connect(LoopbackPort* a, LoopbackPort* b) {
     a->peer_ = b;
     b->peer_ = a;
+  }
+  // How this port makes memory of the kind its receive arena is made of (set by whoever built the arenas).
+  void set_region_factory(std::function<ArenaMem(size_t)> f) { region_factory_ = std::move(f); }
+  int dma_regions(DmaRegion* out, int max) const override {
+    int n = 0;
+    auto put = [&](uint8_t* h, uint8_t* d, size_t bytes, int fd, bool vis) {
+      if (n < max) out[n++] = DmaRegion{h, d, bytes, fd, vis};
+    };
+    put(rx_arena_->host_base(), rx_arena_->dev_base(), rx_arena_->bytes(), rx_arena_->fd(), rx_arena_->gpu_visible());
+    const int nr = n_ref_regions_.load(std::memory_order_acquire);
+    for (int i = 0; i < nr; i++) {
+      const ArenaMem* m = ref_regions_[i].get();
+      put(m->host, m->dev, m->bytes, m->fd, m->gpu_visible);
+    }
+    return n;
+  }
+  bool alloc_dma_region(size_t bytes, DmaRegion* out) override {
+    if (!peer_ || !peer_->region_factory_) return false;
+    auto m = std::make_unique<ArenaMem>(peer_->region_factory_(bytes));
+    if (!m->host) return false;
+    std::lock_guard<std::mutex> g(peer_->region_mu_);
+    const int at = peer_->n_ref_regions_.load();
+    if (at >= kMaxRefRegions) {
+      if (m->release) m->release();
+      return false;
+    }
+    *out = DmaRegion{m->host, m->dev, m->bytes, m->fd, m->gpu_visible};
+    peer_->ref_regions_[at] = std::move(m);
+    peer_->n_ref_regions_.store(at + 1, std::memory_order_release);
+    return true;
   }
   void set_faults(const LoopbackFaults& f) {
     faults_ = f;
     rng_ = SrpcRng(f.seed);
   }
+  LoopbackPort* peer() const { return peer_; }
   PktArena* rx_arena() { return rx_arena_.get(); }
   PktArena* tx_arena() { return tx_arena_.get(); }
 
@@ -354,9 +421,16 @@ class LoopbackPort : public Transport {
     for (int i = 0; i < n; i++) hp[i] = &hdrs[i];
     return send_list(hp.data(), payloads, lens, n);
   }
-  // Payloads handed over by reference live in pinned memory whose device address equals its host address.
+  // Payloads handed over by reference live in one of this port's regions, or in pinned memory whose device address
+  // equals its host address.
   uint8_t* rx_dev_ptr(const SrpcPkt& p) const override {
-    return p.slot == kExternalSlot ? p.payload : rx_arena_->to_dev(p.payload);
+    if (p.slot != kExternalSlot) return rx_arena_->to_dev(p.payload);
+    const int nr = n_ref_regions_.load(std::memory_order_acquire);
+    for (int i = 0; i < nr; i++) {
+      const ArenaMem* m = ref_regions_[i].get();
+      if (p.payload >= m->host && p.payload < m->host + m->bytes) return m->dev + (p.payload - m->host);
+    }
+    return p.payload;
   }
   uint8_t* tx_host_ptr(const SrpcPkt& p) const override { return tx_arena_->to_host(p.payload); }
   bool tx_arena_info(TxArenaInfo* out) const override {

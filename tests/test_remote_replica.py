@@ -23,7 +23,7 @@ def _replica_main(path, app_name, req, resp, mode, max_batch, ready, stop, out):
     ready.set()
     while not stop.is_set():
         time.sleep(0.01)
-    out.put((srv.counters(), srv.worker_stats()["num_req"]))
+    out.put((srv.counters(), srv.worker_stats()["num_req"], srv.pull_stats()))
     srv.stop()
 
 
@@ -44,14 +44,14 @@ def mtu1k(C):
     C.set_rpc_mtu(1024)
 
 
-def _ingress(C, paths, local_app=None, req=REQ, resp=REQ, max_batch=4, steer=0):
+def _ingress(C, paths, local_app=None, req=REQ, resp=REQ, max_batch=4, steer=0, pull=False):
     sp, cp = C.make_loopback_pair(1024, 2048, "shm")
     srv = C.Server(sp, req_size=req, resp_size=resp, server_mode=2, max_batch=max_batch, steer_policy=steer,
                    reassembly_timeout_ns=50_000_000)
     if local_app is not None:
         srv.add_replica(local_app)
     for p in paths:
-        srv.add_remote_replica(p, func_id=FUNC, ingress_device=-1)
+        srv.add_remote_replica(p, func_id=FUNC, ingress_device=-1, pull=pull)
     return srv, cp
 
 
@@ -78,9 +78,56 @@ def test_remote_replica_serves_echo_in_every_worker_mode(C, mtu1k, tmp_path, mod
         assert srv.release_remotes() == 1
     finally:
         stop.set()
-        ctr, served = out.get(timeout=20)
+        ctr, served, _ = out.get(timeout=20)
         proc.join(20)
     assert ctr["allocs"] == 1 and ctr["releases"] == 1 and ctr["peers_lost"] == 0 and served == 120
+
+
+@pytest.mark.parametrize("by_reference", [False, True])
+@pytest.mark.parametrize("mode", [1, 2])
+def test_replica_fetches_described_requests_itself(C, mtu1k, tmp_path, mode, by_reference):
+    """Pull mode: the ingress shares its payload regions at ALLOC time and afterwards only writes where a request's
+    fragments are; the serving process moves the bytes into its ring, serves and pushes the response.  Fragments lie in
+    the receive arena (one descriptor each) or in the sender's by-reference buffer (one descriptor per request)."""
+    proc, path, stop, out = _spawn(tmp_path, f"p{mode}{int(by_reference)}", mode=mode, max_batch=1 if mode < 2 else 4, resp=1024)
+    try:
+        srv, cp = _ingress(C, [path], resp=1024, max_batch=1 if mode < 2 else 4, pull=True)
+        assert srv.remote_info(0)["pull"] == 1
+        srv.start()
+        cli = C.Client(cp, req_size=REQ, resp_size=1024, total=150, warmup=0, payload="echo", verify=True,
+                       send_by_reference=by_reference, n_payloads=8)
+        assert cli.run_closed_loop(6)
+        st = srv.stats()
+        lat = srv.device_latency_ns()
+        srv.stop()
+        assert cli.received == 150 and cli.verify_failures == 0 and st["sg_errors"] == 0
+        assert st["replicas"][0]["pushed"] == 150 and len(lat) == 150 and min(lat) > 0
+        assert srv.release_remotes() == 1
+    finally:
+        stop.set()
+        ctr, served, pulled = out.get(timeout=20)
+        proc.join(20)
+    assert served == 150 and pulled["pulled"] == 150 and pulled["errors"] == 0
+
+
+def test_pull_is_refused_without_shareable_regions(C, mtu1k, tmp_path):
+    """A port whose receive arena is private memory cannot be pulled from: the handshake falls back to push."""
+    proc, path, stop, out = _spawn(tmp_path, "np", resp=1024)
+    try:
+        sp, cp = C.make_loopback_pair(1024, 2048)  # malloc arenas: no descriptor to share
+        srv = C.Server(sp, req_size=REQ, resp_size=1024, server_mode=2, max_batch=4)
+        srv.add_remote_replica(path, func_id=FUNC, ingress_device=-1, pull=True)
+        assert srv.remote_info(0)["pull"] == 0
+        srv.start()
+        cli = C.Client(cp, req_size=REQ, resp_size=1024, total=40, warmup=0, payload="echo", verify=True)
+        assert cli.run_closed_loop(4) and cli.received == 40 and cli.verify_failures == 0
+        srv.stop()
+        srv.release_remotes()
+    finally:
+        stop.set()
+        _, served, pulled = out.get(timeout=20)
+        proc.join(20)
+    assert served == 40 and pulled["pulled"] == 0
 
 
 def test_multi_fragment_responses_are_fetched_from_the_remote_ring(C, mtu1k, tmp_path):
