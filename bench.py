@@ -9,12 +9,17 @@ GPU 0 maps), parses headers, reassembles and steers.  Every rank serves one data
 GPU; the replicas of ranks > 0 sit behind batched servers that handed their request rings and slot doorbells to rank 0.
 A "step" is one full batch (``max_batch`` requests) per GPU.  Numbers:
 
-* ``value`` (device-timed, single ingress): K steps of {GPU 0's scatter-gather kernel pulls a batch's 8 KB fragments
-  out of the pinned arena, deserialises them, stores them into the serving GPU's request ring (over NVLink for
-  replicas on other GPUs) and rings the slot doorbells; the serving GPU's stream, parked on the last doorbell, runs
-  the model's CUDA graph, whose last kernel stores the responses into the ingress transmit arena and completes the
-  slots}.  No host thread takes part between the first doorbell and the last completion.  Timed with CUDA events on
-  every rank's serving stream, max over ranks.
+* ``value`` (device-timed, single ingress): K steps of one batch per GPU, no host thread between a batch's first
+  doorbell and its last completion; CUDA events on every rank's serving stream, max over ranks.  For N > 1 two ways of
+  feeding the replicas of ranks > 0 are measured (``--ingress both``) and the faster is the headline, the other is
+  reported under ``ingress_push`` / ``ingress_pull``:
+  push  GPU 0's scatter-gather kernel pulls a batch's 8 KB fragments out of the pinned arena, deserialises them,
+        stores them into the serving GPU's request ring over NVLink and rings the slot doorbells; the serving GPU's
+        stream, parked on the last doorbell, runs the model's CUDA graph, whose last kernel stores the responses into
+        the ingress transmit arena and completes the slots.  Every request crosses GPU 0's PCIe link.
+  pull  rank 0 shares its payload memory with the replicas (descriptors at ALLOC time) and only describes each
+        request; every serving GPU's own gather kernel fetches its batch over its own PCIe link, beside the graph of
+        the previous batch.  Responses are stored and completed the same way.
 * ``e2e``: the same metric through the public serving API: the load generator sends fragmented requests over the
   loopback transport, the native server reassembles, steers, gathers; the replicas batch dynamically and answer; the
   client receives the responses on the host.  Host->device bytes are the request fragments GPU 0 pulls from pinned
@@ -233,20 +238,39 @@ def device_timed_single_ingress(node, rank: int, world: int, steps: int, warmup:
     return ms, launches
 
 
-def device_timed_per_gpu(srv, steps: int, warmup: int):
-    """The independent arrangement: this GPU gathers its own batches from its own pinned arena (gather of batch i+1 on
-    a second stream beside the graph of batch i), runs the graph, whose last kernel stores the responses into the
-    transmit arena.  CUDA events on the serving stream."""
+def fill_payload(host_addr: int, nbytes: int, kind: str):
+    """Synthetic request bytes at a host address (a shared region that torch did not allocate)."""
+    import ctypes
+
+    import numpy as np
+
+    buf = np.ctypeslib.as_array((ctypes.c_uint8 * nbytes).from_address(host_addr))
+    rng = np.random.default_rng(7)
+    if kind == "ids":
+        buf.view(np.int32)[:] = rng.integers(0, 30522, nbytes // 4, dtype=np.int32)
+    else:
+        buf.view(np.float32)[:] = rng.standard_normal(nbytes // 4, dtype=np.float32)
+
+
+def device_timed_per_gpu(srv, steps: int, warmup: int, src_base: int | None = None, tx_off0: int = 0, tx_slot: int | None = None):
+    """This GPU gathers its own batches from pinned host memory over its own PCIe link (gather of batch i+1 on a second
+    stream beside the graph of batch i) and runs the graph, whose last kernel stores the responses into the transmit
+    arena.  CUDA events on the serving stream.  ``src_base``: device-side address of 2 x max_batch requests in host
+    memory (the ingress's shared payload region, as this process maps it); None: a pinned buffer of this process (the
+    independent arrangement).  ``tx_off0`` / ``tx_slot``: where this GPU's responses go in the transmit arena."""
     import torch
 
     from splitrpc_b200 import _C
 
     app, nb, req, resp = srv.app, srv.max_batch, srv.req_size, srv.resp_size
     mtu, n_sets = 8192, 2
-    pinned = torch.empty(n_sets * nb * req, dtype=torch.uint8).pin_memory()
-    pinned.view(torch.float32).normal_() if req >= 4096 else pinned.view(torch.int32).random_(0, 30522)
+    if src_base is None:
+        pinned = torch.empty(n_sets * nb * req, dtype=torch.uint8).pin_memory()
+        pinned.view(torch.float32).normal_() if req >= 4096 else pinned.view(torch.int32).random_(0, 30522)
+        src_base = pinned.data_ptr()
     req_base, resp_base = app.req_ring[0], app.resp_ring[0]
-    _, tx_dev, tx_bytes, tx_slot = srv.server.tx_arena
+    if tx_slot is None:
+        tx_slot = srv.server.tx_arena[3]
     app.reset_slots()
     stubs = torch.empty(n_sets, 2, dtype=torch.int64).pin_memory()
     first = torch.empty(n_sets, dtype=torch.int32).pin_memory()
@@ -257,9 +281,9 @@ def device_timed_per_gpu(srv, steps: int, warmup: int):
             off = 0
             while off < req:
                 ln = min(mtu, req - off)
-                items.append((pinned.data_ptr() + (s * nb + r) * req + off, req_base + (s * nb + r) * req + off, ln))
+                items.append((src_base + (s * nb + r) * req + off, req_base + (s * nb + r) * req + off, ln))
                 off += ln
-            app.set_tx_off(s * nb + r, (s * nb + r) * tx_slot)
+            app.set_tx_off(s * nb + r, tx_off0 + (s * nb + r) * tx_slot)
         lists.append(_C.sg_list_create(items))
         stubs[s, 0], stubs[s, 1], first[s] = req_base + s * nb * req, resp_base + s * nb * resp, s * nb
     stream = srv.stream
@@ -299,9 +323,12 @@ def device_timed_per_gpu(srv, steps: int, warmup: int):
     stream.synchronize()
     sg_stream.synchronize()
     ms = t0.elapsed_time(t1)
+    ok = all(app.slot_state(s) == WORK_COMPLETE for s in range(n_sets * nb))
     app.reset_slots()
     for h in lists:
         _C.sg_list_destroy(h)
+    if not ok:
+        raise RuntimeError("device-timed loop: a slot was not completed by the serving GPU")
     return ms
 
 
@@ -353,7 +380,7 @@ class PerGpuIngress:
 def run_ours(args, rank: int, world: int, local_rank: int) -> dict:
     import torch
 
-    from splitrpc_b200 import ops
+    from splitrpc_b200 import _C, ops
     from splitrpc_b200.serving import ModelReplica, ModelServer
 
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
@@ -390,69 +417,108 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> dict:
 
     # ---- roles: rank 0 = ingress + replica, the others = replicas behind batched servers
     if rank == 0:
-        # The ingress GPU gathers for every replica.  The gather that also deserialises ResNet images needs about 24 SMs
-        # to run at the PCIe rate (12 are enough when it only feeds its own replica), so with more than one replica the
-        # model kernels of GPU 0 leave 24 SMs to it.
+        # When GPU 0 gathers for every replica ("push"), the gather that also deserialises ResNet images needs about 24
+        # SMs to run at the PCIe rate (12 are enough when it only feeds its own replica), so the model kernels of GPU 0
+        # leave 24 SMs to it; when every replica fetches its own requests ("pull"), every GPU leaves 12.
         node = ModelServer(model, device=local_rank, max_batch=nb, server_mode=2, copy_type=2, outstanding=outstanding,
                            pool_size=pool, n_replicas=world, reserve_sms=12 if world == 1 else 24,
                            steer_policy=0 if world == 1 else 1)
     else:
         node = ModelReplica(model, sock_path(rank), device=local_rank, max_batch=nb, server_mode=-1, pool_size=pool,
                             reserve_sms=12)
-        node.start()
-    barrier()
-    if rank == 0:
-        for r in range(1, world):
-            node.add_remote(sock_path(r))
-    barrier()
-
-    # ---- device-timed, single ingress
     sampler = ClockSampler(local_rank)
     sampler.start()
-    m0 = sampler.mark()
-    ms, launches = device_timed_single_ingress(node, rank, world, args.steps, warm, barrier, cfg["payload"])
-    m1 = sampler.mark()
-    max_ms = allmax(ms)
-    total_launches = int(allsum(launches))
-    ops.check_status()
-    value = world * nb * args.steps / (max_ms / 1e3)
+    mtu, n_sets = 8192, 2
 
-    # ---- end to end through the public API, single ingress
-    if rank == 0:
-        node.stop()  # releases the worker-less batched servers
-    barrier()
-    if rank > 0:
-        node.serve(server_mode=2)
-        node.start()
-    barrier()
-    e2e = {}
-    n_req = int(min(400000, max(nb * args.steps * world, args.e2e_seconds * value)))
-    n_warm = max(nb * warm * world, n_req // 20)
-    m2 = m3 = sampler.mark()
-    if rank == 0:
-        node.new_server(server_mode=2, outstanding=outstanding, n_replicas=world, steer_policy=0 if world == 1 else 1)
-        for r in range(1, world):
-            node.add_remote(sock_path(r))
-        node.start()
-        m2 = sampler.mark()
-        e2e["ref"] = closed_loop(node, n_req, n_warm, outstanding, cfg["payload"], True)
-        m3 = sampler.mark()
-        st = node.server.stats()
-        ws = [node.server.worker_stats(i) for i in range(world)]
-        lat = sorted(node.server.device_latency_ns())
-        e2e["dev_lat"] = [lat[round(q * (len(lat) - 1))] / 1e3 if lat else None for q in (0.5, 0.99)] + [len(lat)]
-        e2e["copy"] = closed_loop(node, max(nb * world * 4, n_req // 4), max(nb, n_warm // 4), outstanding, cfg["payload"], False)
-        e2e["pushed"] = sum(r["pushed"] for r in st["replicas"])
-        e2e["steered"] = [r["steered"] for r in st["replicas"]]
-        e2e["sg_errors"] = st["sg_errors"]
-        hist = ws[0]["batch_hist"]
-        e2e["mean_batch_replica0"] = sum(k * v for k, v in hist.items()) / max(1, sum(hist.values()))
-        e2e["batches"] = [w["num_batches"] for w in ws]
-        node.stop()
-    barrier()
-    clocks_e2e = sampler.summary(m2, m3)
-    if rank > 0:
-        node.stop()
+    def measure(mode: str) -> dict:
+        """Device-timed loop and end-to-end run with the replicas of ranks > 0 fed in `mode`: "push" = GPU 0's gather
+        kernel stores every request into the serving GPU's ring over NVLink; "pull" = rank 0 only describes where the
+        fragments are and every serving GPU fetches them from the shared host memory over its own PCIe link."""
+        pull = mode == "pull"
+        out = {"mode": mode}
+        src_dev = 0
+        if rank == 0:
+            node.recapture(12 if pull or world == 1 else 24)
+            node.new_server(server_mode=2, outstanding=outstanding, n_replicas=world, steer_policy=0 if world == 1 else 1)
+            if pull:
+                # the requests of the timing loop: one shared, pinned region of the ingress port, 2 windows per GPU
+                region = _C.alloc_dma_region(node.client_port, world * n_sets * nb * node.req_size)
+                fill_payload(region[0], region[2], cfg["payload"])
+                src_dev = region[1]
+        else:
+            node.serve(server_mode=-1)
+            node.start()
+        barrier()
+        if rank == 0:
+            for r in range(1, world):
+                node.add_remote(sock_path(r), pull=pull)
+                if bool(node.server.remote_info(r - 1)["pull"]) != pull:
+                    raise RuntimeError("the replica did not accept the requested ingress mode")
+        barrier()
+        m0 = sampler.mark()
+        if pull:
+            if rank > 0:
+                src_dev = node.batched.regions()[1][0]  # region 0 is the receive arena, 1 the buffer allocated above
+            per_rank = n_sets * nb
+            ms = device_timed_per_gpu(node, args.steps, warm, src_base=src_dev + rank * per_rank * node.req_size,
+                                      tx_off0=rank * per_rank * mtu, tx_slot=mtu)
+            launches = (model.kernels_per_forward + 2) * args.steps
+        else:
+            ms, launches = device_timed_single_ingress(node, rank, world, args.steps, warm, barrier, cfg["payload"])
+        m1 = sampler.mark()
+        out["max_ms"] = allmax(ms)
+        out["launches"] = int(allsum(launches))
+        out["clocks"] = sampler.summary(m0, m1)
+        ops.check_status()
+        out["value"] = world * nb * args.steps / (out["max_ms"] / 1e3)
+
+        # ---- end to end through the public API
+        if rank == 0:
+            node.stop()  # releases the worker-less batched servers
+        barrier()
+        if rank > 0:
+            node.serve(server_mode=2)
+            node.start()
+        barrier()
+        e2e = {}
+        n_req = int(min(400000, max(nb * args.steps * world, args.e2e_seconds * out["value"])))
+        n_warm = max(nb * warm * world, n_req // 20)
+        m2 = m3 = sampler.mark()
+        if rank == 0:
+            node.new_server(server_mode=2, outstanding=outstanding, n_replicas=world, steer_policy=0 if world == 1 else 1)
+            for r in range(1, world):
+                node.add_remote(sock_path(r), pull=pull)
+            node.start()
+            m2 = sampler.mark()
+            e2e["ref"] = closed_loop(node, n_req, n_warm, outstanding, cfg["payload"], True)
+            m3 = sampler.mark()
+            st = node.server.stats()
+            ws = [node.server.worker_stats(i) for i in range(world)]
+            lat = sorted(node.server.device_latency_ns())
+            e2e["dev_lat"] = [lat[round(q * (len(lat) - 1))] / 1e3 if lat else None for q in (0.5, 0.99)] + [len(lat)]
+            e2e["copy"] = closed_loop(node, max(nb * world * 4, n_req // 4), max(nb, n_warm // 4), outstanding, cfg["payload"], False)
+            e2e["pushed"] = sum(r["pushed"] for r in st["replicas"])
+            e2e["steered"] = [r["steered"] for r in st["replicas"]]
+            e2e["sg_errors"] = st["sg_errors"]
+            hist = ws[0]["batch_hist"]
+            e2e["mean_batch_replica0"] = sum(k * v for k, v in hist.items()) / max(1, sum(hist.values()))
+            e2e["batches"] = [w["num_batches"] for w in ws]
+            node.stop()
+        barrier()
+        out["clocks_e2e"] = sampler.summary(m2, m3)
+        if rank > 0:
+            node.stop()
+        out["e2e"] = e2e
+        out["n_req"] = n_req
+        return out
+
+    modes = ["push"] if world == 1 else (["pull", "push"] if args.ingress == "both" else [args.ingress])
+    runs = {m: measure(m) for m in modes}
+    head = max(runs.values(), key=lambda r: r["value"])  # the same on every rank (all-reduced values)
+    other = [r for r in runs.values() if r is not head]
+    value, max_ms, total_launches, e2e = head["value"], head["max_ms"], head["launches"], head["e2e"]
+    clocks_dev, clocks_e2e = head["clocks"], head["clocks_e2e"]
+    pull_head = head["mode"] == "pull"
 
     # ---- the independent arrangement (every GPU its own ingress), as a second number
     per_gpu = None
@@ -472,50 +538,73 @@ def run_ours(args, rank: int, world: int, local_rank: int) -> dict:
                    "e2e": round(allsum(r2["rps"]), 1), "e2e_p99_us": round(allmax(r2["p99_us"]), 1),
                    "parallelism": f"dp{world}, one ingress (transport, server, load generator) per GPU"}
     clocks = sampler.stop()
-    clocks_dev = sampler.summary(m0, m1)
 
     result = None
     if rank == 0:
-        ref, cp = e2e["ref"], e2e["copy"]
         req_bytes, resp_bytes = node.req_size, node.resp_size
-        ingress_cap = PCIE_GBS * 1e9 / req_bytes  # requests/s that one ingress can pull over GPU 0's PCIe link
-        sm_e2e = clocks_e2e.get("sm_mhz") or 0
+        # requests/s that fit through the PCIe links that carry them: GPU 0's alone, or every GPU's own
+        ingress_cap = PCIE_GBS * 1e9 / req_bytes * (world if pull_head else 1)
+        step_push = (f"one batch of {nb} requests per GPU: GPU 0 gathers the fragments from the pinned host arena "
+                     "into the serving GPU's ring (NVLink for the other GPUs) and rings the slot doorbells; the serving "
+                     "stream waits on the doorbell and replays the model graph, whose last kernel stores the responses "
+                     "into the ingress transmit arena and completes the slots")
+        step_pull = (f"one batch of {nb} requests per GPU: every GPU's own gather kernel fetches the batch's 8 KB fragments from "
+                     "the ingress's shared pinned host memory over its own PCIe link into its request ring (next batch beside "
+                     "the running graph), then replays the model graph, whose last kernel stores the responses into the "
+                     "ingress transmit arena and completes the slots")
+        path_push = ("loadgen (fragments in pinned host memory, sent by reference) -> loopback NIC -> native server on rank 0 "
+                     "(reassembly, steering) -> GPU 0 gather kernel pulls the fragments over PCIe, writes the serving GPU's ring "
+                     "and rings its doorbells -> worker (dynamic batching) -> CUDA graph -> last kernel stores the responses into "
+                     "the pinned transmit arena and completes the slots -> client")
+        path_pull = ("loadgen (fragments in shared pinned host memory, sent by reference) -> loopback NIC -> native server on rank 0 "
+                     "(reassembly, steering; writes each request's fragment list into the slot's descriptor block) -> the serving "
+                     "process's fetch thread launches its GPU's gather kernel, which pulls the fragments over that GPU's PCIe link "
+                     "and rings the doorbells -> worker (dynamic batching) -> CUDA graph -> last kernel stores the responses into "
+                     "the ingress's pinned transmit arena and completes the slots -> client")
+
+        def e2e_block(run):
+            e, ce = run["e2e"], run["clocks_e2e"]
+            rf, cpm = e["ref"], e["copy"]
+            sm = ce.get("sm_mhz") or 0
+            return {"value": round(rf["rps"], 1), "unit": "req/s", "h2d_bytes_per_step": nb * world * req_bytes,
+                    "d2h_bytes_per_step": nb * world * resp_bytes, "p50_us": round(rf["p50_us"], 1), "p99_us": round(rf["p99_us"], 1),
+                    "slo_ms": args.slo_ms, "slo_met": bool(rf["ok"] and rf["p99_us"] <= args.slo_ms * 1e3),
+                    "requests": rf["requests"], "seconds": rf["seconds"], "outstanding": outstanding,
+                    "sm_mhz_median": ce.get("sm_mhz"), "reasons": ce.get("reasons"),
+                    "value_at_max_clock": round(rf["rps"] * 1965.0 / sm, 1) if sm else None,
+                    "copy_mode": {"value": round(cpm["rps"], 1), "p50_us": round(cpm["p50_us"], 1), "p99_us": round(cpm["p99_us"], 1),
+                                  "requests": cpm["requests"], "note": "the emulated NIC DMA writes every fragment into the receive arena (CPU memcpy by the client thread)"},
+                    "device_timed_latency": {"p50_us": e["dev_lat"][0], "p99_us": e["dev_lat"][1], "samples": e["dev_lat"][2],
+                                             "span": "the gather rings the slot's doorbell -> the serving GPU has stored the response "
+                                                     "(device timers; across two GPUs corrected by their measured offset)"},
+                    "responses_pushed_by_serving_gpu": e["pushed"], "steered": e["steered"], "sg_errors": e["sg_errors"],
+                    "mean_batch_replica0": round(e["mean_batch_replica0"], 2), "batches": e["batches"],
+                    "path": path_pull if run["mode"] == "pull" else path_push}
+
         result = {
             "metric": "req/s (dynamic batching, device-timed, max over ranks)", "value": round(value, 1), "unit": "req/s",
             "n_gpus": world, "steps": args.steps, "warmup": warm, "ms_per_step": round(max_ms / args.steps, 4),
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "impl": "splitrpc_b200",
             "config": {"model": cfg["model"], "global_batch": nb * world, "seq_len": cfg["seq"],
-                       "parallelism": f"dp{world}, single ingress" if world > 1 else "dp1",
-                       "step": f"one batch of {nb} requests per GPU: GPU 0 gathers the fragments from the pinned host arena "
-                               "into the serving GPU's ring (NVLink for the other GPUs) and rings the slot doorbells; the serving "
-                               "stream waits on the doorbell and replays the model graph, whose last kernel stores the responses "
-                               "into the ingress transmit arena and completes the slots",
+                       "parallelism": (f"dp{world}, single ingress, " + ("replicas fetch their requests (pull)" if pull_head else
+                                                                        "GPU 0 pushes over NVLink")) if world > 1 else "dp1",
+                       "step": step_pull if pull_head else step_push,
                        "l2": "256 MiB buffer written between iterations, inside the timed region; inputs alternate between two pinned host sets",
                        "weights": "random init"},
             "clocks": {**clocks_dev, "whole_run": clocks},
             "roofline": {"ingress_pcie_req_s": round(ingress_cap, 0), "value_over_ingress_cap": round(value / ingress_cap, 3),
-                         "note": f"one ingress pulls every request over GPU 0's PCIe link ({PCIE_GBS} GB/s measured): "
-                                 f"{req_bytes} B per request; the NVLink hop ({NVLINK_GBS} GB/s measured per direction) is not the limit"},
-            "e2e": {"value": round(ref["rps"], 1), "unit": "req/s", "h2d_bytes_per_step": nb * world * req_bytes,
-                    "d2h_bytes_per_step": nb * world * resp_bytes, "p50_us": round(ref["p50_us"], 1), "p99_us": round(ref["p99_us"], 1),
-                    "slo_ms": args.slo_ms, "slo_met": bool(ref["ok"] and ref["p99_us"] <= args.slo_ms * 1e3),
-                    "requests": ref["requests"], "seconds": ref["seconds"], "outstanding": outstanding,
-                    "sm_mhz_median": clocks_e2e.get("sm_mhz"), "reasons": clocks_e2e.get("reasons"),
-                    "value_at_max_clock": round(ref["rps"] * 1965.0 / sm_e2e, 1) if sm_e2e else None,
-                    "copy_mode": {"value": round(cp["rps"], 1), "p50_us": round(cp["p50_us"], 1), "p99_us": round(cp["p99_us"], 1),
-                                  "requests": cp["requests"], "note": "the emulated NIC DMA writes every fragment into the receive arena (CPU memcpy by the client thread)"},
-                    "device_timed_latency": {"p50_us": e2e["dev_lat"][0], "p99_us": e2e["dev_lat"][1], "samples": e2e["dev_lat"][2],
-                                             "span": "the gather rings the slot's doorbell -> the serving GPU has stored the response "
-                                                     "(each stamped with the nanosecond timer of the GPU that did it)"},
-                    "responses_pushed_by_serving_gpu": e2e["pushed"], "steered": e2e["steered"], "sg_errors": e2e["sg_errors"],
-                    "mean_batch_replica0": round(e2e["mean_batch_replica0"], 2), "batches": e2e["batches"],
-                    "path": "loadgen (fragments in pinned host memory, sent by reference) -> loopback NIC -> native server on rank 0 "
-                            "(reassembly, steering) -> GPU 0 gather kernel pulls the fragments over PCIe, writes the serving GPU's ring "
-                            "and rings its doorbells -> worker (dynamic batching) -> CUDA graph -> last kernel stores the responses into "
-                            "the pinned transmit arena and completes the slots -> client"},
+                         "note": (f"every GPU fetches its requests over its own PCIe link ({PCIE_GBS} GB/s measured each): "
+                                  f"{req_bytes} B per request" if pull_head else
+                                  f"one ingress pulls every request over GPU 0's PCIe link ({PCIE_GBS} GB/s measured): "
+                                  f"{req_bytes} B per request; the NVLink hop ({NVLINK_GBS} GB/s measured per direction) is not the limit")},
+            "e2e": e2e_block(head),
             "gpu_launches": total_launches,
         }
+        for o in other:
+            result["ingress_" + o["mode"]] = {"value": round(o["value"], 1), "ms_per_step": round(o["max_ms"] / args.steps, 4),
+                                              "gpu_launches": o["launches"], "clocks": o["clocks"],
+                                              "step": step_pull if o["mode"] == "pull" else step_push, "e2e": e2e_block(o)}
         if per_gpu:
             result["ingress_per_gpu"] = per_gpu
     barrier()
@@ -675,6 +764,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--slo-ms", type=float, default=10.0, help="p99 latency objective of the end-to-end phase")
     ap.add_argument("--e2e-seconds", type=float, default=2.0, help="target length of the end-to-end phase")
+    ap.add_argument("--ingress", default="both", choices=["both", "pull", "push"],
+                    help="N > 1: how the replicas of ranks > 0 get their requests (both: measure both, report the faster first)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

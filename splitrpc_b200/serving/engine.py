@@ -5,8 +5,10 @@ Two roles, one per process:
 ``ModelServer``   the ingress.  Owns the loopback transport (receive/transmit arenas in pinned host memory that
                   the GPUs map), the native server threads (header parsing, reassembly, flow steering) and
                   one replica of the model on its own GPU.  Replicas on other
-                  GPUs are added with ``add_remote(path)``: the scatter-gather kernel of the ingress GPU then
-                  writes their request rings over NVLink and rings their slot doorbells itself.
+                  GPUs are added with ``add_remote(path)``: either the scatter-gather kernel of the ingress GPU
+                  writes their request rings over NVLink and rings their slot doorbells itself (push), or the
+                  ingress only describes each request and the replica's GPU fetches the fragments from the shared
+                  host memory over its own PCIe link (``pull=True``).
 ``ModelReplica``  a replica on another GPU (another process): the model's graphs behind a batched server that
                   hands its rings and doorbells to the ingress (``buf_mon`` ALLOC handshake) and runs the worker.
 
@@ -72,6 +74,16 @@ class _GraphModelApp:
         self.stream.synchronize()
         self.app.set_self_push(True)  # the graphs' last kernel stores responses and completes slots
 
+    def recapture(self, reserve_sms: int) -> None:
+        """Captures the graphs again with another number of SMs left out of the model's persistent kernels (no server
+        or worker may be running).  A GPU that gathers for every replica needs more of them than one that only feeds
+        itself."""
+        if reserve_sms == self.reserve_sms:
+            return
+        self.reserve_sms = reserve_sms
+        _C.gemm_reserve_sms(reserve_sms)
+        self._capture()
+
 
 class ModelServer(_GraphModelApp):
     def __init__(self, model, device: int = 0, max_batch: int = 64, server_mode: int = 2, copy_type: int = 2,
@@ -112,10 +124,15 @@ class ModelServer(_GraphModelApp):
                                 device_completion=1 if device_completion else 0)
         self.server.add_replica(self.app)
 
-    def add_remote(self, path: str, timeout_ms: int = 60000) -> int:
-        """Connects to the ``ModelReplica`` listening at ``path`` and adds it to flow steering."""
+    def add_remote(self, path: str, timeout_ms: int = 60000, pull: bool = False) -> int:
+        """Connects to the ``ModelReplica`` listening at ``path`` and adds it to flow steering.
+
+        ``pull=False``: this GPU's gather kernel stores the replica's requests into its ring over NVLink and rings
+        its doorbells.  ``pull=True``: this process shares its payload memory with the replica and only describes
+        each request (where its fragments are); the replica's own GPU fetches them over its own PCIe link, so the
+        ingress GPU's link stops being the bound when several replicas are fed."""
         idx = self.server.add_remote_replica(path, func_id=FUNC_ID, ingress_device=self.device, copy_type=self.copy_type,
-                                             timeout_ms=timeout_ms)
+                                             timeout_ms=timeout_ms, pull=pull)
         self.n_remote += 1
         return idx
 

@@ -27,8 +27,9 @@ def sock_path(tag, rank):
     return os.path.join(tempfile.gettempdir(), f"srpc_{os.environ.get('MASTER_PORT', '0')}_{tag}_{rank}.sock")
 
 
-def check_echo(rank, world):
-    """Generic app (no fused response writer): the push kernel behind the app stores the responses."""
+def check_echo(rank, world, pull=False):
+    """Generic app (no fused response writer): the push kernel behind the app stores the responses.  With ``pull`` the
+    ingress only describes the requests and every serving GPU fetches the fragments from the shared host memory."""
     req = 3 * 8192 + 512  # four fragments, the last one short
     resp = 4096           # one fragment: pushed by the serving GPU
     _C.set_rpc_mtu(8192)
@@ -39,13 +40,21 @@ def check_echo(rank, world):
         srv.add_replica(app)
         dist.barrier()  # the batched servers are listening
         for r in range(1, world):
-            srv.add_remote_replica(sock_path("echo", r), func_id=FUNC, ingress_device=0, copy_type=2)
+            srv.add_remote_replica(sock_path("echo", r), func_id=FUNC, ingress_device=0, copy_type=2, pull=pull)
             info = srv.remote_info(r - 1)
-            assert info["device_id"] == r and info["device_completes"] == 1, info
+            assert info["device_id"] == r and info["device_completes"] == 1 and bool(info["pull"]) == pull, info
         srv.start()
         total = 200 * world
+        # pulled requests come both ways: copied into the receive arena (one descriptor per fragment) and handed over
+        # by reference (one descriptor per request, in a region announced after the handshake)
         cli = _C.Client(cp, req_size=req, resp_size=resp, total=total, warmup=0, payload="echo", verify=True)
         ok = cli.run_closed_loop(8 * world)
+        if pull:
+            cli2 = _C.Client(cp, req_size=req, resp_size=resp, total=total, warmup=0, payload="echo", verify=True,
+                             send_by_reference=True, n_payloads=8, seed=3)
+            ok = ok and cli2.run_closed_loop(8 * world) and cli2.received == total and cli2.verify_failures == 0
+        lat = srv.device_latency_ns()
+        assert lat and 0 < min(lat) and max(lat) < 2_000_000_000, (min(lat), max(lat))
         st = srv.stats()
         srv.stop()
         released = srv.release_remotes()
@@ -61,24 +70,27 @@ def check_echo(rank, world):
         dist.barrier()  # rank 0 has released
         ctr = bs.counters()
         served = bs.worker_stats()["num_req"]
+        pulled = bs.pull_stats()
         bs.stop()
         assert ctr["allocs"] == 1 and ctr["releases"] == 1 and ctr["peers_lost"] == 0 and served > 0, (ctr, served)
+        assert pulled["errors"] == 0 and pulled["pulled"] == (served if pull else 0), (pulled, served)
     ops.check_status()
 
 
-def check_resnet(rank, world):
-    """Fused ingress (gather + deserialise over NVLink) and fused response (softmax + store into the ingress arena)."""
+def check_resnet(rank, world, pull=False):
+    """Fused ingress (gather + deserialise, over NVLink or by the serving GPU itself) and fused response (softmax +
+    store into the ingress arena)."""
     nb = 8
     model = ResNet50(device=rank, max_batch=nb)
     if rank == 0:
         srv = ModelServer(model, device=0, max_batch=nb, outstanding=3 * nb * world, n_replicas=world)
         dist.barrier()
         for r in range(1, world):
-            srv.add_remote(sock_path("resnet", r))
+            srv.add_remote(sock_path("resnet", r), pull=pull)
         n_pay = 4
         total = 6 * nb * world
         with srv:
-            cli = srv.client(total=total, warmup=0, payload="normal", verify=True, n_payloads=n_pay)
+            cli = srv.client(total=total, warmup=0, payload="normal", verify=True, n_payloads=n_pay, send_by_reference=pull)
             ok = cli.run_closed_loop(2 * nb * world)
             st = srv.server.stats()
         assert ok and cli.received == total and st["sg_errors"] == 0, (cli.received, st)
@@ -109,10 +121,11 @@ def main():
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
     dist.init_process_group("gloo")
-    check_echo(rank, world)
-    dist.barrier()
-    check_resnet(rank, world)
-    dist.barrier()
+    for pull in (False, True):
+        check_echo(rank, world, pull)
+        dist.barrier()
+        check_resnet(rank, world, pull)
+        dist.barrier()
     if rank == 0:
         print("INGRESS_OK", flush=True)
     dist.destroy_process_group()
