@@ -442,10 +442,12 @@ PYBIND11_MODULE(_C, m) {
 
   m.def("make_loopback_pair",
         [](size_t slot_bytes, size_t n_slots, const std::string& server_mem) {
+          // the receive rings hold every packet that can be in flight (the caller sizes n_slots for that)
+          const size_t depth = std::max<size_t>(65536, n_slots);
           auto srv = std::make_shared<LoopbackPort>(make_arena(server_mem, slot_bytes * n_slots),
-                                                    make_arena(server_mem, slot_bytes * n_slots), slot_bytes);
+                                                    make_arena(server_mem, slot_bytes * n_slots), slot_bytes, depth);
           auto cli = std::make_shared<LoopbackPort>(make_malloc_arena(slot_bytes * n_slots),
-                                                    make_malloc_arena(slot_bytes * n_slots), slot_bytes);
+                                                    make_malloc_arena(slot_bytes * n_slots), slot_bytes, depth);
           LoopbackPort::connect(srv.get(), cli.get());
           // Buffers that the client fills and hands over by reference are made of the same kind of memory as the
           // server's receive arena (so a shared arena comes with shared by-reference buffers).

@@ -212,8 +212,10 @@ class LoopbackLink {
 
 class LoopbackPort : public Transport {
   static constexpr uint32_t kExternalSlot = 0xFFFFFFFFu;  // packet whose payload is not an arena slot
-  static constexpr uint32_t kExtHdrs = 1u << 16;          // header ring for by-reference packets
-  std::unique_ptr<p2p_rpc_hdr[]> ext_hdrs_{new p2p_rpc_hdr[kExtHdrs]};
+  // Header ring for by-reference packets: as deep as the receive ring, so a header lives at least until its packet
+  // has been taken out of the ring.
+  uint32_t ext_hdrs_n_;
+  std::unique_ptr<p2p_rpc_hdr[]> ext_hdrs_;
   uint32_t ext_next_ = 0;
   std::unique_ptr<PktArena> rx_arena_, tx_arena_;
   MpmcRing<SrpcPkt> rx_ring_;
@@ -303,9 +305,16 @@ class LoopbackPort : public Transport {
 
  public:
   LoopbackPort(ArenaMem rx_mem, ArenaMem tx_mem, size_t slot_bytes, size_t ring_depth = 65536)
-      : rx_arena_(new PktArena(std::move(rx_mem), slot_bytes)),
+      : ext_hdrs_n_(pow2_at_least(2 * ring_depth)),
+        ext_hdrs_(new p2p_rpc_hdr[ext_hdrs_n_]),
+        rx_arena_(new PktArena(std::move(rx_mem), slot_bytes)),
         tx_arena_(new PktArena(std::move(tx_mem), slot_bytes)),
-        rx_ring_(ring_depth) {}
+        rx_ring_(pow2_at_least(ring_depth)) {}
+  static uint32_t pow2_at_least(size_t n) {
+    uint32_t p = 1;
+    while (p < n && p < (1u << 30)) p <<= 1;
+    return p;
+  }
 
   ~LoopbackPort() override {
     for (int i = 0; i < n_ref_regions_.load(); i++)
@@ -371,7 +380,7 @@ class LoopbackPort : public Transport {
     std::lock_guard<std::mutex> g(tx_mu_);
     for (int i = 0; i < n; i++) {
       SrpcPkt p;
-      p.hdr = &peer_->ext_hdrs_[peer_->ext_next_++ & (kExtHdrs - 1)];
+      p.hdr = &peer_->ext_hdrs_[peer_->ext_next_++ & (peer_->ext_hdrs_n_ - 1)];
       std::memcpy(p.hdr, &hdrs[i], RPC_HEADER_LEN);
       p.payload = const_cast<uint8_t*>(payloads[i]);
       p.len = lens[i];
