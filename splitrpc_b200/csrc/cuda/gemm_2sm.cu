@@ -381,9 +381,12 @@ gemm_2sm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
               }
             }
             if (pass == PASSES - 1) {
-              __threadfence_system();  // this thread's stores of every pass have reached the owner
+              // Every thread's stores of every pass are ordered before the barrier; the one system-scope fence behind
+              // it (fences are cumulative) then makes the whole half tile visible on the owner before the count, and
+              // through the count before the flag.  A fence per thread costs hundreds of them per tile.
               named_bar_sync(1, EPI_THREADS);
               if (et == 0) {
+                __threadfence_system();
                 const uint32_t done = atomicAdd(tp.owner_count + owner, 1u) + 1u;
                 if (done == (uint32_t)tp.tiles_per_owner) {
                   atomicExch(tp.owner_count + owner, 0u);
@@ -568,7 +571,8 @@ cudaError_t srpc_gemm_tp_2sm(const void* A, int lda, const void* B, int ldb, int
   tp.mblocks_per_rank = (M / BM) / tp.tp;
   tp.m_rot = 0;
   tp.mblock_bytes = (size_t)BM * lda * 2;
-  tp.n_copy = tp.mblock_ready ? (tp.n_copy + 1) & ~1 : 0;
+  // a copier takes whole 128-row blocks: more copiers than remote blocks would idle on SMs the GEMM could use
+  tp.n_copy = tp.mblock_ready ? (std::min(tp.n_copy, (tp.tp - 1) * tp.mblocks_per_rank) + 1) & ~1 : 0;
   if (tp.rs)
     for (int o = 0; o < tp.tp; o++)
       if ((uintptr_t)tp.dst[o] & 15) return cudaErrorInvalidValue;

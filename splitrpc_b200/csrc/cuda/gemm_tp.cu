@@ -276,9 +276,10 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             *reinterpret_cast<uint4*>(dst + (size_t)(local_m0 + rr) * ep.ldo + col) = q;
           }
         }
-        __threadfence_system();
+        // one cumulative system-scope fence behind the barrier covers every thread's stores of the tile
         named_bar_sync(1, EPI_THREADS);
         if (et == 0) {
+          __threadfence_system();
           const uint32_t done = atomicAdd(tp.owner_count + owner, 1u) + 1u;
           if (done == (uint32_t)tp.tiles_per_owner) {
             atomicExch(tp.owner_count + owner, 0u);
@@ -501,6 +502,7 @@ cudaError_t srpc_gemm_tp(const void* A, int lda, const void* B, int ldb, int M, 
   const int tiles_n = (N + BN - 1) / BN;
   tp.tiles_per_owner = tp.mblocks_per_rank * tiles_n;
   if (!tp.mblock_ready) tp.n_copy = 0;
+  tp.n_copy = std::min(tp.n_copy, std::max(1, (tp.tp - 1) * tp.mblocks_per_rank));  // a copier takes whole row blocks
   static bool attr = false;
   const int smem = STAGES * STAGE_BYTES + 2 * OUT_BYTES + 1024;
   if (!attr) {

@@ -20,7 +20,7 @@ from .bert import BERT_LARGE, BertClassifier, BertConfig
 
 class BertClassifierTP:
     def __init__(self, cfg: BertConfig = BERT_LARGE, seq: int = 384, device: int = 0, batch: int = 16, seed: int = 0,
-                 n_copy: int = 16, group=None):
+                 n_copy: int | None = None, group=None):
         import torch.distributed as dist
 
         self.cfg, self.seq, self.batch = cfg, seq, batch

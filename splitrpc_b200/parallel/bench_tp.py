@@ -67,7 +67,7 @@ def main():
     ap.add_argument("--hidden", type=int, default=1024)
     ap.add_argument("--ffn", type=int, default=4096)
     ap.add_argument("--iters", type=int, default=20)
-    ap.add_argument("--n-copy", type=int, default=16)
+    ap.add_argument("--n-copy", type=int, default=None)
     ap.add_argument("--no-graph", action="store_true", help="time eager launches instead of graph replays")
     args = ap.parse_args()
     rank, world, local_rank = init_distributed()

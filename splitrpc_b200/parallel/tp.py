@@ -23,12 +23,16 @@ class TensorParallel:
 
     N_SITES = 5  # A (input of the first column-parallel GEMM), B (input of the second), RS1, RS2, DONE
 
-    def __init__(self, tokens: int, hidden: int, device: torch.device, n_copy: int = 16, group=None):
+    def __init__(self, tokens: int, hidden: int, device: torch.device, n_copy: int | None = None, group=None):
         import torch.distributed as dist
 
         self.tp = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
         assert tokens % (128 * self.tp) == 0, "tokens must be a multiple of 128 * tp"
+        # Copier blocks of the all-gather kernels.  One moves about 25 GB/s (16 KB bulk copies through its shared memory),
+        # so a shard of several MB wants a few dozen of them; with many ranks the GEMMs are small and can spare the SMs.
+        if n_copy is None:
+            n_copy = 32 if self.tp <= 2 else 64
         self.tokens, self.hidden, self.device, self.n_copy = tokens, hidden, device, n_copy
         self.rows = tokens // self.tp
         bf = 2
