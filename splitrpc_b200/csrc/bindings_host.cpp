@@ -486,14 +486,16 @@ PYBIND11_MODULE(_C, m) {
         py::arg("port"), py::arg("drop") = 0.0, py::arg("duplicate") = 0.0, py::arg("reorder") = 0.0,
         py::arg("truncate") = 0.0, py::arg("zero_token") = false, py::arg("force_seq") = -1, py::arg("seed") = 99);
   m.def("make_udp_port",
-        [](const std::string& ip, int port, size_t slot_bytes, size_t n_slots, const std::string& dst_ip, int dst_port) {
-          auto u = std::make_shared<UdpPort>(ip.c_str(), port, slot_bytes, n_slots);
+        [](const std::string& ip, int port, size_t slot_bytes, size_t n_slots, const std::string& dst_ip, int dst_port,
+           const std::string& mem) {
+          auto u = std::make_shared<UdpPort>(ip.c_str(), port, slot_bytes, make_arena(mem, slot_bytes * n_slots),
+                                             make_arena(mem, slot_bytes * n_slots));
           if (!u->ok()) throw std::runtime_error("UDP bind failed");
           if (!dst_ip.empty()) u->set_destination(dst_ip.c_str(), dst_port);
           return py::make_tuple(PortHolder{u.get(), u}, u->bound_port());
         },
         py::arg("ip"), py::arg("port"), py::arg("slot_bytes"), py::arg("n_slots") = 4096, py::arg("dst_ip") = "",
-        py::arg("dst_port") = 0);
+        py::arg("dst_port") = 0, py::arg("mem") = "malloc");
   m.def("dpdk_available", [] { return init_dpdk_ctx(dpdk_ctx{}) != nullptr; });
 
   // ---- apps

@@ -470,8 +470,12 @@ class UdpPort : public Transport {
 
  public:
   UdpPort(const char* bind_ip, int bind_port, size_t slot_bytes, size_t n_slots = 4096)
-      : rx_arena_(new PktArena(make_malloc_arena(slot_bytes * n_slots), slot_bytes)),
-        tx_arena_(new PktArena(make_malloc_arena(slot_bytes * n_slots), slot_bytes)),
+      : UdpPort(bind_ip, bind_port, slot_bytes, make_malloc_arena(slot_bytes * n_slots), make_malloc_arena(slot_bytes * n_slots)) {}
+  // Arenas supplied by the caller: pinned, GPU-mapped (and shareable) memory when a GPU gathers from the receive arena
+  // and serving GPUs store responses into the transmit arena.
+  UdpPort(const char* bind_ip, int bind_port, size_t slot_bytes, ArenaMem rx_mem, ArenaMem tx_mem)
+      : rx_arena_(new PktArena(std::move(rx_mem), slot_bytes)),
+        tx_arena_(new PktArena(std::move(tx_mem), slot_bytes)),
         scratch_(slot_bytes + RPC_HEADER_TAIL_LEN),
         tx_scratch_(slot_bytes + RPC_HEADER_TAIL_LEN) {
     fd_ = ::socket(AF_INET, SOCK_DGRAM | SOCK_NONBLOCK, 0);
@@ -604,6 +608,13 @@ class UdpPort : public Transport {
   }
   uint64_t tx_arena_offset(const SrpcPkt& p) const override { return (uint64_t)p.slot * tx_arena_->slot_bytes(); }
   uint8_t* rx_host_ptr(uint32_t slot) const override { return rx_arena_->host_ptr(slot); }
+  uint8_t* rx_dev_ptr(const SrpcPkt& p) const override { return rx_arena_->to_dev(p.payload); }
+  uint8_t* tx_host_ptr(const SrpcPkt& p) const override { return tx_arena_->to_host(p.payload); }
+  int dma_regions(DmaRegion* out, int max) const override {
+    if (max < 1) return 0;
+    out[0] = DmaRegion{rx_arena_->host_base(), rx_arena_->dev_base(), rx_arena_->bytes(), rx_arena_->fd(), rx_arena_->gpu_visible()};
+    return 1;
+  }
   const char* name() const override { return "udp"; }
 };
 

@@ -88,7 +88,8 @@ class _GraphModelApp:
 class ModelServer(_GraphModelApp):
     def __init__(self, model, device: int = 0, max_batch: int = 64, server_mode: int = 2, copy_type: int = 2,
                  outstanding: int | None = None, pool_size: int | None = None, batch_sizes=None, reserve_sms: int = 12,
-                 fused_ingress: bool = True, n_replicas: int = 1, steer_policy: int = 0, device_completion: bool = True):
+                 fused_ingress: bool = True, n_replicas: int = 1, steer_policy: int = 0, device_completion: bool = True,
+                 port=None):
         """``reserve_sms``: SMs that the model's persistent kernels leave out of their grids, for the scatter-gather
         kernel that pulls the next batch out of host memory while the current one is computed.  A persistent kernel
         counts on one block per SM: with a foreign block on only a few SMs it takes twice as long (ResNet-50 graph
@@ -101,12 +102,13 @@ class ModelServer(_GraphModelApp):
         self.n_remote = 0
         self._running = False
         self.new_server(server_mode=server_mode, outstanding=outstanding, n_replicas=n_replicas, steer_policy=steer_policy,
-                        device_completion=device_completion)
+                        device_completion=device_completion, port=port)
 
     def new_server(self, server_mode: int = 2, outstanding: int | None = None, n_replicas: int = 1, steer_policy: int = 0,
-                   device_completion: bool = True) -> None:
-        """(Re)creates the transport and the native server around the already captured model: a fresh loopback link, a
-        fresh request pool, this GPU's replica added.  Remote replicas of an earlier server are released first."""
+                   device_completion: bool = True, port=None) -> None:
+        """(Re)creates the transport and the native server around the already captured model: a fresh loopback link
+        (or ``port``, a transport port made by the caller, e.g. ``_C.make_udp_port(..., mem="shm_pinned")``), a fresh
+        request pool, this GPU's replica added.  Remote replicas of an earlier server are released first."""
         self.stop()
         self.server = None
         self.app.reset_slots()
@@ -115,7 +117,10 @@ class ModelServer(_GraphModelApp):
         n_slots = max(1024, 2 * self.outstanding * frags)
         # "shm_pinned": pinned and GPU-mapped like a NIC's registered rings, and a shared mapping, so that replicas
         # in other processes can register the transmit arena with their GPUs and store responses into it
-        self.server_port, self.client_port = _C.make_loopback_pair(MTU, n_slots, "shm_pinned")
+        if port is not None:
+            self.server_port, self.client_port = port, None
+        else:
+            self.server_port, self.client_port = _C.make_loopback_pair(MTU, n_slots, "shm_pinned")
         if self.fused_ingress and not self.app.set_ingress_stem_s2d(self.ingress["mean"], self.ingress["inv_std"]):
             raise RuntimeError("the scatter-gather engine does not support the fused ingress transform")
         self.server = _C.Server(self.server_port, req_size=self.req_size, resp_size=self.resp_size, server_mode=server_mode,

@@ -1,0 +1,57 @@
+"""Load generator main (kernel-UDP transport): closed loop with a fixed number of outstanding requests, or open loop
+at a request rate with deterministic / exponential / hyper-exponential arrivals.
+
+    python -m splitrpc_b200.utils.client --server-ip 127.0.0.1 --server-port 50051 --app resnet50 --total 5000 --outstanding 64
+    python -m splitrpc_b200.utils.client --server-port 50051 --app echo --req-size 4096 --resp-size 1024 --rate 2000 --cov 1
+
+Prints the statistics of the measured requests as one JSON line, with the keys of the original's load generator
+(reference src/lib_loadgen/dist_rpc_bench.cc:274-284, stats_factory.h:135-148).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+
+from .. import _C
+from ..serving.apps import sizes
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
+    ap.add_argument("--server-ip", default="127.0.0.1")
+    ap.add_argument("--server-port", type=int, required=True)
+    ap.add_argument("--bind-ip", default="0.0.0.0")
+    ap.add_argument("--bind-port", type=int, default=0)
+    ap.add_argument("--app", required=True, help="selects request / response sizes and the payload generator")
+    ap.add_argument("--req-size", type=int, default=None)
+    ap.add_argument("--resp-size", type=int, default=None)
+    ap.add_argument("--mtu", type=int, default=8192)
+    ap.add_argument("--total", type=int, default=1000)
+    ap.add_argument("--warmup", type=int, default=100)
+    ap.add_argument("--outstanding", type=int, default=1, help="closed loop: requests in flight")
+    ap.add_argument("--rate", type=float, default=0.0, help="open loop: requests per second (0 = closed loop)")
+    ap.add_argument("--cov", type=float, default=1.0, help="open loop: coefficient of variation of the inter-arrival times")
+    ap.add_argument("--threads", type=int, default=1)
+    ap.add_argument("--verify", action="store_true")
+    ap.add_argument("--exp-name", default="splitrpc")
+    ap.add_argument("--out-dir", default="")
+    args = ap.parse_args(argv)
+    _C.set_rpc_mtu(args.mtu)
+    req, resp, kind = sizes(args.app, args.req_size, args.resp_size)
+    frags = math.ceil(req / args.mtu) + math.ceil(resp / args.mtu)
+    n_slots = max(1024, 4 * max(args.outstanding, 64) * frags)
+    port, bound = _C.make_udp_port(args.bind_ip, args.bind_port, args.mtu, n_slots, args.server_ip, args.server_port)
+    my_ip = "127.0.0.1" if args.bind_ip == "0.0.0.0" else args.bind_ip
+    uri = f"00:00:00:00:00:01,{my_ip},{bound},00:00:00:00:00:02,{args.server_ip},{args.server_port}"
+    cli = _C.Client(port, req_size=req, resp_size=resp, total=args.total + args.warmup, warmup=args.warmup, payload=kind,
+                    verify=args.verify, exp_name=args.exp_name, out_dir=args.out_dir or ".", uri=uri)
+    ok = cli.run_open_loop(args.rate, args.cov, args.threads) if args.rate > 0 else cli.run_closed_loop(args.outstanding)
+    st = dict(cli.post_process())
+    st.update({"ok": bool(ok), "received": int(cli.received), "verify_failures": int(cli.verify_failures)})
+    print(json.dumps(st), flush=True)
+    return 0 if ok else 1
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())
