@@ -65,6 +65,7 @@ def _obj_for(src: Path, hdr_digest: str, verbose_ptxas: bool) -> tuple[Path, lis
     extra = os.environ.get("SPLITRPC_NVCC_EXTRA", "").split()
     # SPLITRPC_PROFILE=1: per-stage host timers and NVTX ranges on the server threads (-DPROFILE_MODE)
     prof = ["-DPROFILE_MODE"] if os.environ.get("SPLITRPC_PROFILE") == "1" else []
+    prof += _dpdk_flags()[0]
     flags = (NVCC_FLAGS + extra + prof + (["-Xptxas", "-v"] if verbose_ptxas else [])) if is_cu else CXX_FLAGS + prof
     key = hashlib.sha256((src.read_text() + hdr_digest + " ".join(flags)).encode()).hexdigest()[:16]
     obj = BUILD / f"{src.stem}.{key}.o"
@@ -73,6 +74,20 @@ def _obj_for(src: Path, hdr_digest: str, verbose_ptxas: bool) -> tuple[Path, lis
     else:
         cmd = [os.environ.get("CXX", "g++"), "-c", str(src), "-o", str(obj)] + flags + _includes()
     return obj, cmd
+
+
+def _dpdk_flags() -> tuple[list[str], list[str]]:
+    """SPLITRPC_WITH_DPDK=1: compile the DPDK port (csrc/host/dpdk_port.h) against the libdpdk that pkg-config finds."""
+    if os.environ.get("SPLITRPC_WITH_DPDK") != "1":
+        return [], []
+    try:
+        cflags = subprocess.run(["pkg-config", "--cflags", "libdpdk"], capture_output=True, text=True, check=True).stdout.split()
+        libs = subprocess.run(["pkg-config", "--libs", "libdpdk"], capture_output=True, text=True, check=True).stdout.split()
+    except (OSError, subprocess.CalledProcessError) as e:
+        raise RuntimeError("SPLITRPC_WITH_DPDK=1 but pkg-config does not know libdpdk") from e
+    # nvcc takes host-compiler options through -Xcompiler; keep only what both compilers understand
+    cflags = [f for f in cflags if f.startswith(("-I", "-D"))]
+    return ["-DSPLITRPC_WITH_DPDK"] + cflags, libs
 
 
 def build(force: bool = False, verbose: bool = False, verbose_ptxas: bool = False) -> Path:
@@ -118,7 +133,7 @@ def _build_locked(force: bool, verbose: bool, verbose_ptxas: bool) -> Path:
     link_key = hashlib.sha256(" ".join(o.name for o in objs).encode()).hexdigest()  # names, not paths: the tree may move
     if force or todo or not TARGET.exists() or not stamp.exists() or stamp.read_text() != link_key:
         tmp = TARGET.with_name(TARGET.name + f".tmp{os.getpid()}")
-        cmd = [_nvcc(), "-shared", "-o", str(tmp)] + [str(o) for o in objs] + GENCODE + ["-cudart", "static", "-lpthread", "-ldl", "-lrt"]
+        cmd = [_nvcc(), "-shared", "-o", str(tmp)] + [str(o) for o in objs] + GENCODE + ["-cudart", "static", "-lpthread", "-ldl", "-lrt"] + _dpdk_flags()[1]
         if verbose:
             print(" ".join(cmd), flush=True)
         r = subprocess.run(cmd, capture_output=True, text=True)

@@ -7,6 +7,7 @@
 
 #include "cuda/apps_gpu.h"
 #include "host/apps_cpu.h"
+#include "host/dpdk_port.h"
 #include "host/loadgen.h"
 #include "host/p2p_rpc_compat.h"
 #include "host/splitrpc_server.h"
@@ -496,7 +497,24 @@ PYBIND11_MODULE(_C, m) {
         },
         py::arg("ip"), py::arg("port"), py::arg("slot_bytes"), py::arg("n_slots") = 4096, py::arg("dst_ip") = "",
         py::arg("dst_port") = 0, py::arg("mem") = "malloc");
-  m.def("dpdk_available", [] { return init_dpdk_ctx(dpdk_ctx{}) != nullptr; });
+#ifdef SPLITRPC_HAVE_DPDK
+  m.def("dpdk_available", [] { return true; });
+  // A port of NIC `nic_port` with header/data split into arenas of kind `mem` (see make_loopback_pair).
+  m.def("make_dpdk_port",
+        [](int nic_port, int queue_id, size_t slot_bytes, size_t n_slots, const std::string& mem) {
+          Transport* t = srpc_open_dpdk_port(nic_port, queue_id, slot_bytes, n_slots, [mem](size_t b) { return make_arena(mem, b); });
+          if (!t) throw std::runtime_error("DPDK port could not be opened");
+          std::shared_ptr<Transport> owner(t);
+          return PortHolder{t, owner};
+        },
+        py::arg("nic_port") = 0, py::arg("queue_id") = 0, py::arg("slot_bytes") = 8192, py::arg("n_slots") = 4096,
+        py::arg("mem") = "shm_pinned");
+#else
+  m.def("dpdk_available", [] { return false; });
+  m.def("make_dpdk_port", [](py::args, py::kwargs) -> PortHolder {
+    throw std::runtime_error("this build has no DPDK (build with SPLITRPC_WITH_DPDK=1 on a machine with libdpdk and a NIC)");
+  });
+#endif
 
   // ---- apps
   py::class_<AppHolder, std::shared_ptr<AppHolder>>(m, "App")

@@ -17,6 +17,7 @@
 
 #include <netinet/in.h>
 #include <sys/socket.h>
+#include <unistd.h>
 
 #include <atomic>
 #include <functional>
@@ -625,10 +626,8 @@ struct dpdk_ctx {
   int nic_port = 0, queue_id = 0, mem_alloc_type = HOST_MEM_ONLY, device_id = 0, zerocopy_mode = 0;
 };
 
-// A DPDK port needs libdpdk, an mlx5 NIC and GPUDirect RDMA; none exist on a
-// machine without a NIC.  The function documents the slot where such a port plugs
-// in (it must implement Transport with its mbuf pools as the arenas) and reports
-// that it is unavailable.
+// A DPDK port needs libdpdk and a NIC.  The port itself is DpdkPort (dpdk_port.h), compiled only into builds made with
+// SPLITRPC_WITH_DPDK=1; this entry point of the original's name reports that a build without it has none.
 static inline Transport* init_dpdk_ctx(const dpdk_ctx&) {
   srpc_log(SRPC_LOG_ERROR, "DPDK transport requested but this build has no DPDK; use the loopback or UDP transport");
   return nullptr;
