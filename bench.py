@@ -661,7 +661,7 @@ def run_tp(args, rank: int, world: int, local_rank: int) -> dict:
         t = torch.tensor([sum(a.elapsed_time(b) for a, b in evs)], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         results["device"] = float(t.item())
-    # ---- end to end: closed-loop clients -> RPC front end on rank 0 -> control broadcast -> TP graph on every rank
+    # ---- end to end: closed-loop clients -> RPC front end on rank 0 -> fan-out kernel + doorbells -> TP graph on every rank
     from splitrpc_b200.serving.tp_server import TensorParallelServer
 
     srv = TensorParallelServer(model, outstanding=2 * B)
@@ -696,8 +696,10 @@ def run_tp(args, rank: int, world: int, local_rank: int) -> dict:
                 "p50_us": round(e2e_p50, 1), "p99_us": round(e2e_p99, 1),
                 "mean_batch": round((n_req + n_warm) / max(1.0, e2e_batches), 2), "outstanding": 2 * B,
                 "path": "loadgen (ids in pinned host memory, sent by reference) -> loopback NIC -> native server on rank 0 "
-                        "(reassembly, dynamic batching, SG kernel pulls the ids over PCIe) -> control broadcast to the "
-                        "peers -> TP graph on every rank -> probabilities to the pinned transmit arena -> client"},
+                        "(reassembly, dynamic batching, SG kernel pulls the ids over PCIe) -> rank 0's graph: fan-out kernel "
+                        "stores the ids into every rank's buffer over NVLink and rings the ranks' doorbells (their streams are "
+                        "parked on them with the TP graph queued behind) -> TP graph on every rank -> last kernel stores the "
+                        "probabilities into the pinned transmit arena and completes the slots -> client"},
         "gpu_launches": model.kernels_per_forward * args.steps,
     }
     dist.barrier()

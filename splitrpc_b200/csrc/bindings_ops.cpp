@@ -32,6 +32,7 @@ static GemmEpilogue make_ep(uintptr_t out, int ldo, bool out_fp32, uintptr_t bia
 }
 
 extern "C" int srpc_stream_write64(cudaStream_t s, uint64_t* addr, uint64_t v);
+extern "C" int srpc_stream_wait32_geq(cudaStream_t s, uint32_t* addr, uint32_t v);
 
 void bind_ops(py::module_& m) {
   m.def("device_caps", [](int dev) {
@@ -88,11 +89,13 @@ void bind_ops(py::module_& m) {
         py::arg("done_word") = 0, py::arg("done_value") = 0);
   // Stream-ordered doorbell operations on a 32-bit word that the device can address (mapped host memory or device
   // memory): the stream waits until the word equals `value` / writes `value` once everything queued before has finished.
-  m.def("stream_wait32", [](uintptr_t stream, uintptr_t addr, uint32_t value) {
+  m.def("stream_wait32", [](uintptr_t stream, uintptr_t addr, uint32_t value, bool geq) {
     const SrpcDeviceOps* o = srpc_cuda_ops();
-    if (!o || o->stream_wait_value32((cudaStream_t)stream, (volatile uint32_t*)addr, value) != 0)
-      throw std::runtime_error(std::string("stream_wait32: ") + (o ? o->last_error() : "no CUDA"));
-  });
+    // geq: the word is a sequence number that only grows; wait until it has reached `value` (cyclic comparison)
+    int rc = !o ? -1 : (geq ? srpc_stream_wait32_geq((cudaStream_t)stream, (uint32_t*)addr, value)
+                            : o->stream_wait_value32((cudaStream_t)stream, (volatile uint32_t*)addr, value));
+    if (rc != 0) throw std::runtime_error(std::string("stream_wait32: ") + (o ? o->last_error() : "no CUDA"));
+  }, py::arg("stream"), py::arg("addr"), py::arg("value"), py::arg("geq") = false);
   m.def("stream_write64", [](uintptr_t stream, uintptr_t addr, uint64_t value) {
     const SrpcDeviceOps* o = srpc_cuda_ops();
     if (!o || srpc_stream_write64((cudaStream_t)stream, (uint64_t*)addr, value) != 0)
@@ -200,6 +203,29 @@ void bind_ops(py::module_& m) {
     check(srpc_tp_begin((const uint32_t*)flags, n, (uint32_t*)epoch_base, delta, (uint32_t*)status, (cudaStream_t)stream),
           "tp_begin");
   });
+  m.def("tp_fanout",
+        [](uintptr_t d_stub, uint32_t req_bytes, uint32_t batch, uint32_t max_batch, uint32_t command, std::vector<uintptr_t> dst,
+           std::vector<uintptr_t> ctrl, std::vector<uintptr_t> doorbell, uintptr_t seq, uintptr_t arrivals, uintptr_t stream) {
+          TpFanout f{};
+          f.tp = (int)dst.size();
+          if (f.tp > TP_MAX_RANKS || ctrl.size() != dst.size() || doorbell.size() != dst.size())
+            throw std::invalid_argument("tp_fanout: one destination, control record and doorbell per rank");
+          f.stub = (const void*)d_stub;
+          f.req_bytes = req_bytes;
+          f.batch = batch;
+          f.max_batch = max_batch;
+          f.command = command;
+          for (int r = 0; r < f.tp; r++) {
+            f.dst[r] = (uint8_t*)dst[(size_t)r];
+            f.ctrl[r] = (uint32_t*)ctrl[(size_t)r];
+            f.doorbell[r] = (uint32_t*)doorbell[(size_t)r];
+          }
+          f.seq = (uint32_t*)seq;
+          f.arrivals = (uint32_t*)arrivals;
+          check(srpc_tp_fanout(f, (cudaStream_t)stream), "tp_fanout");
+        },
+        py::arg("d_stub"), py::arg("req_bytes"), py::arg("batch"), py::arg("max_batch"), py::arg("command"), py::arg("dst"),
+        py::arg("ctrl"), py::arg("doorbell"), py::arg("seq"), py::arg("arrivals"), py::arg("stream"));
   m.def("tp_bump", [](uintptr_t word, uint32_t delta, uintptr_t stream) {
     check(srpc_tp_bump((uint32_t*)word, delta, (cudaStream_t)stream), "tp_bump");
   });

@@ -158,6 +158,13 @@ static int d_write32(cudaStream_t s, volatile uint32_t* addr, uint32_t v) {
   DRV(d->StreamWriteValue32((CUstream)s, (CUdeviceptr)(uintptr_t)addr, v, CU_STREAM_WRITE_VALUE_DEFAULT));
   return 0;
 }
+// Stream-ordered wait until (int32)(*addr - v) >= 0, for sequence-number doorbells that may have moved on.
+extern "C" int srpc_stream_wait32_geq(cudaStream_t s, uint32_t* addr, uint32_t v) {
+  const SrpcDriverApi* d = srpc_driver_api();
+  if (!d->StreamWaitValue32) return fail_drv("cuStreamWaitValue32 unavailable", CUDA_ERROR_NOT_SUPPORTED);
+  DRV(d->StreamWaitValue32((CUstream)s, (CUdeviceptr)(uintptr_t)addr, v, CU_STREAM_WAIT_VALUE_GEQ));
+  return 0;
+}
 extern "C" int srpc_stream_write64(cudaStream_t s, uint64_t* addr, uint64_t v) {
   const SrpcDriverApi* d = srpc_driver_api();
   if (!d->StreamWriteValue64) return fail_drv("cuStreamWriteValue64 unavailable", CUDA_ERROR_NOT_SUPPORTED);

@@ -532,6 +532,47 @@ cudaError_t srpc_gemm_tp(const void* A, int lda, const void* B, int ldb, int M, 
   return cudaGetLastError();
 }
 
+// One block per (rank, 16 KB piece) of the batch; the last block to finish publishes control records and doorbells.
+__global__ void __launch_bounds__(256) tp_fanout_kernel(const TpFanout f) {
+  const uint8_t* src = *reinterpret_cast<const uint8_t* const*>(f.stub);  // g_params::req is the stub's first word
+  const size_t total = (size_t)f.max_batch * f.req_bytes, live = (size_t)f.batch * f.req_bytes;
+  const size_t piece = 16384;
+  const size_t pieces = (total + piece - 1) / piece;
+  for (size_t w = blockIdx.x; w < pieces * (size_t)f.tp; w += gridDim.x) {
+    const int r = (int)(w / pieces);
+    const size_t at = (w % pieces) * piece, end = at + piece < total ? at + piece : total;
+    for (size_t o = at + (size_t)threadIdx.x * 16; o < end; o += (size_t)blockDim.x * 16) {
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (o < live) v = *reinterpret_cast<const uint4*>(src + o);
+      *reinterpret_cast<uint4*>(f.dst[r] + o) = v;
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();  // cumulative: covers the block's stores (ordered before the barrier)
+    if (atomicAdd(f.arrivals, 1u) == gridDim.x - 1) {
+      *f.arrivals = 0;
+      const uint32_t s = *f.seq + 1u;
+      *f.seq = s;
+      for (int r = 0; r < f.tp; r++) {
+        f.ctrl[r][0] = f.command;
+        f.ctrl[r][1] = f.batch;
+      }
+      __threadfence_system();
+      for (int r = 0; r < f.tp; r++) ptx::st_release_sys(f.doorbell[r], s);
+    }
+  }
+}
+
+cudaError_t srpc_tp_fanout(const TpFanout& f, cudaStream_t stream) {
+  if (f.tp < 1 || f.tp > TP_MAX_RANKS || !f.stub || (f.req_bytes & 15u) || f.batch > f.max_batch || !f.seq || !f.arrivals)
+    return cudaErrorInvalidValue;
+  const size_t pieces = ((size_t)f.max_batch * f.req_bytes + 16383) / 16384;
+  const int blocks = (int)std::min<size_t>(pieces * (size_t)f.tp, 64);
+  tp_fanout_kernel<<<blocks > 0 ? blocks : 1, 256, 0, stream>>>(f);
+  return cudaGetLastError();
+}
+
 cudaError_t srpc_tp_signal(const TpSignal& sig, cudaStream_t stream) {
   tp_signal_peers<<<1, 32, 0, stream>>>(sig);
   return cudaGetLastError();

@@ -79,6 +79,25 @@ cudaError_t srpc_tp_begin(const uint32_t* flags, int n, uint32_t* epoch_base, ui
 cudaError_t srpc_tp_bump(uint32_t* word, uint32_t delta, cudaStream_t stream);
 cudaError_t srpc_layernorm_reduce(const TpReduce& rd, int rows, uint32_t* status, cudaStream_t stream);
 
+// Request fan-out of a tensor-parallel replica: the rank that owns the request ring stores the batch's requests into
+// every rank's input buffer (its own included) over peer memory, then a two-word control record {command, batch} and,
+// with a system-scope release store, the next sequence number into every rank's doorbell word.  The other ranks'
+// streams are parked on that word (cuStreamWaitValue32, >=), so no host thread and no collective library sits between
+// the arrival of a batch and the start of the model on any rank.
+struct TpFanout {
+  int tp;
+  const void* stub;          // g_params in device memory: stub->req is where the batch's requests start in the ring
+  uint32_t req_bytes;        // bytes per request (a multiple of 16); requests are contiguous in the ring window
+  uint32_t batch, max_batch; // rows past `batch` are zeroed up to max_batch
+  uint32_t command;
+  uint8_t* dst[TP_MAX_RANKS];       // dst[r]: rank r's input buffer [max_batch, req_bytes]
+  uint32_t* ctrl[TP_MAX_RANKS];     // ctrl[r]: rank r's control record {command, batch}
+  uint32_t* doorbell[TP_MAX_RANKS]; // doorbell[r]: rank r's sequence word
+  uint32_t* seq;             // this rank's counter: every launch publishes ++*seq
+  uint32_t* arrivals;        // zeroed word (block arrival counter)
+};
+cudaError_t srpc_tp_fanout(const TpFanout& f, cudaStream_t stream);
+
 // Bound (ns) of the flag waits of the tensor-parallel kernels on the current device (default 2 s).  A wait that runs
 // out sets GEMM_ERR_TP_SRC_WAIT in the status word and the kernel returns; nothing traps or spins on.
 cudaError_t srpc_tp_set_wait_ns(uint64_t ns);

@@ -64,8 +64,13 @@ class BertClassifierTP:
                     "logits": torch.empty((batch, 8), dtype=torch.float32, device=dev)}
         self.kernels_per_forward = 3 + 7 * cfg.layers + 5
 
-    def forward(self, ids: torch.Tensor, out: torch.Tensor | None = None, d_stub: int = 0) -> torch.Tensor:
-        """``ids``: int32 ``[batch, seq]`` (identical on every rank).  Returns fp32 logits ``[batch, num_labels]``."""
+    def forward(self, ids: torch.Tensor, out: torch.Tensor | None = None, d_stub: int = 0, d_push: int = 0,
+                n_resp: int | None = None, resp_stride: int | None = None) -> torch.Tensor:
+        """``ids``: int32 ``[batch, seq]`` (identical on every rank).  Returns fp32 logits ``[batch, num_labels]``.
+
+        ``out``: probabilities go there.  ``d_stub`` / ``d_push`` (the serving app's stub and response-push block):
+        the first ``n_resp`` rows go to the app's response slots, ``resp_stride`` bytes apart, and the kernel completes
+        the slots when the server has enabled that."""
         cfg, p, b, S, t = self.cfg, self.params, self.buf, self.seq, self.tpc
         B, r, tp = self.batch, self.rank, self.tp
         bl = B // tp
@@ -92,7 +97,8 @@ class BertClassifierTP:
         ops.gemm(b["pooled"], p["cls.w"], bias=p["cls.b"], out=b["logits"])
         logits = b["logits"][:, : cfg.num_labels]
         if out is not None or d_stub:
-            ops.softmax_response(logits, B, out=out, d_stub=0 if out is not None else d_stub, resp_stride=self.resp_size)
+            ops.softmax_response(logits, B if n_resp is None else n_resp, out=out, d_stub=0 if out is not None else d_stub,
+                                 resp_stride=resp_stride or self.resp_size, d_push=0 if out is not None else d_push)
         return logits
 
     __call__ = forward

@@ -34,6 +34,17 @@ def test_tensor_parallel_and_cross_gpu_paths():
     assert r.returncode == 0 and "MULTI_GPU_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
 
 
+def test_tensor_parallel_group_of_one():
+    """The same checks with a single rank (needs one GPU): every "peer" is the rank itself, the fused kernels run
+    without copiers and store their partial tiles into their own slot, the serving front end fans out to itself."""
+    import torch
+
+    if torch.cuda.device_count() < 1:
+        pytest.skip("needs a GPU")
+    r = _torchrun("tp_check.py", 1, 29535)
+    assert r.returncode == 0 and "MULTI_GPU_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+
+
 def test_single_ingress_serving_across_gpus():
     r = _torchrun("ingress_check.py", _world(), 29534)
     assert r.returncode == 0 and "INGRESS_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
