@@ -137,17 +137,32 @@ def test_resnet50_matches_fp32_reference(torch_cuda, fuse_shortcut):
     from splitrpc_b200 import ops
     from splitrpc_b200.models import ResNet50
 
-    m = ResNet50(device=0, max_batch=4, fuse_shortcut=fuse_shortcut)
-    x = torch.randn(3, 3, 224, 224, device="cuda")
-    out = torch.zeros(3, 1000, device="cuda")
-    logits = m.forward(3, x=x, out=out)
+    n = 16
+    m = ResNet50(device=0, max_batch=n, fuse_shortcut=fuse_shortcut)
+    x = torch.randn(n, 3, 224, 224, device="cuda")
+    out = torch.zeros(n, 1000, device="cuda")
+    m.forward(n, x=x, out=out)
     ops.check_status()
-    ref = m.reference_forward(x)
-    assert torch.isfinite(out).all() and abs(out.sum().item() - 3.0) < 1e-3
+    # the oracle in true fp32: no TF32 in cuDNN or cuBLAS
+    tf32 = (torch.backends.cudnn.allow_tf32, torch.backends.cuda.matmul.allow_tf32)
+    torch.backends.cudnn.allow_tf32 = torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        ref = m.reference_forward(x)
+    finally:
+        torch.backends.cudnn.allow_tf32, torch.backends.cuda.matmul.allow_tf32 = tf32
+    assert torch.isfinite(out).all() and (out.sum(1) - 1.0).abs().max().item() < 1e-3
     # bf16 activations through 53 layers: compare the probability rows as vectors
     cos = torch.nn.functional.cosine_similarity(out, ref, dim=1)
-    assert cos.min().item() > 0.98, cos
-    assert (out.argmax(1) == ref.argmax(1)).float().mean().item() >= 2 / 3
+    rel = ((out - ref).norm(dim=1) / ref.norm(dim=1)).max().item()
+    agree = (out.argmax(1) == ref.argmax(1)).float().mean().item()
+    print(f"resnet50 fuse={fuse_shortcut}: min cos {cos.min().item():.5f}, max rel err {rel:.4f}, argmax agreement {agree:.3f}")
+    assert cos.min().item() > 0.999, cos  # measured: 0.99999
+    assert rel < 0.05, rel                # measured: 0.006 - 0.007
+    assert agree >= 15 / 16, agree        # measured: 16 of 16
+    # where the oracle is decisive (its best class leads the runner-up by more than the bf16 noise), the classes agree
+    top2 = ref.topk(2, dim=1).values
+    decisive = (top2[:, 0] - top2[:, 1]) > 0.1 * top2[:, 0]
+    assert bool((out.argmax(1) == ref.argmax(1))[decisive].all())
 
 
 def test_bert_matches_fp32_reference(torch_cuda):

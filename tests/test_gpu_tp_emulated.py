@@ -76,3 +76,27 @@ def test_gemm_reduce_scatter_emulated_ranks(env, T, Kl, N, tp):
     assert bool((flags[:, :tp] == 9).all())
     got = slots.float().sum(1).reshape(T, N)
     assert ((got - total).norm() / total.norm()).item() < 1e-2
+
+
+@pytest.mark.parametrize("rows,hidden,tp", [(3072, 1024, 2), (768, 1024, 8), (384, 320, 2)])
+def test_reduce_layernorm_emulated_ranks(env, rows, hidden, tp):
+    """Sum of the source ranks' partial rows + bias + residual, then LayerNorm, with the flags of every source already
+    published; the kernel's last block publishes the step number to the peers' words."""
+    torch, C, ops = env
+    status = ops.status_word()
+    slots = (torch.randn(tp, rows, hidden, device="cuda") * 0.5).bfloat16()
+    residual = torch.randn(rows, hidden, device="cuda").bfloat16()
+    bias, gamma, beta = torch.randn(hidden, device="cuda"), torch.rand(hidden, device="cuda") + 0.5, torch.randn(hidden, device="cuda")
+    flags = torch.full((8,), 3, dtype=torch.int32, device="cuda")
+    out = torch.zeros(rows, hidden, dtype=torch.bfloat16, device="cuda")
+    peer_words = torch.zeros(tp, dtype=torch.int32, device="cuda")
+    done = torch.zeros(1, dtype=torch.int32, device="cuda")
+    C.layernorm_reduce([slots[r].data_ptr() for r in range(tp)], flags.data_ptr(), 3, bias.data_ptr(), residual.data_ptr(),
+                       gamma.data_ptr(), beta.data_ptr(), out.data_ptr(), rows, hidden, 1e-12, status.data_ptr(),
+                       torch.cuda.current_stream().cuda_stream, 0, [peer_words[p:].data_ptr() for p in range(tp)], 7, done.data_ptr())
+    torch.cuda.synchronize()
+    ops.check_status()
+    z = slots.float().sum(0) + bias + residual.float()
+    ref = torch.nn.functional.layer_norm(z, (hidden,), gamma, beta, 1e-12)
+    assert ((out.float() - ref).norm() / ref.norm()).item() < 1e-2
+    assert bool((peer_words == 7).all()) and int(done) == 0
