@@ -3,7 +3,7 @@
 The original project is a CMake tree whose server needs DPDK, gdrcopy, verbs, ONNX Runtime/TensorRT and an spdlog
 submodule that its repository snapshot does not contain, so it cannot be installed as a whole.  What builds offline is
 its scatter-gather engine: ``src/transport/g_copy_ng.cu`` and the headers it includes are compiled UNMODIFIED from the
-original tree (``--src``, default ``/root/reference/src``) for sm_100a, with two stand-in headers (``spdlog/spdlog.h``:
+original tree (``--src`` or ``SPLITRPC_REFERENCE_SRC``; default: ``reference/src`` beside this repository) for sm_100a, with two stand-in headers (``spdlog/spdlog.h``:
 no-op logging; ``gdrapi.h``: declarations only) and ``ref_harness/ref_driver.cu``, which exports C symbols that call
 the original's ``gather_skbs`` / ``scatter_skbs`` / ``sg_on_gpu`` / ``WaitForAppRunComplete``.  The output directory is
 git-ignored.  On a machine without the original tree an already built library is used as is.
@@ -17,7 +17,10 @@ import subprocess
 import sys
 from pathlib import Path
 
+import os
+
 HERE = Path(__file__).resolve().parent
+DEFAULT_SRC = os.environ.get("SPLITRPC_REFERENCE_SRC") or str(HERE.parent.parent / "reference" / "src")
 OUT = HERE / "_ref"
 LIB = OUT / "libsplitrpc_ref.so"
 GENCODE = ["-gencode", "arch=compute_100a,code=sm_100a"]
@@ -30,7 +33,7 @@ def _nvcc() -> str:
     raise RuntimeError("nvcc not found")
 
 
-def build(src: str = "/root/reference/src", force: bool = False) -> Path | None:
+def build(src: str = DEFAULT_SRC, force: bool = False) -> Path | None:
     """Returns the library path, or None when it neither exists nor can be built."""
     srcdir = Path(src)
     units = [srcdir / "transport" / "g_copy_ng.cu", HERE / "ref_harness" / "ref_driver.cu"]
@@ -62,7 +65,7 @@ def build(src: str = "/root/reference/src", force: bool = False) -> Path | None:
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--src", default="/root/reference/src")
+    ap.add_argument("--src", default=DEFAULT_SRC)
     ap.add_argument("--force", action="store_true")
     a = ap.parse_args()
     p = build(a.src, a.force)
