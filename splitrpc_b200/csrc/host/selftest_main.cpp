@@ -4,8 +4,9 @@
 //   g++ -std=c++17 -O1 -g -fsanitize=address,undefined -pthread -I splitrpc_b200/csrc selftest_main.cpp -o selftest_asan
 //
 // It runs the real server threads (receive, shunter, workers), the CPU scatter-gather engine, CPU apps, the load
-// generator with host-side fault injection, and a replica behind a batched server reached over the control socket
-// (ALLOC handshake, rings and doorbells shared through memfds, responses pushed by the serving side), all in one
+// generator with host-side fault injection, and replicas behind batched servers reached over the control socket
+// (ALLOC handshake, rings and doorbells shared through memfds, responses pushed by the serving side, requests pushed
+// by the ingress or fetched by the serving side from shared payload regions), all in one
 // process, and exits non-zero when a reply is wrong or missing.  The original has no such harness; its host code is
 // only ever run on the full testbed.
 #include <cstdio>
@@ -142,6 +143,48 @@ void scenario_remote(const std::string& sock) {
   expect(bs.counters.allocs == 1 && bs.counters.releases == 1 && bs.counters.peers_lost == 0, "batched server counters");
 }
 
+// Pull mode: the ingress shares its receive arena, describes each request in the slot's descriptor block, and the
+// serving side's fetch thread moves the bytes (CPU engine) before its worker sees the slot.
+void scenario_pull(const std::string& sock) {
+  set_rpc_mtu(1024);
+  auto remote_app = make_cpu_app(cpu_echo_run, 3000, 1000, 64, 4);
+  P2pRpcSgCpuEngine fetch_engine;
+  NvlBatchedServer bs(remote_app.get(), sock, 57, 2, 4);
+  bs.set_pull_engine(&fetch_engine);
+  expect(bs.start(), "batched server listens (pull)");
+  Link l = make_link(1024, 2048);
+  ServerConfig sc;
+  sc.req_size = 3000;
+  sc.resp_size = 1000;
+  sc.server_mode = 2;
+  sc.max_batch = 4;
+  {
+    SplitRpcServer srv(l.server.get(), sc);
+    std::string err;
+    auto remote = NvlRemoteReplica::connect(sock, 57, -1, 2, srv.tx_arena(), 3000, &err, l.server.get());
+    expect(remote != nullptr && remote->pulls(), "ALLOC handshake with payload regions");
+    if (!remote) return;
+    srv.add_remote_replica(remote.get());
+    srv.start();
+    ClientConfig cc;
+    cc.req_size = 3000;
+    cc.resp_size = 1000;
+    cc.total_requests = 300;
+    cc.num_warmup = 0;
+    cc.verify = true;
+    P2pRpcAppClient cli(l.client.get(), cc, echo_fill, echo_check);
+    cli.PreProcessRequests();
+    bool ok = cli.run_closed_loop(6);
+    ServerStats st = srv.stats();
+    srv.stop();
+    expect(ok && cli.received() == 300 && cli.verify_failures() == 0, "echo through a replica that fetches its requests itself");
+    expect(st.replicas.size() == 1 && st.replicas[0].pushed == 300, "responses were pushed by the serving side");
+    expect(bs.pulled() == 300 && bs.pull_errors() == 0, "every request was fetched from its descriptors");
+    expect(remote->release(), "RELEASE (pull)");
+  }
+  bs.stop();
+}
+
 // A producer that vanishes without RELEASE.
 void scenario_lost_peer(const std::string& sock) {
   auto app = make_cpu_app(cpu_echo_run, 1024, 1024, 64, 4);
@@ -165,6 +208,7 @@ int main(int argc, char** argv) {
   srpc_set_log_level(SRPC_LOG_ERROR);
   scenario_modes();
   scenario_remote(dir + "/srpc_selftest_a.sock");
+  scenario_pull(dir + "/srpc_selftest_c.sock");
   scenario_lost_peer(dir + "/srpc_selftest_b.sock");
   std::printf("%s\n", fails ? "SELFTEST FAILED" : "SELFTEST OK");
   return fails ? 1 : 0;
