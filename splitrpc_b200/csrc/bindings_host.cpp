@@ -743,6 +743,22 @@ PYBIND11_MODULE(_C, m) {
              d["pool_size"] = pool->get_pool_size();
              return d;
            })
+      // Writes a fragment list straight into a remote slot's descriptor block and marks the slot RX_DESCRIBED (tests of
+      // the serving side's checks; the server's own describe engine never produces a list that fails them).
+      .def("remote_describe_raw",
+           [](ServerHolder& s, int remote_idx, int slot, std::vector<std::tuple<uint32_t, uint64_t, uint32_t>> frags) {
+             P2pRpcAppRrPool* pool = s.remotes.at((size_t)remote_idx)->pool();
+             P2pRpcAppRrMemPool* mp = pool->rr_mem_pool;
+             if (frags.size() > mp->desc_per_slot()) throw std::invalid_argument("more fragments than the descriptor block holds");
+             SrpcSlotDesc* d = mp->get_slot_desc(slot);
+             uint32_t dst = 0;
+             for (size_t i = 0; i < frags.size(); i++) {
+               d->frag[i] = SrpcFragDesc{((uint64_t)std::get<0>(frags[i]) << 56) | std::get<1>(frags[i]), std::get<2>(frags[i]), dst};
+               dst += std::get<2>(frags[i]);
+             }
+             d->n_frags = (uint32_t)frags.size();
+             __atomic_store_n(pool->get_app_rr(slot)->h_state, (uint32_t)APP_RR_STATUS::RX_DESCRIBED, __ATOMIC_RELEASE);
+           })
       .def("remote_slot_state", [](ServerHolder& s, int remote_idx, int slot) {
         return (uint32_t)__atomic_load_n(s.remotes.at((size_t)remote_idx)->pool()->get_app_rr(slot)->h_state, __ATOMIC_ACQUIRE);
       })

@@ -84,18 +84,23 @@ class NvlBatchedServer {
         continue;
       }
       backoff.busy();
-      bool ok = true;
+      int good = 0;
       for (int j = 0; j < k; j++) {
         const int slot = (pi + j) % n;
         const SrpcSlotDesc* d = mp->get_slot_desc(slot);
         P2pRpcRr* r = rr[(size_t)slot].get();
         r->clear_bufs();
+        // The descriptors come from another process: nothing in them is trusted.  A request may name at most as many
+        // bytes as a ring slot holds, every fragment must lie inside a mapped region.
         const uint32_t nf = d->n_frags;
-        if (nf == 0 || nf > mp->desc_per_slot() || nf > MAX_BI_SIZE) ok = false;
+        bool ok = nf > 0 && nf <= mp->desc_per_slot() && nf <= MAX_BI_SIZE;
+        uint64_t total = 0;
         for (uint32_t f = 0; ok && f < nf; f++) {
           const uint32_t region = (uint32_t)(d->frag[f].where >> 56);
           const uint64_t off = d->frag[f].where & ((1ull << 56) - 1);
-          if (region >= (uint32_t)n_regions_.load(std::memory_order_acquire) || off + d->frag[f].len > regions_[region].bytes) {
+          total += d->frag[f].len;
+          if (d->frag[f].len == 0 || total > app_->req_size || region >= (uint32_t)n_regions_.load(std::memory_order_acquire) ||
+              off + d->frag[f].len > regions_[region].bytes) {
             ok = false;
             break;
           }
@@ -103,19 +108,27 @@ class NvlBatchedServer {
           r->payload_bufs->burst_items[f] = (uintptr_t)(base + off);
           r->payload_bufs->item_size[f] = d->frag[f].len;
         }
-        r->payload_bufs->num_items = ok ? (uint16_t)nf : 0;
+        volatile uint32_t* hstate = pool->get_app_rr(slot)->h_state;
+        if (!ok) {
+          // Hand the slot on anyway (the app answers with whatever the ring holds) rather than stall the ring.
+          pull_errors_++;
+          srpc_log(SRPC_LOG_ERROR, "pull: slot %d carries a malformed fragment list", slot);
+          __atomic_store_n(hstate, (uint32_t)APP_RR_STATUS::RX_COMPLETE, __ATOMIC_RELEASE);
+          continue;
+        }
+        r->payload_bufs->num_items = (uint16_t)nf;
         stubs[(size_t)slot] = pool->window_stub(seq + (uint64_t)j);
-        rp[(size_t)j] = r;
-        sp[(size_t)j] = &stubs[(size_t)slot];
-        hs[(size_t)j] = pool->get_app_rr(slot)->h_state;
-        ds[(size_t)j] = pool->get_app_rr(slot)->d_state;
+        rp[(size_t)good] = r;
+        sp[(size_t)good] = &stubs[(size_t)slot];
+        hs[(size_t)good] = hstate;
+        ds[(size_t)good] = pool->get_app_rr(slot)->d_state;
+        good++;
       }
-      int64_t ticket = ok ? pull_engine_->gather_batch_notify(rp.data(), sp.data(), hs.data(), ds.data(), k, (uint32_t)APP_RR_STATUS::RX_COMPLETE) : -1;
-      if (ticket < 0) {
-        // Hand the slots on anyway (the app answers with whatever the ring holds) rather than stall the ring.
-        pull_errors_++;
-        srpc_log(SRPC_LOG_ERROR, "pull: could not fetch %d described request(s)", k);
-        for (int j = 0; j < k; j++) __atomic_store_n(hs[(size_t)j], (uint32_t)APP_RR_STATUS::RX_COMPLETE, __ATOMIC_RELEASE);
+      if (good > 0 &&
+          pull_engine_->gather_batch_notify(rp.data(), sp.data(), hs.data(), ds.data(), good, (uint32_t)APP_RR_STATUS::RX_COMPLETE) < 0) {
+        pull_errors_ += (uint64_t)good;
+        srpc_log(SRPC_LOG_ERROR, "pull: could not fetch %d described request(s)", good);
+        for (int j = 0; j < good; j++) __atomic_store_n(hs[(size_t)j], (uint32_t)APP_RR_STATUS::RX_COMPLETE, __ATOMIC_RELEASE);
       }
       pulled_ += (uint64_t)k;
       pi = (pi + k) % n;

@@ -243,3 +243,38 @@ def test_host_driven_completion_still_works(C, mtu1k):
     st = srv.stats()
     srv.stop()
     assert st["replicas"][0]["pushed"] == 0 and not app.completion_by_device
+
+
+def test_serving_side_refuses_malformed_descriptors(C, mtu1k, tmp_path):
+    """Descriptor blocks are written by another process, so the serving side checks them: an unknown region, a fragment
+    past the end of its region, more bytes than a ring slot holds and an empty list are counted as fetch errors and
+    nothing is copied; the slot is still handed on, so the ring does not stall."""
+    proc, path, stop, out = _spawn(tmp_path, "bad", mode=-1, resp=1024)  # no worker: the test watches the slot states
+    try:
+        srv, cp = _ingress(C, [path], resp=1024, pull=True)
+        assert srv.remote_info(0)["pull"] == 1
+        arena = 1024 * 2048  # the receive arena of _ingress (region 0)
+        bad = [
+            [(3, 0, 1024)],                       # region that was never shared
+            [(0, arena - 512, 1024)],             # runs past the end of region 0
+            [(0, 0, 4096), (0, 4096, 1024)],      # 5120 bytes into a 4096-byte slot
+            [],                                   # nothing at all
+        ]
+        for slot, frags in enumerate(bad):
+            srv.remote_describe_raw(0, slot, frags)
+        deadline = time.time() + 5
+        while time.time() < deadline and any(srv.remote_slot_state(0, s) != 1 for s in range(len(bad))):
+            time.sleep(0.01)
+        assert [srv.remote_slot_state(0, s) for s in range(len(bad))] == [1] * len(bad)  # RX_COMPLETE
+        # a well-formed list right after them is fetched
+        srv.remote_describe_raw(0, len(bad), [(0, 0, 4096)])
+        deadline = time.time() + 5
+        while time.time() < deadline and srv.remote_slot_state(0, len(bad)) != 1:
+            time.sleep(0.01)
+        assert srv.remote_slot_state(0, len(bad)) == 1
+        srv.release_remotes()
+    finally:
+        stop.set()
+        _, _, pulled = out.get(timeout=20)
+        proc.join(20)
+    assert pulled["errors"] == len(bad) and pulled["pulled"] == len(bad) + 1
