@@ -70,6 +70,7 @@ class SplitRpcServer {
     P2pRpcSgEngine* engine;
     int64_t ticket;
     std::vector<uint32_t> rx_slots;
+    const std::atomic<bool>* replica_down;  // a replica that died will never take its requests out of the buffers
   };
 
   Transport* port_;
@@ -160,7 +161,7 @@ class SplitRpcServer {
     uint64_t t0 = getCurNs();
     while (!inflight_.empty()) {
       Inflight& f = inflight_.front();
-      if (!f.engine->ticket_done(f.ticket)) {
+      if (!f.engine->ticket_done(f.ticket) && !(f.replica_down && f.replica_down->load(std::memory_order_acquire))) {
         if (!wait_all || getCurNs() - t0 > 2000000000ull) return;
         continue;
       }
@@ -298,7 +299,7 @@ class SplitRpcServer {
         did_work = true;
         NVTX_R("gather");
         Replica& rep = *replicas_[target];
-        Inflight fl{rep.engine, 0, {}};
+        Inflight fl{rep.engine, 0, {}, rep.remote ? &rep.down : nullptr};
         if (!cfg_.zerocopy) {
           // Transmit buffers first: the serving side reads a slot's response destination as soon as it sees the
           // doorbell, so the destination has to be in place before the gather (which rings the doorbell) is launched.

@@ -173,12 +173,13 @@ def test_local_and_remote_replicas_share_one_ingress(C, mtu1k, tmp_path):
     assert sum(served) + steered[0] == 300
 
 
-def test_ingress_skips_a_replica_whose_process_died(C, mtu1k, tmp_path):
+@pytest.mark.parametrize("pull", [False, True])
+def test_ingress_skips_a_replica_whose_process_died(C, mtu1k, tmp_path, pull):
     """The replica's process exits between two bursts (no request in flight).  The ingress learns of it on the control
     socket and steers everything to the surviving replica."""
-    proc, path, stop, out = _spawn(tmp_path, "dead", app_name="echo", req=1024, resp=1024)
+    proc, path, stop, out = _spawn(tmp_path, f"dead{int(pull)}", app_name="echo", req=1024, resp=1024)
     local = C.make_app("echo", -1, 1024, 1024, [], 64, 1, 4, "cpu")
-    srv, cp = _ingress(C, [path], local_app=local, req=1024, resp=1024)
+    srv, cp = _ingress(C, [path], local_app=local, req=1024, resp=1024, pull=pull)
     srv.start()
     cli = C.Client(cp, req_size=1024, resp_size=1024, total=80, warmup=0, payload="echo", verify=True)
     assert cli.run_closed_loop(8) and cli.received == 80
