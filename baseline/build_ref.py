@@ -63,6 +63,50 @@ def build(src: str = DEFAULT_SRC, force: bool = False) -> Path | None:
     return LIB
 
 
+LSTM_LIB = OUT / "libsplitrpc_ref_lstm.so"
+LSTM_DIR = OUT / "lstm"  # holds Constant/, copied from the original tree
+
+
+def build_lstm(src: str = DEFAULT_SRC, force: bool = False) -> Path | None:
+    """The original's generated LSTM runtime (``src/apps/nnfusion_lstm/nnfusion_rt.cu``, unmodified) as a library with
+    the C entry points of ``ref_harness/ref_lstm_driver.cu``, and a copy of its ``Constant/`` directory beside it.
+    Two build-time stand-ins: the shim headers of the copy engine's build, and a force-included header that routes the
+    device-side ``cudaDeviceSynchronize`` of its dynamic-parallelism entry point (gone from CUDA 12, never called by
+    the harness) to a no-op.  Returns the library path, or None when it neither exists nor can be built."""
+    srcdir = Path(src)
+    app = srcdir / "apps" / "nnfusion_lstm"
+    units = [app / "nnfusion_rt.cu", HERE / "ref_harness" / "ref_lstm_driver.cu"]
+    have = LSTM_LIB.exists() and (LSTM_DIR / "Constant").is_dir()
+    if not units[0].exists():
+        return LSTM_LIB if have else None
+    OUT.mkdir(exist_ok=True)
+    key = hashlib.sha256(b"".join(u.read_bytes() for u in units)).hexdigest()
+    stamp = OUT / "build_lstm.stamp"
+    if have and stamp.exists() and stamp.read_text() == key and not force:
+        return LSTM_LIB
+    shims = HERE / "ref_harness" / "shims"
+    inc = [f"-I{srcdir}", f"-I{srcdir / 'utils'}", f"-I{srcdir / 'utils' / 'nv_helpers'}", f"-I{srcdir / 'transport'}", f"-I{app}",
+           f"-I{shims}", "-include", str(shims / "cdp_sync_shim.h")]
+    flags = GENCODE + ["-O3", "-std=c++17", "-rdc=true", "-lineinfo", "-w", "-Xcompiler", "-fPIC"]
+    objs = []
+    for u in units:
+        o = OUT / (u.stem + ".o")
+        r = subprocess.run([_nvcc(), "-c", str(u), "-o", str(o)] + flags + inc, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError(f"reference LSTM build failed for {u}:\n{r.stderr[-4000:]}")
+        objs.append(str(o))
+    r = subprocess.run([_nvcc(), "-shared", "-o", str(LSTM_LIB)] + objs + GENCODE + ["-cudart", "static", "-lcudadevrt"],
+                       capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"reference LSTM link failed:\n{r.stderr[-4000:]}")
+    if (LSTM_DIR / "Constant").exists():
+        shutil.rmtree(LSTM_DIR / "Constant")
+    LSTM_DIR.mkdir(exist_ok=True)
+    shutil.copytree(app / "Constant", LSTM_DIR / "Constant")
+    stamp.write_text(key)
+    return LSTM_LIB
+
+
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--src", default=DEFAULT_SRC)
@@ -70,4 +114,6 @@ if __name__ == "__main__":
     a = ap.parse_args()
     p = build(a.src, a.force)
     print(p if p else "unavailable: no original tree and no prebuilt library")
+    q = build_lstm(a.src, a.force)
+    print(q if q else "LSTM: unavailable: no original tree and no prebuilt library")
     sys.exit(0 if p else 1)

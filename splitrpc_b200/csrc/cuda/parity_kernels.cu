@@ -257,6 +257,122 @@ lstm_wavefront_kernel(const g_params* stub, const float* direct_in, float* direc
   }
 }
 
+// ------------------------------------------------------------------ LSTM, whole-GPU wavefront
+// The cluster kernel above gives a layer one SM, whose threads each walk one 1 KB weight row: a wave takes 74 us.  Here
+// every wave is spread over the whole GPU.  A work item is (layer, hidden unit): a warp loads the unit's four gate
+// rows of W and U (8 KB, coalesced 16-byte loads, kept in registers), then for every request of the group forms the
+// four dot products with the layer's input and previous hidden state, reduces them across the warp and lets lane 0
+// update the unit's cell and hidden state.  Up to eight requests share one pass over the weights; larger batches are
+// served group after group.  Waves are separated by a grid-wide barrier (the kernel is launched cooperatively, so all
+// blocks are resident; the wait on the barrier word is bounded).  Layer outputs of a wave live in hbuf[wave parity],
+// which the next wave reads as input (layer below) and as previous state (same layer).
+constexpr int LSTM_GROUP = 8;
+constexpr long long LSTM_BARRIER_CYCLES = 4000000000ll;
+
+struct LstmGridArgs {
+  const g_params* stub;
+  const float* direct_in;
+  float* direct_out;
+  const float* weights;
+  float* hbuf;        // [2][LLAYERS][LSTM_GROUP][LH]
+  float* cbuf;        // [LLAYERS][LSTM_GROUP][LH]
+  unsigned* counter;  // zeroed before the launch
+  uint32_t* status;   // may be null
+  int batch;
+  float forget_bias;
+};
+
+__device__ __forceinline__ float dot4(const float4& a, const float4& b) { return a.x * b.x + a.y * b.y + a.z * b.z + a.w * b.w; }
+
+__global__ void __launch_bounds__(256) lstm_grid_kernel(const LstmGridArgs a) {
+  __shared__ unsigned s_ok;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int gw = blockIdx.x * 8 + warp, nw = gridDim.x * 8;
+  const float* in_base = a.direct_in ? a.direct_in : reinterpret_cast<const float*>(a.stub->req);
+  float* out_base = a.direct_out ? a.direct_out : reinterpret_cast<float*>(a.stub->resp);
+  const size_t per_layer = (size_t)8 * LH * LH + 4 * LH;
+  unsigned target = 0;
+  for (int g0 = 0; g0 < a.batch; g0 += LSTM_GROUP) {
+    const int nb = a.batch - g0 < LSTM_GROUP ? a.batch - g0 : LSTM_GROUP;
+    for (int d = 0; d < LLAYERS + LSTEPS - 1; d++) {
+      const int l_lo = d - (LSTEPS - 1) > 0 ? d - (LSTEPS - 1) : 0, l_hi = d < LLAYERS - 1 ? d : LLAYERS - 1;
+      const int n_items = (l_hi - l_lo + 1) * LH;
+      const float* h_read = a.hbuf + (size_t)((d + 1) & 1) * LLAYERS * LSTM_GROUP * LH;  // what wave d-1 wrote
+      float* h_write = a.hbuf + (size_t)(d & 1) * LLAYERS * LSTM_GROUP * LH;
+      for (int it = gw; it < n_items; it += nw) {
+        const int l = l_lo + it / LH, j = it % LH, t = d - l;
+        const float* W = a.weights + (size_t)l * per_layer;
+        const float* U = W + (size_t)4 * LH * LH;
+        const float* B = U + (size_t)4 * LH * LH;
+        float4 w[4][2], u[4][2];
+#pragma unroll
+        for (int g = 0; g < 4; g++) {
+          const float4* wr = reinterpret_cast<const float4*>(W + ((size_t)g * LH + j) * LH);
+          w[g][0] = __ldg(wr + lane);
+          w[g][1] = __ldg(wr + 32 + lane);
+          if (t > 0) {
+            const float4* ur = reinterpret_cast<const float4*>(U + ((size_t)g * LH + j) * LH);
+            u[g][0] = __ldg(ur + lane);
+            u[g][1] = __ldg(ur + 32 + lane);
+          } else {
+            u[g][0] = u[g][1] = make_float4(0.f, 0.f, 0.f, 0.f);
+          }
+        }
+        const float bi = B[j], bg = B[LH + j], bf = B[2 * LH + j] + a.forget_bias, bo = B[3 * LH + j];
+        for (int b = 0; b < nb; b++) {
+          const float4* xv = l == 0 ? reinterpret_cast<const float4*>(in_base + ((size_t)(g0 + b) * LSTEPS + t) * LH)
+                                    : reinterpret_cast<const float4*>(h_read + ((size_t)(l - 1) * LSTM_GROUP + b) * LH);
+          const float4 x0 = __ldcg(xv + lane), x1 = __ldcg(xv + 32 + lane);
+          float sum[4];
+#pragma unroll
+          for (int g = 0; g < 4; g++) sum[g] = dot4(w[g][0], x0) + dot4(w[g][1], x1);
+          if (t > 0) {
+            const float4* hv = reinterpret_cast<const float4*>(h_read + ((size_t)l * LSTM_GROUP + b) * LH);
+            const float4 h0 = __ldcg(hv + lane), h1 = __ldcg(hv + 32 + lane);
+#pragma unroll
+            for (int g = 0; g < 4; g++) sum[g] += dot4(u[g][0], h0) + dot4(u[g][1], h1);
+          }
+#pragma unroll
+          for (int o = 16; o; o >>= 1) {
+#pragma unroll
+            for (int g = 0; g < 4; g++) sum[g] += __shfl_xor_sync(0xffffffffu, sum[g], o);
+          }
+          if (lane == 0) {
+            float* cp = a.cbuf + ((size_t)l * LSTM_GROUP + b) * LH + j;
+            const float c_prev = t > 0 ? *cp : 0.f;
+            const float c = sigmoidf_(sum[2] + bf) * c_prev + sigmoidf_(sum[0] + bi) * tanhf(sum[1] + bg);
+            const float h = tanhf(c) * sigmoidf_(sum[3] + bo);
+            *cp = c;
+            h_write[((size_t)l * LSTM_GROUP + b) * LH + j] = h;
+            if (l == LLAYERS - 1 && t == LSTEPS - 1) out_base[(size_t)(g0 + b) * LH + j] = h;
+          }
+        }
+      }
+      // grid-wide barrier, bounded
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        target += gridDim.x;
+        __threadfence();
+        atomicAdd(a.counter, 1u);
+        unsigned ok = 1;
+        const long long t0 = clock64();
+        while ((int)(ptx::ld_acquire_gpu(a.counter) - target) < 0) {
+          if (clock64() - t0 > LSTM_BARRIER_CYCLES) {
+            ok = 0;
+            break;
+          }
+        }
+        s_ok = ok;
+      }
+      __syncthreads();
+      if (!s_ok) {
+        if (threadIdx.x == 0 && a.status) atomicExch(a.status, 0x4C53u);  // 'LS': the LSTM's grid barrier ran out
+        return;
+      }
+    }
+  }
+}
+
 }  // namespace
 
 cudaError_t srpc_swap_hdrs(void* const* d_hdr_ptrs, void* d_hdrs_contig, int n, int clear_sockperf, cudaStream_t s) {
@@ -407,13 +523,55 @@ void srpc_parity_preload() {
   (void)cudaFuncGetAttributes(&fa, swap_hdrs_contig_kernel);
   (void)cudaFuncGetAttributes(&fa, lenet_ref_kernel);
   (void)cudaFuncGetAttributes(&fa, lstm_wavefront_kernel);
+  (void)cudaFuncGetAttributes(&fa, lstm_grid_kernel);
   (void)cudaGetLastError();
 }
 
-size_t srpc_lstm_scratch_bytes(int max_clusters) { return (size_t)max_clusters * LLAYERS * LSTEPS * LH * sizeof(float); }
+static constexpr size_t kLstmHbufFloats = (size_t)2 * LLAYERS * LSTM_GROUP * LH, kLstmCbufFloats = (size_t)LLAYERS * LSTM_GROUP * LH;
+static size_t lstm_grid_scratch_bytes() { return (kLstmHbufFloats + kLstmCbufFloats) * sizeof(float) + 256; }
+
+size_t srpc_lstm_scratch_bytes(int max_clusters) {
+  const size_t cluster_form = (size_t)max_clusters * LLAYERS * LSTEPS * LH * sizeof(float);
+  return cluster_form > lstm_grid_scratch_bytes() ? cluster_form : lstm_grid_scratch_bytes();
+}
 
 cudaError_t srpc_lstm(const void* d_stub, const float* direct_in, float* direct_out, const float* weights, float* scratch,
                       int max_clusters, int batch, float forget_bias, cudaStream_t s) {
+  if (batch < 1) return cudaSuccess;
+  // Whole-GPU wavefront (cooperative launch); SPLITRPC_LSTM_CLUSTER=1 or a refused cooperative launch falls back to
+  // the one-cluster-per-request kernel.
+  static const int use_cluster = [] { const char* e = getenv("SPLITRPC_LSTM_CLUSTER"); return e ? atoi(e) : 0; }();
+  static int grid_blocks = 0;
+  if (!use_cluster) {
+    if (!grid_blocks) {
+      int dev = 0, sms = 0, per_sm = 0, coop = 0;
+      cudaGetDevice(&dev);
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+      cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev);
+      cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, lstm_grid_kernel, 256, 0);
+      grid_blocks = (coop && sms > 0 && per_sm > 0) ? sms : -1;
+    }
+    if (grid_blocks > 0) {
+      LstmGridArgs a;
+      a.stub = (const g_params*)d_stub;
+      a.direct_in = direct_in;
+      a.direct_out = direct_out;
+      a.weights = weights;
+      a.hbuf = scratch;
+      a.cbuf = scratch + kLstmHbufFloats;
+      a.counter = reinterpret_cast<unsigned*>(scratch + kLstmHbufFloats + kLstmCbufFloats);
+      a.status = nullptr;
+      a.batch = batch;
+      a.forget_bias = forget_bias;
+      cudaError_t e = cudaMemsetAsync(a.counter, 0, sizeof(unsigned), s);
+      if (e != cudaSuccess) return e;
+      void* args[] = {&a};
+      e = cudaLaunchCooperativeKernel((const void*)lstm_grid_kernel, dim3((unsigned)grid_blocks), dim3(256), args, 0, s);
+      if (e == cudaSuccess) return cudaSuccess;
+      (void)cudaGetLastError();
+      grid_blocks = -1;  // not possible on this device or in this context: use the cluster kernel from now on
+    }
+  }
   int clusters = batch < max_clusters ? batch : max_clusters;
   if (clusters < 1) return cudaSuccess;
   lstm_wavefront_kernel<<<clusters * LLAYERS, 1024, 0, s>>>((const g_params*)d_stub, direct_in, direct_out, weights, scratch,

@@ -212,6 +212,7 @@ static inline std::string load_lstm_constant_dir(const std::string& dir, const s
     (*out)[3 * l + 2].assign((size_t)4 * H, 0.f);
   }
   std::vector<uint8_t> seen((size_t)layers * 12, 0);
+  float forget_bias = 0.f;
   std::string line;
   int line_no = 0;
   std::vector<float> buf;
@@ -219,6 +220,11 @@ static inline std::string load_lstm_constant_dir(const std::string& dir, const s
     line_no++;
     if (line.empty() || line[0] == '#') continue;
     std::istringstream ss(line);
+    if (line.compare(0, 11, "forget_bias") == 0) {  // "forget_bias <value>": added to every forget-gate bias
+      std::string word;
+      if (!(ss >> word >> forget_bias)) return "manifest line " + std::to_string(line_no) + ": expected forget_bias <value>";
+      continue;
+    }
     int layer = -1, id = -1;
     std::string kind, gate, flag;
     if (!(ss >> layer >> kind >> gate >> id)) return "manifest line " + std::to_string(line_no) + ": expected <layer> <W|U|b> <gate> <id>";
@@ -244,6 +250,9 @@ static inline std::string load_lstm_constant_dir(const std::string& dir, const s
   }
   for (size_t i = 0; i < seen.size(); i++)
     if (!seen[i]) return "manifest does not name layer " + std::to_string(i / 12) + " tensor " + std::to_string((i % 12) / 4) + " gate " + std::to_string(i % 4);
+  if (forget_bias != 0.f)  // the cell of the apps adds no constant of its own: fold it into the bias (gate order i, g, f, o)
+    for (int l = 0; l < layers; l++)
+      for (int j = 0; j < H; j++) (*out)[3 * l + 2][(size_t)2 * H + j] += forget_bias;
   return "";
 }
 
