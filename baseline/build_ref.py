@@ -107,6 +107,42 @@ def build_lstm(src: str = DEFAULT_SRC, force: bool = False) -> Path | None:
     return LSTM_LIB
 
 
+LENET_LIB = OUT / "libsplitrpc_ref_lenet.so"
+
+
+def build_lenet(src: str = DEFAULT_SRC, force: bool = False) -> Path | None:
+    """The original's LeNet (``src/apps/lenet/lenet_vanilla.cu``, unmodified) with the C entry points of
+    ``ref_harness/ref_lenet_driver.cu``; same stand-ins as ``build_lstm`` plus a header that maps the NVTX v2 include
+    name onto NVTX v3.  Returns the library path, or None when it neither exists nor can be built."""
+    srcdir = Path(src)
+    app = srcdir / "apps" / "lenet"
+    units = [app / "lenet_vanilla.cu", HERE / "ref_harness" / "ref_lenet_driver.cu"]
+    if not units[0].exists():
+        return LENET_LIB if LENET_LIB.exists() else None
+    OUT.mkdir(exist_ok=True)
+    key = hashlib.sha256(b"".join(u.read_bytes() for u in units)).hexdigest()
+    stamp = OUT / "build_lenet.stamp"
+    if LENET_LIB.exists() and stamp.exists() and stamp.read_text() == key and not force:
+        return LENET_LIB
+    shims = HERE / "ref_harness" / "shims"
+    inc = [f"-I{srcdir}", f"-I{srcdir / 'utils'}", f"-I{srcdir / 'utils' / 'nv_helpers'}", f"-I{srcdir / 'transport'}", f"-I{app}",
+           f"-I{shims}", "-include", str(shims / "cdp_sync_shim.h")]
+    flags = GENCODE + ["-O3", "-std=c++17", "-rdc=true", "-lineinfo", "-w", "-Xcompiler", "-fPIC"]
+    objs = []
+    for u in units:
+        o = OUT / (u.stem + ".o")
+        r = subprocess.run([_nvcc(), "-c", str(u), "-o", str(o)] + flags + inc, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError(f"reference LeNet build failed for {u}:\n{r.stderr[-4000:]}")
+        objs.append(str(o))
+    r = subprocess.run([_nvcc(), "-shared", "-o", str(LENET_LIB)] + objs + GENCODE + ["-cudart", "static", "-lcudadevrt"],
+                       capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"reference LeNet link failed:\n{r.stderr[-4000:]}")
+    stamp.write_text(key)
+    return LENET_LIB
+
+
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--src", default=DEFAULT_SRC)
@@ -116,4 +152,6 @@ if __name__ == "__main__":
     print(p if p else "unavailable: no original tree and no prebuilt library")
     q = build_lstm(a.src, a.force)
     print(q if q else "LSTM: unavailable: no original tree and no prebuilt library")
+    r = build_lenet(a.src, a.force)
+    print(r if r else "LeNet: unavailable: no original tree and no prebuilt library")
     sys.exit(0 if p else 1)

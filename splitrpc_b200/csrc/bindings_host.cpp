@@ -580,6 +580,21 @@ PYBIND11_MODULE(_C, m) {
              a.info->stage_window(first_slot, batch, armed);
            },
            py::arg("req"), py::arg("resp"), py::arg("first_slot"), py::arg("batch"), py::arg("armed") = false)
+      // Queues `n` runs of the app on the window of `batch` requests that starts at slot 0, back to back on the work
+      // stream, and returns without waiting: for device-side timing with events recorded on `work_stream` around it.
+      .def("queue_runs",
+           [](AppHolder& a, int batch, int n) {
+             AppCtx* c = a.info->app_ctx;
+             c->curr_batch_size = batch;
+             *c->h_stub = *a.info->app_rr_pool->get_app_rr(0)->h_stub;
+             c->h_push->first_slot = 0;
+             std::atomic_thread_fence(std::memory_order_seq_cst);
+             for (int i = 0; i < n; i++) {
+               a.info->stage_window(0, batch, false);
+               a.info->app_run(c);
+             }
+           },
+           py::arg("batch"), py::arg("n"))
       .def_property_readonly("pool_size", [](AppHolder& a) { return a.info->app_rr_pool->get_pool_size(); })
       // Slot-level access for stand-alone timing loops and tests (the server's threads do all of this themselves):
       // device-side address of the slot state words, state and response destination of one slot, and a reset of the
