@@ -7,6 +7,7 @@
 
 #include "cuda/apps_gpu.h"
 #include "host/apps_cpu.h"
+#include "host/copy_path_runner.h"
 #include "host/dpdk_port.h"
 #include "host/loadgen.h"
 #include "host/p2p_rpc_compat.h"
@@ -133,6 +134,11 @@ struct AppHolder {
   std::unique_ptr<P2pRpcSgEngine> engine;
   std::string name;
   void* graph_internal = nullptr;  // state of a graph app (owned by the app's cleanup callback)
+};
+
+struct CopyPathHolder {
+  std::shared_ptr<AppHolder> app;
+  std::unique_ptr<CopyPathBatcher> batcher;
 };
 
 std::vector<std::vector<float>> to_weights(const std::vector<py::array_t<float, py::array::c_style | py::array::forcecast>>& ws) {
@@ -686,6 +692,47 @@ PYBIND11_MODULE(_C, m) {
           return py::make_tuple(ns, outs);
         },
         py::arg("app"), py::arg("iters"), py::arg("batch") = 1, py::arg("fill") = py::none());
+
+  // ---- the comparison system's copy path (requests from ordinary host memory, one copy in and out per request)
+  py::class_<CopyPathHolder, std::shared_ptr<CopyPathHolder>>(m, "CopyPathBatcher")
+      .def(py::init([](std::shared_ptr<AppHolder> app, int max_batch) {
+             auto h = std::make_shared<CopyPathHolder>();
+             h->app = app;
+             h->batcher.reset(new CopyPathBatcher(app->info.get(), max_batch));
+             return h;
+           }),
+           py::arg("app"), py::arg("max_batch") = 1)
+      // Blocks (without the interpreter lock) until the request has been through a batch; returns the response.
+      .def("submit",
+           [](CopyPathHolder& h, py::bytes req) {
+             char* data = nullptr;
+             Py_ssize_t len = 0;
+             if (PyBytes_AsStringAndSize(req.ptr(), &data, &len) != 0) throw py::error_already_set();
+             std::string resp(h.batcher->resp_size(), '\0');
+             bool ok;
+             {
+               py::gil_scoped_release rel;
+               ok = h.batcher->submit(data, (size_t)len, resp.data());
+             }
+             if (!ok) throw std::runtime_error("copy path: the batch failed or the worker has stopped");
+             return py::bytes(resp);
+           })
+      .def("times",
+           [](CopyPathHolder& h) {
+             CopyPathTimes t = h.batcher->times();
+             py::dict d;
+             d["h2d_ns"] = t.h2d_ns;
+             d["run_ns"] = t.run_ns;
+             d["d2h_ns"] = t.d2h_ns;
+             d["batches"] = t.batches;
+             d["requests"] = t.requests;
+             return d;
+           })
+      .def_property_readonly("max_batch", [](CopyPathHolder& h) { return h.batcher->max_batch(); })
+      .def("stop", [](CopyPathHolder& h) {
+        py::gil_scoped_release rel;
+        h.batcher->stop();
+      });
 
   // ---- server
   py::class_<ServerHolder, std::shared_ptr<ServerHolder>>(m, "Server")
