@@ -10,6 +10,7 @@ Prints the statistics of the measured requests as one JSON line, with the keys o
 from __future__ import annotations
 
 import argparse
+import os
 import json
 import math
 
@@ -34,11 +35,25 @@ def main(argv=None) -> int:
     ap.add_argument("--cov", type=float, default=1.0, help="open loop: coefficient of variation of the inter-arrival times")
     ap.add_argument("--threads", type=int, default=1)
     ap.add_argument("--verify", action="store_true")
+    ap.add_argument("--client-type", type=int, default=int(os.environ.get("P2P_RPC_CLIENT_TYPE", "0")),
+                    help="0: this package's protocol over kernel UDP; 1: the comparison system's gRPC client "
+                         "(reference src/lib_loadgen/dist_rpc_bench.cc:89-116)")
     ap.add_argument("--exp-name", default="splitrpc")
     ap.add_argument("--out-dir", default="")
     args = ap.parse_args(argv)
     _C.set_rpc_mtu(args.mtu)
     req, resp, kind = sizes(args.app, args.req_size, args.resp_size)
+    if args.client_type == 1:
+        from .grpc_baseline import GrpcClient
+
+        g = GrpcClient(f"{args.server_ip}:{args.server_port}", req)
+        st = g.run_closed_loop(max(1, args.outstanding), args.total, args.warmup)
+        g.close()
+        st["ok"] = st["errors"] == 0 and st["received"] == args.total
+        print(json.dumps(st), flush=True)
+        return 0 if st["ok"] else 1
+    if args.client_type != 0:
+        raise SystemExit("client type 2 (raw DPDK) needs a build with SPLITRPC_WITH_DPDK=1 and a NIC")
     frags = math.ceil(req / args.mtu) + math.ceil(resp / args.mtu)
     n_slots = max(1024, 4 * max(args.outstanding, 64) * frags)
     port, bound = _C.make_udp_port(args.bind_ip, args.bind_port, args.mtu, n_slots, args.server_ip, args.server_port)

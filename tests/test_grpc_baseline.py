@@ -76,3 +76,17 @@ def test_copy_path_server_lenet_matches_oracle(C):
         a, b = cli.one(77, cli.payloads[0]), cli.one(78, cli.payloads[0])
         assert a == b
         cli.close()
+
+
+def test_load_generator_client_type_1(C, capsys):
+    import json
+
+    from splitrpc_b200.utils import client
+
+    app = C.make_app("echo", -1, 1024, 1024, [], 64, 1, 2)
+    with GrpcCopyPathServer(app, 2) as srv:
+        host, port = srv.address.rsplit(":", 1)
+        rc = client.main(["--server-ip", host, "--server-port", port, "--app", "echo", "--req-size", "1024", "--resp-size", "1024",
+                          "--total", "40", "--warmup", "10", "--outstanding", "2", "--client-type", "1"])
+    out = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert rc == 0 and out["ok"] and out["received"] == 40
