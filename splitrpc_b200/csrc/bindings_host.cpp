@@ -1059,6 +1059,44 @@ PYBIND11_MODULE(_C, m) {
       while (pool.consume_rr()) taken++;
       d["v1_exhausts"] = taken == 8 && pool.consume_rr() == nullptr;
     }
+    // first-generation synchronous app server: 32 records through two instances of the CPU echo app
+    {
+      CpuAppState st;
+      st.req_size = st.resp_size = 64;
+      p2p_rpc_v1::P2pRpcAppServer srv(cpu_app_noop, cpu_echo_run, nullptr, cpu_app_noop, 2, -1, 64, 64, 64, &st);
+      p2p_rpc_v1::P2pRpcAppServer::Ring cq(64);
+      srv.register_cq(&cq);
+      std::vector<std::vector<uint8_t>> reqs(32, std::vector<uint8_t>(64)), resps(32, std::vector<uint8_t>(64));
+      std::vector<p2p_rpc_rr*> rrs;
+      for (int i = 0; i < 32; i++) {
+        for (int j = 0; j < 64; j++) reqs[i][j] = (uint8_t)(i * 7 + j);
+        p2p_rpc_rr* rr = rr_proto_alloc(conn, 64, 64);
+        rr->req_token = 100 + i;
+        rr->req_payload = reqs[i].data();
+        rr->resp_payload = resps[i].data();
+        rrs.push_back(rr);
+      }
+      srv.start();
+      bool queued = true;
+      for (p2p_rpc_rr* rr : rrs) queued = queued && srv.enqueue_work(rr);
+      int done = 0;
+      uint64_t seen = 0, t0 = getCurNs();
+      p2p_rpc_rr* out = nullptr;
+      while (done < 32 && getCurNs() - t0 < 5000000000ull) {
+        if (cq.pop(out)) {
+          done++;
+          seen += out->req_token;
+        } else {
+          std::this_thread::yield();
+        }
+      }
+      srv.stop();
+      bool same = true;
+      for (int i = 0; i < 32; i++) same = same && reqs[i] == resps[i];
+      d["v1_app_server"] = srv.init_ok() && queued && done == 32 && same && srv.num_serviced() == 32 && srv.num_failed() == 0 &&
+                           seen == 32 * 100 + 31 * 32 / 2;
+      for (p2p_rpc_rr* rr : rrs) rr_base_free(rr);
+    }
     release_conn_info(conn);
     // socket record + pool: a 2500-byte request through datagram buffers and back
     {

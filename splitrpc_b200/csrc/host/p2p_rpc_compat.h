@@ -13,13 +13,17 @@
 
 #include <netinet/in.h>
 
+#include <atomic>
+#include <memory>
 #include <mutex>
+#include <thread>
 #include <unordered_map>
 #include <vector>
 
 #include "mpmc_ring.h"
 #include "p2p_rpc.h"
 #include "p2p_rpc_app.h"
+#include "p2p_rpc_async_app_server.h"
 
 // ------------------------------------------------------------------ typed buffer pool
 // type -1: plain host memory.  type >= 0: memory that both the CPU and GPU `type` address (the original maps GPU
@@ -242,6 +246,87 @@ class P2pRpcRRPool {
     free_.push(rr);
   }
   size_t num_free() const { return free_.size(); }
+};
+
+// First-generation synchronous app server (reference src/p2p_rpc_app_server.h:31-284): records are submitted on a
+// ring; one worker per app instance takes a record, points the instance's stub at the record's request and response
+// buffers, runs the app, waits for it, and hands the record to the completion ring that the owner registered.  Each
+// instance is a P2pRpcAppInfo (stub, doorbell, stream), so the callbacks are the same ones the current server takes.
+class P2pRpcAppServer {
+ public:
+  using Ring = MpmcRing<p2p_rpc_rr*>;
+  P2pRpcAppServer(AppInitCB init, AppRunCB run, AppCleanupCB cleanup, AppCompleteCB complete, int num_instances, int device_id,
+                  size_t req_size, size_t resp_size, size_t queue_len = 1024, void* internal = nullptr)
+      : sub_queue_(queue_len) {
+    for (int i = 0; i < (num_instances < 1 ? 1 : num_instances); i++)
+      apps_.emplace_back(new P2pRpcAppInfo(init, run, cleanup, complete, device_id, req_size, resp_size, 1, internal, 1, 1));
+  }
+  ~P2pRpcAppServer() { stop(); }
+  bool init_ok() const {
+    for (auto& a : apps_)
+      if (!a->init_ok) return false;
+    return true;
+  }
+  int num_instances() const { return (int)apps_.size(); }
+  void register_cq(Ring* cq) { cq_ = cq; }
+  bool enqueue_work(p2p_rpc_rr* rr) { return sub_queue_.push(rr); }
+
+  // Points the instance's stub at the record and starts the app; does not wait.
+  void do_work(p2p_rpc_rr* rr, int instance = 0) {
+    P2pRpcAppInfo* a = apps_[instance].get();
+    a->app_ctx->h_stub->req = rr->req_payload;
+    a->app_ctx->h_stub->resp = rr->resp_payload;
+    std::atomic_thread_fence(std::memory_order_seq_cst);
+    a->stage_window(0, 1, false);
+    a->app_run(a->app_ctx);
+  }
+  bool sync(int instance = 0) {
+    P2pRpcAppInfo* a = apps_[instance].get();
+    bool ok = a->app_ctx->WaitForAppRunComplete();
+    if (a->app_complete) a->app_complete(a->app_ctx);
+    return ok;
+  }
+  bool do_work_sync(p2p_rpc_rr* rr, int instance = 0) {
+    do_work(rr, instance);
+    return sync(instance);
+  }
+
+  void start() {
+    if (!workers_.empty()) return;
+    stop_.store(false);
+    for (int i = 0; i < num_instances(); i++) workers_.emplace_back([this, i] { rpc_handler(i); });
+  }
+  void stop() {
+    stop_.store(true);
+    for (auto& t : workers_)
+      if (t.joinable()) t.join();
+    workers_.clear();
+  }
+  uint64_t num_serviced() const { return serviced_.load(); }
+  uint64_t num_failed() const { return failed_.load(); }
+
+ private:
+  void rpc_handler(int instance) {
+    IdleBackoff backoff;
+    p2p_rpc_rr* rr = nullptr;
+    while (!stop_.load(std::memory_order_acquire)) {
+      if (!sub_queue_.pop(rr)) {
+        backoff.empty();
+        continue;
+      }
+      backoff.busy();
+      if (!do_work_sync(rr, instance)) failed_.fetch_add(1);
+      serviced_.fetch_add(1);
+      if (cq_)
+        while (!cq_->push(rr) && !stop_.load(std::memory_order_acquire)) std::this_thread::yield();
+    }
+  }
+  std::vector<std::unique_ptr<P2pRpcAppInfo>> apps_;
+  Ring sub_queue_;
+  Ring* cq_ = nullptr;
+  std::vector<std::thread> workers_;
+  std::atomic<bool> stop_{false};
+  std::atomic<uint64_t> serviced_{0}, failed_{0};
 };
 
 }  // namespace p2p_rpc_v1
