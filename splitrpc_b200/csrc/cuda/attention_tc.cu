@@ -21,6 +21,7 @@
 #include "driver_api.h"
 #include "nn_kernels.h"
 #include "ptx.cuh"
+#include "per_device.h"
 
 namespace {
 
@@ -245,12 +246,13 @@ cudaError_t encode(CUtensorMap* m, const void* ptr, uint64_t inner, uint64_t out
 template <int SEQ, bool VMN>
 cudaError_t launch(const CUtensorMap& tqk, const CUtensorMap& tvt, void* out, int ld_out, const float* v_bias, int hidden,
                    int batch, int heads, uint32_t* status, cudaStream_t s) {
-  static bool attr = false;
+  static PerDeviceFlag attr;
+  const int dev = PerDeviceFlag::current();
   const int smem = AttSmem<SEQ>::TOTAL + 1024;
-  if (!attr) {
+  if (attr.needed(dev)) {
     cudaError_t e = cudaFuncSetAttribute(attention_tc<SEQ, VMN>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
-    attr = true;
+    attr.set(dev);
   }
   const float scale_log2e = 0.125f * 1.4426950408889634f;
   attention_tc<SEQ, VMN><<<dim3(heads, batch), ATT_THREADS, smem, s>>>(tqk, tvt, (__nv_bfloat16*)out, ld_out, v_bias, hidden,

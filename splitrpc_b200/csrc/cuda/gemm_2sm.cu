@@ -33,6 +33,7 @@
 #include <cstdlib>
 
 #include "gemm_tcgen05.h"
+#include "per_device.h"
 #include "ptx.cuh"
 #include "tp_device.cuh"
 
@@ -432,11 +433,13 @@ gemm_2sm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
 }
 
 
-// Clusters of two CTAs that can be resident at once (queried once per instantiation).
+// Clusters of two CTAs that can be resident at once (queried once per instantiation and device).
 template <int BN, bool TP>
 cudaError_t max_clusters_2sm(int* out) {
   using C = Cfg<BN>;
-  static int max_clusters = 0;
+  static std::atomic<int> per_device[64];
+  const int dev = PerDeviceFlag::current();
+  int max_clusters = per_device[dev].load(std::memory_order_acquire);
   if (!max_clusters) {
     cudaError_t e = cudaFuncSetAttribute(gemm_2sm_kernel<BN, TP>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
     if (e != cudaSuccess) return e;
@@ -456,6 +459,7 @@ cudaError_t max_clusters_2sm(int* out) {
     if (e != cudaSuccess) return e;
     if (n < 1) return cudaErrorInvalidConfiguration;
     max_clusters = n;
+    per_device[dev].store(n, std::memory_order_release);
   }
   *out = max_clusters;
   return cudaSuccess;

@@ -32,6 +32,7 @@
 
 #include "gemm_tcgen05.h"
 #include "ptx.cuh"
+#include "per_device.h"
 
 namespace {
 
@@ -753,12 +754,13 @@ int num_sms() {
 template <int BN, int STAGES, int OB>
 cudaError_t launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& to, const CUtensorMap& tr,
                    const TileParams& p_in, const GemmEpilogue& ep, int use_tma_store, uint32_t* status, cudaStream_t st) {
-  static bool attr = false;
+  static PerDeviceFlag attr;
+  const int dev = PerDeviceFlag::current();
   const int smem = STAGES * (BM * BK * 2 + BN * BK * 2) + OB * (BN / 64) * BM * 128;
-  if (!attr) {
+  if (attr.needed(dev)) {
     cudaError_t e = cudaFuncSetAttribute(gemm_conv_persistent<BN, STAGES, OB>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
-    attr = true;
+    attr.set(dev);
   }
   TileParams p = p_in;
   const int tiles = p.tiles_m * p.tiles_n;

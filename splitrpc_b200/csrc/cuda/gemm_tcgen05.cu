@@ -19,6 +19,7 @@
 // tensor memory and returns.
 #include "gemm_tcgen05.h"
 #include "ptx.cuh"
+#include "per_device.h"
 
 namespace {
 
@@ -374,12 +375,13 @@ cudaError_t set_smem(F f, int bytes) {
 template <int BN, int STAGES>
 cudaError_t launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, int M, int N, int K, const GemmEpilogue& ep,
                         uint32_t* status, cudaStream_t st) {
-  static bool attr = false;
+  static PerDeviceFlag attr;
+  const int dev = PerDeviceFlag::current();
   const int smem = STAGES * SmemLayout<BN>::STAGE_BYTES + 1024;
-  if (!attr) {
+  if (attr.needed(dev)) {
     cudaError_t e = set_smem(gemm_bf16_tma<BN, STAGES>, smem);
     if (e != cudaSuccess) return e;
-    attr = true;
+    attr.set(dev);
   }
   dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
   gemm_bf16_tma<BN, STAGES><<<grid, GEMM_THREADS, smem, st>>>(ta, tb, M, N, K, ep, status);
@@ -389,12 +391,13 @@ cudaError_t launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, int M, int
 template <int BN, int STAGES>
 cudaError_t launch_conv(const __nv_bfloat16* in, const CUtensorMap& tw, const ConvShape& cs, const GemmEpilogue& ep,
                         uint32_t* status, cudaStream_t st) {
-  static bool attr = false;
+  static PerDeviceFlag attr;
+  const int dev = PerDeviceFlag::current();
   const int smem = STAGES * SmemLayout<BN>::STAGE_BYTES + 1024;
-  if (!attr) {
+  if (attr.needed(dev)) {
     cudaError_t e = set_smem(conv_bf16_igemm<BN, STAGES>, smem);
     if (e != cudaSuccess) return e;
-    attr = true;
+    attr.set(dev);
   }
   const int M = cs.n * cs.oh * cs.ow;
   dim3 grid((cs.cout + BN - 1) / BN, (M + BM - 1) / BM);

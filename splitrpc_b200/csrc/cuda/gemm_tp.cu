@@ -33,6 +33,7 @@
 #include "gemm_tcgen05.h"
 #include "gemm_tp.h"
 #include "ptx.cuh"
+#include "per_device.h"
 #include "tp_device.cuh"
 
 namespace {
@@ -503,12 +504,13 @@ cudaError_t srpc_gemm_tp(const void* A, int lda, const void* B, int ldb, int M, 
   tp.tiles_per_owner = tp.mblocks_per_rank * tiles_n;
   if (!tp.mblock_ready) tp.n_copy = 0;
   tp.n_copy = std::min(tp.n_copy, std::max(1, (tp.tp - 1) * tp.mblocks_per_rank));  // a copier takes whole row blocks
-  static bool attr = false;
+  static PerDeviceFlag attr;
+  const int dev = PerDeviceFlag::current();
   const int smem = STAGES * STAGE_BYTES + 2 * OUT_BYTES + 1024;
-  if (!attr) {
+  if (attr.needed(dev)) {
     cudaError_t e = cudaFuncSetAttribute(gemm_tp_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
-    attr = true;
+    attr.set(dev);
   }
   CUtensorMap ta, tb, to;
   cudaError_t e = map_2d(&ta, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda * 2, BK, BM);

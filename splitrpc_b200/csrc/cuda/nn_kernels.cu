@@ -11,6 +11,7 @@
 
 #include "../host/p2p_rpc_app.h"
 #include "nn_kernels.h"
+#include "per_device.h"
 #include "ptx.cuh"
 #include "resp_push.cuh"
 
@@ -596,11 +597,12 @@ cudaError_t nn_fc_skinny(const void* a, int lda, const void* w, int ldw, const f
                          cudaStream_t s) {
   const size_t smem = (size_t)FC_NB * K * sizeof(float);
   if (K % 8 || lda % 8 || ldw % 8 || (((uintptr_t)a | (uintptr_t)w) & 15) || smem > 200 * 1024 || M <= 0) return cudaErrorInvalidValue;
-  static bool attr_set = false;
-  if (!attr_set) {
+  static PerDeviceFlag attr_set;
+  const int dev = PerDeviceFlag::current();
+  if (attr_set.needed(dev)) {
     cudaError_t e = cudaFuncSetAttribute(fc_skinny, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     if (e != cudaSuccess) return e;
-    attr_set = true;
+    attr_set.set(dev);
   }
   fc_skinny<<<dim3((N + FC_NB - 1) / FC_NB, (M + FC_ROWS - 1) / FC_ROWS), 256, smem, s>>>((const __nv_bfloat16*)a, lda, (const __nv_bfloat16*)w,
                                                                           ldw, bias, out, ldo, M, N, K);
@@ -647,10 +649,11 @@ cudaError_t nn_attention_d64(const void* qkv, void* out, int batch, int seq, int
                                                v_off, ld_out, scale);
   } else if (seq == 384) {
     const int smem = 384 * 66 * 2 + 384 * 64 * 2 + 8 * 384 * 4;
-    static bool attr = false;
-    if (!attr) {
+    static PerDeviceFlag attr;
+    const int dev = PerDeviceFlag::current();
+    if (attr.needed(dev)) {
       cudaFuncSetAttribute(attention_d64<384>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-      attr = true;
+      attr.set(dev);
     }
     attention_d64<384><<<grid, 256, smem, s>>>((const __nv_bfloat16*)qkv, (__nv_bfloat16*)out, heads, ld_qkv, q_off, k_off,
                                                v_off, ld_out, scale);
