@@ -25,6 +25,7 @@
 // is bounded; on a timeout the kernel records an error code, stops issuing work,
 // frees its tensor memory and returns.
 #include <algorithm>
+#include <cstdio>
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
@@ -923,6 +924,15 @@ cudaError_t srpc_gemm_bf16_v2(const void* A, int lda, const void* B, int ldb, in
 
 // Picks the output patch (pw x ph x pn <= 128 pixels) that wastes the fewest tile rows.
 static void pick_patch(int ow, int oh, int nimg, int* pw, int* ph, int* pn) {
+  if (const char* e = getenv("SPLITRPC_CONV_PATCH")) {  // "w,h,n": experiments with the patch shape
+    int w = 0, h = 0, n = 0;
+    if (sscanf(e, "%d,%d,%d", &w, &h, &n) == 3 && w >= 1 && h >= 1 && n >= 1 && w * h * n <= 128 && w <= ow && h <= oh && n <= nimg) {
+      *pw = w;
+      *ph = h;
+      *pn = n;
+      return;
+    }
+  }
   double best = -1;
   for (int w = 1; w <= std::min(ow, 64); w++)
     for (int h = 1; h <= std::min(oh, 128 / w); h++) {
