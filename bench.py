@@ -778,6 +778,11 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    # Standard output carries the result line and nothing else: libraries that write to descriptor 1 themselves (NCCL
+    # prints its version there) are pointed at standard error for the length of the run.
+    sys.stdout.flush()
+    result_out = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
     if args.impl == "reference":
         res = run_reference(args, rank, world, local_rank)
     elif args.config == "lenet5":
@@ -790,8 +795,10 @@ def main():
         res = run_tp(args, rank, world, local_rank)
     else:
         res = run_ours(args, rank, world, local_rank)
+    sys.stdout.flush()
     if rank == 0 and res is not None:
-        print(json.dumps(res), flush=True)
+        result_out.write(json.dumps(res) + "\n")
+        result_out.flush()
 
 
 if __name__ == "__main__":
