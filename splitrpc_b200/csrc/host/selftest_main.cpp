@@ -13,7 +13,9 @@
 #include <string>
 
 #include "host/apps_cpu.h"
+#include "host/copy_path_runner.h"
 #include "host/loadgen.h"
+#include "host/p2p_rpc_compat.h"
 #include "host/splitrpc_server.h"
 
 // The CUDA half is absent from this build.
@@ -201,6 +203,61 @@ void scenario_lost_peer(const std::string& sock) {
   bs.stop();
 }
 
+// The comparison system's copy path: eight caller threads block in the batching worker.
+void scenario_copy_path() {
+  auto app = make_cpu_app(cpu_echo_run, 512, 512, 16, 4);
+  CopyPathBatcher batcher(app.get(), 4);
+  std::vector<std::thread> callers;
+  std::atomic<int> good{0};
+  for (int t = 0; t < 8; t++)
+    callers.emplace_back([&, t] {
+      std::vector<uint8_t> req(512), resp(512);
+      for (int i = 0; i < 50; i++) {
+        for (int j = 0; j < 512; j++) req[j] = (uint8_t)(t * 31 + i * 7 + j);
+        if (batcher.submit(req.data(), req.size(), resp.data()) && req == resp) good++;
+      }
+    });
+  for (auto& c : callers) c.join();
+  CopyPathTimes tm = batcher.times();
+  batcher.stop();
+  std::vector<uint8_t> req(512), resp(512);
+  expect(good.load() == 400 && tm.requests == 400 && tm.batches >= 100 && tm.batches <= 400, "copy path: 400 requests through the batching worker");
+  expect(!batcher.submit(req.data(), req.size(), resp.data()), "copy path: refused after stop");
+}
+
+// First-generation synchronous app server: records through two app instances and the completion ring.
+void scenario_v1_app_server() {
+  CpuAppState st;
+  st.req_size = st.resp_size = 128;
+  p2p_rpc_v1::P2pRpcAppServer srv(cpu_app_noop, cpu_echo_run, nullptr, cpu_app_noop, 2, -1, 128, 128, 64, &st);
+  p2p_rpc_v1::P2pRpcAppServer::Ring cq(64);
+  srv.register_cq(&cq);
+  std::vector<std::vector<uint8_t>> reqs(48, std::vector<uint8_t>(128)), resps(48, std::vector<uint8_t>(128));
+  std::vector<p2p_rpc_rr*> rrs;
+  for (int i = 0; i < 48; i++) {
+    for (int j = 0; j < 128; j++) reqs[i][j] = (uint8_t)(i * 5 + j);
+    p2p_rpc_rr* rr = rr_proto_alloc(nullptr, 128, 128);
+    rr->req_payload = reqs[i].data();
+    rr->resp_payload = resps[i].data();
+    rrs.push_back(rr);
+  }
+  srv.start();
+  bool queued = true;
+  for (p2p_rpc_rr* rr : rrs) queued = queued && srv.enqueue_work(rr);
+  int done = 0;
+  uint64_t t0 = getCurNs();
+  p2p_rpc_rr* out = nullptr;
+  while (done < 48 && getCurNs() - t0 < 5000000000ull) {
+    if (cq.pop(out)) done++;
+    else std::this_thread::yield();
+  }
+  srv.stop();
+  bool same = true;
+  for (int i = 0; i < 48; i++) same = same && reqs[i] == resps[i];
+  expect(queued && done == 48 && same && srv.num_serviced() == 48, "first-generation app server: 48 records through two instances");
+  for (p2p_rpc_rr* rr : rrs) rr_base_free(rr);
+}
+
 }  // namespace
 
 int main(int argc, char** argv) {
@@ -210,6 +267,8 @@ int main(int argc, char** argv) {
   scenario_remote(dir + "/srpc_selftest_a.sock");
   scenario_pull(dir + "/srpc_selftest_c.sock");
   scenario_lost_peer(dir + "/srpc_selftest_b.sock");
+  scenario_copy_path();
+  scenario_v1_app_server();
   std::printf("%s\n", fails ? "SELFTEST FAILED" : "SELFTEST OK");
   return fails ? 1 : 0;
 }
