@@ -741,6 +741,25 @@ def run_lenet5_cpu(args) -> dict:
     oracle_ok = bool(np.allclose(np.frombuffer(cli.response(3), dtype=np.float32), _C.cpu_lenet5(w, x)[0], rtol=1e-4, atol=1e-5))
     hist = ws["batch_hist"]
     rps = st.get("throughput_est", 0.0) if ok else 0.0
+    # the comparison system on the same app: gRPC in front of the copy path, batching what queues up
+    copy_path = None
+    try:
+        from splitrpc_b200.utils.grpc_baseline import GrpcClient, GrpcCopyPathServer
+
+        app2 = _C.make_app("lenet5", -1, 3136, 40, w, 256, 1, nb, "cpu")
+        with GrpcCopyPathServer(app2, nb) as gs:
+            gc = GrpcClient(gs.address, 3136)
+            g = gc.run_closed_loop(outstanding=48, total=min(n_req, 4000), warmup=200)
+            gc.close()
+            t = gs.times()
+        copy_path = {"value": round(g["req_per_s"], 1), "unit": "req/s", "p50_us": round(g["p50_us"], 1), "p99_us": round(g["p99_us"], 1),
+                     "errors": g["errors"], "mean_batch": round(t["requests"] / max(1, t["batches"]), 2),
+                     "copy_in_us_per_req": round(t["h2d_ns"] / max(1, t["requests"]) / 1e3, 2),
+                     "run_us_per_req": round(t["run_ns"] / max(1, t["requests"]) / 1e3, 2),
+                     "copy_out_us_per_req": round(t["d2h_ns"] / max(1, t["requests"]) / 1e3, 2),
+                     "note": "Python grpcio server and client threads: understates what gRPC's C++ server does"}
+    except Exception as e:  # noqa: BLE001 - grpcio is optional
+        copy_path = {"unavailable": f"{type(e).__name__}: {str(e)[:200]}"}
     return {"metric": "req/s (dynamic batching, CPU device, host clock)", "value": round(rps, 1), "unit": "req/s", "n_gpus": 0,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(1e3 * nb / rps, 4) if rps else None,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp32", "data": "synthetic", "impl": "splitrpc_b200",
@@ -749,7 +768,7 @@ def run_lenet5_cpu(args) -> dict:
                     "p50_us": round(st.get("p50_sojournTime_us", 0.0), 1), "p99_us": round(st.get("p99_sojournTime_us", 0.0), 1),
                     "requests": n_req, "seconds": round(wall, 3), "oracle_match": oracle_ok,
                     "mean_batch": round(sum(k * v for k, v in hist.items()) / max(1, sum(hist.values())), 2)},
-            "gpu_launches": 0}
+            "grpc_copy_path": copy_path, "gpu_launches": 0}
 
 
 def run_reference(args, rank: int, world: int, local_rank: int) -> dict:
