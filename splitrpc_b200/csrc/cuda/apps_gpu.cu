@@ -121,14 +121,35 @@ __global__ void mm_kernel(const g_params* stub, size_t req_size, size_t resp_siz
   mm_body(stub->req, stub->resp, req_size, resp_size, d, batch, blockIdx.x, gridDim.x, sm);
 }
 
-// LeNet-5, whole network in one kernel, one image per block (256 threads).
-// Activations stay in shared memory; fc weights stream from L2.
+// LeNet-5, whole network in one kernel, one image per block (any multiple of 32 threads; launched with 1024).
+// Activations stay in shared memory; fc weights stream from L2.  A thread computes the four window positions of one
+// pooled output from a 6 x 6 input patch and the 25 filter taps held in registers (0.6 shared-memory reads per
+// multiply-add, no bounds checks: the image carries a zero border); ReLU is monotonic, so it is applied once, after
+// the max over the window.
 struct LeNetW {
   const float *c1w, *c1b, *c2w, *c2b, *f1w, *f1b, *f2w, *f2b, *f3w, *f3b;
 };
+constexpr int LENET5_THREADS = 1024;
+
+// acc[dy][dx] += patch (6 x 6, row stride `ld`) * taps (5 x 5) for the 2 x 2 window positions
+__device__ __forceinline__ void lenet5_window(const float* ps, int ld, const float* wk, float& a00, float& a01, float& a10, float& a11) {
+  float wreg[25];
+#pragma unroll
+  for (int i = 0; i < 25; i++) wreg[i] = wk[i];
+#pragma unroll
+  for (int i = 0; i < 6; i++)
+#pragma unroll
+    for (int j = 0; j < 6; j++) {
+      const float v = ps[i * ld + j];
+      if (i < 5 && j < 5) a00 += v * wreg[i * 5 + j];
+      if (i < 5 && j > 0) a01 += v * wreg[i * 5 + j - 1];
+      if (i > 0 && j < 5) a10 += v * wreg[(i - 1) * 5 + j];
+      if (i > 0 && j > 0) a11 += v * wreg[(i - 1) * 5 + j - 1];
+    }
+}
 
 __device__ __forceinline__ void lenet5_body(const uint8_t* req, uint8_t* resp, const LeNetW& w, int batch, int b0, int nb) {
-  __shared__ float x[28 * 28];
+  __shared__ float x[32 * 32];  // the image with a zero border of two pixels
   __shared__ float p1[6 * 14 * 14];
   __shared__ float p2[16 * 5 * 5];
   __shared__ float f1[120];
@@ -136,76 +157,55 @@ __device__ __forceinline__ void lenet5_body(const uint8_t* req, uint8_t* resp, c
   __shared__ float lg[10];
   __shared__ float wc1[6 * 25 + 6];
   __shared__ float wc2[16 * 6 * 25 + 16];
-  const int t = threadIdx.x;
-  for (int i = t; i < 150; i += 256) wc1[i] = w.c1w[i];
-  for (int i = t; i < 6; i += 256) wc1[150 + i] = w.c1b[i];
-  for (int i = t; i < 2400; i += 256) wc2[i] = w.c2w[i];
-  for (int i = t; i < 16; i += 256) wc2[2400 + i] = w.c2b[i];
+  const int t = threadIdx.x, nt = blockDim.x, warp = t / 32, lane = t % 32, nw = nt / 32;
+  for (int i = t; i < 150; i += nt) wc1[i] = w.c1w[i];
+  for (int i = t; i < 6; i += nt) wc1[150 + i] = w.c1b[i];
+  for (int i = t; i < 2400; i += nt) wc2[i] = w.c2w[i];
+  for (int i = t; i < 16; i += nt) wc2[2400 + i] = w.c2b[i];
+  for (int i = t; i < 32 * 32; i += nt) x[i] = 0.f;
   for (int b = b0; b < batch; b += nb) {
     const float* in = reinterpret_cast<const float*>(req + (size_t)b * LENET5_REQ_BYTES);
     float* out = reinterpret_cast<float*>(resp + (size_t)b * LENET5_RESP_BYTES);
     __syncthreads();
-    for (int i = t; i < 784; i += 256) x[i] = __ldcg(in + i);  // not through L1: see mm_body
+    for (int i = t; i < 784; i += nt) x[(i / 28 + 2) * 32 + i % 28 + 2] = __ldcg(in + i);  // not through L1: see mm_body
     __syncthreads();
-    // conv1 (pad 2) + relu + 2x2 maxpool fused: each thread makes pooled outputs
-    for (int o = t; o < 6 * 14 * 14; o += 256) {
-      int k = o / 196, r = (o % 196) / 14, c = o % 14;
-      float best = -1e30f;
-      for (int dy = 0; dy < 2; dy++)
-        for (int dx = 0; dx < 2; dx++) {
-          int oh = 2 * r + dy, ow = 2 * c + dx;
-          float acc = wc1[150 + k];
-          for (int i = 0; i < 5; i++) {
-            int ih = oh + i - 2;
-            if (ih < 0 || ih >= 28) continue;
-            for (int j = 0; j < 5; j++) {
-              int iw = ow + j - 2;
-              if (iw < 0 || iw >= 28) continue;
-              acc += x[ih * 28 + iw] * wc1[k * 25 + i * 5 + j];
-            }
-          }
-          best = fmaxf(best, acc);
-        }
-      p1[o] = fmaxf(best, 0.f);
+    // conv1 (pad 2) + 2x2 maxpool + relu: each thread makes pooled outputs
+    for (int o = t; o < 6 * 14 * 14; o += nt) {
+      const int k = o / 196, r = (o % 196) / 14, c = o % 14;
+      float a00 = 0.f, a01 = 0.f, a10 = 0.f, a11 = 0.f;
+      lenet5_window(x + (2 * r) * 32 + 2 * c, 32, wc1 + k * 25, a00, a01, a10, a11);
+      p1[o] = fmaxf(fmaxf(fmaxf(a00, a01), fmaxf(a10, a11)) + wc1[150 + k], 0.f);
     }
     __syncthreads();
-    // conv2 (no pad) + relu + maxpool
-    for (int o = t; o < 16 * 5 * 5; o += 256) {
-      int k = o / 25, r = (o % 25) / 5, c = o % 5;
-      float best = -1e30f;
-      for (int dy = 0; dy < 2; dy++)
-        for (int dx = 0; dx < 2; dx++) {
-          int oh = 2 * r + dy, ow = 2 * c + dx;
-          float acc = wc2[2400 + k];
-          for (int ch = 0; ch < 6; ch++)
-            for (int i = 0; i < 5; i++)
-              for (int j = 0; j < 5; j++)
-                acc += p1[ch * 196 + (oh + i) * 14 + ow + j] * wc2[(k * 6 + ch) * 25 + i * 5 + j];
-          best = fmaxf(best, acc);
-        }
-      p2[o] = fmaxf(best, 0.f);
+    // conv2 (no pad) + maxpool + relu
+    for (int o = t; o < 16 * 5 * 5; o += nt) {
+      const int k = o / 25, r = (o % 25) / 5, c = o % 5;
+      float a00 = 0.f, a01 = 0.f, a10 = 0.f, a11 = 0.f;
+      for (int ch = 0; ch < 6; ch++)
+        lenet5_window(p1 + ch * 196 + (2 * r) * 14 + 2 * c, 14, wc2 + (k * 6 + ch) * 25, a00, a01, a10, a11);
+      p2[o] = fmaxf(fmaxf(fmaxf(a00, a01), fmaxf(a10, a11)) + wc2[2400 + k], 0.f);
     }
     __syncthreads();
     // fc1: 120 outputs, warp per output row
-    for (int o = t / 32; o < 120; o += 8) {
+    for (int o = warp; o < 120; o += nw) {
       float acc = 0.f;
-      for (int i = t % 32; i < 400; i += 32) acc += p2[i] * w.f1w[o * 400 + i];
+      for (int i = lane; i < 400; i += 32) acc += p2[i] * w.f1w[o * 400 + i];
       for (int s = 16; s; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
-      if (t % 32 == 0) f1[o] = fmaxf(acc + w.f1b[o], 0.f);
+      if (lane == 0) f1[o] = fmaxf(acc + w.f1b[o], 0.f);
     }
     __syncthreads();
-    for (int o = t / 32; o < 84; o += 8) {
+    for (int o = warp; o < 84; o += nw) {
       float acc = 0.f;
-      for (int i = t % 32; i < 120; i += 32) acc += f1[i] * w.f2w[o * 120 + i];
+      for (int i = lane; i < 120; i += 32) acc += f1[i] * w.f2w[o * 120 + i];
       for (int s = 16; s; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
-      if (t % 32 == 0) f2[o] = fmaxf(acc + w.f2b[o], 0.f);
+      if (lane == 0) f2[o] = fmaxf(acc + w.f2b[o], 0.f);
     }
     __syncthreads();
-    for (int o = t / 32; o < 10; o += 8) {
+    for (int o = warp; o < 10; o += nw) {
       float acc = 0.f;
-      for (int i = t % 32; i < 84; i += 32) acc += f2[i] * w.f3w[o * 84 + i];
+      for (int i = lane; i < 84; i += 32) acc += f2[i] * w.f3w[o * 84 + i];
       for (int s = 16; s; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
-      if (t % 32 == 0) lg[o] = acc + w.f3b[o];
+      if (lane == 0) lg[o] = acc + w.f3b[o];
     }
     __syncthreads();
     if (t == 0) {
@@ -221,7 +221,7 @@ __device__ __forceinline__ void lenet5_body(const uint8_t* req, uint8_t* resp, c
   }
 }
 
-__global__ void __launch_bounds__(256) lenet5_kernel(const g_params* stub, LeNetW w, int batch) {
+__global__ void __launch_bounds__(LENET5_THREADS, 1) lenet5_kernel(const g_params* stub, LeNetW w, int batch) {
   lenet5_body(stub->req, stub->resp, w, batch, blockIdx.x, gridDim.x);
 }
 
@@ -236,7 +236,7 @@ struct ResidentArgs {
   LeNetW w;
 };
 template <int KIND>
-__global__ void app_resident(const g_params* stub, volatile uint32_t* door_bell, ResidentArgs a, uint64_t idle_ns, uint32_t* status,
+__global__ void __launch_bounds__(1024, 1) app_resident(const g_params* stub, volatile uint32_t* door_bell, ResidentArgs a, uint64_t idle_ns, uint32_t* status,
                              const RespPushCtx* push) {
   extern __shared__ float dyn_sm[];
   __shared__ uint32_t s_batch, s_leave;
@@ -309,7 +309,7 @@ void launch_kernels(AppCtx* c, int batch) {
   } else if (s->name == "matmul") {
     mm_kernel<<<batch, 256, (size_t)s->dim * s->dim * 4, q>>>(c->d_stub, s->req_size, s->resp_size, s->dim, batch);
   } else if (s->name == "lenet5") {
-    lenet5_kernel<<<batch, 256, 0, q>>>(c->d_stub, lenet_w(s), batch);
+    lenet5_kernel<<<batch, LENET5_THREADS, 0, q>>>(c->d_stub, lenet_w(s), batch);
   } else if (s->name == "lenet_ref") {
     const float* b = s->d_weights;
     srpc_lenet_ref(c->d_stub, nullptr, nullptr, b + s->w_off[0], b + s->w_off[1], b + s->w_off[2], b + s->w_off[3], batch, q);
@@ -366,7 +366,7 @@ int gpu_app_run(AppCtx* c) {
                                                                                                s->idle_ns, s->d_pt_status, c->d_push_mapped);
       } else {
         a.w = lenet_w(s);
-        app_resident<RESIDENT_LENET5><<<1, 256, 0, c->work_stream>>>(c->d_stub_mapped, c->d_door_bell, a, s->idle_ns, s->d_pt_status, c->d_push_mapped);
+        app_resident<RESIDENT_LENET5><<<1, LENET5_THREADS, 0, c->work_stream>>>(c->d_stub_mapped, c->d_door_bell, a, s->idle_ns, s->d_pt_status, c->d_push_mapped);
       }
     }
     c->NotifyAppRunStart();
