@@ -15,19 +15,121 @@
 //            (uint8 pixels, (x-127)/128, conv pad 1, tanh, maxpool, dense, softmax)
 #pragma once
 
+#include <atomic>
 #include <cmath>
+#include <condition_variable>
+#include <cstdlib>
 #include <cstring>
 #include <fstream>
+#include <functional>
+#include <memory>
+#include <mutex>
 #include <sstream>
 #include <string>
+#include <thread>
 #include <vector>
 
 #include "p2p_rpc_app.h"
+
+// Helper threads that share the requests of a batch (CPU apps whose work per request is tens of microseconds or more).
+// The caller takes part; helpers sleep on a condition variable between batches.
+class CpuBatchPool {
+ public:
+  explicit CpuBatchPool(int helpers) {
+    for (int i = 0; i < helpers; i++) threads_.emplace_back([this] { loop(); });
+  }
+  ~CpuBatchPool() {
+    {
+      std::lock_guard<std::mutex> g(mu_);
+      stop_ = true;
+      gen_++;
+    }
+    cv_.notify_all();
+    for (auto& t : threads_) t.join();
+  }
+  // fn(i) for i in [0, n), spread over the caller and the helpers; returns when all are done
+  template <class F>
+  void run(int n, F&& fn) {
+    if (n <= 1 || threads_.empty()) {
+      for (int i = 0; i < n; i++) fn(i);
+      return;
+    }
+    std::function<void(int)> f = fn;
+    {
+      std::lock_guard<std::mutex> g(mu_);
+      fn_ = &f;
+      n_ = n;
+      next_.store(0, std::memory_order_relaxed);
+      pending_ = n;
+      gen_++;
+    }
+    cv_.notify_all();
+    work();
+    std::unique_lock<std::mutex> lk(mu_);
+    done_cv_.wait(lk, [&] { return pending_ == 0 && active_ == 0; });
+    fn_ = nullptr;
+  }
+
+ private:
+  void work() {
+    int finished = 0;
+    for (;;) {
+      const int i = next_.fetch_add(1, std::memory_order_relaxed);
+      if (i >= n_) break;
+      (*fn_)(i);
+      finished++;
+    }
+    if (finished) {
+      std::lock_guard<std::mutex> g(mu_);
+      pending_ -= finished;
+      if (pending_ == 0) done_cv_.notify_all();
+    }
+  }
+  void loop() {
+    uint64_t seen = 0;
+    std::unique_lock<std::mutex> lk(mu_);
+    for (;;) {
+      cv_.wait(lk, [&] { return gen_ != seen; });
+      seen = gen_;
+      if (stop_) return;
+      if (!fn_) continue;
+      active_++;
+      lk.unlock();
+      work();
+      lk.lock();
+      active_--;
+      if (pending_ == 0 && active_ == 0) done_cv_.notify_all();
+    }
+  }
+  std::vector<std::thread> threads_;
+  std::mutex mu_;
+  std::condition_variable cv_, done_cv_;
+  const std::function<void(int)>* fn_ = nullptr;
+  int n_ = 0, pending_ = 0, active_ = 0;
+  std::atomic<int> next_{0};
+  uint64_t gen_ = 0;
+  bool stop_ = false;
+};
 
 struct CpuAppState {
   size_t req_size = 0, resp_size = 0;
   std::vector<std::vector<float>> weights;  // app specific
   int dim = 0;                              // matmul dimension
+  std::unique_ptr<CpuBatchPool> pool;       // created by the first batch that can use it
+  // Requests of one batch spread over the caller and up to three helper threads (P2P_RPC_CPU_APP_THREADS, default
+  // min(4, half of the cores)).
+  CpuBatchPool* batch_pool() {
+    if (!pool) {
+      int want = 0;
+      if (const char* e = getenv("P2P_RPC_CPU_APP_THREADS")) want = atoi(e);
+      if (want <= 0) {
+        const int hw = (int)std::thread::hardware_concurrency();
+        want = hw / 2 < 4 ? (hw / 2 > 1 ? hw / 2 : 1) : 4;
+      }
+      pool.reset(new CpuBatchPool(want - 1));
+    }
+    return pool.get();
+  }
 };
 
 static inline CpuAppState* cpu_state(AppCtx* c) { return static_cast<CpuAppState*>(c->app_ctx_internal); }
@@ -80,23 +182,27 @@ static inline int cpu_mm_run(AppCtx* c) {
 // ---- generic layers (NCHW, fp32)
 static inline void cpu_conv2d(const float* in, int C, int H, int W, const float* w, const float* bias, int K, int R,
                               int pad, float* out) {
-  int OH = H + 2 * pad - R + 1, OW = W + 2 * pad - R + 1;
-  for (int k = 0; k < K; k++)
-    for (int oh = 0; oh < OH; oh++)
-      for (int ow = 0; ow < OW; ow++) {
-        float acc = bias ? bias[k] : 0.f;
-        for (int c = 0; c < C; c++)
-          for (int r = 0; r < R; r++) {
-            int ih = oh + r - pad;
-            if (ih < 0 || ih >= H) continue;
-            for (int q = 0; q < R; q++) {
-              int iw = ow + q - pad;
-              if (iw < 0 || iw >= W) continue;
-              acc += in[(c * H + ih) * W + iw] * w[((k * C + c) * R + r) * R + q];
-            }
+  // One filter tap at a time over whole output rows: the inner loop is a contiguous multiply-add (vectorised by the
+  // compiler), and the padding turns into loop bounds instead of a test per element.
+  const int OH = H + 2 * pad - R + 1, OW = W + 2 * pad - R + 1;
+  for (int k = 0; k < K; k++) {
+    float* ok = out + (size_t)k * OH * OW;
+    const float b = bias ? bias[k] : 0.f;
+    for (int i = 0; i < OH * OW; i++) ok[i] = b;
+    for (int c = 0; c < C; c++)
+      for (int r = 0; r < R; r++) {
+        const int oh_lo = pad - r > 0 ? pad - r : 0, oh_hi = H + pad - r < OH ? H + pad - r : OH;
+        for (int q = 0; q < R; q++) {
+          const int ow_lo = pad - q > 0 ? pad - q : 0, ow_hi = W + pad - q < OW ? W + pad - q : OW;
+          const float wv = w[((k * C + c) * R + r) * R + q];
+          for (int oh = oh_lo; oh < oh_hi; oh++) {
+            float* o = ok + oh * OW;
+            const float* x = in + (c * H + oh + r - pad) * W + (q - pad);
+            for (int ow = ow_lo; ow < ow_hi; ow++) o[ow] += x[ow] * wv;
           }
-        out[(k * OH + oh) * OW + ow] = acc;
+        }
       }
+  }
 }
 static inline void cpu_maxpool2(const float* in, int C, int H, int W, float* out) {
   int OH = H / 2, OW = W / 2;
@@ -109,9 +215,15 @@ static inline void cpu_maxpool2(const float* in, int C, int H, int W, float* out
 }
 static inline void cpu_dense(const float* in, int n_in, const float* w, const float* bias, int n_out, float* out) {
   for (int o = 0; o < n_out; o++) {
+    // eight partial sums: a plain running sum is a dependency chain that the compiler may not reorder
+    float part[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    const float* wr = w + (size_t)o * n_in;
+    int i = 0;
+    for (; i + 8 <= n_in; i += 8)
+      for (int j = 0; j < 8; j++) part[j] += in[i + j] * wr[i + j];
     float acc = bias ? bias[o] : 0.f;
-    for (int i = 0; i < n_in; i++) acc += in[i] * w[o * n_in + i];
-    out[o] = acc;
+    for (; i < n_in; i++) acc += in[i] * wr[i];
+    out[o] = acc + ((part[0] + part[1]) + (part[2] + part[3])) + ((part[4] + part[5]) + (part[6] + part[7]));
   }
 }
 static inline void cpu_softmax(float* v, int n) {
@@ -147,9 +259,12 @@ static inline void cpu_lenet5_one(const CpuAppState* s, const float* x, float* y
 }
 static inline int cpu_lenet5_run(AppCtx* c) {
   CpuAppState* s = cpu_state(c);
-  for (int b = 0; b < c->curr_batch_size; b++)
-    cpu_lenet5_one(s, reinterpret_cast<const float*>(c->h_stub->req + (size_t)b * s->req_size),
-                   reinterpret_cast<float*>(c->h_stub->resp + (size_t)b * s->resp_size));
+  const uint8_t* req = c->h_stub->req;
+  uint8_t* resp = c->h_stub->resp;
+  s->batch_pool()->run(c->curr_batch_size, [s, req, resp](int b) {
+    cpu_lenet5_one(s, reinterpret_cast<const float*>(req + (size_t)b * s->req_size),
+                   reinterpret_cast<float*>(resp + (size_t)b * s->resp_size));
+  });
   return 1;
 }
 
@@ -169,9 +284,11 @@ static inline void cpu_lenet_ref_one(const CpuAppState* s, const uint8_t* px, fl
 }
 static inline int cpu_lenet_ref_run(AppCtx* c) {
   CpuAppState* s = cpu_state(c);
-  for (int b = 0; b < c->curr_batch_size; b++)
-    cpu_lenet_ref_one(s, c->h_stub->req + (size_t)b * s->req_size,
-                      reinterpret_cast<float*>(c->h_stub->resp + (size_t)b * s->resp_size));
+  const uint8_t* req = c->h_stub->req;
+  uint8_t* resp = c->h_stub->resp;
+  s->batch_pool()->run(c->curr_batch_size, [s, req, resp](int b) {
+    cpu_lenet_ref_one(s, req + (size_t)b * s->req_size, reinterpret_cast<float*>(resp + (size_t)b * s->resp_size));
+  });
   return 1;
 }
 

@@ -9,6 +9,7 @@
 // by the ingress or fetched by the serving side from shared payload regions), all in one
 // process, and exits non-zero when a reply is wrong or missing.  The original has no such harness; its host code is
 // only ever run on the full testbed.
+#include <algorithm>
 #include <cstdio>
 #include <string>
 
@@ -225,6 +226,20 @@ void scenario_copy_path() {
   expect(!batcher.submit(req.data(), req.size(), resp.data()), "copy path: refused after stop");
 }
 
+// The helper threads that share a batch of a CPU app.
+void scenario_batch_pool() {
+  CpuBatchPool pool(3);
+  std::vector<int> hits(64);
+  bool ok = true;
+  for (int round = 0; round < 300; round++) {
+    const int n = 1 + round % 64;
+    std::fill(hits.begin(), hits.end(), 0);
+    pool.run(n, [&](int i) { hits[i] += 1 + round; });
+    for (int i = 0; i < 64; i++) ok = ok && hits[i] == (i < n ? 1 + round : 0);
+  }
+  expect(ok, "batch pool: every index exactly once, 300 rounds");
+}
+
 // First-generation synchronous app server: records through two app instances and the completion ring.
 void scenario_v1_app_server() {
   CpuAppState st;
@@ -268,6 +283,7 @@ int main(int argc, char** argv) {
   scenario_pull(dir + "/srpc_selftest_c.sock");
   scenario_lost_peer(dir + "/srpc_selftest_b.sock");
   scenario_copy_path();
+  scenario_batch_pool();
   scenario_v1_app_server();
   std::printf("%s\n", fails ? "SELFTEST FAILED" : "SELFTEST OK");
   return fails ? 1 : 0;
