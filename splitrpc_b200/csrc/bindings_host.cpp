@@ -475,6 +475,13 @@ PYBIND11_MODULE(_C, m) {
     int n = lp && lp->peer() ? lp->peer()->dma_regions(all, NVL_MAX_REGIONS) : 0;
     return py::make_tuple((uintptr_t)r.host_base, (uintptr_t)r.dev_base, (size_t)r.bytes, n - 1);
   });
+  // Copy lanes of the emulated NIC DMA of a loopback port (threads that write the fragments of a burst into the peer's
+  // receive arena; 1 = the sending thread alone).
+  m.def("set_loopback_dma_lanes", [](PortHolder& p, int lanes) {
+    auto* lp = dynamic_cast<LoopbackPort*>(p.port);
+    if (!lp) throw std::invalid_argument("not a loopback port");
+    lp->set_dma_lanes(lanes);
+  }, py::arg("port"), py::arg("lanes"));
   m.def("set_loopback_faults",
         [](PortHolder& p, double drop, double dup, double reorder, double truncate, bool zero_token, int force_seq,
            uint64_t seed) {

@@ -29,87 +29,8 @@
 #include <thread>
 #include <vector>
 
+#include "cpu_batch_pool.h"
 #include "p2p_rpc_app.h"
-
-// Helper threads that share the requests of a batch (CPU apps whose work per request is tens of microseconds or more).
-// The caller takes part; helpers sleep on a condition variable between batches.
-class CpuBatchPool {
- public:
-  explicit CpuBatchPool(int helpers) {
-    for (int i = 0; i < helpers; i++) threads_.emplace_back([this] { loop(); });
-  }
-  ~CpuBatchPool() {
-    {
-      std::lock_guard<std::mutex> g(mu_);
-      stop_ = true;
-      gen_++;
-    }
-    cv_.notify_all();
-    for (auto& t : threads_) t.join();
-  }
-  // fn(i) for i in [0, n), spread over the caller and the helpers; returns when all are done
-  template <class F>
-  void run(int n, F&& fn) {
-    if (n <= 1 || threads_.empty()) {
-      for (int i = 0; i < n; i++) fn(i);
-      return;
-    }
-    std::function<void(int)> f = fn;
-    {
-      std::lock_guard<std::mutex> g(mu_);
-      fn_ = &f;
-      n_ = n;
-      next_.store(0, std::memory_order_relaxed);
-      pending_ = n;
-      gen_++;
-    }
-    cv_.notify_all();
-    work();
-    std::unique_lock<std::mutex> lk(mu_);
-    done_cv_.wait(lk, [&] { return pending_ == 0 && active_ == 0; });
-    fn_ = nullptr;
-  }
-
- private:
-  void work() {
-    int finished = 0;
-    for (;;) {
-      const int i = next_.fetch_add(1, std::memory_order_relaxed);
-      if (i >= n_) break;
-      (*fn_)(i);
-      finished++;
-    }
-    if (finished) {
-      std::lock_guard<std::mutex> g(mu_);
-      pending_ -= finished;
-      if (pending_ == 0) done_cv_.notify_all();
-    }
-  }
-  void loop() {
-    uint64_t seen = 0;
-    std::unique_lock<std::mutex> lk(mu_);
-    for (;;) {
-      cv_.wait(lk, [&] { return gen_ != seen; });
-      seen = gen_;
-      if (stop_) return;
-      if (!fn_) continue;
-      active_++;
-      lk.unlock();
-      work();
-      lk.lock();
-      active_--;
-      if (pending_ == 0 && active_ == 0) done_cv_.notify_all();
-    }
-  }
-  std::vector<std::thread> threads_;
-  std::mutex mu_;
-  std::condition_variable cv_, done_cv_;
-  const std::function<void(int)>* fn_ = nullptr;
-  int n_ = 0, pending_ = 0, active_ = 0;
-  std::atomic<int> next_{0};
-  uint64_t gen_ = 0;
-  bool stop_ = false;
-};
 
 struct CpuAppState {
   size_t req_size = 0, resp_size = 0;

@@ -24,6 +24,9 @@
 #include <memory>
 #include <mutex>
 
+#include <vector>
+
+#include "cpu_batch_pool.h"
 #include "mpmc_ring.h"
 #include "p2p_rpc.h"
 
@@ -231,18 +234,24 @@ class LoopbackPort : public Transport {
   std::atomic<int> n_ref_regions_{0};  // entries below it never change: readers need no lock
   std::mutex region_mu_;
 
-  // The emulated DMA: place one packet into the peer's receive arena.
-  bool deliver(const p2p_rpc_hdr* hdr, const uint8_t* payload_host, uint32_t len, uint32_t slot) {
+  // The emulated DMA, in two steps: write one packet's header and payload into the peer's receive arena (any thread),
+  // then make it visible in the peer's receive ring (the sending thread, in order).
+  bool dma_write(const p2p_rpc_hdr* hdr, const uint8_t* payload_host, uint32_t len, uint32_t slot) {
     PktArena* a = peer_->rx_arena_.get();
-    if (len > a->slot_bytes()) {
+    if (len > a->slot_bytes()) return false;
+    std::memcpy(a->hdr_ptr(slot), hdr, RPC_HEADER_LEN);
+    if (len) std::memcpy(a->host_ptr(slot), payload_host, len);
+    return true;
+  }
+  bool dma_publish(uint32_t len, uint32_t slot, bool written) {
+    PktArena* a = peer_->rx_arena_.get();
+    if (!written) {
+      a->release(slot);
       counters.tx_dropped++;
       return false;
     }
-    p2p_rpc_hdr* h = a->hdr_ptr(slot);
-    std::memcpy(h, hdr, RPC_HEADER_LEN);
-    if (len) std::memcpy(a->host_ptr(slot), payload_host, len);
     SrpcPkt p;
-    p.hdr = h;
+    p.hdr = a->hdr_ptr(slot);
     p.payload = a->host_ptr(slot);
     p.len = len;
     p.slot = slot;
@@ -254,6 +263,16 @@ class LoopbackPort : public Transport {
     }
     return true;
   }
+  // Copy lanes of the emulated DMA engine: bursts of eight packets or more are written by this many threads (the
+  // sender among them).  One lane is the sender alone.
+  std::unique_ptr<CpuBatchPool> dma_pool_;
+  struct DmaJob {
+    p2p_rpc_hdr hdr;
+    const uint8_t* payload;
+    uint32_t len, slot;
+    bool written;
+  };
+  std::vector<DmaJob> dma_jobs_;  // scratch of send_list (under tx_mu_)
 
   int send_list(const p2p_rpc_hdr* const* hdrs, const uint8_t* const* payloads, const uint32_t* lens, int n) {
     std::lock_guard<std::mutex> g(tx_mu_);
@@ -285,22 +304,34 @@ class LoopbackPort : public Transport {
       counters.arena_full++;
       return 0;
     }
+    dma_jobs_.resize(order.size());
     for (size_t k = 0; k < order.size(); k++) {
       int i = order[k];
-      uint32_t slot = (uint32_t)((first + k) % a->num_slots());
-      p2p_rpc_hdr h = *hdrs[i];
-      uint32_t len = lens[i];
-      if (faults_.zero_token) h.req_token = 0;
-      if (faults_.force_seq >= 0) h.seq_num = (uint16_t)faults_.force_seq;
+      DmaJob& j = dma_jobs_[k];
+      j.slot = (uint32_t)((first + k) % a->num_slots());
+      j.hdr = *hdrs[i];
+      j.payload = payloads[i];
+      j.len = lens[i];
+      j.written = false;
+      if (faults_.zero_token) j.hdr.req_token = 0;
+      if (faults_.force_seq >= 0) j.hdr.seq_num = (uint16_t)faults_.force_seq;
       if (faults_.truncate > 0 && rng_.uniform() < faults_.truncate) {
-        len = len > faults_.truncate_bytes ? len - faults_.truncate_bytes : 0;
+        j.len = j.len > faults_.truncate_bytes ? j.len - faults_.truncate_bytes : 0;
         counters.injected_faults++;
       }
-      if (deliver(&h, payloads[i], len, slot)) {
-        counters.tx_pkts++;
-        counters.tx_bytes += len;
-      }
     }
+    auto write_one = [this](int k) {
+      DmaJob& j = dma_jobs_[(size_t)k];
+      j.written = dma_write(&j.hdr, j.payload, j.len, j.slot);
+    };
+    if (dma_pool_ && dma_jobs_.size() >= 8) dma_pool_->run((int)dma_jobs_.size(), write_one);
+    else
+      for (size_t k = 0; k < dma_jobs_.size(); k++) write_one((int)k);
+    for (const DmaJob& j : dma_jobs_)
+      if (dma_publish(j.len, j.slot, j.written)) {
+        counters.tx_pkts++;
+        counters.tx_bytes += j.len;
+      }
     return n;
   }
 
@@ -320,6 +351,10 @@ class LoopbackPort : public Transport {
   ~LoopbackPort() override {
     for (int i = 0; i < n_ref_regions_.load(); i++)
       if (ref_regions_[i]->release) ref_regions_[i]->release();
+  }
+  void set_dma_lanes(int lanes) {
+    std::lock_guard<std::mutex> g(tx_mu_);
+    dma_pool_.reset(lanes > 1 ? new CpuBatchPool(lanes - 1) : nullptr);
   }
   static void connect(LoopbackPort* a, LoopbackPort* b) {
     a->peer_ = b;
