@@ -9,8 +9,11 @@ from conftest import lenet5_weights
 
 
 def _serve(C, app_name, req, resp, total, mode, max_batch, payload, outstanding=8, weights=(), zerocopy=0, engine="",
-           mtu_slots=8192, faults=None, drain_ns=10_000_000_000, open_rate=None, warmup=10):
+           mtu_slots=8192, faults=None, drain_ns=10_000_000_000, open_rate=None, warmup=10, dma_lanes=1):
     sp, cp = C.make_loopback_pair(mtu_slots, 2048)
+    if dma_lanes > 1:
+        C.set_loopback_dma_lanes(cp, dma_lanes)
+        C.set_loopback_dma_lanes(sp, dma_lanes)
     if faults:
         C.set_loopback_faults(cp, **faults)
     app = C.make_app(app_name, -1, req, resp, list(weights), 256, 1, max_batch, engine)
@@ -38,6 +41,14 @@ def test_echo_multi_fragment_all_server_modes(C, mtu1k, mode, max_batch):
         assert set(ws["batch_hist"]) == {max_batch}
     else:
         assert max(ws["batch_hist"]) <= max_batch
+
+
+def test_emulated_dma_with_several_copy_lanes(C, mtu1k):
+    """Bursts of eight fragments or more are written by three threads; duplicates and reordering on the wire on top."""
+    ok, cli, st, ss, ws = _serve(C, "echo", 20000, 20000, 300, 2, 4, "echo", outstanding=8, mtu_slots=1024, dma_lanes=3,
+                                 faults=dict(duplicate=0.05, reorder=0.1, seed=5))
+    assert ok and cli.received == 300 and cli.verify_failures == 0 and cli.bad_tokens == 0
+    assert ss["rx_pkts"] >= 300 * 20
 
 
 def test_vec_add_large_request(C, mtu8k):
