@@ -29,7 +29,7 @@ def test_nn_layers_match_pytorch(torch_cuda):
     assert torch.equal(ops.maxpool3x3s2(x).float(), ref)
     y = torch.randn(3, 5, 5, 640, device="cuda").bfloat16()
     torch.testing.assert_close(ops.global_avgpool(y).float(), y.float().mean((1, 2)), rtol=1e-2, atol=1e-2)
-    for m_rows, n_cols, k in ((64, 1000, 2048), (5, 10, 512), (130, 77, 256)):
+    for m_rows, n_cols, k in ((64, 1000, 2048), (5, 10, 512), (130, 77, 256), (70, 100, 1024)):
         a = torch.randn(m_rows, k, device="cuda").bfloat16()
         w = (torch.randn(n_cols, k, device="cuda") * 0.05).bfloat16()
         bias = torch.randn(n_cols, device="cuda")
