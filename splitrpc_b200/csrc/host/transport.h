@@ -16,10 +16,12 @@
 #pragma once
 
 #include <netinet/in.h>
+#include <sched.h>
 #include <sys/socket.h>
 #include <unistd.h>
 
 #include <atomic>
+#include <deque>
 #include <functional>
 #include <memory>
 #include <mutex>
@@ -499,7 +501,12 @@ class LoopbackPort : public Transport {
 class UdpPort : public Transport {
   int fd_ = -1;
   std::unique_ptr<PktArena> rx_arena_, tx_arena_;
-  std::vector<uint8_t> scratch_, tx_scratch_;  // receive side / transmit side staging
+  static constexpr int kBatch = 32;
+  std::deque<uint32_t> posted_;  // receive slots handed to the kernel, oldest first
+  mmsghdr rx_msgs_[kBatch], tx_msgs_[kBatch];
+  iovec rx_iov_[2 * kBatch], tx_iov_[2 * kBatch];
+  sockaddr_in rx_from_[kBatch], tx_to_[kBatch];
+  uint32_t tx_len_[kBatch];
   std::mutex tx_mu_;
   sockaddr_in default_dst_{};
   bool has_dst_ = false;
@@ -511,9 +518,7 @@ class UdpPort : public Transport {
   // and serving GPUs store responses into the transmit arena.
   UdpPort(const char* bind_ip, int bind_port, size_t slot_bytes, ArenaMem rx_mem, ArenaMem tx_mem)
       : rx_arena_(new PktArena(std::move(rx_mem), slot_bytes)),
-        tx_arena_(new PktArena(std::move(tx_mem), slot_bytes)),
-        scratch_(slot_bytes + RPC_HEADER_TAIL_LEN),
-        tx_scratch_(slot_bytes + RPC_HEADER_TAIL_LEN) {
+        tx_arena_(new PktArena(std::move(tx_mem), slot_bytes)) {
     fd_ = ::socket(AF_INET, SOCK_DGRAM | SOCK_NONBLOCK, 0);
     int sz = 2 << 20;
     setsockopt(fd_, SOL_SOCKET, SO_RCVBUF, &sz, sizeof(sz));
@@ -545,29 +550,48 @@ class UdpPort : public Transport {
     has_dst_ = true;
   }
 
+  // Receive: up to kBatch arena slots are kept posted like the descriptors of a NIC receive queue; one recvmmsg
+  // fills as many of them as datagrams are waiting, and the kernel scatters every datagram straight into its places
+  // (22 header bytes into the slot's header, the rest into the slot's payload): header/data split without a staging
+  // copy.  Slots that stay empty remain posted for the next call.
   int rx_burst(SrpcPkt* out, int max) override {
-    int n = 0;
-    while (n < max) {
-      sockaddr_in from{};
-      socklen_t fl = sizeof(from);
-      ssize_t r = ::recvfrom(fd_, scratch_.data(), scratch_.size(), 0, (sockaddr*)&from, &fl);
-      if (r < 0) break;
-      if ((size_t)r < RPC_HEADER_TAIL_LEN) {
-        counters.rx_runts++;
-        continue;
-      }
+    const int want = max < kBatch ? max : kBatch;
+    while ((int)posted_.size() < want) {
       uint32_t slot = 0;
       if (!rx_arena_->claim(1, &slot)) {
         counters.arena_full++;
         break;
       }
+      std::memset(rx_arena_->hdr_ptr(slot), 0, sizeof(p2p_rpc_hdr));
+      posted_.push_back(slot);
+    }
+    const int np = (int)posted_.size() < want ? (int)posted_.size() : want;
+    if (np == 0) return 0;
+    for (int i = 0; i < np; i++) {
+      const uint32_t slot = posted_[(size_t)i];
+      rx_iov_[2 * i] = iovec{get_req_tail(rx_arena_->hdr_ptr(slot)), RPC_HEADER_TAIL_LEN};
+      rx_iov_[2 * i + 1] = iovec{rx_arena_->host_ptr(slot), rx_arena_->slot_bytes()};
+      std::memset(&rx_msgs_[i], 0, sizeof(mmsghdr));
+      rx_msgs_[i].msg_hdr.msg_iov = &rx_iov_[2 * i];
+      rx_msgs_[i].msg_hdr.msg_iovlen = 2;
+      rx_msgs_[i].msg_hdr.msg_name = &rx_from_[i];
+      rx_msgs_[i].msg_hdr.msg_namelen = sizeof(sockaddr_in);
+    }
+    const int r = ::recvmmsg(fd_, rx_msgs_, (unsigned)np, MSG_DONTWAIT, nullptr);
+    if (r <= 0) return 0;
+    int n = 0;
+    for (int i = 0; i < r; i++) {
+      const uint32_t slot = posted_[(size_t)i];
+      const size_t got = rx_msgs_[i].msg_len;
+      if (got < RPC_HEADER_TAIL_LEN || (rx_msgs_[i].msg_hdr.msg_flags & MSG_TRUNC)) {
+        counters.rx_runts++;
+        rx_arena_->release(slot);
+        continue;
+      }
       p2p_rpc_hdr* h = rx_arena_->hdr_ptr(slot);
-      std::memset(h, 0, sizeof(*h));
-      std::memcpy(get_req_tail(h), scratch_.data(), RPC_HEADER_TAIL_LEN);
-      get_ip_header(h)->src_ip = from.sin_addr.s_addr;
-      get_udp_header(h)->src_port = from.sin_port;
-      uint32_t len = (uint32_t)(r - (ssize_t)RPC_HEADER_TAIL_LEN);
-      std::memcpy(rx_arena_->host_ptr(slot), scratch_.data() + RPC_HEADER_TAIL_LEN, len);
+      get_ip_header(h)->src_ip = rx_from_[i].sin_addr.s_addr;
+      get_udp_header(h)->src_port = rx_from_[i].sin_port;
+      const uint32_t len = (uint32_t)(got - RPC_HEADER_TAIL_LEN);
       out[n].hdr = h;
       out[n].payload = rx_arena_->host_ptr(slot);
       out[n].len = len;
@@ -575,6 +599,7 @@ class UdpPort : public Transport {
       counters.rx_bytes += len;
       n++;
     }
+    posted_.erase(posted_.begin(), posted_.begin() + r);
     counters.rx_pkts += (uint64_t)n;
     return n;
   }
@@ -593,7 +618,9 @@ class UdpPort : public Transport {
     }
     return true;
   }
-  int send_one(const p2p_rpc_hdr* h, const uint8_t* payload, uint32_t len) {
+  // Transmit: sendmmsg over {22 header bytes, payload} pairs, one system call per burst of up to kBatch datagrams and
+  // no staging copy.
+  sockaddr_in destination_of(const p2p_rpc_hdr* h) const {
     sockaddr_in to = default_dst_;
     const ipv4_hdr* ip = get_ip_header(const_cast<p2p_rpc_hdr*>(h));
     const udp_hdr* u = get_udp_header(const_cast<p2p_rpc_hdr*>(h));
@@ -602,36 +629,66 @@ class UdpPort : public Transport {
       to.sin_addr.s_addr = ip->dst_ip;
       to.sin_port = u->dst_port;
     }
+    return to;
+  }
+  template <class At>
+  int send_many(int n, At&& at) {  // at(i, &hdr, &payload, &len)
     std::lock_guard<std::mutex> g(tx_mu_);
-    if (len + RPC_HEADER_TAIL_LEN > tx_scratch_.size()) {
-      counters.tx_dropped++;
-      return 0;
-    }
-    std::memcpy(tx_scratch_.data(), reinterpret_cast<const uint8_t*>(h) + UDP_HEADER_LEN, RPC_HEADER_TAIL_LEN);
-    if (len) std::memcpy(tx_scratch_.data() + RPC_HEADER_TAIL_LEN, payload, len);
-    for (int tries = 0; tries < 100; tries++) {
-      ssize_t r = ::sendto(fd_, tx_scratch_.data(), RPC_HEADER_TAIL_LEN + len, 0, (sockaddr*)&to, sizeof(to));
-      if (r >= 0) {
-        counters.tx_pkts++;
-        counters.tx_bytes += len;
-        return 1;
+    int sent_total = 0;
+    for (int base = 0; base < n; base += kBatch) {
+      const int m = n - base < kBatch ? n - base : kBatch;
+      int k = 0;
+      for (int i = 0; i < m; i++) {
+        const p2p_rpc_hdr* h = nullptr;
+        const uint8_t* payload = nullptr;
+        uint32_t len = 0;
+        at(base + i, &h, &payload, &len);
+        if (len > rx_arena_->slot_bytes()) {
+          counters.tx_dropped++;
+          continue;
+        }
+        tx_to_[k] = destination_of(h);
+        tx_iov_[2 * k] = iovec{const_cast<uint8_t*>(reinterpret_cast<const uint8_t*>(h)) + UDP_HEADER_LEN, RPC_HEADER_TAIL_LEN};
+        tx_iov_[2 * k + 1] = iovec{const_cast<uint8_t*>(payload), len};
+        std::memset(&tx_msgs_[k], 0, sizeof(mmsghdr));
+        tx_msgs_[k].msg_hdr.msg_iov = &tx_iov_[2 * k];
+        tx_msgs_[k].msg_hdr.msg_iovlen = len ? 2 : 1;
+        tx_msgs_[k].msg_hdr.msg_name = &tx_to_[k];
+        tx_msgs_[k].msg_hdr.msg_namelen = sizeof(sockaddr_in);
+        tx_len_[k] = len;
+        k++;
       }
+      int done = 0;
+      for (int tries = 0; done < k && tries < 100; tries++) {
+        const int r = ::sendmmsg(fd_, tx_msgs_ + done, (unsigned)(k - done), MSG_DONTWAIT);
+        if (r > 0) {
+          for (int i = 0; i < r; i++) counters.tx_bytes += tx_len_[done + i];
+          done += r;
+        } else {
+          sched_yield();  // socket buffer full: let the receiver drain
+        }
+      }
+      counters.tx_pkts += (uint64_t)done;
+      counters.tx_dropped += (uint64_t)(k - done);
+      sent_total += done;
     }
-    counters.tx_dropped++;
-    return 0;
+    return sent_total;
   }
   int tx_burst(const SrpcPkt* pkts, int n) override {
-    int s = 0;
-    for (int i = 0; i < n; i++) {
-      s += send_one(pkts[i].hdr, tx_arena_->host_ptr(pkts[i].slot), pkts[i].len);
-      tx_arena_->release(pkts[i].slot);
-    }
+    const int s = send_many(n, [&](int i, const p2p_rpc_hdr** h, const uint8_t** p, uint32_t* len) {
+      *h = pkts[i].hdr;
+      *p = tx_arena_->host_ptr(pkts[i].slot);
+      *len = pkts[i].len;
+    });
+    for (int i = 0; i < n; i++) tx_arena_->release(pkts[i].slot);
     return s;
   }
   int tx_copy(const p2p_rpc_hdr* hdrs, const uint8_t* const* payloads, const uint32_t* lens, int n) override {
-    int s = 0;
-    for (int i = 0; i < n; i++) s += send_one(&hdrs[i], payloads[i], lens[i]);
-    return s;
+    return send_many(n, [&](int i, const p2p_rpc_hdr** h, const uint8_t** p, uint32_t* len) {
+      *h = &hdrs[i];
+      *p = payloads[i];
+      *len = lens[i];
+    });
   }
   bool tx_arena_info(TxArenaInfo* out) const override {
     out->host_base = tx_arena_->host_base();
