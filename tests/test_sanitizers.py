@@ -34,3 +34,24 @@ def test_host_core_is_clean_under_sanitizers(tmp_path, flags, name):
     out = r.stdout + r.stderr
     assert r.returncode == 0 and "SELFTEST OK" in out, out[-4000:]
     assert "ThreadSanitizer" not in out and "AddressSanitizer" not in out and "runtime error" not in out, out[-4000:]
+
+
+def test_host_core_builds_and_reports_in_profile_mode(tmp_path):
+    """-DPROFILE_MODE compiles the per-stage timers (and NVTX ranges where the header is present) into the host core;
+    the engines print their [N, Mean, p90, p95, p99, min, max] lines at teardown."""
+    cxx = shutil.which("g++") or shutil.which(os.environ.get("CXX", "g++"))
+    if not cxx:
+        pytest.skip("no C++ compiler")
+    exe = tmp_path / "selftest_prof"
+    cmd = [cxx, "-std=c++17", "-O1", "-DPROFILE_MODE", "-pthread", "-I", os.path.join(ROOT, "splitrpc_b200", "csrc"), SRC, "-o",
+           str(exe), "-lrt"]
+    cuda_inc = "/usr/local/cuda/include"
+    if os.path.isdir(cuda_inc):
+        cmd[1:1] = ["-I", cuda_inc]  # nvtx3 headers, when present
+    b = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    assert b.returncode == 0, b.stderr[-3000:]
+    r = subprocess.run([str(exe), str(tmp_path)], capture_output=True, text=True, timeout=600)
+    out = r.stdout + r.stderr
+    assert r.returncode == 0 and "SELFTEST OK" in out, out[-3000:]
+    lines = [l for l in out.splitlines() if l.startswith("Gather stats(ns) [N, Mean, p90, p95, p99, min, max]:")]
+    assert lines and any(int(l.split(":")[1].split(",")[0]) > 0 for l in lines), out[-3000:]
