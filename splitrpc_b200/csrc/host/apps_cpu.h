@@ -85,18 +85,24 @@ static inline int mm_dim_from_req(size_t req_size) {
 }
 static inline int cpu_mm_run(AppCtx* c) {
   CpuAppState* s = cpu_state(c);
-  int d = s->dim ? s->dim : mm_dim_from_req(s->req_size);
-  for (int b = 0; b < c->curr_batch_size; b++) {
-    const float* A = reinterpret_cast<const float*>(c->h_stub->req + (size_t)b * s->req_size);
+  const int d = s->dim ? s->dim : mm_dim_from_req(s->req_size);
+  const uint8_t* req = c->h_stub->req;
+  uint8_t* resp = c->h_stub->resp;
+  s->batch_pool()->run(c->curr_batch_size, [s, d, req, resp](int b) {
+    const float* A = reinterpret_cast<const float*>(req + (size_t)b * s->req_size);
     const float* B = A + (size_t)d * d;
-    float* C = reinterpret_cast<float*>(c->h_stub->resp + (size_t)b * s->resp_size);
-    for (int i = 0; i < d; i++)
-      for (int j = 0; j < d; j++) {
-        float acc = 0.f;
-        for (int k = 0; k < d; k++) acc += A[i * d + k] * B[k * d + j];
-        C[i * d + j] = acc;
+    float* C = reinterpret_cast<float*>(resp + (size_t)b * s->resp_size);
+    // row of C += A[i][k] * row k of B: the inner loop runs along contiguous memory
+    for (int i = 0; i < d; i++) {
+      float* ci = C + (size_t)i * d;
+      for (int j = 0; j < d; j++) ci[j] = 0.f;
+      for (int k = 0; k < d; k++) {
+        const float a = A[(size_t)i * d + k];
+        const float* bk = B + (size_t)k * d;
+        for (int j = 0; j < d; j++) ci[j] += a * bk[j];
       }
-  }
+    }
+  });
   return 1;
 }
 
@@ -334,9 +340,11 @@ static inline void cpu_lstm_forward(const std::vector<std::vector<float>>& w, in
 static inline int cpu_lstm_run(AppCtx* c) {
   CpuAppState* s = cpu_state(c);
   const int H = 256, steps = 8, layers = 8;
-  for (int b = 0; b < c->curr_batch_size; b++)
-    cpu_lstm_forward(s->weights, layers, steps, H, 0.0f,
-                     reinterpret_cast<const float*>(c->h_stub->req + (size_t)b * s->req_size),
-                     reinterpret_cast<float*>(c->h_stub->resp + (size_t)b * s->resp_size));
+  const uint8_t* req = c->h_stub->req;
+  uint8_t* resp = c->h_stub->resp;
+  s->batch_pool()->run(c->curr_batch_size, [s, req, resp](int b) {
+    cpu_lstm_forward(s->weights, layers, steps, H, 0.0f, reinterpret_cast<const float*>(req + (size_t)b * s->req_size),
+                     reinterpret_cast<float*>(resp + (size_t)b * s->resp_size));
+  });
   return 1;
 }
