@@ -1043,6 +1043,25 @@ PYBIND11_MODULE(_C, m) {
       d["mapped_pool"] = gp != nullptr && BufItemPool<g_params>::get_dev_ptr(gp) != nullptr;
       if (gp) BufItemPool<g_params>::delete_buf_item_pool(gp, device);
     }
+    // helper names of the original
+    {
+      const uint64_t abs_ns = getAbsCurNs();
+      d["helper_names"] = get_rpc_mtu() == rpc_mtu() && is_zerocopy_mode() == (int16_t)get_zerocopy_mode() && !getBasePath().empty() &&
+                          !getDatasetBasePath().empty() && abs_ns > 1600000000ull * 1000000000ull && getCurTsAsString().size() >= 19;
+      P2pRpcAppRrPool slots(4, -1, 64, 32);
+      P2pRpcAppRr* r = slots.get_next();
+      r->set_dummy_input_on_gpu();
+      r->set_dummy_output_on_gpu();
+      uint32_t in0 = 0, out0 = 7;
+      std::memcpy(&in0, r->h_stub->req + 60, 4);
+      std::memcpy(&out0, r->h_stub->resp + 28, 4);
+      d["slot_dummy_fill"] = in0 == 1u && out0 == 0u && slots.rr_mem_pool->get_state_addr_range() == (void*)slots.rr_mem_pool->get_doorbells_host();
+      P2pRpcRRPool pool(4);
+      pool.setup_and_init_rr_pool(nullptr, 128);
+      P2pRpcRr* any = nullptr;
+      d["rr_pool_names"] = pool.get_rr_pool_container().size() == 4 && pool.get_pool_size() == 4 && pool.consume_rx_ready_rr() == nullptr &&
+                           pool.consume_tx_ready_rr() == nullptr && pool.get_next_rx_ready_rr(&any) == 0;
+    }
     // first-generation record + pool
     p2p_rpc_conn_info* conn = initialize_src_conn_info("b8:ce:f6:cc:6a:52,192.168.25.1,50051");
     {

@@ -18,7 +18,10 @@
 #include <unistd.h>
 
 #include <climits>
+#include <cstdio>
+#include <cstring>
 #include <numeric>
+#include <vector>
 
 #include "config_utils.h"
 
@@ -504,6 +507,7 @@ class P2pRpcAppRrMemPool {
   size_t get_resp_addr_pool_size() const { return resp_.capacity; }
   bool is_double_mapped() const { return req_.double_mapped && resp_.double_mapped; }
   volatile uint32_t* get_doorbells_host() const { return h_doorbells_; }
+  void* get_state_addr_range() const { return (void*)h_doorbells_; }  // the original's name for the same range
   volatile uint32_t* get_doorbells_device() const { return d_doorbells_; }
   SrpcSlotDesc* get_slot_desc(int slot) const { return (SrpcSlotDesc*)(h_desc_ + (size_t)slot * srpc_desc_stride(req_size_)); }
   uint32_t desc_per_slot() const { return srpc_desc_per_slot(req_size_); }
@@ -529,6 +533,45 @@ class P2pRpcAppRr {
   void print_app_rr_info() const {
     std::printf("app_rr %p idx=%d req=%p resp=%p state=%u\n", (const void*)this, rr_idx, (void*)h_stub->req,
                 (void*)h_stub->resp, h_state ? *h_state : 0u);
+  }
+
+  // Debugging aids with the original's names (reference src/p2p_rpc_app_rr.h:49-79): fill the slot's request with
+  // 32-bit ones / its response with zeros, and print the first words of either as floats and as integers.  The
+  // buffers may be device memory: the bytes travel through a host staging copy on the default stream.
+  int device_id = -1;  // set by the pool; < 0: the rings are host memory
+  void set_dummy_input_on_gpu() { fill_words(h_stub->req, req_size, 1u); }
+  void set_dummy_output_on_gpu() { fill_words(h_stub->resp, resp_size, 0u); }
+  void dump_input_on_gpu(size_t max_words = 16) const { dump_words("Input", h_stub->req, req_size, max_words); }
+  void dump_output_on_gpu(size_t max_words = 16) const { dump_words("Output", h_stub->resp, resp_size, max_words); }
+
+ private:
+  void fill_words(uint8_t* p, size_t bytes, uint32_t value) {
+    std::vector<uint32_t> host(bytes / 4, value);
+    copy_bytes(p, host.data(), host.size() * 4, true);
+  }
+  void dump_words(const char* what, const uint8_t* p, size_t bytes, size_t max_words) const {
+    const size_t n = bytes / 4 < max_words ? bytes / 4 : max_words;
+    std::vector<uint32_t> host(n);
+    const_cast<P2pRpcAppRr*>(this)->copy_bytes(host.data(), p, n * 4, false);
+    std::printf("%s: app_rr %p idx=%d at %p:", what, (const void*)this, rr_idx, (const void*)p);
+    for (size_t i = 0; i < n; i++) {
+      float f;
+      std::memcpy(&f, &host[i], 4);
+      std::printf(" %g(%u)", f, host[i]);
+    }
+    std::printf("\n");
+  }
+  // to_slot: host -> slot memory, else slot memory -> host
+  void copy_bytes(void* dst, const void* src, size_t n, bool to_slot) {
+    (void)to_slot;
+    if (device_id < 0) {
+      std::memcpy(dst, src, n);
+      return;
+    }
+    const SrpcDeviceOps* ops = srpc_require_cuda("slot dump");
+    ops->set_device(device_id);
+    ops->memcpy_async(dst, src, n, nullptr);
+    ops->stream_sync(nullptr);
   }
 };
 
@@ -597,6 +640,7 @@ class P2pRpcAppRrPool {
       r.h_stub->req = nullptr;
       r.h_stub->resp = nullptr;
       r.rr_idx = i;
+      r.device_id = device_id_;
     }
   }
 

@@ -15,7 +15,10 @@
 
 #include <atomic>
 #include <memory>
+#include <chrono>
+#include <ctime>
 #include <mutex>
+#include <string>
 #include <thread>
 #include <unordered_map>
 #include <vector>
@@ -91,6 +94,29 @@ class BufItemPool {
     return it == table().end() ? nullptr : it->second.dev;
   }
 };
+
+// ------------------------------------------------------------------ helper names of the original
+// (reference src/utils/config_utils.h:34-40,83-96, src/utils/time_utils.h:42-47,72-78, src/p2p_rpc_app_rr_mem_pool.h:29)
+static inline std::string getBasePath() { return get_p2p_path(); }
+static inline std::string getDatasetBasePath() { return get_dataset_path(); }
+static inline size_t get_rpc_mtu() { return rpc_mtu(); }
+static inline int16_t is_zerocopy_mode() { return (int16_t)get_zerocopy_mode(); }
+// wall-clock time in ns with microsecond resolution (getCurNs is the monotonic clock)
+static inline uint64_t getAbsCurNs() {
+  return (uint64_t)std::chrono::duration_cast<std::chrono::microseconds>(std::chrono::system_clock::now().time_since_epoch()).count() *
+         1000ull;
+}
+static inline std::string getCurTsAsString() {
+  const std::time_t t = std::time(nullptr);
+  std::tm tm{};
+  localtime_r(&t, &tm);
+  char buf[64];
+  std::strftime(buf, sizeof(buf), "%d-%m-%Y %H-%M-%S", &tm);
+  return buf;
+}
+// The original keeps a second ring-memory class without the double mapping; here the double mapping is a property of
+// the ring allocation inside the one class (and absent where the platform cannot provide it).
+using P2pRpcAppRrSimpleMemPool = P2pRpcAppRrMemPool;
 
 // ------------------------------------------------------------------ first-generation record
 enum RR_STATUS : uint32_t { RR_V1_UNUSED = 0, RR_V1_INUSE = 1 };

@@ -226,6 +226,16 @@ class P2pRpcRRPool {
     P2pRpcRr* rr = nullptr;
     return rx_ready_.pop(rr) ? rr : nullptr;
   }
+  // The original's spellings of the two dequeues (reference src/p2p_rpc_rr_pool_ng.h:163-187) and of the record list.
+  P2pRpcRr* consume_rx_ready_rr() { return get_next_rx_ready_rr(); }
+  int get_next_rx_ready_rr(P2pRpcRr** next_rr) {
+    *next_rr = get_next_rx_ready_rr();
+    return *next_rr ? 1 : 0;
+  }
+  P2pRpcRr* consume_tx_ready_rr() { return get_next_tx_ready_rr(); }
+  std::vector<P2pRpcRr*>& get_rr_pool_container() { return all_; }
+  P2pRpcRr** get_rr_pool() { return all_.data(); }
+  int get_pool_size() const { return pool_size_; }
   void mark_tx_ready_rr(P2pRpcRr* rr) {
     rr->rr_state = RR_FINISH;
     while (!tx_ready_.push(rr)) cpu_relax();

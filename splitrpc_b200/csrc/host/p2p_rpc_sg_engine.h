@@ -257,6 +257,8 @@ class P2pRpcSgCpuEngine : public P2pRpcSgEngine {
     return rc;
   }
   int copy_list(const p2p_sk_buf* skb) override { return run(skb); }
+  // the original's name and return convention (1 = done; reference src/p2p_rpc_sg_engine.h:139-145)
+  int sg_on_cpu(p2p_sk_buf* skb) { return run(skb) == 0 ? 1 : 0; }
   const char* name() const override { return "cpu"; }
 };
 
