@@ -10,6 +10,7 @@
 #include "host/copy_path_runner.h"
 #include "host/dpdk_port.h"
 #include "host/loadgen.h"
+#include "host/loadgen_compat.h"
 #include "host/p2p_rpc_compat.h"
 #include "host/splitrpc_server.h"
 

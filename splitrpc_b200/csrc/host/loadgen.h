@@ -127,6 +127,24 @@ class StatsManager {
     if (it == metrics_.end()) it = metrics_.emplace(metric, new Measure<uint64_t>(metric)).first;
     it->second->add(value);
   }
+  // The experiment clock and the explicit spellings of the original (reference src/lib_loadgen/stats_factory.h:57-85,
+  // 118-123): a measurement may be declared before its first sample, raw samples can be fetched or dumped by name.
+  uint64_t expStartTimeNs = getCurNs(), expEndTimeNs = 0;
+  void startExp(uint64_t set_start = 0) {
+    expStartTimeNs = set_start ? set_start : getCurNs();
+    resetStats();
+  }
+  void endExp() {
+    expEndTimeNs = getCurNs();
+    trackStatInfo("exec_time_ns", (double)(expEndTimeNs - expStartTimeNs));
+  }
+  void addMeasurementType(const std::string& metric) {
+    if (metrics_.find(metric) == metrics_.end()) metrics_.emplace(metric, new Measure<uint64_t>(metric));
+  }
+  std::vector<uint64_t>& getRawMeasure(const std::string& metric) { return samples(metric); }
+  void dumpRawStats() {
+    for (auto& kv : metrics_) kv.second->dumpStatsToFile(exp_name_, out_dir_);
+  }
   void trackStatInfo(const std::string& k, const std::string& v) { info_str_[k] = v; }
   void trackStatInfo(const std::string& k, double v) { info_num_[k] = v; }
   void resetStats() {
@@ -453,6 +471,8 @@ class P2pRpcAppClient {
     exit_flag_.store(true, std::memory_order_release);
     if (listener_.joinable()) listener_.join();
   }
+  // Makes a CompleteReqListener() that runs on a thread of the caller's return.
+  void request_exit() { exit_flag_.store(true, std::memory_order_release); }
 
   // Waits (bounded) until every issued request was answered.
   bool drain() {

@@ -16,6 +16,7 @@
 #include "host/apps_cpu.h"
 #include "host/copy_path_runner.h"
 #include "host/loadgen.h"
+#include "host/loadgen_compat.h"
 #include "host/p2p_rpc_compat.h"
 #include "host/splitrpc_server.h"
 
@@ -226,6 +227,52 @@ void scenario_copy_path() {
   expect(!batcher.submit(req.data(), req.size(), resp.data()), "copy path: refused after stop");
 }
 
+// A driver written against the original's client interface: setters, CreateRequest / SchedRequest per call, the
+// listener on a thread of its own, PostProcessResponses into the caller's statistics object.
+void scenario_base_client() {
+  set_rpc_mtu(1024);
+  Link l = make_link(1024, 2048);
+  auto app = make_cpu_app(cpu_echo_run, 3000, 3000, 64, 4);
+  P2pRpcSgCpuEngine eng;
+  ServerConfig sc;
+  sc.req_size = sc.resp_size = 3000;
+  sc.server_mode = 2;
+  sc.max_batch = 4;
+  SplitRpcServer srv(l.server.get(), sc);
+  srv.add_replica(app.get(), &eng);
+  srv.start();
+  StatsManager stats("selftest_base_client", "/tmp");
+  stats.startExp();
+  TransportAppClient tc(&stats, l.client.get(), "");
+  BaseClient* cli = &tc;
+  cli->SetMaxRequests(60);
+  cli->SetWarmupRequests(10);
+  cli->SetMaxPayloadSize(3000, 3000);
+  cli->SetVerifyRun(1);
+  cli->SetReqRespCb(echo_fill, echo_check);
+  cli->SetClosedLoop();
+  cli->PreProcessRequests();
+  std::thread listener([cli] { cli->CompleteReqListener(); });
+  int issued = 0;
+  while (void* tag = cli->CreateRequest(nullptr)) {
+    cli->SchedRequest(tag);
+    issued++;
+    // at most four calls in flight
+    uint64_t t0 = getCurNs();
+    while ((int)tc.received() + 4 <= issued && getCurNs() - t0 < 5000000000ull) std::this_thread::yield();
+  }
+  uint64_t t0 = getCurNs();
+  while (tc.received() < 60 && getCurNs() - t0 < 5000000000ull) std::this_thread::yield();
+  cli->exit_client();
+  listener.join();
+  cli->PostProcessResponses();
+  stats.endExp();
+  srv.stop();
+  expect(issued == 60 && cli->n_r_sent == 60 && cli->n_r_recv == 60 && !cli->is_client_listening() && cli->isValidToken((void*)60) &&
+             !cli->isValidToken((void*)61) && stats.getRawMeasure("sojournTime").size() == 50 && tc.engine()->verify_failures() == 0,
+         "original client interface: 60 calls, 50 recorded");
+}
+
 // The helper threads that share a batch of a CPU app.
 void scenario_batch_pool() {
   CpuBatchPool pool(3);
@@ -282,6 +329,7 @@ int main(int argc, char** argv) {
   scenario_remote(dir + "/srpc_selftest_a.sock");
   scenario_pull(dir + "/srpc_selftest_c.sock");
   scenario_lost_peer(dir + "/srpc_selftest_b.sock");
+  scenario_base_client();
   scenario_copy_path();
   scenario_batch_pool();
   scenario_v1_app_server();
