@@ -20,7 +20,7 @@ class BaseClient {
   StatsManager* StatsCollector;
   uint64_t startTimeNs = 0, endTimeNs = 0;
   bool closedLoop = false;
-  volatile bool exit_flag = false;
+  std::atomic<bool> exit_flag{false};  // (a plain volatile flag in the original: a data race between the driver and the listener)
   bool verify_run = false;
   uint32_t maxRequests = UINT_MAX, n_r_warmup = 0;
   app_req_cb req_cb;
