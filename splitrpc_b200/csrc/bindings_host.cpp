@@ -1164,6 +1164,53 @@ PYBIND11_MODULE(_C, m) {
       d["udp_exhausts"] = taken == 4;
       set_rpc_mtu(old_mtu);
     }
+    // socket helpers of the kernel-UDP path: a 2500-byte request and a 40-byte response between two sockets
+    {
+      size_t old_mtu = rpc_mtu();
+      set_rpc_mtu(1024);
+      sockaddr_in a_srv{}, a_cli{};
+      a_srv.sin_family = a_cli.sin_family = AF_INET;
+      inet_pton(AF_INET, "127.0.0.1", &a_srv.sin_addr);
+      inet_pton(AF_INET, "127.0.0.1", &a_cli.sin_addr);
+      int s_srv = initUdpSock(&a_srv), s_cli = initUdpSock(&a_cli);
+      socklen_t sl = sizeof(a_srv);
+      getsockname(s_srv, (sockaddr*)&a_srv, &sl);
+      bool ok = s_srv >= 0 && s_cli >= 0;
+      UdpRrPool srv_pool(4), cli_pool(4);
+      srv_pool.setup_and_init_rr_pool(2500, 40);
+      cli_pool.setup_and_init_rr_pool(2500, 40);
+      UdpRpcHdr uh{};
+      uh.req_token = 4242;
+      UdpRr* call = cli_pool.get_rr(&uh);
+      seedGenerator(7);
+      for (size_t i = 0; i < 2500; i++) call->req_payload[i] = (uint8_t)uniformint(0, 255);
+      call->si_other = a_srv;
+      call->alloc_req_bufs();
+      call->req_to_bufs();
+      ok = ok && udp_rr_send_req(s_cli, call) >= 0;
+      UdpRr* got = nullptr;
+      for (int tries = 0; ok && !got && tries < 50; tries++) udp_rr_recv_req(s_srv, &got, &srv_pool);
+      ok = ok && got != nullptr && got->req_token == 4242;
+      if (ok) {
+        got->bufs_to_req();
+        ok = std::memcmp(got->req_payload, call->req_payload, 2500) == 0;
+        for (size_t i = 0; i < 40; i++) got->resp_payload[i] = (uint8_t)(i * 3);
+        got->alloc_resp_bufs();
+        got->resp_to_bufs();
+        ok = ok && udp_rr_send_resp(s_srv, got) >= 0;
+        UdpRr* back = nullptr;
+        for (int tries = 0; ok && !back && tries < 50; tries++) udp_rr_recv_resp(s_cli, &back, &cli_pool);
+        ok = ok && back == call;
+        if (ok) {
+          back->bufs_to_resp();
+          for (size_t i = 0; i < 40; i++) ok = ok && back->resp_payload[i] == (uint8_t)(i * 3);
+        }
+      }
+      d["udp_socket_helpers"] = ok;
+      if (s_srv >= 0) ::close(s_srv);
+      if (s_cli >= 0) ::close(s_cli);
+      set_rpc_mtu(old_mtu);
+    }
     return d;
   }, py::arg("device") = -1);
 

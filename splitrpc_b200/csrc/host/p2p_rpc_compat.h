@@ -12,6 +12,12 @@
 #pragma once
 
 #include <netinet/in.h>
+#include <unistd.h>
+#include <sys/time.h>
+#include <sys/socket.h>
+#include <arpa/inet.h>
+#include <limits>
+#include <random>
 
 #include <atomic>
 #include <memory>
@@ -459,6 +465,15 @@ class UdpRr {
   size_t bufs_to_resp() { return bufs_to_payload(resp_bufs, resp_payload, max_resp_size); }
   bool is_req_ready() const { return req_size == max_req_size; }
   bool is_resp_ready() const { return resp_size == max_resp_size; }
+  void rr_print_req_bufs() const { print_bufs("req", req_bufs); }
+  void rr_print_resp_bufs() const { print_bufs("resp", resp_bufs); }
+
+ private:
+  void print_bufs(const char* what, const p2p_bufs* b) const {
+    std::printf("UdpRr %p token %lu %s buffers: %u\n", (const void*)this, (unsigned long)req_token, what, (unsigned)b->num_items);
+    for (size_t i = 0; i < b->num_items; i++)
+      std::printf("  [%zu] %p, %zu bytes\n", i, (const void*)b->burst_items[i], (size_t)b->item_size[i]);
+  }
 };
 
 // Pool of socket-path records over one request arena and one response arena (its own, or the caller's: the original's
@@ -537,6 +552,15 @@ class UdpRrPool {
     return process_.pop(rr) ? rr : nullptr;
   }
   void mark_ready_rr(UdpRr* rr) { ready_.push(rr); }
+  // All bytes of the record are there: out of the by-token table and into the ready queue in one step.
+  void complete_rr(UdpRr* rr) {
+    {
+      std::lock_guard<std::mutex> g(mu_);
+      rr_cache_.erase(rr->req_token);
+    }
+    rr->rr_state = UDP_RR_READY;
+    ready_.push(rr);
+  }
   UdpRr* consume_ready_rr() {
     UdpRr* rr = nullptr;
     return ready_.pop(rr) ? rr : nullptr;
@@ -546,3 +570,140 @@ class UdpRrPool {
     return *next_rr ? 1 : 0;
   }
 };
+
+// ------------------------------------------------------------------ socket helpers of the kernel-UDP path
+// (reference src/transport/udp_rx_tx.h:15-100, src/transport/udp_transport.h:16-170).  A datagram is a UdpRpcHdr and up
+// to rpc_mtu() payload bytes.  The receive helpers take one datagram, file it under its token's record and hand out
+// a record once all of its bytes are there; unlike the original they drop a datagram when the pool has no free record
+// and they test a response for completeness with the response size.
+static inline size_t udp_rpc_max_mtu() { return rpc_mtu() + UDP_RPC_HEADER_LEN; }
+#define UDP_RPC_MAX_MTU (udp_rpc_max_mtu())
+
+// A bound datagram socket (2 MB buffers; with `timeout` a receive returns after 100 ms without data); -1 on failure.
+static inline int initUdpSock(sockaddr_in* si_me, bool timeout = true) {
+  int s = ::socket(AF_INET, SOCK_DGRAM, IPPROTO_UDP);
+  if (s < 0) return -1;
+  int sz = 2 << 20;
+  setsockopt(s, SOL_SOCKET, SO_RCVBUF, &sz, sizeof(sz));
+  setsockopt(s, SOL_SOCKET, SO_SNDBUF, &sz, sizeof(sz));
+  if (timeout) {
+    timeval tv{0, 100000};
+    setsockopt(s, SOL_SOCKET, SO_RCVTIMEO, &tv, sizeof(tv));
+  }
+  if (::bind(s, (sockaddr*)si_me, sizeof(*si_me)) != 0) {
+    ::close(s);
+    return -1;
+  }
+  return s;
+}
+// One datagram of at most `len` bytes; its length, or -1 when none arrived (time-out) or the call failed.
+static inline int getData(int udp_sock, sockaddr_in* si_other, void* data, size_t len) {
+  socklen_t slen = sizeof(*si_other);
+  const ssize_t r = ::recvfrom(udp_sock, data, len, 0, (sockaddr*)si_other, &slen);
+  return r < 0 ? -1 : (int)r;
+}
+// `len` bytes in datagrams of at most `seg_size` bytes.
+static inline void sendData(int udp_sock, sockaddr_in* si_other, void* out, size_t len, size_t seg_size) {
+  const uint8_t* p = (const uint8_t*)out;
+  while (len > 0) {
+    const size_t n = len < seg_size ? len : seg_size;
+    if (::sendto(udp_sock, p, n, 0, (sockaddr*)si_other, sizeof(*si_other)) < 0) return;
+    p += n;
+    len -= n;
+  }
+}
+static inline int udp_rr_send_req(int udp_sock, UdpRr* rr) {
+  for (size_t i = 0; i < rr->req_bufs->num_items; i++)
+    sendData(udp_sock, &rr->si_other, (void*)rr->req_bufs->burst_items[i], rr->req_bufs->item_size[i], UDP_RPC_MAX_MTU);
+  return (int)rr->req_size;
+}
+static inline int udp_rr_send_resp(int udp_sock, UdpRr* rr) {
+  for (size_t i = 0; i < rr->resp_bufs->num_items; i++)
+    sendData(udp_sock, &rr->si_other, (void*)rr->resp_bufs->burst_items[i], rr->resp_bufs->item_size[i], UDP_RPC_MAX_MTU);
+  return (int)rr->resp_size;
+}
+// Takes one datagram into its record; `as_resp` selects the response side.  The record owns the buffer from then on.
+static inline UdpRr* udp_rr_take_datagram(int udp_sock, UdpRrPool* rr_pool, bool as_resp) {
+  uint8_t* buf = new uint8_t[UDP_RPC_MAX_MTU];
+  sockaddr_in si_other{};
+  const int len = getData(udp_sock, &si_other, buf, UDP_RPC_MAX_MTU);
+  UdpRr* rr = nullptr;
+  if (len >= (int)UDP_RPC_HEADER_LEN) {
+    const UdpRpcHdr* h = (const UdpRpcHdr*)buf;
+    if (h->seq_num < MAX_BI_SIZE) rr = rr_pool->get_rr(h);
+    if (rr) {
+      rr->si_other = si_other;
+      if (as_resp) rr->rr_merge_resp_buf((uintptr_t)buf, (size_t)len, h->seq_num);
+      else rr->rr_merge_req_buf((uintptr_t)buf, (size_t)len, h->seq_num);
+      return rr;
+    }
+  }
+  delete[] buf;
+  return nullptr;
+}
+static inline int udp_rr_recv_req(int udp_sock, UdpRr** new_call_id, UdpRrPool* rr_pool) {
+  if (UdpRr* rr = udp_rr_take_datagram(udp_sock, rr_pool, false))
+    if (rr->is_req_ready()) rr_pool->complete_rr(rr);
+  *new_call_id = rr_pool->consume_ready_rr();
+  return *new_call_id ? 1 : 0;
+}
+static inline int udp_rr_recv_resp(int udp_sock, UdpRr** new_call_id, UdpRrPool* rr_pool) {
+  if (UdpRr* rr = udp_rr_take_datagram(udp_sock, rr_pool, true))
+    if (rr->is_resp_ready()) rr_pool->complete_rr(rr);
+  *new_call_id = rr_pool->consume_ready_rr();
+  return *new_call_id ? 1 : 0;
+}
+// Two-thread form: the listener files datagrams and queues complete requests for the processor, which flattens their
+// buffers into the request payload and marks them ready.  Both leave when `force_quit` is set.
+static inline void udp_rr_recv_req_listener(int udp_sock, UdpRrPool* rr_pool, const std::atomic<bool>& force_quit) {
+  while (!force_quit.load(std::memory_order_acquire))
+    if (UdpRr* rr = udp_rr_take_datagram(udp_sock, rr_pool, false))
+      if (rr->is_req_ready()) rr_pool->mark_process_rr(rr);
+}
+static inline void udp_rr_recv_req_processor(UdpRrPool* rr_pool, const std::atomic<bool>& force_quit) {
+  IdleBackoff backoff;
+  while (!force_quit.load(std::memory_order_acquire)) {
+    UdpRr* rr = rr_pool->consume_process_rr();
+    if (!rr) {
+      backoff.empty();
+      continue;
+    }
+    backoff.busy();
+    rr->bufs_to_req();
+    rr->release_req_bufs();
+    rr_pool->mark_ready_rr(rr);
+  }
+}
+
+// ------------------------------------------------------------------ small utilities of the original
+// (reference src/utils/debug_utils.h:12-60, src/utils/random_utils.h:10-32)
+static inline void hexDump(const char* desc, const void* addr, int len) {
+  const unsigned char* pc = (const unsigned char*)addr;
+  if (desc) std::printf("%s:\n", desc);
+  for (int i = 0; i < len; i += 16) {
+    std::printf("  %04x ", i);
+    for (int j = 0; j < 16; j++) {
+      if (i + j < len) std::printf(" %02x", pc[i + j]);
+      else std::printf("   ");
+    }
+    std::printf("  ");
+    for (int j = 0; j < 16 && i + j < len; j++) std::printf("%c", pc[i + j] >= 0x20 && pc[i + j] <= 0x7e ? pc[i + j] : '.');
+    std::printf("\n");
+  }
+}
+inline std::mt19937_64& srpc_global_generator() {
+  static std::mt19937_64 g;
+  return g;
+}
+static inline void seedGenerator(unsigned int seed) { srpc_global_generator().seed(seed); }
+static inline void seedGeneratorRand() {
+  std::random_device rd;
+  srpc_global_generator().seed(rd());
+}
+static inline double uniform01() {
+  return std::generate_canonical<double, std::numeric_limits<double>::digits>(srpc_global_generator());
+}
+static inline int uniformint(int min, int max) {
+  std::uniform_int_distribution<int> dist(min, max);
+  return dist(srpc_global_generator());
+}
