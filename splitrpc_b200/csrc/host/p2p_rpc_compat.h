@@ -210,6 +210,20 @@ static inline void rr_print_bufs(const p2p_rpc_rr* rr) {
   print_bufs(rr->payload_bufs);
 }
 
+// Payload memory by device id, with the original's names (reference src/p2p_rpc_rr_pool.h:15-50): -1 host memory,
+// >= 0 memory that GPU addresses too (mapped pinned), anything else none.
+static inline uint8_t* alloc_cpu_mem(size_t mem_size) { return mem_size ? BufItemPool<uint8_t>::create_buf_item_pool((int)mem_size, -1) : nullptr; }
+static inline void free_cpu_mem(uint8_t* mem) {
+  if (mem) BufItemPool<uint8_t>::delete_buf_item_pool(mem);
+}
+static inline uint8_t* alloc_mem(size_t mem_size, int device_id) {
+  if (device_id < -1 || mem_size == 0) return nullptr;
+  return BufItemPool<uint8_t>::create_buf_item_pool((int)mem_size, device_id);
+}
+static inline void free_mem(uint8_t* mem, int device_id) {
+  if (mem && device_id >= -1) BufItemPool<uint8_t>::delete_buf_item_pool(mem);
+}
+
 namespace p2p_rpc_v1 {
 
 // Pool of first-generation records that also owns each record's request and response payload memory: host memory
@@ -221,9 +235,15 @@ class P2pRpcRRPool {
   std::vector<p2p_rpc_rr*> rr_pool_;
   std::mutex mu_;
 
-  static uint8_t* alloc_mem(size_t n, int dev) {
-    if (dev == -2 || n == 0) return nullptr;
-    return BufItemPool<uint8_t>::create_buf_item_pool((int)n, dev);
+  // A record with its own request and response memory on the named devices.
+  static p2p_rpc_rr* alloc_new_rr(const p2p_rpc_conn_info* src_conn_info, size_t req_size, size_t resp_size, int req_device_id = -2,
+                                  int resp_device_id = -2) {
+    p2p_rpc_rr* rr = rr_proto_alloc(src_conn_info, req_size, resp_size);
+    rr->req_payload = alloc_mem(req_size, req_device_id);
+    rr->resp_payload = alloc_mem(resp_size, resp_device_id);
+    rr->req_device_id = req_device_id;
+    rr->resp_device_id = resp_device_id;
+    return rr;
   }
 
  public:
@@ -237,13 +257,11 @@ class P2pRpcRRPool {
   }
   int get_pool_size() const { return pool_size_; }
   std::vector<p2p_rpc_rr*>& get_rr_pool() { return rr_pool_; }
+  std::vector<p2p_rpc_rr*>& get_rr_pool_container() { return rr_pool_; }
 
   void setup_and_init_rr_pool(const p2p_rpc_conn_info* src_conn_info, size_t req_size, size_t resp_size, int device_id) {
     for (int i = 0; i < pool_size_; i++) {
-      p2p_rpc_rr* rr = rr_proto_alloc(src_conn_info, req_size, resp_size);
-      rr->req_payload = alloc_mem(req_size, device_id);
-      rr->resp_payload = alloc_mem(resp_size, device_id);
-      rr->req_device_id = rr->resp_device_id = device_id;
+      p2p_rpc_rr* rr = alloc_new_rr(src_conn_info, req_size, resp_size, device_id, device_id);
       rr_pool_.push_back(rr);
       free_.push(rr);
     }
