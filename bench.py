@@ -74,7 +74,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.FIELDS}",
-                                          "--format=csv,noheader,nounits", "-lms", "200"], stdout=subprocess.PIPE,
+                                          "--format=csv,noheader,nounits", "-lms", "50"], stdout=subprocess.PIPE,
                                          stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
@@ -87,7 +87,7 @@ class ClockSampler:
     def mark(self) -> float:
         return time.perf_counter()
 
-    def summary(self, t_from: float | None = None, t_to: float | None = None) -> dict:
+    def summary(self, t_from: float | None = None, t_to: float | None = None, _widened: bool = False) -> dict:
         sm, mx, pw, reasons = [], 0, [], set()
         names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
         for t, s in list(self.samples):
@@ -102,8 +102,14 @@ class ClockSampler:
                         reasons.add(n)
             except (ValueError, IndexError):
                 continue
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx or None, "reasons": sorted(reasons),
-                "samples": len(sm), "power_w_max": max(pw) if pw else None}
+        out = {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx or None, "reasons": sorted(reasons),
+               "samples": len(sm), "power_w_max": max(pw) if pw else None}
+        if not sm and t_from is not None and t_to is not None and not _widened:
+            # a timed region shorter than the sampling period: the samples just around it (the GPU is under the same
+            # load right before, in the warm-up steps, and right after)
+            out = self.summary(t_from - 0.3, t_to + 0.3, _widened=True)
+            out["window"] = "within 0.3 s of the timed region (none fell inside it)"
+        return out
 
     def stop(self) -> dict:
         if self.proc:
