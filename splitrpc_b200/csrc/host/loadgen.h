@@ -306,6 +306,7 @@ class P2pRpcAppClient {
   std::vector<std::vector<uint8_t>> resp_bufs_;      // reassembly buffer per token
   std::atomic<uint64_t> n_sent_{0}, n_recv_{0}, n_bad_token_{0}, n_verify_fail_{0}, next_idx_{0};
   std::atomic<bool> exit_flag_{false};
+  std::atomic<int> issuing_{0};  // send_next() calls between taking a call number and having sent it
   std::thread listener_;
   app_req_cb req_cb_;
   app_resp_cb resp_cb_;
@@ -411,15 +412,26 @@ class P2pRpcAppClient {
     return true;
   }
 
+  // Takes the next call number and sends it.  `issuing_` covers the gap between taking the last number and counting
+  // the call as sent: without it drain() could see "all numbers taken, as many replies as sends" in that gap and end the
+  // run one reply short.
   bool send_next() {
+    issuing_.fetch_add(1);
     uint64_t idx = next_idx_.fetch_add(1);
-    if (idx >= cfg_.total_requests) return false;
-    uint64_t t0 = getCurNs();
-    while (!SchedRequest(idx)) {
-      if (exit_flag_.load() || getCurNs() - t0 > cfg_.drain_timeout_ns) return false;
-      std::this_thread::yield();
+    bool sent = false;
+    if (idx < cfg_.total_requests) {
+      uint64_t t0 = getCurNs();
+      sent = true;
+      while (!SchedRequest(idx)) {
+        if (exit_flag_.load() || getCurNs() - t0 > cfg_.drain_timeout_ns) {
+          sent = false;
+          break;
+        }
+        std::this_thread::yield();
+      }
     }
-    return true;
+    issuing_.fetch_sub(1);
+    return sent;
   }
 
   // Receives reply fragments, reassembles by token, stamps completion; in closed
@@ -477,7 +489,7 @@ class P2pRpcAppClient {
   // Waits (bounded) until every issued request was answered.
   bool drain() {
     uint64_t t0 = getCurNs();
-    while (!(next_idx_.load() >= cfg_.total_requests && n_recv_.load() >= n_sent_.load())) {
+    while (!(next_idx_.load() >= cfg_.total_requests && issuing_.load() == 0 && n_recv_.load() >= n_sent_.load())) {
       if (getCurNs() - t0 > cfg_.drain_timeout_ns) return false;
       std::this_thread::sleep_for(std::chrono::microseconds(50));
     }
