@@ -90,3 +90,24 @@ def test_load_generator_client_type_1(C, capsys):
                           "--total", "40", "--warmup", "10", "--outstanding", "2", "--client-type", "1"])
     out = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
     assert rc == 0 and out["ok"] and out["received"] == 40
+
+
+def test_load_generator_main_reads_the_original_environment(C, capsys, monkeypatch):
+    """No flags at all: server address, sizes, counts, loop type and client type come from the P2P_RPC_* variables."""
+    import json
+
+    from splitrpc_b200.utils import client
+
+    app = C.make_app("echo", -1, 512, 512, [], 64, 1, 2)
+    with GrpcCopyPathServer(app, 2) as srv:
+        host, port = srv.address.rsplit(":", 1)
+        env = {"P2P_RPC_URI": f"00:00:00:00:00:01,127.0.0.1,0,00:00:00:00:00:02,{host},{port}", "P2P_RPC_APP": "echo",
+               "P2P_RPC_REQ_SIZE": "512", "P2P_RPC_RESP_SIZE": "512", "P2P_RPC_BENCH_TOTAL_REQUESTS": "30", "P2P_RPC_REQ_GEN_TYPE": "0",
+               "P2P_RPC_BENCH_ARR_RATE": "3", "P2P_RPC_CLIENT_TYPE": "1", "P2P_RPC_CLIENT_VERIFY_RUN": "1"}
+        for k, v in env.items():
+            monkeypatch.setenv(k, v)
+        monkeypatch.delenv("P2P_RPC_NUM_WARMUP", raising=False)
+        rc = client.main([])
+    out = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert rc == 0 and out["ok"] and out["received"] == 30  # 3 warm-up calls (10 %) come on top
+    assert srv.calls == 33
