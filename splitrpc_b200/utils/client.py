@@ -31,6 +31,7 @@ def main(argv=None) -> int:
     # the total), P2P_RPC_REQ_GEN_TYPE (0 closed loop, 1 open loop), P2P_RPC_BENCH_ARR_RATE (open loop: requests per
     # second; closed loop: requests in flight), P2P_RPC_ARR_RATE_COV, P2P_RPC_N_GEN_THR, P2P_RPC_CLIENT_TYPE,
     # P2P_RPC_CLIENT_VERIFY_RUN, P2P_RPC_BENCH_EXP_NAME, P2P_RPC_DUMP_RAW_STATS, P2P_RPC_MTU, P2P_RPC_RANDOM_SEED.
+    # (P2P_RPC_N_LISTENER_THR is accepted and has no effect: one listener thread reassembles all replies.)
     uri_env = [f.strip() for f in os.environ.get("P2P_RPC_URI", "").split(",")]
     uri_ok = len(uri_env) == 6
     total_d = _env("P2P_RPC_BENCH_TOTAL_REQUESTS", 1000)
