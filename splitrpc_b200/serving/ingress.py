@@ -17,6 +17,7 @@ Prints one JSON line of counters on exit.
 from __future__ import annotations
 
 import argparse
+import os
 import json
 import math
 import signal
@@ -28,22 +29,30 @@ from .apps import BUILTIN, build_model, make_builtin, sizes
 FUNC_ID = 1234
 
 
+def _env(name: str, default, cast=None):
+    """Default of a flag from the original's environment variable of that meaning (reference src/utils/config_utils.h)."""
+    v = os.environ.get(name)
+    if v is None or v == "":
+        return default
+    return (cast or type(default))(v)
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
-    ap.add_argument("--app", required=True)
-    ap.add_argument("--device", type=int, default=0, help="device of the local replica and of the gather kernels; -1 = CPU")
+    ap.add_argument("--app", default=os.environ.get("P2P_RPC_APP"), required="P2P_RPC_APP" not in os.environ)
+    ap.add_argument("--device", type=int, default=_env("P2P_RPC_CUDA_DEVICE_ID", 0), help="device of the local replica and of the gather kernels; -1 = CPU")
     ap.add_argument("--no-local", action="store_true", help="serve no replica in this process (proxy only)")
     ap.add_argument("--ip", default="0.0.0.0")
     ap.add_argument("--port", type=int, default=50051, help="UDP port to listen on (0 = any; the bound port is printed)")
     ap.add_argument("--replica", action="append", default=[], help="control socket of a replica process (repeatable)")
     ap.add_argument("--pull", action="store_true", help="remote replicas fetch their requests themselves")
-    ap.add_argument("--mode", type=int, default=2)
-    ap.add_argument("--max-batch", type=int, default=64)
+    ap.add_argument("--mode", type=int, default=_env("P2P_RPC_SERVER_MODE", 2))
+    ap.add_argument("--max-batch", type=int, default=_env("P2P_RPC_ORT_BATCH_SIZE", 64))
     ap.add_argument("--pool", type=int, default=256)
     ap.add_argument("--outstanding", type=int, default=None, help="requests in flight to size the arenas for")
-    ap.add_argument("--req-size", type=int, default=None)
-    ap.add_argument("--resp-size", type=int, default=None)
-    ap.add_argument("--mtu", type=int, default=8192)
+    ap.add_argument("--req-size", type=int, default=_env("P2P_RPC_REQ_SIZE", None, int))
+    ap.add_argument("--resp-size", type=int, default=_env("P2P_RPC_RESP_SIZE", None, int))
+    ap.add_argument("--mtu", type=int, default=_env("P2P_RPC_MTU", 8192))
     ap.add_argument("--steer", type=int, default=1, help="0 round robin in runs of max-batch, 1 least outstanding")
     ap.add_argument("--func-id", type=int, default=FUNC_ID)
     ap.add_argument("--seconds", type=float, default=0.0)

@@ -11,6 +11,7 @@ descriptors over a Unix socket in place of RDMA region keys.  Prints one JSON li
 from __future__ import annotations
 
 import argparse
+import os
 import json
 import signal
 import time
@@ -21,17 +22,25 @@ from .apps import BUILTIN, build_model, make_builtin, sizes
 FUNC_ID = 1234
 
 
+def _env(name: str, default, cast=None):
+    """Default of a flag from the original's environment variable of that meaning (reference src/utils/config_utils.h)."""
+    v = os.environ.get(name)
+    if v is None or v == "":
+        return default
+    return (cast or type(default))(v)
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
-    ap.add_argument("--app", required=True, help=f"model ({'resnet50, bert_base'}) or built-in app ({', '.join(sorted(BUILTIN))})")
-    ap.add_argument("--device", type=int, default=0, help="GPU index, -1 = CPU device (built-in apps only)")
+    ap.add_argument("--app", default=os.environ.get("P2P_RPC_APP"), required="P2P_RPC_APP" not in os.environ, help=f"model ({'resnet50, bert_base'}) or built-in app ({', '.join(sorted(BUILTIN))})")
+    ap.add_argument("--device", type=int, default=_env("P2P_RPC_CUDA_DEVICE_ID", 0), help="GPU index, -1 = CPU device (built-in apps only)")
     ap.add_argument("--path", required=True, help="Unix socket path of the control channel")
-    ap.add_argument("--mode", type=int, default=2, help="worker: 0 fixed batch, 1 stream armed, 2 dynamic batching")
-    ap.add_argument("--max-batch", type=int, default=64)
+    ap.add_argument("--mode", type=int, default=_env("P2P_RPC_SERVER_MODE", 2), help="worker: 0 fixed batch, 1 stream armed, 2 dynamic batching")
+    ap.add_argument("--max-batch", type=int, default=_env("P2P_RPC_ORT_BATCH_SIZE", 64))
     ap.add_argument("--pool", type=int, default=256, help="slots of the request / response rings")
-    ap.add_argument("--req-size", type=int, default=None)
-    ap.add_argument("--resp-size", type=int, default=None)
-    ap.add_argument("--mtu", type=int, default=8192)
+    ap.add_argument("--req-size", type=int, default=_env("P2P_RPC_REQ_SIZE", None, int))
+    ap.add_argument("--resp-size", type=int, default=_env("P2P_RPC_RESP_SIZE", None, int))
+    ap.add_argument("--mtu", type=int, default=_env("P2P_RPC_MTU", 8192))
     ap.add_argument("--func-id", type=int, default=FUNC_ID)
     ap.add_argument("--seconds", type=float, default=0.0, help="serve this long, 0 = until SIGINT / SIGTERM")
     args = ap.parse_args(argv)

@@ -248,7 +248,7 @@ def main(argv=None) -> int:
         from .. import _C
 
         name, device = os.environ.get("P2P_RPC_APP", "echo"), _env("P2P_RPC_CUDA_DEVICE_ID", -1)
-        batch = _env("P2P_RPC_MAX_BATCH_SIZE", 1)
+        batch = _env("P2P_RPC_ORT_BATCH_SIZE", _env("P2P_RPC_MAX_BATCH_SIZE", 1))  # the original's name first
         app = _C.make_app(name, device, req, resp, [], max(64, batch), 1, batch)
         srv = GrpcCopyPathServer(app, batch, uri).start()
         print(f"copy-path server for {name} on {srv.address}, batches of up to {batch}", flush=True)
