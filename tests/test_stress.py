@@ -93,3 +93,70 @@ def test_servers_stopped_idle_after_traffic_and_mid_run(C):
             assert time.time() - t0 < 5.0, (it, kind, mode)
     finally:
         C.set_rpc_mtu(8192)
+
+
+def _replica_proc(path, app_name, req, resp, mode, max_batch, mtu, ready, stop):
+    from splitrpc_b200 import _C as C
+
+    C.set_rpc_mtu(mtu)
+    app = C.make_app(app_name, -1, req, resp, [], 64, 1, max_batch, "cpu")
+    srv = C.BatchedServer(app, path, func_id=77, server_mode=mode, max_batch=max_batch)
+    srv.start()
+    ready.set()
+    while not stop.is_set():
+        time.sleep(0.005)
+    srv.stop()
+
+
+def test_random_single_ingress_setups_across_processes(C, tmp_path):
+    """Replicas in child processes (one or two, any worker mode), fed by push or by pull, with or without a local
+    replica beside them, payloads copied or handed over by reference: every call is answered once and correctly."""
+    import multiprocessing as mp
+
+    ctx = mp.get_context("spawn")
+    rnd = random.Random(11)
+    try:
+        for it in range(8):
+            mtu = rnd.choice([1024, 4096])
+            appname = rnd.choice(["echo", "vec_add"])
+            req = rnd.randint(1, 20000)
+            resp = req if appname == "vec_add" else rnd.randint(1, min(req, 6000))
+            mode = rnd.choice([0, 1, 2])
+            batch = rnd.choice([1, 2, 4]) if mode == 2 else 1
+            pull, n_rep, local = rnd.choice([False, True]), rnd.choice([1, 2]), rnd.choice([False, True])
+            outstanding, total = rnd.randint(1, 12), 60
+            procs = []
+            for r in range(n_rep):
+                path = str(tmp_path / f"s{it}_{r}.sock")
+                ready, stop = ctx.Event(), ctx.Event()
+                p = ctx.Process(target=_replica_proc, args=(path, appname, req, resp, mode, batch, mtu, ready, stop), daemon=True)
+                p.start()
+                assert ready.wait(60), "replica process did not come up"
+                procs.append((p, path, stop))
+            try:
+                C.set_rpc_mtu(mtu)
+                nfr = -(-req // mtu) + -(-resp // mtu)
+                sp, cp = C.make_loopback_pair(mtu, max(2048, 4 * outstanding * nfr), "shm")
+                srv = C.Server(sp, req_size=req, resp_size=resp, server_mode=2, max_batch=batch, steer_policy=rnd.choice([0, 1]),
+                               reassembly_timeout_ns=50_000_000)
+                if local:
+                    srv.add_replica(C.make_app(appname, -1, req, resp, [], 64, 1, batch, "cpu"))
+                for _, path, _ in procs:
+                    srv.add_remote_replica(path, func_id=77, ingress_device=-1, pull=pull)
+                srv.start()
+                cli = C.Client(cp, req_size=req, resp_size=resp, total=total, warmup=0, payload=appname, verify=True,
+                               drain_timeout_ns=10_000_000_000, send_by_reference=rnd.choice([False, True]) if pull else False)
+                ok = cli.run_closed_loop(outstanding)
+                st = srv.stats()
+                srv.stop()
+                srv.release_remotes()
+                cfg = dict(it=it, mtu=mtu, app=appname, req=req, resp=resp, mode=mode, batch=batch, pull=pull, n_rep=n_rep, local=local)
+                assert ok and cli.received == total and cli.verify_failures == 0 and cli.bad_tokens == 0 and st["sg_errors"] == 0, (cfg, st)
+                del srv
+            finally:
+                for p, _, stop in procs:
+                    stop.set()
+                for p, _, _ in procs:
+                    p.join(10)
+    finally:
+        C.set_rpc_mtu(8192)
