@@ -19,6 +19,7 @@
 #include "host/loadgen_compat.h"
 #include "host/p2p_rpc_compat.h"
 #include "host/splitrpc_server.h"
+#include "host/transport_rr_api.h"
 
 // The CUDA half is absent from this build.
 extern "C" const SrpcDeviceOps* srpc_cuda_ops() { return nullptr; }
@@ -227,6 +228,52 @@ void scenario_copy_path() {
   expect(!batcher.submit(req.data(), req.size(), resp.data()), "copy path: refused after stop");
 }
 
+// A serve loop written against the original's record-level transport calls (one request at a time): receive a
+// complete request, flatten it, give the received packets back, take transmit buffers, write the reply (the request's
+// first bytes, each plus one), set the headers from the caller's connection, send.
+void scenario_record_api() {
+  set_rpc_mtu(1024);
+  Link l = make_link(1024, 2048);
+  const size_t req = 2500, resp = 1500;
+  p2p_rpc_conn_info* server_conn = initialize_src_conn_info("b8:ce:f6:cc:6a:52,192.168.25.1,50051");
+  P2pRpcRRPool pool(63);
+  pool.setup_and_init_rr_pool(server_conn, req);
+  std::atomic<bool> cancel{false};
+  std::atomic<int> served{0};
+  Transport* port = l.server.get();
+  std::thread server([&] {
+    std::vector<uint8_t> flat(req);
+    P2pRpcRr* rr = nullptr;
+    while (rr_recv_sync(port, &rr, pool, cancel)) {
+      gather_payload_on_cpu(rr->payload_bufs, flat.data());
+      rr_release_mbufs(port, rr);
+      while (rr_alloc_mbufs(port, rr, resp) == 0 && !cancel.load()) std::this_thread::yield();
+      size_t off = 0;
+      for (uint16_t i = 0; i < rr->payload_bufs->num_items; i++) {
+        uint8_t* dst = port->tx_host_ptr(SrpcPkt{nullptr, (uint8_t*)rr->payload_bufs->burst_items[i], 0, 0});
+        for (size_t k = 0; k < rr->payload_bufs->item_size[i]; k++) dst[k] = (uint8_t)(flat[off + k] + 1);
+        off += rr->payload_bufs->item_size[i];
+      }
+      rr_set_hdr(&rr->_client_conn_info, rr, resp);
+      if (rr_send(port, rr, pool)) served++;
+    }
+  });
+  ClientConfig cc;
+  cc.req_size = req;
+  cc.resp_size = resp;
+  cc.total_requests = 80;
+  cc.num_warmup = 0;
+  cc.verify = true;
+  P2pRpcAppClient cli(l.client.get(), cc, vec_add_fill, [](const uint8_t* rq, const uint8_t* rs, size_t n) { return vec_add_check(rq, rs, n); });
+  cli.PreProcessRequests();
+  bool ok = cli.run_closed_loop(5);
+  cancel.store(true);
+  server.join();
+  release_conn_info(server_conn);
+  expect(ok && cli.received() == 80 && cli.verify_failures() == 0 && served.load() == 80 && pool.num_partial() == 0,
+         "serve loop on the original's record-level transport calls: 80 requests");
+}
+
 // A driver written against the original's client interface: setters, CreateRequest / SchedRequest per call, the
 // listener on a thread of its own, PostProcessResponses into the caller's statistics object.
 void scenario_base_client() {
@@ -329,6 +376,7 @@ int main(int argc, char** argv) {
   scenario_remote(dir + "/srpc_selftest_a.sock");
   scenario_pull(dir + "/srpc_selftest_c.sock");
   scenario_lost_peer(dir + "/srpc_selftest_b.sock");
+  scenario_record_api();
   scenario_base_client();
   scenario_copy_path();
   scenario_batch_pool();
