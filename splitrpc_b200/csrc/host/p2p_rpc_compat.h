@@ -352,6 +352,12 @@ class P2pRpcAppServer {
       if (t.joinable()) t.join();
     workers_.clear();
   }
+  // The worker loop of one instance on the caller's thread, until stop() (the original's name for it; start() runs one
+  // per instance on threads of its own).
+  void HandleRpcs(int instance = 0) {
+    stop_.store(false);
+    rpc_handler(instance);
+  }
   uint64_t num_serviced() const { return serviced_.load(); }
   uint64_t num_failed() const { return failed_.load(); }
 
